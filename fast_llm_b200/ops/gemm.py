@@ -1,0 +1,114 @@
+"""bf16 GEMMs on the tcgen05 tensor cores (`csrc/gemm_tcgen05.cu`) with a PyTorch path for CPU tensors.
+
+Three contractions cover training (parity with the dense paths of the reference's `fast_llm/functional/linear.py:27-107`,
+which calls cuBLAS through `torch.nn.functional.linear` / `addmm`):
+
+    matmul_nt(x, w)            y  = x @ w.T          forward            (both operands K-major)
+    matmul_nn(dy, w)           dx = dy @ w           input gradient     (B is MN-major in memory)
+    matmul_tn(dy, x, out=...)  dw (+)= dy.T @ x      weight gradient    (both operands MN-major), accumulates in place
+"""
+
+import os
+
+import torch
+
+from fast_llm_b200.ops import _lib
+
+_EPI_STORE_BF16, _EPI_STORE_F32, _EPI_ACC_F32, _EPI_ACC_BF16 = 0, 1, 2, 3
+
+
+def _backend() -> str:
+    return os.environ.get("FLB_GEMM", "tcgen05")
+
+
+def _native_ok(a: torch.Tensor, b: torch.Tensor) -> bool:
+    return (
+        a.is_cuda
+        and a.dtype == torch.bfloat16
+        and b.dtype == torch.bfloat16
+        and _backend() == "tcgen05"
+        and a.stride(-1) == 1
+        and b.stride(-1) == 1
+        and a.stride(0) % 8 == 0
+        and b.stride(0) % 8 == 0
+        and a.data_ptr() % 16 == 0
+        and b.data_ptr() % 16 == 0
+    )
+
+
+def gemm_raw(a, b, out, m, n, k, a_mn, b_mn, epilogue, block_n=0, max_ctas=0):
+    lib = _lib.get_lib()
+    _lib.check(
+        lib.flb_gemm_bf16(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k, a.stride(0), b.stride(0), out.stride(0),
+            int(a_mn), int(b_mn), epilogue, block_n, max_ctas, _lib.stream_ptr(),
+        ),
+        "flb_gemm_bf16",
+    )
+    _lib.count_launch()
+    return out
+
+
+def _epilogue(out: torch.Tensor, accumulate: bool) -> int:
+    if out.dtype == torch.bfloat16:
+        return _EPI_ACC_BF16 if accumulate else _EPI_STORE_BF16
+    assert out.dtype == torch.float32, out.dtype
+    return _EPI_ACC_F32 if accumulate else _EPI_STORE_F32
+
+
+def matmul_nt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False,
+              out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """x [M, K] @ w[N, K]^T -> [M, N]."""
+    m, k = x.shape
+    n = w.shape[0]
+    assert w.shape[1] == k, (x.shape, w.shape)
+    if out is None:
+        assert not accumulate
+        out = torch.empty(m, n, dtype=out_dtype or x.dtype, device=x.device)
+    if m == 0:
+        return out
+    if _native_ok(x, w) and out.stride(-1) == 1:
+        return gemm_raw(x, w, out, m, n, k, False, False, _epilogue(out, accumulate))
+    res = torch.matmul(x, w.t())
+    return out.add_(res) if accumulate else out.copy_(res)
+
+
+def matmul_nn(dy: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False,
+              out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """dy [M, K] @ w[K, N] -> [M, N]."""
+    m, k = dy.shape
+    n = w.shape[1]
+    assert w.shape[0] == k, (dy.shape, w.shape)
+    if out is None:
+        assert not accumulate
+        out = torch.empty(m, n, dtype=out_dtype or dy.dtype, device=dy.device)
+    if m == 0:
+        return out
+    if _native_ok(dy, w) and out.stride(-1) == 1:
+        return gemm_raw(dy, w, out, m, n, k, False, True, _epilogue(out, accumulate))
+    res = torch.matmul(dy, w)
+    return out.add_(res) if accumulate else out.copy_(res)
+
+
+def matmul_tn(dy: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False,
+              out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """dy[T, M]^T @ x[T, N] -> [M, N] (weight gradient); `out` may be the fp32 or bf16 gradient buffer."""
+    t, m = dy.shape
+    n = x.shape[1]
+    assert x.shape[0] == t, (dy.shape, x.shape)
+    if out is None:
+        assert not accumulate
+        out = torch.empty(m, n, dtype=out_dtype or dy.dtype, device=dy.device)
+    if t == 0:
+        return out if accumulate else out.zero_()
+    if _native_ok(dy, x) and out.stride(-1) == 1:
+        return gemm_raw(dy, x, out, m, n, t, True, True, _epilogue(out, accumulate))
+    res = torch.matmul(dy.t(), x)
+    return out.add_(res) if accumulate else out.copy_(res)
+
+
+def check_device_errors() -> None:
+    """Raise if a GEMM kernel gave up on a bounded wait since the last check (synchronises the device)."""
+    word = _lib.get_lib().flb_gemm_error_word()
+    if word:
+        raise _lib.KernelLibraryError(f"tcgen05 GEMM aborted a bounded wait (role code {word})")

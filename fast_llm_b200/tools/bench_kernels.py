@@ -1,0 +1,120 @@
+"""Kernel micro-benchmarks: device time (CUDA events, L2 flushed between iterations) and fraction of the measured peaks.
+
+Counterpart of the reference's `tools/benchmark/triton_kernels/` harness.  Usage:
+    python -m fast_llm_b200.tools.bench_kernels [--json out.json] [gemm] [elementwise]
+Peaks come from MEASURED_PEAKS.json at the repository root when present, else the stated fallbacks.
+"""
+
+import json
+import pathlib
+import sys
+
+import torch
+
+
+def _peaks():
+    path = pathlib.Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if path.exists():
+        d = json.loads(path.read_text())
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def time_op(fn, iters=10, warmup=3):
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    times = []
+    for _ in range(iters):
+        flush.zero_()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(end))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def bench_gemm(results):
+    from fast_llm_b200.ops.gemm import matmul_nn, matmul_nt, matmul_tn
+
+    _, tflops_peak, kind = _peaks()
+    t = 8192
+    shapes = [("qkv", 4096, 6144), ("dense", 4096, 4096), ("mlp1", 4096, 28672), ("mlp2", 14336, 4096), ("head", 4096, 32000)]
+    for name, k, n in shapes:
+        x = torch.randn(t, k, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+        dy = torch.randn(t, n, device="cuda", dtype=torch.bfloat16)
+        gw = torch.zeros(n, k, device="cuda", dtype=torch.float32)
+        flops = 2.0 * t * k * n
+        rows = {
+            "fprop": (lambda: matmul_nt(x, w), lambda: torch.matmul(x, w.t())),
+            "dgrad": (lambda: matmul_nn(dy, w), lambda: torch.matmul(dy, w)),
+            "wgrad_acc_f32": (lambda: matmul_tn(dy, x, out=gw, accumulate=True), lambda: gw.addmm_(dy.t(), x) if False else torch.matmul(dy.t(), x)),
+        }
+        for kind_name, (ours, lib) in rows.items():
+            ms = time_op(ours)
+            ms_lib = time_op(lib)
+            r = {"op": f"gemm_{name}_{kind_name}", "shape": [t, n, k], "ms": ms, "tflops": flops / ms / 1e9,
+                 "frac_of_peak": flops / ms / 1e9 / tflops_peak, "peak_kind": kind, "cublas_ms": ms_lib,
+                 "cublas_tflops": flops / ms_lib / 1e9}
+            results.append(r)
+            print(json.dumps(r), flush=True)
+        del x, w, dy, gw
+
+
+def bench_elementwise(results):
+    from fast_llm_b200.ops.activation import ActivationType, act_bwd_native, act_fwd_native
+    from fast_llm_b200.ops.cross_entropy import cross_entropy_forward_backward
+    from fast_llm_b200.ops.normalization import _bwd_native, _fwd_native
+    from fast_llm_b200.ops.optim import adamw
+    from fast_llm_b200.ops.rotary import rope_
+
+    gbs_peak, _, kind = _peaks()
+    t, h, f = 8192, 4096, 14336
+
+    def rec(name, nbytes, fn):
+        ms = time_op(fn)
+        r = {"op": name, "ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_peak": nbytes / ms / 1e6 / gbs_peak, "peak_kind": kind}
+        results.append(r)
+        print(json.dumps(r), flush=True)
+
+    x = torch.randn(t, h, device="cuda", dtype=torch.bfloat16)
+    d = torch.randn(t, h, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(h, device="cuda", dtype=torch.bfloat16)
+    rec("add_rmsnorm_fwd", 4 * t * h * 2, lambda: _fwd_native(x, d, w, None, 1e-5, False, False))
+    _, y, rstd, _ = _fwd_native(x, d, w, None, 1e-5, False, False)
+    rec("rmsnorm_bwd", 4 * t * h * 2, lambda: _bwd_native(y, x, w, None, rstd, None, d, False, False, True))
+    gu = torch.randn(t, 2 * f, device="cuda", dtype=torch.bfloat16)
+    go = torch.randn(t, f, device="cuda", dtype=torch.bfloat16)
+    rec("swiglu_fwd", 3 * t * f * 2, lambda: act_fwd_native(gu, True, ActivationType.silu))
+    rec("swiglu_bwd_recompute", 6 * t * f * 2, lambda: act_bwd_native(go, gu, True, ActivationType.silu, True))
+    qkv = torch.randn(t, 6144, device="cuda", dtype=torch.bfloat16)
+    ang = torch.arange(t, device="cuda", dtype=torch.float64)[:, None] * (10000.0 ** (-torch.arange(0, 128, 2, device="cuda", dtype=torch.float64) / 128))[None]
+    table = torch.cat([ang.cos(), ang.sin()], -1).float().contiguous()
+    rec("rope_qk", 2 * t * 5120 * 2, lambda: rope_(qkv, table, None, 40, 128, 128))
+    logits = torch.randn(t, 32000, device="cuda", dtype=torch.bfloat16)
+    labels = torch.randint(0, 32000, (t,), device="cuda")
+    rec("cross_entropy_fwd_bwd", 3 * t * 32000 * 2, lambda: cross_entropy_forward_backward(logits, labels, 1.0, in_place=False))
+    n = 256 * 1024 * 1024
+    pw, pg, pm, pv = (torch.zeros(n, device="cuda") for _ in range(4))
+    lp = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    rec("adamw", n * 30, lambda: adamw(pw, pg, pm, pv, lp, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1))
+
+
+def main(argv):
+    results = []
+    which = [a for a in argv if not a.startswith("--")] or ["gemm", "elementwise"]
+    if "gemm" in which:
+        bench_gemm(results)
+    if "elementwise" in which:
+        bench_elementwise(results)
+    if "--json" in argv:
+        pathlib.Path(argv[argv.index("--json") + 1]).write_text(json.dumps(results, indent=1))
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])

@@ -1,0 +1,258 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 restatement of the same op."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _lib_loaded():
+    from fast_llm_b200.ops import _lib
+
+    assert _lib.get_lib().flb_abi_version() == 1
+    yield
+    from fast_llm_b200.ops.gemm import check_device_errors
+
+    check_device_errors()
+
+
+GEMM_SHAPES = [(128, 256, 64), (256, 512, 128), (384, 768, 320), (1024, 1024, 1024), (200, 328, 136), (8, 4096, 512),
+               (4096, 1024, 4096), (130, 4104, 72)]
+
+
+@pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
+@pytest.mark.parametrize("block_n", [0, 128, 256])
+def test_gemm_nt(m, n, k, block_n):
+    from fast_llm_b200.ops.gemm import gemm_raw
+
+    torch.manual_seed(0)
+    x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+    out = torch.full((m, n), float("nan"), device="cuda", dtype=torch.bfloat16)
+    gemm_raw(x, w, out, m, n, k, False, False, 0, block_n=block_n)
+    ref = x.float() @ w.float().t()
+    assert _rel_err(out, ref) < 1e-2
+    assert torch.isfinite(out).all()
+
+
+@pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
+def test_gemm_nn(m, n, k):
+    from fast_llm_b200.ops.gemm import matmul_nn
+
+    torch.manual_seed(1)
+    dy = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(k, n, device="cuda", dtype=torch.bfloat16)
+    out = matmul_nn(dy, w)
+    ref = dy.float() @ w.float()
+    assert _rel_err(out, ref) < 1e-2
+
+
+@pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_tn_accumulate(m, n, k, out_dtype):
+    from fast_llm_b200.ops.gemm import matmul_tn
+
+    torch.manual_seed(2)
+    dy = torch.randn(k, m, device="cuda", dtype=torch.bfloat16)
+    x = torch.randn(k, n, device="cuda", dtype=torch.bfloat16)
+    base = torch.randn(m, n, device="cuda", dtype=out_dtype)
+    out = base.clone()
+    matmul_tn(dy, x, out=out, accumulate=True)
+    ref = base.float() + dy.float().t() @ x.float()
+    assert _rel_err(out, ref) < (1e-2 if out_dtype == torch.bfloat16 else 2e-3)
+    out2 = torch.empty(m, n, device="cuda", dtype=out_dtype)
+    matmul_tn(dy, x, out=out2, accumulate=False)
+    assert _rel_err(out2, dy.float().t() @ x.float()) < 1e-2
+
+
+def test_gemm_mixed_majors_and_strided_views():
+    from fast_llm_b200.ops.gemm import gemm_raw, matmul_nt
+
+    torch.manual_seed(3)
+    m, n, k = 256, 384, 192
+    a_t = torch.randn(k, m, device="cuda", dtype=torch.bfloat16)  # A MN-major
+    b = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)  # B K-major
+    out = torch.empty(m, n, device="cuda", dtype=torch.float32)
+    gemm_raw(a_t, b, out, m, n, k, True, False, 1)
+    assert _rel_err(out, a_t.float().t() @ b.float().t()) < 1e-2
+    # operands that are column slices of wider buffers (leading dimension > logical width)
+    big = torch.randn(m, 3 * k, device="cuda", dtype=torch.bfloat16)
+    xs = big[:, k : 2 * k]
+    outs = torch.empty(m, 2 * n, device="cuda", dtype=torch.bfloat16)
+    matmul_nt(xs, b, out=outs[:, n:])
+    assert _rel_err(outs[:, n:], xs.float() @ b.float().t()) < 1e-2
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 256), (300, 4096), (17, 8192), (5, 1000)])
+@pytest.mark.parametrize("layer_norm", [False, True])
+@pytest.mark.parametrize("zero_centered", [False, True])
+def test_norm(rows, cols, layer_norm, zero_centered):
+    from fast_llm_b200.ops.normalization import add_norm, norm, norm_reference
+
+    torch.manual_seed(0)
+    x = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)
+    d = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(cols, device="cuda") * 0.1 + (0 if zero_centered else 1)).bfloat16().requires_grad_()
+    b = (torch.randn(cols, device="cuda") * 0.1).bfloat16().requires_grad_() if layer_norm else None
+    xr, dr = x.clone().requires_grad_(), d.clone().requires_grad_()
+    x.requires_grad_(), d.requires_grad_()
+    res, y = add_norm(x, d, w, b, 1e-5, zero_centered, layer_norm)
+    gy, gr = torch.randn_like(y), torch.randn_like(res)
+    (y.float() * gy).sum().add((res.float() * gr).sum()).backward()
+    wr = w.detach().float().requires_grad_()
+    br = b.detach().float().requires_grad_() if b is not None else None
+    res_r = (xr.float() + dr.float()).bfloat16().float()
+    y_r = norm_reference(res_r, wr, br, 1e-5, zero_centered, layer_norm)
+    ((y_r * gy).sum() + (res_r * gr).sum()).backward()
+    assert _rel_err(y, y_r) < 1e-2
+    assert _rel_err(res, res_r) < 1e-6
+    assert _rel_err(x.grad, xr.grad) < 1.5e-2
+    assert _rel_err(d.grad, dr.grad) < 1.5e-2
+    assert _rel_err(w.grad, wr.grad) < 1.5e-2
+    if b is not None:
+        assert _rel_err(b.grad, br.grad) < 1.5e-2
+    y2 = norm(x.detach(), w.detach(), None if b is None else b.detach(), 1e-5, zero_centered, layer_norm)
+    assert _rel_err(y2, norm_reference(x.detach().float(), wr, br, 1e-5, zero_centered, layer_norm)) < 1e-2
+
+
+def test_norm_grad_buffer_accumulation():
+    from fast_llm_b200.ops.normalization import norm
+
+    x = torch.randn(128, 512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = torch.ones(512, device="cuda", dtype=torch.bfloat16)
+    w.grad_buffer = torch.zeros(512, device="cuda", dtype=torch.float32)
+    w.param_grad_is_zero = True
+    for _ in range(2):
+        norm(x, w).float().sum().backward()
+    xf = x.detach().float()
+    ref = 2 * (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5)).sum(0)
+    assert _rel_err(w.grad_buffer, ref) < 1e-2
+    assert w.param_grad_is_zero is False
+
+
+@pytest.mark.parametrize("rot_dim", [128, 64])
+def test_rope(rot_dim):
+    from fast_llm_b200.ops.rotary import rope_, rope_reference
+
+    torch.manual_seed(0)
+    tokens, heads, kv, hd = 333, 8, 2, 128
+    x = torch.randn(tokens, (heads + 2 * kv) * hd, device="cuda", dtype=torch.bfloat16)
+    pos = torch.randint(0, 1000, (tokens,), device="cuda", dtype=torch.int32)
+    ang = torch.arange(1000, device="cuda", dtype=torch.float64)[:, None] * (10000.0 ** (-torch.arange(0, rot_dim, 2, device="cuda", dtype=torch.float64) / rot_dim))[None]
+    table = torch.cat([ang.cos(), ang.sin()], -1).float().contiguous()
+    ref = rope_reference(x.float(), table, pos, heads + kv, hd, rot_dim)
+    y = rope_(x.clone(), table, pos, heads + kv, hd, rot_dim)
+    assert _rel_err(y, ref) < 5e-3
+    assert torch.equal(y[:, (heads + kv) * hd :], x[:, (heads + kv) * hd :])
+    back = rope_(y.clone(), table, pos, heads + kv, hd, rot_dim, conj=True)
+    assert _rel_err(back, x) < 1e-2
+
+
+@pytest.mark.parametrize("gated", [True, False])
+@pytest.mark.parametrize("act", ["silu", "gelu", "relu", "squared_relu", "sigmoid", "identity", "gelu_erf"])
+def test_mlp_activation(gated, act):
+    from fast_llm_b200.ops.activation import ActivationType, mlp_activation, mlp_activation_reference
+
+    torch.manual_seed(0)
+    a = ActivationType(act)
+    x = torch.randn(257, 1024, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    xr = x.detach().float().requires_grad_()
+    y = mlp_activation(x, gated, a)
+    yr = mlp_activation_reference(xr, gated, a)
+    g = torch.randn_like(y)
+    y.backward(g)
+    yr.backward(g.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("vocab", [32000, 1003])
+def test_cross_entropy(dtype, vocab):
+    from fast_llm_b200.ops.cross_entropy import cross_entropy_forward_backward, cross_entropy_reference
+
+    torch.manual_seed(0)
+    rows = 97
+    ld = (vocab + 7) // 8 * 8
+    buf = (torch.randn(rows, ld, device="cuda") * 3).to(dtype)
+    logits = buf[:, :vocab]
+    labels = torch.randint(0, vocab, (rows,), device="cuda")
+    labels[::7] = -100
+    loss_r, z_r, grad_r = cross_entropy_reference(logits.float(), labels, 0.37, 1.5, 1e-3)
+    loss, z, grad = cross_entropy_forward_backward(logits, labels, 0.37, 1.5, 1e-3, in_place=False)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    assert _rel_err(loss, loss_r) < 1e-4
+    assert _rel_err(z, z_r) < 1e-4
+    assert _rel_err(grad, grad_r) < tol
+    # sharded: two halves merged by hand must equal the unsharded result
+    gs = torch.tensor([0.37], device="cuda")
+    loss2, _, grad2 = cross_entropy_forward_backward(logits.clone(), labels, gs, 1.5, 1e-3, in_place=True)
+    assert _rel_err(loss2, loss_r) < 1e-4
+    assert _rel_err(grad2, grad_r) < tol
+
+
+def test_adamw_and_norm_kernels():
+    from fast_llm_b200.ops.optim import adamw, adamw_reference, clip_coeff, sumsq
+
+    torch.manual_seed(0)
+    n = 1_000_003
+    w = torch.randn(n + 1, device="cuda")[:n]
+    n = (n // 4) * 4 + 3
+    w = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda")
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    lp = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    wr, mr, vr = w.clone(), m.clone(), v.clone()
+    nsq = torch.zeros(1, device="cuda")
+    sumsq(g, nsq)
+    assert abs(nsq.item() - g.double().pow(2).sum().item()) / nsq.item() < 1e-5
+    coeff = torch.empty(1, device="cuda")
+    norm = torch.empty(1, device="cuda")
+    clip_coeff(nsq, 1.0, 0.5, coeff, norm)
+    expect_norm = g.double().norm().item() * 0.5
+    assert abs(norm.item() - expect_norm) / expect_norm < 1e-5
+    expect_coeff = 0.5 * min(1.0, 1.0 / (expect_norm + 1e-6))
+    assert abs(coeff.item() - expect_coeff) / expect_coeff < 1e-5
+    for step in (1, 2, 3):
+        adamw(w, g, m, v, lp, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, 1.0, coeff)
+        adamw_reference(wr, g, mr, vr, None, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, expect_coeff)
+    assert _rel_err(w, wr) < 1e-5
+    assert _rel_err(m, mr) < 1e-5
+    assert _rel_err(v, vr) < 1e-5
+    assert torch.equal(lp, w.bfloat16())
+
+
+def test_embedding_and_pointwise():
+    from fast_llm_b200.ops.pointwise import axpby_, bias_residual, embedding, fill_
+
+    torch.manual_seed(0)
+    w = torch.randn(1000, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    ids = torch.randint(0, 1200, (4, 77), device="cuda")
+    out = embedding(ids, w, 100, 1100, 2.0)
+    mask = (ids >= 100) & (ids < 1100)
+    ref = torch.nn.functional.embedding((ids - 100).clamp(0, 999), w.detach().float()) * mask[..., None] * 2.0
+    assert _rel_err(out, ref) < 1e-2
+    g = torch.randn_like(out)
+    out.backward(g)
+    wr = w.detach().float().requires_grad_()
+    (torch.nn.functional.embedding((ids - 100).clamp(0, 999), wr) * mask[..., None] * 2.0 * g.float()).sum().backward()
+    assert _rel_err(w.grad, wr.grad) < 1e-2
+    a = torch.randn(100003, device="cuda")
+    b = torch.randn(100003, device="cuda", dtype=torch.bfloat16)
+    o = torch.empty(100003, device="cuda", dtype=torch.bfloat16)
+    axpby_(o, a, b, 0.5, 2.0)
+    assert _rel_err(o, a * 0.5 + b.float() * 2) < 1e-2
+    fill_(o, 3.0)
+    assert (o == 3).all()
+    x = torch.randn(33, 512, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(512, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        r = bias_residual(x, bias, x, 0.5)
+    assert _rel_err(r, (x.float() + bias.float()) * 0.5 + x.float()) < 1e-2
