@@ -1,0 +1,172 @@
+"""AdamW over flat shard slices with global-norm clipping and loss scaling, entirely on the device.
+
+Per step: unscale check -> squared norm of every gradient-shard slice (deterministic two-stage reduction) ->
+all-reduce over the world -> a one-thread kernel turns it into the clip coefficient -> one fused Adam launch per
+parameter group reads the coefficient through a pointer and writes fp32 master weights, moments and the bf16 weight
+buffer slice.  No `.item()` on the way.  Parity: `fast_llm/engine/optimizer/optimizer.py:53-311`.
+"""
+
+import logging
+
+import torch
+
+from fast_llm_b200.engine.optimizer.config import GradientScalerConfig, OptimizerConfig
+from fast_llm_b200.engine.optimizer.learning_rate import create_schedule_from_config
+from fast_llm_b200.ops.optim import adamw, clip_coeff, sumsq
+from fast_llm_b200.parallel.collectives import all_reduce
+
+logger = logging.getLogger(__name__)
+
+
+class GradScaler:
+    """No scaling."""
+
+    def __init__(self, scale: float = 1.0, distributed=None):
+        self._scale = scale
+        self._distributed = distributed
+
+    @property
+    def grad_scale(self) -> float:
+        return self._scale
+
+    def state_dict(self) -> dict:
+        return {"scale": self._scale}
+
+    def load(self, state: dict) -> None:
+        self._scale = state.get("scale", self._scale)
+
+    def check_overflow(self, grad_slices) -> bool:
+        return False
+
+    def update(self, found_overflow: bool) -> None:
+        pass
+
+
+class ConstantGradScaler(GradScaler):
+    pass
+
+
+class DynamicGradScaler(GradScaler):
+    """fp16 loss scaling: halve after `hysteresis` overflowing steps, double after `window` clean ones."""
+
+    def __init__(self, config: GradientScalerConfig, distributed=None):
+        super().__init__(config.initial, distributed)
+        self._config = config
+        self._growth_tracker = 0
+        self._hysteresis_tracker = config.hysteresis
+
+    def state_dict(self):
+        return {"scale": self._scale, "growth_tracker": self._growth_tracker, "hysteresis_tracker": self._hysteresis_tracker}
+
+    def load(self, state):
+        super().load(state)
+        self._growth_tracker = state.get("growth_tracker", 0)
+        self._hysteresis_tracker = state.get("hysteresis_tracker", self._config.hysteresis)
+
+    def check_overflow(self, grad_slices) -> bool:
+        flag = torch.zeros(1, dtype=torch.float32, device=grad_slices[0].device if grad_slices else "cpu")
+        for g in grad_slices:
+            flag += (~torch.isfinite(g)).any().float()
+        if self._distributed is not None:
+            all_reduce(flag, group=self._distributed.world_group)
+        return bool(flag.item() > 0)
+
+    def update(self, found_overflow: bool) -> None:
+        if found_overflow:
+            self._growth_tracker = 0
+            self._hysteresis_tracker -= 1
+            if self._hysteresis_tracker <= 0:
+                self._scale = max(self._scale / 2, self._config.minimum)
+        else:
+            self._growth_tracker += 1
+            if self._growth_tracker >= self._config.window:
+                self._growth_tracker = 0
+                self._hysteresis_tracker = self._config.hysteresis
+                self._scale *= 2
+
+
+def get_grad_scaler(config: GradientScalerConfig, compute_dtype: torch.dtype, distributed=None) -> GradScaler:
+    if config.constant is not None and config.constant > 0:
+        return ConstantGradScaler(config.constant, distributed)
+    if compute_dtype == torch.float16:
+        return DynamicGradScaler(config, distributed)
+    return GradScaler(1.0, distributed)
+
+
+class Optimizer:
+    def __init__(self, config: OptimizerConfig, param_groups: list[dict], grad_norm_slices: list[torch.Tensor], distributed,
+                 compute_dtype: torch.dtype = torch.float32):
+        config.validate()
+        self._config = config
+        self._param_groups = param_groups
+        self._grad_norm_slices = grad_norm_slices
+        self._distributed = distributed
+        self._lr_schedule = create_schedule_from_config(config.learning_rate)
+        self._current_step = 0
+        self._grad_scaler = get_grad_scaler(config.gradient_scaler, compute_dtype, distributed)
+        device = distributed.device
+        self._normsq = torch.zeros(1, dtype=torch.float32, device=device)
+        self._coeff = torch.ones(1, dtype=torch.float32, device=device)
+        self._norm = torch.zeros(1, dtype=torch.float32, device=device)
+
+    @property
+    def grad_scale(self) -> float:
+        return self._grad_scaler.grad_scale
+
+    @property
+    def current_step(self) -> int:
+        return self._current_step
+
+    @property
+    def grad_norm(self) -> torch.Tensor:
+        return self._norm
+
+    def learning_rate(self, step: int | None = None) -> float:
+        return self._lr_schedule(self._current_step if step is None else step)
+
+    def _compute_clip_coefficient(self) -> None:
+        first = True
+        for g in self._grad_norm_slices:
+            if g.numel():
+                sumsq(g, self._normsq, accumulate=not first)
+                first = False
+        if first:
+            self._normsq.zero_()
+        all_reduce(self._normsq, group=self._distributed.world_group)
+        clip_coeff(self._normsq, self._config.gradient_norm_clipping, 1.0 / self._grad_scaler.grad_scale, self._coeff, self._norm)
+
+    @torch.no_grad()
+    def step(self, metrics: dict | None = None) -> bool:
+        """Returns True if the weights were updated (False when an fp16 overflow skipped the step)."""
+        overflow = self._grad_scaler.check_overflow([g["grads"] for g in self._param_groups])
+        self._grad_scaler.update(overflow)
+        if metrics is not None:
+            metrics["loss_scale"] = self._grad_scaler.grad_scale
+        if overflow:
+            return False
+        self._current_step += 1
+        lr = self._lr_schedule(self._current_step)
+        self._compute_clip_coefficient()
+        c = self._config
+        for group in self._param_groups:
+            lr_scale = group["lr_scale"] * (c.default_learning_rate_scale if group["lr_scale"] == 1.0 else 1.0)
+            adamw(group["params"], group["grads"], group["exp_avgs"], group["exp_avgs_sq"], group.get("buffer"),
+                  lr * lr_scale, c.beta_1, c.beta_2, c.epsilon, c.weight_decay if group["weight_decay"] else 0.0,
+                  self._current_step, 1.0, self._coeff)
+        if metrics is not None:
+            metrics["learning_rate"] = lr
+            metrics["grad_norm"] = self._norm  # device tensor; converted when logged
+        return True
+
+    def save(self) -> dict:
+        return {"current_step": self._current_step, "grad_scaler": self._grad_scaler.state_dict()}
+
+    def load(self, state: dict, validate: bool = True) -> None:
+        self._current_step = state.get("current_step", 0)
+        self._grad_scaler.load(state.get("grad_scaler", {}))
+
+    def reset_state(self) -> None:
+        self._current_step = 0
+        for group in self._param_groups:
+            group["exp_avgs"].zero_()
+            group["exp_avgs_sq"].zero_()

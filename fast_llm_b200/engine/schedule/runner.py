@@ -1,0 +1,280 @@
+"""Executes a `Schedule`: one optimizer step = every forward / backward step of the plan, gradient reduction,
+optimizer update and loss reduction.
+
+Streams: compute runs on the current stream; ZeRO weight gathers and gradient reductions run on a `data` stream and
+pipeline transfers on a `pipeline` stream, ordered against compute with events, so they overlap with the neighbouring
+stage's math.  On CPU the same code runs with mock streams.  Parity: `fast_llm/engine/schedule/runner.py:65-556`.
+"""
+
+import collections
+import logging
+import time
+import typing
+
+import torch
+
+from fast_llm_b200.engine.multi_stage.config import StageMode
+from fast_llm_b200.engine.multi_stage.multi_stage import MultiStageModel
+from fast_llm_b200.engine.schedule.config import EventType, MockEvent, MockStream, ScheduleConfig, StepType
+from fast_llm_b200.engine.schedule.schedule import Schedule, Step
+from fast_llm_b200.layers.kwargs import BlockKwargs, LanguageModelKwargs
+from fast_llm_b200.parallel.collectives import all_reduce, recv, send
+from fast_llm_b200.parallel.topology import DistributedConfig
+from fast_llm_b200.utils import Assert
+
+logger = logging.getLogger(__name__)
+
+
+class BatchContext:
+    """Everything alive during one optimizer step."""
+
+    def __init__(self, iteration: int, schedule: Schedule):
+        self.iteration = iteration
+        self.schedule = schedule
+        self.data: dict[int, list] = {}  # data_index -> [(tokens, kwargs) per micro-sequence]
+        self.contexts: dict[tuple, typing.Any] = {}
+        self.outputs: dict[tuple, torch.Tensor] = {}
+        self.grads: dict[tuple, torch.Tensor] = {}
+        self.kv_leaves: dict[tuple, list] = {}  # (stage, data_index, micro_sequence) -> detached key/value prefixes
+        self.losses: dict[str, list] = collections.defaultdict(list)
+        self.metrics: dict = {}
+        self.pending_sends: list = []
+        self.profile_events: list = []
+        self.data_iterator = None
+
+
+class ScheduleRunner:
+    def __init__(self, *, config: ScheduleConfig, multi_stage: MultiStageModel, distributed_config: DistributedConfig):
+        config.validate()
+        self._config = config
+        self._multi_stage = multi_stage
+        self._distributed_config = distributed_config
+        self._is_setup = False
+        self._num_stages = len(multi_stage.stages)
+
+    def setup(self, distributed, optimizer=None) -> None:
+        assert not self._is_setup
+        self._is_setup = True
+        self._distributed = distributed
+        self._optimizer = optimizer
+        self._stages_on_device = self._multi_stage.stages_on_device
+        self._use_cuda = distributed.device.type == "cuda"
+        if self._use_cuda:
+            self._compute_stream = torch.cuda.current_stream(distributed.device)
+            overlap_data = self._config.data_overlap and self._distributed_config.data_parallel > 1
+            self._data_stream = torch.cuda.Stream(distributed.device) if overlap_data else self._compute_stream
+            overlap_pipe = self._config.pipeline_overlap and self._distributed_config.pipeline_parallel > 1
+            self._pipeline_stream = torch.cuda.Stream(distributed.device) if overlap_pipe else self._compute_stream
+            self._event = lambda: torch.cuda.Event()
+        else:
+            self._compute_stream = self._data_stream = self._pipeline_stream = MockStream()
+            self._event = MockEvent
+        self._loss_definitions = {d.name: d for d in self._multi_stage.base_model.get_loss_definitions()}
+        self._throttle_events: collections.deque = collections.deque()
+
+    def _stream_ctx(self, stream):
+        if self._use_cuda and stream is not self._compute_stream:
+            return torch.cuda.stream(stream)
+        return MockStream()
+
+    # ------------------------------------------------------------------------------------------------
+    def run_step(self, data_iterator: typing.Iterator, schedule: Schedule, *, iteration: int = 1, return_metrics: bool = False,
+                 preprocessed: bool = False) -> tuple[dict[str, float | int], bool, dict | None]:
+        assert self._is_setup
+        training = schedule.phase.is_training
+        if training:
+            assert self._multi_stage.stages_on_device is not None and self._optimizer is not None or self._config.skip_step
+        context = BatchContext(iteration, schedule)
+        context.data_iterator = data_iterator
+        context.preprocessed = preprocessed
+        metrics = context.metrics if return_metrics else None
+        self._distributed.set_step(iteration, schedule.phase)
+        if self._data_stream is not self._compute_stream:
+            self._data_stream.wait_stream(self._compute_stream)
+        if self._pipeline_stream is not self._compute_stream:
+            self._pipeline_stream.wait_stream(self._compute_stream)
+        if training:
+            for stage in self._stages_on_device.values():
+                stage.reset_gradients()
+        for step in schedule.steps:
+            self._run_one(context, step)
+        for handle in context.pending_sends:
+            if handle is not None:
+                handle.wait()
+        if self._data_stream is not self._compute_stream:
+            self._compute_stream.wait_stream(self._data_stream)
+        if self._pipeline_stream is not self._compute_stream:
+            self._compute_stream.wait_stream(self._pipeline_stream)
+        Assert.empty(context.contexts)
+
+        update_successful = True
+        if training and not self._config.skip_step:
+            update_successful = self._optimizer.step(context.metrics if return_metrics else None)
+            # Adam wrote the new weights into this rank's slice of the weight buffers.  With one data rank that is the
+            # whole buffer; otherwise the next restore all-gathers the other slices.
+            if self._distributed_config.data_parallel > 1 or self._multi_stage._num_weight_buffers < len(self._stages_on_device):
+                self._multi_stage.invalidate_buffers()
+        losses = self._reduce_losses(context, schedule)
+        return losses, update_successful, (context.metrics if return_metrics else None)
+
+    # ------------------------------------------------------------------------------------------------
+    def _get_data(self, context: BatchContext, data_index: int):
+        if data_index not in context.data:
+            t0 = time.perf_counter()
+            batch = next(context.data_iterator)
+            t1 = time.perf_counter()
+            if context.preprocessed:
+                inputs = batch
+            else:
+                inputs = self._multi_stage.base_model.preprocess_batch(
+                    batch, phase=context.schedule.phase, iteration=context.iteration, metrics=context.metrics,
+                    device=self._distributed.device)
+            Assert.eq(len(inputs), self._config.micro_batch_splits)
+            grad_output = (self._optimizer.grad_scale if self._optimizer is not None else 1.0) / self._config.sequential_micro_batches
+            for _, kwargs in inputs:
+                kwargs[BlockKwargs.grad_output] = grad_output
+            context.data[data_index] = inputs
+            context.metrics["data_wait_ms"] = context.metrics.get("data_wait_ms", 0.0) + (t1 - t0) * 1e3
+            context.metrics["preprocess_ms"] = context.metrics.get("preprocess_ms", 0.0) + (time.perf_counter() - t1) * 1e3
+        return context.data[data_index]
+
+    def _run_one(self, context: BatchContext, step: Step) -> None:
+        if self._config.throttle_cpu and self._use_cuda:
+            self._throttle()
+        stage = self._stages_on_device[step.stage]
+        if step.restore:
+            with self._stream_ctx(self._data_stream):
+                stage.restore_parameters()
+            if self._data_stream is not self._compute_stream:
+                self._compute_stream.wait_stream(self._data_stream)
+        if step.type_ == StepType.forward:
+            self._forward(context, step, stage)
+        else:
+            self._backward(context, step, stage)
+        if step.reduce:
+            if self._data_stream is not self._compute_stream:
+                self._data_stream.wait_stream(self._compute_stream)
+            with self._stream_ctx(self._data_stream):
+                stage.reduce_gradients(step.reduce_accumulate)
+                if step.reduce_accumulate or self._multi_stage._num_grad_buffers < len(self._stages_on_device):
+                    stage.reset_gradients()
+
+    def _throttle(self) -> None:
+        event = torch.cuda.Event()
+        event.record()
+        self._throttle_events.append(event)
+        limit = self._config.throttle_cpu_delay + 8
+        while len(self._throttle_events) > limit:
+            self._throttle_events.popleft().synchronize()
+
+    def _forward(self, context: BatchContext, step: Step, stage) -> None:
+        inputs = self._get_data(context, step.data_index)
+        tokens, kwargs = inputs[step.micro_sequence]
+        if step.stage == 0:
+            input_ = tokens
+        elif step.recv_from is not None:
+            input_ = self._recv(step, kwargs, forward=True)
+        else:
+            input_ = context.outputs.pop((step.stage - 1, step.data_index, step.micro_sequence))
+        splits = self._config.micro_batch_splits
+        if splits > 1:
+            kwargs = dict(kwargs)
+            if step.micro_sequence > 0:
+                leaves = context.kv_leaves[(step.stage, step.data_index, step.micro_sequence - 1)]
+                kwargs[BlockKwargs.past_key_values] = list(leaves)
+            if step.micro_sequence < splits - 1:
+                kwargs[BlockKwargs.presents] = []
+        output, ctx = stage.forward(input_, kwargs, context.losses, context.metrics)
+        presents = kwargs.get(BlockKwargs.presents) if splits > 1 else None
+        if presents:
+            training = context.schedule.phase.is_training
+            context.kv_leaves[step.key] = [kv.detach().requires_grad_(training) for kv in presents]
+        if context.schedule.phase.is_training:
+            context.contexts[step.key] = (ctx, presents)
+        if step.stage < self._num_stages - 1:
+            if step.send_to is not None:
+                self._send(context, step, output)
+            else:
+                context.outputs[step.key] = output
+
+    def _backward(self, context: BatchContext, step: Step, stage) -> None:
+        if step.stage == self._num_stages - 1:
+            output_grad = None
+        elif step.recv_from is not None:
+            _, kwargs = context.data[step.data_index][step.micro_sequence]
+            output_grad = self._recv(step, kwargs, forward=False)
+        else:
+            output_grad = context.grads.pop((step.stage + 1, step.data_index, step.micro_sequence))
+        ctx, presents = context.contexts.pop(step.key)
+        if presents:
+            leaves = context.kv_leaves.pop(step.key)
+            input_, output = ctx
+            tensors, grads = [output], [output_grad]
+            for kv, leaf in zip(presents, leaves):
+                if leaf.grad is not None:
+                    tensors.append(kv)
+                    grads.append(leaf.grad)
+            torch.autograd.backward(tensors, grads)
+            input_grad = None
+            if torch.is_tensor(input_) and input_.is_floating_point() and input_.requires_grad:
+                input_grad, input_.grad = input_.grad, None
+        else:
+            context.kv_leaves.pop(step.key, None)
+            input_grad = stage.backward(output_grad, ctx)
+        if step.stage > 0:
+            if step.send_to is not None:
+                self._send(context, step, input_grad)
+            else:
+                context.grads[step.key] = input_grad
+        if step.stage == 0 and step.micro_sequence == 0:
+            last_use = all(s.data_index != step.data_index or s.local_index <= step.local_index for s in context.schedule.steps)
+            if last_use:
+                context.data.pop(step.data_index, None)
+
+    # ---- pipeline transfers (NCCL / Gloo point to point on the pipeline stream)
+    def _hidden_shape(self, kwargs) -> tuple[int, int]:
+        tokens = kwargs[BlockKwargs.num_tokens]
+        dc = self._distributed_config
+        if dc.sequence_tensor_parallel:
+            tokens //= dc.tensor_parallel
+        return (tokens, self._multi_stage.base_model._hidden_dim.size)
+
+    def _recv(self, step: Step, kwargs, forward: bool) -> torch.Tensor:
+        shape = self._hidden_shape(kwargs)
+        dtype = self._distributed_config.compute_dtype.torch
+        with self._stream_ctx(self._pipeline_stream):
+            buffer = torch.empty(shape, dtype=dtype, device=self._distributed.device)
+            if self._config.debug_send_recv:
+                header = torch.empty(2, dtype=torch.int64, device=self._distributed.device)
+                recv(header, step.recv_from, self._distributed.pipeline_group)
+                Assert.eq(header.tolist(), [step.data_index * 1000 + step.micro_sequence, buffer.numel()])
+            recv(buffer, step.recv_from, self._distributed.pipeline_group)
+        if self._pipeline_stream is not self._compute_stream:
+            self._compute_stream.wait_stream(self._pipeline_stream)
+        return buffer
+
+    def _send(self, context: BatchContext, step: Step, tensor: torch.Tensor) -> None:
+        if self._pipeline_stream is not self._compute_stream:
+            self._pipeline_stream.wait_stream(self._compute_stream)
+        with self._stream_ctx(self._pipeline_stream):
+            tensor = tensor.contiguous()
+            if self._config.debug_send_recv:
+                header = torch.tensor([step.data_index * 1000 + step.micro_sequence, tensor.numel()], dtype=torch.int64, device=tensor.device)
+                context.pending_sends.append(send(header, step.send_to, self._distributed.pipeline_group, async_op=True))
+            context.pending_sends.append(send(tensor, step.send_to, self._distributed.pipeline_group, async_op=True))
+            if self._use_cuda:
+                tensor.record_stream(self._pipeline_stream) if self._pipeline_stream is not self._compute_stream else None
+
+    # ---- losses
+    def _reduce_losses(self, context: BatchContext, schedule: Schedule) -> dict[str, float]:
+        out = {}
+        count = self._config.sequential_micro_batches
+        for name, definition in self._loss_definitions.items():
+            definition.count = count
+            values = context.losses.get(name, [])
+            # micro-sequences of one micro-batch are already normalised by the whole micro-batch's label count
+            out[name] = definition.reduce(values, self._distributed)
+        for name, values in context.losses.items():
+            if name not in out and values:
+                out[name] = (torch.stack([v.float().reshape(()) for v in values]).sum() / count).item()
+        return out

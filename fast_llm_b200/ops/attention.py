@@ -1,0 +1,137 @@
+"""Variable-length (packed documents) causal attention with GQA and sliding window.
+
+`packed_attention(qkv, ...)` takes the fused projection output `[tokens, (heads + 2*kv_heads) * head_dim]` and returns
+`[tokens, heads * head_dim]`; its backward writes dq, dk, dv into one packed gradient so the fused QKV projection's
+backward is a single GEMM.  `attention(q, k, v, ...)` is the general form (keys may include a prefix from earlier
+micro-sequences or other sequence-data-parallel ranks; causal masks are bottom-right aligned).
+
+On GPUs the softmax(QK^T)V core is the flash-attention 2 library kernel (a library call, like cuBLAS for a plain GEMM);
+on CPU a per-document PyTorch restatement, which doubles as the test oracle (math of `fast_llm/layers/attention/
+attention.py:209-256`).
+"""
+
+import torch
+
+from fast_llm_b200.ops import _lib
+
+
+def attention_reference(q, k, v, cu_seqlens_q, cu_seqlens_k, causal: bool, window_size: int | None, scale: float):
+    """q [Tq, Hq, D], k/v [Tk, Hkv, D] -> [Tq, Hq, D]; fp32 math, differentiable."""
+    hq, hkv = q.shape[1], k.shape[1]
+    rep = hq // hkv
+    outs = []
+    cq = cu_seqlens_q.tolist()
+    ck = cu_seqlens_k.tolist()
+    for i in range(len(cq) - 1):
+        qs = q[cq[i] : cq[i + 1]].float()
+        ks = k[ck[i] : ck[i + 1]].float().repeat_interleave(rep, dim=1)
+        vs = v[ck[i] : ck[i + 1]].float().repeat_interleave(rep, dim=1)
+        lq, lk = qs.shape[0], ks.shape[0]
+        if lq == 0:
+            continue
+        scores = torch.einsum("qhd,khd->hqk", qs, ks) * scale
+        qi = torch.arange(lq, device=q.device)[:, None] + (lk - lq)
+        ki = torch.arange(lk, device=q.device)[None, :]
+        mask = torch.ones(lq, lk, dtype=torch.bool, device=q.device)
+        if causal:
+            mask &= ki <= qi
+        if window_size is not None:
+            mask &= ki > qi - window_size if causal else (ki - qi).abs() < window_size
+        scores = scores.masked_fill(~mask[None], float("-inf"))
+        probs = torch.softmax(scores, dim=-1)
+        probs = torch.nan_to_num(probs)
+        outs.append(torch.einsum("hqk,khd->qhd", probs, vs))
+    return torch.cat(outs, 0).to(q.dtype) if outs else q.new_zeros(q.shape)
+
+
+def _window(window_size, causal):
+    if window_size is None:
+        return (-1, 0 if causal else -1)
+    # a window of w tokens = the current token plus w - 1 earlier ones
+    return (window_size - 1, 0 if causal else window_size - 1)
+
+
+def _use_flash(q):
+    return q.is_cuda and q.dtype in (torch.bfloat16, torch.float16)
+
+
+class _FlashAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cu_q, cu_k, max_q, max_k, causal, window_size, scale, dropout_p):
+        from flash_attn.flash_attn_interface import _flash_attn_varlen_forward
+
+        wl, wr = _window(window_size, causal)
+        out, lse, _, rng_state = _flash_attn_varlen_forward(q, k, v, cu_q, cu_k, max_q, max_k, dropout_p, scale, causal,
+                                                            window_size_left=wl, window_size_right=wr)
+        ctx.save_for_backward(q, k, v, out, lse, cu_q, cu_k, rng_state)
+        ctx.args = (max_q, max_k, causal, wl, wr, scale, dropout_p)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
+
+        q, k, v, out, lse, cu_q, cu_k, rng_state = ctx.saved_tensors
+        max_q, max_k, causal, wl, wr, scale, dropout_p = ctx.args
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        _flash_attn_varlen_backward(dout.contiguous(), q, k, v, out, lse, dq, dk, dv, cu_q, cu_k, max_q, max_k, dropout_p,
+                                    scale, causal, wl, wr, 0.0, None, False, rng_state)
+        return dq, dk, dv, None, None, None, None, None, None, None, None
+
+
+def attention(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int, max_seqlen_k: int, *, causal: bool = True,
+              window_size: int | None = None, scale: float | None = None, dropout_p: float = 0.0):
+    scale = q.shape[-1] ** -0.5 if scale is None else scale
+    if _use_flash(q):
+        return _FlashAttention.apply(q, k, v, cu_seqlens_q.int(), cu_seqlens_k.int(), max_seqlen_q, max_seqlen_k, causal,
+                                     window_size, scale, dropout_p)
+    return attention_reference(q, k, v, cu_seqlens_q, cu_seqlens_k, causal, window_size, scale)
+
+
+class _PackedFlashAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, cu, max_len, heads, kv_heads, head_dim, causal, window_size, scale, dropout_p):
+        from flash_attn.flash_attn_interface import _flash_attn_varlen_forward
+
+        t = qkv.shape[0]
+        nq, nkv = heads * head_dim, kv_heads * head_dim
+        q = qkv[:, :nq].view(t, heads, head_dim)
+        k = qkv[:, nq : nq + nkv].view(t, kv_heads, head_dim)
+        v = qkv[:, nq + nkv :].view(t, kv_heads, head_dim)
+        wl, wr = _window(window_size, causal)
+        out, lse, _, rng_state = _flash_attn_varlen_forward(q, k, v, cu, cu, max_len, max_len, dropout_p, scale, causal,
+                                                            window_size_left=wl, window_size_right=wr)
+        ctx.save_for_backward(qkv, out, lse, cu, rng_state)
+        ctx.args = (max_len, heads, kv_heads, head_dim, causal, wl, wr, scale, dropout_p)
+        return out.view(t, nq)
+
+    @staticmethod
+    def backward(ctx, dout):
+        from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
+
+        qkv, out, lse, cu, rng_state = ctx.saved_tensors
+        max_len, heads, kv_heads, head_dim, causal, wl, wr, scale, dropout_p = ctx.args
+        t = qkv.shape[0]
+        nq, nkv = heads * head_dim, kv_heads * head_dim
+        dqkv = torch.empty_like(qkv)
+        views = lambda x: (x[:, :nq].view(t, heads, head_dim), x[:, nq : nq + nkv].view(t, kv_heads, head_dim),
+                           x[:, nq + nkv :].view(t, kv_heads, head_dim))
+        q, k, v = views(qkv)
+        dq, dk, dv = views(dqkv)
+        _flash_attn_varlen_backward(dout.contiguous().view(t, heads, head_dim), q, k, v, out, lse, dq, dk, dv, cu, cu,
+                                    max_len, max_len, dropout_p, scale, causal, wl, wr, 0.0, None, False, rng_state)
+        return dqkv, None, None, None, None, None, None, None, None, None
+
+
+def packed_attention(qkv, cu_seqlens, max_seqlen: int, heads: int, kv_heads: int, head_dim: int, *, causal: bool = True,
+                     window_size: int | None = None, scale: float | None = None, dropout_p: float = 0.0):
+    scale = head_dim**-0.5 if scale is None else scale
+    if _use_flash(qkv):
+        return _PackedFlashAttention.apply(qkv, cu_seqlens.int(), max_seqlen, heads, kv_heads, head_dim, causal,
+                                           window_size, scale, dropout_p)
+    t = qkv.shape[0]
+    nq, nkv = heads * head_dim, kv_heads * head_dim
+    q = qkv[:, :nq].reshape(t, heads, head_dim)
+    k = qkv[:, nq : nq + nkv].reshape(t, kv_heads, head_dim)
+    v = qkv[:, nq + nkv :].reshape(t, kv_heads, head_dim)
+    return attention_reference(q, k, v, cu_seqlens, cu_seqlens, causal, window_size, scale).reshape(t, nq)

@@ -70,7 +70,11 @@ def cross_entropy_forward_backward(logits: torch.Tensor, labels: torch.Tensor, g
     grad = None
     gs_val, gs_ptr = 1.0, None
     if grad_scale is not None:
-        grad = logits if in_place else torch.empty_like(logits)
+        if in_place:
+            grad = logits
+        else:
+            pad = 8 if logits.dtype == torch.bfloat16 else 4
+            grad = torch.empty(rows, (cols + pad - 1) // pad * pad, dtype=logits.dtype, device=logits.device)[:, :cols]
         if torch.is_tensor(grad_scale):
             gs_ptr = grad_scale.float().contiguous()
         else:

@@ -1,0 +1,98 @@
+"""Linear layers with hand-written backward passes and tensor / sequence parallel collectives.
+
+    linear(x, W, b)                        y = x W^T + b
+    mode "output" (column parallel)        W split along its output rows; with sequence parallelism the input holds
+                                           T/tp tokens and is all-gathered first, and the input gradient is
+                                           reduce-scattered (all-reduced without SP)
+    mode "input"  (row parallel)           W split along its input columns; the partial outputs are reduce-scattered
+                                           (SP) or all-reduced, the bias is added after the reduction
+`transposed_weight` stores W as [in, out] (the MLP's second layer).  Weight gradients are accumulated by the GEMM
+epilogue straight into the parameter's gradient buffer.  Parity: `fast_llm/functional/linear.py:27-273`.
+"""
+
+import torch
+
+from fast_llm_b200.ops.gemm import matmul_nn, matmul_nt, matmul_tn
+from fast_llm_b200.ops.param_grad import accumulate_param_grad, wgrad_target
+from fast_llm_b200.parallel.ops import gather_op, reduce_op, reduce_scatter_op
+
+
+def _forward_matmul(x2, weight, transposed_weight):
+    return matmul_nn(x2, weight) if transposed_weight else matmul_nt(x2, weight)
+
+
+def _dgrad(dy2, weight, transposed_weight):
+    return matmul_nt(dy2, weight) if transposed_weight else matmul_nn(dy2, weight)
+
+
+def weight_grad(dy2: torch.Tensor, x2: torch.Tensor, weight: torch.Tensor, transposed_weight: bool):
+    """Accumulate dW into the gradient buffer (returns None) or return it for autograd."""
+    buf, accumulate = wgrad_target(weight)
+    a, b = (x2, dy2) if transposed_weight else (dy2, x2)
+    if buf is not None:
+        matmul_tn(a, b, out=buf.view(weight.shape), accumulate=accumulate)
+        return None
+    return matmul_tn(a, b, out_dtype=weight.dtype)
+
+
+def bias_grad(dy2: torch.Tensor, bias: torch.Tensor):
+    return accumulate_param_grad(bias, dy2.sum(0, dtype=torch.float32).to(bias.dtype) if dy2.dtype != torch.float32 else dy2.sum(0))
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, transposed_weight, mode, group, sequence_parallel):
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        x_in = x2
+        if mode == "output" and sequence_parallel and group is not None:
+            x2 = gather_op(x2, group, 0)
+        y = _forward_matmul(x2, weight, transposed_weight)
+        if mode == "input" and group is not None:
+            y = reduce_scatter_op(y, group, dim=0) if sequence_parallel else reduce_op(y, group)
+        if bias is not None:
+            y = y + bias
+        ctx.save_for_backward(x_in, weight, bias)
+        ctx.args = (transposed_weight, mode, group, sequence_parallel, shape)
+        return y.view(*shape[:-1], y.shape[-1]) if y.shape[0] == x_in.shape[0] else y.view(-1, y.shape[-1]) if len(shape) == 2 else y.view(*_lead_shape(shape, y.shape[0]), y.shape[-1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_in, weight, bias = ctx.saved_tensors
+        transposed_weight, mode, group, sequence_parallel, shape = ctx.args
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        db = bias_grad(dy2, bias) if bias is not None else None
+        x2 = x_in
+        if mode == "input" and sequence_parallel and group is not None:
+            dy2 = gather_op(dy2, group, 0)
+        gather_handle = None
+        if mode == "output" and sequence_parallel and group is not None:
+            x2, gather_handle = gather_op(x_in, group, 0, async_op=True)
+        dx = _dgrad(dy2, weight, transposed_weight) if ctx.needs_input_grad[0] else None
+        reduce_handle = None
+        if dx is not None and mode == "output" and group is not None:
+            if sequence_parallel:
+                dx, reduce_handle = reduce_scatter_op(dx, group, dim=0, async_op=True)
+            else:
+                dx, reduce_handle = reduce_op(dx, group, async_op=True)
+        if gather_handle is not None:
+            gather_handle.wait()
+        dw = weight_grad(dy2, x2, weight, transposed_weight) if weight.requires_grad or getattr(weight, "grad_buffer", None) is not None else None
+        if reduce_handle is not None:
+            reduce_handle.wait()
+        if dx is not None:
+            dx = dx.view(shape) if dx.numel() == x_in.numel() else dx
+        return dx, dw, db, None, None, None, None
+
+
+def _lead_shape(shape, rows):
+    # [batch, seq, h] inputs whose token count changed through a collective: keep a flat token dimension
+    return (rows,)
+
+
+def linear(x, weight, bias=None, *, transposed_weight: bool = False, mode: str = "none", group=None,
+           sequence_parallel: bool = False):
+    """Differentiable linear layer; see the module docstring for `mode`."""
+    return _Linear.apply(x, weight, bias, transposed_weight, mode, group, sequence_parallel)

@@ -30,6 +30,10 @@ def wgrad_target(param: torch.Tensor) -> tuple[torch.Tensor | None, bool]:
     """(buffer to accumulate a weight gradient into, whether to add to its current content)."""
     if not has_grad_buffer(param):
         return None, False
-    accumulate = not getattr(param, "param_grad_is_zero", False)
-    param.param_grad_is_zero = False
-    return param.grad_buffer, accumulate
+    # A joint view over several neighbouring parameters (fused QKV) tracks the state of its sources.
+    sources = getattr(param, "_sources", None) or (param,)
+    zero = [getattr(s, "param_grad_is_zero", False) for s in sources]
+    assert all(zero) or not any(zero), "fused parameters must be accumulated together"
+    for s in sources:
+        s.param_grad_is_zero = False
+    return param.grad_buffer, not zero[0]

@@ -107,7 +107,7 @@ def bench_elementwise(results):
 
 def main(argv):
     results = []
-    which = [a for a in argv if not a.startswith("--")] or ["gemm", "elementwise"]
+    which = [a for a in argv if a in ("gemm", "elementwise")] or ["gemm", "elementwise"]
     if "gemm" in which:
         bench_gemm(results)
     if "elementwise" in which:
