@@ -1,0 +1,349 @@
+"""Headline benchmark: Mistral-7B pre-training throughput (tokens/s), bf16, 8192-token micro-batches, 256k-token
+global batch, ZeRO-1 data parallelism over N GPUs of one node, synthetic uniform-random tokens, random init.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
+
+Prints ONE JSON line on rank 0.  `value` is the whole-job tokens/s from CUDA events around K optimizer steps (max over
+ranks) with device-resident inputs; `e2e` repeats the measurement through the trainer's own data path: every step's
+inputs come from pinned host memory (H2D) and the step's loss is read back (D2H).  `--impl reference` runs the
+unmodified reference installed under baseline/_ref through its own trainer on the same config.
+"""
+
+import argparse
+import json
+import os
+import pathlib
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = pathlib.Path(__file__).resolve().parent
+PUBLISHED_TOKENS_PER_SEC_PER_GPU = 9800.0  # reference README: Mistral-7B on 32 x H100
+GLOBAL_BATCH_TOKENS = 262144
+MICRO_BATCH_TOKENS = 8192
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=int(os.environ.get("WORLD_SIZE", 1)))
+    p.add_argument("--steps", type=int, default=3)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--layers", type=int, default=32, help="debug only: any value other than 32 marks the result invalid")
+    p.add_argument("--global-batch-tokens", type=int, default=GLOBAL_BATCH_TOKENS)
+    p.add_argument("--no-e2e", action="store_true")
+    return p.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self._gpu = gpu_index
+        self._proc = None
+        self._path = ROOT / "gpurun_out" / f"clocks_bench_{gpu_index}.csv"
+
+    def start(self):
+        try:
+            self._path.parent.mkdir(exist_ok=True)
+            self._file = open(self._path, "w")
+            self._proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                                           "-i", str(self._gpu)], stdout=self._file, stderr=subprocess.DEVNULL)
+        except Exception:
+            self._proc = None
+
+    def stop(self) -> dict:
+        if self._proc is None:
+            return {}
+        self._proc.terminate()
+        try:
+            self._proc.wait(timeout=5)
+        except Exception:
+            self._proc.kill()
+        self._file.close()
+        clocks, max_clocks, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self._path.read_text().splitlines():
+            cells = [c.strip() for c in line.split(",")]
+            if len(cells) < 9:
+                continue
+            try:
+                clocks.append(float(cells[1]))
+                max_clocks.append(float(cells[2]))
+            except ValueError:
+                continue
+            for name, cell in zip(names, cells[5:9]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        if not clocks:
+            return {}
+        return {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max(max_clocks), "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def _dist_env(args):
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            # convenience: relaunch under torchrun
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1",
+                   "--master-port", os.environ.get("MASTER_PORT", "29533"), str(pathlib.Path(__file__).resolve()), *sys.argv[1:]]
+            raise SystemExit(subprocess.call(cmd))
+        raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    os.environ.setdefault("LOCAL_WORLD_SIZE", str(world))
+    return rank, world, local_rank
+
+
+def _max_over_ranks(value: float, world: int) -> float:
+    import torch
+
+    if world == 1:
+        return value
+    t = torch.tensor([value], dtype=torch.float64, device="cuda")
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return t.item()
+
+
+def _barrier(world: int):
+    import torch
+
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+
+
+def _time_steps(step_fn, steps: int, world: int) -> float:
+    """Milliseconds per step: CUDA events on the launching stream around exactly `steps` steps, max over ranks."""
+    import torch
+
+    _barrier(world)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(steps):
+        step_fn(i)
+    end.record()
+    _barrier(world)
+    return _max_over_ranks(start.elapsed_time(end), world) / steps
+
+
+def config_updates(args, world: int) -> dict:
+    depth = args.global_batch_tokens // MICRO_BATCH_TOKENS // world
+    return {
+        ("model", "multi_stage", "zero_stage"): 1,
+        ("schedule", "depth_first_micro_batches"): depth,
+        ("training", "train_iters"): 2 * (args.warmup + args.steps) + 2,
+        ("training", "num_workers"): 2,
+        ("training", "logs", "interval"): 10**9,
+        ("training", "evaluators"): {},
+        ("run", "experiment_dir"): None,
+        ("model", "base_model", "decoder", "num_blocks"): args.layers,
+    }
+
+
+def result_line(args, world, ms_per_step, clocks, launches, e2e, impl, extra=None):
+    tokens = args.global_batch_tokens
+    value = tokens / (ms_per_step / 1e3)
+    line = {
+        "metric": "tokens/s, Mistral-7B 8k-token micro-batch, 256k-token global batch (whole job)",
+        "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": value / world / PUBLISHED_TOKENS_PER_SEC_PER_GPU, "tokens_per_sec_per_gpu": value / world,
+        "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights", "impl": impl,
+        "config": {"model": "Mistral-7B (32 layers, hidden 4096, 32/8 heads, SwiGLU 14336, vocab 32000, window 4096)" if args.layers == 32 else f"INVALID: {args.layers} layers",
+                   "global_batch": tokens, "seq_len": MICRO_BATCH_TOKENS, "micro_batch_tokens": MICRO_BATCH_TOKENS,
+                   "parallelism": f"dp{world} ZeRO-1, {tokens // MICRO_BATCH_TOKENS // world} sequential micro-batches",
+                   "l2": "no explicit flush: every step streams > 100 GB of weights, gradients and activations per GPU (L2 is 126 MB)"},
+        "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
+    }
+    if extra:
+        line.update(extra)
+    return line
+
+
+def run_ours(args):
+    os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+    rank, world, local_rank = _dist_env(args)
+    import torch
+    import yaml
+
+    sys.path.insert(0, str(ROOT))
+    import fast_llm_b200.models.auto  # noqa: F401
+    from fast_llm_b200.models.gpt.trainer import GPTTrainerConfig
+    from fast_llm_b200.ops import _lib
+    from fast_llm_b200.parallel.distributed import Distributed
+    from fast_llm_b200.parallel.topology import PhaseType
+
+    torch.cuda.set_device(local_rank)
+    base = yaml.safe_load((ROOT / "examples" / "mistral.yaml").read_text())
+    config = GPTTrainerConfig.from_dict(base, config_updates(args, world))
+    config.validate()
+    distributed = Distributed(config.model.distributed)
+    run = config.get_run(distributed)
+    trainer = config.get_trainer_class()(config=config)
+    with run:
+        trainer.setup(distributed, run)
+        trainer._prepare_training_state()
+        schedule = trainer._schedules[PhaseType.training]
+        runner = trainer.runner
+        samples_per_step = schedule.samples_per_batch
+        state = {"iteration": 0}
+
+        # ---- device-resident inputs: one preprocessed micro-batch per sequential slot, reused every step
+        iterator = trainer._data.get_iterator("training", consumed_samples=0, num_workers=2)
+        resident = []
+        for _ in range(config.schedule.sequential_micro_batches):
+            resident.append(trainer.multi_stage.base_model.preprocess_batch(next(iterator), phase=PhaseType.training, iteration=1,
+                                                                            device=distributed.device))
+        torch.cuda.synchronize()
+
+        def resident_iter():
+            while True:
+                for item in resident:
+                    # kwargs are consumed (label counts cached, etc.): hand out shallow copies
+                    yield [(tokens, dict(kwargs)) for tokens, kwargs in item]
+
+        res_it = resident_iter()
+        loss_box = {}
+
+        def step_resident(_):
+            state["iteration"] += 1
+            losses, ok, _m = runner.run_step(res_it, schedule, iteration=state["iteration"], preprocessed=True)
+            loss_box.update(losses)
+
+        for i in range(args.warmup):
+            step_resident(i)
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        launches_before = _lib.launch_count
+        ms = _time_steps(step_resident, args.steps, world)
+        launches = _lib.launch_count - launches_before
+        clocks = sampler.stop() if rank == 0 else {}
+
+        # ---- end to end: the trainer's own data path (pinned host memory -> device every step, loss read back)
+        e2e = None
+        if not args.no_e2e:
+            data_it = trainer._data.get_iterator("training", consumed_samples=samples_per_step, num_workers=2)
+            probe = next(data_it)
+            h2d = sum(inp.nbytes() for inp in probe) * config.schedule.sequential_micro_batches
+            d2h = 4 * max(len(runner._loss_definitions), 1)
+
+            def step_e2e(_):
+                state["iteration"] += 1
+                losses, ok, _m = runner.run_step(data_it, schedule, iteration=state["iteration"])
+                loss_box.update(losses)
+
+            # the probe consumed one micro-batch; a short warm-up refills the prefetch queue
+            step_e2e(0)
+            ms_e2e = _time_steps(step_e2e, args.steps, world)
+            e2e = {"value": args.global_batch_tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                   "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                   "how": "Trainer data iterator (pinned host batches) -> ScheduleRunner.run_step -> loss.item()"}
+        from fast_llm_b200.ops.gemm import check_device_errors
+
+        check_device_errors()
+        peak = torch.cuda.max_memory_allocated() / 2**30
+    if rank == 0:
+        extra = {"final_loss": loss_box.get("lm_loss"), "peak_memory_gib": peak}
+        print(json.dumps(result_line(args, world, ms, clocks, launches, e2e, "ours", extra)), flush=True)
+    distributed.shutdown()
+
+
+def run_reference(args):
+    ref = ROOT / "baseline" / "_ref"
+    if not (ref / "fast_llm" / "engine").is_dir():
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is missing or incomplete (offline install not present)"}))
+        return
+    os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+    os.environ.setdefault("PYTHONHASHSEED", "0")
+    rank, world, local_rank = _dist_env(args)
+    sys.path.insert(0, str(ref))
+    try:
+        import torch
+        import yaml
+
+        torch.cuda.set_device(local_rank)
+        dynamo_ok = True
+        try:
+            torch.compile(lambda x: x * 2 + 1)(torch.ones(8, device="cuda"))
+        except Exception:
+            dynamo_ok = False
+        if not dynamo_ok:
+            os.environ["TORCHDYNAMO_DISABLE"] = "1"
+        import fast_llm.data.auto  # noqa: F401
+        import fast_llm.models.auto  # noqa: F401
+        from fast_llm.engine.distributed.config import PhaseType
+        from fast_llm.engine.distributed.distributed import Distributed
+        from fast_llm.models.gpt.config import GPTTrainerConfig
+
+        base = yaml.safe_load((ref / "examples" / "mistral.yaml").read_text())
+        updates = config_updates(args, world)
+        updates[("run", "torch_dynamo_enable")] = dynamo_ok
+        config = GPTTrainerConfig.from_dict(base, updates)
+        config.validate()
+        distributed = Distributed(config.model.distributed)
+        run = config.get_run(distributed)
+        trainer = config.get_trainer_class()(config=config)
+        times = []
+        with run:
+            trainer.setup(distributed, run)
+            # Time every call of the reference's own ScheduleRunner.run_step from the outside (its code is untouched).
+            inner = trainer._runner.run_step
+            total = args.warmup + args.steps
+            events = []
+
+            def timed_run_step(*a, **k):
+                n = len(events)
+                if n == args.warmup:
+                    _barrier(world)
+                start = torch.cuda.Event(enable_timing=True)
+                start.record()
+                out = inner(*a, **k)
+                end = torch.cuda.Event(enable_timing=True)
+                end.record()
+                events.append((start, end))
+                return out
+
+            trainer._runner.run_step = timed_run_step
+            sampler = ClockSampler(local_rank)
+            if rank == 0:
+                sampler.start()
+            object.__setattr__(config.training, "train_iters", total) if False else None
+            trainer.run()
+            _barrier(world)
+            clocks = sampler.stop() if rank == 0 else {}
+        timed = events[args.warmup : args.warmup + args.steps]
+        if len(timed) < args.steps:
+            raise RuntimeError(f"reference ran {len(events)} steps, expected at least {args.warmup + args.steps}")
+        span = timed[0][0].elapsed_time(timed[-1][1])
+        ms = _max_over_ranks(span, world) / args.steps
+        if rank == 0:
+            e2e = {"value": args.global_batch_tokens / (ms / 1e3), "unit": "tokens/s", "ms_per_step": ms,
+                   "how": "reference Trainer.run(): its own data loader (H2D) and loss reduction (D2H) are inside every step"}
+            extra = {"torch_dynamo_enable": dynamo_ok, "peak_memory_gib": torch.cuda.max_memory_allocated() / 2**30,
+                     "note": "apex / mamba_ssm absent: the reference uses its torch fallbacks for fused Adam and norms"}
+            print(json.dumps(result_line(args, world, ms, clocks, None, e2e, "reference", extra)), flush=True)
+    except Exception as e:  # report, do not crash the driver
+        msg = f"{type(e).__name__}: {str(e).splitlines()[0] if str(e) else ''}"[:300]
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": msg, "n_gpus": world}), flush=True)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

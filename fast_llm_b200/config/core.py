@@ -314,6 +314,11 @@ class Config:
                 self._explicit_fields.add(name)
             else:
                 value = field.make_default()
+                if value is MISSING:
+                    # nested configs always exist: default-construct them (concrete default of a registry base)
+                    nested = _config_class_of(self._type_hints().get(name))
+                    if nested is not None:
+                        value = nested._get_default_subclass()()
             object.__setattr__(self, name, value)
         if kwargs:
             raise TypeError(f"Unknown fields for {type(self).__name__}: {sorted(kwargs)}")

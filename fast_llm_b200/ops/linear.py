@@ -54,7 +54,7 @@ class _Linear(torch.autograd.Function):
             y = y + bias
         ctx.save_for_backward(x_in, weight, bias)
         ctx.args = (transposed_weight, mode, group, sequence_parallel, shape)
-        return y.view(*shape[:-1], y.shape[-1]) if y.shape[0] == x_in.shape[0] else y.view(-1, y.shape[-1]) if len(shape) == 2 else y.view(*_lead_shape(shape, y.shape[0]), y.shape[-1])
+        return y
 
     @staticmethod
     def backward(ctx, dy):
@@ -82,17 +82,15 @@ class _Linear(torch.autograd.Function):
         dw = weight_grad(dy2, x2, weight, transposed_weight) if weight.requires_grad or getattr(weight, "grad_buffer", None) is not None else None
         if reduce_handle is not None:
             reduce_handle.wait()
-        if dx is not None:
-            dx = dx.view(shape) if dx.numel() == x_in.numel() else dx
         return dx, dw, db, None, None, None, None
-
-
-def _lead_shape(shape, rows):
-    # [batch, seq, h] inputs whose token count changed through a collective: keep a flat token dimension
-    return (rows,)
 
 
 def linear(x, weight, bias=None, *, transposed_weight: bool = False, mode: str = "none", group=None,
            sequence_parallel: bool = False):
     """Differentiable linear layer; see the module docstring for `mode`."""
-    return _Linear.apply(x, weight, bias, transposed_weight, mode, group, sequence_parallel)
+    # Flatten outside the autograd node so its output is a fresh tensor (rotary later rotates it in place).
+    lead = x.shape[:-1]
+    y = _Linear.apply(x.reshape(-1, x.shape[-1]), weight, bias, transposed_weight, mode, group, sequence_parallel)
+    if len(lead) != 1 and y.shape[0] == lead.numel():
+        y = y.view(*lead, y.shape[-1])
+    return y
