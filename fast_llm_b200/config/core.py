@@ -473,7 +473,10 @@ class Config:
         return out
 
     def to_copy(self, *updates, strict: bool = True, update_type: UpdateType = UpdateType.override):
-        return type(self).from_dict(self, *updates, strict=strict, update_type=update_type)
+        out = type(self).from_dict(self, *updates, strict=strict, update_type=update_type)
+        if self._validated:
+            out.validate()
+        return out
 
     def to_serialized(self, verbose: int | None = FieldVerboseLevel.core) -> dict:
         return self.to_dict(verbose, serialized=True)

@@ -32,7 +32,7 @@ class RunnableConfig(Config):
                 sub = None
             if sub is not None and sub is not cls:
                 return sub.parse_and_run(args[1:])
-            if sub is None:
+            if sub is None and cls._abstract:
                 raise KeyError(f"Unknown sub-command {args[0]!r} for {cls.__name__}")
         parsed, unparsed = cls._get_parser().parse_known_args(args)
         with NoAutoValidate():

@@ -29,7 +29,10 @@ class FastLLMModel(MultiStageModel):
     def load_checkpoint(self, config: CheckpointLoadConfig) -> dict | None:
         config.validate()
         config.setup(type(self._config))
-        handler = config.format.get_handler_class()(self)
+        handler_class = config.format.get_handler_class()
+        if hasattr(handler_class, "resolve"):  # `auto` formats pick the concrete handler from the files
+            handler_class = handler_class.resolve(config.path)
+        handler = handler_class(self)
         metadata = handler.load(config)
         self._finalize_load(reset_optimizer=not config.optimizer_state)
         return metadata

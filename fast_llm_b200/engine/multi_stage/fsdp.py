@@ -226,9 +226,12 @@ class FSDP:
     def restore_parameters(self) -> None:
         """Rebuild the compute-dtype weight buffer from the fp32 shards (copy own slice, all-gather the rest)."""
         assert self._mode.support_forward
-        self._weight_buffer_local_shard.copy_(self._weight_shard)
-        if self._fsdp_dim.size > 1:
-            all_gather_into_tensor(self._weight_buffer, self._weight_buffer_local_shard, group=self._fsdp_group)
+        # A shared buffer is re-filled between a stage's forward and backward with the very same values; keep the
+        # version counter so tensors saved for backward (views of this buffer) stay valid for autograd.
+        with torch.autograd._unsafe_preserve_version_counter(self._weight_buffer):
+            self._weight_buffer_local_shard.copy_(self._weight_shard)
+            if self._fsdp_dim.size > 1:
+                all_gather_into_tensor(self._weight_buffer, self._weight_buffer_local_shard, group=self._fsdp_group)
 
     # ---- gradients
     def reset_gradients(self) -> None:

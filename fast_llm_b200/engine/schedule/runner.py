@@ -186,7 +186,7 @@ class ScheduleRunner:
                 kwargs[BlockKwargs.presents] = []
         output, ctx = stage.forward(input_, kwargs, context.losses, context.metrics)
         presents = kwargs.get(BlockKwargs.presents) if splits > 1 else None
-        if presents:
+        if presents is not None:
             training = context.schedule.phase.is_training
             context.kv_leaves[step.key] = [kv.detach().requires_grad_(training) for kv in presents]
         if context.schedule.phase.is_training:

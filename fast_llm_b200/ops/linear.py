@@ -52,13 +52,17 @@ class _Linear(torch.autograd.Function):
             y = reduce_scatter_op(y, group, dim=0) if sequence_parallel else reduce_op(y, group)
         if bias is not None:
             y = y + bias
-        ctx.save_for_backward(x_in, weight, bias)
+        # Parameters are views of buffers that ZeRO-3 re-fills between forward and backward (with the same values):
+        # keep them as plain attributes so autograd's version check does not fire.
+        ctx.save_for_backward(x_in)
+        ctx.weight, ctx.bias = weight, bias
         ctx.args = (transposed_weight, mode, group, sequence_parallel, shape)
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x_in, weight, bias = ctx.saved_tensors
+        (x_in,) = ctx.saved_tensors
+        weight, bias = ctx.weight, ctx.bias
         transposed_weight, mode, group, sequence_parallel, shape = ctx.args
         dy2 = dy.reshape(-1, dy.shape[-1])
         if not dy2.is_contiguous():

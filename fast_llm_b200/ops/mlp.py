@@ -72,14 +72,15 @@ class _MLP(torch.autograd.Function):
         if b2 is not None:
             y = y + b2
         keep_input = x_in if (recompute.recompute_sparse_input or (sequence_parallel and group is not None)) else x2
-        ctx.save_for_backward(keep_input, w1, b1, w2, b2, None if recompute.recompute_layer_1 else h,
-                              None if recompute.recompute_activation else a)
+        ctx.save_for_backward(keep_input, None if recompute.recompute_layer_1 else h, None if recompute.recompute_activation else a)
+        ctx.params = (w1, b1, w2, b2)  # buffer views: kept outside autograd's version tracking (ZeRO-3 re-gathers them)
         ctx.args = (gated, act, group, sequence_parallel, recompute, shape)
         return y.view(*shape[:-1], y.shape[-1]) if y.shape[0] == x_in.shape[0] else y
 
     @staticmethod
     def backward(ctx, dy):
-        x_saved, w1, b1, w2, b2, h, a = ctx.saved_tensors
+        x_saved, h, a = ctx.saved_tensors
+        w1, b1, w2, b2 = ctx.params
         gated, act, group, sequence_parallel, recompute, shape = ctx.args
         dy2 = dy.reshape(-1, dy.shape[-1])
         if not dy2.is_contiguous():

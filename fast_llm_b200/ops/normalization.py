@@ -92,7 +92,8 @@ class _NormFunction(torch.autograd.Function):
         delta2 = None if delta is None else delta.reshape(-1, shape[-1])
         res, y, rstd, mean = _fwd_native(x2.contiguous(), None if delta2 is None else delta2.contiguous(), weight, bias,
                                          eps, zero_centered, layer_norm)
-        ctx.save_for_backward(x2 if res is None else res, weight, bias, rstd, mean)
+        ctx.save_for_backward(x2 if res is None else res, rstd, mean)
+        ctx.params = (weight, bias)
         ctx.args = (zero_centered, layer_norm, shape, delta is not None)
         if delta is None:
             return y.view(shape)
@@ -100,7 +101,8 @@ class _NormFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, *grads):
-        x2, weight, bias, rstd, mean = ctx.saved_tensors
+        x2, rstd, mean = ctx.saved_tensors
+        weight, bias = ctx.params
         zero_centered, layer_norm, shape, has_delta = ctx.args
         if has_delta:
             dres, dy = grads

@@ -68,7 +68,8 @@ class _Embedding(torch.autograd.Function):
         _lib.check(_lib.get_lib().flb_embedding_fwd(ids.data_ptr(), weight.data_ptr(), out.data_ptr(), ids.numel(),
                                                     weight.shape[1], vocab_begin, vocab_end, scale, _lib.stream_ptr()), "flb_embedding_fwd")
         _lib.count_launch()
-        ctx.save_for_backward(ids, weight)
+        ctx.save_for_backward(ids)
+        ctx.weight = weight
         ctx.args = (vocab_begin, vocab_end, scale)
         return out
 
@@ -76,7 +77,8 @@ class _Embedding(torch.autograd.Function):
     def backward(ctx, grad):
         from fast_llm_b200.ops.param_grad import has_grad_buffer
 
-        ids, weight = ctx.saved_tensors
+        (ids,) = ctx.saved_tensors
+        weight = ctx.weight
         vocab_begin, vocab_end, scale = ctx.args
         grad = grad.contiguous()
         target = None

@@ -1,0 +1,173 @@
+"""End-to-end training on CPU: loss goes down, schedules are equivalent, checkpoints resume bit-exactly,
+formats round-trip and match Hugging Face transformers numerically."""
+
+import copy
+import json
+import pathlib
+
+import pytest
+import torch
+
+from tests.common import build_trainer, tiny_trainer_config, train_steps
+
+
+def test_loss_decreases():
+    trainer, _ = build_trainer(tiny_trainer_config({("optimizer", "learning_rate", "base"): 3e-3}))
+    losses = train_steps(trainer, 8)
+    assert all(l == l for l in losses)
+    assert losses[0] > 6.0  # ~ln(512)
+    assert losses[-1] < losses[0] - 0.02
+
+
+@pytest.mark.parametrize("schedule", [{"depth_first_micro_batches": 4}, {"breadth_first_micro_batches": 4},
+                                      {"depth_first_micro_batches": 2, "breadth_first_micro_batches": 2}])
+def test_micro_batch_schedules_are_equivalent(schedule):
+    """Gradient accumulation order must not matter: df4 == bf4 == df2 x bf2 (same 4 micro-batches per step)."""
+    base, _ = build_trainer(tiny_trainer_config({("schedule", "depth_first_micro_batches"): 4}))
+    ref = train_steps(base, 2)
+    other, _ = build_trainer(tiny_trainer_config({("schedule", k): v for k, v in schedule.items()}))
+    got = train_steps(other, 2)
+    assert got == pytest.approx(ref, rel=1e-5)
+    torch.testing.assert_close(other.multi_stage.get_shard("weights"), base.multi_stage.get_shard("weights"), rtol=1e-4, atol=1e-6)
+
+
+def test_zero_stages_are_equivalent():
+    ref_trainer, _ = build_trainer(tiny_trainer_config({("schedule", "depth_first_micro_batches"): 2}))
+    ref = train_steps(ref_trainer, 2)
+    for stage in (2, 3):
+        t, _ = build_trainer(tiny_trainer_config({("schedule", "depth_first_micro_batches"): 2, ("model", "multi_stage", "zero_stage"): stage}))
+        assert train_steps(t, 2) == pytest.approx(ref, rel=1e-5)
+        torch.testing.assert_close(t.multi_stage.get_shard("weights"), ref_trainer.multi_stage.get_shard("weights"), rtol=1e-4, atol=1e-6)
+
+
+def test_micro_sequences_match_whole_sequence():
+    whole, _ = build_trainer(tiny_trainer_config())
+    ref = train_steps(whole, 2)
+    split, _ = build_trainer(tiny_trainer_config({("schedule", "micro_batch_splits"): 4}))
+    assert train_steps(split, 2) == pytest.approx(ref, rel=2e-4)
+    torch.testing.assert_close(split.multi_stage.get_shard("weights"), whole.multi_stage.get_shard("weights"), rtol=2e-3, atol=2e-5)
+
+
+def test_layers_per_stage_does_not_change_results():
+    a, _ = build_trainer(tiny_trainer_config())
+    b, _ = build_trainer(tiny_trainer_config({("model", "multi_stage", "layers_per_stage"): 2}))
+    assert len(b.multi_stage.stages) < len(a.multi_stage.stages)
+    assert train_steps(b, 2) == pytest.approx(train_steps(a, 2), rel=1e-5)
+
+
+def test_cross_entropy_splits():
+    a, _ = build_trainer(tiny_trainer_config())
+    b, _ = build_trainer(tiny_trainer_config({("model", "base_model", "head", "cross_entropy_splits"): 4}))
+    assert train_steps(b, 2) == pytest.approx(train_steps(a, 2), rel=1e-5)
+
+
+def test_tied_embeddings_gradient_is_sum_of_both_uses():
+    skip = {("schedule", "skip_step"): True}
+    tied, _ = build_trainer(tiny_trainer_config({("model", "base_model", "tied_embedding_weight"): True, **skip}))
+    names = tied.multi_stage.parameter_names
+    assert "head.output_weights" not in names and "embeddings.word_embeddings_weight" in names
+    untied, _ = build_trainer(tiny_trainer_config(skip))
+    # same weights everywhere, head = embedding
+    src = {n: t for n, _, t in tied.multi_stage.get_state_tensor_iterator(("weights",))}
+    for name in untied.multi_stage.parameter_names:
+        untied.multi_stage.import_state_tensor(name, "weights", src.get(name, src["embeddings.word_embeddings_weight"]))
+    untied.multi_stage.invalidate_buffers()
+    loss_tied = train_steps(tied, 1)
+    loss_untied = train_steps(untied, 1)
+    assert loss_tied == pytest.approx(loss_untied, rel=1e-6)
+    g = lambda t, n: t.multi_stage.get_parameter_stage(n).get_parameter_meta(n).tensor.grad_buffer
+    expected = g(untied, "embeddings.word_embeddings_weight") + g(untied, "head.output_weights")
+    torch.testing.assert_close(g(tied, "embeddings.word_embeddings_weight"), expected, rtol=1e-4, atol=1e-7)
+
+
+def test_checkpoint_resume_is_exact(tmp_path):
+    cfg = {("run", "experiment_dir"): str(tmp_path / "exp"), ("training", "checkpoint", "interval"): 2, ("training", "train_iters"): 4}
+    full, _ = build_trainer(tiny_trainer_config(cfg))
+    losses_full = train_steps(full, 4)
+    first, _ = build_trainer(tiny_trainer_config(cfg))
+    train_steps(first, 2)
+    first._completed_steps = 2
+    first._save_checkpoint(first._config.training.checkpoint, {})
+    ckpt = tmp_path / "exp" / "checkpoint" / "2"
+    assert (ckpt / "ok").exists() and (ckpt / "metadata.yaml").exists() and (ckpt / "rank_0.safetensors").exists()
+    resumed, _ = build_trainer(tiny_trainer_config(cfg))
+    assert resumed.completed_steps == 2 and resumed.optimizer.current_step == 2
+    losses_resumed = train_steps(resumed, 2, start=2)
+    assert losses_resumed == losses_full[2:]
+    assert torch.equal(resumed.multi_stage.get_shard("weights"), full.multi_stage.get_shard("weights"))
+    assert torch.equal(resumed.multi_stage.get_shard("exp_avgs_sq"), full.multi_stage.get_shard("exp_avgs_sq"))
+
+
+def _model_from(path, fmt, **updates):
+    from fast_llm_b200.engine.checkpoint.config import CheckpointLoadConfig
+    from fast_llm_b200.engine.multi_stage.config import StageMode
+    from fast_llm_b200.models.gpt.model import GPTModel
+
+    return GPTModel.from_pretrained(CheckpointLoadConfig(path=path, format=fmt), {("distributed", "use_cuda"): False, **updates},
+                                    mode=StageMode.inference, use_cpu=True)
+
+
+def test_format_conversion_chain(tmp_path):
+    """distributed -> fast_llm -> llama (HF) -> fast_llm: weights survive every hop bit-exactly."""
+    from fast_llm_b200.engine.checkpoint.config import CheckpointSaveConfig
+
+    trainer, _ = build_trainer(tiny_trainer_config())
+    train_steps(trainer, 1)
+    model = trainer.multi_stage
+    reference = {n: t.clone() for n, s, t in model.get_state_tensor_iterator(("weights",))}
+    model.save_checkpoint(CheckpointSaveConfig(path=tmp_path / "dist", format="distributed", optimizer_state=True))
+    path, fmt = tmp_path / "dist", "distributed"
+    for hop, next_fmt in enumerate(["fast_llm", "llama", "fast_llm", "distributed"]):
+        loaded = _model_from(path, fmt)
+        got = {n: t for n, s, t in loaded.get_state_tensor_iterator(("weights",))}
+        assert got.keys() == reference.keys()
+        for n in reference:
+            assert torch.equal(got[n], reference[n]), (hop, n)
+        path, fmt = tmp_path / f"hop{hop}", next_fmt
+        loaded.save_checkpoint(CheckpointSaveConfig(path=path, format=fmt))
+    hf_config = json.loads((tmp_path / "hop1" / "config.json").read_text())
+    assert hf_config["model_type"] == "llama" and hf_config["num_key_value_heads"] == 2
+
+
+def test_huggingface_export_matches_transformers(tmp_path):
+    transformers = pytest.importorskip("transformers")
+    from fast_llm_b200.engine.checkpoint.config import CheckpointSaveConfig
+    from fast_llm_b200.engine.inference.runner import InferenceRunner
+
+    trainer, distributed = build_trainer(tiny_trainer_config())
+    train_steps(trainer, 1)
+    trainer.multi_stage.save_checkpoint(CheckpointSaveConfig(path=tmp_path / "hf", format="llama"))
+    hf = transformers.AutoModelForCausalLM.from_pretrained(tmp_path / "hf", torch_dtype=torch.float32)
+    tokens = torch.randint(0, 512, (1, 96))
+    with torch.no_grad():
+        expected = hf(tokens).logits[0]
+    model = _model_from(tmp_path / "hf", "llama")
+    runner = InferenceRunner(model)
+    runner.setup(model.distributed)
+    logits = runner.forward_tokens(tokens[0])
+    torch.testing.assert_close(logits, expected, rtol=2e-4, atol=2e-4)
+    # and the import path: a model created by transformers loads here
+    hf_config = transformers.LlamaConfig(vocab_size=320, hidden_size=48, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                                         num_key_value_heads=2, head_dim=12, rope_theta=5000.0, rms_norm_eps=1e-6, tie_word_embeddings=False)
+    torch.manual_seed(0)
+    hf2 = transformers.LlamaForCausalLM(hf_config)
+    hf2.save_pretrained(tmp_path / "hf2", safe_serialization=True)
+    model2 = _model_from(tmp_path / "hf2", "auto")
+    runner2 = InferenceRunner(model2)
+    runner2.setup(model2.distributed)
+    tokens2 = torch.randint(0, 320, (1, 64))
+    with torch.no_grad():
+        expected2 = hf2(tokens2).logits[0]
+    torch.testing.assert_close(runner2.forward_tokens(tokens2[0]), expected2, rtol=2e-4, atol=2e-4)
+
+
+def test_convert_cli(tmp_path):
+    from fast_llm_b200.cli import fast_llm_main
+    from fast_llm_b200.engine.checkpoint.config import CheckpointSaveConfig
+
+    trainer, _ = build_trainer(tiny_trainer_config())
+    trainer.multi_stage.save_checkpoint(CheckpointSaveConfig(path=tmp_path / "src", format="fast_llm"))
+    fast_llm_main(["convert", "gpt", f"input.path={tmp_path / 'src'}", "input.format=fast_llm", f"output.path={tmp_path / 'dst'}",
+                   "output.format=mistral", "use_cpu=true"])
+    assert (tmp_path / "dst" / "ok").exists() and (tmp_path / "dst" / "config.json").exists()
+    assert json.loads((tmp_path / "dst" / "config.json").read_text())["model_type"] == "mistral"
