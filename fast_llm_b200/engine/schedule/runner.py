@@ -130,7 +130,10 @@ class ScheduleRunner:
                     batch, phase=context.schedule.phase, iteration=context.iteration, metrics=context.metrics,
                     device=self._distributed.device)
             Assert.eq(len(inputs), self._config.micro_batch_splits)
-            grad_output = (self._optimizer.grad_scale if self._optimizer is not None else 1.0) / self._config.sequential_micro_batches
+            # Gradients are averaged over the whole data group, but the sequence-data ranks of one sample hold
+            # partial gradients that must be summed: pre-multiply by their number.
+            grad_output = ((self._optimizer.grad_scale if self._optimizer is not None else 1.0) / self._config.sequential_micro_batches
+                           * self._distributed_config.sequence_data_parallel)
             for _, kwargs in inputs:
                 kwargs[BlockKwargs.grad_output] = grad_output
             context.data[data_index] = inputs

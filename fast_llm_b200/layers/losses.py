@@ -149,11 +149,13 @@ class LanguageModelLoss:
         self._sequence_parallel = distributed_config.sequence_tensor_parallel and not vocab_parallel
         self._group = None
         self._tp_group = None
+        self._sdp_group = None
         self._vocab_begin = 0
 
     def setup(self, distributed, logits_group, vocab_begin: int) -> None:
         self._group = logits_group
         self._tp_group = distributed.tensor_group
+        self._sdp_group = distributed.sequence_data_group
         self._vocab_begin = vocab_begin
 
     def get_loss_definitions(self, count: int = 1) -> list[LossDef]:
@@ -186,10 +188,14 @@ class LanguageModelLoss:
         return kwargs[key]
 
     def _finalize(self, per_token_sum: torch.Tensor) -> torch.Tensor:
-        """Sum partial per-token sums over sequence-parallel shards."""
+        """Sum partial per-token sums over the ranks that share one micro-batch (sequence-parallel token shards,
+        sequence-data-parallel token slices)."""
         if self._sequence_parallel and self._tp_group is not None:
             per_token_sum = per_token_sum.clone()
             all_reduce(per_token_sum, group=self._tp_group)
+        if self._sdp_group is not None:
+            per_token_sum = per_token_sum.clone()
+            all_reduce(per_token_sum, group=self._sdp_group)
         return per_token_sum
 
     def forward_backward(self, logits, kwargs, grad_output, split_index, num_splits, logits_scale, accumulate_into=None):

@@ -156,7 +156,9 @@ def safe_barrier(group: ProcessGroup | None, value: int | str = 1, timeout: floa
     """Barrier that also detects desynchronised ranks: every rank must arrive with the same tag."""
     if group is None:
         return
-    hashed = hash(value) % 2**32
+    import zlib
+
+    hashed = zlib.crc32(str(value).encode())  # stable across processes (str hashes are salted per process)
     with set_timeout(group, timeout):
         total = allreduce_scalar(hashed, dtype=torch.int64, group=group, device=device)
     if total != hashed * group.size():

@@ -32,9 +32,9 @@ def gather_op(x: torch.Tensor, group, dim: int = 0, async_op: bool = False, out:
         out = x.new_empty([n * x.shape[0], *x.shape[1:]]) if out is None else out
         handle = all_gather_into_tensor(out, x, group, async_op=async_op)
         return (out, handle) if async_op else out
-    tmp = x.new_empty([n, *x.shape])
+    tmp = x.new_empty([n * x.shape[0], *x.shape[1:]])
     all_gather_into_tensor(tmp, x, group)
-    res = torch.cat(list(tmp.unbind(0)), dim=dim)
+    res = torch.cat(list(tmp.chunk(n, dim=0)), dim=dim)
     return (res, None) if async_op else res
 
 

@@ -239,6 +239,13 @@ class ParameterMeta:
         assert self.param_init_method is not None, f"No init method for {self.tensor_name}"
         reproducible = distributed.config.reproducible_init if reproducible is None else reproducible
         generator = distributed.tp_init_generator if self.is_tensor_parallel and not reproducible else distributed.pp_init_generator
+        if reproducible:
+            # One private stream per parameter, keyed by its name: the values do not depend on which other
+            # parameters this rank initialises (pipeline / stage splits) nor on how the parameter is sharded.
+            import zlib
+
+            seed = (distributed.config.seed + distributed.config.pp_gen_init_seed_shift + zlib.crc32(self.tensor_name.encode())) % 2**63
+            generator = torch.Generator(device=generator.device).manual_seed(seed)
         if reproducible and self.is_tensor_parallel:
             full = torch.empty(self.global_shape, dtype=torch.float32, device=generator.device)
             self.param_init_method(self, full, generator)

@@ -1,0 +1,57 @@
+"""Parallel layouts on CPU ranks (Gloo): every layout must reproduce the single-process run on the same global batch."""
+
+import pytest
+import torch
+
+from tests.common import build_trainer, tiny_trainer_config, train_steps
+from tests.distributed_utils import run_distributed
+
+STEPS = 2
+
+
+def _single(updates: dict, steps: int = STEPS):
+    trainer, _ = build_trainer(tiny_trainer_config(updates))
+    losses = train_steps(trainer, steps)
+    weights = {n: t.clone() for n, _, t in trainer.multi_stage.get_state_tensor_iterator(("weights",))}
+    return losses, weights
+
+
+def _rank_main(rank, world_size, updates, steps):
+    updates = {**updates, ("model", "distributed", "world_size"): world_size, ("model", "distributed", "rank"): rank,
+               ("model", "distributed", "local_world_size"): world_size, ("model", "distributed", "backend"): "gloo"}
+    trainer, distributed = build_trainer(tiny_trainer_config(updates))
+    losses = train_steps(trainer, steps)
+    # numpy arrays travel by value through the result queue (torch tensors would be shared-memory handles)
+    weights = {n: t.clone().numpy() for n, _, t in trainer.multi_stage.get_state_tensor_iterator(("weights",))}
+    distributed.shutdown()
+    return losses, weights
+
+
+LAYOUTS = {
+    "dp2": (2, {}, {("schedule", "depth_first_micro_batches"): 2}),
+    "dp2_z2": (2, {("model", "multi_stage", "zero_stage"): 2}, {("schedule", "depth_first_micro_batches"): 2}),
+    "dp2_z3": (2, {("model", "multi_stage", "zero_stage"): 3}, {("schedule", "depth_first_micro_batches"): 2}),
+    "dp2_df2": (2, {("schedule", "depth_first_micro_batches"): 2}, {("schedule", "depth_first_micro_batches"): 4}),
+    "tp2": (2, {("model", "distributed", "tensor_parallel"): 2}, {}),
+    "stp2": (2, {("model", "distributed", "tensor_parallel"): 2, ("model", "distributed", "sequence_tensor_parallel"): True}, {}),
+    "stp2_novp": (2, {("model", "distributed", "tensor_parallel"): 2, ("model", "distributed", "sequence_tensor_parallel"): True,
+                      ("model", "base_model", "embeddings", "vocab_parallel"): False}, {}),
+    "sdp2": (2, {("model", "distributed", "sequence_data_parallel"): 2}, {}),
+    "pp2": (2, {("model", "distributed", "pipeline_parallel"): 2, ("schedule", "breadth_first_micro_batches"): 2},
+            {("schedule", "breadth_first_micro_batches"): 2}),
+    "dp2_stp2": (4, {("model", "distributed", "tensor_parallel"): 2, ("model", "distributed", "sequence_tensor_parallel"): True},
+                 {("schedule", "depth_first_micro_batches"): 2}),
+}
+
+
+@pytest.mark.parametrize("name", list(LAYOUTS))
+def test_layout_matches_single_process(name):
+    world_size, parallel_updates, single_updates = LAYOUTS[name]
+    # reproducible_init makes the initial weights independent of the layout
+    common = {("model", "distributed", "reproducible_init"): True}
+    ref_losses, ref_weights = _single({**common, **single_updates})
+    results = run_distributed(_rank_main, world_size, {**common, **parallel_updates}, STEPS)
+    for losses, weights in results:
+        assert losses == pytest.approx(ref_losses, rel=2e-4), name
+        for key, value in weights.items():
+            torch.testing.assert_close(torch.from_numpy(value), ref_weights[key], rtol=2e-3, atol=2e-5, msg=lambda m: f"{name} {key}: {m}")
