@@ -263,7 +263,11 @@ def run_reference(args):
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is missing or incomplete (offline install not present)"}))
         return
     os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
-    os.environ.setdefault("PYTHONHASHSEED", "0")
+    if os.environ.get("PYTHONHASHSEED") != "0":
+        # The reference's barrier compares hash(str) across ranks, which only agrees when string hashing is unsalted;
+        # the salt is fixed at interpreter start, so restart this process with it disabled.
+        os.environ["PYTHONHASHSEED"] = "0"
+        os.execve(sys.executable, [sys.executable, *sys.argv], os.environ)
     rank, world, local_rank = _dist_env(args)
     sys.path.insert(0, str(ref))
     try:

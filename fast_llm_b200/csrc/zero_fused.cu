@@ -1,0 +1,182 @@
+// ZeRO gradient reduction and optimizer step fused with their collectives, over NVLink peer memory.
+//
+// Every data-parallel rank holds the full fp32 (or bf16) gradient buffer of a stage and the full bf16 weight buffer in
+// symmetric memory: the same allocation exists at the same offset on every rank and all of them are mapped into every
+// process (peer pointers).  Two kernels replace reduce-scatter -> copy -> norm -> Adam -> cast -> all-gather:
+//
+//   flb_rs_reduce   rank r sums slice r of ALL ranks' gradient buffers (plain peer loads, fixed rank order, so the
+//                   result is deterministic), scales by 1/dp, writes the fp32 gradient shard and per-CTA partial sums
+//                   of squares for the gradient norm.
+//   flb_adam_push   AdamW on the rank's fp32 shard (weights, moments) and stores the new bf16 weights straight into
+//                   slice r of EVERY rank's weight buffer (peer stores) - the all-gather happens inside the update.
+//
+// Ranks meet through flb_symm_barrier: a one-CTA kernel that writes an epoch number into each peer's signal pad
+// (st.release.sys) and waits (ld.acquire.sys) until every peer has written the same epoch into ours.  The wait is bounded
+// by a clock deadline; on expiry the kernel raises an error word and returns, so a missing peer can never hang the GPU.
+// No multimem / TMA is involved: loads and stores are ordinary global accesses to peer addresses.
+#include "common.cuh"
+
+namespace {
+using namespace flb;
+constexpr int kThreads = 256;
+constexpr int kMaxRanks = 16;
+constexpr long long kBarrierLimitCycles = 20000000000ll;  // about 10 s at boost clock
+
+struct PeerPtrs {
+  void* p[kMaxRanks];
+};
+
+__global__ void symm_barrier_kernel(PeerPtrs signal_pads, int rank, int world, int slot, unsigned epoch, int* err_word) {
+  const int peer = threadIdx.x;
+  if (peer >= world) return;
+  // tell `peer` that this rank reached the barrier: pad layout [slot][source rank]
+  unsigned* remote = reinterpret_cast<unsigned*>(signal_pads.p[peer]) + slot * kMaxRanks + rank;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  const unsigned* local = reinterpret_cast<const unsigned*>(signal_pads.p[rank]) + slot * kMaxRanks + peer;
+  const long long t0 = clock64();
+  for (;;) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local) : "memory");
+    if ((int)(v - epoch) >= 0) break;
+    if (clock64() - t0 > kBarrierLimitCycles) {
+      atomicExch(err_word, 100 + peer);
+      break;
+    }
+    __nanosleep(200);
+  }
+}
+
+template <typename GradT>
+__device__ __forceinline__ float4 load4(const GradT* p, long long i);
+template <>
+__device__ __forceinline__ float4 load4<float>(const float* p, long long i) {
+  return reinterpret_cast<const float4*>(p)[i];
+}
+template <>
+__device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p, long long i) {
+  const uint2 raw = reinterpret_cast<const uint2*>(p)[i];
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
+// grads.p[r]: base of rank r's gradient buffer for this stage (element type GradT); this rank reduces
+// elements [rank*shard, (rank+1)*shard) into grad_shard (fp32).  shard % 4 == 0.
+template <typename GradT>
+__global__ void __launch_bounds__(kThreads)
+rs_reduce_kernel(PeerPtrs grads, int rank, int world, long long shard, float scale, float* __restrict__ grad_shard,
+                 int accumulate, float* __restrict__ sumsq_partial) {
+  __shared__ float scratch[32];
+  const long long nvec = shard >> 2;
+  const long long base = (long long)rank * nvec;
+  float ss = 0.f;
+  for (long long i = blockIdx.x * (long long)kThreads + threadIdx.x; i < nvec; i += (long long)gridDim.x * kThreads) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < world; ++r) {
+      const float4 v = load4<GradT>(reinterpret_cast<const GradT*>(grads.p[r]), base + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+    if (accumulate) {
+      const float4 o = reinterpret_cast<const float4*>(grad_shard)[i];
+      acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w;
+    }
+    reinterpret_cast<float4*>(grad_shard)[i] = acc;
+    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+  }
+  const float t = block_sum(ss, scratch);
+  if (threadIdx.x == 0 && sumsq_partial) sumsq_partial[blockIdx.x] = t;
+}
+
+// AdamW on n fp32 elements; the bf16 result goes to element offset `lp_offset` of every rank's weight buffer.
+__global__ void __launch_bounds__(kThreads)
+adam_push_kernel(float* __restrict__ w, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
+                 PeerPtrs weight_buffers, int world, long long lp_offset, long long n, float lr, float beta1, float beta2,
+                 float eps, float wd, float inv_bc1, float inv_bc2, float gscale, const float* __restrict__ gscale_ptr) {
+  const float sc = gscale * (gscale_ptr ? *gscale_ptr : 1.f);
+  const long long nvec = n >> 2;
+  for (long long i = blockIdx.x * (long long)kThreads + threadIdx.x; i < nvec; i += (long long)gridDim.x * kThreads) {
+    float4 wv = reinterpret_cast<float4*>(w)[i];
+    const float4 gv = reinterpret_cast<const float4*>(g)[i];
+    float4 mv = reinterpret_cast<float4*>(m)[i];
+    float4 vv = reinterpret_cast<float4*>(v)[i];
+    float* wp = &wv.x; const float* gp = &gv.x; float* mp = &mv.x; float* vp = &vv.x;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float gj = gp[j] * sc;
+      mp[j] = beta1 * mp[j] + (1.f - beta1) * gj;
+      vp[j] = beta2 * vp[j] + (1.f - beta2) * gj * gj;
+      wp[j] -= lr * ((mp[j] * inv_bc1) / (sqrtf(vp[j] * inv_bc2) + eps) + wd * wp[j]);
+    }
+    reinterpret_cast<float4*>(w)[i] = wv;
+    reinterpret_cast<float4*>(m)[i] = mv;
+    reinterpret_cast<float4*>(v)[i] = vv;
+    __nv_bfloat162 lo = __floats2bfloat162_rn(wv.x, wv.y), hi = __floats2bfloat162_rn(wv.z, wv.w);
+    const uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    for (int r = 0; r < world; ++r)
+      reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(weight_buffers.p[r]) + lp_offset)[i] = packed;
+  }
+}
+
+int fill_ptrs(PeerPtrs& out, const void* const* ptrs, int world) {
+  if (world < 1 || world > kMaxRanks) return FLB_ERR_TOO_LARGE;
+  for (int i = 0; i < kMaxRanks; ++i) out.p[i] = i < world ? const_cast<void*>(ptrs[i]) : nullptr;
+  return FLB_OK;
+}
+
+}  // namespace
+
+FLB_API int flb_symm_max_ranks() { return kMaxRanks; }
+// Bytes of signal pad each rank must provide (zero-initialised): [slots][kMaxRanks] u32.
+FLB_API int flb_symm_signal_pad_bytes(int slots) { return slots * kMaxRanks * 4; }
+
+// All ranks of the group call this with the same slot and epoch (epochs of a slot must increase).
+FLB_API int flb_symm_barrier(const void* const* signal_pads, int rank, int world, int slot, unsigned epoch, int* err_word,
+                             cudaStream_t stream) {
+  PeerPtrs pads;
+  const int st = fill_ptrs(pads, signal_pads, world);
+  if (st) return st;
+  symm_barrier_kernel<<<1, 32, 0, stream>>>(pads, rank, world, slot, epoch, err_word);
+  FLB_CHECK_LAUNCH();
+  return FLB_OK;
+}
+
+FLB_API int flb_rs_reduce_blocks() { return 148 * 4; }
+
+// grad_ptrs[r]: rank r's gradient buffer of the stage (grad_dtype 0 fp32 / 1 bf16).  sumsq_partial: flb_rs_reduce_blocks()
+// floats (may be null).  Call between two flb_symm_barrier's: peers must have finished writing, and must not overwrite
+// their buffers before every rank has read them.
+FLB_API int flb_rs_reduce(const void* const* grad_ptrs, int grad_dtype, int rank, int world, long long shard, float scale,
+                          float* grad_shard, int accumulate, float* sumsq_partial, cudaStream_t stream) {
+  if (shard % 4) return FLB_ERR_SHAPE;
+  PeerPtrs grads;
+  const int st = fill_ptrs(grads, grad_ptrs, world);
+  if (st) return st;
+  const int blocks = flb_rs_reduce_blocks();
+  if (grad_dtype == 0)
+    rs_reduce_kernel<float><<<blocks, kThreads, 0, stream>>>(grads, rank, world, shard, scale, grad_shard, accumulate, sumsq_partial);
+  else
+    rs_reduce_kernel<__nv_bfloat16><<<blocks, kThreads, 0, stream>>>(grads, rank, world, shard, scale, grad_shard, accumulate, sumsq_partial);
+  FLB_CHECK_LAUNCH();
+  return FLB_OK;
+}
+
+// n % 4 == 0; lp_offset (elements into every rank's bf16 weight buffer) % 4 == 0.
+FLB_API int flb_adam_push(float* w, const float* g, float* m, float* v, const void* const* weight_buffers, int world,
+                          long long lp_offset, long long n, float lr, float beta1, float beta2, float eps, float wd, int step,
+                          float gscale, const float* gscale_ptr, cudaStream_t stream) {
+  if (n <= 0) return FLB_OK;
+  if ((n % 4) || (lp_offset % 4)) return FLB_ERR_SHAPE;
+  PeerPtrs bufs;
+  const int st = fill_ptrs(bufs, weight_buffers, world);
+  if (st) return st;
+  const float inv_bc1 = 1.f / (1.f - powf(beta1, (float)step));
+  const float inv_bc2 = 1.f / (1.f - powf(beta2, (float)step));
+  long long blocks = ((n >> 2) + kThreads - 1) / kThreads;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  adam_push_kernel<<<(int)blocks, kThreads, 0, stream>>>(w, g, m, v, bufs, world, lp_offset, n, lr, beta1, beta2, eps, wd,
+                                                          inv_bc1, inv_bc2, gscale, gscale_ptr);
+  FLB_CHECK_LAUNCH();
+  return FLB_OK;
+}

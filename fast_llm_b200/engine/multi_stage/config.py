@@ -69,6 +69,7 @@ class MultiStageConfig(StageConfig):
     num_weight_buffers: int | None = Field(default=None, desc="Shared weight buffers (default from zero_stage).", hint=FieldHint.expert, valid=skip_valid_if_none(check_field(Assert.geq, 1)))
     num_grad_buffers: int | None = Field(default=None, desc="Shared gradient buffers (default from zero_stage).", hint=FieldHint.expert, valid=skip_valid_if_none(check_field(Assert.geq, 1)))
     zero_stage: int | None = Field(default=None, desc="ZeRO stage 1, 2 or 3.", hint=FieldHint.performance)
+    fused_collectives: bool = Field(default=True, desc="Keep ZeRO weight/gradient buffers in NVLink symmetric memory and run the gradient reduction and the optimizer update as kernels fused with their collectives (GPU, data_parallel > 1, ZeRO-1/2 with per-stage buffers).", hint=FieldHint.performance)
     pipeline_delay: float = Field(default=0.0, desc="Estimated pipeline communication delay in units of a stage's compute time.", hint=FieldHint.expert, valid=check_field(Assert.geq, 0))
 
     def _validate(self):

@@ -67,6 +67,7 @@ class FSDP:
         self._mode = StageMode.off_device
         self._is_setup = False
         self._grad_shard_is_buffer = False
+        self._weight_arena = self._grad_arena = None
 
     # ---- layout queries
     @property
@@ -140,6 +141,10 @@ class FSDP:
         begin = min(max(self._parameter_begins_in_buffer[name] - shard_begin, 0), self._shard_size)
         end = min(max(self._parameter_ends_in_buffer[name] - shard_begin, 0), self._shard_size)
         return begin, end
+
+    def set_symmetric_arenas(self, weight_arena, grad_arena) -> None:
+        """Buffers live in NVLink symmetric memory: reductions and weight updates use the fused peer-memory kernels."""
+        self._weight_arena, self._grad_arena = weight_arena, grad_arena
 
     # ---- memory binding
     def setup(self, mode: StageMode, weight_shard: torch.Tensor | None, grad_shard: torch.Tensor | None,
@@ -254,8 +259,16 @@ class FSDP:
                 param.param_grad_is_zero = False
         if self._sp_end > self._sp_begin and self._tensor_group is not None:
             all_reduce(self._grad_buffer[self._sp_begin : self._sp_end], group=self._tensor_group)
+        if self._fsdp_dim.size > 1 and getattr(self, "_grad_arena", None) is not None:
+            # Fused path: after a bounded barrier (every rank finished this stage's backward) each rank sums its slice of
+            # all ranks' gradient buffers straight out of peer memory into its fp32 gradient shard.
+            from fast_llm_b200.parallel.symmetric import rs_reduce
+
+            self._grad_arena.barrier(0)
+            rs_reduce(self._grad_arena, self._grad_buffer, self._grad_shard, self._shard_size, 1.0 / self._fsdp_dim.size,
+                      accumulate, None)
+            return
         if self._fsdp_dim.size > 1:
-            out = self._grad_buffer_local_shard if self._grad_buffer_dtype == self._shard_dtype or True else None
             reduce_scatter_tensor(self._grad_buffer_local_shard, self._grad_buffer, op=torch.distributed.ReduceOp.AVG, group=self._fsdp_group)
         if self._grad_shard_is_buffer:
             assert not accumulate or self._fsdp_dim.size == 1

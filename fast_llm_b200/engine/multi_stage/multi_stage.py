@@ -172,20 +172,44 @@ class MultiStageModel:
         if mode.support_backward and not dp1_alias:
             self._shards[ShardName.grads] = allocator(grad_total, shard_dtype, "grads_shard")
 
-        # ---- buffers
-        weight_buffers, grad_buffers = {}, {}
+        # ---- buffers (in NVLink symmetric memory when the fused ZeRO kernels will use them)
+        from fast_llm_b200.parallel.symmetric import SymmetricArena, symmetric_memory_available
+
+        self._weight_arena = self._grad_arena = None
+        use_symmetric = (
+            ms.fused_collectives and mode.support_backward and dist_config.data_parallel > 1
+            and dist_config.compute_dtype.torch == torch.bfloat16 and num_weight_buffers == len(local)
+            and num_grad_buffers == len(local) and symmetric_memory_available(self._distributed.data_group, device)
+        )
+
+        def carve(sizes_bytes: list[int], what: str):
+            aligned = [(n + 255) // 256 * 256 for n in sizes_bytes]
+            arena = SymmetricArena(sum(aligned), self._distributed.data_group, device)
+            out, off = [], 0
+            for n, a in zip(sizes_bytes, aligned):
+                out.append(arena.buffer[off : off + n])
+                off += a
+            return arena, out
+
         if mode.support_forward:
             sizes = [0] * num_weight_buffers
             for k, (s, stage) in enumerate(local):
                 sizes[k % num_weight_buffers] = max(sizes[k % num_weight_buffers], sum(f.buffer_size for f in stage.fsdps))
-            self._weight_buffers = [allocator(n, dist_config.compute_dtype.torch, f"weight_buffer_{i}") for i, n in enumerate(sizes)]
+            wdtype = dist_config.compute_dtype.torch
+            if use_symmetric:
+                self._weight_arena, raw = carve([n * wdtype.itemsize for n in sizes], "weights")
+                self._weight_buffers = [b.view(wdtype) for b in raw]
+            else:
+                self._weight_buffers = [allocator(n, wdtype, f"weight_buffer_{i}") for i, n in enumerate(sizes)]
         if mode.support_backward:
             sizes = [0] * num_grad_buffers
-            dtype_bytes = 0
             for k, (s, stage) in enumerate(local):
                 nbytes = sum(f.grad_buffer_size * f.grad_buffer_dtype.itemsize for f in stage.fsdps)
                 sizes[k % num_grad_buffers] = max(sizes[k % num_grad_buffers], nbytes)
-            self._grad_buffers = [allocator(n, torch.uint8, f"grad_buffer_{i}") for i, n in enumerate(sizes)]
+            if use_symmetric:
+                self._grad_arena, self._grad_buffers = carve(sizes, "grads")
+            else:
+                self._grad_buffers = [allocator(n, torch.uint8, f"grad_buffer_{i}") for i, n in enumerate(sizes)]
             for b in self._grad_buffers:
                 b.zero_()
         self._buffer_registry = {}
@@ -217,6 +241,8 @@ class MultiStageModel:
                 wbufs.append(wbuf)
                 gbufs.append(gbuf)
                 grad_shards.append(gshard)
+            for fsdp in stage.fsdps:
+                fsdp.set_symmetric_arenas(self._weight_arena, self._grad_arena)
             stage.setup(distributed=self._distributed, mode=mode, weight_shards=weight_shards, grad_shards=grad_shards,
                         weight_buffers=wbufs, grad_buffers=gbufs, buffer_registry=self._buffer_registry,
                         weight_buffer_index=wi if num_weight_buffers < len(local) else ("own", s),
@@ -234,6 +260,15 @@ class MultiStageModel:
             logger.info(f"Model: {self._num_stages} stages, {n_params:,} parameters (per tensor rank), "
                         f"{len(local)} stages on this rank, shard {total:,} elements, "
                         f"{num_weight_buffers} weight / {num_grad_buffers} grad buffers, mode {mode.value}")
+
+    @property
+    def weight_arena(self):
+        """Symmetric-memory arena holding every weight buffer (None when the fused ZeRO path is off)."""
+        return getattr(self, "_weight_arena", None)
+
+    @property
+    def grad_arena(self):
+        return getattr(self, "_grad_arena", None)
 
     @property
     def shards(self) -> dict[str, torch.Tensor]:

@@ -26,6 +26,10 @@ class GradScaler:
         self._distributed = distributed
 
     @property
+    def pushes_weights_to_peers(self) -> bool:
+        return self._weight_arena is not None
+
+    @property
     def grad_scale(self) -> float:
         return self._scale
 
@@ -95,12 +99,14 @@ def get_grad_scaler(config: GradientScalerConfig, compute_dtype: torch.dtype, di
 
 class Optimizer:
     def __init__(self, config: OptimizerConfig, param_groups: list[dict], grad_norm_slices: list[torch.Tensor], distributed,
-                 compute_dtype: torch.dtype = torch.float32):
+                 compute_dtype: torch.dtype = torch.float32, weight_arena=None):
         config.validate()
         self._config = config
         self._param_groups = param_groups
         self._grad_norm_slices = grad_norm_slices
         self._distributed = distributed
+        # weight buffers in NVLink symmetric memory: Adam pushes the new bf16 weights to every data-parallel peer
+        self._weight_arena = weight_arena
         self._lr_schedule = create_schedule_from_config(config.learning_rate)
         self._current_step = 0
         self._grad_scaler = get_grad_scaler(config.gradient_scaler, compute_dtype, distributed)
@@ -108,6 +114,10 @@ class Optimizer:
         self._normsq = torch.zeros(1, dtype=torch.float32, device=device)
         self._coeff = torch.ones(1, dtype=torch.float32, device=device)
         self._norm = torch.zeros(1, dtype=torch.float32, device=device)
+
+    @property
+    def pushes_weights_to_peers(self) -> bool:
+        return self._weight_arena is not None
 
     @property
     def grad_scale(self) -> float:
@@ -150,9 +160,19 @@ class Optimizer:
         c = self._config
         for group in self._param_groups:
             lr_scale = group["lr_scale"] * (c.default_learning_rate_scale if group["lr_scale"] == 1.0 else 1.0)
-            adamw(group["params"], group["grads"], group["exp_avgs"], group["exp_avgs_sq"], group.get("buffer"),
-                  lr * lr_scale, c.beta_1, c.beta_2, c.epsilon, c.weight_decay if group["weight_decay"] else 0.0,
-                  self._current_step, 1.0, self._coeff)
+            wd = c.weight_decay if group["weight_decay"] else 0.0
+            if self._weight_arena is not None and group.get("buffer") is not None and group["params"].numel() % 4 == 0:
+                from fast_llm_b200.parallel.symmetric import adam_push
+
+                adam_push(self._weight_arena, group["params"], group["grads"], group["exp_avgs"], group["exp_avgs_sq"],
+                          group["buffer"], lr * lr_scale, c.beta_1, c.beta_2, c.epsilon, wd, self._current_step, self._coeff)
+            else:
+                assert self._weight_arena is None, "parameter group not aligned for the fused update"
+                adamw(group["params"], group["grads"], group["exp_avgs"], group["exp_avgs_sq"], group.get("buffer"),
+                      lr * lr_scale, c.beta_1, c.beta_2, c.epsilon, wd, self._current_step, 1.0, self._coeff)
+        if self._weight_arena is not None:
+            # every rank's pushes have landed (and every rank is done reading gradients) once all pass this barrier
+            self._weight_arena.barrier(1)
         if metrics is not None:
             metrics["learning_rate"] = lr
             metrics["grad_norm"] = self._norm  # device tensor; converted when logged

@@ -112,7 +112,8 @@ class ScheduleRunner:
             update_successful = self._optimizer.step(context.metrics if return_metrics else None)
             # Adam wrote the new weights into this rank's slice of the weight buffers.  With one data rank that is the
             # whole buffer; otherwise the next restore all-gathers the other slices.
-            if self._distributed_config.data_parallel > 1 or self._multi_stage._num_weight_buffers < len(self._stages_on_device):
+            fused = getattr(self._optimizer, "pushes_weights_to_peers", False)
+            if (self._distributed_config.data_parallel > 1 and not fused) or self._multi_stage._num_weight_buffers < len(self._stages_on_device):
                 self._multi_stage.invalidate_buffers()
         losses = self._reduce_losses(context, schedule)
         return losses, update_successful, (context.metrics if return_metrics else None)

@@ -78,7 +78,8 @@ class Trainer:
             runner.setup(distributed, ref_config)
             self._multi_stage.base_model.add_reference_model(name, runner)
         self._optimizer = Optimizer(config.optimizer, self._multi_stage.get_param_groups(), self._multi_stage.get_grad_norm_slices(),
-                                    distributed, compute_dtype=config.model.distributed.compute_dtype.torch)
+                                    distributed, compute_dtype=config.model.distributed.compute_dtype.torch,
+                                    weight_arena=self._multi_stage.weight_arena)
         self._runner.setup(distributed, self._optimizer)
         cache_dir = None if run.experiment_directory is None else run.experiment_directory / "dataset_cache"
         self._data.setup(cache_dir)

@@ -39,6 +39,12 @@ _SIGNATURES = {
     "flb_clip_coeff": [_p, _f, _f, _p, _p, _p],
     "flb_adamw": [_p, _p, _p, _p, _p, _ll, _f, _f, _f, _f, _f, _i, _f, _p, _p, _p],
     "flb_abi_version": [],
+    "flb_symm_max_ranks": [],
+    "flb_symm_signal_pad_bytes": [_i],
+    "flb_symm_barrier": [_p, _i, _i, _i, ctypes.c_uint, _p, _p],
+    "flb_rs_reduce_blocks": [],
+    "flb_rs_reduce": [_p, _i, _i, _i, _ll, _f, _p, _i, _p, _p],
+    "flb_adam_push": [_p, _p, _p, _p, _p, _i, _ll, _ll, _f, _f, _f, _f, _f, _i, _f, _p, _p],
 }
 
 _STATUS = {1: "unsupported shape or alignment", 2: "CUDA error", 3: "tensor map encoding failed", 4: "size exceeds the stated maximum"}
