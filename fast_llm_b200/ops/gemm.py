@@ -36,8 +36,11 @@ def _native_ok(a: torch.Tensor, b: torch.Tensor) -> bool:
     )
 
 
-def gemm_raw(a, b, out, m, n, k, a_mn, b_mn, epilogue, block_n=0, max_ctas=0):
+def gemm_raw(a, b, out, m, n, k, a_mn, b_mn, epilogue, block_n=None, max_ctas=0):
+    """block_n: None/0 = choose (CTA-pair kernel for large shapes), 128/256 = one-CTA kernel, 512 = CTA-pair kernel."""
     lib = _lib.get_lib()
+    if block_n is None:
+        block_n = int(os.environ.get("FLB_GEMM_BLOCK_N", 0))
     _lib.check(
         lib.flb_gemm_bf16(
             a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k, a.stride(0), b.stride(0), out.stride(0),

@@ -22,12 +22,12 @@ def _lib_loaded():
     check_device_errors()
 
 
-GEMM_SHAPES = [(128, 256, 64), (256, 512, 128), (384, 768, 320), (1024, 1024, 1024), (200, 328, 136), (8, 4096, 512),
+GEMM_SHAPES = [(512, 768, 256), (1000, 520, 200), (128, 256, 64), (256, 512, 128), (384, 768, 320), (1024, 1024, 1024), (200, 328, 136), (8, 4096, 512),
                (4096, 1024, 4096), (130, 4104, 72)]
 
 
 @pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
-@pytest.mark.parametrize("block_n", [0, 128, 256])
+@pytest.mark.parametrize("block_n", [0, 128, 256, 512])
 def test_gemm_nt(m, n, k, block_n):
     from fast_llm_b200.ops.gemm import gemm_raw
 
@@ -81,6 +81,9 @@ def test_gemm_mixed_majors_and_strided_views():
     out = torch.empty(m, n, device="cuda", dtype=torch.float32)
     gemm_raw(a_t, b, out, m, n, k, True, False, 1)
     assert _rel_err(out, a_t.float().t() @ b.float().t()) < 1e-2
+    for block_n in (256, 512):
+        gemm_raw(a_t, b, out.fill_(float("nan")), m, n, k, True, False, 1, block_n=block_n)
+        assert _rel_err(out, a_t.float().t() @ b.float().t()) < 1e-2
     # operands that are column slices of wider buffers (leading dimension > logical width)
     big = torch.randn(m, 3 * k, device="cuda", dtype=torch.bfloat16)
     xs = big[:, k : 2 * k]

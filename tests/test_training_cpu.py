@@ -171,3 +171,36 @@ def test_convert_cli(tmp_path):
                    "output.format=mistral", "use_cpu=true"])
     assert (tmp_path / "dst" / "ok").exists() and (tmp_path / "dst" / "config.json").exists()
     assert json.loads((tmp_path / "dst" / "config.json").read_text())["model_type"] == "mistral"
+
+
+MOE_UPDATES = {("model", "base_model", "decoder", "block", "mlp"): {
+    "type": "moe", "experts": 4, "experts_per_token": 2, "intermediate_size": 64, "gated": True, "activation": "silu",
+    "add_linear_biases": False, "auxiliary_loss_coefficient": 0.01, "z_loss_coefficient": 0.001}}
+
+
+def test_moe_dropless_matches_looped_and_trains():
+    dropless, _ = build_trainer(tiny_trainer_config(MOE_UPDATES))
+    looped_updates = {("model", "base_model", "decoder", "block", "mlp"): {**MOE_UPDATES[("model", "base_model", "decoder", "block", "mlp")], "implementation": "looped"}}
+    looped, _ = build_trainer(tiny_trainer_config(looped_updates))
+    a, b = train_steps(dropless, 3), train_steps(looped, 3)
+    assert a == pytest.approx(b, rel=1e-5)
+    torch.testing.assert_close(dropless.multi_stage.get_shard("weights"), looped.multi_stage.get_shard("weights"), rtol=1e-4, atol=1e-6)
+    assert "load_balancing_loss" in dropless.runner._loss_definitions and "router_z_loss" in dropless.runner._loss_definitions
+
+
+def test_mixtral_export_matches_transformers(tmp_path):
+    transformers = pytest.importorskip("transformers")
+    from fast_llm_b200.engine.checkpoint.config import CheckpointSaveConfig
+    from fast_llm_b200.engine.inference.runner import InferenceRunner
+
+    trainer, _ = build_trainer(tiny_trainer_config({**MOE_UPDATES, ("model", "base_model", "decoder", "block", "mixer", "window_size"): 32}))
+    train_steps(trainer, 1)
+    trainer.multi_stage.save_checkpoint(CheckpointSaveConfig(path=tmp_path / "hf", format="mixtral"))
+    hf = transformers.AutoModelForCausalLM.from_pretrained(tmp_path / "hf", torch_dtype=torch.float32)
+    tokens = torch.randint(0, 512, (1, 24))
+    with torch.no_grad():
+        expected = hf(tokens).logits[0]
+    model = _model_from(tmp_path / "hf", "mixtral")
+    runner = InferenceRunner(model)
+    runner.setup(model.distributed)
+    torch.testing.assert_close(runner.forward_tokens(tokens[0]), expected, rtol=3e-4, atol=3e-4)
