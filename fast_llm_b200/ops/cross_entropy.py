@@ -46,7 +46,9 @@ def cross_entropy_forward_backward(logits: torch.Tensor, labels: torch.Tensor, g
     """Returns (loss_per_token fp32, z_per_token fp32, grad_logits).  `grad_scale` may be a float or a 1-element
     device tensor (kept on the device: no host sync); None skips the backward.  With `in_place` the gradient
     overwrites `logits`."""
-    native = logits.is_cuda and logits.dtype in (torch.bfloat16, torch.float32) and logits.stride(-1) == 1
+    vec = 8 if logits.dtype == torch.bfloat16 else 4
+    native = (logits.is_cuda and logits.dtype in (torch.bfloat16, torch.float32) and logits.stride(-1) == 1
+              and logits.stride(0) % vec == 0 and logits.data_ptr() % 16 == 0)
     if not native:
         return cross_entropy_reference(logits, labels, grad_scale, logits_scale, z_coef, group, vocab_begin)
     lib = _lib.get_lib()
