@@ -1,6 +1,8 @@
 // Optimizer kernels over flat fp32 shards: deterministic sum of squares (gradient norm), clip coefficient computed on
 // the device (no host round trip), and fused AdamW that also writes the bf16 copy of the updated weights.
 #include "common.cuh"
+#include "no_alloc.h"
+#include <mutex>
 
 namespace {
 using namespace flb;
@@ -120,6 +122,49 @@ FLB_API int flb_adamw(float* w, const float* g, float* m, float* v, void* w_lp, 
   if (blocks < 1) blocks = 1;
   adamw_kernel<<<(int)blocks, kThreads, 0, stream>>>(w, g, m, v, (__nv_bfloat16*)w_lp, n, lr, beta1, beta2, eps, wd,
                                                       inv_bc1, inv_bc2, gscale, gscale_ptr, noop_flag);
+  FLB_CHECK_LAUNCH();
+  return FLB_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Variant of flb_sumsq for callers that cannot allocate: the per-block partial sums live in a scratch array that is
+// part of the library image instead of a caller-provided buffer.  See no_alloc.h for the contract.
+// ------------------------------------------------------------------------------------------------
+static_assert(FLB_NO_ALLOC_SCRATCH_FLOATS == kSumsqBlocks, "built-in scratch must hold one partial per block");
+static __device__ __align__(256) float g_sumsq_scratch[FLB_NO_ALLOC_SCRATCH_FLOATS];
+
+namespace {
+// In host code `g_sumsq_scratch` is only a handle for the symbol, not a device address: resolve the real address once
+// per device (with that device current) and hand the kernels that pointer.
+int no_alloc_scratch(float** out) {
+  static float* addresses[64] = {};
+  static std::mutex mu;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return flb_record_cuda_error(e);
+  if (dev < 0 || dev >= 64) return FLB_ERR_SHAPE;
+  std::lock_guard<std::mutex> lock(mu);
+  if (addresses[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_sumsq_scratch);
+    if (e != cudaSuccess) return flb_record_cuda_error(e);
+    addresses[dev] = static_cast<float*>(p);
+  }
+  *out = addresses[dev];
+  return FLB_OK;
+}
+}  // namespace
+
+FLB_API int flb_sumsq_no_alloc(const float* x, long long n, float* out, int accumulate, cudaStream_t stream) {
+  if (n < 0 || (reinterpret_cast<uintptr_t>(x) & 15)) return FLB_ERR_SHAPE;
+  if (n > FLB_NO_ALLOC_MAX_ELEMENTS) return FLB_ERR_TOO_LARGE;
+  float* scratch = nullptr;
+  const int st = no_alloc_scratch(&scratch);
+  if (st != FLB_OK) return st;
+  // Every block writes its own slot before the final kernel reads any, so stale contents of earlier calls are harmless.
+  sumsq_partial_kernel<<<kSumsqBlocks, kThreads, 0, stream>>>(x, n, scratch);
+  FLB_CHECK_LAUNCH();
+  sumsq_final_kernel<<<1, kThreads, 0, stream>>>(scratch, kSumsqBlocks, out, accumulate);
   FLB_CHECK_LAUNCH();
   return FLB_OK;
 }
