@@ -1,0 +1,393 @@
+// Flash-attention forward on tcgen05 tensor cores: packed variable-length documents, causal + sliding window, GQA,
+// head size 128, bf16 in / bf16 out, fp32 softmax statistics.
+//
+// One CTA owns 128 query rows of one head of one document and walks the key/value tiles (128 rows) it may see:
+//   warp 0      TMA: Q once, then K_j / V_j into two-deep rings
+//   warp 1      one thread issues  S_j = Q K_j^T  (tcgen05.mma, accumulator in TMEM, two S buffers)  and
+//               O += P_j V_j  (P_j read from shared memory, V_j as an MN-major operand)
+//   warps 2-5   softmax, one query row per thread: tcgen05.ld of the S row, running max / sum in the exp2 domain,
+//               masks on the diagonal and window edges, P_j written as bf16 into the swizzled K-major tile the second
+//               MMA reads, O rescaled in TMEM only when the running max moved by more than 2^8 (lazy rescaling);
+//               finally O / l is written out with the row's log-sum-exp.
+// The S buffer of tile j+1 is computed while tile j is in softmax.  All mbarrier waits are bounded (error word).
+//
+// Layout contract: `qkv` rows hold [q heads | k heads | v heads] x 128 (any row stride that is a multiple of 8
+// elements); out rows hold heads x 128; lse is [heads, total_tokens] fp32 (natural log), the layout the backward expects.
+#include "tcgen05.cuh"
+#include <mutex>
+
+namespace {
+using namespace flb_tc;
+
+constexpr int D = 128;           // head size
+constexpr int BM = 128;          // query rows per CTA
+constexpr int BN = 128;          // key rows per tile
+constexpr int kThreadsAttn = 192;
+constexpr int PANEL_BYTES = 128 * 128;  // 128 rows x 64 bf16
+constexpr int TILE_BYTES_ATTN = 2 * PANEL_BYTES;
+constexpr int SMEM_Q = 0, SMEM_K = TILE_BYTES_ATTN, SMEM_V = 3 * TILE_BYTES_ATTN, SMEM_P = 5 * TILE_BYTES_ATTN;
+constexpr int SMEM_BARS = 6 * TILE_BYTES_ATTN;
+constexpr int SMEM_TOTAL = SMEM_BARS + 256 + 1024;
+constexpr float kRescaleThreshold = 8.f;  // log2 units
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+struct AttnParams {
+  const int* cu_q;       // [batch + 1] query offsets
+  const int* cu_k;       // [batch + 1] key offsets (== cu_q for self attention without prefix)
+  __nv_bfloat16* out;    // [total_q, heads * D]
+  float* lse;            // [heads, total_q]
+  long long total_q;
+  int heads, kv_heads, q_col0, k_col0, v_col0;  // column (element) offsets of the q / k / v blocks inside a row
+  int blocks_per_doc;    // ceil(max_seqlen_q / BM)
+  int causal, window;    // window <= 0: unlimited; else a query sees the `window` most recent keys including itself
+  float scale_log2;      // softmax scale * log2(e)
+  int* err_word;
+};
+
+__global__ void __launch_bounds__(kThreadsAttn, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv, const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  const uint32_t sbase = raw_addr + pad;
+  const uint32_t bar0 = sbase + SMEM_BARS;
+  // barriers: 0 q_full, 1-2 k_full, 3-4 k_empty, 5-6 v_full, 7-8 v_empty, 9-10 s_full, 11-12 s_empty, 13 p_full, 14 pv_done
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SMEM_BARS + 8 * 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y;
+  const int kv_head = head / (p.heads / p.kv_heads);
+  const int doc = blockIdx.x / p.blocks_per_doc;
+  // heavy (late) query blocks first: they see the most keys
+  const int qblk = p.blocks_per_doc - 1 - (blockIdx.x % p.blocks_per_doc);
+  const int q_begin = p.cu_q[doc], q_len = p.cu_q[doc + 1] - q_begin;
+  const int k_begin = p.cu_k[doc], k_len = p.cu_k[doc + 1] - k_begin;
+  const int q0 = qblk * BM;
+  if (q0 >= q_len) return;  // uniform for the CTA: nothing allocated yet
+  const int shift = k_len - q_len;  // bottom-right aligned causal mask: query i sees keys <= i + shift
+  // key range this block needs
+  int kv_hi = k_len;
+  if (p.causal) kv_hi = min(k_len, q0 + BM + shift);
+  int kv_lo = 0;
+  if (p.window > 0) kv_lo = max(0, q0 + shift - p.window + 1);
+  const int tile_lo = kv_lo / BN, tile_hi = (kv_hi + BN - 1) / BN;
+  const int num_tiles = max(tile_hi - tile_lo, 0);
+
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_q) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_kv) : "memory");
+    mbar_init(bar(0), 1);
+    for (int i = 1; i <= 8; ++i) mbar_init(bar(i), 1);
+    mbar_init(bar(9), 1); mbar_init(bar(10), 1);
+    mbar_init(bar(11), 4); mbar_init(bar(12), 4);
+    mbar_init(bar(13), 4);
+    mbar_init(bar(14), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem_s[2] = {tmem, tmem + 128};
+  const uint32_t tmem_o = tmem + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- producer
+      mbar_expect_tx(bar(0), TILE_BYTES_ATTN);
+      for (int c = 0; c < 2; ++c)
+        tma_load_2d(sbase + SMEM_Q + c * PANEL_BYTES, &tmap_q, bar(0), p.q_col0 + head * D + c * 64, q_begin + q0);
+      bool ok = true;
+      for (int j = 0; j < num_tiles && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int row = k_begin + (tile_lo + j) * BN;
+        if (!mbar_wait(bar(3 + s), ph ^ 1u, abort_flag, p.err_word, 21)) { ok = false; break; }
+        mbar_expect_tx(bar(1 + s), TILE_BYTES_ATTN);
+        for (int c = 0; c < 2; ++c)
+          tma_load_2d(sbase + SMEM_K + s * TILE_BYTES_ATTN + c * PANEL_BYTES, &tmap_kv, bar(1 + s), p.k_col0 + kv_head * D + c * 64, row);
+        if (!mbar_wait(bar(7 + s), ph ^ 1u, abort_flag, p.err_word, 22)) { ok = false; break; }
+        mbar_expect_tx(bar(5 + s), TILE_BYTES_ATTN);
+        for (int c = 0; c < 2; ++c)
+          tma_load_2d(sbase + SMEM_V + s * TILE_BYTES_ATTN + c * PANEL_BYTES, &tmap_kv, bar(5 + s), p.v_col0 + kv_head * D + c * 64, row);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- MMA issuer
+      constexpr uint32_t idesc_qk = make_idesc(BM, BN, false, false);
+      constexpr uint32_t idesc_pv = make_idesc(BM, D, false, true);
+      bool ok = mbar_wait(bar(0), 0, abort_flag, p.err_word, 23);
+      auto issue_qk = [&](int j) -> bool {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(bar(1 + s), ph, abort_flag, p.err_word, 24)) return false;        // K_j landed
+        if (!mbar_wait(bar(11 + s), ph ^ 1u, abort_flag, p.err_word, 25)) return false;  // S buffer drained
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < D / UMMA_K; ++k) {
+          const uint32_t off = (k >> 2) * PANEL_BYTES + (k & 3) * 32;
+          umma_bf16(tmem_s[s], make_smem_desc(sbase + SMEM_Q + off, 16, 1024),
+                    make_smem_desc(sbase + SMEM_K + s * TILE_BYTES_ATTN + off, 16, 1024), idesc_qk, k != 0);
+        }
+        umma_commit(bar(9 + s));  // S_j ready
+        umma_commit(bar(3 + s));  // K slot free
+        return true;
+      };
+      if (ok && num_tiles > 0) ok = issue_qk(0);
+      for (int j = 0; j < num_tiles && ok; ++j) {
+        if (j + 1 < num_tiles) ok = issue_qk(j + 1);
+        if (!ok) break;
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(bar(13), j & 1, abort_flag, p.err_word, 26)) { ok = false; break; }   // P_j written
+        if (!mbar_wait(bar(5 + s), ph, abort_flag, p.err_word, 27)) { ok = false; break; }   // V_j landed
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < BN / UMMA_K; ++k) {
+          const uint32_t a_off = (k >> 2) * PANEL_BYTES + (k & 3) * 32;  // P: K-major panels over keys
+          const uint32_t b_off = k * 2048;                                // V: 16 key rows per step
+          umma_bf16(tmem_o, make_smem_desc(sbase + SMEM_P + a_off, 16, 1024),
+                    make_smem_desc(sbase + SMEM_V + s * TILE_BYTES_ATTN + b_off, PANEL_BYTES, 1024), idesc_pv, (j | k) != 0);
+        }
+        umma_commit(bar(14));     // O updated, P free
+        umma_commit(bar(7 + s));  // V slot free
+      }
+    }
+  } else {
+    // ---- softmax / correction / epilogue: one query row per thread
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;          // row inside the block
+    const int qi = q0 + r;                      // row inside the document
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < num_tiles && ok; ++j) {
+      const int s = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!mbar_wait(bar(9 + s), ph, abort_flag, p.err_word, 28)) { ok = false; break; }
+      tc_fence_after();
+      const int kbase = (tile_lo + j) * BN;
+      // which columns of this tile may this row see?  [col_lo, col_hi)
+      int col_hi = k_len - kbase;
+      if (p.causal) col_hi = min(col_hi, qi + shift + 1 - kbase);
+      int col_lo = 0;
+      if (p.window > 0) col_lo = max(0, qi + shift - p.window + 1 - kbase);
+      const bool full_tile = (col_lo <= 0) && (col_hi >= BN);
+      // pass 1: row maximum
+      float tile_max = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem_s[s] + lane_addr + c * 32, v);
+        tmem_wait_ld();
+        if (full_tile) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) tile_max = fmaxf(tile_max, __uint_as_float(v[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = c * 32 + i;
+            if (col >= col_lo && col < col_hi) tile_max = fmaxf(tile_max, __uint_as_float(v[i]));
+          }
+        }
+      }
+      tile_max *= p.scale_log2;
+      float m_new = m;
+      float alpha = 1.f;
+      if (tile_max > m + kRescaleThreshold || m == -INFINITY) {
+        m_new = fmaxf(m, tile_max);
+        alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
+      }
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      // pass 2: probabilities, packed to bf16
+      uint32_t packed[64];
+      float row_sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem_s[s] + lane_addr + c * 32, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float e0 = exp2f(__uint_as_float(v[i]) * p.scale_log2 - m_use);
+          float e1 = exp2f(__uint_as_float(v[i + 1]) * p.scale_log2 - m_use);
+          if (!full_tile) {
+            const int col = c * 32 + i;
+            if (col < col_lo || col >= col_hi) e0 = 0.f;
+            if (col + 1 < col_lo || col + 1 >= col_hi) e1 = 0.f;
+          }
+          row_sum += e0 + e1;
+          __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
+          packed[c * 16 + (i >> 1)] = *reinterpret_cast<uint32_t*>(&b);
+        }
+      }
+      // the S buffer may be overwritten by the MMA of tile j + 2
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(11 + s));
+      // P buffer and O are free once the previous PV MMA has completed
+      if (j > 0) {
+        if (!mbar_wait(bar(14), (j - 1) & 1, abort_flag, p.err_word, 29)) { ok = false; break; }
+        tc_fence_after();
+      }
+      l = l * alpha + row_sum;
+      m = m_new;
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        // rescale this warp's 32 rows of O in TMEM
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld32(tmem_o + lane_addr + c * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+          tmem_st32(tmem_o + lane_addr + c * 32, v);
+        }
+        tmem_wait_st();
+      }
+      // write P_j: two K-major panels of 64 keys, 128-byte swizzle (16-byte chunk index XOR row % 8)
+      uint8_t* prow = smem + SMEM_P + r * 128;
+#pragma unroll
+      for (int ch = 0; ch < 16; ++ch) {
+        const int panel = ch >> 3, chunk = ch & 7;
+        uint4 val = make_uint4(packed[ch * 4], packed[ch * 4 + 1], packed[ch * 4 + 2], packed[ch * 4 + 3]);
+        *reinterpret_cast<uint4*>(prow + panel * PANEL_BYTES + ((chunk ^ (r & 7)) << 4)) = val;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(13));
+    }
+    // ---- epilogue
+    if (ok && num_tiles > 0) ok = mbar_wait(bar(14), (num_tiles - 1) & 1, abort_flag, p.err_word, 30);
+    tc_fence_after();
+    const bool valid_row = qi < q_len;
+    const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+    __nv_bfloat16* orow = p.out + ((long long)(q_begin + qi) * p.heads + head) * D;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t v[32];
+      if (num_tiles > 0 && ok) {
+        tmem_ld32(tmem_o + lane_addr + c * 32, v);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0u;
+      }
+      if (valid_row) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          float f[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[g * 8 + i]) * inv_l;
+          *reinterpret_cast<flb::bf16x8*>(orow + c * 32 + g * 8) = flb::pack8(f);
+        }
+      }
+    }
+    if (valid_row) p.lse[(long long)head * p.total_q + q_begin + qi] = (l > 0.f) ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+bool row_tmap(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows, uint64_t row_stride_elems) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {row_stride_elems * 2};
+  cuuint32_t box[2] = {64, 128};
+  cuuint32_t es[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+int* attn_err_word() {
+  static int* words[64] = {};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!words[dev]) {
+    if (cudaMalloc(&words[dev], sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(words[dev], 0, sizeof(int));
+  }
+  return words[dev];
+}
+}  // namespace
+
+// q rows: [total_q, q_stride] with query head h at columns q_col0 + h*128; kv rows: [total_k, kv_stride] with key head g at
+// k_col0 + g*128 and value head g at v_col0 + g*128 (q and kv may be the same packed tensor).  head size must be 128.
+FLB_API int flb_attention_fwd(const void* q, long long q_stride, int q_col0, const void* kv, long long kv_stride, int k_col0,
+                              int v_col0, const int* cu_q, const int* cu_k, int batch, int max_seqlen_q, long long total_q,
+                              long long total_k, int heads, int kv_heads, int head_dim, void* out, float* lse, int causal, int window,
+                              float softmax_scale, cudaStream_t stream) {
+  if (head_dim != D || heads % kv_heads || q_stride % 8 || kv_stride % 8 || batch <= 0) return FLB_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(kv) & 15) || (q_col0 % 8) || (k_col0 % 8) || (v_col0 % 8))
+    return FLB_ERR_SHAPE;
+  CUtensorMap tq, tkv;
+  if (!row_tmap(&tq, q, (uint64_t)q_stride, (uint64_t)total_q, (uint64_t)q_stride)) return FLB_ERR_TMA;
+  if (!row_tmap(&tkv, kv, (uint64_t)kv_stride, (uint64_t)total_k, (uint64_t)kv_stride)) return FLB_ERR_TMA;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    if (e != cudaSuccess) return flb_record_cuda_error(e);
+    configured = true;
+  }
+  AttnParams p;
+  p.cu_q = cu_q; p.cu_k = cu_k; p.out = (__nv_bfloat16*)out; p.lse = lse; p.total_q = total_q;
+  p.heads = heads; p.kv_heads = kv_heads; p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;
+  p.blocks_per_doc = (max_seqlen_q + BM - 1) / BM;
+  p.causal = causal; p.window = window; p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.err_word = attn_err_word();
+  if (!p.err_word) return FLB_ERR_CUDA;
+  dim3 grid(p.blocks_per_doc * batch, heads);
+  attn_fwd_kernel<<<grid, kThreadsAttn, SMEM_TOTAL, stream>>>(tq, tkv, p);
+  FLB_CHECK_LAUNCH();
+  return FLB_OK;
+}
+
+FLB_API int flb_attention_error_word() {
+  int* w = attn_err_word();
+  if (!w) return -1;
+  int v = 0;
+  if (cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (v) cudaMemset(w, 0, sizeof(int));
+  return v;
+}

@@ -55,6 +55,28 @@ def _use_flash(q):
     return q.is_cuda and q.dtype in (torch.bfloat16, torch.float16)
 
 
+def _use_native_forward(t: torch.Tensor, head_dim: int, dropout_p: float) -> bool:
+    import os
+
+    return (t.is_cuda and t.dtype == torch.bfloat16 and head_dim == 128 and dropout_p == 0.0 and t.stride(-1) == 1
+            and os.environ.get("FLB_ATTENTION", "tcgen05") == "tcgen05")
+
+
+def attention_forward_native(q2d, q_col0, kv2d, k_col0, v_col0, cu_q, cu_k, max_seqlen_q, heads, kv_heads, head_dim, causal, window_size, scale):
+    """tcgen05 forward (`csrc/attention_fwd.cu`).  q2d / kv2d: 2-D row views ([tokens, row_stride]) holding the heads at the
+    given column offsets.  Returns (out [tokens, heads, head_dim], lse [heads, tokens] fp32)."""
+    total_q, total_k = q2d.shape[0], kv2d.shape[0]
+    out = torch.empty(total_q, heads, head_dim, dtype=q2d.dtype, device=q2d.device)
+    lse = torch.empty(heads, total_q, dtype=torch.float32, device=q2d.device)
+    _lib.check(
+        _lib.get_lib().flb_attention_fwd(
+            q2d.data_ptr(), q2d.stride(0), q_col0, kv2d.data_ptr(), kv2d.stride(0), k_col0, v_col0, cu_q.data_ptr(), cu_k.data_ptr(),
+            cu_q.numel() - 1, max_seqlen_q, total_q, total_k, heads, kv_heads, head_dim, out.data_ptr(), lse.data_ptr(), int(causal),
+            int(window_size or 0), float(scale), _lib.stream_ptr()), "flb_attention_fwd")
+    _lib.count_launch()
+    return out, lse
+
+
 class _FlashAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, cu_q, cu_k, max_q, max_k, causal, window_size, scale, dropout_p):
@@ -99,8 +121,12 @@ class _PackedFlashAttention(torch.autograd.Function):
         k = qkv[:, nq : nq + nkv].view(t, kv_heads, head_dim)
         v = qkv[:, nq + nkv :].view(t, kv_heads, head_dim)
         wl, wr = _window(window_size, causal)
-        out, lse, _, rng_state = _flash_attn_varlen_forward(q, k, v, cu, cu, max_len, max_len, dropout_p, scale, causal,
-                                                            window_size_left=wl, window_size_right=wr)
+        if _use_native_forward(qkv, head_dim, dropout_p) and (causal or window_size is None):
+            out, lse = attention_forward_native(qkv, 0, qkv, nq, nq + nkv, cu, cu, max_len, heads, kv_heads, head_dim, causal, window_size, scale)
+            rng_state = None
+        else:
+            out, lse, _, rng_state = _flash_attn_varlen_forward(q, k, v, cu, cu, max_len, max_len, dropout_p, scale, causal,
+                                                                window_size_left=wl, window_size_right=wr)
         ctx.save_for_backward(qkv, out, lse, cu, rng_state)
         ctx.args = (max_len, heads, kv_heads, head_dim, causal, wl, wr, scale, dropout_p)
         return out.view(t, nq)

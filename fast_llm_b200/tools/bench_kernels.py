@@ -123,6 +123,29 @@ def bench_gemm_tiles(results):
             print(json.dumps(r), flush=True)
 
 
+def bench_attention(results):
+    """Forward attention at the Mistral-7B shape (8192 tokens, 32/8 heads, window 4096): tcgen05 kernel vs the library."""
+    from flash_attn.flash_attn_interface import _flash_attn_varlen_forward
+
+    from fast_llm_b200.ops.attention import attention_forward_native
+
+    _, tflops_peak, kind = _peaks()
+    t, heads, kv, d, window = 8192, 32, 8, 128, 4096
+    qkv = torch.randn(t, (heads + 2 * kv) * d, device="cuda", dtype=torch.bfloat16)
+    cu = torch.tensor([0, t], device="cuda", dtype=torch.int32)
+    nq, nkv = heads * d, kv * d
+    keys = (window * (window + 1) / 2 + (t - window) * window) / t  # average keys per query
+    flops = 4.0 * t * keys * heads * d
+    q, k, v = qkv[:, :nq].view(t, heads, d), qkv[:, nq:nq + nkv].view(t, kv, d), qkv[:, nq + nkv:].view(t, kv, d)
+    ours = lambda: attention_forward_native(qkv, 0, qkv, nq, nq + nkv, cu, cu, t, heads, kv, d, True, window, d**-0.5)
+    lib = lambda: _flash_attn_varlen_forward(q, k, v, cu, cu, t, t, 0.0, d**-0.5, True, window_size_left=window - 1, window_size_right=0)
+    ms, ms_lib = time_op(ours), time_op(lib)
+    r = {"op": "attention_fwd_mistral", "ms": ms, "tflops": flops / ms / 1e9, "frac_of_peak": flops / ms / 1e9 / tflops_peak,
+         "peak_kind": kind, "cublas_ms": ms_lib, "cublas_tflops": flops / ms_lib / 1e9, "note": "second pair = flash_attn 2 library"}
+    results.append(r)
+    print(json.dumps(r), flush=True)
+
+
 def profile_gemm():
     """Small fixed workload for an ncu capture: three launches of the fprop GEMM on operands larger than L2."""
     from fast_llm_b200.ops.gemm import matmul_nt
@@ -142,7 +165,9 @@ def main(argv):
         return profile_gemm()
     if "gemm_tiles" in argv:
         bench_gemm_tiles(results)
-    which = [a for a in argv if a in ("gemm", "elementwise")] or ([] if "gemm_tiles" in argv else ["gemm", "elementwise"])
+    if "attention" in argv:
+        bench_attention(results)
+    which = [a for a in argv if a in ("gemm", "elementwise")] or ([] if ("gemm_tiles" in argv or "attention" in argv) else ["gemm", "elementwise"])
     if "gemm" in which:
         bench_gemm(results)
     if "elementwise" in which:

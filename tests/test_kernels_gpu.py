@@ -259,3 +259,72 @@ def test_embedding_and_pointwise():
     with torch.no_grad():
         r = bias_residual(x, bias, x, 0.5)
     assert _rel_err(r, (x.float() + bias.float()) * 0.5 + x.float()) < 1e-2
+
+
+def _attention_case(doc_lengths, heads, kv_heads, causal, window, seed=0):
+    from fast_llm_b200.ops.attention import attention_forward_native, attention_reference
+
+    torch.manual_seed(seed)
+    d = 128
+    total = sum(doc_lengths)
+    qkv = torch.randn(total, (heads + 2 * kv_heads) * d, device="cuda", dtype=torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor(doc_lengths).cumsum(0)), device="cuda", dtype=torch.int32)
+    nq, nkv = heads * d, kv_heads * d
+    out, lse = attention_forward_native(qkv, 0, qkv, nq, nq + nkv, cu, cu, max(doc_lengths), heads, kv_heads, d, causal, window, d**-0.5)
+    q = qkv[:, :nq].reshape(total, heads, d)
+    k = qkv[:, nq : nq + nkv].reshape(total, kv_heads, d)
+    v = qkv[:, nq + nkv :].reshape(total, kv_heads, d)
+    ref = attention_reference(q.float(), k.float(), v.float(), cu, cu, causal, window, d**-0.5)
+    return out, lse, ref, (q, k, v, cu)
+
+
+@pytest.mark.parametrize("doc_lengths,heads,kv_heads,causal,window", [
+    ([128], 1, 1, True, None),
+    ([256], 2, 1, True, None),
+    ([1000], 4, 2, True, None),
+    ([300, 77, 513, 1], 4, 2, True, None),
+    ([1500], 4, 1, True, 256),
+    ([700, 900], 8, 2, True, 100),
+    ([640], 2, 2, False, None),
+    ([2048], 8, 2, True, 1024),
+])
+def test_attention_forward_tcgen05(doc_lengths, heads, kv_heads, causal, window):
+    from fast_llm_b200.ops import _lib
+
+    out, lse, ref, (q, k, v, cu) = _attention_case(doc_lengths, heads, kv_heads, causal, window)
+    assert _lib.get_lib().flb_attention_error_word() == 0
+    assert torch.isfinite(out).all()
+    assert _rel_err(out, ref) < 1.5e-2
+    # log-sum-exp against a direct computation for one head of the first document
+    n = doc_lengths[0]
+    s = (q[:n, 0].float() @ k[:n, 0].float().t()) * 128**-0.5
+    i = torch.arange(n, device="cuda")
+    mask = torch.ones(n, n, dtype=torch.bool, device="cuda")
+    if causal:
+        mask &= i[None, :] <= i[:, None]
+    if window:
+        mask &= i[None, :] > i[:, None] - window
+    expected = torch.logsumexp(s.masked_fill(~mask, float("-inf")), -1)
+    assert _rel_err(lse[0, :n], expected) < 2e-3
+
+
+def test_packed_attention_native_forward_library_backward():
+    """The autograd path: tcgen05 forward, library backward fed with our log-sum-exp."""
+    from fast_llm_b200.ops.attention import attention_reference, packed_attention
+
+    torch.manual_seed(1)
+    heads, kv_heads, d = 4, 2, 128
+    lengths = [384, 200]
+    total = sum(lengths)
+    qkv = torch.randn(total, (heads + 2 * kv_heads) * d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    cu = torch.tensor([0, 384, 584], device="cuda", dtype=torch.int32)
+    out = packed_attention(qkv, cu, max(lengths), heads, kv_heads, d, causal=True, window_size=128)
+    g = torch.randn_like(out)
+    out.backward(g)
+    ref_in = qkv.detach().float().requires_grad_()
+    nq, nkv = heads * d, kv_heads * d
+    ref = attention_reference(ref_in[:, :nq].reshape(total, heads, d), ref_in[:, nq : nq + nkv].reshape(total, kv_heads, d),
+                              ref_in[:, nq + nkv :].reshape(total, kv_heads, d), cu, cu, True, 128, d**-0.5).reshape(total, nq)
+    ref.backward(g.float())
+    assert _rel_err(out, ref) < 1.5e-2
+    assert _rel_err(qkv.grad, ref_in.grad) < 3e-2
