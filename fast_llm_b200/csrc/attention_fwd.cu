@@ -335,8 +335,14 @@ bool row_tmap(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows, 
   cuuint64_t strides[1] = {row_stride_elems * 2};
   cuuint32_t box[2] = {64, 128};
   cuuint32_t es[2] = {1, 1};
-  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  CUresult res = CUDA_SUCCESS;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    res = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (res != CUDA_ERROR_INVALID_CONTEXT) break;
+    cudaFree(nullptr);  // a thread that made no runtime call yet has no current context: bind the primary one
+  }
+  return res == CUDA_SUCCESS;
 }
 int* attn_err_word() {
   static int* words[64] = {};

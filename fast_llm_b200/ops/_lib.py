@@ -41,6 +41,9 @@ _SIGNATURES = {
     "flb_abi_version": [],
     "flb_attention_fwd": [_p, _ll, _i, _p, _ll, _i, _i, _p, _p, _i, _i, _ll, _ll, _i, _i, _i, _p, _p, _i, _i, _f, _p],
     "flb_attention_error_word": [],
+    "flb_attention_bwd": [_p, _ll, _i, _p, _ll, _i, _i, _p, _p, _p, _p, _p, _i, _i, _ll, _ll, _i, _i, _i, _p, _ll, _p, _ll, _p, _p,
+                          _i, _i, _f, _p],
+    "flb_attention_bwd_error_word": [],
     "flb_symm_max_ranks": [],
     "flb_symm_signal_pad_bytes": [_i],
     "flb_symm_barrier": [_p, _i, _i, _i, ctypes.c_uint, _p, _p],

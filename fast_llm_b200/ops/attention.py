@@ -5,8 +5,9 @@
 backward is a single GEMM.  `attention(q, k, v, ...)` is the general form (keys may include a prefix from earlier
 micro-sequences or other sequence-data-parallel ranks; causal masks are bottom-right aligned).
 
-On GPUs the softmax(QK^T)V core is the flash-attention 2 library kernel (a library call, like cuBLAS for a plain GEMM);
-on CPU a per-document PyTorch restatement, which doubles as the test oracle (math of `fast_llm/layers/attention/
+On B200 the packed path runs this package's tcgen05 kernels (`csrc/attention_fwd.cu`, `csrc/attention_bwd.cu`; bf16, head
+size 128); other shapes, dropout and the prefix form use the flash-attention 2 library kernel (a library call, like
+cuBLAS for a plain GEMM); on CPU a per-document PyTorch restatement, which doubles as the test oracle (math of `fast_llm/layers/attention/
 attention.py:209-256`).
 """
 
@@ -77,6 +78,29 @@ def attention_forward_native(q2d, q_col0, kv2d, k_col0, v_col0, cu_q, cu_k, max_
     return out, lse
 
 
+def _use_native_backward() -> bool:
+    import os
+
+    return os.environ.get("FLB_ATTENTION_BWD", "tcgen05") == "tcgen05"
+
+
+def attention_backward_native(q2d, q_col0, kv2d, k_col0, v_col0, out, dout, lse, cu_q, cu_k, max_seqlen_k, heads, kv_heads, head_dim,
+                              dq2d, dkv2d, causal, window_size, scale):
+    """tcgen05 backward (`csrc/attention_bwd.cu`).  Writes dq into `dq2d` and dk / dv into `dkv2d` at the column offsets the
+    forward inputs have in `q2d` / `kv2d` (the gradient buffers mirror the input layout)."""
+    total_q, total_k = q2d.shape[0], kv2d.shape[0]
+    delta = torch.empty(heads, total_q, dtype=torch.float32, device=q2d.device)
+    dq_accum = torch.empty(heads * ((total_q + 31) // 32) * 32 * head_dim, dtype=torch.float32, device=q2d.device)
+    dout = dout.contiguous()
+    _lib.check(
+        _lib.get_lib().flb_attention_bwd(
+            q2d.data_ptr(), q2d.stride(0), q_col0, kv2d.data_ptr(), kv2d.stride(0), k_col0, v_col0, out.data_ptr(), dout.data_ptr(),
+            lse.data_ptr(), cu_q.data_ptr(), cu_k.data_ptr(), cu_q.numel() - 1, max_seqlen_k, total_q, total_k, heads, kv_heads, head_dim,
+            dq2d.data_ptr(), dq2d.stride(0), dkv2d.data_ptr(), dkv2d.stride(0), delta.data_ptr(), dq_accum.data_ptr(), int(causal),
+            int(window_size or 0), float(scale), _lib.stream_ptr()), "flb_attention_bwd")
+    _lib.count_launch(3)
+
+
 class _FlashAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, cu_q, cu_k, max_q, max_k, causal, window_size, scale, dropout_p):
@@ -129,6 +153,8 @@ class _PackedFlashAttention(torch.autograd.Function):
                                                                 window_size_left=wl, window_size_right=wr)
         ctx.save_for_backward(qkv, out, lse, cu, rng_state)
         ctx.args = (max_len, heads, kv_heads, head_dim, causal, wl, wr, scale, dropout_p)
+        ctx.native = rng_state is None and _use_native_backward()
+        ctx.window_size = window_size
         return out.view(t, nq)
 
     @staticmethod
@@ -140,6 +166,10 @@ class _PackedFlashAttention(torch.autograd.Function):
         t = qkv.shape[0]
         nq, nkv = heads * head_dim, kv_heads * head_dim
         dqkv = torch.empty_like(qkv)
+        if ctx.native:
+            attention_backward_native(qkv, 0, qkv, nq, nq + nkv, out, dout.view(t, nq), lse, cu, cu, max_len, heads, kv_heads, head_dim,
+                                      dqkv, dqkv, causal, ctx.window_size, scale)
+            return dqkv, None, None, None, None, None, None, None, None, None
         views = lambda x: (x[:, :nq].view(t, heads, head_dim), x[:, nq : nq + nkv].view(t, kv_heads, head_dim),
                            x[:, nq + nkv :].view(t, kv_heads, head_dim))
         q, k, v = views(qkv)

@@ -144,6 +144,23 @@ def bench_attention(results):
          "peak_kind": kind, "cublas_ms": ms_lib, "cublas_tflops": flops / ms_lib / 1e9, "note": "second pair = flash_attn 2 library"}
     results.append(r)
     print(json.dumps(r), flush=True)
+    # backward: 2.5x the forward FLOPs (five tile products against two)
+    from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
+
+    from fast_llm_b200.ops.attention import attention_backward_native
+
+    out, lse = ours()
+    dout = torch.randn(t, nq, device="cuda", dtype=torch.bfloat16)
+    dqkv = torch.empty_like(qkv)
+    dq, dk, dv = dqkv[:, :nq].view(t, heads, d), dqkv[:, nq:nq + nkv].view(t, kv, d), dqkv[:, nq + nkv:].view(t, kv, d)
+    ours_b = lambda: attention_backward_native(qkv, 0, qkv, nq, nq + nkv, out, dout, lse, cu, cu, t, heads, kv, d, dqkv, dqkv, True, window, d**-0.5)
+    lib_b = lambda: _flash_attn_varlen_backward(dout.view(t, heads, d), q, k, v, out, lse, dq, dk, dv, cu, cu, t, t, 0.0, d**-0.5, True,
+                                                window - 1, 0, 0.0, None, False, None)
+    ms, ms_lib = time_op(ours_b), time_op(lib_b)
+    r = {"op": "attention_bwd_mistral", "ms": ms, "tflops": 2.5 * flops / ms / 1e9, "frac_of_peak": 2.5 * flops / ms / 1e9 / tflops_peak,
+         "peak_kind": kind, "cublas_ms": ms_lib, "cublas_tflops": 2.5 * flops / ms_lib / 1e9, "note": "second pair = flash_attn 2 library"}
+    results.append(r)
+    print(json.dumps(r), flush=True)
 
 
 def profile_gemm():

@@ -308,10 +308,45 @@ def test_attention_forward_tcgen05(doc_lengths, heads, kv_heads, causal, window)
     assert _rel_err(lse[0, :n], expected) < 2e-3
 
 
-def test_packed_attention_native_forward_library_backward():
+@pytest.mark.parametrize("doc_lengths,heads,kv_heads,causal,window", [
+    ([128], 1, 1, True, None),
+    ([256], 2, 1, True, None),
+    ([1000], 4, 2, True, None),
+    ([300, 77, 513, 1], 4, 2, True, None),
+    ([1500], 4, 1, True, 256),
+    ([700, 900], 8, 2, True, 100),
+    ([640], 2, 2, False, None),
+    ([2048], 8, 2, True, 1024),
+])
+def test_attention_backward_tcgen05(doc_lengths, heads, kv_heads, causal, window):
+    """dq, dk, dv of the tcgen05 backward against autograd through the fp32 restatement."""
+    from fast_llm_b200.ops import _lib
+    from fast_llm_b200.ops.attention import attention_reference, packed_attention
+
+    torch.manual_seed(3)
+    d = 128
+    total = sum(doc_lengths)
+    nq, nkv = heads * d, kv_heads * d
+    qkv = torch.randn(total, nq + 2 * nkv, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    cu = torch.tensor([0] + list(torch.tensor(doc_lengths).cumsum(0)), device="cuda", dtype=torch.int32)
+    out = packed_attention(qkv, cu, max(doc_lengths), heads, kv_heads, d, causal=causal, window_size=window)
+    g = torch.randn_like(out)
+    out.backward(g)
+    assert _lib.get_lib().flb_attention_bwd_error_word() == 0
+    ref_in = qkv.detach().float().requires_grad_()
+    ref = attention_reference(ref_in[:, :nq].reshape(total, heads, d), ref_in[:, nq : nq + nkv].reshape(total, kv_heads, d),
+                              ref_in[:, nq + nkv :].reshape(total, kv_heads, d), cu, cu, causal, window, d**-0.5).reshape(total, nq)
+    ref.backward(g.float())
+    assert torch.isfinite(qkv.grad).all()
+    for name, lo, hi in (("dq", 0, nq), ("dk", nq, nq + nkv), ("dv", nq + nkv, nq + 2 * nkv)):
+        assert _rel_err(qkv.grad[:, lo:hi], ref_in.grad[:, lo:hi]) < 3e-2, name
+
+
+def test_packed_attention_native_forward_library_backward(monkeypatch):
     """The autograd path: tcgen05 forward, library backward fed with our log-sum-exp."""
     from fast_llm_b200.ops.attention import attention_reference, packed_attention
 
+    monkeypatch.setenv("FLB_ATTENTION_BWD", "library")
     torch.manual_seed(1)
     heads, kv_heads, d = 4, 2, 128
     lengths = [384, 200]
