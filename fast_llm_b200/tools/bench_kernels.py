@@ -163,6 +163,23 @@ def bench_attention(results):
     print(json.dumps(r), flush=True)
 
 
+def profile_attention():
+    """Small fixed workload for an ncu capture: two forward + backward launches of attention at the Mistral-7B shape."""
+    from fast_llm_b200.ops.attention import attention_backward_native, attention_forward_native
+
+    t, heads, kv, d, window = 8192, 32, 8, 128, 4096
+    nq, nkv = heads * d, kv * d
+    qkv = torch.randn(t, nq + 2 * nkv, device="cuda", dtype=torch.bfloat16)
+    cu = torch.tensor([0, t], device="cuda", dtype=torch.int32)
+    dout = torch.randn(t, nq, device="cuda", dtype=torch.bfloat16)
+    dqkv = torch.empty_like(qkv)
+    for _ in range(2):
+        out, lse = attention_forward_native(qkv, 0, qkv, nq, nq + nkv, cu, cu, t, heads, kv, d, True, window, d**-0.5)
+        attention_backward_native(qkv, 0, qkv, nq, nq + nkv, out, dout, lse, cu, cu, t, heads, kv, d, dqkv, dqkv, True, window, d**-0.5)
+    torch.cuda.synchronize()
+    print("profile_attention done")
+
+
 def profile_gemm():
     """Small fixed workload for an ncu capture: three launches of the fprop GEMM on operands larger than L2."""
     from fast_llm_b200.ops.gemm import matmul_nt
@@ -180,6 +197,8 @@ def main(argv):
     results = []
     if "profile_gemm" in argv:
         return profile_gemm()
+    if "profile_attention" in argv:
+        return profile_attention()
     if "gemm_tiles" in argv:
         bench_gemm_tiles(results)
     if "attention" in argv:
