@@ -1,0 +1,253 @@
+"""State-space / linear-attention recurrences over packed documents: Mamba selective scan, gated delta rule (scalar decay)
+and Kimi delta attention (per-channel decay).
+
+All three are linear recurrences `state_t = decay_t * state_{t-1} + write_t` evaluated chunk by chunk: inside a chunk the
+contributions are combined with pairwise decays `exp(c_t - c_s)`, `s <= t` (always <= 1, so no overflow however strong the
+decay), and the state is carried from chunk to chunk.  `chunked_scan` runs the chunk loop without building an autograd
+graph, keeps only the state at each chunk boundary and re-evaluates one chunk at a time in the backward pass, so memory
+stays at one chunk of intermediates plus `chunks x state`.  Documents never share state: the loop restarts at every
+document boundary given by `cu_seqlens`.
+
+Each op has a token-by-token restatement (`*_reference`) used as the test oracle.
+Parity (semantics): `fast_llm/layers/ssm/mamba.py:183-236` (selective scan call), `fast_llm/layers/ssm/gdn.py:41-210`
+(gated delta rule), `fast_llm/layers/ssm/kda.py:33-203` (KDA and its gate).
+"""
+
+import typing
+
+import torch
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# chunk loop with boundary-state checkpointing
+# ----------------------------------------------------------------------------------------------------------------------
+class _ChunkedScan(torch.autograd.Function):
+    """forward(step, n_seq, n_shared, chunk, boundaries, state0, *seq_inputs, *shared_inputs) -> (outputs, final_state)
+
+    `step(state, seq_chunk_tuple, shared_tuple) -> (out_chunk, new_state)` must be differentiable torch code.
+    `boundaries` is the sorted list of document starts + total length; chunks never straddle a boundary and the state is
+    reset to zero at each document start.
+    """
+
+    @staticmethod
+    def forward(ctx, step, n_seq, chunk, boundaries, state_shape, *tensors):
+        seq, shared = tensors[:n_seq], tensors[n_seq:]
+        ctx.step, ctx.n_seq, ctx.spans = step, n_seq, []
+        outs, states = [], []
+        ref = seq[0]
+        with torch.no_grad():
+            for begin, end in zip(boundaries[:-1], boundaries[1:]):
+                state = torch.zeros(state_shape, dtype=torch.float32, device=ref.device)
+                for lo in range(begin, end, chunk):
+                    hi = min(lo + chunk, end)
+                    states.append(state)
+                    ctx.spans.append((lo, hi, lo == begin))
+                    out, state = step(state, tuple(t[lo:hi] for t in seq), shared)
+                    outs.append(out)
+        ctx.save_for_backward(*tensors, *states)
+        ctx.n_tensors = len(tensors)
+        if not outs:
+            return ref.new_zeros((0,) + tuple(state_shape[:0]))
+        return torch.cat(outs, 0)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        saved = ctx.saved_tensors
+        tensors, states = saved[: ctx.n_tensors], saved[ctx.n_tensors :]
+        seq, shared = tensors[: ctx.n_seq], tensors[ctx.n_seq :]
+        seq_grads = [torch.zeros_like(t) if t.is_floating_point() else None for t in seq]
+        shared_grads = [torch.zeros_like(t, dtype=torch.float32) if t.is_floating_point() else None for t in shared]
+        grad_state = None
+        for index in range(len(ctx.spans) - 1, -1, -1):
+            lo, hi, first = ctx.spans[index]
+            with torch.enable_grad():
+                state_in = states[index].detach().requires_grad_(not first)
+                chunk_in = tuple(t[lo:hi].detach().requires_grad_(t.is_floating_point()) for t in seq)
+                shared_in = tuple(t.detach().requires_grad_(t.is_floating_point()) for t in shared)
+                out, state_out = ctx.step(state_in, chunk_in, shared_in)
+                targets = [out] if grad_state is None else [out, state_out]
+                grads_in = [grad_out[lo:hi]] if grad_state is None else [grad_out[lo:hi], grad_state]
+                wanted = [t for t in (*chunk_in, *shared_in, state_in) if t.requires_grad]
+                grads = torch.autograd.grad(targets, wanted, grads_in, allow_unused=True)
+            it = iter(grads)
+            for i, t in enumerate(chunk_in):
+                if t.requires_grad:
+                    g = next(it)
+                    if g is not None:
+                        seq_grads[i][lo:hi] = g
+            for i, t in enumerate(shared_in):
+                if t.requires_grad:
+                    g = next(it)
+                    if g is not None:
+                        shared_grads[i] += g
+            grad_state = None if first else next(it)
+        shared_grads = [None if g is None else g.to(t.dtype) for g, t in zip(shared_grads, shared)]
+        return (None, None, None, None, None, *seq_grads, *shared_grads)
+
+
+def chunked_scan(step: typing.Callable, state_shape, seq_inputs, shared_inputs, cu_seqlens, chunk: int) -> torch.Tensor:
+    total = seq_inputs[0].shape[0]
+    boundaries = [0, total] if cu_seqlens is None else [int(b) for b in cu_seqlens.tolist()]
+    if boundaries[-1] < total:  # trailing padding forms its own document
+        boundaries.append(total)
+    return _ChunkedScan.apply(step, len(seq_inputs), chunk, boundaries, tuple(state_shape), *seq_inputs, *shared_inputs)
+
+
+def _lower_mask(n: int, device, strict: bool) -> torch.Tensor:
+    return torch.ones(n, n, dtype=torch.bool, device=device).tril(-1 if strict else 0)
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# Mamba selective scan
+# ----------------------------------------------------------------------------------------------------------------------
+def _selective_scan_step(state, chunk_in, shared):
+    """state [d, n]; x, dt, z [L, d]; b, c [L, groups, n] (each group serves d / groups adjacent channels); a [d, n]; skip [d]."""
+    x, dt, b, c, z = chunk_in
+    a, skip, dt_bias = shared
+    if b.shape[1] != x.shape[1]:
+        b = b.repeat_interleave(x.shape[1] // b.shape[1], dim=1)
+    if c.shape[1] != x.shape[1]:
+        c = c.repeat_interleave(x.shape[1] // c.shape[1], dim=1)
+    xf, dtf = x.float(), dt.float()
+    if dt_bias is not None:
+        dtf = dtf + dt_bias.float()
+    dtf = torch.nn.functional.softplus(dtf)
+    log_decay = dtf[:, :, None] * a.float()[None]  # [L, d, n], <= 0
+    cum = log_decay.cumsum(0)
+    write = (dtf * xf)[:, :, None] * b.float()  # [L, d, n]
+    length = x.shape[0]
+    mask = _lower_mask(length, x.device, strict=False)[:, :, None, None]
+    pair = torch.where(mask, (cum[:, None] - cum[None, :]).clamp(max=0.0).exp(), torch.zeros((), device=x.device))
+    states = cum.exp() * state[None] + torch.einsum("tsdn,sdn->tdn", pair, write)
+    y = (states * c.float()).sum(-1) + skip.float()[None] * xf
+    if z is not None:
+        y = y * torch.nn.functional.silu(z.float())
+    return y.to(x.dtype), states[-1]
+
+
+def selective_scan(x, dt, a, b, c, skip, z=None, dt_bias=None, cu_seqlens=None, chunk: int = 16) -> torch.Tensor:
+    """y_t = C_t . h_t + D x_t (times silu(z_t)), h_t = exp(softplus(dt_t + bias) A) h_{t-1} + softplus(.) B_t x_t.
+
+    x, dt, z: [tokens, channels]; a: [channels, state] (negative); b, c: [tokens, groups, state] with `groups` dividing
+    `channels` (group i serves channels [i * channels / groups, (i + 1) * channels / groups)); skip: [channels].
+    """
+    def step(state, chunk_in, shared):
+        xs, dts, bs, cs, *rest = chunk_in
+        zs = rest[0] if z is not None else None
+        a_, skip_, *bias_ = shared
+        return _selective_scan_step(state, (xs, dts, bs, cs, zs), (a_, skip_, bias_[0] if bias_ else None))
+
+    seq = [x, dt, b, c] + ([z] if z is not None else [])
+    shared = [a, skip] + ([dt_bias] if dt_bias is not None else [])
+    return chunked_scan(step, a.shape, seq, shared, cu_seqlens, chunk)
+
+
+def selective_scan_reference(x, dt, a, b, c, skip, z=None, dt_bias=None, cu_seqlens=None) -> torch.Tensor:
+    total = x.shape[0]
+    starts = {0} if cu_seqlens is None else set(int(s) for s in cu_seqlens.tolist())
+    dtf = dt.float() + (0 if dt_bias is None else dt_bias.float())
+    dtf = torch.nn.functional.softplus(dtf)
+    h = torch.zeros_like(a, dtype=torch.float32)
+    ys = []
+    for t in range(total):
+        if t in starts:
+            h = torch.zeros_like(h)
+        bt = b[t].float().repeat_interleave(x.shape[1] // b.shape[1], dim=0)
+        ct = c[t].float().repeat_interleave(x.shape[1] // c.shape[1], dim=0)
+        h = (dtf[t][:, None] * a.float()).exp() * h + (dtf[t] * x[t].float())[:, None] * bt
+        y = (h * ct).sum(-1) + skip.float() * x[t].float()
+        if z is not None:
+            y = y * torch.nn.functional.silu(z[t].float())
+        ys.append(y)
+    return torch.stack(ys).to(x.dtype)
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# Delta rule with scalar (gated DeltaNet) or per-channel (KDA) decay
+# ----------------------------------------------------------------------------------------------------------------------
+def l2_normalize(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    return x * torch.rsqrt((x * x).sum(-1, keepdim=True) + eps)
+
+
+def _delta_rule_step(state, chunk_in, shared):
+    """One chunk of S_t = Decay_t S_{t-1} + beta_t k_t (v_t - k_t^T Decay_t S_{t-1})^T ; o_t = S_t^T q_t.
+
+    state [h, dk, dv]; q, k [L, h, dk]; v [L, h, dv]; g [L, h] or [L, h, dk] (log decay); beta [L, h].
+    With u_t the corrected values, (I + Lmat) U = V - (K o Gamma) S_0 where Lmat[t, s] = beta_s <k_t, k_s>_{decay(t, s)} (s < t).
+    """
+    q, k, v, g, beta = (t.float() for t in chunk_in)
+    length = q.shape[0]
+    per_channel = g.dim() == 3
+    cum = g.cumsum(0)  # inclusive
+    low = _lower_mask(length, q.device, strict=False)
+    if per_channel:
+        pair = torch.where(low[:, :, None, None], (cum[:, None] - cum[None, :]).clamp(max=0.0).exp(), torch.zeros((), device=q.device))
+        kk = torch.einsum("thd,shd,tshd->hts", k, k, pair)
+        qk = torch.einsum("thd,shd,tshd->hts", q, k, pair)
+        k_in = k * cum.exp()  # reads of the incoming state
+        q_in = q * cum.exp()
+        k_out = k * (cum[-1:] - cum).exp()  # writes carried to the chunk end
+        state_decay = cum[-1].exp()[:, :, None]
+    else:
+        pair = torch.where(low[:, :, None], (cum[:, None] - cum[None, :]).clamp(max=0.0).exp(), torch.zeros((), device=q.device))  # [t, s, h]
+        pair = pair.permute(2, 0, 1)
+        kk = torch.einsum("thd,shd->hts", k, k) * pair
+        qk = torch.einsum("thd,shd->hts", q, k) * pair
+        k_in = k * cum.exp()[:, :, None]
+        q_in = q * cum.exp()[:, :, None]
+        k_out = k * (cum[-1:] - cum).exp()[:, :, None]
+        state_decay = cum[-1].exp()[:, None, None]
+    beta_h = beta.t()  # [h, L]
+    strict = _lower_mask(length, q.device, strict=True)
+    system = torch.eye(length, device=q.device)[None] + torch.where(strict[None], kk * beta_h[:, None, :], torch.zeros((), device=q.device))
+    rhs = v.transpose(0, 1) - torch.einsum("thd,hde->hte", k_in, state)  # [h, L, dv]
+    u = torch.linalg.solve_triangular(system, rhs, upper=False, unitriangular=True)
+    ub = u * beta_h[:, :, None]
+    out = torch.einsum("thd,hde->hte", q_in, state) + torch.einsum("hts,hse->hte", qk, ub)
+    new_state = state * state_decay + torch.einsum("shd,hse->hde", k_out, ub)
+    return out.transpose(0, 1).to(chunk_in[2].dtype), new_state
+
+
+def chunk_delta_rule(q, k, v, g, beta, cu_seqlens=None, chunk: int = 64, normalize_qk: bool = True, scale: float | None = None) -> torch.Tensor:
+    """q, k [tokens, heads, dk]; v [tokens, heads, dv]; g [tokens, heads(, dk)] log decay; beta [tokens, heads] -> [tokens, heads, dv]."""
+    if normalize_qk:
+        q, k = l2_normalize(q.float()), l2_normalize(k.float())
+    q = q * (q.shape[-1] ** -0.5 if scale is None else scale)
+    heads, dk, dv = q.shape[1], q.shape[2], v.shape[2]
+    if g.dim() == 3:
+        chunk = min(chunk, 32)  # the pairwise per-channel decay tensor is [L, L, heads, dk]
+    return chunked_scan(_delta_rule_step, (heads, dk, dv), [q, k, v, g, beta], [], cu_seqlens, chunk)
+
+
+def delta_rule_reference(q, k, v, g, beta, cu_seqlens=None, normalize_qk: bool = True, scale: float | None = None) -> torch.Tensor:
+    if normalize_qk:
+        q, k = l2_normalize(q.float()), l2_normalize(k.float())
+    q = q.float() * (q.shape[-1] ** -0.5 if scale is None else scale)
+    k, vf, gf, bf = k.float(), v.float(), g.float(), beta.float()
+    total, heads, dk = q.shape
+    starts = {0} if cu_seqlens is None else set(int(s) for s in cu_seqlens.tolist())
+    state = torch.zeros(heads, dk, v.shape[2], dtype=torch.float32, device=q.device)
+    outs = []
+    for t in range(total):
+        if t in starts:
+            state = torch.zeros_like(state)
+        decay = gf[t].exp()
+        state = state * (decay[:, :, None] if gf.dim() == 3 else decay[:, None, None])
+        read = torch.einsum("hd,hde->he", k[t], state)
+        state = state + bf[t][:, None, None] * torch.einsum("hd,he->hde", k[t], vf[t] - read)
+        outs.append(torch.einsum("hd,hde->he", q[t], state))
+    return torch.stack(outs).to(v.dtype)
+
+
+def gdn_log_decay(alpha: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor) -> torch.Tensor:
+    """g = -exp(A_log) * softplus(alpha + dt_bias); alpha [tokens, heads]."""
+    return -a_log.float().exp() * torch.nn.functional.softplus(alpha.float() + dt_bias.float())
+
+
+def kda_gate(g: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor | None = None) -> torch.Tensor:
+    """Per-channel log decay: -exp(A_log[head]) * softplus(g + dt_bias); g [tokens, heads, head_dim]."""
+    heads, dim = g.shape[-2:]
+    g = g.float()
+    if dt_bias is not None:
+        g = g + dt_bias.float().view(heads, dim)
+    return -a_log.float().view(heads, 1).exp() * torch.nn.functional.softplus(g)
