@@ -115,3 +115,55 @@ def test_hybrid_model_trains(name):
     losses = train_steps(trainer, 6)
     assert all(torch.isfinite(torch.tensor(losses)))
     assert losses[-1] < losses[0]
+
+
+def _stochastic_config(**kwargs):
+    base = copy.deepcopy(TINY_BASE_MODEL)
+    attention = base["decoder"]["block"]["mixer"]
+    base["decoder"]["block"]["mixer"] = {"type": "stochastic", "mixers": {"attention": attention, "gdn": MIXERS["gdn"]}, **kwargs}
+    base["decoder"]["num_blocks"] = 4
+    return tiny_trainer_config({("model", "base_model"): base, ("data", "micro_batch_size"): 64})
+
+
+def _stochastic_layers(trainer):
+    from fast_llm_b200.layers.stochastic_mixer import StochasticMixer
+
+    return [layer for _, layer in trainer._multi_stage.base_model.named_sublayers() if isinstance(layer, StochasticMixer)]
+
+
+@pytest.mark.parametrize("strategy", ["uniform", "full_layout"])
+def test_stochastic_mixer_trains_and_samples(strategy):
+    trainer, _ = build_trainer(_stochastic_config(sampling_strategy=strategy))
+    losses = train_steps(trainer, 8)
+    assert all(torch.isfinite(torch.tensor(losses)))
+    layers = _stochastic_layers(trainer)
+    assert len(layers) == 4
+    totals = {"attention": 0, "gdn": 0}
+    for layer in layers:
+        assert sum(layer.selection_counts.values()) == 8
+        for name, count in layer.selection_counts.items():
+            totals[name] += count
+    assert totals["attention"] > 0 and totals["gdn"] > 0
+
+
+def test_stochastic_mixer_predefined_layout_and_eval():
+    layout = ["gdn", "attention", "attention", "gdn"]
+    trainer, _ = build_trainer(_stochastic_config(predefined_layouts=[layout], predefined_layout_probabilities=[1.0]))
+    train_steps(trainer, 3)
+    for layer, expected in zip(_stochastic_layers(trainer), layout):
+        assert layer.selection_counts[expected] == 3
+    # outside training the main mixer (the first one) runs
+    layer = _stochastic_layers(trainer)[0]
+    assert layer._sample_mixer_name({"training": False}) == "attention"
+
+
+def test_stochastic_allocation_is_a_composition():
+    trainer, _ = build_trainer(_stochastic_config(sampling_strategy="full_layout"))
+    layer = _stochastic_layers(trainer)[0]
+    generator = torch.Generator().manual_seed(0)
+    seen = set()
+    for _ in range(200):
+        counts = layer.sample_allocation(4, generator)
+        assert sum(counts) == 4 and all(c >= 0 for c in counts)
+        seen.add(tuple(counts))
+    assert seen == {(i, 4 - i) for i in range(5)}
