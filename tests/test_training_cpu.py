@@ -204,3 +204,27 @@ def test_mixtral_export_matches_transformers(tmp_path):
     runner = InferenceRunner(model)
     runner.setup(model.distributed)
     torch.testing.assert_close(runner.forward_tokens(tokens[0]), expected, rtol=3e-4, atol=3e-4)
+
+
+def test_multi_token_prediction():
+    """Extra prediction heads train; with zero weight on them the trunk behaves exactly like the plain model."""
+    import copy
+
+    from tests.common import TINY_BASE_MODEL
+
+    def run(heads, coefficients):
+        base = copy.deepcopy(TINY_BASE_MODEL)
+        base["head"]["prediction_heads"] = heads
+        if coefficients is not None:
+            base["head"]["prediction_loss_coefficient"] = coefficients
+        trainer, _ = build_trainer(tiny_trainer_config({("model", "base_model"): base}))
+        return trainer, train_steps(trainer, 3)
+
+    _, plain = run(1, None)
+    trainer, silent = run(2, [1.0, 0.0])
+    assert plain == pytest.approx(silent, rel=1e-5)
+    trainer, both = run(3, [1.0, 0.5, 0.25])
+    names = {meta.tensor_name for _, meta in trainer._multi_stage.base_model.named_parameter_metas()}
+    assert "multi_token_prediction.blocks.1.mlp.layer_1.weight" in names
+    assert "multi_token_prediction.heads.0.final_norm.weight" in names
+    assert both != pytest.approx(plain, rel=1e-5)  # the extra heads change the trunk's gradients
