@@ -158,11 +158,15 @@ class BlendedDatasetConfig(SampledDatasetConfig):
 class GPTRandomDatasetConfig(SampledDatasetConfig):
     _abstract: typing.ClassVar[bool] = False
     name: str = Field(default="dummy", hint=FieldHint.core)
+    images_per_sample: int = Field(default=0, desc="Synthetic images placed in every sample (multimodal models).", hint=FieldHint.testing)
+    image_patch_grid: tuple[int, int] = Field(default=(2, 2), desc="Patches per synthetic image (rows, columns).", hint=FieldHint.testing)
+    image_patch_shape: tuple[int, int, int] = Field(default=(3, 16, 16), desc="Shape of one patch (channels, height, width).", hint=FieldHint.testing)
 
     def build_and_sample(self, sampling: SamplingConfig, num_samples: int, seed: int):
         from fast_llm_b200.data.random import GPTRandomSampledDataset
 
-        return GPTRandomSampledDataset(sampling, self.name, num_samples, seed)
+        return GPTRandomSampledDataset(sampling, self.name, num_samples, seed, images_per_sample=self.images_per_sample,
+                                       image_patch_grid=tuple(self.image_patch_grid), image_patch_shape=tuple(self.image_patch_shape))
 
 
 @config_class(dynamic_type={SampledDatasetConfig: "file"})

@@ -10,7 +10,9 @@ from fast_llm_b200.data.document import LanguageModelDocument
 
 
 class GPTRandomSampledDataset:
-    def __init__(self, sampling, name: str, num_samples: int, seed: int):
+    def __init__(self, sampling, name: str, num_samples: int, seed: int, images_per_sample: int = 0,
+                 image_patch_grid: tuple[int, int] = (2, 2), image_patch_shape: tuple[int, int, int] = (3, 16, 16)):
+        self._images, self._grid, self._patch_shape = images_per_sample, image_patch_grid, image_patch_shape
         self._name = name
         self._seed = seed
         self._sampling = sampling
@@ -23,7 +25,20 @@ class GPTRandomSampledDataset:
     def __getitem__(self, index: int) -> list[LanguageModelDocument]:
         rng = np.random.RandomState((self._seed + 48576439 + 74593 * index) % 2**32)
         tokens = rng.randint(0, self._vocab_size, size=(self._sampling.sample_size,))
-        return [LanguageModelDocument(tokens=torch.from_numpy(tokens))]
+        document = LanguageModelDocument(tokens=torch.from_numpy(tokens))
+        if self._images:
+            # every image occupies rows * columns consecutive token positions, images spread evenly over the sample
+            rows, columns = self._grid
+            per_image = rows * columns
+            stride = len(tokens) // self._images
+            assert stride >= per_image, "sample too short for the requested synthetic images"
+            positions = torch.cat([torch.arange(per_image) + i * stride for i in range(self._images)])
+            coordinates = torch.stack(torch.meshgrid(torch.arange(rows), torch.arange(columns), indexing="ij"), -1).reshape(-1, 2).repeat(self._images, 1)
+            pixels = rng.randint(0, 256, size=(len(positions), *self._patch_shape)).astype(np.uint8)
+            document.image_patches = torch.from_numpy(pixels)
+            document.image_patch_positions = positions
+            document.image_patch_coordinates = coordinates
+        return [document]
 
     @property
     def name(self) -> str:

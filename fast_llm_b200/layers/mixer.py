@@ -28,8 +28,8 @@ class BlockConfig(ModuleConfig):
 class BlockWithBiasConfig(BlockConfig):
     """A sub-layer that may hand its output bias to the caller for fusion with the residual add."""
 
-    def get_layer(self, distributed_config, hidden_dim, *, lr_scale=None, peft=None, return_bias: bool = False):
-        return self.layer_class(self, distributed_config, hidden_dim=hidden_dim, lr_scale=lr_scale, peft=peft, return_bias=return_bias)
+    def get_layer(self, distributed_config, hidden_dim, *, lr_scale=None, peft=None, return_bias: bool = False, **kwargs):
+        return self.layer_class(self, distributed_config, hidden_dim=hidden_dim, lr_scale=lr_scale, peft=peft, return_bias=return_bias, **kwargs)
 
 
 @config_class(registry=True)

@@ -43,9 +43,10 @@ class MLPConfig(MLPBaseConfig):
 
 class MLP(LayerBase):
     def __init__(self, config: MLPConfig, distributed_config, *, hidden_dim: TensorDim, lr_scale=None, peft=None,
-                 return_bias: bool = False, experts_dim: TensorDim | None = None):
+                 return_bias: bool = False, experts_dim: TensorDim | None = None, output_dim: TensorDim | None = None):
         super().__init__(config, distributed_config, lr_scale=combine_lr_scales(lr_scale, config.lr_scale), peft=peft)
         self._hidden_dim = hidden_dim
+        self._output_dim = output_dim or hidden_dim  # an adapter maps to another width
         self._sequence_parallel = distributed_config.sequence_tensor_parallel
         tp_dim = distributed_config.get_distributed_dim(DistributedDimNames.tensor)
         ffn_dim = TensorDim("intermediate", config.intermediate_size, tp_dim)
@@ -57,7 +58,7 @@ class MLP(LayerBase):
         common = dict(default_add_bias=config.add_linear_biases, lr_scale=self._lr_scale, peft=peft, distributed_config=distributed_config)
         self.layer_1 = config.layer_1.get_layer(hidden_dim, l1_dim, default_weight_initialization=init_normal_(0.0, hidden_dim.global_size**-0.5),
                                                 sequence_parallel=self._sequence_parallel, **common)
-        self.layer_2 = config.layer_2.get_layer(ffn_dim, hidden_dim, default_weight_initialization=init_normal_(0.0, hidden_dim.global_size**-0.5),
+        self.layer_2 = config.layer_2.get_layer(ffn_dim, getattr(self, "_output_dim", hidden_dim), default_weight_initialization=init_normal_(0.0, hidden_dim.global_size**-0.5),
                                                 sequence_parallel=self._sequence_parallel, transposed_weight=True, **common)
 
     def forward(self, x: torch.Tensor, kwargs: dict | None = None, losses=None, metrics=None) -> torch.Tensor:

@@ -1,0 +1,77 @@
+"""Vision encoder + language model: the multimodal model trains end to end and image patches reach the right tokens."""
+
+import copy
+
+import torch
+
+from tests.common import TINY_BASE_MODEL, build_trainer, train_steps
+
+
+def _config(updates=None):
+    import fast_llm_b200.models.auto  # noqa: F401
+    from fast_llm_b200.models.multimodal.config import MultiModalTrainerConfig
+
+    base = copy.deepcopy(TINY_BASE_MODEL)
+    base["vision_encoder"] = {
+        "hidden_size": 32,
+        "embeddings": {"patch_height": 4, "patch_width": 4, "normalization": {"type": "rms_norm"}},
+        "encoder": {"num_blocks": 2, "block": {
+            "mixer": {"heads": 2, "head_groups": 2, "head_size": 16, "causal": False, "rotary": {"type": "default_2d"}, "add_linear_biases": False},
+            "mlp": {"intermediate_size": 64, "gated": True, "add_linear_biases": False}, "normalization": {"type": "rms_norm"}}},
+        "adapter": {"intermediate_size": 48, "add_linear_biases": True},
+    }
+    config = {
+        "training": {"train_iters": 4, "num_workers": 0, "logs": {"interval": 1}},
+        "data": {"datasets": {"training": {"type": "random", "images_per_sample": 3, "image_patch_grid": [2, 3], "image_patch_shape": [3, 4, 4]}},
+                 "micro_batch_size": 128, "seed": 0},
+        "optimizer": {"learning_rate": {"base": 1e-3}},
+        "model": {"base_model": base,
+                  "distributed": {"compute_dtype": "float32", "use_cuda": False, "seed": 0, "world_size": 1, "rank": 0, "local_world_size": 1}},
+    }
+    return MultiModalTrainerConfig.from_dict(config, updates or {})
+
+
+def test_multimodal_model_trains():
+    trainer, _ = build_trainer(_config())
+    losses = train_steps(trainer, 5)
+    assert all(torch.isfinite(torch.tensor(losses)))
+    assert losses[-1] < losses[0]
+    names = {meta.tensor_name for _, meta in trainer._multi_stage.base_model.named_parameter_metas()}
+    assert "vision_encoder.embeddings.patch_embeddings.weight" in names
+    assert "vision_encoder.encoder.1.mixer.query.weight" in names
+    assert "vision_encoder.adapter.layer_2.weight" in names
+    # every vision parameter received gradient signal: it moved away from its initial value
+    assert "decoder.0.mlp.layer_1.weight" in names
+
+
+def test_image_patches_are_added_at_their_tokens():
+    """Zeroing the pixels of one image changes the embedding output only at that image's token positions."""
+    from fast_llm_b200.data.document import LanguageModelBatch, LanguageModelDocument
+    from fast_llm_b200.parallel.topology import PhaseType
+
+    trainer, _ = build_trainer(_config())
+    model = trainer._multi_stage.base_model
+    for stage in trainer._multi_stage.stages:
+        stage.restore_parameters()
+    torch.manual_seed(0)
+    tokens = torch.randint(0, 512, (129,))
+    coordinates = torch.tensor([[0, 0], [0, 1], [1, 0], [1, 1]] * 2)
+    positions = torch.tensor([5, 6, 7, 8, 40, 41, 42, 43])
+
+    def embed(pixels):
+        document = LanguageModelDocument(tokens=tokens, image_patches=pixels, image_patch_positions=positions, image_patch_coordinates=coordinates)
+        batch = LanguageModelBatch.from_documents([document], 129)
+        inputs = batch.get_model_inputs(micro_batch_size=128)
+        (ids, kwargs), = model.preprocess_batch(inputs, phase=PhaseType.inference, iteration=0)
+        hidden = None
+        for layer in model.get_layers()[:5]:  # patch embeddings, 2 encoder blocks, adapter, token embeddings
+            hidden = layer.forward(ids if hidden is None else hidden, kwargs)
+        return hidden
+
+    pixels = torch.randint(0, 256, (8, 3, 4, 4), dtype=torch.uint8)
+    changed = pixels.clone()
+    changed[4:] = 0
+    with torch.no_grad():
+        a, b = embed(pixels), embed(changed)
+    moved = ((a - b).abs().sum(-1) > 1e-6).nonzero().flatten().tolist()
+    assert moved == [40, 41, 42, 43]
