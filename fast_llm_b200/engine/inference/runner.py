@@ -41,8 +41,9 @@ class InferenceRunner:
         return kwargs
 
     @torch.no_grad()
-    def forward_tokens(self, tokens: torch.Tensor, document_lengths: list[int] | None = None) -> torch.Tensor:
-        """Logits [tokens, vocab] for a flat token stream (one document unless lengths are given)."""
+    def forward_tokens(self, tokens: torch.Tensor, document_lengths: list[int] | None = None, output_hidden_states=None):
+        """Logits [tokens, vocab] for a flat token stream (one document unless lengths are given).  With
+        `output_hidden_states` (a list of layer names, possibly empty) returns `(logits, {name: hidden})`."""
         n = len(tokens)
         lengths = document_lengths or [n]
         batch = LanguageModelBatch(tokens=torch.cat([tokens.cpu().long(), torch.full((1,), -100, dtype=torch.long)]),
@@ -51,7 +52,12 @@ class InferenceRunner:
         kwargs = inp.to_kwargs(self._distributed.device)
         kwargs.pop("labels", None)
         kwargs["return_logits"] = True
+        if output_hidden_states:
+            kwargs["output_hidden_states"] = set(output_hidden_states)
+            kwargs["hidden_states"] = {}
         for layer in self._model.base_model.get_layers():
             layer.preprocess(kwargs)
         self.forward_kwargs(kwargs["token_ids"], kwargs)
+        if output_hidden_states is not None:
+            return kwargs["logits"], kwargs.get("hidden_states", {})
         return kwargs["logits"]
