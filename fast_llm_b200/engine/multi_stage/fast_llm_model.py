@@ -26,6 +26,18 @@ class FastLLMModel(MultiStageModel):
         metadata = self._config.to_metadata(config, shards=list(handler.get_shard_names(config)), metadata=extra_metadata or {})
         handler.save(config, metadata)
 
+    def iter_exported_tensors(self, config):
+        """Yield (shard name, exported tensor name, tensor) in the checkpoint format of `config` without touching disk
+        (used to stream weights to inference workers).  Collective: every rank must iterate."""
+        config.validate()
+        config.setup(type(self._config))
+        handler = config.format.get_handler_class()(self)
+        pending: dict = {}
+        data_type = config.data_type.torch if getattr(config, "data_type", None) is not None else None
+        for parameter_name, shard_name, tensor in self.get_state_tensor_iterator(handler.get_shard_names(config), data_type):
+            for name, converted in handler._export_tensors(parameter_name, shard_name, tensor, pending).items():
+                yield shard_name, name, converted
+
     def load_checkpoint(self, config: CheckpointLoadConfig) -> dict | None:
         config.validate()
         config.setup(type(self._config))

@@ -104,7 +104,10 @@ class Trainer:
     # ------------------------------------------------------------------------------------------------
     def run(self) -> None:
         assert self._is_setup
-        with self._config.profiling.get_profiler(distributed_config=self._config.model.distributed, start_step=self._completed_steps, run=self._run) as profiler:
+        from fast_llm_b200.engine.training.wandb import Wandb
+
+        self._wandb = Wandb(self._config.training.wandb, self._run, self._config, module=getattr(self, "_wandb_module", None))
+        with self._wandb, self._config.profiling.get_profiler(distributed_config=self._config.model.distributed, start_step=self._completed_steps, run=self._run) as profiler:
             self._run_training(profiler)
 
     def _run_training(self, profiler) -> None:
@@ -155,7 +158,10 @@ class Trainer:
                     nan_iters += not all(math.isfinite(v) for v in reduced_losses.values())
                 self._completed_steps += 1
                 for callback in self._callbacks.values():
-                    callback.step_end(self._completed_steps, reduced_losses, update_successful, step_metrics)
+                    extra = callback.step_end(self._completed_steps, reduced_losses, update_successful, step_metrics,
+                                              self._completed_steps * self._samples_per_batch)
+                    if extra and step_metrics is not None:
+                        step_metrics.update(extra)
                 if is_logging:
                     if has_gpu:
                         torch.cuda.synchronize()
