@@ -1,0 +1,48 @@
+"""The evaluation-harness adapter, without the harness: scores and generations against direct computation."""
+
+import torch
+
+from tests.common import build_trainer, tiny_trainer_config
+from tests.test_preparation import tokenizer_path  # noqa: F401  (fixture)
+
+
+def test_loglikelihood_and_generation(tokenizer_path):  # noqa: F811
+    from fast_llm_b200.data.config import TokenizerConfig
+    from fast_llm_b200.engine.evaluation.evaluators import FastLLMLmEvalWrapper
+    from fast_llm_b200.engine.inference.huggingface import HuggingfaceGPTModelForCausalLM
+
+    trainer, _ = build_trainer(tiny_trainer_config())
+    model = HuggingfaceGPTModelForCausalLM(trainer._multi_stage)
+    tokenizer = TokenizerConfig.from_dict({"path": str(tokenizer_path)}).get_tokenizer()
+    wrapper = FastLLMLmEvalWrapper(model, tokenizer, batch_size=2, max_new_tokens=5)
+    requests = [("the quick brown", " fox jumps"), ("hello", " world"), ("pack my box with", " five"), ("", "hello world")]
+    scores = wrapper.loglikelihood(requests)
+    assert len(scores) == 4
+    for (context, continuation), (score, greedy) in zip(requests, scores):
+        context_tokens, continuation_tokens = wrapper._encode_pair(context, continuation)
+        ids = torch.tensor([context_tokens + continuation_tokens])
+        log_probs = torch.log_softmax(model(input_ids=ids).logits[0].float(), -1)
+        n = len(continuation_tokens)
+        expected = sum(log_probs[len(context_tokens) - 1 + i, t].item() for i, t in enumerate(continuation_tokens))
+        assert abs(score - expected) < 1e-3, (context, continuation)
+        assert isinstance(greedy, bool) and n > 0
+    rolling = wrapper.loglikelihood_rolling([("the quick brown fox",)])
+    tokens = wrapper.tok_encode("the quick brown fox")
+    assert abs(rolling[0] - wrapper._score([([tokenizer.bod_id], tokens)])[0][0]) < 1e-4
+    text = wrapper.generate_until([("the quick", {"until": ["\n"], "max_gen_toks": 4})])
+    assert isinstance(text[0], str)
+
+
+def test_evaluate_command(tmp_path, capsys):
+    """`fast-llm evaluate gpt ...` runs the configured evaluators once without training."""
+    from fast_llm_b200.cli import fast_llm_main
+
+    args = ["evaluate", "gpt", "model.base_model.embeddings.vocab_size=512", "model.base_model.hidden_size=64",
+            "model.base_model.decoder.num_blocks=1", "model.base_model.decoder.block.mixer.heads=4", "model.base_model.decoder.block.mixer.head_groups=2",
+            "model.base_model.decoder.block.mixer.head_size=16", "model.base_model.decoder.block.mixer.rotary.type=default",
+            "model.base_model.decoder.block.mlp.intermediate_size=128", "model.distributed.use_cuda=false", "model.distributed.compute_dtype=float32",
+            "data.datasets.validation.type=random", "data.micro_batch_size=64", "training.evaluators.validation.iterations=2",
+            "training.evaluators.validation.interval=1", "training.num_workers=0"]
+    fast_llm_main(args)
+    captured = capsys.readouterr()
+    assert "validation @ validation" in captured.out + captured.err and "lm loss" in captured.out + captured.err
