@@ -25,6 +25,7 @@
 // global error word, every role leaves its loop, TMEM is released and the kernel returns.  The host reads the error
 // word with flb_gemm_error_word().
 #include "tcgen05.cuh"
+#include <cstdlib>
 #include <mutex>
 
 namespace {
@@ -38,7 +39,8 @@ struct Cfg {
   static constexpr int B_BYTES = BLOCK_N * BLOCK_K * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BLOCK_N == 256) ? 4 : 6;
-  static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int TILE_BYTES = RING_BYTES + 4 * kEpiWarpBytes;  // operand ring + epilogue staging (4 warps)
   static constexpr int BAR_BYTES = 256;
   static constexpr int SMEM_BYTES = TILE_BYTES + BAR_BYTES + 1024;  // + slack for 1024-byte alignment
   static constexpr int TMEM_COLS = 2 * BLOCK_N;                     // 512 or 256 (powers of two)
@@ -46,8 +48,9 @@ struct Cfg {
 
 template <int BLOCK_N, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(kNumThreads, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, void* __restrict__ Cv,
-            int M, int N, int K, long long ldc, int* __restrict__ err_word) {
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const __grid_constant__ CUtensorMap tmap_c, int use_tma_c, void* __restrict__ Cv, int M, int N, int K, long long ldc,
+            int* __restrict__ err_word) {
   using C = Cfg<BLOCK_N>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -175,6 +178,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int it = 0;
     bool ok = true;
+    uint32_t epi_counter = 0;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
       int m_blk, n_blk;
       tile_coords(tile, num_m, num_n, m_blk, n_blk);
@@ -184,17 +188,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       tc_fence_after();
       const int row = m_blk * BLOCK_M + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BLOCK_N;
+      if (use_tma_c) {
+        epilogue_tma<EPI>(&tmap_c, smem + C::RING_BYTES + q * kEpiWarpBytes, taddr, BLOCK_N, m_blk * BLOCK_M + q * 32, n_blk * BLOCK_N, M, N,
+                          lane, epi_counter);
+      } else {
 #pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c * 32, r);
-        tmem_wait_ld();
-        store_chunk<EPI>(r, Cv, row, n_blk * BLOCK_N + c * 32, M, N, ldc);
+        for (int c = 0; c < BLOCK_N / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_wait_ld();
+          store_chunk<EPI>(r, Cv, row, n_blk * BLOCK_N + c * 32, M, N, ldc);
+        }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
     }
+    if (lane == 0) tma_store_wait_all();
   }
 
   tc_fence_before();
@@ -214,7 +224,8 @@ struct PairCfg {
   static constexpr int B_BYTES = (TILE_N / 2) * BLOCK_K * 2;   // this CTA's half of the B tile
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;        // 32 KiB
   static constexpr int STAGES = 6;
-  static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int TILE_BYTES = RING_BYTES + 4 * kEpiWarpBytes;  // operand ring + epilogue staging (4 warps)
   static constexpr int BAR_BYTES = 256;
   static constexpr int SMEM_BYTES = TILE_BYTES + BAR_BYTES + 1024;
   static constexpr int TMEM_COLS = 2 * TILE_N;
@@ -222,8 +233,9 @@ struct PairCfg {
 
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
-gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, void* __restrict__ Cv,
-                 int M, int N, int K, long long ldc, int* __restrict__ err_word) {
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_c, int use_tma_c, void* __restrict__ Cv, int M, int N, int K, long long ldc,
+                 int* __restrict__ err_word) {
   using C = PairCfg;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -360,6 +372,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int q = warp & 3;
     int it = 0;
     bool ok = true;
+    uint32_t epi_counter = 0;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
       int m_blk, n_blk;
       tile_coords(tile, num_m, num_n, m_blk, n_blk);
@@ -369,17 +382,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tc_fence_after();
       const int row = m_blk * C::TILE_M + (int)cta_rank * BLOCK_M + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * C::TILE_N;
+      if (use_tma_c) {
+        epilogue_tma<EPI>(&tmap_c, smem + C::RING_BYTES + q * kEpiWarpBytes, taddr, C::TILE_N,
+                          m_blk * C::TILE_M + (int)cta_rank * BLOCK_M + q * 32, n_blk * C::TILE_N, M, N, lane, epi_counter);
+      } else {
 #pragma unroll 1
-      for (int c = 0; c < C::TILE_N / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c * 32, r);
-        tmem_wait_ld();
-        store_chunk<EPI>(r, Cv, row, n_blk * C::TILE_N + c * 32, M, N, ldc);
+        for (int c = 0; c < C::TILE_N / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_wait_ld();
+          store_chunk<EPI>(r, Cv, row, n_blk * C::TILE_N + c * 32, M, N, ldc);
+        }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
     }
+    if (lane == 0) tma_store_wait_all();
   }
 
   tc_fence_before();
@@ -430,6 +449,33 @@ bool make_tmap(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer
   return r == CUDA_SUCCESS;
 }
 
+// 2-D tensor map over the output: boxes of 32 rows x 128 bytes (64 bf16 or 32 fp32 columns), 128-byte swizzle.
+bool make_tmap_c(CUtensorMap* map, void* ptr, uint64_t cols, uint64_t rows, uint64_t ld_elems, bool f32) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld_elems * (f32 ? 4 : 2)};
+  cuuint32_t box[2] = {f32 ? 32u : 64u, 32u};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = CUDA_SUCCESS;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    r = enc(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_ERROR_INVALID_CONTEXT) break;
+    cudaFree(nullptr);
+  }
+  return r == CUDA_SUCCESS;
+}
+
+// FLB_GEMM_EPILOGUE=direct keeps the register -> global epilogue (for comparisons); default is the TMA epilogue.
+bool tma_epilogue_enabled() {
+  static const bool enabled = [] {
+    const char* v = getenv("FLB_GEMM_EPILOGUE");
+    return !(v && v[0] == 'd');
+  }();
+  return enabled;
+}
+
 struct DeviceState {
   int num_sms = 0;
   int* err_word = nullptr;
@@ -452,8 +498,8 @@ DeviceState* device_state() {
 }
 
 template <int BLOCK_N, bool A_MN, bool B_MN, int EPI>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, long long ldc, int max_ctas,
-           DeviceState* st, cudaStream_t stream) {
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, int use_tc, void* C, int M, int N, int K, long long ldc,
+           int max_ctas, DeviceState* st, cudaStream_t stream) {
   using Cf = Cfg<BLOCK_N>;
   auto kern = gemm_kernel<BLOCK_N, A_MN, B_MN, EPI>;
   static bool configured = false;
@@ -466,14 +512,14 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, 
   int grid = st->num_sms;
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = tiles;
-  kern<<<grid, kNumThreads, Cf::SMEM_BYTES, stream>>>(ta, tb, C, M, N, K, ldc, st->err_word);
+  kern<<<grid, kNumThreads, Cf::SMEM_BYTES, stream>>>(ta, tb, tc, use_tc, C, M, N, K, ldc, st->err_word);
   FLB_CHECK_LAUNCH();
   return FLB_OK;
 }
 
 template <bool A_MN, bool B_MN, int EPI>
-int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, long long ldc, int max_ctas,
-                DeviceState* st, cudaStream_t stream) {
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, int use_tc, void* C, int M, int N, int K,
+                long long ldc, int max_ctas, DeviceState* st, cudaStream_t stream) {
   auto kern = gemm_pair_kernel<A_MN, B_MN, EPI>;
   static bool configured = false;
   if (!configured) {
@@ -485,39 +531,39 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, in
   int clusters = st->num_sms / 2;
   if (max_ctas > 1 && max_ctas / 2 < clusters) clusters = max_ctas / 2;
   if (tiles < clusters) clusters = tiles;
-  kern<<<2 * clusters, kNumThreads, PairCfg::SMEM_BYTES, stream>>>(ta, tb, C, M, N, K, ldc, st->err_word);
+  kern<<<2 * clusters, kNumThreads, PairCfg::SMEM_BYTES, stream>>>(ta, tb, tc, use_tc, C, M, N, K, ldc, st->err_word);
   FLB_CHECK_LAUNCH();
   return FLB_OK;
 }
 
 template <int BLOCK_N, bool A_MN, bool B_MN>
-int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, long long ldc,
-                 int max_ctas, DeviceState* st, cudaStream_t stream) {
+int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, int use_tc, void* C, int M, int N, int K,
+                 long long ldc, int max_ctas, DeviceState* st, cudaStream_t stream) {
   if constexpr (BLOCK_N == 0) {
     switch (epi) {
-      case EPI_STORE_BF16: return launch_pair<A_MN, B_MN, EPI_STORE_BF16>(ta, tb, C, M, N, K, ldc, max_ctas, st, stream);
-      case EPI_STORE_F32: return launch_pair<A_MN, B_MN, EPI_STORE_F32>(ta, tb, C, M, N, K, ldc, max_ctas, st, stream);
-      case EPI_ACC_F32: return launch_pair<A_MN, B_MN, EPI_ACC_F32>(ta, tb, C, M, N, K, ldc, max_ctas, st, stream);
-      case EPI_ACC_BF16: return launch_pair<A_MN, B_MN, EPI_ACC_BF16>(ta, tb, C, M, N, K, ldc, max_ctas, st, stream);
+      case EPI_STORE_BF16: return launch_pair<A_MN, B_MN, EPI_STORE_BF16>(ta, tb, tc, use_tc, C, M, N, K, ldc, max_ctas, st, stream);
+      case EPI_STORE_F32: return launch_pair<A_MN, B_MN, EPI_STORE_F32>(ta, tb, tc, use_tc, C, M, N, K, ldc, max_ctas, st, stream);
+      case EPI_ACC_F32: return launch_pair<A_MN, B_MN, EPI_ACC_F32>(ta, tb, tc, use_tc, C, M, N, K, ldc, max_ctas, st, stream);
+      case EPI_ACC_BF16: return launch_pair<A_MN, B_MN, EPI_ACC_BF16>(ta, tb, tc, use_tc, C, M, N, K, ldc, max_ctas, st, stream);
     }
   } else {
     switch (epi) {
-      case EPI_STORE_BF16: return launch<BLOCK_N, A_MN, B_MN, EPI_STORE_BF16>(ta, tb, C, M, N, K, ldc, max_ctas, st, stream);
-      case EPI_STORE_F32: return launch<BLOCK_N, A_MN, B_MN, EPI_STORE_F32>(ta, tb, C, M, N, K, ldc, max_ctas, st, stream);
-      case EPI_ACC_F32: return launch<BLOCK_N, A_MN, B_MN, EPI_ACC_F32>(ta, tb, C, M, N, K, ldc, max_ctas, st, stream);
-      case EPI_ACC_BF16: return launch<BLOCK_N, A_MN, B_MN, EPI_ACC_BF16>(ta, tb, C, M, N, K, ldc, max_ctas, st, stream);
+      case EPI_STORE_BF16: return launch<BLOCK_N, A_MN, B_MN, EPI_STORE_BF16>(ta, tb, tc, use_tc, C, M, N, K, ldc, max_ctas, st, stream);
+      case EPI_STORE_F32: return launch<BLOCK_N, A_MN, B_MN, EPI_STORE_F32>(ta, tb, tc, use_tc, C, M, N, K, ldc, max_ctas, st, stream);
+      case EPI_ACC_F32: return launch<BLOCK_N, A_MN, B_MN, EPI_ACC_F32>(ta, tb, tc, use_tc, C, M, N, K, ldc, max_ctas, st, stream);
+      case EPI_ACC_BF16: return launch<BLOCK_N, A_MN, B_MN, EPI_ACC_BF16>(ta, tb, tc, use_tc, C, M, N, K, ldc, max_ctas, st, stream);
     }
   }
   return FLB_ERR_SHAPE;
 }
 
 template <int BLOCK_N>
-int dispatch_major(int a_mn, int b_mn, int epi, const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N,
-                   int K, long long ldc, int max_ctas, DeviceState* st, cudaStream_t stream) {
-  if (!a_mn && !b_mn) return dispatch_epi<BLOCK_N, false, false>(epi, ta, tb, C, M, N, K, ldc, max_ctas, st, stream);
-  if (!a_mn && b_mn) return dispatch_epi<BLOCK_N, false, true>(epi, ta, tb, C, M, N, K, ldc, max_ctas, st, stream);
-  if (a_mn && !b_mn) return dispatch_epi<BLOCK_N, true, false>(epi, ta, tb, C, M, N, K, ldc, max_ctas, st, stream);
-  return dispatch_epi<BLOCK_N, true, true>(epi, ta, tb, C, M, N, K, ldc, max_ctas, st, stream);
+int dispatch_major(int a_mn, int b_mn, int epi, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, int use_tc, void* C,
+                   int M, int N, int K, long long ldc, int max_ctas, DeviceState* st, cudaStream_t stream) {
+  if (!a_mn && !b_mn) return dispatch_epi<BLOCK_N, false, false>(epi, ta, tb, tc, use_tc, C, M, N, K, ldc, max_ctas, st, stream);
+  if (!a_mn && b_mn) return dispatch_epi<BLOCK_N, false, true>(epi, ta, tb, tc, use_tc, C, M, N, K, ldc, max_ctas, st, stream);
+  if (a_mn && !b_mn) return dispatch_epi<BLOCK_N, true, false>(epi, ta, tb, tc, use_tc, C, M, N, K, ldc, max_ctas, st, stream);
+  return dispatch_epi<BLOCK_N, true, true>(epi, ta, tb, tc, use_tc, C, M, N, K, ldc, max_ctas, st, stream);
 }
 
 }  // namespace
@@ -551,11 +597,18 @@ FLB_API int flb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, i
   if (!b_mn_major) ok = make_tmap(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BLOCK_K, b_rows);
   else ok = make_tmap(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BLOCK_K);
   if (!ok) return FLB_ERR_TMA;
+  // C goes out through TMA stores (reduce-adds for the accumulate epilogues) when its layout allows a tensor map
+  const bool c_f32 = (epilogue == EPI_STORE_F32 || epilogue == EPI_ACC_F32);
+  const long long c_elem = c_f32 ? 4 : 2;
+  CUtensorMap tc = ta;
+  int use_tc = 0;
+  if (!(reinterpret_cast<uintptr_t>(C) & 15) && (ldc * c_elem) % 16 == 0 && tma_epilogue_enabled())
+    use_tc = make_tmap_c(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, c_f32) ? 1 : 0;
   if (block_n == 512)
-    return dispatch_major<0>(a_mn_major, b_mn_major, epilogue, ta, tb, C, M, N, K, ldc, max_ctas, st, stream);
+    return dispatch_major<0>(a_mn_major, b_mn_major, epilogue, ta, tb, tc, use_tc, C, M, N, K, ldc, max_ctas, st, stream);
   if (block_n == 256)
-    return dispatch_major<256>(a_mn_major, b_mn_major, epilogue, ta, tb, C, M, N, K, ldc, max_ctas, st, stream);
-  return dispatch_major<128>(a_mn_major, b_mn_major, epilogue, ta, tb, C, M, N, K, ldc, max_ctas, st, stream);
+    return dispatch_major<256>(a_mn_major, b_mn_major, epilogue, ta, tb, tc, use_tc, C, M, N, K, ldc, max_ctas, st, stream);
+  return dispatch_major<128>(a_mn_major, b_mn_major, epilogue, ta, tb, tc, use_tc, C, M, N, K, ldc, max_ctas, st, stream);
 }
 
 // Reads (and clears) the error word the GEMM kernels raise when a bounded wait expires.

@@ -204,6 +204,76 @@ __device__ __forceinline__ void store_chunk(const uint32_t* r, void* Cv, int row
 }
 
 // Cluster helpers.
+// ---- epilogue through shared memory and TMA stores -------------------------------------------------------------------
+// A warp drains its 32 accumulator rows in pieces of one 128-byte row segment (64 bf16 or 32 fp32 columns): registers ->
+// swizzled shared memory (conflict-free 16-byte stores) -> one TMA tensor store (or reduce-add, for the accumulate
+// epilogues) per piece.  Two 4 KiB buffers per warp alternate; `cp.async.bulk.wait_group.read 1` guards their reuse.
+constexpr int kEpiWarpBytes = 2 * 4096;
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap), "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* tmap, uint32_t src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap), "r"(src),
+               "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// Drains `width` accumulator columns starting at TMEM address `taddr` (this warp's lane quarter) into rows row0..row0+31,
+// columns col0.. of C.  `counter` alternates the two buffers across calls.  Rows / columns past M / N are clipped by TMA.
+template <int EPI>
+__device__ __forceinline__ void epilogue_tma(const CUtensorMap* tmap_c, uint8_t* warp_buf, uint32_t taddr, int width, int row0,
+                                             int col0, int M, int N, int lane, uint32_t& counter) {
+  constexpr bool kF32 = (EPI == EPI_STORE_F32 || EPI == EPI_ACC_F32);
+  constexpr bool kReduce = (EPI == EPI_ACC_F32 || EPI == EPI_ACC_BF16);
+  constexpr int kCols = kF32 ? 32 : 64;
+#pragma unroll 1
+  for (int c = 0; c < width; c += kCols) {
+    if (row0 >= M || col0 + c >= N) break;  // nothing of this piece (nor of the following ones) lies inside C
+    uint8_t* buf = warp_buf + (counter & 1u) * 4096;
+    ++counter;
+    if (lane == 0) tma_store_wait_read_1();
+    __syncwarp();
+    uint8_t* row_ptr = buf + lane * 128;
+    if constexpr (kF32) {
+      uint32_t r[32];
+      tmem_ld32(taddr + c, r);
+      tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<uint4*>(row_ptr + ((j ^ (lane & 7)) << 4)) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+    } else {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c + h * 32, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t pk[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2 * e]), __uint_as_float(r[8 * j + 2 * e + 1]));
+            pk[e] = *reinterpret_cast<uint32_t*>(&b);
+          }
+          *reinterpret_cast<uint4*>(row_ptr + (((h * 4 + j) ^ (lane & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+      }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) {
+      if constexpr (kReduce) tma_reduce_add_2d(tmap_c, smem_u32(buf), col0 + c, row0);
+      else tma_store_2d(tmap_c, smem_u32(buf), col0 + c, row0);
+      tma_store_commit();
+    }
+  }
+}
+
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));

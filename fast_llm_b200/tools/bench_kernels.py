@@ -180,6 +180,26 @@ def profile_attention():
     print("profile_attention done")
 
 
+def profile_gemm_shapes():
+    """ncu workload: one launch each of the CTA-pair GEMM in four layouts / shapes of the Mistral-7B MLP."""
+    from fast_llm_b200.ops.gemm import matmul_nn, matmul_nt
+
+    t, h, f = 8192, 4096, 14336
+    x = torch.randn(t, h, device="cuda", dtype=torch.bfloat16)
+    w1 = torch.randn(2 * f, h, device="cuda", dtype=torch.bfloat16)
+    dy1 = torch.randn(t, 2 * f, device="cuda", dtype=torch.bfloat16)
+    w2 = torch.randn(f, h, device="cuda", dtype=torch.bfloat16)   # stored transposed: [ffn, hidden]
+    a2 = torch.randn(t, f, device="cuda", dtype=torch.bfloat16)
+    dy2 = torch.randn(t, h, device="cuda", dtype=torch.bfloat16)
+    for _ in range(2):
+        matmul_nt(x, w1)        # mlp1 fprop  [8192, 28672, 4096]  A, B K-major
+        matmul_nn(dy1, w1)      # mlp1 dgrad  [8192, 4096, 28672]  B MN-major
+        matmul_nn(a2, w2)       # mlp2 fprop  [8192, 4096, 14336]  B MN-major (transposed weight)
+        matmul_nt(dy2, w2)      # mlp2 dgrad  [8192, 14336, 4096]  A, B K-major
+    torch.cuda.synchronize()
+    print("profile_gemm_shapes done")
+
+
 def profile_gemm():
     """Small fixed workload for an ncu capture: three launches of the fprop GEMM on operands larger than L2."""
     from fast_llm_b200.ops.gemm import matmul_nt
@@ -197,6 +217,8 @@ def main(argv):
     results = []
     if "profile_gemm" in argv:
         return profile_gemm()
+    if "profile_gemm_shapes" in argv:
+        return profile_gemm_shapes()
     if "profile_attention" in argv:
         return profile_attention()
     if "gemm_tiles" in argv:
