@@ -575,9 +575,10 @@ int dispatch_major(int a_mn, int b_mn, int epi, const CUtensorMap& ta, const CUt
 //   block_n: 0 = choose; 128 / 256 = one-CTA kernel with that tile width; 512 = CTA-pair kernel (256 x 256 tiles).
 //   max_ctas: limit the persistent grid (0 = one CTA per SM).
 // Pointers must be 16-byte aligned and lda/ldb multiples of 8 elements (TMA stride rule).
-FLB_API int flb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
-                          long long ldc, int a_mn_major, int b_mn_major, int epilogue, int block_n, int max_ctas,
-                          cudaStream_t stream) {
+// flags: bit 0 = write C with plain register stores instead of TMA (used when C is another GPU's memory).
+FLB_API int flb_gemm_bf16_ex(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                             long long ldc, int a_mn_major, int b_mn_major, int epilogue, int block_n, int max_ctas, int flags,
+                             cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return FLB_ERR_SHAPE;
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
     return FLB_ERR_SHAPE;
@@ -602,7 +603,7 @@ FLB_API int flb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, i
   const long long c_elem = c_f32 ? 4 : 2;
   CUtensorMap tc = ta;
   int use_tc = 0;
-  if (!(reinterpret_cast<uintptr_t>(C) & 15) && (ldc * c_elem) % 16 == 0 && tma_epilogue_enabled())
+  if (!(flags & 1) && !(reinterpret_cast<uintptr_t>(C) & 15) && (ldc * c_elem) % 16 == 0 && tma_epilogue_enabled())
     use_tc = make_tmap_c(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, c_f32) ? 1 : 0;
   if (block_n == 512)
     return dispatch_major<0>(a_mn_major, b_mn_major, epilogue, ta, tb, tc, use_tc, C, M, N, K, ldc, max_ctas, st, stream);
@@ -613,6 +614,12 @@ FLB_API int flb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, i
 
 // Reads (and clears) the error word the GEMM kernels raise when a bounded wait expires.
 // Synchronises the device.  0 = no error; 1..4 / 11..14 = which role gave up (one-CTA / pair kernel).
+FLB_API int flb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                          long long ldc, int a_mn_major, int b_mn_major, int epilogue, int block_n, int max_ctas,
+                          cudaStream_t stream) {
+  return flb_gemm_bf16_ex(A, B, C, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, epilogue, block_n, max_ctas, 0, stream);
+}
+
 FLB_API int flb_gemm_error_word() {
   DeviceState* st = device_state();
   if (!st) return -1;

@@ -142,6 +142,56 @@ FLB_API int flb_symm_barrier(const void* const* signal_pads, int rank, int world
   return FLB_OK;
 }
 
+// out[i] = sum over slots s (in slot order) of in[s * n + i]; bf16 in and out, fp32 accumulation.  The reduce step of the
+// fused GEMM + reduce-scatter: every tensor-parallel peer stored its partial tile rows into one slot of this rank's
+// staging buffer from inside its GEMM epilogue.
+__global__ void slot_sum_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int slots, long long n) {
+  const long long nvec = n >> 3;
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < slots; ++s) {
+      float f[8];
+      unpack8(*reinterpret_cast<const bf16x8*>(in + s * n + v * 8), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+    *reinterpret_cast<bf16x8*>(out + v * 8) = pack8(acc);
+  }
+}
+
+// Pull `bytes` (multiple of 16) from a peer's memory into local memory with a small grid, so that it can run beside a
+// GEMM on the remaining SMs: the gather half of the fused all-gather + GEMM.  Remote lines are not cached in the local
+// L2, so operands that many tiles re-read must cross NVLink once and be read locally afterwards.
+__global__ void peer_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long n16) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  // four independent loads in flight per thread hide the NVLink round trip
+  for (; i + 3 * stride < n16; i += 4 * stride) {
+    const uint4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], d = src[i + 3 * stride];
+    dst[i] = a; dst[i + stride] = b; dst[i + 2 * stride] = c; dst[i + 3 * stride] = d;
+  }
+  for (; i < n16; i += stride) dst[i] = src[i];
+}
+
+FLB_API int flb_peer_copy(const void* src, void* dst, long long bytes, int ctas, cudaStream_t stream) {
+  if (bytes % 16 || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15)) return FLB_ERR_SHAPE;
+  if (bytes == 0) return FLB_OK;
+  if (ctas <= 0) ctas = 24;
+  peer_copy_kernel<<<ctas, 512, 0, stream>>>((const uint4*)src, (uint4*)dst, bytes >> 4);
+  FLB_CHECK_LAUNCH();
+  return FLB_OK;
+}
+
+FLB_API int flb_slot_sum_bf16(const void* in, void* out, int slots, long long n, cudaStream_t stream) {
+  if (n % 8 || slots <= 0) return FLB_ERR_SHAPE;
+  if (n == 0) return FLB_OK;
+  long long blocks = ((n >> 3) + kThreads - 1) / kThreads;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  slot_sum_kernel<<<(int)blocks, kThreads, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, slots, n);
+  FLB_CHECK_LAUNCH();
+  return FLB_OK;
+}
+
 FLB_API int flb_rs_reduce_blocks() { return 148 * 4; }
 
 // grad_ptrs[r]: rank r's gradient buffer of the stage (grad_dtype 0 fp32 / 1 bf16).  sumsq_partial: flb_rs_reduce_blocks()

@@ -182,6 +182,13 @@ class MultiStageModel:
             and num_grad_buffers == len(local) and symmetric_memory_available(self._distributed.data_group, device)
         )
 
+        # tensor-parallel GEMMs fused with their all-gather / reduce-scatter (sequence-parallel layout)
+        if (ms.fused_collectives and dist_config.tensor_parallel > 1 and dist_config.sequence_tensor_parallel
+                and dist_config.compute_dtype.torch == torch.bfloat16 and symmetric_memory_available(self._distributed.tensor_group, device)):
+            from fast_llm_b200.parallel import fused_tp
+
+            fused_tp.enable_lazy(self._distributed.tensor_group, device)
+
         def carve(sizes_bytes: list[int], what: str):
             aligned = [(n + 255) // 256 * 256 for n in sizes_bytes]
             arena = SymmetricArena(sum(aligned), self._distributed.data_group, device)

@@ -19,6 +19,7 @@ _p, _i, _ll, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_flo
 
 _SIGNATURES = {
     "flb_gemm_bf16": [_p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _i, _i, _p],
+    "flb_gemm_bf16_ex": [_p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _p],
     "flb_gemm_error_word": [],
     "flb_norm_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _f, _i, _i, _p],
     "flb_norm_bwd_parts": [_i],
@@ -49,6 +50,8 @@ _SIGNATURES = {
     "flb_symm_barrier": [_p, _i, _i, _i, ctypes.c_uint, _p, _p],
     "flb_rs_reduce_blocks": [],
     "flb_rs_reduce": [_p, _i, _i, _i, _ll, _f, _p, _i, _p, _p],
+    "flb_slot_sum_bf16": [_p, _p, _i, _ll, _p],
+    "flb_peer_copy": [_p, _p, _ll, _i, _p],
     "flb_adam_push": [_p, _p, _p, _p, _p, _i, _ll, _ll, _f, _f, _f, _f, _f, _i, _f, _p, _p],
 }
 

@@ -36,15 +36,20 @@ def _native_ok(a: torch.Tensor, b: torch.Tensor) -> bool:
     )
 
 
-def gemm_raw(a, b, out, m, n, k, a_mn, b_mn, epilogue, block_n=None, max_ctas=0):
-    """block_n: None/0 = choose (CTA-pair kernel for large shapes), 128/256 = one-CTA kernel, 512 = CTA-pair kernel."""
+def gemm_raw(a, b, out, m, n, k, a_mn, b_mn, epilogue, block_n=None, max_ctas=0, *, a_ptr=None, b_ptr=None, c_ptr=None,
+             direct_store: bool = False):
+    """block_n: None/0 = choose (CTA-pair kernel for large shapes), 128/256 = one-CTA kernel, 512 = CTA-pair kernel.
+
+    `a_ptr` / `b_ptr` / `c_ptr` replace the address of the corresponding tensor (same layout, e.g. the same buffer in a
+    tensor-parallel peer's symmetric memory); `direct_store` writes C with register stores instead of TMA."""
     lib = _lib.get_lib()
     if block_n is None:
         block_n = int(os.environ.get("FLB_GEMM_BLOCK_N", 0))
     _lib.check(
-        lib.flb_gemm_bf16(
-            a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k, a.stride(0), b.stride(0), out.stride(0),
-            int(a_mn), int(b_mn), epilogue, block_n, max_ctas, _lib.stream_ptr(),
+        lib.flb_gemm_bf16_ex(
+            a.data_ptr() if a_ptr is None else a_ptr, b.data_ptr() if b_ptr is None else b_ptr,
+            out.data_ptr() if c_ptr is None else c_ptr, m, n, k, a.stride(0), b.stride(0), out.stride(0),
+            int(a_mn), int(b_mn), epilogue, block_n, max_ctas, int(direct_store), _lib.stream_ptr(),
         ),
         "flb_gemm_bf16",
     )

@@ -14,6 +14,7 @@ import torch
 
 from fast_llm_b200.ops.gemm import matmul_nn, matmul_nt, matmul_tn
 from fast_llm_b200.ops.param_grad import accumulate_param_grad, wgrad_target
+from fast_llm_b200.parallel import fused_tp
 from fast_llm_b200.parallel.ops import gather_op, reduce_op, reduce_scatter_op
 
 
@@ -45,11 +46,18 @@ class _Linear(torch.autograd.Function):
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
         x_in = x2
-        if mode == "output" and sequence_parallel and group is not None:
-            x2 = gather_op(x2, group, 0)
-        y = _forward_matmul(x2, weight, transposed_weight)
-        if mode == "input" and group is not None:
-            y = reduce_scatter_op(y, group, dim=0) if sequence_parallel else reduce_op(y, group)
+        fused = fused_tp.usable(group, sequence_parallel, x2, weight)
+        world = group.size() if group is not None else 1
+        if fused is not None and mode == "output" and fused.fits(x2.shape[0] * world, x2.shape[1]):
+            y = fused.all_gather_matmul(x2, weight, transposed_weight)  # the gather is the GEMM's operand fetch
+        elif fused is not None and mode == "input" and fused.fits(x2.shape[0], weight.shape[1] if transposed_weight else weight.shape[0]):
+            y = fused.matmul_reduce_scatter(x2, weight, transposed_weight)  # partial tiles leave from the epilogue
+        else:
+            if mode == "output" and sequence_parallel and group is not None:
+                x2 = gather_op(x2, group, 0)
+            y = _forward_matmul(x2, weight, transposed_weight)
+            if mode == "input" and group is not None:
+                y = reduce_scatter_op(y, group, dim=0) if sequence_parallel else reduce_op(y, group)
         if bias is not None:
             y = y + bias
         # Parameters are views of buffers that ZeRO-3 re-fills between forward and backward (with the same values):
@@ -68,6 +76,14 @@ class _Linear(torch.autograd.Function):
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         db = bias_grad(dy2, bias) if bias is not None else None
+        fused = fused_tp.usable(group, sequence_parallel, dy2, x_in, weight) if mode in ("input", "output") else None
+        if fused is not None:
+            world = group.size()
+            tokens = max(dy2.shape[0], x_in.shape[0])
+            if not (fused.fits(tokens, dy2.shape[1] if mode == "input" else x_in.shape[1]) and tokens == min(dy2.shape[0], x_in.shape[0]) * world):
+                fused = None
+        if fused is not None:
+            return _Linear._backward_fused(ctx, fused, dy2, x_in, weight, transposed_weight, mode, db)
         x2 = x_in
         if mode == "input" and sequence_parallel and group is not None:
             dy2 = gather_op(dy2, group, 0)
@@ -87,6 +103,28 @@ class _Linear(torch.autograd.Function):
         if reduce_handle is not None:
             reduce_handle.wait()
         return dx, dw, db, None, None, None, None
+
+
+def _backward_fused(ctx, fused, dy2, x_in, weight, transposed_weight, mode, db):
+    """Backward of a sequence-parallel linear layer with every collective folded into a GEMM."""
+    has_buffer = weight.requires_grad or getattr(weight, "grad_buffer", None) is not None
+    buf, accumulate = wgrad_target(weight) if has_buffer else (None, False)
+    out = buf.view(weight.shape) if buf is not None else (torch.empty(weight.shape, dtype=weight.dtype, device=weight.device) if has_buffer else None)
+    if mode == "output":
+        # dy holds all tokens (local output features); x is sharded over tokens
+        dx = fused.matmul_reduce_scatter(dy2, weight, not transposed_weight) if ctx.needs_input_grad[0] else None
+        if out is not None:  # dW = dy^T gather(x)   (or gather(x)^T dy for a transposed weight)
+            fused.gathered_wgrad(dy2, x_in, out, accumulate, shard_is_a=transposed_weight)
+    else:
+        # dy is sharded over tokens; x holds all tokens (local input features)
+        dx = fused.all_gather_matmul(dy2, weight, not transposed_weight) if ctx.needs_input_grad[0] else None
+        if out is not None:  # dW = gather(dy)^T x   (or x^T gather(dy))
+            fused.gathered_wgrad(x_in, dy2, out, accumulate, shard_is_a=not transposed_weight)
+    dw = None if buf is not None else out
+    return dx, dw, db, None, None, None, None
+
+
+_Linear._backward_fused = staticmethod(_backward_fused)
 
 
 def linear(x, weight, bias=None, *, transposed_weight: bool = False, mode: str = "none", group=None,

@@ -191,7 +191,11 @@ def profile_gemm_shapes():
     w2 = torch.randn(f, h, device="cuda", dtype=torch.bfloat16)   # stored transposed: [ffn, hidden]
     a2 = torch.randn(t, f, device="cuda", dtype=torch.bfloat16)
     dy2 = torch.randn(t, h, device="cuda", dtype=torch.bfloat16)
+    from fast_llm_b200.ops.gemm import matmul_tn
+
+    grad1 = torch.zeros(2 * f, h, device="cuda", dtype=torch.float32)
     for _ in range(2):
+        matmul_tn(dy1, x, out=grad1, accumulate=True)   # mlp1 wgrad [28672, 4096, 8192]  A, B MN-major, fp32 accumulate
         matmul_nt(x, w1)        # mlp1 fprop  [8192, 28672, 4096]  A, B K-major
         matmul_nn(dy1, w1)      # mlp1 dgrad  [8192, 4096, 28672]  B MN-major
         matmul_nn(a2, w2)       # mlp2 fprop  [8192, 4096, 14336]  B MN-major (transposed weight)
