@@ -6,6 +6,8 @@
 //     S  = Q_i K_j^T          dP = dO_i V_j^T                       (accumulators T0 / T1 in TMEM, alternating)
 //     dV += P^T dO_i          dK += dS^T Q_i                        (accumulators resident in TMEM for the whole CTA)
 //     dQ_i = dS K_j           (into the TMEM buffer S occupied; drained with vector fp32 reductions into dq_accum)
+// The MMA thread issues S of the next pair as soon as dS of this pair has left its TMEM buffer, so the compute warps work
+// on P(n + 1) while dK(n) / dQ(n) run; softmax statistics are loaded one pair ahead.
 // Eight compute warps (two per TMEM lane quarter, each pair splitting the 128 columns) turn S into P = exp2(S c - lse),
 // dP into dS = P (dP - delta) scale, write both as bf16 into swizzled shared-memory tiles that serve as MN-major A
 // operands (P^T, dS^T) and as the K-major A operand (dS) without any transposition, and drain dQ.
@@ -131,18 +133,23 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       bool ok = mbar_wait(bar(0), 0, abort_flag, p.err_word, 43);
       auto kmajor = [&](uint32_t base, int k) { return make_smem_desc(base + (k >> 2) * PANEL + (k & 3) * 32, 16, 1024); };
       auto mnmajor = [&](uint32_t base, int k) { return make_smem_desc(base + k * 2048, PANEL, 1024); };
+      // S(n) = Q K^T into T[n & 1]; issued one pair ahead (right after dS(n - 1) released that buffer)
+      auto issue_s = [&](int n) -> bool {
+        const int s = n & 1;
+        if (!mbar_wait(bar(1 + s), (n >> 1) & 1, abort_flag, p.err_word, 44)) return false;   // Q(n) landed
+        tc_fence_after();
+        const uint32_t qb = sb + S_Q + s * TILE;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_bf16(tmem_t(s), kmajor(qb, k), kmajor(sb + S_K, k), idesc_kk, k != 0);
+        umma_commit(bar(7));
+        return true;
+      };
+      if (ok && num_pairs > 0) ok = issue_s(0);
       for (int n = 0; n < num_pairs && ok; ++n) {
         const int s = n & 1;
-        const uint32_t ph = (n >> 1) & 1;
         const uint32_t par = n & 1;
         const uint32_t t_s = tmem_t(s), t_dp = tmem_t(s ^ 1);
         const uint32_t qb = sb + S_Q + s * TILE;
-        // S = Q K^T   (its TMEM buffer was released when dS of the previous pair was produced)
-        if (!mbar_wait(bar(1 + s), ph, abort_flag, p.err_word, 44)) { ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 8; ++k) umma_bf16(t_s, kmajor(qb, k), kmajor(sb + S_K, k), idesc_kk, k != 0);
-        umma_commit(bar(7));
         // dP = dO V^T  (its buffer held dQ of the previous pair: wait until that was drained)
         if (!mbar_wait(bar(5), par, abort_flag, p.err_word, 45)) { ok = false; break; }
         if (n > 0 && !mbar_wait(bar(12), (n - 1) & 1, abort_flag, p.err_word, 46)) { ok = false; break; }
@@ -156,8 +163,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_bf16(tmem_dv, mnmajor(sb + S_P, k), mnmajor(sb + S_DO, k), idesc_mm, (n | k) != 0);
         umma_commit(bar(6));  // dO slot free
-        // dK += dS^T Q ; dQ = dS K
+        // dS(n) is in shared memory: its source buffer T[s ^ 1] is free for S(n + 1), which goes first so that the compute
+        // warps can start on P(n + 1) while dK / dQ of this pair run
         if (!mbar_wait(bar(11), par, abort_flag, p.err_word, 48)) { ok = false; break; }
+        if (n + 1 < num_pairs && !issue_s(n + 1)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_bf16(tmem_dk, mnmajor(sb + S_DS, k), mnmajor(qb, k), idesc_mm, (n | k) != 0);
@@ -176,31 +185,32 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     uint8_t* p_row = smem + S_P + half * PANEL + r * 128;
     uint8_t* ds_row = smem + S_DS + half * PANEL + r * 128;
     bool ok = true;
-    for (int n = 0; n < num_pairs && ok; ++n) {
-      const int s = n & 1;
-      const uint32_t par = n & 1;
-      const int head = pair_head(n), q0 = pair_q0(n);
-      const int qi = q0 + r;
-      const bool row_ok = qi < q_len;
-      const long long stat_idx = (long long)head * p.total_q + q_begin + qi;
-      const float lse2 = row_ok ? p.lse[stat_idx] * 1.4426950408889634f : 0.f;
-      const float delta = row_ok ? p.delta[stat_idx] : 0.f;
+    const int cbase = half * 64;
+    // softmax statistics of the row this thread owns, loaded one pair ahead of their use
+    auto load_stats = [&](int n, float& lse2, float& delta) {
+      const bool in_range = n < num_pairs && pair_q0(min(n, num_pairs - 1)) + r < q_len;
+      const int n_ = min(n, num_pairs - 1);
+      const long long idx = (long long)pair_head(n_) * p.total_q + q_begin + pair_q0(n_) + r;
+      lse2 = in_range ? p.lse[idx] * 1.4426950408889634f : 0.f;
+      delta = in_range ? p.delta[idx] : 0.f;
+    };
+    uint32_t pk[32];
+    // P(n) = exp2(S(n) c - lse) -> registers (kept for dS) and shared memory (operand of dV)
+    auto compute_p = [&](int n, float lse2) -> bool {
+      const int qi = pair_q0(n) + r;
       // visible key columns of this row inside the key block: [col_lo, col_hi)
       int col_hi = k_len - k0;
       if (p.causal) col_hi = min(col_hi, qi + shift + 1 - k0);
       int col_lo = 0;
       if (p.window > 0) col_lo = max(0, qi + shift - p.window + 1 - k0);
-      if (!row_ok) col_hi = col_lo;  // rows past the document contribute nothing
-      const int cbase = half * 64;
+      if (qi >= q_len) col_hi = col_lo;  // rows past the document contribute nothing
       const bool full = (col_lo <= cbase) && (col_hi >= cbase + 64);
-      // ---- P = exp2(S c - lse)
-      if (!mbar_wait(bar(7), par, abort_flag, p.err_word, 49)) { ok = false; break; }
+      if (!mbar_wait(bar(7), n & 1, abort_flag, p.err_word, 49)) return false;
       tc_fence_after();
-      uint32_t pk[32];
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
-        tmem_ld32(tmem_t(s) + lane_addr + cbase + c * 32, v);
+        tmem_ld32(tmem_t(n & 1) + lane_addr + cbase + c * 32, v);
         tmem_wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -215,8 +225,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           pk[c * 16 + (i >> 1)] = *reinterpret_cast<uint32_t*>(&b);
         }
       }
-      // the P tile may be overwritten once the previous pair's dV MMA is done; that MMA precedes dQ of the previous pair,
-      // whose completion (bar 9) this thread already observed while draining dQ
+      // the completion of S(n) that was just observed also covers dV(n - 1), the last reader of the P tile
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch)
         *reinterpret_cast<uint4*>(p_row + ((ch ^ (r & 7)) << 4)) = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
@@ -224,7 +233,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(10));
-      // ---- dS = P (dP - delta) scale
+      return true;
+    };
+    float lse2_next = 0.f, delta_next = 0.f, delta = 0.f;
+    if (num_pairs > 0) {
+      load_stats(0, lse2_next, delta_next);
+      delta = delta_next;
+      ok = compute_p(0, lse2_next);
+      load_stats(1, lse2_next, delta_next);
+    }
+    for (int n = 0; n < num_pairs && ok; ++n) {
+      const int s = n & 1;
+      const uint32_t par = n & 1;
+      // ---- dS(n) = P (dP - delta) scale
       if (!mbar_wait(bar(8), par, abort_flag, p.err_word, 50)) { ok = false; break; }
       tc_fence_after();
       uint32_t dsk[32];
@@ -242,6 +263,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           dsk[c * 16 + (i >> 1)] = *reinterpret_cast<uint32_t*>(&b);
         }
       }
+      // dK(n - 1) / dQ(n - 1), the last readers of the dS tile, completed before dQ(n - 1) was drained
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch)
         *reinterpret_cast<uint4*>(ds_row + ((ch ^ (r & 7)) << 4)) = make_uint4(dsk[ch * 4], dsk[ch * 4 + 1], dsk[ch * 4 + 2], dsk[ch * 4 + 3]);
@@ -249,9 +271,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(11));
-      // ---- drain dQ (this thread: 64 of the 128 head-dimension columns of its row)
+      // ---- P(n + 1), while dK(n) / dQ(n) run
+      if (n + 1 < num_pairs) {
+        delta = delta_next;
+        if (!compute_p(n + 1, lse2_next)) { ok = false; break; }
+        load_stats(n + 2, lse2_next, delta_next);
+      }
+      // ---- drain dQ(n) (this thread: 64 of the 128 head-dimension columns of its row)
       if (!mbar_wait(bar(9), par, abort_flag, p.err_word, 51)) { ok = false; break; }
       tc_fence_after();
+      const int head = pair_head(n), qi = pair_q0(n) + r;
+      const bool row_ok = qi < q_len;
       // accumulator layout [head][token / 32][column / 4][token % 32][4]: the 32 rows of a warp are adjacent
       const long long tok = q_begin + qi;
       float* dq_row = p.dq_accum + ((((long long)head * p.tok_groups + (tok >> 5)) * (D / 4) + (cbase >> 2)) * 32 + (tok & 31)) * 4;
@@ -270,6 +300,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(12));
     }
+    if (ok && num_pairs > 0) tc_fence_after();
     // ---- write dK, dV of this key block (bf16); rows past the document are skipped
     if (ok && num_pairs > 0) {
       // the last commit (bar 9 of the last pair) covered every MMA; it was observed above

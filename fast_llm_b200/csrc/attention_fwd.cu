@@ -1,15 +1,17 @@
 // Flash-attention forward on tcgen05 tensor cores: packed variable-length documents, causal + sliding window, GQA,
 // head size 128, bf16 in / bf16 out, fp32 softmax statistics.
 //
-// One CTA owns 128 query rows of one head of one document and walks the key/value tiles (128 rows) it may see:
-//   warp 0      TMA: Q once, then K_j / V_j into two-deep rings
-//   warp 1      one thread issues  S_j = Q K_j^T  (tcgen05.mma, accumulator in TMEM, two S buffers)  and
-//               O += P_j V_j  (P_j read from shared memory, V_j as an MN-major operand)
-//   warps 2-5   softmax, one query row per thread: tcgen05.ld of the S row, running max / sum in the exp2 domain,
-//               masks on the diagonal and window edges, P_j written as bf16 into the swizzled K-major tile the second
-//               MMA reads, O rescaled in TMEM only when the running max moved by more than 2^8 (lazy rescaling);
-//               finally O / l is written out with the row's log-sum-exp.
-// The S buffer of tile j+1 is computed while tile j is in softmax.  All mbarrier waits are bounded (error word).
+// One CTA owns TWO 128-row query tiles (256 consecutive rows) of one head of one document and walks the key/value tiles
+// (128 rows) either of them may see; the two query tiles share every K / V tile and alternate on the tensor pipe, so
+// the softmax of one overlaps the MMAs of the other:
+//   warp 0      TMA: Q0, Q1 once, then K_j (two-deep ring) and V_j (one slot)
+//   warp 1      one thread issues, per key tile:  O_0 += P_0 V_j,  S_0 = Q_0 K_{j+1}^T,  O_1 += P_1 V_j,  S_1 = Q_1 K_{j+1}^T
+//               (tcgen05.mma; S_t and O_t live in TMEM, P_t in shared memory, V_j is an MN-major operand)
+//   warps 2-5   softmax of query tile 0, warps 6-9 of query tile 1, one query row per thread: tcgen05.ld of the S row,
+//               running max / sum in the exp2 domain, masks on the diagonal and window edges, P written as bf16 into the
+//               swizzled K-major tile the second MMA reads, O rescaled in TMEM only when the running max moved by more than
+//               2^8 (lazy rescaling); finally O / l is written out with the row's log-sum-exp.
+// All mbarrier waits are bounded (error word).
 //
 // Layout contract: `qkv` rows hold [q heads | k heads | v heads] x 128 (any row stride that is a multiple of 8
 // elements); out rows hold heads x 128; lse is [heads, total_tokens] fp32 (natural log), the layout the backward expects.
@@ -20,13 +22,14 @@ namespace {
 using namespace flb_tc;
 
 constexpr int D = 128;           // head size
-constexpr int BM = 128;          // query rows per CTA
+constexpr int BM = 128;          // rows of one query tile (a CTA owns two)
 constexpr int BN = 128;          // key rows per tile
-constexpr int kThreadsAttn = 192;
+constexpr int kThreadsAttn = 320;
 constexpr int PANEL_BYTES = 128 * 128;  // 128 rows x 64 bf16
 constexpr int TILE_BYTES_ATTN = 2 * PANEL_BYTES;
-constexpr int SMEM_Q = 0, SMEM_K = TILE_BYTES_ATTN, SMEM_V = 3 * TILE_BYTES_ATTN, SMEM_P = 5 * TILE_BYTES_ATTN;
-constexpr int SMEM_BARS = 6 * TILE_BYTES_ATTN;
+// shared memory tiles: Q0 Q1 | K ring (2) | V | P0 P1
+constexpr int SMEM_Q = 0, SMEM_K = 2 * TILE_BYTES_ATTN, SMEM_V = 4 * TILE_BYTES_ATTN, SMEM_P = 5 * TILE_BYTES_ATTN;
+constexpr int SMEM_BARS = 7 * TILE_BYTES_ATTN;
 constexpr int SMEM_TOTAL = SMEM_BARS + 256 + 1024;
 constexpr float kRescaleThreshold = 8.f;  // log2 units
 
@@ -50,7 +53,7 @@ struct AttnParams {
   float* lse;            // [heads, total_q]
   long long total_q;
   int heads, kv_heads, q_col0, k_col0, v_col0;  // column (element) offsets of the q / k / v blocks inside a row
-  int blocks_per_doc;    // ceil(max_seqlen_q / BM)
+  int blocks_per_doc;    // ceil(max_seqlen_q / (2 * BM))
   int causal, window;    // window <= 0: unlimited; else a query sees the `window` most recent keys including itself
   float scale_log2;      // softmax scale * log2(e)
   int* err_word;
@@ -64,7 +67,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint8_t* smem = smem_raw + pad;
   const uint32_t sbase = raw_addr + pad;
   const uint32_t bar0 = sbase + SMEM_BARS;
-  // barriers: 0 q_full, 1-2 k_full, 3-4 k_empty, 5-6 v_full, 7-8 v_empty, 9-10 s_full, 11-12 s_empty, 13 p_full, 14 pv_done
+  // barriers: 0-1 q_full[t], 2-3 k_full[s], 4-5 k_empty[s], 6 v_full, 7 v_empty, 8-9 s_full[t], 10-11 s_empty[t],
+  //           12-13 p_full[t], 14-15 pv_done[t]
   auto bar = [&](int i) { return bar0 + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SMEM_BARS + 8 * 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -77,12 +81,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const int qblk = p.blocks_per_doc - 1 - (blockIdx.x % p.blocks_per_doc);
   const int q_begin = p.cu_q[doc], q_len = p.cu_q[doc + 1] - q_begin;
   const int k_begin = p.cu_k[doc], k_len = p.cu_k[doc + 1] - k_begin;
-  const int q0 = qblk * BM;
+  const int q0 = qblk * 2 * BM;
   if (q0 >= q_len) return;  // uniform for the CTA: nothing allocated yet
+  const int num_q = (q0 + BM < q_len) ? 2 : 1;  // query tiles of this CTA that hold rows
   const int shift = k_len - q_len;  // bottom-right aligned causal mask: query i sees keys <= i + shift
-  // key range this block needs
+  // key range either query tile needs (a tile outside one query tile's own range is fully masked for it)
   int kv_hi = k_len;
-  if (p.causal) kv_hi = min(k_len, q0 + BM + shift);
+  if (p.causal) kv_hi = min(k_len, q0 + num_q * BM + shift);
   int kv_lo = 0;
   if (p.window > 0) kv_lo = max(0, q0 + shift - p.window + 1);
   const int tile_lo = kv_lo / BN, tile_hi = (kv_hi + BN - 1) / BN;
@@ -91,12 +96,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_q) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_kv) : "memory");
-    mbar_init(bar(0), 1);
-    for (int i = 1; i <= 8; ++i) mbar_init(bar(i), 1);
-    mbar_init(bar(9), 1); mbar_init(bar(10), 1);
-    mbar_init(bar(11), 4); mbar_init(bar(12), 4);
-    mbar_init(bar(13), 4);
-    mbar_init(bar(14), 1);
+    for (int i = 0; i <= 9; ++i) mbar_init(bar(i), 1);
+    for (int i = 10; i <= 13; ++i) mbar_init(bar(i), 4);
+    mbar_init(bar(14), 1); mbar_init(bar(15), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -109,28 +111,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tmem_s[2] = {tmem, tmem + 128};
-  const uint32_t tmem_o = tmem + 256;
+  // TMEM columns: S_0 | S_1 | O_0 | O_1
 
   if (warp == 0) {
     if (lane == 0) {
       // ---- producer
-      mbar_expect_tx(bar(0), TILE_BYTES_ATTN);
-      for (int c = 0; c < 2; ++c)
-        tma_load_2d(sbase + SMEM_Q + c * PANEL_BYTES, &tmap_q, bar(0), p.q_col0 + head * D + c * 64, q_begin + q0);
+      for (int t = 0; t < num_q; ++t) {
+        mbar_expect_tx(bar(t), TILE_BYTES_ATTN);
+        for (int c = 0; c < 2; ++c)
+          tma_load_2d(sbase + SMEM_Q + t * TILE_BYTES_ATTN + c * PANEL_BYTES, &tmap_q, bar(t), p.q_col0 + head * D + c * 64, q_begin + q0 + t * BM);
+      }
       bool ok = true;
       for (int j = 0; j < num_tiles && ok; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         const int row = k_begin + (tile_lo + j) * BN;
-        if (!mbar_wait(bar(3 + s), ph ^ 1u, abort_flag, p.err_word, 21)) { ok = false; break; }
-        mbar_expect_tx(bar(1 + s), TILE_BYTES_ATTN);
+        if (!mbar_wait(bar(4 + s), ph ^ 1u, abort_flag, p.err_word, 21)) { ok = false; break; }
+        mbar_expect_tx(bar(2 + s), TILE_BYTES_ATTN);
         for (int c = 0; c < 2; ++c)
-          tma_load_2d(sbase + SMEM_K + s * TILE_BYTES_ATTN + c * PANEL_BYTES, &tmap_kv, bar(1 + s), p.k_col0 + kv_head * D + c * 64, row);
-        if (!mbar_wait(bar(7 + s), ph ^ 1u, abort_flag, p.err_word, 22)) { ok = false; break; }
-        mbar_expect_tx(bar(5 + s), TILE_BYTES_ATTN);
+          tma_load_2d(sbase + SMEM_K + s * TILE_BYTES_ATTN + c * PANEL_BYTES, &tmap_kv, bar(2 + s), p.k_col0 + kv_head * D + c * 64, row);
+        if (!mbar_wait(bar(7), (j & 1) ^ 1u, abort_flag, p.err_word, 22)) { ok = false; break; }
+        mbar_expect_tx(bar(6), TILE_BYTES_ATTN);
         for (int c = 0; c < 2; ++c)
-          tma_load_2d(sbase + SMEM_V + s * TILE_BYTES_ATTN + c * PANEL_BYTES, &tmap_kv, bar(5 + s), p.v_col0 + kv_head * D + c * 64, row);
+          tma_load_2d(sbase + SMEM_V + c * PANEL_BYTES, &tmap_kv, bar(6), p.v_col0 + kv_head * D + c * 64, row);
       }
     }
   } else if (warp == 1) {
@@ -138,55 +141,59 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // ---- MMA issuer
       constexpr uint32_t idesc_qk = make_idesc(BM, BN, false, false);
       constexpr uint32_t idesc_pv = make_idesc(BM, D, false, true);
-      bool ok = mbar_wait(bar(0), 0, abort_flag, p.err_word, 23);
-      auto issue_qk = [&](int j) -> bool {
+      bool ok = true;
+      // S_t = Q_t K_j^T; the last query tile to read K_j releases its slot
+      auto issue_qk = [&](int t, int j) -> bool {
         const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(bar(1 + s), ph, abort_flag, p.err_word, 24)) return false;        // K_j landed
-        if (!mbar_wait(bar(11 + s), ph ^ 1u, abort_flag, p.err_word, 25)) return false;  // S buffer drained
+        if (t == 0 && !mbar_wait(bar(2 + s), (j >> 1) & 1, abort_flag, p.err_word, 24)) return false;       // K_j landed
+        if (j > 0 && !mbar_wait(bar(10 + t), (j - 1) & 1, abort_flag, p.err_word, 25)) return false;         // S_t drained
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < D / UMMA_K; ++k) {
           const uint32_t off = (k >> 2) * PANEL_BYTES + (k & 3) * 32;
-          umma_bf16(tmem_s[s], make_smem_desc(sbase + SMEM_Q + off, 16, 1024),
+          umma_bf16(tmem + t * 128, make_smem_desc(sbase + SMEM_Q + t * TILE_BYTES_ATTN + off, 16, 1024),
                     make_smem_desc(sbase + SMEM_K + s * TILE_BYTES_ATTN + off, 16, 1024), idesc_qk, k != 0);
         }
-        umma_commit(bar(9 + s));  // S_j ready
-        umma_commit(bar(3 + s));  // K slot free
+        umma_commit(bar(8 + t));                       // S_t(j) ready
+        if (t == num_q - 1) umma_commit(bar(4 + s));   // K slot free
         return true;
       };
-      if (ok && num_tiles > 0) ok = issue_qk(0);
+      for (int t = 0; t < num_q && ok; ++t) {
+        ok = mbar_wait(bar(t), 0, abort_flag, p.err_word, 23);
+        if (ok && num_tiles > 0) ok = issue_qk(t, 0);
+      }
       for (int j = 0; j < num_tiles && ok; ++j) {
-        if (j + 1 < num_tiles) ok = issue_qk(j + 1);
-        if (!ok) break;
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(bar(13), j & 1, abort_flag, p.err_word, 26)) { ok = false; break; }   // P_j written
-        if (!mbar_wait(bar(5 + s), ph, abort_flag, p.err_word, 27)) { ok = false; break; }   // V_j landed
-        tc_fence_after();
+        for (int t = 0; t < num_q && ok; ++t) {
+          // S_t of the next key tile first: it only needs S_t(j) drained, and runs while this tile's P_t is being written
+          if (j + 1 < num_tiles && !issue_qk(t, j + 1)) { ok = false; break; }
+          if (!mbar_wait(bar(12 + t), j & 1, abort_flag, p.err_word, 26)) { ok = false; break; }           // P_t(j) written
+          if (t == 0 && !mbar_wait(bar(6), j & 1, abort_flag, p.err_word, 27)) { ok = false; break; }       // V_j landed
+          tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < BN / UMMA_K; ++k) {
-          const uint32_t a_off = (k >> 2) * PANEL_BYTES + (k & 3) * 32;  // P: K-major panels over keys
-          const uint32_t b_off = k * 2048;                                // V: 16 key rows per step
-          umma_bf16(tmem_o, make_smem_desc(sbase + SMEM_P + a_off, 16, 1024),
-                    make_smem_desc(sbase + SMEM_V + s * TILE_BYTES_ATTN + b_off, PANEL_BYTES, 1024), idesc_pv, (j | k) != 0);
+          for (int k = 0; k < BN / UMMA_K; ++k) {
+            const uint32_t a_off = (k >> 2) * PANEL_BYTES + (k & 3) * 32;  // P: K-major panels over keys
+            const uint32_t b_off = k * 2048;                                // V: 16 key rows per step
+            umma_bf16(tmem + 256 + t * 128, make_smem_desc(sbase + SMEM_P + t * TILE_BYTES_ATTN + a_off, 16, 1024),
+                      make_smem_desc(sbase + SMEM_V + b_off, PANEL_BYTES, 1024), idesc_pv, (j | k) != 0);
+          }
+          umma_commit(bar(14 + t));                     // O_t updated, P_t free
+          if (t == num_q - 1) umma_commit(bar(7));      // V slot free
         }
-        umma_commit(bar(14));     // O updated, P free
-        umma_commit(bar(7 + s));  // V slot free
       }
     }
   } else {
-    // ---- softmax / correction / epilogue: one query row per thread
+    // ---- softmax / correction / epilogue: one query row per thread, warps 2-5 own query tile 0, warps 6-9 tile 1
+    const int t = (warp - 2) >> 2;
     const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;          // row inside the block
-    const int qi = q0 + r;                      // row inside the document
+    const int r = quarter * 32 + lane;          // row inside the query tile
+    const int qi = q0 + t * BM + r;             // row inside the document
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tmem_s = tmem + t * 128, tmem_o = tmem + 256 + t * 128;
+    const bool active = t < num_q;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < num_tiles && ok; ++j) {
-      const int s = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      if (!mbar_wait(bar(9 + s), ph, abort_flag, p.err_word, 28)) { ok = false; break; }
+    for (int j = 0; j < num_tiles && ok && active; ++j) {
+      if (!mbar_wait(bar(8 + t), j & 1, abort_flag, p.err_word, 28)) { ok = false; break; }
       tc_fence_after();
       const int kbase = (tile_lo + j) * BN;
       // which columns of this tile may this row see?  [col_lo, col_hi)
@@ -200,7 +207,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
-        tmem_ld32(tmem_s[s] + lane_addr + c * 32, v);
+        tmem_ld32(tmem_s + lane_addr + c * 32, v);
         tmem_wait_ld();
         if (full_tile) {
 #pragma unroll
@@ -227,7 +234,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
-        tmem_ld32(tmem_s[s] + lane_addr + c * 32, v);
+        tmem_ld32(tmem_s + lane_addr + c * 32, v);
         tmem_wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -243,13 +250,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           packed[c * 16 + (i >> 1)] = *reinterpret_cast<uint32_t*>(&b);
         }
       }
-      // the S buffer may be overwritten by the MMA of tile j + 2
+      // S_t may be overwritten by the MMA of the next key tile
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(11 + s));
-      // P buffer and O are free once the previous PV MMA has completed
+      if (lane == 0) mbar_arrive(bar(10 + t));
+      // P_t and O_t are free once the previous PV MMA of this query tile has completed
       if (j > 0) {
-        if (!mbar_wait(bar(14), (j - 1) & 1, abort_flag, p.err_word, 29)) { ok = false; break; }
+        if (!mbar_wait(bar(14 + t), (j - 1) & 1, abort_flag, p.err_word, 29)) { ok = false; break; }
         tc_fence_after();
       }
       l = l * alpha + row_sum;
@@ -267,8 +274,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
         tmem_wait_st();
       }
-      // write P_j: two K-major panels of 64 keys, 128-byte swizzle (16-byte chunk index XOR row % 8)
-      uint8_t* prow = smem + SMEM_P + r * 128;
+      // write P: two K-major panels of 64 keys, 128-byte swizzle (16-byte chunk index XOR row % 8)
+      uint8_t* prow = smem + SMEM_P + t * TILE_BYTES_ATTN + r * 128;
 #pragma unroll
       for (int ch = 0; ch < 16; ++ch) {
         const int panel = ch >> 3, chunk = ch & 7;
@@ -278,35 +285,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(13));
+      if (lane == 0) mbar_arrive(bar(12 + t));
     }
     // ---- epilogue
-    if (ok && num_tiles > 0) ok = mbar_wait(bar(14), (num_tiles - 1) & 1, abort_flag, p.err_word, 30);
-    tc_fence_after();
-    const bool valid_row = qi < q_len;
-    const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
-    __nv_bfloat16* orow = p.out + ((long long)(q_begin + qi) * p.heads + head) * D;
+    if (active) {
+      if (ok && num_tiles > 0) ok = mbar_wait(bar(14 + t), (num_tiles - 1) & 1, abort_flag, p.err_word, 30);
+      tc_fence_after();
+      const bool valid_row = qi < q_len;
+      const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = p.out + ((long long)(q_begin + qi) * p.heads + head) * D;
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
-      uint32_t v[32];
-      if (num_tiles > 0 && ok) {
-        tmem_ld32(tmem_o + lane_addr + c * 32, v);
-        tmem_wait_ld();
-      } else {
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        if (num_tiles > 0 && ok) {
+          tmem_ld32(tmem_o + lane_addr + c * 32, v);
+          tmem_wait_ld();
+        } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = 0u;
-      }
-      if (valid_row) {
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+        if (valid_row) {
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          float f[8];
+          for (int g = 0; g < 4; ++g) {
+            float f[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[g * 8 + i]) * inv_l;
-          *reinterpret_cast<flb::bf16x8*>(orow + c * 32 + g * 8) = flb::pack8(f);
+            for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[g * 8 + i]) * inv_l;
+            *reinterpret_cast<flb::bf16x8*>(orow + c * 32 + g * 8) = flb::pack8(f);
+          }
         }
       }
+      if (valid_row) p.lse[(long long)head * p.total_q + q_begin + qi] = (l > 0.f) ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
     }
-    if (valid_row) p.lse[(long long)head * p.total_q + q_begin + qi] = (l > 0.f) ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
   }
 
   tc_fence_before();
@@ -379,7 +388,7 @@ FLB_API int flb_attention_fwd(const void* q, long long q_stride, int q_col0, con
   AttnParams p;
   p.cu_q = cu_q; p.cu_k = cu_k; p.out = (__nv_bfloat16*)out; p.lse = lse; p.total_q = total_q;
   p.heads = heads; p.kv_heads = kv_heads; p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;
-  p.blocks_per_doc = (max_seqlen_q + BM - 1) / BM;
+  p.blocks_per_doc = (max_seqlen_q + 2 * BM - 1) / (2 * BM);
   p.causal = causal; p.window = window; p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.err_word = attn_err_word();
   if (!p.err_word) return FLB_ERR_CUDA;
