@@ -65,6 +65,38 @@ class MixtralCheckpointFormat(GPTHuggingfaceCheckpointFormat):
         return MixtralHuggingfaceCheckpointHandler
 
 
+class MTPLlamaCheckpointFormat(GPTHuggingfaceCheckpointFormat):
+    name: typing.ClassVar[str] = "mtp_llama"
+
+    @classmethod
+    def get_handler_class(cls):
+        return MTPLlamaHuggingfaceCheckpointHandler
+
+
+class DiffusionDreamCheckpointFormat(GPTHuggingfaceCheckpointFormat):
+    name: typing.ClassVar[str] = "dream"
+
+    @classmethod
+    def get_handler_class(cls):
+        return DiffusionDreamHuggingfaceCheckpointHandler
+
+
+class DiffusionLlamaCheckpointFormat(GPTHuggingfaceCheckpointFormat):
+    name: typing.ClassVar[str] = "diffusion_llama"
+
+    @classmethod
+    def get_handler_class(cls):
+        return DiffusionLlamaHuggingfaceCheckpointHandler
+
+
+class AprielHybridSSMCheckpointFormat(GPTHuggingfaceCheckpointFormat):
+    name: typing.ClassVar[str] = "apriel_hybrid_ssm"
+
+    @classmethod
+    def get_handler_class(cls):
+        return AprielHybridSSMHuggingfaceCheckpointHandler
+
+
 class AutoGPTHuggingfaceCheckpointFormat(GPTHuggingfaceCheckpointFormat):
     name: typing.ClassVar[str] = "auto"
 
@@ -323,12 +355,192 @@ class MixtralHuggingfaceCheckpointHandler(MistralHuggingfaceCheckpointHandler):
         ]
 
 
+class MTPLlamaHuggingfaceCheckpointHandler(LlamaHuggingfaceCheckpointHandler):
+    """Llama with multi-token-prediction heads: head d > 1 = one more transformer layer `model.mtp_heads.{d-2}` plus its own
+    final norm `model.mtp_norms.{d-1}`; the first head's norm is `model.mtp_norms.0` (`mtp_llama.py:32-107`)."""
+
+    format = MTPLlamaCheckpointFormat
+    architecture = "MTPLlamaForCausalLM"
+    model_type = "mtp_llama"
+
+    @classmethod
+    def _export_extra(cls, c, out):
+        out["prediction_heads"] = c.head.prediction_heads
+        out["auto_map"] = {"AutoConfig": "configuration_mtp_llama.MTPLlamaConfig", "AutoModel": "modeling_mtp_llama.MTPLlamaModel",
+                           "AutoModelForCausalLM": "modeling_mtp_llama.MTPLlamaForCausalLM"}
+
+    @classmethod
+    def import_config(cls, h):
+        out = super().import_config(h)
+        out["head"]["prediction_heads"] = h.get("prediction_heads", 1)
+        return out
+
+    @classmethod
+    def get_weight_converters(cls, c):
+        block = cls._block(c)
+        out = [conv for conv in super().get_weight_converters(c) if conv.fast_llm_name != ("head.final_norm.weight",)]
+        out.append(WeightConverter("head.final_norm.weight", "model.mtp_norms.0.weight"))
+        for index in range(c.head.prediction_heads - 1):
+            ours, theirs = f"multi_token_prediction.blocks.{index}", f"model.mtp_heads.{index}"
+            out.append(WeightConverter(f"{ours}.norm_1.weight", f"{theirs}.input_layernorm.weight"))
+            out.append(WeightConverter(f"{ours}.norm_2.weight", f"{theirs}.post_attention_layernorm.weight"))
+            out += cls._attention_converters(block.mixer, f"{ours}.mixer", f"{theirs}.self_attn")
+            out += cls._mlp_converters(block.mlp, f"{ours}.mlp", f"{theirs}.mlp")
+            out.append(WeightConverter(f"multi_token_prediction.heads.{index}.final_norm.weight", f"model.mtp_norms.{index + 1}.weight"))
+        return out
+
+
+class DiffusionDreamHuggingfaceCheckpointHandler(Qwen2HuggingfaceCheckpointHandler):
+    """Dream (masked-diffusion language model on the Qwen2 architecture): same tensors, its own modeling files."""
+
+    format = DiffusionDreamCheckpointFormat
+    architecture = "DreamModel"
+    model_type = "Dream"
+
+    @classmethod
+    def _export_extra(cls, c, out):
+        super()._export_extra(c, out)
+        out["auto_map"] = {"AutoConfig": "configuration_dream.DreamConfig", "AutoModel": "modeling_dream.DreamModel"}
+
+
+class DiffusionLlamaHuggingfaceCheckpointHandler(LlamaHuggingfaceCheckpointHandler):
+    format = DiffusionLlamaCheckpointFormat
+    architecture = "DiffusionLlamaModel"
+    model_type = "diffusion_llama"
+
+    @classmethod
+    def _export_extra(cls, c, out):
+        out["auto_map"] = {"AutoConfig": "configuration_diffusion_llama.DiffusionLlamaConfig", "AutoModel": "modeling_diffusion_llama.DiffusionLlamaModel"}
+
+
+class AprielHybridSSMHuggingfaceCheckpointHandler(MistralHuggingfaceCheckpointHandler):
+    """Apriel hybrid: a per-layer `hybrid_block_layout` of "t" (attention), "m2" (Mamba) and "gdn" (gated DeltaNet) blocks
+    sharing one MLP / normalization config; Mamba sizes sit in `ssm_cfg` (`apriel.py:36-469`)."""
+
+    format = AprielHybridSSMCheckpointFormat
+    architecture = "AprielHybridSSMForCausalLM"
+    model_type = "apriel_ssm_thinker_hybrid"
+    layout_names = {"AttentionConfig": "t", "MambaConfig": "m2", "GatedDeltaNetConfig": "gdn"}
+
+    @classmethod
+    def _blocks(cls, c) -> list:
+        return c.decoder.block_configs()
+
+    @classmethod
+    def _block(cls, base_model_config):
+        blocks = cls._blocks(base_model_config)
+        attention = [b for b in blocks if type(b.mixer).__name__ == "AttentionConfig"]
+        return (attention or blocks)[0]
+
+    @classmethod
+    def export_config(cls, c) -> dict:
+        blocks = cls._blocks(c)
+        layout = [cls.layout_names[type(b.mixer).__name__] for b in blocks]
+        if "t" in layout:
+            out = super().export_config(c)
+        else:  # no attention block to describe: borrow the shared parts from the first block
+            first = blocks[0]
+            out = {"model_type": cls.model_type, "architectures": [cls.architecture], "vocab_size": c.embeddings.vocab_size,
+                   "hidden_size": c.hidden_size, "num_hidden_layers": len(blocks), "intermediate_size": first.mlp.intermediate_size,
+                   "hidden_act": first.mlp.activation.hf_name, "rms_norm_eps": first.normalization.epsilon,
+                   "tie_word_embeddings": c.tied_embedding_weight, "torch_dtype": "bfloat16"}
+        out["num_hidden_layers"] = len(blocks)
+        out["hybrid_block_layout"] = layout
+        mamba = next((b.mixer for b in blocks if type(b.mixer).__name__ == "MambaConfig"), None)
+        if mamba is not None:
+            out["ssm_cfg"] = {"d_state": mamba.state_size, "d_inner": mamba.d_inner, "d_xb": mamba.d_xb, "dt_rank": mamba.dt_rank,
+                              "bias": mamba.add_linear_biases, "repeat_kv_before_conv": mamba.repeat_kv_before_conv,
+                              "conv_bias": cls._enabled(mamba.convolution_layer.bias, mamba.add_linear_biases),
+                              "dt_proj_bias": cls._enabled(mamba.dt_layer.bias, mamba.add_linear_biases), "d_conv": mamba.convolution_layer.kernel_size}
+        gdn = next((b.mixer for b in blocks if type(b.mixer).__name__ == "GatedDeltaNetConfig"), None)
+        if gdn is not None:
+            out["linear_attn_config"] = {"gdn_value_head_dim": gdn.value_head_dim, "gdn_key_head_dim": gdn.key_head_dim,
+                                         "gdn_num_value_heads": gdn.value_heads, "gdn_num_key_heads": gdn.key_heads,
+                                         "gdn_linear_conv_kernel_size": gdn.convolution_layer.kernel_size}
+        out["auto_map"] = {"AutoConfig": "configuration_apriel_hybrid_ssm.AprielHybridSSMConfig",
+                           "AutoModel": "modeling_apriel_hybrid_ssm.AprielHybridSSMModel",
+                           "AutoModelForCausalLM": "modeling_apriel_hybrid_ssm.AprielHybridSSMForCausalLM"}
+        return out
+
+    @staticmethod
+    def _enabled(bias_config, default: bool) -> bool:
+        return default if bias_config.enabled is None else bias_config.enabled
+
+    @classmethod
+    def import_config(cls, h: dict) -> dict:
+        out = super().import_config(h)
+        shared = out["decoder"]["block"]
+        layout = h.get("hybrid_block_layout") or ["t"] * h["num_hidden_layers"]
+        ssm = h.get("ssm_cfg", {})
+        hidden = h["hidden_size"]
+        d_inner = ssm.get("d_inner") or hidden * ssm.get("expand", 1)
+        dt_rank = ssm.get("dt_rank", "auto")
+        mixers = {
+            "t": shared["mixer"],
+            "m2": {"type": "mamba", "state_size": ssm.get("d_state", 16), "d_inner": d_inner, "d_xb": ssm.get("d_xb") or hidden,
+                   "dt_rank": -(-hidden // 16) if dt_rank == "auto" else dt_rank, "add_linear_biases": ssm.get("bias", False),
+                   "repeat_kv_before_conv": ssm.get("repeat_kv_before_conv", True),
+                   "convolution_layer": {"kernel_size": ssm.get("d_conv", 4), "bias": {"enabled": ssm.get("conv_bias", True)}},
+                   "dt_layer": {"bias": {"enabled": ssm.get("dt_proj_bias", True)}}},
+        }
+        linear = h.get("linear_attn_config", {})
+        if linear:
+            mixers["gdn"] = {"type": "gdn", "value_head_dim": linear["gdn_value_head_dim"], "key_head_dim": linear["gdn_key_head_dim"],
+                             "value_heads": linear["gdn_num_value_heads"], "key_heads": linear["gdn_num_key_heads"],
+                             "convolution_layer": {"kernel_size": linear.get("gdn_linear_conv_kernel_size", 4)}}
+        names = list(dict.fromkeys(layout))
+        out["decoder"] = {"type": "pattern", "num_blocks": len(layout), "pattern": layout,
+                          "blocks": {name: {**shared, "mixer": mixers[name]} for name in names}}
+        return out
+
+    @classmethod
+    def _mixer_converters(cls, mixer, ours: str, theirs: str) -> list[WeightConverter]:
+        kind = type(mixer).__name__
+        if kind == "AttentionConfig":
+            return cls._attention_converters(mixer, ours, f"{theirs}.self_attn")
+        theirs = f"{theirs}.mixer"
+        if kind == "MambaConfig":
+            bias = mixer.add_linear_biases
+            out = []
+            for name in ("in_proj", "dt_in_proj", "out_proj"):
+                out += cls._linear(f"{ours}.{name}", f"{theirs}.{name}", bias)
+            out += cls._linear(f"{ours}.dt_proj", f"{theirs}.dt_proj", cls._enabled(mixer.dt_layer.bias, bias))
+            out += cls._linear(f"{ours}.convolution", f"{theirs}.conv1d", cls._enabled(mixer.convolution_layer.bias, bias))
+            out += [WeightConverter(f"{ours}.A_log", f"{theirs}.A_log"), WeightConverter(f"{ours}.D", f"{theirs}.D")]
+            return out
+        if kind == "GatedDeltaNetConfig":
+            out = []
+            for name in ("in_proj_qkvz", "in_proj_ba", "out_proj"):
+                out += cls._linear(f"{ours}.{name}", f"{theirs}.{name}", False)
+            out += cls._linear(f"{ours}.convolution", f"{theirs}.conv1d", False)
+            out += [WeightConverter(f"{ours}.A_log", f"{theirs}.A_log"), WeightConverter(f"{ours}.dt_bias", f"{theirs}.dt_bias"),
+                    WeightConverter(f"{ours}.norm.weight", f"{theirs}.norm.weight")]
+            return out
+        raise NotImplementedError(f"No Apriel mapping for {kind}")
+
+    @classmethod
+    def get_weight_converters(cls, c) -> list[WeightConverter]:
+        out = [WeightConverter("embeddings.word_embeddings_weight", "model.embed_tokens.weight")]
+        for i, block in enumerate(cls._blocks(c)):
+            ours, theirs = f"decoder.{i}", f"model.layers.{i}"
+            out.append(WeightConverter(f"{ours}.norm_1.weight", f"{theirs}.input_layernorm.weight"))
+            out.append(WeightConverter(f"{ours}.norm_2.weight", f"{theirs}.post_attention_layernorm.weight"))
+            out += cls._mixer_converters(block.mixer, f"{ours}.mixer", theirs)
+            out += cls._mlp_converters(block.mlp, f"{ours}.mlp", f"{theirs}.mlp")
+        out.append(WeightConverter("head.final_norm.weight", "model.norm.weight"))
+        out.append(IgnoreImportWeightConverter("lm_head.weight") if c.tied_embedding_weight else WeightConverter("head.output_weights", "lm_head.weight"))
+        return out
+
+
 class AutoGPTHuggingfaceCheckpointHandler(HuggingfaceStateDictCheckpointHandler):
     """Dispatches on `model_type` of config.json when loading; cannot be used for saving."""
 
     format = AutoGPTHuggingfaceCheckpointFormat
     handler_map = {"llama": LlamaHuggingfaceCheckpointHandler, "mistral": MistralHuggingfaceCheckpointHandler,
-                   "qwen2": Qwen2HuggingfaceCheckpointHandler, "mixtral": MixtralHuggingfaceCheckpointHandler}
+                   "qwen2": Qwen2HuggingfaceCheckpointHandler, "mixtral": MixtralHuggingfaceCheckpointHandler,
+                   "mtp_llama": MTPLlamaHuggingfaceCheckpointHandler, "Dream": DiffusionDreamHuggingfaceCheckpointHandler,
+                   "diffusion_llama": DiffusionLlamaHuggingfaceCheckpointHandler,
+                   "apriel_ssm_thinker_hybrid": AprielHybridSSMHuggingfaceCheckpointHandler}
 
     def __new__(cls, model):
         raise TypeError("resolve the concrete handler with get_handler_class(path) first")
@@ -352,4 +564,5 @@ class AutoGPTHuggingfaceCheckpointHandler(HuggingfaceStateDictCheckpointHandler)
 
 
 GPT_CHECKPOINT_FORMATS = (AutoGPTHuggingfaceCheckpointFormat, LlamaCheckpointFormat, Qwen2CheckpointFormat, MistralCheckpointFormat,
-                          MixtralCheckpointFormat)
+                          MixtralCheckpointFormat, MTPLlamaCheckpointFormat, DiffusionDreamCheckpointFormat, DiffusionLlamaCheckpointFormat,
+                          AprielHybridSSMCheckpointFormat)

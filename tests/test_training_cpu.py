@@ -228,3 +228,72 @@ def test_multi_token_prediction():
     assert "multi_token_prediction.blocks.1.mlp.layer_1.weight" in names
     assert "multi_token_prediction.heads.0.final_norm.weight" in names
     assert both != pytest.approx(plain, rel=1e-5)  # the extra heads change the trunk's gradients
+
+
+def _round_trip(tmp_path, base_model, format_name):
+    """Export to an external format, import into a fresh model, compare logits."""
+    from fast_llm_b200.engine.checkpoint.config import CheckpointLoadConfig, CheckpointSaveConfig
+    from fast_llm_b200.engine.inference.runner import InferenceRunner
+    from fast_llm_b200.models.gpt.model import GPTModel
+
+    trainer, _ = build_trainer(tiny_trainer_config({("model", "base_model"): base_model}))
+    path = tmp_path / format_name
+    trainer.multi_stage.save_checkpoint(CheckpointSaveConfig(path=path, format=format_name))
+    loaded = GPTModel.from_pretrained(CheckpointLoadConfig(path=path, format=format_name), use_cpu=True)
+    tokens = torch.randint(0, 512, (40,))
+    runners = []
+    for model in (trainer.multi_stage, loaded):
+        runner = InferenceRunner(model)
+        runner.setup()
+        runners.append(runner)
+    torch.testing.assert_close(runners[0].forward_tokens(tokens), runners[1].forward_tokens(tokens), rtol=1e-4, atol=1e-4)
+    return json.loads((path / "config.json").read_text())
+
+
+def test_mtp_llama_and_apriel_hybrid_round_trip(tmp_path):
+    import copy
+
+    from tests.common import TINY_BASE_MODEL
+
+    mtp = copy.deepcopy(TINY_BASE_MODEL)
+    mtp["head"]["prediction_heads"] = 2
+    config = _round_trip(tmp_path, mtp, "mtp_llama")
+    assert config["prediction_heads"] == 2 and config["model_type"] == "mtp_llama"
+
+    hybrid = copy.deepcopy(TINY_BASE_MODEL)
+    attention_block = hybrid["decoder"]["block"]
+    mamba_block = copy.deepcopy(attention_block)
+    mamba_block["mixer"] = {"type": "mamba", "d_inner": 64, "d_xb": 32, "state_size": 8, "dt_rank": 4, "add_linear_biases": False,
+                            "convolution_layer": {"bias": {"enabled": True}}, "dt_layer": {"bias": {"enabled": True}}}
+    hybrid["decoder"] = {"type": "pattern", "blocks": {"t": attention_block, "m2": mamba_block}, "pattern": ["t", "m2", "m2"], "num_blocks": 3}
+    config = _round_trip(tmp_path, hybrid, "apriel_hybrid_ssm")
+    assert config["hybrid_block_layout"] == ["t", "m2", "m2"] and config["ssm_cfg"]["d_state"] == 8
+
+
+def test_checkpoint_surgery_tools(tmp_path):
+    """MoE upcycling and MTP-head surgery produce checkpoints this framework loads."""
+    from fast_llm_b200.engine.checkpoint.config import CheckpointLoadConfig, CheckpointSaveConfig
+    from fast_llm_b200.models.gpt.model import GPTModel
+    from fast_llm_b200.tools.checkpoint_surgery import AddExpertsConfig, AddPredictionHeadsConfig, load_hf_state
+
+    moe, _ = build_trainer(tiny_trainer_config(MOE_UPDATES))
+    moe.multi_stage.save_checkpoint(CheckpointSaveConfig(path=tmp_path / "moe", format="mixtral"))
+    surgery = AddExpertsConfig.from_dict({"hf_checkpoint": str(tmp_path / "moe"), "output_dir": str(tmp_path / "moe6"), "num_new_experts": 2,
+                                          "expert_init_std": 0.01, "router_init_std": 0.01})
+    surgery.validate()
+    surgery.run()
+    config, state = load_hf_state(tmp_path / "moe6")
+    assert config["num_local_experts"] == 6 and state["model.layers.0.block_sparse_moe.gate.weight"].shape[0] == 6
+    assert "model.layers.1.block_sparse_moe.experts.5.w2.weight" in state
+    bigger = GPTModel.from_pretrained(CheckpointLoadConfig(path=tmp_path / "moe6", format="mixtral"), use_cpu=True)
+    assert bigger.config.base_model.decoder.block.mlp.experts == 6
+
+    dense, _ = build_trainer(tiny_trainer_config())
+    dense.multi_stage.save_checkpoint(CheckpointSaveConfig(path=tmp_path / "llama", format="llama"))
+    heads = AddPredictionHeadsConfig.from_dict({"hf_checkpoint": str(tmp_path / "llama"), "output_dir": str(tmp_path / "mtp"), "num_prediction_heads": 3})
+    heads.validate()
+    heads.run()
+    loaded = GPTModel.from_pretrained(CheckpointLoadConfig(path=tmp_path / "mtp", format="mtp_llama"), use_cpu=True)
+    assert loaded.config.base_model.head.prediction_heads == 3
+    _, state = load_hf_state(tmp_path / "mtp")
+    torch.testing.assert_close(state["model.mtp_heads.1.mlp.down_proj.weight"], state["model.layers.1.mlp.down_proj.weight"])
