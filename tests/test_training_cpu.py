@@ -297,3 +297,47 @@ def test_checkpoint_surgery_tools(tmp_path):
     assert loaded.config.base_model.head.prediction_heads == 3
     _, state = load_hf_state(tmp_path / "mtp")
     torch.testing.assert_close(state["model.mtp_heads.1.mlp.down_proj.weight"], state["model.layers.1.mlp.down_proj.weight"])
+
+
+def test_push_model_selects_stages_and_uploads(tmp_path):
+    """Only checkpoints without a commit are uploaded, oldest first, each staged with the tokenizer."""
+    from fast_llm_b200.engine.checkpoint.config import CheckpointSaveConfig
+    from fast_llm_b200.tools.push_model import PushConfig
+
+    trainer, _ = build_trainer(tiny_trainer_config())
+    for iteration in (10, 20, 30):
+        trainer.multi_stage.save_checkpoint(CheckpointSaveConfig(path=tmp_path / "run" / "export" / "llama" / str(iteration), format="llama"))
+        (tmp_path / "run" / "export" / "llama" / str(iteration) / "ok").touch()  # the trainer marks finished exports
+    (tmp_path / "run" / "export" / "llama" / "40").mkdir()  # incomplete: no `ok` marker
+    tokenizer = tmp_path / "tok" / "tokenizer.json"
+    tokenizer.parent.mkdir()
+    tokenizer.write_text("{}")
+    (tokenizer.parent / "tokenizer_config.json").write_text("{}")
+
+    class Commit:
+        def __init__(self, title):
+            self.title = title
+
+    class FakeApi:
+        def __init__(self):
+            self.uploads = []
+
+        def create_repo(self, name, private, exist_ok):
+            self.repo = name
+
+        def list_repo_commits(self, name):
+            return [Commit("initial commit"), Commit("10")]
+
+        def upload_folder(self, folder_path, repo_id, commit_message):
+            import pathlib
+
+            self.uploads.append((commit_message, sorted(p.name for p in pathlib.Path(folder_path).iterdir())))
+
+    config = PushConfig.from_dict({"experiment_dir": str(tmp_path / "run"), "repo_name": "org/model", "model_type": "llama", "tokenizer_path": str(tokenizer)})
+    config.validate()
+    api = FakeApi()
+    assert config.run(api) == [20, 30]
+    assert [message for message, _ in api.uploads] == ["20", "30"]
+    assert {"config.json", "tokenizer.json", "tokenizer_config.json"} <= set(api.uploads[0][1])
+    assert any(name.endswith(".safetensors") for name in api.uploads[0][1])
+    assert not (tmp_path / "run" / "export_tmp").exists()
