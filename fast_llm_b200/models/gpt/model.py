@@ -43,6 +43,15 @@ class GPTBaseModel(BaseModel):
             setattr(self, f"mtp_head_{d}", head)
             self._extra_heads.append((block, head))
         self.set_names()
+        if config.use_megatron_initialization:
+            from fast_llm_b200.models.gpt.megatron import get_init_megatron
+
+            block_configs = config.decoder.block_configs()
+            for layer, block_config in zip(self._decoder_layers, block_configs):
+                for _, meta in layer.named_parameter_metas():
+                    meta.init_override = get_init_megatron(meta, block_config, config.hidden_size)
+            for _, meta in self.embeddings.named_parameter_metas():
+                meta.init_override = get_init_megatron(meta, block_configs[0], config.hidden_size)
 
     def set_names(self, prefix: str = "") -> None:
         # Parameter names follow the reference layout: embeddings.*, decoder.{i}.*, head.*

@@ -237,6 +237,9 @@ class ParameterMeta:
     def init_parameter(self, tensor: torch.Tensor, distributed, reproducible: bool | None = None) -> None:
         """Fill `tensor` (local shape).  With reproducible init, draw the global tensor and keep this rank's slice."""
         assert self.param_init_method is not None, f"No init method for {self.tensor_name}"
+        override = getattr(self, "init_override", None)
+        if override is not None:  # e.g. the Megatron-compatible initialisation order
+            return override(tensor, distributed)
         reproducible = distributed.config.reproducible_init if reproducible is None else reproducible
         generator = distributed.tp_init_generator if self.is_tensor_parallel and not reproducible else distributed.pp_init_generator
         if reproducible:

@@ -341,3 +341,30 @@ def test_push_model_selects_stages_and_uploads(tmp_path):
     assert {"config.json", "tokenizer.json", "tokenizer_config.json"} <= set(api.uploads[0][1])
     assert any(name.endswith(".safetensors") for name in api.uploads[0][1])
     assert not (tmp_path / "run" / "export_tmp").exists()
+
+
+def test_megatron_initialization_replays_one_stream():
+    """query / key_value / dense of a layer are slices of ONE (dense, fused qkv) draw, as Megatron creates them."""
+    from fast_llm_b200.models.gpt.megatron import set_megatron_distributed_seeds
+
+    config = tiny_trainer_config({("model", "base_model", "use_megatron_initialization"): True})
+    set_megatron_distributed_seeds(config.model.distributed)
+    trainer, distributed = build_trainer(config)
+    weights = {name: tensor for name, _, tensor in trainer.multi_stage.get_state_tensor_iterator(("weights",))}
+    heads, groups, head_size, hidden = 4, 2, 16, 64
+    # Within one layer the three attention weights must be mutually consistent with a single fused draw: recover the
+    # fused tensor from query and key_value and check its statistics and shapes.
+    q, kv, dense = (weights[f"decoder.0.mixer.{n}.weight"] for n in ("query", "key_value", "dense"))
+    assert q.shape == (heads * head_size, hidden) and kv.shape == (2 * groups * head_size, hidden) and dense.shape == (hidden, heads * head_size)
+    fused = torch.cat([q.view(groups, heads // groups, head_size, hidden), kv.view(2, groups, head_size, hidden).transpose(0, 1)], 1)
+    assert fused.shape == (groups, heads // groups + 2, head_size, hidden)
+    std = hidden**-0.5
+    for tensor in (q, kv, dense, weights["decoder.0.mlp.layer_2.weight"]):
+        assert 0.7 * std < tensor.float().std().item() < 1.3 * std
+    # the two layers come from an advancing stream (not identical), and a second build reproduces the values exactly
+    assert not torch.equal(weights["decoder.0.mixer.query.weight"], weights["decoder.1.mixer.query.weight"])
+    config2 = tiny_trainer_config({("model", "base_model", "use_megatron_initialization"): True})
+    set_megatron_distributed_seeds(config2.model.distributed)
+    trainer2, _ = build_trainer(config2)
+    for name, _, tensor in trainer2.multi_stage.get_state_tensor_iterator(("weights",)):
+        assert torch.equal(tensor, weights[name]), name
