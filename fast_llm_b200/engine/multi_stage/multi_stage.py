@@ -57,16 +57,24 @@ class MultiStageModel:
                 for _, meta in layer.named_parameter_metas():
                     meta_stage[id(meta)] = s
         self._tied_duplicates: dict[str, tuple] = {}
+        # Copies on ANOTHER pipeline rank keep storage of their own: they receive the owner's values after
+        # initialisation / loading, and both sides add each other's gradient before their data-parallel reduction, so the
+        # copies stay identical (`fast_llm/engine/multi_stage/multi_stage.py` tied groups, `runner.py:243`).
+        self._tied_remote: list[tuple] = []
         duplicate_names = set()
         for name, metas in self._tied_parameters.items():
             owner = metas[0]
+            owner_rank = meta_stage[id(owner)] % pp
+            holders = {owner_rank: owner}
             for dup in metas[1:]:
-                owner_rank = meta_stage[id(owner)] % pp
                 dup_rank = meta_stage[id(dup)] % pp
-                if owner_rank != dup_rank:
-                    raise NotImplementedError("Tied parameters on different pipeline ranks are not supported yet")
-                duplicate_names.add(dup.tensor_name)
-                self._tied_duplicates[dup.tensor_name] = (owner, dup, meta_stage[id(owner)], meta_stage[id(dup)])
+                if dup_rank in holders:
+                    local_owner = holders[dup_rank]
+                    duplicate_names.add(dup.tensor_name)
+                    self._tied_duplicates[dup.tensor_name] = (local_owner, dup, meta_stage[id(local_owner)], meta_stage[id(dup)])
+                else:
+                    holders[dup_rank] = dup
+                    self._tied_remote.append((owner, dup, meta_stage[id(owner)], meta_stage[id(dup)]))
 
         self._stages = [
             Stage(config=config.multi_stage, layers=layers[splits[s] : splits[s + 1]], distributed_config=config.distributed,
@@ -305,6 +313,72 @@ class MultiStageModel:
     def initialize_weights(self) -> None:
         for stage in self._stages_on_device.values():
             stage.initialize_weights()
+        self.synchronize_tied_weights()
+
+    # ---- tied parameters held by two pipeline ranks
+    @property
+    def tied_remote_stages(self) -> set[int]:
+        """Stages on this rank whose gradient reduction must wait for the exchange with the other holder."""
+        pp_rank, pp = self._config.distributed.pipeline_rank, self._config.distributed.pipeline_parallel
+        return {s for _, _, a, b in self._tied_remote for s in (a, b) if s % pp == pp_rank and s in self._stages_on_device}
+
+    def _pipeline_peer(self, stage_index: int) -> int:
+        """Rank, inside the pipeline group, of the holder of `stage_index`."""
+        return stage_index % self._config.distributed.pipeline_parallel
+
+    def _export_parameter(self, name: str, shard_name: str = "weights") -> torch.Tensor:
+        s = self._parameter_stages[name]
+        stage = self._stages_on_device[s]
+        for i, fsdp in enumerate(stage.fsdps):
+            if name in fsdp.parameter_names:
+                shard = self._shards[shard_name][self._stage_shard_ranges[(s, i)]]
+                for got, tensor in fsdp.export_shard(shard):
+                    if got == name:
+                        return fsdp.get_parameter_meta(name).local_to_global(tensor)
+        raise KeyError(name)
+
+    def synchronize_tied_weights(self) -> None:
+        """Send the owner's weights to the copies on other pipeline ranks (after initialisation or loading)."""
+        from fast_llm_b200.parallel.collectives import recv, send
+
+        pp_rank, pp = self._config.distributed.pipeline_rank, self._config.distributed.pipeline_parallel
+        group = self._distributed.pipeline_group
+        for owner, dup, owner_stage, dup_stage in self._tied_remote:
+            if owner_stage % pp == pp_rank and owner_stage in self._stages_on_device:
+                value = self._export_parameter(owner.tensor_name).float().contiguous()
+                send(value, self._pipeline_peer(dup_stage), group)
+            elif dup_stage % pp == pp_rank and dup_stage in self._stages_on_device:
+                value = torch.empty(dup.global_shape, dtype=torch.float32, device=self._distributed.device)
+                recv(value, self._pipeline_peer(owner_stage), group)
+                self.import_state_tensor(dup.tensor_name, "weights", value)
+                self._stages_on_device[dup_stage].invalidate_buffer()
+
+    def exchange_tied_gradients(self) -> None:
+        """Both holders of a tied parameter end up with the sum of their gradient buffers (before the data reduction)."""
+        from fast_llm_b200.parallel.collectives import recv, send
+
+        pp_rank, pp = self._config.distributed.pipeline_rank, self._config.distributed.pipeline_parallel
+        group = self._distributed.pipeline_group
+        for owner, dup, owner_stage, dup_stage in self._tied_remote:
+            mine, other_stage = (owner, dup_stage) if owner_stage % pp == pp_rank else (dup, owner_stage)
+            if not ((owner_stage % pp == pp_rank and owner_stage in self._stages_on_device) or (dup_stage % pp == pp_rank and dup_stage in self._stages_on_device)):
+                continue
+            param = mine.tensor
+            grad = param.grad_buffer
+            if getattr(param, "param_grad_is_zero", False):
+                grad.zero_()
+                param.param_grad_is_zero = False
+            peer = self._pipeline_peer(other_stage)
+            theirs = torch.empty_like(grad)
+            local = grad.contiguous()
+            # the lower pipeline rank sends first: a fixed order avoids both sides blocking in a send
+            if pp_rank < other_stage % pp:
+                send(local, peer, group)
+                recv(theirs, peer, group)
+            else:
+                recv(theirs, peer, group)
+                send(local, peer, group)
+            grad.add_(theirs)
 
     def invalidate_buffers(self) -> None:
         for stage in self._stages_on_device.values():

@@ -58,6 +58,7 @@ class ScheduleRunner:
         self._distributed = distributed
         self._optimizer = optimizer
         self._stages_on_device = self._multi_stage.stages_on_device
+        self._tied_remote_stages = self._multi_stage.tied_remote_stages
         self._use_cuda = distributed.device.type == "cuda"
         if self._use_cuda:
             self._compute_stream = torch.cuda.current_stream(distributed.device)
@@ -96,11 +97,20 @@ class ScheduleRunner:
         if training:
             for stage in self._stages_on_device.values():
                 stage.reset_gradients()
+        context.deferred_reduces = []
         for step in schedule.steps:
             self._run_one(context, step)
         for handle in context.pending_sends:
             if handle is not None:
                 handle.wait()
+        if training and context.deferred_reduces:
+            # stages holding a copy of a parameter tied across pipeline ranks: first add the other holder's gradient
+            if self._data_stream is not self._compute_stream:
+                self._data_stream.wait_stream(self._compute_stream)
+            with self._stream_ctx(self._data_stream):
+                self._multi_stage.exchange_tied_gradients()
+                for stage, accumulate in context.deferred_reduces:
+                    stage.reduce_gradients(accumulate)
         if self._data_stream is not self._compute_stream:
             self._compute_stream.wait_stream(self._data_stream)
         if self._pipeline_stream is not self._compute_stream:
@@ -158,6 +168,11 @@ class ScheduleRunner:
         if step.reduce:
             if self._data_stream is not self._compute_stream:
                 self._data_stream.wait_stream(self._compute_stream)
+            if step.stage in self._tied_remote_stages:
+                # its gradient buffer is still missing the contribution of the other pipeline rank: reduce at the end
+                Assert.custom(lambda ok: ok, not step.reduce_accumulate and self._multi_stage._num_grad_buffers >= len(self._stages_on_device))
+                context.deferred_reduces.append((stage, step.reduce_accumulate))
+                return
             with self._stream_ctx(self._data_stream):
                 stage.reduce_gradients(step.reduce_accumulate)
                 if step.reduce_accumulate or self._multi_stage._num_grad_buffers < len(self._stages_on_device):
