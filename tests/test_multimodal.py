@@ -75,3 +75,31 @@ def test_image_patches_are_added_at_their_tokens():
         a, b = embed(pixels), embed(changed)
     moved = ((a - b).abs().sum(-1) > 1e-6).nonzero().flatten().tolist()
     assert moved == [40, 41, 42, 43]
+
+
+def test_llava_round_trip(tmp_path):
+    """Export to the llava layout (conv-shaped patch kernel, language_model.* prefix) and load it back."""
+    import json
+
+    import safetensors
+
+    from fast_llm_b200.engine.checkpoint.config import CheckpointLoadConfig, CheckpointSaveConfig
+    from fast_llm_b200.models.multimodal.model import MultiModalModel
+
+    trainer, _ = build_trainer(_config({("model", "base_model", "image_token_index"): 7,
+                                        ("model", "base_model", "vision_encoder", "adapter", "intermediate_size"): 64}))  # llava: adapter width = text hidden size
+    path = tmp_path / "llava"
+    trainer.multi_stage.save_checkpoint(CheckpointSaveConfig(path=path, format="llava"))
+    config = json.loads((path / "config.json").read_text())
+    assert config["model_type"] == "llava" and config["vision_config"]["patch_size"] == 4 and config["text_config"]["model_type"] == "mistral"
+    names = {}
+    for file in path.glob("*.safetensors"):
+        with safetensors.safe_open(str(file), framework="pt") as f:
+            for key in f.keys():
+                names[key] = f.get_slice(key).get_shape()
+    assert names["vision_tower.patch_conv.weight"] == [32, 3, 4, 4]
+    assert "language_model.model.layers.0.self_attn.q_proj.weight" in names and "multi_modal_projector.linear_2.bias" in names
+    loaded = MultiModalModel.from_pretrained(CheckpointLoadConfig(path=path, format="llava"), use_cpu=True)
+    original = {n: t for n, _, t in trainer.multi_stage.get_state_tensor_iterator(("weights",))}
+    for name, _, tensor in loaded.get_state_tensor_iterator(("weights",)):
+        torch.testing.assert_close(tensor.float(), original[name].float(), rtol=1e-2, atol=1e-2, msg=lambda m: f"{name}: {m}")
