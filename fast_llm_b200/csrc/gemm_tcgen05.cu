@@ -218,8 +218,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 // ------------------------------------------------------------------------------------------------
 // CTA-pair kernel: clusters of two CTAs, 256 x 256 tiles, tcgen05.mma.cta_group::2 issued by the leader (cluster rank 0)
 // ------------------------------------------------------------------------------------------------
+constexpr int PairTileM = 256, PairTileN = 256;
 struct PairCfg {
-  static constexpr int TILE_M = 256, TILE_N = 256;
+  static constexpr int TILE_M = PairTileM, TILE_N = PairTileN;
   static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;        // this CTA's 128 rows of A
   static constexpr int B_BYTES = (TILE_N / 2) * BLOCK_K * 2;   // this CTA's half of the B tile
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;        // 32 KiB
@@ -231,11 +232,65 @@ struct PairCfg {
   static constexpr int TMEM_COLS = 2 * TILE_N;
 };
 
-template <bool A_MN, bool B_MN, int EPI>
+// Grouped (mixture-of-experts) GEMMs on the same kernel.  Rows of A / C are sorted by expert and every expert's range is
+// padded to a multiple of the tile height, so a row block belongs to one expert; `row_begin[e]` (device memory, e = 0..E)
+// are the padded range starts - the launch never needs the routing result on the host.
+//   kGroupRows   C[rows of e] = A[rows of e] * B_e   : B holds E matrices stacked along its row dimension
+//                (fprop and dgrad of both MLP layers)
+//   kGroupWgrad  C_e (+)= A[rows of e]^T * B[rows of e] : contraction over the expert's rows, C holds E matrices stacked
+//                along its rows (weight gradients)
+enum GroupMode : int { kGroupNone = 0, kGroupRows = 1, kGroupWgrad = 2 };
+struct GroupArgs {
+  const int* row_begin;  // [experts + 1]
+  int experts;
+  int b_rows_per_expert;  // kGroupRows: rows of B (N if K-major, K if MN-major) per expert
+};
+struct TileInfo {
+  int m0, n0;      // coordinates in A (row or M index) and B (N index) of the tile, before the CTA's half offset
+  int c_row0;      // first row of C
+  int b_row_off;   // added to B's row coordinate (kGroupRows)
+  int k_begin, num_kb;
+};
+
+template <int GROUP>
+__device__ __forceinline__ int grouped_num_tiles(const GroupArgs& g, int M, int N, int num_m, int num_n) {
+  if constexpr (GROUP == kGroupRows) return (g.row_begin[g.experts] / PairTileM) * num_n;
+  if constexpr (GROUP == kGroupWgrad) return g.experts * num_m * num_n;
+  return num_m * num_n;
+}
+
+template <int GROUP>
+__device__ __forceinline__ TileInfo grouped_tile(const GroupArgs& g, int tile, int num_m, int num_n, int M, int K) {
+  TileInfo t;
+  int m_blk, n_blk;
+  if constexpr (GROUP == kGroupNone) {
+    tile_coords(tile, num_m, num_n, m_blk, n_blk);
+    t.m0 = m_blk * PairTileM; t.n0 = n_blk * PairTileN; t.c_row0 = t.m0; t.b_row_off = 0; t.k_begin = 0;
+    t.num_kb = (K + BLOCK_K - 1) / BLOCK_K;
+  } else if constexpr (GROUP == kGroupRows) {
+    const int rows_m = g.row_begin[g.experts] / PairTileM;
+    tile_coords(tile, rows_m, num_n, m_blk, n_blk);
+    t.m0 = m_blk * PairTileM; t.n0 = n_blk * PairTileN; t.c_row0 = t.m0; t.k_begin = 0;
+    t.num_kb = (K + BLOCK_K - 1) / BLOCK_K;
+    int e = 0;
+    while (e + 1 < g.experts && g.row_begin[e + 1] <= t.m0) ++e;
+    t.b_row_off = e * g.b_rows_per_expert;
+  } else {
+    const int per_expert = num_m * num_n;
+    const int e = tile / per_expert;
+    tile_coords(tile - e * per_expert, num_m, num_n, m_blk, n_blk);
+    t.m0 = m_blk * PairTileM; t.n0 = n_blk * PairTileN; t.c_row0 = e * M + t.m0; t.b_row_off = 0;
+    t.k_begin = g.row_begin[e];
+    t.num_kb = (g.row_begin[e + 1] - g.row_begin[e]) / BLOCK_K;
+  }
+  return t;
+}
+
+template <bool A_MN, bool B_MN, int EPI, int GROUP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_c, int use_tma_c, void* __restrict__ Cv, int M, int N, int K, long long ldc,
-                 int* __restrict__ err_word) {
+                 int* __restrict__ err_word, const GroupArgs group) {
   using C = PairCfg;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -286,8 +341,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   const int num_m = (M + C::TILE_M - 1) / C::TILE_M;
   const int num_n = (N + C::TILE_N - 1) / C::TILE_N;
-  const int num_tiles = num_m * num_n;
-  const int num_kb = (K + BLOCK_K - 1) / BLOCK_K;
+  const int num_tiles = grouped_num_tiles<GROUP>(group, M, N, num_m, num_n);
+  const int c_rows = (GROUP == kGroupWgrad) ? group.experts * M : ((GROUP == kGroupRows) ? group.row_begin[group.experts] : M);
   const int cluster_id = blockIdx.x >> 1;
   const int num_clusters = gridDim.x >> 1;
 
@@ -298,17 +353,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        int m_blk, n_blk;
-        tile_coords(tile, num_m, num_n, m_blk, n_blk);
-        const int m0 = m_blk * C::TILE_M + (int)cta_rank * BLOCK_M;
-        const int n0 = n_blk * C::TILE_N + (int)cta_rank * (C::TILE_N / 2);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const TileInfo ti = grouped_tile<GROUP>(group, tile, num_m, num_n, M, K);
+        const int m0 = ti.m0 + (int)cta_rank * BLOCK_M;
+        const int n0 = ti.n0 + (int)cta_rank * (C::TILE_N / 2);
+        for (int kb = 0; kb < ti.num_kb; ++kb) {
           if (!mbar_wait<true>(empty_bar(stage), phase ^ 1u, abort_flag, err_word, 11)) { ok = false; break; }
           const uint32_t a_dst = smem_base + stage * C::STAGE_BYTES;
           const uint32_t b_dst = a_dst + C::A_BYTES;
           if (leader) mbar_expect_tx(full_bar(stage), 2 * C::STAGE_BYTES);
           const uint32_t fb = map_to_cta(full_bar(stage), 0);
-          const int k0 = kb * BLOCK_K;
+          const int k0 = ti.k_begin + kb * BLOCK_K;
           if constexpr (!A_MN) {
             tma_load_2d_pair(a_dst, &tmap_a, fb, k0, m0);
           } else {
@@ -316,10 +370,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             for (int c = 0; c < BLOCK_M / 64; ++c) tma_load_2d_pair(a_dst + c * 8192, &tmap_a, fb, m0 + c * 64, k0);
           }
           if constexpr (!B_MN) {
-            tma_load_2d_pair(b_dst, &tmap_b, fb, k0, n0);
+            tma_load_2d_pair(b_dst, &tmap_b, fb, k0, ti.b_row_off + n0);
           } else {
 #pragma unroll
-            for (int c = 0; c < C::TILE_N / 2 / 64; ++c) tma_load_2d_pair(b_dst + c * 8192, &tmap_b, fb, n0 + c * 64, k0);
+            for (int c = 0; c < C::TILE_N / 2 / 64; ++c) tma_load_2d_pair(b_dst + c * 8192, &tmap_b, fb, n0 + c * 64, ti.b_row_off + k0);
           }
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -343,6 +397,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (!mbar_wait<true>(tempty_bar(acc), acc_phase ^ 1u, abort_flag, err_word, 12)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * C::TILE_N;
+        const int num_kb = grouped_tile<GROUP>(group, tile, num_m, num_n, M, K).num_kb;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait<true>(full_bar(stage), phase, abort_flag, err_word, 13)) { ok = false; break; }
           tc_fence_after();
@@ -362,8 +417,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
         if (ok) {
-          umma_commit_pair(tfull_bar(acc));
-          umma_commit_pair(map_to_cta(tfull_bar(acc), 1));
+          if (num_kb > 0) {
+            umma_commit_pair(tfull_bar(acc));
+            umma_commit_pair(map_to_cta(tfull_bar(acc), 1));
+          } else {
+            // an expert without rows: nothing was issued, release the epilogue warps directly
+            mbar_arrive(tfull_bar(acc));
+            mbar_arrive_cluster(map_to_cta(tfull_bar(acc), 1));
+          }
         }
       }
     }
@@ -374,24 +435,31 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     bool ok = true;
     uint32_t epi_counter = 0;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
-      int m_blk, n_blk;
-      tile_coords(tile, num_m, num_n, m_blk, n_blk);
+      const TileInfo ti = grouped_tile<GROUP>(group, tile, num_m, num_n, M, K);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait<true>(tfull_bar(acc), acc_phase, abort_flag, err_word, 14)) { ok = false; break; }
       tc_fence_after();
-      const int row = m_blk * C::TILE_M + (int)cta_rank * BLOCK_M + q * 32 + lane;
+      const int row0 = ti.c_row0 + (int)cta_rank * BLOCK_M + q * 32;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * C::TILE_N;
-      if (use_tma_c) {
-        epilogue_tma<EPI>(&tmap_c, smem + C::RING_BYTES + q * kEpiWarpBytes, taddr, C::TILE_N,
-                          m_blk * C::TILE_M + (int)cta_rank * BLOCK_M + q * 32, n_blk * C::TILE_N, M, N, lane, epi_counter);
+      const bool empty = ti.num_kb == 0;  // grouped weight gradient of an expert without rows: the tile is zero
+      if (empty) {
+        if constexpr (EPI == EPI_STORE_BF16 || EPI == EPI_STORE_F32) {
+          uint32_t zeros[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) zeros[i] = 0u;
+#pragma unroll 1
+          for (int c = 0; c < C::TILE_N / 32; ++c) store_chunk<EPI>(zeros, Cv, row0 + lane, ti.n0 + c * 32, c_rows, N, ldc);
+        }
+      } else if (use_tma_c) {
+        epilogue_tma<EPI>(&tmap_c, smem + C::RING_BYTES + q * kEpiWarpBytes, taddr, C::TILE_N, row0, ti.n0, c_rows, N, lane, epi_counter);
       } else {
 #pragma unroll 1
         for (int c = 0; c < C::TILE_N / 32; ++c) {
           uint32_t r[32];
           tmem_ld32(taddr + c * 32, r);
           tmem_wait_ld();
-          store_chunk<EPI>(r, Cv, row, n_blk * C::TILE_N + c * 32, M, N, ldc);
+          store_chunk<EPI>(r, Cv, row0 + lane, ti.n0 + c * 32, c_rows, N, ldc);
         }
       }
       tc_fence_before();
@@ -517,21 +585,23 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, 
   return FLB_OK;
 }
 
-template <bool A_MN, bool B_MN, int EPI>
+template <bool A_MN, bool B_MN, int EPI, int GROUP = kGroupNone>
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, int use_tc, void* C, int M, int N, int K,
-                long long ldc, int max_ctas, DeviceState* st, cudaStream_t stream) {
-  auto kern = gemm_pair_kernel<A_MN, B_MN, EPI>;
+                long long ldc, int max_ctas, DeviceState* st, cudaStream_t stream, GroupArgs group = GroupArgs{nullptr, 0, 0},
+                int tiles_upper_bound = 0) {
+  auto kern = gemm_pair_kernel<A_MN, B_MN, EPI, GROUP>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM_BYTES);
     if (e != cudaSuccess) return flb_record_cuda_error(e);
     configured = true;
   }
-  const int tiles = ((M + PairCfg::TILE_M - 1) / PairCfg::TILE_M) * ((N + PairCfg::TILE_N - 1) / PairCfg::TILE_N);
+  int tiles = ((M + PairCfg::TILE_M - 1) / PairCfg::TILE_M) * ((N + PairCfg::TILE_N - 1) / PairCfg::TILE_N);
+  if (GROUP != kGroupNone) tiles = tiles_upper_bound;
   int clusters = st->num_sms / 2;
   if (max_ctas > 1 && max_ctas / 2 < clusters) clusters = max_ctas / 2;
   if (tiles < clusters) clusters = tiles;
-  kern<<<2 * clusters, kNumThreads, PairCfg::SMEM_BYTES, stream>>>(ta, tb, tc, use_tc, C, M, N, K, ldc, st->err_word);
+  kern<<<2 * clusters, kNumThreads, PairCfg::SMEM_BYTES, stream>>>(ta, tb, tc, use_tc, C, M, N, K, ldc, st->err_word, group);
   FLB_CHECK_LAUNCH();
   return FLB_OK;
 }
@@ -614,6 +684,53 @@ FLB_API int flb_gemm_bf16_ex(const void* A, const void* B, void* C, int M, int N
 
 // Reads (and clears) the error word the GEMM kernels raise when a bounded wait expires.
 // Synchronises the device.  0 = no error; 1..4 / 11..14 = which role gave up (one-CTA / pair kernel).
+// Grouped GEMMs of a mixture-of-experts layer (CTA-pair kernel).  `row_begin`: device array [experts + 1] of the first row of
+// every expert in the expert-sorted row space, each a multiple of 256; `rows_upper_bound`: host-side bound on
+// row_begin[experts] (a multiple of 256; the A / C buffers have that many rows).
+//   mode 1: C[rows, N] = A[rows, K] * B_e, B = experts stacked matrices, [N, K] each (b_mn 0) or [K, N] each (b_mn 1)
+//   mode 2: C_e[M, N] (+)= A[rows of e, M]^T * B[rows of e, N]   (epilogue 0..3 as in flb_gemm_bf16); M % 256 == 0
+FLB_API int flb_grouped_gemm_bf16(const void* A, const void* B, void* C, const int* row_begin, int experts, int rows_upper_bound,
+                                  int M, int N, int K, long long lda, long long ldb, long long ldc, int b_mn_major, int epilogue, int mode,
+                                  cudaStream_t stream) {
+  if (experts <= 0 || rows_upper_bound <= 0 || rows_upper_bound % PairTileM || N <= 0) return FLB_ERR_SHAPE;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return FLB_ERR_SHAPE;
+  DeviceState* st = device_state();
+  if (!st) return FLB_ERR_CUDA;
+  const bool c_f32 = (epilogue == EPI_STORE_F32 || epilogue == EPI_ACC_F32);
+  CUtensorMap ta, tb, tc;
+  GroupArgs group{row_begin, experts, 0};
+  const int num_n = (N + PairTileN - 1) / PairTileN;
+  if (mode == kGroupRows) {
+    if (K <= 0 || epilogue != EPI_STORE_BF16) return FLB_ERR_SHAPE;
+    group.b_rows_per_expert = b_mn_major ? K : N;
+    if (!make_tmap(&ta, A, (uint64_t)K, (uint64_t)rows_upper_bound, (uint64_t)lda, BLOCK_K, BLOCK_M)) return FLB_ERR_TMA;
+    const bool ok = b_mn_major ? make_tmap(&tb, B, (uint64_t)N, (uint64_t)experts * K, (uint64_t)ldb, 64, BLOCK_K)
+                               : make_tmap(&tb, B, (uint64_t)K, (uint64_t)experts * N, (uint64_t)ldb, BLOCK_K, 128u);
+    if (!ok) return FLB_ERR_TMA;
+    if ((reinterpret_cast<uintptr_t>(C) & 15) || (ldc * 2) % 16) return FLB_ERR_SHAPE;
+    if (!make_tmap_c(&tc, C, (uint64_t)N, (uint64_t)rows_upper_bound, (uint64_t)ldc, false)) return FLB_ERR_TMA;
+    const int tiles = rows_upper_bound / PairTileM * num_n;
+    if (b_mn_major)
+      return launch_pair<false, true, EPI_STORE_BF16, kGroupRows>(ta, tb, tc, 1, C, rows_upper_bound, N, K, ldc, 0, st, stream, group, tiles);
+    return launch_pair<false, false, EPI_STORE_BF16, kGroupRows>(ta, tb, tc, 1, C, rows_upper_bound, N, K, ldc, 0, st, stream, group, tiles);
+  }
+  if (mode == kGroupWgrad) {
+    if (M <= 0 || M % PairTileM) return FLB_ERR_SHAPE;
+    if (!make_tmap(&ta, A, (uint64_t)M, (uint64_t)rows_upper_bound, (uint64_t)lda, 64, BLOCK_K)) return FLB_ERR_TMA;
+    if (!make_tmap(&tb, B, (uint64_t)N, (uint64_t)rows_upper_bound, (uint64_t)ldb, 64, BLOCK_K)) return FLB_ERR_TMA;
+    if ((reinterpret_cast<uintptr_t>(C) & 15) || (ldc * (c_f32 ? 4 : 2)) % 16) return FLB_ERR_SHAPE;
+    if (!make_tmap_c(&tc, C, (uint64_t)N, (uint64_t)experts * M, (uint64_t)ldc, c_f32)) return FLB_ERR_TMA;
+    const int tiles = experts * (M / PairTileM) * num_n;
+    switch (epilogue) {
+      case EPI_STORE_BF16: return launch_pair<true, true, EPI_STORE_BF16, kGroupWgrad>(ta, tb, tc, 1, C, M, N, rows_upper_bound, ldc, 0, st, stream, group, tiles);
+      case EPI_STORE_F32: return launch_pair<true, true, EPI_STORE_F32, kGroupWgrad>(ta, tb, tc, 1, C, M, N, rows_upper_bound, ldc, 0, st, stream, group, tiles);
+      case EPI_ACC_F32: return launch_pair<true, true, EPI_ACC_F32, kGroupWgrad>(ta, tb, tc, 1, C, M, N, rows_upper_bound, ldc, 0, st, stream, group, tiles);
+      case EPI_ACC_BF16: return launch_pair<true, true, EPI_ACC_BF16, kGroupWgrad>(ta, tb, tc, 1, C, M, N, rows_upper_bound, ldc, 0, st, stream, group, tiles);
+    }
+  }
+  return FLB_ERR_SHAPE;
+}
+
 FLB_API int flb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                           long long ldc, int a_mn_major, int b_mn_major, int epilogue, int block_n, int max_ctas,
                           cudaStream_t stream) {

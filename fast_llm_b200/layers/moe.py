@@ -238,6 +238,13 @@ class MixtureOfExpertMLP(MLP):
 
             x2 = gather(x2, group, 0, reduce_grads=True)
         scores, top_experts = self._route(x2, kwargs, losses)
+        from fast_llm_b200.ops.grouped_gemm import grouped_available
+
+        if (c.implementation != MoEImplementation.looped and group is None and grouped_available(x2, c.intermediate_size, c.gated)
+                and not self.layer_1._has_bias and self.layer_1._forward_hook is None and self.layer_2._forward_hook is None
+                and torch.is_tensor(self.layer_1.weight) and self.layer_1.weight.is_contiguous()):
+            out = self._forward_grouped(x2, scores, top_experts)
+            return out.view(*shape[:-1], out.shape[-1])
         w1s, w2s = self._expert_weights()
         if c.implementation == MoEImplementation.looped:
             out = self._forward_looped(x2, scores, top_experts, w1s, w2s, group)
@@ -252,6 +259,19 @@ class MixtureOfExpertMLP(MLP):
         recompute = c.recompute_level if c.recompute_level != MLPRecomputeLevel.none else MLPRecomputeLevel.activation
         # tensor-parallel experts: partial sums are all-reduced inside (sequence parallelism is handled by the caller)
         return mlp(rows, w1, None, w2, None, gated=c.gated, activation=c.activation, group=group, sequence_parallel=False, recompute_level=recompute)
+
+    def _forward_grouped(self, x2, scores, top_experts):
+        """All experts in one launch per product: rows sorted by expert and padded to whole tiles on the device (no host
+        synchronisation), six grouped GEMMs on the tcgen05 kernel (`ops/grouped_gemm.py`)."""
+        from fast_llm_b200.ops.grouped_gemm import expert_layout, grouped_mlp
+
+        c = self._config
+        token_index, dest, row_begin, rows, order = expert_layout(top_experts, c.experts)
+        xs = torch.zeros(rows, x2.shape[1], dtype=x2.dtype, device=x2.device).index_copy(0, dest, x2.index_select(0, token_index))
+        ys = grouped_mlp(xs, row_begin, self.layer_1.weight, self.layer_2.weight, c.experts, c.gated, c.activation)
+        weighted = ys.index_select(0, dest).float() * scores.reshape(-1).index_select(0, order)[:, None]
+        out = torch.zeros(x2.shape[0], x2.shape[1], dtype=torch.float32, device=x2.device).index_add(0, token_index, weighted)
+        return out.to(x2.dtype)
 
     def _forward_dropless(self, x2, scores, top_experts, w1s, w2s, group):
         c = self._config

@@ -363,3 +363,97 @@ def test_packed_attention_native_forward_library_backward(monkeypatch):
     ref.backward(g.float())
     assert _rel_err(out, ref) < 1.5e-2
     assert _rel_err(qkv.grad, ref_in.grad) < 3e-2
+
+
+def _expert_layout_case(tokens, k, experts, seed=0):
+    from fast_llm_b200.ops.grouped_gemm import expert_layout
+
+    torch.manual_seed(seed)
+    top = torch.stack([torch.randperm(experts, device="cuda")[:k] for _ in range(tokens)])
+    if experts > 2:
+        top[top == experts - 1] = 0  # leave the last expert without tokens
+    return top, expert_layout(top, experts)
+
+
+@pytest.mark.parametrize("b_mn", [False, True])
+def test_grouped_gemm_rows(b_mn):
+    from fast_llm_b200.ops.grouped_gemm import grouped_rows
+
+    experts, n, k = 4, 384, 192
+    top, (token_index, dest, row_begin, rows, order) = _expert_layout_case(700, 2, experts)
+    a = torch.zeros(rows, k, device="cuda", dtype=torch.bfloat16)
+    a[dest] = torch.randn(dest.numel(), k, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(experts * (k if b_mn else n), n if b_mn else k, device="cuda", dtype=torch.bfloat16)
+    out = grouped_rows(a, b, row_begin, experts, n, k, b_mn)
+    begins = row_begin.tolist()
+    for e in range(experts):
+        lo, hi = begins[e], begins[e + 1]
+        if hi == lo:
+            continue
+        w = b[e * k : (e + 1) * k].float() if b_mn else b[e * n : (e + 1) * n].float().t()
+        assert _rel_err(out[lo:hi], a[lo:hi].float() @ w) < 1e-2, e
+    from fast_llm_b200.ops.gemm import check_device_errors
+
+    check_device_errors()
+
+
+@pytest.mark.parametrize("accumulate,dtype", [(False, torch.float32), (True, torch.float32), (False, torch.bfloat16)])
+def test_grouped_gemm_wgrad(accumulate, dtype):
+    from fast_llm_b200.ops.grouped_gemm import grouped_wgrad
+
+    experts, m, n = 4, 256, 192
+    top, (token_index, dest, row_begin, rows, order) = _expert_layout_case(900, 2, experts, seed=1)
+    a = torch.zeros(rows, m, device="cuda", dtype=torch.bfloat16)
+    b = torch.zeros(rows, n, device="cuda", dtype=torch.bfloat16)
+    a[dest] = torch.randn(dest.numel(), m, device="cuda", dtype=torch.bfloat16)
+    b[dest] = torch.randn(dest.numel(), n, device="cuda", dtype=torch.bfloat16)
+    start = torch.randn(experts * m, n, device="cuda", dtype=dtype)
+    out = start.clone()
+    grouped_wgrad(a, b, out, row_begin, experts, accumulate)
+    begins = row_begin.tolist()
+    for e in range(experts):
+        lo, hi = begins[e], begins[e + 1]
+        expected = a[lo:hi].float().t() @ b[lo:hi].float()
+        if accumulate:
+            expected = expected + start[e * m : (e + 1) * m].float()
+        got = out[e * m : (e + 1) * m].float()
+        if hi == lo and not accumulate:
+            assert (got == 0).all(), "an expert without rows must produce a zero gradient"
+        else:
+            assert _rel_err(got, expected) < 2e-2, e
+
+
+def test_moe_grouped_matches_looped():
+    """The MoE layer on the grouped tcgen05 GEMMs against the per-expert loop: outputs, input and weight gradients."""
+    import fast_llm_b200.models.auto  # noqa: F401
+    from fast_llm_b200.layers.moe import MoEMLPConfig
+    from fast_llm_b200.parallel.topology import DistributedConfig
+    from fast_llm_b200.tensor import TensorDim
+
+    def build(implementation):
+        config = MoEMLPConfig.from_dict({"type": "moe", "experts": 4, "experts_per_token": 2, "intermediate_size": 256, "gated": True,
+                                         "activation": "silu", "add_linear_biases": False, "implementation": implementation})
+        config.validate()
+        distributed_config = DistributedConfig.from_dict({"compute_dtype": "bf16", "seed": 0, "world_size": 1, "rank": 0, "local_world_size": 1})
+        distributed_config.validate()
+        layer = config.get_layer(distributed_config, TensorDim("hidden", 128))
+        layer.set_names("mlp.")
+        return layer.materialize(device=torch.device("cuda"), dtype=torch.bfloat16)
+
+    grouped, looped = build("dropless"), build("looped")
+    for (_, a), (_, b) in zip(grouped.named_parameter_metas(), looped.named_parameter_metas()):
+        b.tensor.data.copy_(a.tensor.data)
+    torch.manual_seed(0)
+    x = torch.randn(600, 128, device="cuda", dtype=torch.bfloat16)
+    g = torch.randn(600, 128, device="cuda", dtype=torch.bfloat16)
+    results = []
+    for layer in (grouped, looped):
+        xi = x.clone().requires_grad_()
+        y = layer.forward(xi, {"training": True})
+        y.backward(g)
+        results.append((y.detach().float(), xi.grad.float(), {n: m.tensor.grad.float() for n, m in layer.named_parameter_metas() if m.tensor.grad is not None}))
+    (y0, dx0, w0), (y1, dx1, w1) = results
+    assert _rel_err(y0, y1) < 2e-2 and _rel_err(dx0, dx1) < 3e-2
+    assert set(w0) == set(w1) and {"layer_1.weight", "layer_2.weight"} <= set(w0)
+    for name in w0:
+        assert _rel_err(w0[name], w1[name]) < 3e-2, name
