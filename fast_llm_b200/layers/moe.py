@@ -263,15 +263,13 @@ class MixtureOfExpertMLP(MLP):
     def _forward_grouped(self, x2, scores, top_experts):
         """All experts in one launch per product: rows sorted by expert and padded to whole tiles on the device (no host
         synchronisation), six grouped GEMMs on the tcgen05 kernel (`ops/grouped_gemm.py`)."""
-        from fast_llm_b200.ops.grouped_gemm import expert_layout, grouped_mlp
+        from fast_llm_b200.ops.grouped_gemm import combine, dispatch, expert_rows, grouped_mlp
 
         c = self._config
-        token_index, dest, row_begin, rows, order = expert_layout(top_experts, c.experts)
-        xs = torch.zeros(rows, x2.shape[1], dtype=x2.dtype, device=x2.device).index_copy(0, dest, x2.index_select(0, token_index))
+        rows, row_begin, padded_rows = expert_rows(top_experts, c.experts)
+        xs = dispatch(x2, rows, padded_rows)
         ys = grouped_mlp(xs, row_begin, self.layer_1.weight, self.layer_2.weight, c.experts, c.gated, c.activation)
-        weighted = ys.index_select(0, dest).float() * scores.reshape(-1).index_select(0, order)[:, None]
-        out = torch.zeros(x2.shape[0], x2.shape[1], dtype=torch.float32, device=x2.device).index_add(0, token_index, weighted)
-        return out.to(x2.dtype)
+        return combine(ys, rows, scores)
 
     def _forward_dropless(self, x2, scores, top_experts, w1s, w2s, group):
         c = self._config

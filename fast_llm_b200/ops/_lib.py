@@ -19,6 +19,9 @@ _p, _i, _ll, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_flo
 
 _SIGNATURES = {
     "flb_gemm_bf16": [_p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _i, _i, _p],
+    "flb_moe_dispatch": [_p, _p, _p, _p, _i, _i, _i, _p],
+    "flb_moe_combine": [_p, _p, _p, _p, _i, _i, _i, _p],
+    "flb_moe_score_grad": [_p, _p, _p, _p, _i, _i, _i, _p],
     "flb_grouped_gemm_bf16": [_p, _p, _p, _p, _i, _i, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _p],
     "flb_gemm_bf16_ex": [_p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _p],
     "flb_gemm_error_word": [],

@@ -92,6 +92,76 @@ def grouped_mlp(x, row_begin, w1, w2, experts: int, gated: bool, activation: Act
     return _GroupedMLP.apply(x, row_begin, w1, w2, experts, gated, activation)
 
 
+def _dispatch_raw(x, rows, scale, padded_rows: int) -> torch.Tensor:
+    tokens, k = rows.shape
+    out = torch.zeros(padded_rows, x.shape[1], dtype=x.dtype, device=x.device)  # padding rows stay zero
+    _lib.check(_lib.get_lib().flb_moe_dispatch(x.data_ptr(), rows.data_ptr(), _lib.ptr(scale), out.data_ptr(), tokens, k, x.shape[1], _lib.stream_ptr()),
+               "flb_moe_dispatch")
+    _lib.count_launch()
+    return out
+
+
+def _combine_raw(y, rows, scores) -> torch.Tensor:
+    tokens, k = rows.shape
+    out = torch.empty(tokens, y.shape[1], dtype=y.dtype, device=y.device)
+    _lib.check(_lib.get_lib().flb_moe_combine(y.data_ptr(), rows.data_ptr(), _lib.ptr(scores), out.data_ptr(), tokens, k, y.shape[1], _lib.stream_ptr()),
+               "flb_moe_combine")
+    _lib.count_launch()
+    return out
+
+
+class _Dispatch(torch.autograd.Function):
+    """xs[rows[t, j]] = x[t]: copies every token to the row of each of its experts."""
+
+    @staticmethod
+    def forward(ctx, x, rows, padded_rows):
+        ctx.save_for_backward(rows)
+        return _dispatch_raw(x.contiguous(), rows, None, padded_rows)
+
+    @staticmethod
+    def backward(ctx, grad):
+        (rows,) = ctx.saved_tensors
+        return _combine_raw(grad.contiguous(), rows, None), None, None
+
+
+class _Combine(torch.autograd.Function):
+    """out[t] = sum_j scores[t, j] * y[rows[t, j]]"""
+
+    @staticmethod
+    def forward(ctx, y, rows, scores):
+        scores = scores.float().contiguous()
+        ctx.save_for_backward(y, rows, scores)
+        return _combine_raw(y.contiguous(), rows, scores)
+
+    @staticmethod
+    def backward(ctx, grad):
+        y, rows, scores = ctx.saved_tensors
+        grad = grad.contiguous()
+        tokens, k = rows.shape
+        dy = _dispatch_raw(grad, rows, scores, y.shape[0])
+        dscores = torch.empty(tokens, k, dtype=torch.float32, device=y.device)
+        _lib.check(_lib.get_lib().flb_moe_score_grad(y.data_ptr(), rows.data_ptr(), grad.data_ptr(), dscores.data_ptr(), tokens, k, y.shape[1],
+                                                     _lib.stream_ptr()), "flb_moe_score_grad")
+        _lib.count_launch()
+        return dy, None, dscores
+
+
+def dispatch(x: torch.Tensor, rows: torch.Tensor, padded_rows: int) -> torch.Tensor:
+    return _Dispatch.apply(x, rows, padded_rows)
+
+
+def combine(y: torch.Tensor, rows: torch.Tensor, scores: torch.Tensor) -> torch.Tensor:
+    return _Combine.apply(y, rows, scores)
+
+
+def expert_rows(top_experts: torch.Tensor, experts: int) -> tuple[torch.Tensor, torch.Tensor, int]:
+    """(rows int32 [tokens, k]: row of every (token, choice) in the expert-sorted padded space, row_begin, padded size)."""
+    token_index, dest, row_begin, rows_upper_bound, order = expert_layout(top_experts, experts)
+    rows = torch.empty(top_experts.numel(), dtype=torch.int32, device=top_experts.device)
+    rows[order] = dest.to(torch.int32)
+    return rows.view(top_experts.shape), row_begin, rows_upper_bound
+
+
 def expert_layout(top_experts: torch.Tensor, experts: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, int]:
     """Device-side layout of the expert-sorted, padded row space.
 

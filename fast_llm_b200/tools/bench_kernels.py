@@ -163,6 +163,50 @@ def bench_attention(results):
     print(json.dumps(r), flush=True)
 
 
+def bench_moe(results):
+    """Mixtral-8x7B MLP layer (hidden 4096, ffn 14336, 8 experts, top-2) at 8192 tokens, forward + backward: grouped
+    tcgen05 GEMMs against the per-expert loop."""
+    import fast_llm_b200.models.auto  # noqa: F401
+    from fast_llm_b200.layers.moe import MoEMLPConfig
+    from fast_llm_b200.parallel.topology import DistributedConfig
+    from fast_llm_b200.tensor import TensorDim
+
+    _, tflops_peak, kind = _peaks()
+    tokens, hidden, ffn, experts, top_k = 8192, 4096, 14336, 8, 2
+
+    def build(implementation):
+        config = MoEMLPConfig.from_dict({"type": "moe", "experts": experts, "experts_per_token": top_k, "intermediate_size": ffn, "gated": True,
+                                         "activation": "silu", "add_linear_biases": False, "implementation": implementation})
+        config.validate()
+        dc = DistributedConfig.from_dict({"compute_dtype": "bf16", "seed": 0, "world_size": 1, "rank": 0, "local_world_size": 1})
+        dc.validate()
+        layer = config.get_layer(dc, TensorDim("hidden", hidden))
+        layer.set_names("mlp.")
+        return layer.materialize(device=torch.device("cuda"), dtype=torch.bfloat16)
+
+    x = torch.randn(tokens, hidden, device="cuda", dtype=torch.bfloat16)
+    g = torch.randn(tokens, hidden, device="cuda", dtype=torch.bfloat16)
+    flops = 3 * 2.0 * tokens * top_k * hidden * ffn * 3  # three products of [rows, hidden] x [hidden, ffn] per direction, fwd + 2x bwd
+    timings = {}
+    for implementation in ("dropless", "looped"):
+        layer = build(implementation)
+
+        def step():
+            xi = x.detach().requires_grad_()
+            layer.forward(xi, {"training": True}).backward(g)
+            for _, meta in layer.named_parameter_metas():
+                meta.tensor.grad = None
+
+        timings[implementation] = time_op(step)
+        del layer
+        torch.cuda.empty_cache()
+    ms, ms_loop = timings["dropless"], timings["looped"]
+    r = {"op": "moe_mixtral_layer_fwd_bwd", "ms": ms, "tflops": flops / ms / 1e9, "frac_of_peak": flops / ms / 1e9 / tflops_peak, "peak_kind": kind,
+         "cublas_ms": ms_loop, "cublas_tflops": flops / ms_loop / 1e9, "note": "second pair = per-expert loop on the same tcgen05 GEMM (host sync per layer)"}
+    results.append(r)
+    print(json.dumps(r), flush=True)
+
+
 def profile_attention():
     """Small fixed workload for an ncu capture: two forward + backward launches of attention at the Mistral-7B shape."""
     from fast_llm_b200.ops.attention import attention_backward_native, attention_forward_native
@@ -229,7 +273,9 @@ def main(argv):
         bench_gemm_tiles(results)
     if "attention" in argv:
         bench_attention(results)
-    which = [a for a in argv if a in ("gemm", "elementwise")] or ([] if ("gemm_tiles" in argv or "attention" in argv) else ["gemm", "elementwise"])
+    if "moe" in argv:
+        bench_moe(results)
+    which = [a for a in argv if a in ("gemm", "elementwise")] or ([] if ("gemm_tiles" in argv or "attention" in argv or "moe" in argv) else ["gemm", "elementwise"])
     if "gemm" in which:
         bench_gemm(results)
     if "elementwise" in which:
