@@ -376,6 +376,12 @@ class MTPLlamaHuggingfaceCheckpointHandler(LlamaHuggingfaceCheckpointHandler):
         return out
 
     @classmethod
+    def get_extra_files(cls):
+        from fast_llm_b200.external_models.mtp_llama import configuration_mtp_llama, modeling_mtp_llama
+
+        return [pathlib.Path(configuration_mtp_llama.__file__), pathlib.Path(modeling_mtp_llama.__file__)]
+
+    @classmethod
     def get_weight_converters(cls, c):
         block = cls._block(c)
         out = [conv for conv in super().get_weight_converters(c) if conv.fast_llm_name != ("head.final_norm.weight",)]

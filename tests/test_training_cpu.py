@@ -259,6 +259,21 @@ def test_mtp_llama_and_apriel_hybrid_round_trip(tmp_path):
     mtp["head"]["prediction_heads"] = 2
     config = _round_trip(tmp_path, mtp, "mtp_llama")
     assert config["prediction_heads"] == 2 and config["model_type"] == "mtp_llama"
+    # the exported directory carries stand-alone modelling code that `transformers` can load, and its heads agree with ours
+    assert (tmp_path / "mtp_llama" / "modeling_mtp_llama.py").exists() and (tmp_path / "mtp_llama" / "configuration_mtp_llama.py").exists()
+    from fast_llm_b200.engine.checkpoint.config import CheckpointLoadConfig
+    from fast_llm_b200.engine.inference.runner import InferenceRunner
+    from fast_llm_b200.external_models.mtp_llama.modeling_mtp_llama import MTPLlamaForCausalLM
+    from fast_llm_b200.models.gpt.model import GPTModel
+
+    external = MTPLlamaForCausalLM.from_pretrained(str(tmp_path / "mtp_llama"), torch_dtype=torch.float32)
+    tokens = torch.randint(0, 512, (1, 24))
+    with torch.no_grad():
+        logits = external(input_ids=tokens, return_all_prediction_heads=True).logits
+    assert logits.shape == (1, 24, 2, 512)
+    runner = InferenceRunner(GPTModel.from_pretrained(CheckpointLoadConfig(path=tmp_path / "mtp_llama", format="mtp_llama"), use_cpu=True))
+    runner.setup()
+    torch.testing.assert_close(logits[0, :, 0], runner.forward_tokens(tokens[0]), rtol=1e-4, atol=1e-4)
 
     hybrid = copy.deepcopy(TINY_BASE_MODEL)
     attention_block = hybrid["decoder"]["block"]
