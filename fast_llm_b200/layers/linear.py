@@ -154,26 +154,10 @@ class CausalConv1d(LayerBase):
 
     def forward(self, x: torch.Tensor, document_index: torch.Tensor | None = None) -> torch.Tensor:
         """x: [tokens, channels]. Tokens of different documents (document_index) do not see each other."""
-        tokens, channels = x.shape
-        w = self.weight  # [channels, 1, k]
-        k = w.shape[-1]
-        out = torch.zeros_like(x, dtype=torch.float32)
-        xf = x.float()
-        for j in range(k):
-            shift = k - 1 - j
-            shifted = torch.zeros_like(xf)
-            if shift == 0:
-                shifted = xf
-            elif shift < tokens:
-                shifted[shift:] = xf[:-shift]
-                if document_index is not None:
-                    same = torch.zeros(tokens, dtype=torch.bool, device=x.device)
-                    same[shift:] = document_index[shift:] == document_index[:-shift]
-                    shifted = shifted * same[:, None]
-            out = out + shifted * w[:, 0, j].float()[None, :]
-        if self._has_bias:
-            out = out + self.bias.float()[None, :]
-        return activation_reference(out, self._activation).to(x.dtype)
+        from fast_llm_b200.ops.ssm import causal_conv1d
+
+        weight = self.weight  # [channels, 1, k]
+        return causal_conv1d(x, weight.reshape(weight.shape[0], weight.shape[-1]), self.bias if self._has_bias else None, document_index, self._activation)
 
     def __call__(self, *args, **kwargs):
         return self.forward(*args, **kwargs)

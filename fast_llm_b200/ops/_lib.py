@@ -19,6 +19,11 @@ _p, _i, _ll, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_flo
 
 _SIGNATURES = {
     "flb_gemm_bf16": [_p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _i, _i, _p],
+    "flb_causal_conv1d_fwd": [_p, _p, _p, _p, _p, _ll, _i, _i, _i, _p],
+    "flb_causal_conv1d_bwd": [_p, _p, _p, _p, _p, _p, _p, _p, _ll, _i, _i, _i, _i, _p],
+    "flb_selective_scan_chunks": [_ll],
+    "flb_selective_scan_fwd": [_p] * 9 + [_ll, _i, _i, _i, _i, _p, _p, _p, _p],
+    "flb_selective_scan_bwd": [_p] * 9 + [_ll, _i, _i, _i, _i] + [_p] * 13,
     "flb_moe_dispatch": [_p, _p, _p, _p, _i, _i, _i, _p],
     "flb_moe_combine": [_p, _p, _p, _p, _i, _i, _i, _p],
     "flb_moe_score_grad": [_p, _p, _p, _p, _i, _i, _i, _p],

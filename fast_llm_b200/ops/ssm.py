@@ -93,6 +93,81 @@ def chunked_scan(step: typing.Callable, state_shape, seq_inputs, shared_inputs, 
     return _ChunkedScan.apply(step, len(seq_inputs), chunk, boundaries, tuple(state_shape), *seq_inputs, *shared_inputs)
 
 
+# ----------------------------------------------------------------------------------------------------------------------
+# depthwise causal convolution
+# ----------------------------------------------------------------------------------------------------------------------
+def causal_conv1d_reference(x, weight, bias, document_index, activation) -> torch.Tensor:
+    """x [tokens, channels]; weight [channels, k]; out[t] = act(bias + sum_j weight[:, j] * x[t - (k - 1 - j)]) within a document."""
+    from fast_llm_b200.ops.activation import activation_reference
+
+    tokens = x.shape[0]
+    k = weight.shape[-1]
+    xf = x.float()
+    out = torch.zeros_like(xf)
+    for j in range(k):
+        shift = k - 1 - j
+        if shift >= tokens:
+            continue
+        shifted = torch.zeros_like(xf)
+        shifted[shift:] = xf[: tokens - shift]
+        if document_index is not None and shift > 0:
+            same = torch.zeros(tokens, dtype=torch.bool, device=x.device)
+            same[shift:] = document_index[shift:] == document_index[: tokens - shift]
+            shifted = shifted * same[:, None]
+        out = out + shifted * weight[:, j].float()[None, :]
+    if bias is not None:
+        out = out + bias.float()[None, :]
+    return activation_reference(out, activation).to(x.dtype)
+
+
+class _CausalConv1d(torch.autograd.Function):
+    TOKENS_PER_BLOCK = 512
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, document_index, activation):
+        from fast_llm_b200.ops import _lib
+
+        x = x.contiguous()
+        w32 = weight.float().contiguous()
+        b32 = None if bias is None else bias.float().contiguous()
+        doc = None if document_index is None else document_index.to(torch.int32).contiguous()
+        out = torch.empty_like(x)
+        tokens, channels = x.shape
+        _lib.check(_lib.get_lib().flb_causal_conv1d_fwd(x.data_ptr(), w32.data_ptr(), _lib.ptr(b32), _lib.ptr(doc), out.data_ptr(), tokens, channels,
+                                                       w32.shape[1], activation.code, _lib.stream_ptr()), "flb_causal_conv1d_fwd")
+        _lib.count_launch()
+        ctx.save_for_backward(x, w32, b32, doc)
+        ctx.activation, ctx.has_bias, ctx.dtypes = activation, bias is not None, (weight.dtype, None if bias is None else bias.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        from fast_llm_b200.ops import _lib
+
+        x, w32, b32, doc = ctx.saved_tensors
+        tokens, channels = x.shape
+        width = w32.shape[1]
+        grad = grad.contiguous()
+        dpre, dx = torch.empty_like(x), torch.empty_like(x)
+        blocks = (tokens + _CausalConv1d.TOKENS_PER_BLOCK - 1) // _CausalConv1d.TOKENS_PER_BLOCK
+        partial = torch.empty(blocks, channels, width + 1, dtype=torch.float32, device=x.device)
+        _lib.check(_lib.get_lib().flb_causal_conv1d_bwd(x.data_ptr(), w32.data_ptr(), _lib.ptr(b32), _lib.ptr(doc), grad.data_ptr(), dpre.data_ptr(),
+                                                       dx.data_ptr(), partial.data_ptr(), tokens, channels, width, ctx.activation.code,
+                                                       _CausalConv1d.TOKENS_PER_BLOCK, _lib.stream_ptr()), "flb_causal_conv1d_bwd")
+        _lib.count_launch(3)
+        sums = partial.sum(0)  # fixed order: deterministic
+        dw = sums[:, :width].to(ctx.dtypes[0])
+        db = sums[:, width].to(ctx.dtypes[1]) if ctx.has_bias else None
+        return dx, dw, db, None, None
+
+
+def causal_conv1d(x, weight, bias, document_index, activation) -> torch.Tensor:
+    """Depthwise causal convolution with fused bias and activation; weight [channels, k] (k <= 8)."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and weight.shape[-1] <= 8:
+        return _CausalConv1d.apply(x, weight, bias, document_index, activation)
+    return causal_conv1d_reference(x, weight, bias, document_index, activation)
+
+
 def _lower_mask(n: int, device, strict: bool) -> torch.Tensor:
     return torch.ones(n, n, dtype=torch.bool, device=device).tril(-1 if strict else 0)
 
@@ -125,12 +200,90 @@ def _selective_scan_step(state, chunk_in, shared):
     return y.to(x.dtype), states[-1]
 
 
+class _SelectiveScan(torch.autograd.Function):
+    """Chunk-parallel CUDA scan (`csrc/ssm.cu`): three launches forward, three backward; the only saved state beyond the
+    inputs is the [chunks, channels, state] start state and decay product of every 64-token chunk."""
+
+    @staticmethod
+    def forward(ctx, x, dt, a, b, c, skip, z, dt_bias, starts):
+        from fast_llm_b200.ops import _lib
+
+        lib = _lib.get_lib()
+        x, dt, b, c = x.contiguous(), dt.contiguous(), b.contiguous(), c.contiguous()
+        z = None if z is None else z.contiguous()
+        a32, skip32 = a.float().contiguous(), skip.float().contiguous()
+        bias32 = None if dt_bias is None else dt_bias.float().contiguous()
+        tokens, channels = x.shape
+        state = a32.shape[1]
+        chunks = lib.flb_selective_scan_chunks(tokens)
+        chunk_state = torch.empty(chunks, channels, state, dtype=torch.float32, device=x.device)
+        chunk_decay = torch.empty_like(chunk_state)
+        y = torch.empty_like(x)
+        _lib.check(lib.flb_selective_scan_fwd(x.data_ptr(), dt.data_ptr(), a32.data_ptr(), b.data_ptr(), c.data_ptr(), skip32.data_ptr(), _lib.ptr(z),
+                                              _lib.ptr(bias32), _lib.ptr(starts), tokens, channels, state, b.shape[1], c.shape[1],
+                                              chunk_state.data_ptr(), chunk_decay.data_ptr(), y.data_ptr(), _lib.stream_ptr()), "flb_selective_scan_fwd")
+        _lib.count_launch(3)
+        ctx.save_for_backward(x, dt, a32, b, c, skip32, z, bias32, starts, chunk_state, chunk_decay)
+        ctx.dtypes = (a.dtype, skip.dtype, None if dt_bias is None else dt_bias.dtype)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from fast_llm_b200.ops import _lib
+
+        lib = _lib.get_lib()
+        x, dt, a32, b, c, skip32, z, bias32, starts, chunk_state, chunk_decay = ctx.saved_tensors
+        tokens, channels = x.shape
+        state, chunks = a32.shape[1], chunk_state.shape[0]
+        dy = dy.contiguous()
+        dx, ddt = torch.empty_like(x), torch.empty_like(dt)
+        dz = None if z is None else torch.empty_like(z)
+        db = torch.zeros(b.shape, dtype=torch.float32, device=x.device)
+        dc = torch.zeros(c.shape, dtype=torch.float32, device=x.device)
+        adjoint = torch.empty_like(chunk_state)
+        da_partial = torch.empty_like(chunk_state)
+        dskip_partial = torch.empty(chunks, channels, dtype=torch.float32, device=x.device)
+        dbias_partial = torch.empty_like(dskip_partial)
+        _lib.check(lib.flb_selective_scan_bwd(x.data_ptr(), dt.data_ptr(), a32.data_ptr(), b.data_ptr(), c.data_ptr(), skip32.data_ptr(), _lib.ptr(z),
+                                              _lib.ptr(bias32), _lib.ptr(starts), tokens, channels, state, b.shape[1], c.shape[1],
+                                              chunk_state.data_ptr(), chunk_decay.data_ptr(), adjoint.data_ptr(), dy.data_ptr(), dx.data_ptr(),
+                                              ddt.data_ptr(), _lib.ptr(dz), db.data_ptr(), dc.data_ptr(), da_partial.data_ptr(),
+                                              dskip_partial.data_ptr(), dbias_partial.data_ptr(), _lib.stream_ptr()), "flb_selective_scan_bwd")
+        _lib.count_launch(3)
+        da = da_partial.sum(0).to(ctx.dtypes[0])
+        dskip = dskip_partial.sum(0).to(ctx.dtypes[1])
+        dbias = None if bias32 is None else dbias_partial.sum(0).to(ctx.dtypes[2])
+        return dx, ddt, da, db.to(b.dtype), dc.to(c.dtype), dskip, dz, dbias, None
+
+
+def _scan_kernel_applies(x, dt, a, b, c, z) -> bool:
+    if not (x.is_cuda and all(t is None or t.dtype == torch.bfloat16 for t in (x, dt, b, c, z))):
+        return False
+    channels, state = a.shape
+    if state > 32 or state & (state - 1) or channels % b.shape[1] or channels % c.shape[1]:
+        return False
+    return channels % (128 // state) == 0
+
+
+def document_starts(cu_seqlens, tokens: int, device) -> torch.Tensor | None:
+    """uint8 [tokens], 1 at the first token of every document (None for one document)."""
+    if cu_seqlens is None or cu_seqlens.numel() <= 2:
+        return None
+    starts = torch.zeros(tokens, dtype=torch.uint8, device=device)
+    starts[cu_seqlens[:-1].to(device=device, dtype=torch.long)] = 1
+    return starts
+
+
 def selective_scan(x, dt, a, b, c, skip, z=None, dt_bias=None, cu_seqlens=None, chunk: int = 16) -> torch.Tensor:
     """y_t = C_t . h_t + D x_t (times silu(z_t)), h_t = exp(softplus(dt_t + bias) A) h_{t-1} + softplus(.) B_t x_t.
 
     x, dt, z: [tokens, channels]; a: [channels, state] (negative); b, c: [tokens, groups, state] with `groups` dividing
     `channels` (group i serves channels [i * channels / groups, (i + 1) * channels / groups)); skip: [channels].
+    bf16 CUDA inputs run the chunk-parallel kernels; everything else the chunked PyTorch restatement below.
     """
+    if _scan_kernel_applies(x, dt, a, b, c, z):
+        return _SelectiveScan.apply(x, dt, a, b, c, skip, z, dt_bias, document_starts(cu_seqlens, x.shape[0], x.device))
+
     def step(state, chunk_in, shared):
         xs, dts, bs, cs, *rest = chunk_in
         zs = rest[0] if z is not None else None

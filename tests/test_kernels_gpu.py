@@ -457,3 +457,55 @@ def test_moe_grouped_matches_looped():
     assert set(w0) == set(w1) and {"layer_1.weight", "layer_2.weight"} <= set(w0)
     for name in w0:
         assert _rel_err(w0[name], w1[name]) < 3e-2, name
+
+
+@pytest.mark.parametrize("tokens,channels,width,act,with_docs", [(1000, 64, 4, "silu", True), (257, 136, 3, "identity", False), (33, 8, 8, "gelu", True)])
+def test_causal_conv1d(tokens, channels, width, act, with_docs):
+    from fast_llm_b200.ops.activation import ActivationType
+    from fast_llm_b200.ops.ssm import causal_conv1d, causal_conv1d_reference
+
+    torch.manual_seed(0)
+    x = torch.randn(tokens, channels, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(channels, width, device="cuda") * 0.5).bfloat16().requires_grad_()
+    b = torch.randn(channels, device="cuda").bfloat16().requires_grad_()
+    doc = torch.sort(torch.randint(0, 5, (tokens,), device="cuda")).values.int() if with_docs else None
+    g = torch.randn(tokens, channels, device="cuda", dtype=torch.bfloat16)
+    out = causal_conv1d(x, w, b, doc, ActivationType(act))
+    out.backward(g)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    ref = causal_conv1d_reference(xr, wr, br, doc, ActivationType(act))
+    ref.backward(g.float())
+    assert _rel_err(out, ref) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 2e-2
+    assert _rel_err(w.grad, wr.grad) < 2e-2
+    assert _rel_err(b.grad, br.grad) < 2e-2
+
+
+@pytest.mark.parametrize("tokens,channels,state,groups_b,groups_c,gated,docs", [
+    (200, 64, 16, 2, 4, True, [0, 70, 71, 200]), (130, 32, 8, 1, 4, False, None), (64, 128, 16, 8, 8, True, [0, 64]), (300, 32, 4, 1, 1, True, [0, 129, 300])])
+def test_selective_scan_kernel(tokens, channels, state, groups_b, groups_c, gated, docs):
+    from fast_llm_b200.ops.ssm import _SelectiveScan, document_starts, selective_scan, selective_scan_reference
+
+    torch.manual_seed(0)
+    dev = "cuda"
+    x = torch.randn(tokens, channels, device=dev).bfloat16().requires_grad_()
+    dt = (torch.randn(tokens, channels, device=dev) - 1).bfloat16().requires_grad_()
+    a = (-torch.rand(channels, state, device=dev) * 2 - 0.1).requires_grad_()
+    b = torch.randn(tokens, groups_b, state, device=dev).bfloat16().requires_grad_()
+    c = torch.randn(tokens, groups_c, state, device=dev).bfloat16().requires_grad_()
+    skip = torch.randn(channels, device=dev).requires_grad_()
+    z = torch.randn(tokens, channels, device=dev).bfloat16().requires_grad_() if gated else None
+    bias = torch.randn(channels, device=dev).requires_grad_()
+    cu = None if docs is None else torch.tensor(docs, device=dev, dtype=torch.int32)
+    g = torch.randn(tokens, channels, device=dev).bfloat16()
+    inputs = [x, dt, a, b, c, skip] + ([z] if gated else []) + [bias]
+    out = selective_scan(x, dt, a, b, c, skip, z, bias, cu)
+    assert out.grad_fn is not None and type(out.grad_fn).__name__.startswith("_SelectiveScan")
+    out.backward(g)
+    refs = [t.detach().float().requires_grad_() for t in inputs]
+    rz = refs[6] if gated else None
+    ref = selective_scan_reference(refs[0], refs[1], refs[2], refs[3], refs[4], refs[5], rz, refs[-1], cu)
+    ref.backward(g.float())
+    assert _rel_err(out, ref) < 1e-2
+    for name, t, r in zip(["x", "dt", "a", "b", "c", "skip"] + (["z"] if gated else []) + ["bias"], inputs, refs):
+        assert _rel_err(t.grad, r.grad) < 2e-2, name
