@@ -3,13 +3,16 @@
 //   flb_causal_conv1d_fwd / _bwd   depthwise causal convolution (kernel width <= 8) with fused bias and activation; a token
 //                                  never sees tokens of another document (`doc_index`).
 //   flb_selective_scan_fwd / _bwd  Mamba selective scan  h_t = exp(dt_t A) h_{t-1} + dt_t B_t x_t,  y_t = <C_t, h_t> + D x_t,
-//                                  y_t *= silu(z_t), with dt_t = softplus(dt_raw_t + dt_bias).  The sequence is cut into
-//                                  chunks that are scanned in parallel from a zero state; a second kernel chains the chunk
-//                                  summaries (decay product, end state) in order; a third re-scans every chunk from its
-//                                  true start state and emits y.  The backward pass runs the same three phases in
-//                                  reverse on the adjoint recurrence, recomputing the states of a chunk from its saved
-//                                  start state.  One thread owns one (channel, state index) pair; the `state` lanes of a
-//                                  channel sit in one warp and reduce <C, h> with shuffles.
+//                                  y_t *= silu(z_t), with dt_t = softplus(dt_raw_t + dt_bias).  One thread owns one channel
+//                                  and keeps its `state` values in registers, so x / dt / z loads are coalesced across the
+//                                  block and <C_t, h_t> needs no shuffles.  The sequence is cut into 64-token chunks that
+//                                  are scanned in parallel from a zero state; a second kernel chains the chunk summaries
+//                                  (decay product, end state) in order; a third re-scans every chunk from its true start
+//                                  state and emits y.  The backward pass chains the adjoint the same way in reverse, then
+//                                  walks every chunk backwards in sub-chunks whose states are recomputed from checkpoints
+//                                  (written by a re-run of the third forward kernel, not kept between forward and
+//                                  backward).  Gradients of B and C, which are shared by the channels of a group, are
+//                                  transposed through shared memory and summed in a fixed order.
 //
 // These replace the external `causal_conv1d_fn` and `selective_scan_fn` kernels the reference calls
 // (`fast_llm/layers/common/linear/convolution.py:15-68`, `fast_llm/layers/ssm/mamba.py:183-236`).
@@ -22,131 +25,189 @@ using namespace flb;
 // causal conv1d
 // ----------------------------------------------------------------------------------------------------------------------
 constexpr int kMaxWidth = 8;
+constexpr int kConvThreads = 128;
 
-// thread = (token, 8 channels)
-__global__ void conv1d_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
-                                  const int* __restrict__ doc, __nv_bfloat16* __restrict__ out, long long tokens, int channels, int width,
-                                  int act) {
-  const int nvec = channels >> 3;
-  const long long total = tokens * nvec;
-  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
-    const long long t = idx / nvec;
-    const int c0 = (int)(idx - t * nvec) * 8;
+struct Row8 {
+  float f[8];
+  int doc;  // -1: no such token
+};
+
+__device__ __forceinline__ Row8 load_row(const __nv_bfloat16* base, const int* doc, long long t, long long tokens, int channels, int c0) {
+  Row8 r;
+  if (t >= 0 && t < tokens) {
+    unpack8(*reinterpret_cast<const bf16x8*>(base + t * channels + c0), r.f);
+    r.doc = doc ? doc[t] : 0;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r.f[i] = 0.f;
+    r.doc = -1;
+  }
+  return r;
+}
+
+// One thread owns 8 adjacent channels (their taps live in registers) and walks a segment of tokens, keeping the previous
+// W - 1 rows in registers so that every row of x is read once.
+// BACKWARD false: out = act(conv(x)).  BACKWARD true: out = dpre = dout * act'(conv(x)), and the segment's contribution to the
+// weight / bias gradient goes to partial[segment, channel, 0..W-1 | W].
+template <int W, bool BACKWARD>
+__global__ void __launch_bounds__(kConvThreads) conv1d_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                                                              const float* __restrict__ bias, const int* __restrict__ doc,
+                                                              const __nv_bfloat16* __restrict__ dout, __nv_bfloat16* __restrict__ out,
+                                                              float* __restrict__ partial, long long tokens, int channels, int act, int segment) {
+  const int vec = blockIdx.x * kConvThreads + threadIdx.x;
+  if (vec >= (channels >> 3)) return;
+  const int c0 = vec * 8;
+  float taps[W][8], offset[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    offset[i] = bias ? bias[c0 + i] : 0.f;
+#pragma unroll
+    for (int j = 0; j < W; ++j) taps[j][i] = w[(c0 + i) * W + j];
+  }
+  const long long t0 = (long long)blockIdx.y * segment, t1 = min(t0 + segment, tokens);
+  constexpr int H = W > 1 ? W - 1 : 1;
+  Row8 hist[H];  // hist[k] = row t - (W - 1) + k
+#pragma unroll
+  for (int k = 0; k < W - 1; ++k) hist[k] = load_row(x, doc, t0 - (W - 1) + k, tokens, channels, c0);
+  float sums[W + 1][8];
+  if (BACKWARD) {
+#pragma unroll
+    for (int j = 0; j <= W; ++j)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sums[j][i] = 0.f;
+  }
+#pragma unroll 4
+  for (long long t = t0; t < t1; ++t) {
+    const Row8 row = load_row(x, doc, t, tokens, channels, c0);
+    float pre[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) pre[i] = offset[i] + taps[W - 1][i] * row.f[i];
+#pragma unroll
+    for (int k = 0; k < W - 1; ++k) {
+      const float same = hist[k].doc == row.doc ? 1.f : 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) pre[i] += same * taps[k][i] * hist[k].f[i];
+    }
+    if (!BACKWARD) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) pre[i] = act_fwd(pre[i], act);
+      *reinterpret_cast<bf16x8*>(out + t * channels + c0) = pack8(pre);
+    } else {
+      float g[8];
+      unpack8(*reinterpret_cast<const bf16x8*>(dout + t * channels + c0), g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        g[i] *= act_grad(pre[i], act);
+        sums[W][i] += g[i];
+        sums[W - 1][i] += g[i] * row.f[i];
+      }
+#pragma unroll
+      for (int k = 0; k < W - 1; ++k) {
+        const float same = hist[k].doc == row.doc ? 1.f : 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sums[k][i] += same * g[i] * hist[k].f[i];
+      }
+      *reinterpret_cast<bf16x8*>(out + t * channels + c0) = pack8(g);
+    }
+#pragma unroll
+    for (int k = 0; k + 1 < W - 1; ++k) hist[k] = hist[k + 1];
+    if (W > 1) hist[H - 1] = row;
+  }
+  if (BACKWARD) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j <= W; ++j) partial[((long long)blockIdx.y * channels + c0 + i) * (W + 1) + j] = sums[j][i];
+  }
+}
+
+// dx[t] = sum_j w[j] dpre[t + (W - 1 - j)] over the tokens of the same document; the next W - 1 rows are kept in registers.
+template <int W>
+__global__ void __launch_bounds__(kConvThreads) conv1d_dx_kernel(const __nv_bfloat16* __restrict__ dpre, const float* __restrict__ w,
+                                                                 const int* __restrict__ doc, __nv_bfloat16* __restrict__ dx, long long tokens,
+                                                                 int channels, int segment) {
+  const int vec = blockIdx.x * kConvThreads + threadIdx.x;
+  if (vec >= (channels >> 3)) return;
+  const int c0 = vec * 8;
+  float taps[W][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < W; ++j) taps[j][i] = w[(c0 + i) * W + j];
+  const long long t0 = (long long)blockIdx.y * segment, t1 = min(t0 + segment, tokens);
+  constexpr int H = W > 1 ? W - 1 : 1;
+  Row8 current = load_row(dpre, doc, t0, tokens, channels, c0);
+  Row8 next[H];  // next[k] = row t + 1 + k
+#pragma unroll
+  for (int k = 0; k < W - 1; ++k) next[k] = load_row(dpre, doc, t0 + 1 + k, tokens, channels, c0);
+#pragma unroll 4
+  for (long long t = t0; t < t1; ++t) {
     float acc[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = bias ? bias[c0 + i] : 0.f;
-    const int my_doc = doc ? doc[t] : 0;
-    for (int j = 0; j < width; ++j) {
-      const long long s = t - (width - 1 - j);
-      if (s < 0 || (doc && doc[s] != my_doc)) continue;
-      float f[8];
-      unpack8(*reinterpret_cast<const bf16x8*>(x + s * channels + c0), f);
+    for (int i = 0; i < 8; ++i) acc[i] = taps[W - 1][i] * current.f[i];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] += f[i] * w[(c0 + i) * width + j];
-    }
+    for (int k = 0; k < W - 1; ++k) {
+      const float same = next[k].doc == current.doc ? 1.f : 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = act_fwd(acc[i], act);
-    *reinterpret_cast<bf16x8*>(out + t * channels + c0) = pack8(acc);
-  }
-}
-
-// dpre[t] = dout[t] * act'(pre[t]) is recomputed where needed.  dx[t] = sum_j w[j] dpre[t + (width - 1 - j)].
-__device__ __forceinline__ void conv_pre(const __nv_bfloat16* x, const float* w, const float* bias, const int* doc, long long t, int c0,
-                                         int channels, int width, float* pre) {
-#pragma unroll
-  for (int i = 0; i < 8; ++i) pre[i] = bias ? bias[c0 + i] : 0.f;
-  const int my_doc = doc ? doc[t] : 0;
-  for (int j = 0; j < width; ++j) {
-    const long long s = t - (width - 1 - j);
-    if (s < 0 || (doc && doc[s] != my_doc)) continue;
-    float f[8];
-    unpack8(*reinterpret_cast<const bf16x8*>(x + s * channels + c0), f);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) pre[i] += f[i] * w[(c0 + i) * width + j];
-  }
-}
-
-__global__ void conv1d_dpre_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
-                                   const int* __restrict__ doc, const __nv_bfloat16* __restrict__ dout, __nv_bfloat16* __restrict__ dpre,
-                                   long long tokens, int channels, int width, int act) {
-  const int nvec = channels >> 3;
-  const long long total = tokens * nvec;
-  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
-    const long long t = idx / nvec;
-    const int c0 = (int)(idx - t * nvec) * 8;
-    float pre[8], g[8];
-    conv_pre(x, w, bias, doc, t, c0, channels, width, pre);
-    unpack8(*reinterpret_cast<const bf16x8*>(dout + t * channels + c0), g);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) g[i] *= act_grad(pre[i], act);
-    *reinterpret_cast<bf16x8*>(dpre + t * channels + c0) = pack8(g);
-  }
-}
-
-__global__ void conv1d_dx_kernel(const __nv_bfloat16* __restrict__ dpre, const float* __restrict__ w, const int* __restrict__ doc,
-                                 __nv_bfloat16* __restrict__ dx, long long tokens, int channels, int width) {
-  const int nvec = channels >> 3;
-  const long long total = tokens * nvec;
-  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
-    const long long t = idx / nvec;
-    const int c0 = (int)(idx - t * nvec) * 8;
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    const int my_doc = doc ? doc[t] : 0;
-    for (int j = 0; j < width; ++j) {
-      const long long s = t + (width - 1 - j);
-      if (s >= tokens || (doc && doc[s] != my_doc)) continue;
-      float g[8];
-      unpack8(*reinterpret_cast<const bf16x8*>(dpre + s * channels + c0), g);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] += g[i] * w[(c0 + i) * width + j];
+      for (int i = 0; i < 8; ++i) acc[i] += same * taps[W - 2 - k][i] * next[k].f[i];
     }
     *reinterpret_cast<bf16x8*>(dx + t * channels + c0) = pack8(acc);
-  }
-}
-
-// partial[block, c, j] = sum over the block's tokens of dpre[t, c] x[t - (width-1-j), c]; partial[block, c, width] = sum dpre.
-// grid (token blocks, channel blocks of 128); thread = channel; deterministic (the host sums the blocks in order).
-__global__ void conv1d_dw_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dpre, const int* __restrict__ doc,
-                                 float* __restrict__ partial, long long tokens, int channels, int width, int tokens_per_block) {
-  const int c = blockIdx.y * blockDim.x + threadIdx.x;
-  if (c >= channels) return;
-  const long long t0 = (long long)blockIdx.x * tokens_per_block;
-  const long long t1 = min(t0 + tokens_per_block, tokens);
-  float acc[kMaxWidth + 1];
+    if (W > 1) {
+      current = next[0];
 #pragma unroll
-  for (int j = 0; j <= kMaxWidth; ++j) acc[j] = 0.f;
-  for (long long t = t0; t < t1; ++t) {
-    const float g = bf2f(dpre[t * channels + c]);
-    acc[kMaxWidth] += g;
-    const int my_doc = doc ? doc[t] : 0;
-#pragma unroll
-    for (int j = 0; j < kMaxWidth; ++j) {
-      if (j >= width) break;
-      const long long s = t - (width - 1 - j);
-      if (s < 0 || (doc && doc[s] != my_doc)) continue;
-      acc[j] += g * bf2f(x[s * channels + c]);
+      for (int k = 0; k + 1 < W - 1; ++k) next[k] = next[k + 1];
+      next[H - 1] = load_row(dpre, doc, t + W, tokens, channels, c0);
+    } else {
+      current = load_row(dpre, doc, t + 1, tokens, channels, c0);
     }
   }
-  float* dst = partial + ((long long)blockIdx.x * channels + c) * (width + 1);
-  for (int j = 0; j < width; ++j) dst[j] = acc[j];
-  dst[width] = acc[kMaxWidth];
 }
 
-int grid_1d(long long items, int threads) {
-  long long blocks = (items + threads - 1) / threads;
-  return (int)(blocks > 148ll * 16 ? 148ll * 16 : (blocks < 1 ? 1 : blocks));
+constexpr int kConvSegment = 32;  // tokens per thread in the forward and dx kernels
+
+template <int W>
+int conv_forward(const __nv_bfloat16* x, const float* w, const float* bias, const int* doc, __nv_bfloat16* out, long long tokens, int channels, int act,
+                 cudaStream_t stream) {
+  dim3 grid((unsigned)(((channels >> 3) + kConvThreads - 1) / kConvThreads), (unsigned)((tokens + kConvSegment - 1) / kConvSegment));
+  conv1d_kernel<W, false><<<grid, kConvThreads, 0, stream>>>(x, w, bias, doc, nullptr, out, nullptr, tokens, channels, act, kConvSegment);
+  FLB_CHECK_LAUNCH();
+  return FLB_OK;
 }
+
+template <int W>
+int conv_backward(const __nv_bfloat16* x, const float* w, const float* bias, const int* doc, const __nv_bfloat16* dout, __nv_bfloat16* dpre,
+                  __nv_bfloat16* dx, float* partial, long long tokens, int channels, int act, int tokens_per_block, cudaStream_t stream) {
+  const unsigned vec_blocks = (unsigned)(((channels >> 3) + kConvThreads - 1) / kConvThreads);
+  dim3 grid(vec_blocks, (unsigned)((tokens + tokens_per_block - 1) / tokens_per_block));
+  conv1d_kernel<W, true><<<grid, kConvThreads, 0, stream>>>(x, w, bias, doc, dout, dpre, partial, tokens, channels, act, tokens_per_block);
+  FLB_CHECK_LAUNCH();
+  dim3 dx_grid(vec_blocks, (unsigned)((tokens + kConvSegment - 1) / kConvSegment));
+  conv1d_dx_kernel<W><<<dx_grid, kConvThreads, 0, stream>>>(dpre, w, doc, dx, tokens, channels, kConvSegment);
+  FLB_CHECK_LAUNCH();
+  return FLB_OK;
+}
+
+#define FLB_CONV_WIDTHS(CALL) \
+  switch (width) {            \
+    case 1: return CALL(1);   \
+    case 2: return CALL(2);   \
+    case 3: return CALL(3);   \
+    case 4: return CALL(4);   \
+    case 5: return CALL(5);   \
+    case 6: return CALL(6);   \
+    case 7: return CALL(7);   \
+    default: return CALL(8);  \
+  }
 }  // namespace
 
-// x, out: [tokens, channels] bf16; w: [channels, width] fp32; bias: [channels] fp32 or null; doc: [tokens] int32 or null.
+// x, out: [tokens, channels] bf16; w: [channels, width] fp32; bias: [channels] fp32 or null; doc: [tokens] int32 (>= 0) or null.
 FLB_API int flb_causal_conv1d_fwd(const void* x, const float* w, const float* bias, const int* doc, void* out, long long tokens, int channels,
                                   int width, int act, cudaStream_t stream) {
   if (channels % 8 || width <= 0 || width > kMaxWidth || tokens < 0) return FLB_ERR_SHAPE;
   if (tokens == 0) return FLB_OK;
-  conv1d_fwd_kernel<<<grid_1d(tokens * (channels / 8), 256), 256, 0, stream>>>((const __nv_bfloat16*)x, w, bias, doc, (__nv_bfloat16*)out, tokens,
-                                                                                channels, width, act);
-  FLB_CHECK_LAUNCH();
-  return FLB_OK;
+#define FLB_CONV_FWD(W) conv_forward<W>((const __nv_bfloat16*)x, w, bias, doc, (__nv_bfloat16*)out, tokens, channels, act, stream)
+  FLB_CONV_WIDTHS(FLB_CONV_FWD)
+#undef FLB_CONV_FWD
 }
 
 FLB_API int flb_causal_conv1d_partial_blocks(long long tokens, int tokens_per_block) { return (int)((tokens + tokens_per_block - 1) / tokens_per_block); }
@@ -156,25 +217,23 @@ FLB_API int flb_causal_conv1d_bwd(const void* x, const float* w, const float* bi
                                   float* partial, long long tokens, int channels, int width, int act, int tokens_per_block, cudaStream_t stream) {
   if (channels % 8 || width <= 0 || width > kMaxWidth || tokens < 0 || tokens_per_block <= 0) return FLB_ERR_SHAPE;
   if (tokens == 0) return FLB_OK;
-  const int grid = grid_1d(tokens * (channels / 8), 256);
-  conv1d_dpre_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, w, bias, doc, (const __nv_bfloat16*)dout, (__nv_bfloat16*)dpre, tokens,
-                                               channels, width, act);
-  FLB_CHECK_LAUNCH();
-  conv1d_dx_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)dpre, w, doc, (__nv_bfloat16*)dx, tokens, channels, width);
-  FLB_CHECK_LAUNCH();
-  dim3 dw_grid((unsigned)((tokens + tokens_per_block - 1) / tokens_per_block), (unsigned)((channels + 127) / 128));
-  conv1d_dw_kernel<<<dw_grid, 128, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dpre, doc, partial, tokens, channels, width,
-                                                tokens_per_block);
-  FLB_CHECK_LAUNCH();
-  return FLB_OK;
+#define FLB_CONV_BWD(W)                                                                                                                     \
+  conv_backward<W>((const __nv_bfloat16*)x, w, bias, doc, (const __nv_bfloat16*)dout, (__nv_bfloat16*)dpre, (__nv_bfloat16*)dx, partial, tokens, \
+                   channels, act, tokens_per_block, stream)
+  FLB_CONV_WIDTHS(FLB_CONV_BWD)
+#undef FLB_CONV_BWD
 }
 
 // ----------------------------------------------------------------------------------------------------------------------
 // selective scan
 // ----------------------------------------------------------------------------------------------------------------------
 namespace {
-constexpr int kScanThreads = 128;
-constexpr int kChunk = 64;  // tokens per chunk (also the number of states a thread keeps in registers in the backward)
+constexpr int kScanThreads = 128;  // channels per block
+constexpr int kChunk = 64;         // tokens per chunk
+constexpr float kLog2e = 1.4426950408889634f;
+
+// Tokens per backward sub-chunk: the thread keeps sub x state values of recomputed states in registers.
+__host__ __device__ constexpr int scan_sub(int state) { return state >= 8 ? 64 / state : 8; }
 
 struct ScanArgs {
   const __nv_bfloat16* x;       // [T, D]
@@ -187,87 +246,201 @@ struct ScanArgs {
   const float* dt_bias;         // [D] or null
   const unsigned char* start;   // [T] 1 where a document starts, or null
   long long tokens;
-  int channels, state, groups_b, groups_c, chunks;
+  int channels, groups_b, groups_c, chunks;
 };
 
-__device__ __forceinline__ float softplus(float v) { return v > 20.f ? v : log1pf(__expf(v)); }
+// log(1 + e^v); below -15 the sum rounds to 1 and the series' first term e^v is exact to fp32.
+__device__ __forceinline__ float softplus(float v) {
+  const float e = __expf(v);
+  return v > 20.f ? v : (v < -15.f ? e : __logf(1.f + e));
+}
 __device__ __forceinline__ float sigmoidf(float v) { return 1.f / (1.f + __expf(-v)); }
 
-struct Lane {
-  int d, n, gb, gc;
+template <int N>
+__device__ __forceinline__ void load_state_vec(const __nv_bfloat16* p, float (&out)[N]) {
+  if constexpr (N >= 8) {
+#pragma unroll
+    for (int k = 0; k < N / 8; ++k) unpack8(*reinterpret_cast<const bf16x8*>(p + 8 * k), out + 8 * k);
+  } else {
+#pragma unroll
+    for (int k = 0; k < N / 2; ++k) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p + 2 * k));
+      out[2 * k] = f.x;
+      out[2 * k + 1] = f.y;
+    }
+  }
+}
+
+// Per-thread constants of one channel.  Threads past the last channel work on channel 0 and never store.
+template <int N>
+struct Channel {
+  int d;
   bool valid;
+  float a[N], a2[N];  // a and a * log2(e)
+  float bias, skip;
+  const __nv_bfloat16 *b, *c;  // this channel's group inside a token's B / C row
+  long long b_stride, c_stride;
+  __device__ __forceinline__ Channel(const ScanArgs& p) {
+    const int raw = blockIdx.x * kScanThreads + threadIdx.x;
+    valid = raw < p.channels;
+    d = valid ? raw : 0;
+#pragma unroll
+    for (int n = 0; n < N; ++n) {
+      a[n] = p.a[(long long)d * N + n];
+      a2[n] = a[n] * kLog2e;
+    }
+    bias = p.dt_bias ? p.dt_bias[d] : 0.f;
+    skip = p.skip[d];
+    b = p.b + (d / (p.channels / p.groups_b)) * N;
+    c = p.c + (d / (p.channels / p.groups_c)) * N;
+    b_stride = (long long)p.groups_b * N;
+    c_stride = (long long)p.groups_c * N;
+  }
 };
-__device__ __forceinline__ Lane lane_of(const ScanArgs& p) {
-  Lane l;
-  const int per_block = kScanThreads / p.state;
-  l.n = threadIdx.x % p.state;
-  l.d = blockIdx.x * per_block + threadIdx.x / p.state;
-  l.valid = l.d < p.channels;
-  const int dd = l.valid ? l.d : 0;
-  l.gb = dd / (p.channels / p.groups_b);
-  l.gc = dd / (p.channels / p.groups_c);
-  l.d = dd;
-  return l;
+
+// Scratch layouts: [chunk or checkpoint][state index][channel], so the block's accesses are coalesced.
+__device__ __forceinline__ long long scratch_index(long long slot, int n, int states, int channels, int d) {
+  return (slot * states + n) * channels + d;
 }
 
-// Phase 1: scan the chunk from a zero state; chunk_state[chunk, d, n] = end state, chunk_decay[chunk, d, n] = product of decays.
-__global__ void scan_chunk_summary_kernel(const ScanArgs p, float* __restrict__ chunk_state, float* __restrict__ chunk_decay) {
-  const Lane l = lane_of(p);
+// Phase 1: scan the chunk from a zero state -> its end state and the product of its decays.
+template <int N>
+__global__ void __launch_bounds__(kScanThreads, N <= 16 ? 8 : 2) scan_summary_kernel(const ScanArgs p, float* __restrict__ chunk_state, float* __restrict__ chunk_decay) {
+  const Channel<N> ch(p);
+  if (!ch.valid) return;
   const int chunk = blockIdx.y;
-  const long long t0 = (long long)chunk * kChunk, t1 = min(t0 + kChunk, p.tokens);
-  const float a = p.a[l.d * p.state + l.n];
-  const float bias = p.dt_bias ? p.dt_bias[l.d] : 0.f;
-  float h = 0.f, decay = 1.f;
-  for (long long t = t0; t < t1; ++t) {
-    const float dt = softplus(bf2f(p.dt[t * p.channels + l.d]) + bias);
-    const float da = (p.start && p.start[t]) ? 0.f : __expf(dt * a);
-    const float write = dt * bf2f(p.x[t * p.channels + l.d]) * bf2f(p.b[(t * p.groups_b + l.gb) * p.state + l.n]);
-    h = da * h + write;
-    decay *= da;
+  const long long t0 = (long long)chunk * kChunk;
+  const int len = (int)min((long long)kChunk, p.tokens - t0);
+  const __nv_bfloat16* xp = p.x + t0 * p.channels + ch.d;
+  const __nv_bfloat16* dtp = p.dt + t0 * p.channels + ch.d;
+  const __nv_bfloat16* bp = ch.b + t0 * ch.b_stride;
+  const unsigned char* sp = p.start ? p.start + t0 : nullptr;
+  float h[N];
+#pragma unroll
+  for (int n = 0; n < N; ++n) h[n] = 0.f;
+  float dt_sum = 0.f;
+  bool cut = false;
+  float x_next = bf2f(*xp), dt_next = bf2f(*dtp);  // one token ahead: these two come from DRAM, B rows are shared and L1-hot
+  for (int i = 0; i < len; ++i) {
+    const float dtv = softplus(dt_next + ch.bias);
+    const float w = dtv * x_next;
+    if (i + 1 < len) {
+      xp += p.channels;
+      dtp += p.channels;
+      x_next = bf2f(*xp);
+      dt_next = bf2f(*dtp);
+    }
+    float bv[N];
+    load_state_vec<N>(bp, bv);
+    bp += ch.b_stride;
+    dt_sum += dtv;
+    if (sp && sp[i]) {  // uniform over the grid's x dimension
+      cut = true;
+#pragma unroll
+      for (int n = 0; n < N; ++n) h[n] = w * bv[n];
+    } else {
+#pragma unroll
+      for (int n = 0; n < N; ++n) h[n] = fmaf(h[n], exp2f(dtv * ch.a2[n]), w * bv[n]);
+    }
   }
-  if (l.valid) {
-    const long long idx = ((long long)chunk * p.channels + l.d) * p.state + l.n;
-    chunk_state[idx] = h;
-    chunk_decay[idx] = decay;
+#pragma unroll
+  for (int n = 0; n < N; ++n) {
+    const long long idx = scratch_index(chunk, n, N, p.channels, ch.d);
+    chunk_state[idx] = h[n];
+    chunk_decay[idx] = cut ? 0.f : exp2f(dt_sum * ch.a2[n]);
   }
 }
 
-// Phase 2: chain the summaries in order.  chunk_state is overwritten by the state at the START of every chunk.
-__global__ void scan_chain_kernel(float* __restrict__ chunk_state, const float* __restrict__ chunk_decay, int chunks, long long per_chunk) {
+// Phase 2: chain the summaries in order (REVERSE: from the last chunk back, for the adjoint).  `carried` is overwritten by
+// the value ENTERING every chunk: the state at its start, or the adjoint of the state at its end.
+template <bool REVERSE>
+__global__ void scan_chain_kernel(float* __restrict__ carried, const float* __restrict__ chunk_decay, int chunks, long long per_chunk) {
   const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (i >= per_chunk) return;
-  float h = 0.f;
-  for (int c = 0; c < chunks; ++c) {
-    const long long idx = c * per_chunk + i;
-    const float end = chunk_decay[idx] * h + chunk_state[idx];
-    chunk_state[idx] = h;
-    h = end;
+  constexpr int kBatch = 16;  // loads of a batch are in flight together; only the multiply-adds are serial
+  float value = 0.f;
+  for (int c0 = 0; c0 < chunks; c0 += kBatch) {
+    float decay[kBatch], own[kBatch];
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) {
+      const int c = REVERSE ? chunks - 1 - (c0 + k) : c0 + k;
+      const bool live = c0 + k < chunks;
+      decay[k] = live ? chunk_decay[c * per_chunk + i] : 0.f;
+      own[k] = live ? carried[c * per_chunk + i] : 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) {
+      if (c0 + k < chunks) {
+        const int c = REVERSE ? chunks - 1 - (c0 + k) : c0 + k;
+        carried[c * per_chunk + i] = value;
+        value = fmaf(decay[k], value, own[k]);
+      }
+    }
   }
 }
 
-// Phase 3: re-scan from the true start state and emit y.
-__global__ void scan_output_kernel(const ScanArgs p, const float* __restrict__ chunk_start, __nv_bfloat16* __restrict__ y) {
-  const Lane l = lane_of(p);
+// Phase 3: re-scan from the true start state.  CHECKPOINT false: emit y.  CHECKPOINT true: write the state before every
+// scan_sub(N)-th token instead (the backward pass recomputes from those).
+template <int N, bool CHECKPOINT>
+__global__ void __launch_bounds__(kScanThreads, N <= 16 ? 8 : 2) scan_output_kernel(const ScanArgs p, const float* __restrict__ chunk_start, __nv_bfloat16* __restrict__ y,
+                                                                     float* __restrict__ checkpoints) {
+  constexpr int SUB = scan_sub(N);
+  const Channel<N> ch(p);
+  if (!ch.valid) return;
   const int chunk = blockIdx.y;
-  const long long t0 = (long long)chunk * kChunk, t1 = min(t0 + kChunk, p.tokens);
-  const float a = p.a[l.d * p.state + l.n];
-  const float bias = p.dt_bias ? p.dt_bias[l.d] : 0.f;
-  const float skip = p.skip[l.d];
-  float h = chunk_start[((long long)chunk * p.channels + l.d) * p.state + l.n];
-  for (long long t = t0; t < t1; ++t) {
-    const float dt = softplus(bf2f(p.dt[t * p.channels + l.d]) + bias);
-    const float xv = bf2f(p.x[t * p.channels + l.d]);
-    const float da = (p.start && p.start[t]) ? 0.f : __expf(dt * a);
-    h = da * h + dt * xv * bf2f(p.b[(t * p.groups_b + l.gb) * p.state + l.n]);
-    float acc = h * bf2f(p.c[(t * p.groups_c + l.gc) * p.state + l.n]);
-    for (int o = p.state >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (l.n == 0 && l.valid) {
-      float out = acc + skip * xv;
-      if (p.z) {
-        const float zv = bf2f(p.z[t * p.channels + l.d]);
-        out *= zv * sigmoidf(zv);
+  const long long t0 = (long long)chunk * kChunk;
+  const int len = (int)min((long long)kChunk, p.tokens - t0);
+  const __nv_bfloat16* xp = p.x + t0 * p.channels + ch.d;
+  const __nv_bfloat16* dtp = p.dt + t0 * p.channels + ch.d;
+  const __nv_bfloat16* zp = p.z ? p.z + t0 * p.channels + ch.d : nullptr;
+  const __nv_bfloat16* bp = ch.b + t0 * ch.b_stride;
+  const __nv_bfloat16* cp = ch.c + t0 * ch.c_stride;
+  const unsigned char* sp = p.start ? p.start + t0 : nullptr;
+  __nv_bfloat16* yp = CHECKPOINT ? nullptr : y + t0 * p.channels + ch.d;
+  float* kp = CHECKPOINT ? checkpoints + scratch_index(t0 / SUB, 0, N, p.channels, ch.d) : nullptr;
+  float h[N];
+#pragma unroll
+  for (int n = 0; n < N; ++n) h[n] = chunk_start[scratch_index(chunk, n, N, p.channels, ch.d)];
+  float x_next = bf2f(*xp), dt_next = bf2f(*dtp), z_next = (!CHECKPOINT && zp) ? bf2f(*zp) : 0.f;
+  for (int i = 0; i < len; ++i) {
+    if (CHECKPOINT && i % SUB == 0) {
+#pragma unroll
+      for (int n = 0; n < N; ++n) kp[(long long)n * p.channels] = h[n];
+      kp += (long long)N * p.channels;
+    }
+    const float dtv = softplus(dt_next + ch.bias);
+    const float xv = x_next, zv = z_next;
+    const float w = dtv * xv;
+    if (i + 1 < len) {
+      xp += p.channels;
+      dtp += p.channels;
+      x_next = bf2f(*xp);
+      dt_next = bf2f(*dtp);
+      if (!CHECKPOINT && zp) {
+        zp += p.channels;
+        z_next = bf2f(*zp);
       }
-      y[t * p.channels + l.d] = f2bf(out);
+    }
+    float bv[N];
+    load_state_vec<N>(bp, bv);
+    bp += ch.b_stride;
+    if (sp && sp[i]) {
+#pragma unroll
+      for (int n = 0; n < N; ++n) h[n] = w * bv[n];
+    } else {
+#pragma unroll
+      for (int n = 0; n < N; ++n) h[n] = fmaf(h[n], exp2f(dtv * ch.a2[n]), w * bv[n]);
+    }
+    if (!CHECKPOINT) {
+      float cv[N];
+      load_state_vec<N>(cp, cv);
+      cp += ch.c_stride;
+      float out = ch.skip * xv;
+#pragma unroll
+      for (int n = 0; n < N; ++n) out = fmaf(h[n], cv[n], out);
+      if (p.z) out *= zv * sigmoidf(zv);
+      *yp = f2bf(out);
+      yp += p.channels;
     }
   }
 }
@@ -277,182 +450,291 @@ struct ScanGrads {
   __nv_bfloat16* dx;        // [T, D]
   __nv_bfloat16* ddt;       // [T, D]
   __nv_bfloat16* dz;        // [T, D] or null
-  float* db;                // [T, Gb, N] fp32, zero-initialised (atomic adds)
+  float* db;                // [T, Gb, N] fp32, zero-initialised
   float* dc;                // [T, Gc, N] fp32, zero-initialised
-  float* da_partial;        // [chunks, D, N]
+  float* da_partial;        // [chunks, N, D]
   float* dskip_partial;     // [chunks, D]
   float* dbias_partial;     // [chunks, D]
 };
 
 // Backward phase 1: adjoint reaching the start of the chunk when nothing flows in from later chunks.
-__global__ void scan_bwd_summary_kernel(const ScanArgs p, const ScanGrads g, float* __restrict__ chunk_adjoint) {
-  const Lane l = lane_of(p);
+template <int N>
+__global__ void __launch_bounds__(kScanThreads, N <= 16 ? 8 : 2) scan_bwd_summary_kernel(const ScanArgs p, const __nv_bfloat16* __restrict__ dy, float* __restrict__ chunk_adjoint) {
+  const Channel<N> ch(p);
+  if (!ch.valid) return;
   const int chunk = blockIdx.y;
-  const long long t0 = (long long)chunk * kChunk, t1 = min(t0 + kChunk, p.tokens);
-  const float a = p.a[l.d * p.state + l.n];
-  const float bias = p.dt_bias ? p.dt_bias[l.d] : 0.f;
-  float adj = 0.f;
-  for (long long t = t1 - 1; t >= t0; --t) {
-    float gy = bf2f(g.dy[t * p.channels + l.d]);
-    if (p.z) {
-      const float zv = bf2f(p.z[t * p.channels + l.d]);
-      gy *= zv * sigmoidf(zv);
-    }
-    adj += gy * bf2f(p.c[(t * p.groups_c + l.gc) * p.state + l.n]);
-    const float dt = softplus(bf2f(p.dt[t * p.channels + l.d]) + bias);
-    adj *= (p.start && p.start[t]) ? 0.f : __expf(dt * a);  // adjoint of the state BEFORE token t
-  }
-  if (l.valid) chunk_adjoint[((long long)chunk * p.channels + l.d) * p.state + l.n] = adj;
-}
-
-// Backward phase 2: chunk_adjoint becomes the adjoint of the state at the END of every chunk (what later chunks send back).
-__global__ void scan_bwd_chain_kernel(float* __restrict__ chunk_adjoint, const float* __restrict__ chunk_decay, int chunks, long long per_chunk) {
-  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-  if (i >= per_chunk) return;
-  float incoming = 0.f;  // adjoint of the end state of the chunk being visited
-  for (int c = chunks - 1; c >= 0; --c) {
-    const long long idx = c * per_chunk + i;
-    const float at_start = chunk_adjoint[idx] + chunk_decay[idx] * incoming;
-    chunk_adjoint[idx] = incoming;
-    incoming = at_start;
-  }
-}
-
-// Backward phase 3: recompute the chunk's states from its start state, then walk back.
-__global__ void scan_bwd_kernel(const ScanArgs p, const ScanGrads g, const float* __restrict__ chunk_start, const float* __restrict__ chunk_adjoint) {
-  const Lane l = lane_of(p);
-  const int chunk = blockIdx.y;
-  const long long t0 = (long long)chunk * kChunk, t1 = min(t0 + kChunk, p.tokens);
-  const int len = (int)(t1 - t0);
-  const float a = p.a[l.d * p.state + l.n];
-  const float bias = p.dt_bias ? p.dt_bias[l.d] : 0.f;
-  const float skip = p.skip[l.d];
-  const long long sidx = ((long long)chunk * p.channels + l.d) * p.state + l.n;
-  float states[kChunk + 1];  // states[i] = state before token t0 + i
-  states[0] = chunk_start[sidx];
+  const long long t0 = (long long)chunk * kChunk;
+  const int len = (int)min((long long)kChunk, p.tokens - t0);
+  const long long last = (t0 + len - 1) * p.channels + ch.d;
+  const __nv_bfloat16* dyp = dy + last;
+  const __nv_bfloat16* dtp = p.dt + last;
+  const __nv_bfloat16* zp = p.z ? p.z + last : nullptr;
+  const __nv_bfloat16* cp = ch.c + (t0 + len - 1) * ch.c_stride;
+  const unsigned char* sp = p.start ? p.start + t0 : nullptr;
+  float adj[N];
 #pragma unroll
-  for (int i = 0; i < kChunk; ++i) {
-    if (i < len) {
-      const long long t = t0 + i;
-      const float dt = softplus(bf2f(p.dt[t * p.channels + l.d]) + bias);
-      const float da = (p.start && p.start[t]) ? 0.f : __expf(dt * a);
-      states[i + 1] = da * states[i] + dt * bf2f(p.x[t * p.channels + l.d]) * bf2f(p.b[(t * p.groups_b + l.gb) * p.state + l.n]);
+  for (int n = 0; n < N; ++n) adj[n] = 0.f;
+  float dy_next = bf2f(*dyp), dt_next = bf2f(*dtp), z_next = zp ? bf2f(*zp) : 0.f;
+  for (int i = len - 1; i >= 0; --i) {
+    float gy = dy_next;
+    if (zp) gy *= z_next * sigmoidf(z_next);
+    const float dtv = softplus(dt_next + ch.bias);
+    if (i > 0) {
+      dyp -= p.channels;
+      dtp -= p.channels;
+      dy_next = bf2f(*dyp);
+      dt_next = bf2f(*dtp);
+      if (zp) {
+        zp -= p.channels;
+        z_next = bf2f(*zp);
+      }
+    }
+    if (sp && sp[i]) {  // nothing flows across a document start
+#pragma unroll
+      for (int n = 0; n < N; ++n) adj[n] = 0.f;
     } else {
-      states[i + 1] = states[i];
-    }
-  }
-  float adj = chunk_adjoint[sidx];  // adjoint of the state after the chunk's last token
-  float grad_a = 0.f, grad_skip = 0.f, grad_bias = 0.f;
+      float cv[N];
+      load_state_vec<N>(cp, cv);
 #pragma unroll
-  for (int i = kChunk - 1; i >= 0; --i) {
-    if (i >= len) continue;
-    const long long t = t0 + i;
-    const long long td = t * p.channels + l.d;
-    const float raw = bf2f(p.dt[td]) + bias;
-    const float dt = softplus(raw);
-    const float xv = bf2f(p.x[td]);
-    const float bv = bf2f(p.b[(t * p.groups_b + l.gb) * p.state + l.n]);
-    const float cv = bf2f(p.c[(t * p.groups_c + l.gc) * p.state + l.n]);
-    const bool is_start = p.start && p.start[t];
-    const float da = is_start ? 0.f : __expf(dt * a);
-    float gy = bf2f(g.dy[td]);
-    float zv = 0.f, gate = 1.f;
-    if (p.z) {
-      zv = bf2f(p.z[td]);
-      gate = zv * sigmoidf(zv);
+      for (int n = 0; n < N; ++n) adj[n] = fmaf(gy, cv[n], adj[n]) * exp2f(dtv * ch.a2[n]);  // adjoint of the state BEFORE token t
     }
-    const float gyraw = gy * gate;
-    // y_raw = <c, h_t> + skip x
-    float dot = states[i + 1] * cv;
-    for (int o = p.state >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    adj += gyraw * cv;                       // adjoint of h_t
-    const float grad_c = gyraw * states[i + 1];
-    // h_t = da h_{t-1} + dt x b
-    const float grad_da = adj * states[i];   // zero decay at a document start carries no gradient (da is a constant 0 there)
-    const float grad_write = adj;
-    float grad_dt = (is_start ? 0.f : grad_da * da * a) + grad_write * xv * bv;
-    float grad_x = grad_write * dt * bv;
-    const float grad_b = grad_write * dt * xv;
-    grad_a += is_start ? 0.f : grad_da * da * dt;
-    adj *= da;                               // adjoint of h_{t-1}
-    for (int o = p.state >> 1; o > 0; o >>= 1) {
-      grad_dt += __shfl_xor_sync(0xffffffffu, grad_dt, o);
-      grad_x += __shfl_xor_sync(0xffffffffu, grad_x, o);
-    }
-    if (l.valid) {
-      atomicAdd(g.db + (t * p.groups_b + l.gb) * p.state + l.n, grad_b);
-      atomicAdd(g.dc + (t * p.groups_c + l.gc) * p.state + l.n, grad_c);
-      if (l.n == 0) {
-        const float yraw = dot + skip * xv;
-        grad_x += gyraw * skip;
-        const float grad_raw = grad_dt * sigmoidf(raw);
-        g.dx[td] = f2bf(grad_x);
-        g.ddt[td] = f2bf(grad_raw);
-        if (g.dz) {
-          const float s = sigmoidf(zv);
-          g.dz[td] = f2bf(gy * yraw * s * (1.f + zv * (1.f - s)));
-        }
-        grad_skip += gyraw * xv;
-        grad_bias += grad_raw;
+    cp -= ch.c_stride;
+  }
+#pragma unroll
+  for (int n = 0; n < N; ++n) chunk_adjoint[scratch_index(chunk, n, N, p.channels, ch.d)] = adj[n];
+}
+
+// Sum the per-channel contributions rows[lane][i * N + n] of this warp's 32 channels into out[token, group, n].  A group
+// that lies wholly inside the warp's channels is stored; one that continues in other warps is added atomically.
+template <int N, int SUB>
+__device__ __forceinline__ void reduce_group_grads(const float* rows, float* __restrict__ out, int groups, int group_size, int channels, int warp_c0,
+                                                   long long token0, int live) {
+  constexpr int ROW = SUB * N + 4;
+  const int lane = threadIdx.x & 31;
+  const int c_end = min(warp_c0 + 32, channels);
+  const int g_hi = (c_end - 1) / group_size;
+  for (int g = warp_c0 / group_size; g <= g_hi; ++g) {
+    const int first = g * group_size, last = first + group_size;
+    const int r0 = max(first, warp_c0) - warp_c0, r1 = min(last, c_end) - warp_c0;
+    const bool whole = first >= warp_c0 && last <= c_end;
+#pragma unroll
+    for (int o = lane; o < SUB * N; o += 32) {
+      const int i = o / N;
+      if (i < live) {
+        float sum = 0.f;
+#pragma unroll 8
+        for (int r = r0; r < r1; ++r) sum += rows[r * ROW + o];
+        float* dst = out + ((token0 + i) * groups + g) * N + (o % N);
+        if (whole) *dst = sum;
+        else atomicAdd(dst, sum);
       }
     }
   }
-  if (l.valid) {
-    g.da_partial[sidx] = grad_a;
-    if (l.n == 0) {
-      g.dskip_partial[(long long)chunk * p.channels + l.d] = grad_skip;
-      g.dbias_partial[(long long)chunk * p.channels + l.d] = grad_bias;
+}
+
+// Backward phase 3: walk the chunk backwards, one sub-chunk of recomputed states at a time.  Warps never wait on one another.
+template <int N>
+__global__ void __launch_bounds__(kScanThreads, N <= 16 ? 3 : 2) scan_bwd_kernel(const ScanArgs p, const ScanGrads g, const float* __restrict__ checkpoints,
+                                                                  const float* __restrict__ chunk_adjoint) {
+  constexpr int SUB = scan_sub(N);
+  constexpr int ROW = SUB * N + 4;  // 16-byte row writes from 8 lanes and column sums both spread over all banks
+  extern __shared__ __align__(16) float scan_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp_c0 = blockIdx.x * kScanThreads + warp * 32;
+  if (warp_c0 >= p.channels) return;
+  float* warp_c = scan_smem + (warp * 2) * 32 * ROW;
+  float* warp_b = warp_c + 32 * ROW;
+  float* rows_c = warp_c + lane * ROW;
+  float* rows_b = warp_b + lane * ROW;
+  const Channel<N> ch(p);
+  const int chunk = blockIdx.y;
+  const long long t0 = (long long)chunk * kChunk;
+  const int len = (int)min((long long)kChunk, p.tokens - t0);
+  float adj[N], grad_a[N];
+#pragma unroll
+  for (int n = 0; n < N; ++n) {
+    adj[n] = chunk_adjoint[scratch_index(chunk, n, N, p.channels, ch.d)];
+    grad_a[n] = 0.f;
+  }
+  float grad_skip = 0.f, grad_bias = 0.f;
+  for (int s = (len + SUB - 1) / SUB - 1; s >= 0; --s) {
+    const long long ts = t0 + (long long)s * SUB;
+    const int live = min(SUB, len - s * SUB);
+    const long long base = ts * p.channels + ch.d;
+    const float* kp = checkpoints + scratch_index(ts / SUB, 0, N, p.channels, ch.d);
+    // every per-channel value of the sub-chunk, loaded up front
+    float raw[SUB], xv[SUB], gy[SUB], zv[SUB];
+#pragma unroll
+    for (int i = 0; i < SUB; ++i) {
+      const bool in = i < live;
+      const long long td = base + (long long)i * p.channels;
+      raw[i] = in ? bf2f(p.dt[td]) + ch.bias : 0.f;
+      xv[i] = in ? bf2f(p.x[td]) : 0.f;
+      gy[i] = in ? bf2f(g.dy[td]) : 0.f;
+      zv[i] = (in && p.z) ? bf2f(p.z[td]) : 0.f;
     }
+    // recompute: after[i][n] = state after token ts + i
+    float after[SUB][N], dtv[SUB];
+    {
+      float h[N];
+#pragma unroll
+      for (int n = 0; n < N; ++n) h[n] = kp[(long long)n * p.channels];
+#pragma unroll
+      for (int i = 0; i < SUB; ++i) {
+        dtv[i] = softplus(raw[i]);
+        if (i < live) {
+          float bv[N];
+          load_state_vec<N>(ch.b + (ts + i) * ch.b_stride, bv);
+          const float w = dtv[i] * xv[i];
+          if (p.start && p.start[ts + i]) {
+#pragma unroll
+            for (int n = 0; n < N; ++n) h[n] = w * bv[n];
+          } else {
+#pragma unroll
+            for (int n = 0; n < N; ++n) h[n] = fmaf(h[n], exp2f(dtv[i] * ch.a2[n]), w * bv[n]);
+          }
+        }
+#pragma unroll
+        for (int n = 0; n < N; ++n) after[i][n] = h[n];
+      }
+    }
+#pragma unroll
+    for (int i = SUB - 1; i >= 0; --i) {
+      if (i >= live) continue;  // uniform over the block
+      const long long t = ts + i;
+      float bv[N], cv[N];
+      load_state_vec<N>(ch.b + t * ch.b_stride, bv);
+      load_state_vec<N>(ch.c + t * ch.c_stride, cv);
+      const bool is_start = p.start && p.start[t];
+      const float gate = p.z ? zv[i] * sigmoidf(zv[i]) : 1.f;
+      const float gyraw = gy[i] * gate;
+      const float w = dtv[i] * xv[i];
+      float dot = 0.f, through_a = 0.f, adj_b = 0.f;
+      float4 part_c, part_b;
+#pragma unroll
+      for (int n = 0; n < N; ++n) {
+        const float before = i > 0 ? after[i > 0 ? i - 1 : 0][n] : kp[(long long)n * p.channels];
+        dot = fmaf(after[i][n], cv[n], dot);
+        adj[n] = fmaf(gyraw, cv[n], adj[n]);  // adjoint of the state after token t
+        reinterpret_cast<float*>(&part_c)[n & 3] = gyraw * after[i][n];
+        reinterpret_cast<float*>(&part_b)[n & 3] = adj[n] * w;
+        if ((n & 3) == 3) {
+          *reinterpret_cast<float4*>(rows_c + i * N + n - 3) = part_c;
+          *reinterpret_cast<float4*>(rows_b + i * N + n - 3) = part_b;
+        }
+        adj_b = fmaf(adj[n], bv[n], adj_b);
+        const float decay = is_start ? 0.f : exp2f(dtv[i] * ch.a2[n]);
+        adj[n] *= decay;                        // adjoint of the state before token t
+        const float through = adj[n] * before;  // adjoint of the decay, times the decay
+        through_a = fmaf(through, ch.a[n], through_a);
+        grad_a[n] = fmaf(through, dtv[i], grad_a[n]);
+      }
+      const float slope = raw[i] > 20.f ? 1.f : sigmoidf(raw[i]);
+      const float grad_raw = (through_a + adj_b * xv[i]) * slope;
+      if (ch.valid) {
+        const long long td = base + (long long)i * p.channels;
+        g.dx[td] = f2bf(adj_b * dtv[i] + gyraw * ch.skip);
+        g.ddt[td] = f2bf(grad_raw);
+        if (g.dz) {
+          const float sg = sigmoidf(zv[i]);
+          g.dz[td] = f2bf(gy[i] * (dot + ch.skip * xv[i]) * sg * (1.f + zv[i] * (1.f - sg)));
+        }
+      }
+      grad_skip = fmaf(gyraw, xv[i], grad_skip);
+      grad_bias += grad_raw;
+    }
+    __syncwarp();
+    reduce_group_grads<N, SUB>(warp_c, g.dc, p.groups_c, p.channels / p.groups_c, p.channels, warp_c0, ts, live);
+    reduce_group_grads<N, SUB>(warp_b, g.db, p.groups_b, p.channels / p.groups_b, p.channels, warp_c0, ts, live);
+    __syncwarp();
+  }
+  if (ch.valid) {
+#pragma unroll
+    for (int n = 0; n < N; ++n) g.da_partial[scratch_index(chunk, n, N, p.channels, ch.d)] = grad_a[n];
+    g.dskip_partial[(long long)chunk * p.channels + ch.d] = grad_skip;
+    g.dbias_partial[(long long)chunk * p.channels + ch.d] = grad_bias;
   }
 }
 
-int scan_check(const ScanArgs& p) {
-  if (p.state < 1 || p.state > 32 || (p.state & (p.state - 1)) || p.channels <= 0 || p.groups_b <= 0 || p.groups_c <= 0) return FLB_ERR_SHAPE;
-  if (p.channels % p.groups_b || p.channels % p.groups_c || p.channels % (kScanThreads / p.state)) return FLB_ERR_SHAPE;
+template <int N>
+int scan_forward(const ScanArgs& p, float* chunk_state, float* chunk_decay, __nv_bfloat16* y, cudaStream_t stream) {
+  dim3 grid((unsigned)((p.channels + kScanThreads - 1) / kScanThreads), (unsigned)p.chunks);
+  scan_summary_kernel<N><<<grid, kScanThreads, 0, stream>>>(p, chunk_state, chunk_decay);
+  FLB_CHECK_LAUNCH();
+  const long long per_chunk = (long long)p.channels * N;
+  scan_chain_kernel<false><<<(unsigned)((per_chunk + 255) / 256), 256, 0, stream>>>(chunk_state, chunk_decay, p.chunks, per_chunk);
+  FLB_CHECK_LAUNCH();
+  scan_output_kernel<N, false><<<grid, kScanThreads, 0, stream>>>(p, chunk_state, y, nullptr);
+  FLB_CHECK_LAUNCH();
+  return FLB_OK;
+}
+
+template <int N>
+int scan_backward(const ScanArgs& p, const ScanGrads& g, const float* chunk_start, const float* chunk_decay, float* chunk_adjoint, float* checkpoints,
+                  cudaStream_t stream) {
+  constexpr int kSmem = 2 * kScanThreads * (scan_sub(N) * N + 4) * (int)sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(scan_bwd_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) return FLB_ERR_CUDA;
+    configured = true;
+  }
+  dim3 grid((unsigned)((p.channels + kScanThreads - 1) / kScanThreads), (unsigned)p.chunks);
+  scan_output_kernel<N, true><<<grid, kScanThreads, 0, stream>>>(p, chunk_start, nullptr, checkpoints);
+  FLB_CHECK_LAUNCH();
+  scan_bwd_summary_kernel<N><<<grid, kScanThreads, 0, stream>>>(p, g.dy, chunk_adjoint);
+  FLB_CHECK_LAUNCH();
+  const long long per_chunk = (long long)p.channels * N;
+  scan_chain_kernel<true><<<(unsigned)((per_chunk + 255) / 256), 256, 0, stream>>>(chunk_adjoint, chunk_decay, p.chunks, per_chunk);
+  FLB_CHECK_LAUNCH();
+  scan_bwd_kernel<N><<<grid, kScanThreads, kSmem, stream>>>(p, g, checkpoints, chunk_adjoint);
+  FLB_CHECK_LAUNCH();
+  return FLB_OK;
+}
+
+int scan_check(const ScanArgs& p, int state) {
+  if (state != 4 && state != 8 && state != 16 && state != 32) return FLB_ERR_SHAPE;
+  if (p.channels <= 0 || p.groups_b <= 0 || p.groups_c <= 0 || p.channels % p.groups_b || p.channels % p.groups_c) return FLB_ERR_SHAPE;
   return FLB_OK;
 }
 }  // namespace
 
 FLB_API int flb_selective_scan_chunks(long long tokens) { return (int)((tokens + kChunk - 1) / kChunk); }
+// Number of state checkpoints the backward pass needs ([checkpoints, state, channels] fp32).
+FLB_API int flb_selective_scan_checkpoints(long long tokens, int state) { return (int)((tokens + scan_sub(state) - 1) / scan_sub(state)); }
 
-// chunk_state, chunk_decay: scratch [chunks, D, N] fp32 (chunk_state ends up holding the state at the start of every chunk and
+// chunk_state, chunk_decay: scratch [chunks, N, D] fp32 (chunk_state ends up holding the state at the start of every chunk and
 // chunk_decay the decay product of every chunk: keep both for the backward pass).
 FLB_API int flb_selective_scan_fwd(const void* x, const void* dt, const float* a, const void* b, const void* c, const float* skip, const void* z,
                                    const float* dt_bias, const unsigned char* start, long long tokens, int channels, int state, int groups_b,
                                    int groups_c, float* chunk_state, float* chunk_decay, void* y, cudaStream_t stream) {
   ScanArgs p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)dt, a, (const __nv_bfloat16*)b, (const __nv_bfloat16*)c, skip, (const __nv_bfloat16*)z,
-             dt_bias, start, tokens, channels, state, groups_b, groups_c, flb_selective_scan_chunks(tokens)};
-  if (int st = scan_check(p)) return st;
+             dt_bias, start, tokens, channels, groups_b, groups_c, flb_selective_scan_chunks(tokens)};
+  if (int st = scan_check(p, state)) return st;
   if (tokens == 0) return FLB_OK;
-  dim3 grid((unsigned)(channels / (kScanThreads / state)), (unsigned)p.chunks);
-  scan_chunk_summary_kernel<<<grid, kScanThreads, 0, stream>>>(p, chunk_state, chunk_decay);
-  FLB_CHECK_LAUNCH();
-  const long long per_chunk = (long long)channels * state;
-  scan_chain_kernel<<<(unsigned)((per_chunk + 255) / 256), 256, 0, stream>>>(chunk_state, chunk_decay, p.chunks, per_chunk);
-  FLB_CHECK_LAUNCH();
-  scan_output_kernel<<<grid, kScanThreads, 0, stream>>>(p, chunk_state, (__nv_bfloat16*)y);
-  FLB_CHECK_LAUNCH();
-  return FLB_OK;
+  switch (state) {
+    case 4: return scan_forward<4>(p, chunk_state, chunk_decay, (__nv_bfloat16*)y, stream);
+    case 8: return scan_forward<8>(p, chunk_state, chunk_decay, (__nv_bfloat16*)y, stream);
+    case 16: return scan_forward<16>(p, chunk_state, chunk_decay, (__nv_bfloat16*)y, stream);
+    default: return scan_forward<32>(p, chunk_state, chunk_decay, (__nv_bfloat16*)y, stream);
+  }
 }
 
-// chunk_start / chunk_decay: as left by the forward call.  chunk_adjoint: scratch [chunks, D, N].  db, dc must be zero on entry.
+// chunk_start / chunk_decay: as left by the forward call.  chunk_adjoint: scratch [chunks, N, D]; checkpoints: scratch
+// [flb_selective_scan_checkpoints, N, D].  db, dc must be zero on entry.  da_partial is [chunks, N, D].
 FLB_API int flb_selective_scan_bwd(const void* x, const void* dt, const float* a, const void* b, const void* c, const float* skip, const void* z,
                                    const float* dt_bias, const unsigned char* start, long long tokens, int channels, int state, int groups_b,
-                                   int groups_c, const float* chunk_start, const float* chunk_decay, float* chunk_adjoint, const void* dy, void* dx,
-                                   void* ddt, void* dz, float* db, float* dc, float* da_partial, float* dskip_partial, float* dbias_partial,
-                                   cudaStream_t stream) {
+                                   int groups_c, const float* chunk_start, const float* chunk_decay, float* chunk_adjoint, float* checkpoints,
+                                   const void* dy, void* dx, void* ddt, void* dz, float* db, float* dc, float* da_partial, float* dskip_partial,
+                                   float* dbias_partial, cudaStream_t stream) {
   ScanArgs p{(const __nv_bfloat16*)x, (const __nv_bfloat16*)dt, a, (const __nv_bfloat16*)b, (const __nv_bfloat16*)c, skip, (const __nv_bfloat16*)z,
-             dt_bias, start, tokens, channels, state, groups_b, groups_c, flb_selective_scan_chunks(tokens)};
-  if (int st = scan_check(p)) return st;
+             dt_bias, start, tokens, channels, groups_b, groups_c, flb_selective_scan_chunks(tokens)};
+  if (int st = scan_check(p, state)) return st;
   if (tokens == 0) return FLB_OK;
   ScanGrads g{(const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, (__nv_bfloat16*)ddt, (__nv_bfloat16*)dz, db, dc, da_partial, dskip_partial, dbias_partial};
-  dim3 grid((unsigned)(channels / (kScanThreads / state)), (unsigned)p.chunks);
-  scan_bwd_summary_kernel<<<grid, kScanThreads, 0, stream>>>(p, g, chunk_adjoint);
-  FLB_CHECK_LAUNCH();
-  const long long per_chunk = (long long)channels * state;
-  scan_bwd_chain_kernel<<<(unsigned)((per_chunk + 255) / 256), 256, 0, stream>>>(chunk_adjoint, chunk_decay, p.chunks, per_chunk);
-  FLB_CHECK_LAUNCH();
-  scan_bwd_kernel<<<grid, kScanThreads, 0, stream>>>(p, g, chunk_start, chunk_adjoint);
-  FLB_CHECK_LAUNCH();
-  return FLB_OK;
+  switch (state) {
+    case 4: return scan_backward<4>(p, g, chunk_start, chunk_decay, chunk_adjoint, checkpoints, stream);
+    case 8: return scan_backward<8>(p, g, chunk_start, chunk_decay, chunk_adjoint, checkpoints, stream);
+    case 16: return scan_backward<16>(p, g, chunk_start, chunk_decay, chunk_adjoint, checkpoints, stream);
+    default: return scan_backward<32>(p, g, chunk_start, chunk_decay, chunk_adjoint, checkpoints, stream);
+  }
 }

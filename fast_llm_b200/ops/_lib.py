@@ -23,7 +23,8 @@ _SIGNATURES = {
     "flb_causal_conv1d_bwd": [_p, _p, _p, _p, _p, _p, _p, _p, _ll, _i, _i, _i, _i, _p],
     "flb_selective_scan_chunks": [_ll],
     "flb_selective_scan_fwd": [_p] * 9 + [_ll, _i, _i, _i, _i, _p, _p, _p, _p],
-    "flb_selective_scan_bwd": [_p] * 9 + [_ll, _i, _i, _i, _i] + [_p] * 13,
+    "flb_selective_scan_checkpoints": [_ll, _i],
+    "flb_selective_scan_bwd": [_p] * 9 + [_ll, _i, _i, _i, _i] + [_p] * 14,
     "flb_moe_dispatch": [_p, _p, _p, _p, _i, _i, _i, _p],
     "flb_moe_combine": [_p, _p, _p, _p, _i, _i, _i, _p],
     "flb_moe_score_grad": [_p, _p, _p, _p, _i, _i, _i, _p],

@@ -121,7 +121,7 @@ def causal_conv1d_reference(x, weight, bias, document_index, activation) -> torc
 
 
 class _CausalConv1d(torch.autograd.Function):
-    TOKENS_PER_BLOCK = 512
+    TOKENS_PER_BLOCK = 64
 
     @staticmethod
     def forward(ctx, x, weight, bias, document_index, activation):
@@ -154,7 +154,7 @@ class _CausalConv1d(torch.autograd.Function):
         _lib.check(_lib.get_lib().flb_causal_conv1d_bwd(x.data_ptr(), w32.data_ptr(), _lib.ptr(b32), _lib.ptr(doc), grad.data_ptr(), dpre.data_ptr(),
                                                        dx.data_ptr(), partial.data_ptr(), tokens, channels, width, ctx.activation.code,
                                                        _CausalConv1d.TOKENS_PER_BLOCK, _lib.stream_ptr()), "flb_causal_conv1d_bwd")
-        _lib.count_launch(3)
+        _lib.count_launch(2)
         sums = partial.sum(0)  # fixed order: deterministic
         dw = sums[:, :width].to(ctx.dtypes[0])
         db = sums[:, width].to(ctx.dtypes[1]) if ctx.has_bias else None
@@ -201,8 +201,8 @@ def _selective_scan_step(state, chunk_in, shared):
 
 
 class _SelectiveScan(torch.autograd.Function):
-    """Chunk-parallel CUDA scan (`csrc/ssm.cu`): three launches forward, three backward; the only saved state beyond the
-    inputs is the [chunks, channels, state] start state and decay product of every 64-token chunk."""
+    """Chunk-parallel CUDA scan (`csrc/ssm.cu`): three launches forward, four backward; the only saved state beyond the
+    inputs is the [chunks, state, channels] start state and decay product of every 64-token chunk."""
 
     @staticmethod
     def forward(ctx, x, dt, a, b, c, skip, z, dt_bias, starts):
@@ -216,7 +216,7 @@ class _SelectiveScan(torch.autograd.Function):
         tokens, channels = x.shape
         state = a32.shape[1]
         chunks = lib.flb_selective_scan_chunks(tokens)
-        chunk_state = torch.empty(chunks, channels, state, dtype=torch.float32, device=x.device)
+        chunk_state = torch.empty(chunks, state, channels, dtype=torch.float32, device=x.device)
         chunk_decay = torch.empty_like(chunk_state)
         y = torch.empty_like(x)
         _lib.check(lib.flb_selective_scan_fwd(x.data_ptr(), dt.data_ptr(), a32.data_ptr(), b.data_ptr(), c.data_ptr(), skip32.data_ptr(), _lib.ptr(z),
@@ -235,6 +235,7 @@ class _SelectiveScan(torch.autograd.Function):
         x, dt, a32, b, c, skip32, z, bias32, starts, chunk_state, chunk_decay = ctx.saved_tensors
         tokens, channels = x.shape
         state, chunks = a32.shape[1], chunk_state.shape[0]
+        checkpoints = torch.empty(lib.flb_selective_scan_checkpoints(tokens, state), state, channels, dtype=torch.float32, device=x.device)
         dy = dy.contiguous()
         dx, ddt = torch.empty_like(x), torch.empty_like(dt)
         dz = None if z is None else torch.empty_like(z)
@@ -246,11 +247,11 @@ class _SelectiveScan(torch.autograd.Function):
         dbias_partial = torch.empty_like(dskip_partial)
         _lib.check(lib.flb_selective_scan_bwd(x.data_ptr(), dt.data_ptr(), a32.data_ptr(), b.data_ptr(), c.data_ptr(), skip32.data_ptr(), _lib.ptr(z),
                                               _lib.ptr(bias32), _lib.ptr(starts), tokens, channels, state, b.shape[1], c.shape[1],
-                                              chunk_state.data_ptr(), chunk_decay.data_ptr(), adjoint.data_ptr(), dy.data_ptr(), dx.data_ptr(),
+                                              chunk_state.data_ptr(), chunk_decay.data_ptr(), adjoint.data_ptr(), checkpoints.data_ptr(), dy.data_ptr(), dx.data_ptr(),
                                               ddt.data_ptr(), _lib.ptr(dz), db.data_ptr(), dc.data_ptr(), da_partial.data_ptr(),
                                               dskip_partial.data_ptr(), dbias_partial.data_ptr(), _lib.stream_ptr()), "flb_selective_scan_bwd")
-        _lib.count_launch(3)
-        da = da_partial.sum(0).to(ctx.dtypes[0])
+        _lib.count_launch(4)
+        da = da_partial.sum(0).t().to(ctx.dtypes[0])
         dskip = dskip_partial.sum(0).to(ctx.dtypes[1])
         dbias = None if bias32 is None else dbias_partial.sum(0).to(ctx.dtypes[2])
         return dx, ddt, da, db.to(b.dtype), dc.to(c.dtype), dskip, dz, dbias, None
@@ -260,9 +261,7 @@ def _scan_kernel_applies(x, dt, a, b, c, z) -> bool:
     if not (x.is_cuda and all(t is None or t.dtype == torch.bfloat16 for t in (x, dt, b, c, z))):
         return False
     channels, state = a.shape
-    if state > 32 or state & (state - 1) or channels % b.shape[1] or channels % c.shape[1]:
-        return False
-    return channels % (128 // state) == 0
+    return state in (4, 8, 16, 32) and channels % b.shape[1] == 0 and channels % c.shape[1] == 0
 
 
 def document_starts(cu_seqlens, tokens: int, device) -> torch.Tensor | None:

@@ -207,6 +207,62 @@ def bench_moe(results):
     print(json.dumps(r), flush=True)
 
 
+def bench_ssm(results):
+    """Mamba mixer inner ops at 8192 tokens, d_inner 4096, state 16: causal conv1d and selective scan, forward and backward.
+    The scan is bounded by exp throughput (tokens x channels x state exponentials per pass), not by HBM: both are reported."""
+    from fast_llm_b200.ops.activation import ActivationType
+    from fast_llm_b200.ops.ssm import causal_conv1d, selective_scan
+
+    hbm, _, kind = _peaks()
+    tokens, channels, state, groups = 8192, 4096, 16, 32
+    dev = "cuda"
+    x = torch.randn(tokens, channels, device=dev).bfloat16().requires_grad_()
+    w = torch.randn(channels, 4, device=dev).bfloat16().requires_grad_()
+    bias = torch.randn(channels, device=dev).bfloat16().requires_grad_()
+    g = torch.randn(tokens, channels, device=dev).bfloat16()
+    silu = ActivationType("silu")
+    out = [None]
+
+    def conv_fwd():
+        out[0] = causal_conv1d(x, w, bias, None, silu)
+
+    ms = time_op(conv_fwd)
+    nbytes = 2 * tokens * channels * 2
+    r = {"op": "causal_conv1d_fwd", "ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_peak": nbytes / ms / 1e6 / hbm, "peak_kind": kind}
+    results.append(r)
+    print(json.dumps(r), flush=True)
+    ms = time_op(lambda: torch.autograd.grad(out[0], (x, w, bias), g, retain_graph=True))
+    nbytes = 6 * tokens * channels * 2  # x, dout -> dpre; dpre -> dx; x, dpre -> dw
+    r = {"op": "causal_conv1d_bwd", "ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_peak": nbytes / ms / 1e6 / hbm, "peak_kind": kind}
+    results.append(r)
+    print(json.dumps(r), flush=True)
+
+    dt = (torch.randn(tokens, channels, device=dev) - 1).bfloat16().requires_grad_()
+    z = torch.randn(tokens, channels, device=dev).bfloat16().requires_grad_()
+    a = (-torch.rand(channels, state, device=dev) - 0.1).requires_grad_()
+    b = torch.randn(tokens, groups, state, device=dev).bfloat16().requires_grad_()
+    c = torch.randn(tokens, channels // state, state, device=dev).bfloat16().requires_grad_()
+    skip = torch.randn(channels, device=dev).requires_grad_()
+    dt_bias = torch.randn(channels, device=dev).requires_grad_()
+
+    def scan_fwd():
+        out[0] = selective_scan(x, dt, a, b, c, skip, z, dt_bias, None)
+
+    ms = time_op(scan_fwd)
+    nbytes = 4 * tokens * channels * 2
+    exps = 2.0 * tokens * channels * state
+    r = {"op": "selective_scan_fwd", "ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_peak": nbytes / ms / 1e6 / hbm, "peak_kind": kind,
+         "gexp_per_s": exps / ms / 1e6}
+    results.append(r)
+    print(json.dumps(r), flush=True)
+    ms = time_op(lambda: torch.autograd.grad(out[0], (x, dt, a, b, c, skip, z, dt_bias), g, retain_graph=True))
+    nbytes = 8 * tokens * channels * 2
+    r = {"op": "selective_scan_bwd", "ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_peak": nbytes / ms / 1e6 / hbm, "peak_kind": kind,
+         "gexp_per_s": 1.5 * exps / ms / 1e6}
+    results.append(r)
+    print(json.dumps(r), flush=True)
+
+
 def profile_attention():
     """Small fixed workload for an ncu capture: two forward + backward launches of attention at the Mistral-7B shape."""
     from fast_llm_b200.ops.attention import attention_backward_native, attention_forward_native
@@ -275,7 +331,9 @@ def main(argv):
         bench_attention(results)
     if "moe" in argv:
         bench_moe(results)
-    which = [a for a in argv if a in ("gemm", "elementwise")] or ([] if ("gemm_tiles" in argv or "attention" in argv or "moe" in argv) else ["gemm", "elementwise"])
+    if "ssm" in argv:
+        bench_ssm(results)
+    which = [a for a in argv if a in ("gemm", "elementwise")] or ([] if ("gemm_tiles" in argv or "attention" in argv or "moe" in argv or "ssm" in argv) else ["gemm", "elementwise"])
     if "gemm" in which:
         bench_gemm(results)
     if "elementwise" in which:

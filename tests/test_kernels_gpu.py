@@ -482,7 +482,7 @@ def test_causal_conv1d(tokens, channels, width, act, with_docs):
 
 
 @pytest.mark.parametrize("tokens,channels,state,groups_b,groups_c,gated,docs", [
-    (200, 64, 16, 2, 4, True, [0, 70, 71, 200]), (130, 32, 8, 1, 4, False, None), (64, 128, 16, 8, 8, True, [0, 64]), (300, 32, 4, 1, 1, True, [0, 129, 300])])
+    (200, 64, 16, 2, 4, True, [0, 70, 71, 200]), (130, 32, 8, 1, 4, False, None), (64, 128, 16, 8, 8, True, [0, 64]), (300, 32, 4, 1, 1, True, [0, 129, 300]), (97, 384, 16, 2, 24, True, [0, 50, 97]), (70, 256, 32, 4, 8, False, None)])
 def test_selective_scan_kernel(tokens, channels, state, groups_b, groups_c, gated, docs):
     from fast_llm_b200.ops.ssm import _SelectiveScan, document_starts, selective_scan, selective_scan_reference
 
