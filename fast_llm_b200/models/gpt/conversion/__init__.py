@@ -1,6 +1,6 @@
 """Hugging Face checkpoint formats of the GPT model family."""
 
-try:
-    from fast_llm_b200.models.gpt.conversion.formats import GPT_CHECKPOINT_FORMATS  # noqa: F401
-except ImportError:  # formats module not built yet
-    GPT_CHECKPOINT_FORMATS = ()
+from fast_llm_b200.models.gpt.conversion.apriel2 import Apriel2TextCheckpointFormat
+from fast_llm_b200.models.gpt.conversion.formats import GPT_CHECKPOINT_FORMATS as _BASE_FORMATS
+
+GPT_CHECKPOINT_FORMATS = _BASE_FORMATS + (Apriel2TextCheckpointFormat,)

@@ -554,6 +554,10 @@ class AutoGPTHuggingfaceCheckpointHandler(HuggingfaceStateDictCheckpointHandler)
     @classmethod
     def resolve(cls, path) -> type[HuggingfaceStateDictCheckpointHandler]:
         model_type = json.loads((pathlib.Path(path) / "config.json").read_text())["model_type"]
+        if model_type == "apriel2_text":
+            from fast_llm_b200.models.gpt.conversion.apriel2 import Apriel2HuggingfaceCheckpointHandler
+
+            return Apriel2HuggingfaceCheckpointHandler
         return cls.handler_map[model_type]
 
     @classmethod

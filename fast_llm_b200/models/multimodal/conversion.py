@@ -22,7 +22,7 @@ from fast_llm_b200.engine.checkpoint.external import (
     TransposeWeightConverter,
     WeightConverter,
 )
-from fast_llm_b200.models.gpt.conversion.formats import MistralHuggingfaceCheckpointHandler
+from fast_llm_b200.models.gpt.conversion.formats import AprielHybridSSMHuggingfaceCheckpointHandler, MistralHuggingfaceCheckpointHandler
 from fast_llm_b200.ops.activation import ActivationType
 from fast_llm_b200.utils import Assert, div
 
@@ -138,4 +138,187 @@ class LlavaHuggingfaceCheckpointHandler(HuggingfaceStateDictCheckpointHandler):
         return out
 
 
-MULTIMODAL_CHECKPOINT_FORMATS: tuple = (LlavaCheckpointFormat,)
+class LlavaHybridSSMCheckpointFormat(CheckpointFormat):
+    support_optimizer: typing.ClassVar[bool] = False
+    name: typing.ClassVar[str] = "llava_hybrid_ssm"
+
+    @classmethod
+    def get_handler_class(cls):
+        return LlavaHybridSSMHuggingfaceCheckpointHandler
+
+
+class LlavaHybridSSMHuggingfaceCheckpointHandler(LlavaHuggingfaceCheckpointHandler):
+    """Llava with an Apriel hybrid (attention / Mamba / gated DeltaNet) language model
+    (`fast_llm/models/multimodal/conversion/llava_hybrid.py:13-47`)."""
+
+    format = LlavaHybridSSMCheckpointFormat
+    architecture = "LlavaHybridForConditionalGeneration"
+    text_handler = AprielHybridSSMHuggingfaceCheckpointHandler
+
+    @classmethod
+    def export_config(cls, c) -> dict:
+        out = super().export_config(c)
+        out["text_config"].pop("auto_map", None)
+        out["auto_map"] = {"AutoConfig": "configuration_llava_hybrid.LlavaHybridConfig", "AutoModel": "modeling_llava_hybrid.LlavaHybridModel",
+                           "AutoModelForCausalLM": "modeling_llava_hybrid.LlavaHybridForConditionalGeneration",
+                           "AutoModelForImageTextToText": "modeling_llava_hybrid.LlavaHybridForConditionalGeneration"}
+        return out
+
+
+class Apriel2CheckpointFormat(CheckpointFormat):
+    support_optimizer: typing.ClassVar[bool] = False
+    name: typing.ClassVar[str] = "apriel2"
+
+    @classmethod
+    def get_handler_class(cls):
+        return Apriel2MultimodalHuggingfaceCheckpointHandler
+
+
+class Apriel2MultimodalHuggingfaceCheckpointHandler(HuggingfaceStateDictCheckpointHandler):
+    """Apriel2 with a vision encoder: the text format's keys at the top level plus a `vision_encoder` section
+    {hidden_size, embeddings {patch_height, patch_width, normalization}, encoder {type: fixed, num_blocks, block},
+    adapter {type: mlp, ...}} and `image_token_index`.  Vision weights live under `model.vision_encoder.{embeddings,
+    encoder.blocks.{i}, adapter}`; the adapter keeps the llava names `linear_1` / `linear_2`
+    (`fast_llm/models/multimodal/conversion/apriel2.py:48-528`)."""
+
+    format = Apriel2CheckpointFormat
+    architecture = "Apriel2ForConditionalGeneration"
+    model_type = "apriel2"
+
+    @classmethod
+    def get_model_config_class(cls):
+        from fast_llm_b200.models.multimodal.config import MultiModalModelConfig
+
+        return MultiModalModelConfig
+
+    @classmethod
+    def export_config(cls, c) -> dict:
+        from fast_llm_b200.models.gpt.conversion import apriel2 as text
+
+        out = text.Apriel2HuggingfaceCheckpointHandler.export_config(c)
+        vision = c.vision_encoder
+        e = vision.embeddings
+        Assert.eq(e.patch_height, e.patch_width)
+        block = vision.encoder.block
+        mixer = block.mixer
+        Assert.eq(type(mixer).__name__, "AttentionConfig")
+        rotary_kind = type(mixer.rotary).__name__
+        rotary = ({"type": "pixtral_2d", "theta": mixer.rotary.theta, "patch_size": e.patch_height, "max_image_size": 1024}
+                  if rotary_kind == "Rotary2DConfig" else {"type": "mistral_1d", "theta": mixer.rotary.theta})
+        mlp, adapter = block.mlp, vision.adapter
+
+        def mlp_section(m):
+            return {"type": "mlp", "intermediate_size": m.intermediate_size, "activation": m.activation.hf_name, "gated": m.gated,
+                    "add_linear_biases": m.add_linear_biases}
+
+        out.update({
+            "model_type": cls.model_type, "architectures": [cls.architecture], "image_token_index": c.image_token_index,
+            "vision_encoder": {
+                "hidden_size": vision.hidden_size, "num_hidden_layers": vision.encoder.num_blocks, "patch_size": e.patch_height, "num_channels": 3,
+                "embeddings": {"patch_height": e.patch_height, "patch_width": e.patch_width, "input_channels": 3,
+                               "normalization": text._normalization_export(e.normalization)},
+                "encoder": {"type": "fixed", "num_blocks": vision.encoder.num_blocks, "block": {
+                    "mixer": {"type": "attention", "heads": mixer.heads, "head_groups": mixer.head_groups, "head_size": mixer.head_size,
+                              "add_linear_biases": mixer.add_linear_biases, "causal": mixer.causal, "cross_document_attention": False, "rotary": rotary},
+                    "mlp": mlp_section(mlp), "normalization": text._normalization_export(block.normalization)}},
+                "adapter": mlp_section(adapter),
+            },
+            "auto_map": {"AutoConfig": "configuration_apriel2.Apriel2Config", "AutoModel": "modeling_apriel2.Apriel2Model",
+                         "AutoModelForCausalLM": "modeling_apriel2.Apriel2ForConditionalGeneration",
+                         "AutoModelForImageTextToText": "modeling_apriel2.Apriel2ForConditionalGeneration"},
+        })
+        return out
+
+    @classmethod
+    def import_config(cls, h: dict) -> dict:
+        from fast_llm_b200.models.gpt.conversion import apriel2 as text
+
+        out = text.Apriel2HuggingfaceCheckpointHandler.import_config(h)
+        v = h["vision_encoder"]
+        block = v["encoder"]["block"]
+        mixer = dict(block["mixer"])
+        rotary = dict(mixer.get("rotary", {"type": "pixtral_2d"}))
+        rotary["type"] = {"pixtral_2d": "default_2d", "mistral_1d": "default"}.get(rotary.get("type"), rotary.get("type"))
+        rotary.pop("patch_size", None)
+        rotary.pop("max_image_size", None)
+        mixer["rotary"] = rotary
+        mixer.pop("cross_document_attention", None)
+
+        def mlp_section(m):
+            section = {"type": "mlp", **{k: m[k] for k in ("intermediate_size", "gated", "add_linear_biases") if k in m}}
+            if "activation" in m:
+                section["activation"] = ActivationType.from_hf_name(m["activation"]).value
+            return section
+
+        out["vision_encoder"] = {
+            "hidden_size": v["hidden_size"],
+            "embeddings": {"patch_height": v["embeddings"]["patch_height"], "patch_width": v["embeddings"]["patch_width"],
+                           "normalization": dict(v["embeddings"]["normalization"])},
+            "encoder": {"type": "fixed", "num_blocks": v["encoder"]["num_blocks"],
+                        "block": {"mixer": mixer, "mlp": mlp_section(block["mlp"]), "normalization": dict(block["normalization"])}},
+            "adapter": mlp_section(v["adapter"]),
+        }
+        out["image_token_index"] = h.get("image_token_index")
+        return out
+
+    @classmethod
+    def get_weight_converters(cls, c) -> list[WeightConverter]:
+        from fast_llm_b200.models.gpt.conversion import apriel2 as text
+
+        vision = c.vision_encoder
+        e = vision.embeddings
+        prefix = "model.vision_encoder"
+        out = [PatchEmbeddingWeightConverter("vision_encoder.embeddings.patch_embeddings.weight", f"{prefix}.embeddings.patch_embeddings.weight",
+                                             (e.input_channels, e.patch_height, e.patch_width)),
+               WeightConverter("vision_encoder.embeddings.normalization.weight", f"{prefix}.embeddings.normalization.weight")]
+        for i, block in enumerate(vision.encoder.block_configs()):
+            out += text._block_weights(block, f"vision_encoder.encoder.{i}", f"{prefix}.encoder.blocks.{i}")
+        adapter = vision.adapter
+        out.append(WeightConverter("vision_encoder.adapter.layer_1.weight", f"{prefix}.adapter.linear_1.weight"))
+        out.append(TransposeWeightConverter("vision_encoder.adapter.layer_2.weight", f"{prefix}.adapter.linear_2.weight"))
+        if adapter.add_linear_biases:
+            out.append(WeightConverter("vision_encoder.adapter.layer_1.bias", f"{prefix}.adapter.linear_1.bias"))
+            out.append(WeightConverter("vision_encoder.adapter.layer_2.bias", f"{prefix}.adapter.linear_2.bias"))
+        return out + text.Apriel2HuggingfaceCheckpointHandler.get_weight_converters(c)
+
+
+class AutoMultimodalCheckpointFormat(CheckpointFormat):
+    support_optimizer: typing.ClassVar[bool] = False
+    name: typing.ClassVar[str] = "auto"
+
+    @classmethod
+    def get_handler_class(cls):
+        return AutoMultimodalHuggingfaceCheckpointHandler
+
+
+class AutoMultimodalHuggingfaceCheckpointHandler(HuggingfaceStateDictCheckpointHandler):
+    """Picks the handler from config.json (`fast_llm/models/multimodal/conversion/auto.py:1-23`); loading only."""
+
+    format = AutoMultimodalCheckpointFormat
+
+    def __new__(cls, model):
+        raise TypeError("resolve the concrete handler with resolve(path) first")
+
+    @classmethod
+    def resolve(cls, path):
+        import json
+        import pathlib
+
+        config = json.loads((pathlib.Path(path) / "config.json").read_text())
+        architecture = (config.get("architectures") or [None])[0]
+        by_architecture = {handler.architecture: handler for handler in (LlavaHuggingfaceCheckpointHandler, LlavaHybridSSMHuggingfaceCheckpointHandler,
+                                                                        Apriel2MultimodalHuggingfaceCheckpointHandler)}
+        return by_architecture[architecture]
+
+    @classmethod
+    def load_metadata(cls, config):
+        return cls.resolve(config.path).load_metadata(config)
+
+    @classmethod
+    def get_model_config_class(cls):
+        from fast_llm_b200.models.multimodal.config import MultiModalModelConfig
+
+        return MultiModalModelConfig
+
+
+MULTIMODAL_CHECKPOINT_FORMATS: tuple = (AutoMultimodalCheckpointFormat, LlavaCheckpointFormat, LlavaHybridSSMCheckpointFormat, Apriel2CheckpointFormat)

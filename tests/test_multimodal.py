@@ -103,3 +103,61 @@ def test_llava_round_trip(tmp_path):
     original = {n: t for n, _, t in trainer.multi_stage.get_state_tensor_iterator(("weights",))}
     for name, _, tensor in loaded.get_state_tensor_iterator(("weights",)):
         torch.testing.assert_close(tensor.float(), original[name].float(), rtol=1e-2, atol=1e-2, msg=lambda m: f"{name}: {m}")
+
+
+def test_apriel2_multimodal_round_trip(tmp_path):
+    """The Apriel2 layout nests the vision encoder under `vision_encoder` and keeps the text keys at the top level."""
+    import json
+
+    import safetensors
+
+    from fast_llm_b200.engine.checkpoint.config import CheckpointLoadConfig, CheckpointSaveConfig
+    from fast_llm_b200.models.multimodal.model import MultiModalModel
+
+    trainer, _ = build_trainer(_config({("model", "base_model", "image_token_index"): 7}))
+    path = tmp_path / "apriel2"
+    trainer.multi_stage.save_checkpoint(CheckpointSaveConfig(path=path, format="apriel2"))
+    config = json.loads((path / "config.json").read_text())
+    assert config["model_type"] == "apriel2" and config["architectures"] == ["Apriel2ForConditionalGeneration"]
+    assert config["decoder"]["type"] == "fixed" and config["vision_encoder"]["encoder"]["block"]["mixer"]["rotary"]["type"] == "pixtral_2d"
+    assert config["vision_encoder"]["adapter"]["intermediate_size"] == 48 and config["image_token_index"] == 7
+    names = {}
+    for file in path.glob("*.safetensors"):
+        with safetensors.safe_open(str(file), framework="pt") as f:
+            for key in f.keys():
+                names[key] = f.get_slice(key).get_shape()
+    assert names["model.vision_encoder.embeddings.patch_embeddings.weight"] == [32, 3, 4, 4]
+    assert "model.vision_encoder.encoder.blocks.1.mixer.k_proj.weight" in names and "model.vision_encoder.adapter.linear_2.bias" in names
+    assert "model.decoder.blocks.0.mixer.q_proj.weight" in names
+    for format_name in ("apriel2", "auto"):
+        loaded = MultiModalModel.from_pretrained(CheckpointLoadConfig(path=path, format=format_name), use_cpu=True)
+        original = {n: t for n, _, t in trainer.multi_stage.get_state_tensor_iterator(("weights",))}
+        for name, _, tensor in loaded.get_state_tensor_iterator(("weights",)):
+            torch.testing.assert_close(tensor.float(), original[name].float(), rtol=1e-2, atol=1e-2, msg=lambda m: f"{name}: {m}")
+
+
+def test_llava_hybrid_round_trip(tmp_path):
+    """Llava around an Apriel hybrid language model (attention + Mamba blocks)."""
+    import json
+
+    from fast_llm_b200.engine.checkpoint.config import CheckpointLoadConfig, CheckpointSaveConfig
+    from fast_llm_b200.models.multimodal.model import MultiModalModel
+
+    attention_block = copy.deepcopy(TINY_BASE_MODEL["decoder"]["block"])
+    mamba_block = copy.deepcopy(attention_block)
+    mamba_block["mixer"] = {"type": "mamba", "d_inner": 64, "d_xb": 32, "state_size": 8, "dt_rank": 4, "add_linear_biases": False,
+                            "convolution_layer": {"bias": {"enabled": True}}, "dt_layer": {"bias": {"enabled": True}}}
+    decoder = {"type": "pattern", "blocks": {"t": attention_block, "m2": mamba_block}, "pattern": ["t", "m2"], "num_blocks": 2}
+    trainer, _ = build_trainer(_config({("model", "base_model", "image_token_index"): 7, ("model", "base_model", "decoder"): decoder,
+                                        ("model", "base_model", "vision_encoder", "adapter", "intermediate_size"): 64}))
+    path = tmp_path / "llava_hybrid"
+    trainer.multi_stage.save_checkpoint(CheckpointSaveConfig(path=path, format="llava_hybrid_ssm"))
+    config = json.loads((path / "config.json").read_text())
+    assert config["architectures"] == ["LlavaHybridForConditionalGeneration"] and config["text_config"]["hybrid_block_layout"] == ["t", "m2"]
+    loaded = MultiModalModel.from_pretrained(CheckpointLoadConfig(path=path, format="llava_hybrid_ssm"), use_cpu=True)
+    original = {n: t for n, _, t in trainer.multi_stage.get_state_tensor_iterator(("weights",))}
+    count = 0
+    for name, _, tensor in loaded.get_state_tensor_iterator(("weights",)):
+        torch.testing.assert_close(tensor.float(), original[name].float(), rtol=1e-2, atol=1e-2, msg=lambda m: f"{name}: {m}")
+        count += 1
+    assert count == len(original)

@@ -285,6 +285,48 @@ def test_mtp_llama_and_apriel_hybrid_round_trip(tmp_path):
     assert config["hybrid_block_layout"] == ["t", "m2", "m2"] and config["ssm_cfg"]["d_state"] == 8
 
 
+def test_apriel2_round_trip(tmp_path):
+    """A pattern decoder with every mixer kind of the Apriel2 format, one of them stochastic."""
+    import copy
+
+    from tests.common import TINY_BASE_MODEL
+
+    base = copy.deepcopy(TINY_BASE_MODEL)
+    attention_block = base["decoder"]["block"]
+
+    def with_mixer(mixer):
+        block = copy.deepcopy(attention_block)
+        block["mixer"] = mixer
+        return block
+
+    mamba = {"type": "mamba", "d_inner": 64, "d_xb": 32, "state_size": 8, "dt_rank": 4, "add_linear_biases": False,
+             "convolution_layer": {"bias": {"enabled": True}}, "dt_layer": {"bias": {"enabled": True}}}
+    gdn = {"type": "gdn", "value_heads": 4, "key_heads": 2, "key_head_dim": 8, "value_head_dim": 8, "convolution_layer": {"kernel_size": 3}}
+    kda = {"type": "kda", "heads": 2, "head_dim": 8, "convolution_layer": {"kernel_size": 3}}
+    stochastic = {"type": "stochastic", "mixers": {"attn": copy.deepcopy(attention_block["mixer"]), "gdn": copy.deepcopy(gdn)}, "main_mixer_name": "attn"}
+    base["decoder"] = {"type": "pattern", "num_blocks": 5, "pattern": ["t", "m", "g", "k", "s"],
+                       "blocks": {"t": attention_block, "m": with_mixer(mamba), "g": with_mixer(gdn), "k": with_mixer(kda), "s": with_mixer(stochastic)}}
+    config = _round_trip(tmp_path, base, "apriel2_text")
+    assert config["model_type"] == "apriel2_text" and config["decoder"]["type"] == "pattern"
+    blocks = config["decoder"]["blocks"]
+    assert [blocks[name]["mixer"]["type"] for name in ("t", "m", "g", "k", "s")] == ["attention", "mamba", "gdn", "kda", "stochastic"]
+    assert blocks["t"]["mixer"]["rotary"]["type"] == "mistral_1d" and blocks["m"]["mixer"]["d_conv"] == 4
+    assert set(blocks["s"]["mixer"]["mixers"]) == {"attn", "gdn"}
+    from safetensors import safe_open
+
+    names = set()
+    for file in (tmp_path / "apriel2_text").glob("*.safetensors"):
+        with safe_open(file, "pt") as f:
+            names |= set(f.keys())
+    assert "model.decoder.blocks.4.mixer.mixers.gdn.in_proj_qkvz.weight" in names
+    assert "model.decoder.blocks.3.mixer.f_a_proj.weight" in names and "model.decoder.blocks.1.mixer.conv1d.bias" in names
+    # the `auto` format recognises it from config.json
+    from fast_llm_b200.engine.checkpoint.config import CheckpointLoadConfig
+    from fast_llm_b200.models.gpt.model import GPTModel
+
+    GPTModel.from_pretrained(CheckpointLoadConfig(path=tmp_path / "apriel2_text", format="auto"), use_cpu=True)
+
+
 def test_checkpoint_surgery_tools(tmp_path):
     """MoE upcycling and MTP-head surgery produce checkpoints this framework loads."""
     from fast_llm_b200.engine.checkpoint.config import CheckpointLoadConfig, CheckpointSaveConfig
