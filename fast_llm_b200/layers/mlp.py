@@ -53,6 +53,11 @@ class MLP(LayerBase):
         l1_dim = ConcatenatedTensorDim("gate_and_up", (ffn_dim, ffn_dim)) if config.gated else ffn_dim
         self._ffn_dim = ffn_dim
         self._build(config, distributed_config, hidden_dim, l1_dim, ffn_dim, peft)
+        # optional norms of this branch alone (a hybrid MoE gives its dense and routed branches their own)
+        if config.pre_norm is not None:
+            self.pre_norm = config.pre_norm.get_layer(hidden_dim, lr_scale=self._lr_scale, peft=peft, distributed_config=distributed_config)
+        if config.post_norm is not None:
+            self.post_norm = config.post_norm.get_layer(self._output_dim, lr_scale=self._lr_scale, peft=peft, distributed_config=distributed_config)
 
     def _build(self, config, distributed_config, hidden_dim, l1_dim, ffn_dim, peft):
         common = dict(default_add_bias=config.add_linear_biases, lr_scale=self._lr_scale, peft=peft, distributed_config=distributed_config)
@@ -62,6 +67,15 @@ class MLP(LayerBase):
                                                 sequence_parallel=self._sequence_parallel, transposed_weight=True, **common)
 
     def forward(self, x: torch.Tensor, kwargs: dict | None = None, losses=None, metrics=None) -> torch.Tensor:
+        c = self._config
+        if c.pre_norm is not None:
+            x = self.pre_norm(x)
+        out = self._forward(x, kwargs, losses, metrics)
+        if c.post_norm is not None:
+            out = self.post_norm(out)
+        return out
+
+    def _forward(self, x: torch.Tensor, kwargs: dict | None = None, losses=None, metrics=None) -> torch.Tensor:
         c = self._config
         l1, l2 = self.layer_1, self.layer_2
         if l1._forward_hook is not None or l2._forward_hook is not None:

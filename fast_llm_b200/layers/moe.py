@@ -225,7 +225,7 @@ class MixtureOfExpertMLP(MLP):
             out.append(views)
         return out
 
-    def forward(self, x: torch.Tensor, kwargs: dict | None = None, losses=None, metrics=None) -> torch.Tensor:
+    def _forward(self, x: torch.Tensor, kwargs: dict | None = None, losses=None, metrics=None) -> torch.Tensor:
         kwargs = kwargs or {}
         c = self._config
         shape = x.shape

@@ -558,6 +558,10 @@ class AutoGPTHuggingfaceCheckpointHandler(HuggingfaceStateDictCheckpointHandler)
             from fast_llm_b200.models.gpt.conversion.apriel2 import Apriel2HuggingfaceCheckpointHandler
 
             return Apriel2HuggingfaceCheckpointHandler
+        if model_type == "gemma4_text":
+            from fast_llm_b200.models.gpt.conversion.gemma4 import Gemma4HuggingfaceCheckpointHandler
+
+            return Gemma4HuggingfaceCheckpointHandler
         return cls.handler_map[model_type]
 
     @classmethod

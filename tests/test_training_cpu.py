@@ -327,6 +327,68 @@ def test_apriel2_round_trip(tmp_path):
     GPTModel.from_pretrained(CheckpointLoadConfig(path=tmp_path / "apriel2_text", format="auto"), use_cpu=True)
 
 
+@pytest.mark.parametrize("moe", [False, True])
+def test_gemma4_round_trip(tmp_path, moe):
+    """Sliding / full attention pattern with head norms, shared key-value, post-norms, frozen output scale, soft-capped
+    logits; with `moe` the MLP is a dense branch plus a routed mixture of experts stored batched."""
+    import copy
+
+    from tests.common import TINY_BASE_MODEL
+
+    base = copy.deepcopy(TINY_BASE_MODEL)
+    hidden = base["hidden_size"]
+    norm = {"type": "rms_norm", "epsilon": 1e-6}
+
+    def attention(sliding):
+        out = {"type": "attention", "heads": 4, "head_groups": 2, "head_size": 16 if sliding else 32, "add_linear_biases": False, "softmax_scale_power": 0,
+               "query_norm": dict(norm), "key_norm": dict(norm), "value_norm": {"type": "fixed_rms_norm", "epsilon": 1e-6},
+               "rotary": {"type": "default", "theta": 10000.0} if sliding else {"type": "proportional", "theta": 1000000.0, "partial_rotary_factor": 0.25}}
+        if sliding:
+            out["window_size"] = 16
+        else:
+            out["shared_key_value"] = True
+            out["head_groups"] = 1
+        return out
+
+    dense = {"type": "mlp", "intermediate_size": 96, "gated": True, "add_linear_biases": False, "activation": "gelu"}
+
+    def block(sliding):
+        out = {"type": "decoder", "mixer": attention(sliding), "normalization": dict(norm), "post_mixer_normalization": dict(norm),
+               "post_mlp_normalization": dict(norm), "output_scale": {"enabled": True, "lr_scale": 0}}
+        if moe:
+            routed = {"type": "moe", "intermediate_size": 32, "gated": True, "add_linear_biases": False, "activation": "gelu", "experts": 4,
+                      "experts_per_token": 2, "router_normalization": {"type": "fixed_rms_norm", "epsilon": 1e-6}, "router_scale": {"enabled": True},
+                      "router_input_scale": hidden**-0.5, "router_per_expert_scale": {"enabled": True}, "pre_norm": dict(norm), "post_norm": dict(norm)}
+            out["mlp"] = {"type": "hybrid_moe", "dense": {**dense, "pre_norm": dict(norm), "post_norm": dict(norm)}, "routed": routed}
+            out["pre_mlp_normalization"] = {"type": "none"}
+        else:
+            out["mlp"] = dict(dense)
+            out["pre_mlp_normalization"] = dict(norm)
+        return out
+
+    base["decoder"] = {"type": "pattern", "num_blocks": 3, "pattern": ["sliding_attention", "sliding_attention", "full_attention"],
+                       "blocks": {"sliding_attention": block(True), "full_attention": block(False)}}
+    base["embeddings"]["embedding_scale"] = hidden**0.5
+    base["head"]["final_logit_softcap"] = 30.0
+    base["head"]["normalization"] = dict(norm)
+    config = _round_trip(tmp_path, base, "gemma4")
+    assert config["model_type"] == "gemma4_text" and config["layer_types"] == ["sliding_attention"] * 2 + ["full_attention"]
+    assert config["head_dim"] == 16 and config["global_head_dim"] == 32 and config["num_global_key_value_heads"] == 1 and config["attention_k_eq_v"]
+    assert config["final_logit_softcapping"] == 30.0 and config["enable_moe_block"] == moe
+    from safetensors import safe_open
+
+    shapes = {}
+    for file in (tmp_path / "gemma4").glob("*.safetensors"):
+        with safe_open(file, "pt") as f:
+            for key in f.keys():
+                shapes[key] = list(f.get_slice(key).get_shape())
+    assert "model.layers.2.self_attn.v_proj.weight" not in shapes and "model.layers.0.self_attn.v_proj.weight" in shapes
+    assert "model.layers.1.layer_scalar" in shapes and "model.layers.0.self_attn.q_norm.weight" in shapes
+    if moe:
+        assert shapes["model.layers.0.experts.gate_up_proj"] == [4, 64, hidden] and shapes["model.layers.0.experts.down_proj"] == [4, hidden, 32]
+        assert "model.layers.0.router.per_expert_scale" in shapes and "model.layers.0.pre_feedforward_layernorm_2.weight" in shapes
+
+
 def test_checkpoint_surgery_tools(tmp_path):
     """MoE upcycling and MTP-head surgery produce checkpoints this framework loads."""
     from fast_llm_b200.engine.checkpoint.config import CheckpointLoadConfig, CheckpointSaveConfig
