@@ -5,6 +5,10 @@
 //   flb_ce_grad  : given merged (max, sumexp, target) writes the per-token loss and the logit gradients
 //                  grad_j = g * ((1 + 2 z lse) softmax_j - [j == label]) * logits_scale   (may alias logits)
 // Also carries the z-loss term z * lse^2.  Labels < 0 are ignored (zero loss and gradient).
+// Vocabulary-parallel exchange without a collective library: `flb_ce_stats_exchange` stores this rank's three numbers per
+// token straight into slot `rank` of every peer's statistics buffer (NVLink peer stores from the statistics kernel); after one
+// device-side barrier `flb_ce_grad` reads `slots` local slots per token and merges them (global max, rescaled sum-exp,
+// summed target logit) on the fly.
 #include "common.cuh"
 
 namespace {
@@ -23,10 +27,16 @@ template <> struct Vec<float> {
   static __device__ __forceinline__ void store(float* p, const float* f) { *reinterpret_cast<float4*>(p) = *reinterpret_cast<const float4*>(f); }
 };
 
+struct StatPeers {
+  float* p[8];
+  int world;  // 0: write to `stats` only
+  int rank;
+};
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 ce_stats_kernel(const T* __restrict__ logits, const long long* __restrict__ labels, float* __restrict__ stats,
-                int rows, int cols, long long ld, long long vocab_begin, float logits_scale) {
+                int rows, int cols, long long ld, long long vocab_begin, float logits_scale, const StatPeers peers) {
   __shared__ float scratch[32];
   constexpr int VN = Vec<T>::N;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -58,9 +68,19 @@ ce_stats_kernel(const T* __restrict__ logits, const long long* __restrict__ labe
       if (lab >= 0 && lab < cols) {
         if constexpr (sizeof(T) == 2) tgt = bf2f(p[lab]) * logits_scale; else tgt = p[lab] * logits_scale;
       }
-      stats[row * 3 + 0] = gm;
-      stats[row * 3 + 1] = gs;
-      stats[row * 3 + 2] = tgt;
+      if (peers.world == 0) {
+        stats[row * 3 + 0] = gm;
+        stats[row * 3 + 1] = gs;
+        stats[row * 3 + 2] = tgt;
+      } else {
+        const long long at = ((long long)peers.rank * rows + row) * 3;
+        for (int r = 0; r < peers.world; ++r) {
+          float* dst = peers.p[r] + at;
+          dst[0] = gm;
+          dst[1] = gs;
+          dst[2] = tgt;
+        }
+      }
     }
   }
 }
@@ -70,7 +90,7 @@ __global__ void __launch_bounds__(kThreads)
 ce_grad_kernel(const T* __restrict__ logits, const long long* __restrict__ labels, const float* __restrict__ stats,
                T* __restrict__ grad, float* __restrict__ loss_out, float* __restrict__ z_out, int rows, int cols,
                long long ld, long long ld_grad, long long vocab_begin, float logits_scale, float grad_scale,
-               const float* __restrict__ grad_scale_ptr, float z_coef) {
+               const float* __restrict__ grad_scale_ptr, float z_coef, int slots) {
   constexpr int VN = Vec<T>::N;
   const float gscale = grad_scale * (grad_scale_ptr ? *grad_scale_ptr : 1.f);
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -78,11 +98,19 @@ ce_grad_kernel(const T* __restrict__ logits, const long long* __restrict__ label
     T* g = grad ? grad + (long long)row * ld_grad : nullptr;
     const long long label = labels[row];
     const bool valid = label >= 0;
-    const float m = stats[row * 3 + 0];
-    const float se = stats[row * 3 + 1];
+    // merge the shards' statistics (one slot when the vocabulary is not split)
+    float m = stats[row * 3 + 0], se = stats[row * 3 + 1], target = stats[row * 3 + 2];
+    for (int r = 1; r < slots; ++r) {
+      const float* other = stats + ((long long)r * rows + row) * 3;
+      const float om = other[0];
+      const float nm = fmaxf(m, om);
+      se = se * __expf(m - nm) + other[1] * __expf(om - nm);
+      m = nm;
+      target += other[2];
+    }
     const float lse = m + __logf(se);
     if (threadIdx.x == 0) {
-      if (loss_out) loss_out[row] = valid ? (lse - stats[row * 3 + 2]) : 0.f;
+      if (loss_out) loss_out[row] = valid ? (lse - target) : 0.f;
       if (z_out) z_out[row] = valid ? lse * lse : 0.f;
     }
     if (!g) continue;
@@ -114,31 +142,65 @@ ce_grad_kernel(const T* __restrict__ logits, const long long* __restrict__ label
 
 }  // namespace
 
+static int ce_stats_launch(const void* logits, int dtype, const long long* labels, float* stats, int rows, int cols, long long ld,
+                           long long vocab_begin, float logits_scale, const StatPeers& peers, cudaStream_t stream);
+
 FLB_API int flb_ce_stats(const void* logits, int dtype, const long long* labels, float* stats, int rows, int cols,
                          long long ld, long long vocab_begin, float logits_scale, cudaStream_t stream) {
+  StatPeers none{};
+  return ce_stats_launch(logits, dtype, labels, stats, rows, cols, ld, vocab_begin, logits_scale, none, stream);
+}
+
+// peer_stats[r]: rank r's statistics buffer [world, rows, 3] fp32 (peer-mapped); this rank fills slot `rank` of each.
+FLB_API int flb_ce_stats_exchange(const void* logits, int dtype, const long long* labels, const void* const* peer_stats, int rank, int world,
+                                  int rows, int cols, long long ld, long long vocab_begin, float logits_scale, cudaStream_t stream) {
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) return FLB_ERR_SHAPE;
+  StatPeers peers{};
+  for (int r = 0; r < world; ++r) peers.p[r] = (float*)peer_stats[r];
+  peers.world = world;
+  peers.rank = rank;
+  return ce_stats_launch(logits, dtype, labels, nullptr, rows, cols, ld, vocab_begin, logits_scale, peers, stream);
+}
+
+static int ce_stats_launch(const void* logits, int dtype, const long long* labels, float* stats, int rows, int cols, long long ld,
+                           long long vocab_begin, float logits_scale, const StatPeers& peers, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return FLB_ERR_SHAPE;
   if (dtype == 1) {
     if (ld % 8 || (reinterpret_cast<uintptr_t>(logits) & 15)) return FLB_ERR_SHAPE;
-    ce_stats_kernel<__nv_bfloat16><<<rows, kThreads, 0, stream>>>((const __nv_bfloat16*)logits, labels, stats, rows, cols, ld, vocab_begin, logits_scale);
+    ce_stats_kernel<__nv_bfloat16><<<rows, kThreads, 0, stream>>>((const __nv_bfloat16*)logits, labels, stats, rows, cols, ld, vocab_begin, logits_scale, peers);
   } else {
     if (ld % 4 || (reinterpret_cast<uintptr_t>(logits) & 15)) return FLB_ERR_SHAPE;
-    ce_stats_kernel<float><<<rows, kThreads, 0, stream>>>((const float*)logits, labels, stats, rows, cols, ld, vocab_begin, logits_scale);
+    ce_stats_kernel<float><<<rows, kThreads, 0, stream>>>((const float*)logits, labels, stats, rows, cols, ld, vocab_begin, logits_scale, peers);
   }
   FLB_CHECK_LAUNCH();
   return FLB_OK;
 }
 
+FLB_API int flb_ce_grad_slots(const void* logits, int dtype, const long long* labels, const float* stats, int slots, void* grad,
+                              float* loss_out, float* z_out, int rows, int cols, long long ld, long long ld_grad,
+                              long long vocab_begin, float logits_scale, float grad_scale, const float* grad_scale_ptr,
+                              float z_coef, cudaStream_t stream);
+
 FLB_API int flb_ce_grad(const void* logits, int dtype, const long long* labels, const float* stats, void* grad,
                         float* loss_out, float* z_out, int rows, int cols, long long ld, long long ld_grad,
                         long long vocab_begin, float logits_scale, float grad_scale, const float* grad_scale_ptr,
                         float z_coef, cudaStream_t stream) {
-  if (rows <= 0 || cols <= 0) return FLB_ERR_SHAPE;
+  return flb_ce_grad_slots(logits, dtype, labels, stats, 1, grad, loss_out, z_out, rows, cols, ld, ld_grad, vocab_begin, logits_scale, grad_scale,
+                           grad_scale_ptr, z_coef, stream);
+}
+
+// stats: [slots, rows, 3]; the slots are merged per token.
+FLB_API int flb_ce_grad_slots(const void* logits, int dtype, const long long* labels, const float* stats, int slots, void* grad,
+                              float* loss_out, float* z_out, int rows, int cols, long long ld, long long ld_grad,
+                              long long vocab_begin, float logits_scale, float grad_scale, const float* grad_scale_ptr,
+                              float z_coef, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0 || slots < 1) return FLB_ERR_SHAPE;
   if (dtype == 1) {
     if (ld % 8 || ld_grad % 8) return FLB_ERR_SHAPE;
-    ce_grad_kernel<__nv_bfloat16><<<rows, kThreads, 0, stream>>>((const __nv_bfloat16*)logits, labels, stats, (__nv_bfloat16*)grad, loss_out, z_out, rows, cols, ld, ld_grad, vocab_begin, logits_scale, grad_scale, grad_scale_ptr, z_coef);
+    ce_grad_kernel<__nv_bfloat16><<<rows, kThreads, 0, stream>>>((const __nv_bfloat16*)logits, labels, stats, (__nv_bfloat16*)grad, loss_out, z_out, rows, cols, ld, ld_grad, vocab_begin, logits_scale, grad_scale, grad_scale_ptr, z_coef, slots);
   } else {
     if (ld % 4 || ld_grad % 4) return FLB_ERR_SHAPE;
-    ce_grad_kernel<float><<<rows, kThreads, 0, stream>>>((const float*)logits, labels, stats, (float*)grad, loss_out, z_out, rows, cols, ld, ld_grad, vocab_begin, logits_scale, grad_scale, grad_scale_ptr, z_coef);
+    ce_grad_kernel<float><<<rows, kThreads, 0, stream>>>((const float*)logits, labels, stats, (float*)grad, loss_out, z_out, rows, cols, ld, ld_grad, vocab_begin, logits_scale, grad_scale, grad_scale_ptr, z_coef, slots);
   }
   FLB_CHECK_LAUNCH();
   return FLB_OK;

@@ -197,6 +197,12 @@ class MultiStageModel:
 
             fused_tp.enable_lazy(self._distributed.tensor_group, device)
 
+        # vocabulary-parallel loss statistics exchanged by the loss kernels themselves
+        if ms.fused_collectives and dist_config.tensor_parallel > 1 and symmetric_memory_available(self._distributed.tensor_group, device):
+            from fast_llm_b200.parallel import fused_ce
+
+            fused_ce.enable(self._distributed.tensor_group, device)
+
         def carve(sizes_bytes: list[int], what: str):
             aligned = [(n + 255) // 256 * 256 for n in sizes_bytes]
             arena = SymmetricArena(sum(aligned), self._distributed.data_group, device)

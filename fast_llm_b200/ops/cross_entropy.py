@@ -55,18 +55,34 @@ def cross_entropy_forward_backward(logits: torch.Tensor, labels: torch.Tensor, g
     rows, cols = logits.shape
     dtype_code = 1 if logits.dtype == torch.bfloat16 else 0
     labels = labels.contiguous()
-    stats = torch.empty(rows, 3, dtype=torch.float32, device=logits.device)
-    _lib.check(lib.flb_ce_stats(logits.data_ptr(), dtype_code, labels.data_ptr(), stats.data_ptr(), rows, cols,
-                                logits.stride(0), vocab_begin, logits_scale, _lib.stream_ptr()), "flb_ce_stats")
-    _lib.count_launch()
+    slots = 1
+    fused = None
     if group is not None:
-        # Merge shards: global max, rescaled sum-exp, summed target logit.
-        local_max = stats[:, 0].clone()
-        gmax = local_max.clone()
-        torch.distributed.all_reduce(gmax, op=torch.distributed.ReduceOp.MAX, group=group)
-        packed = torch.stack([stats[:, 1] * torch.exp(local_max - gmax), stats[:, 2]], 0)
-        torch.distributed.all_reduce(packed, group=group)
-        stats = torch.stack([gmax, packed[0], packed[1]], 1).contiguous()
+        from fast_llm_b200.parallel import fused_ce
+
+        context = fused_ce.get(group)
+        fused = context.slots(rows) if context is not None else None
+    if fused is not None:
+        # statistics go straight into every peer's buffer; the gradient kernel merges the shards
+        stats, peer_ptrs = fused
+        slots = context.world
+        _lib.check(lib.flb_ce_stats_exchange(logits.data_ptr(), dtype_code, labels.data_ptr(), peer_ptrs, context.rank, context.world, rows, cols,
+                                             logits.stride(0), vocab_begin, logits_scale, _lib.stream_ptr()), "flb_ce_stats_exchange")
+        _lib.count_launch()
+        context.barrier()
+    else:
+        stats = torch.empty(rows, 3, dtype=torch.float32, device=logits.device)
+        _lib.check(lib.flb_ce_stats(logits.data_ptr(), dtype_code, labels.data_ptr(), stats.data_ptr(), rows, cols,
+                                    logits.stride(0), vocab_begin, logits_scale, _lib.stream_ptr()), "flb_ce_stats")
+        _lib.count_launch()
+        if group is not None:
+            # Merge shards: global max, rescaled sum-exp, summed target logit.
+            local_max = stats[:, 0].clone()
+            gmax = local_max.clone()
+            torch.distributed.all_reduce(gmax, op=torch.distributed.ReduceOp.MAX, group=group)
+            packed = torch.stack([stats[:, 1] * torch.exp(local_max - gmax), stats[:, 2]], 0)
+            torch.distributed.all_reduce(packed, group=group)
+            stats = torch.stack([gmax, packed[0], packed[1]], 1).contiguous()
     loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
     z = torch.empty(rows, dtype=torch.float32, device=logits.device)
     grad = None
@@ -82,9 +98,9 @@ def cross_entropy_forward_backward(logits: torch.Tensor, labels: torch.Tensor, g
         else:
             gs_val = float(grad_scale)
     _lib.check(
-        lib.flb_ce_grad(logits.data_ptr(), dtype_code, labels.data_ptr(), stats.data_ptr(), _lib.ptr(grad),
+        lib.flb_ce_grad_slots(logits.data_ptr(), dtype_code, labels.data_ptr(), stats.data_ptr(), slots, _lib.ptr(grad),
                         loss.data_ptr(), z.data_ptr(), rows, cols, logits.stride(0),
                         grad.stride(0) if grad is not None else logits.stride(0), vocab_begin, logits_scale, gs_val,
-                        _lib.ptr(gs_ptr), z_coef, _lib.stream_ptr()), "flb_ce_grad")
+                        _lib.ptr(gs_ptr), z_coef, _lib.stream_ptr()), "flb_ce_grad_slots")
     _lib.count_launch()
     return loss, z, grad

@@ -86,7 +86,7 @@ class FusedTensorParallel:
         shard_bytes = max_tokens // self.world * max_width * 2
         staging_bytes = max_tokens * max_width * 2
         self._shard_bytes, self._staging_bytes = shard_bytes, staging_bytes
-        self.arena = SymmetricArena(2 * shard_bytes + 2 * staging_bytes, group, device)
+        self.arena = SymmetricArena(2 * shard_bytes + 2 * staging_bytes, self.group, device)
         self._gather_calls = self._scatter_calls = 0
         self.direct_peer_stores = False  # True: register stores instead of TMA tensor stores into the peers' staging slots
         # local landing zone of gathered operands, side stream and per-chunk events for the copy / GEMM pipeline

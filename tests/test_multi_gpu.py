@@ -128,3 +128,85 @@ def test_fused_tensor_parallel_linear_matches_nccl():
         for relative, repeat in errors:
             assert relative < 0.15, errors  # bf16 partial sums are rounded once more on the fused path
             assert repeat == 0.0, errors  # deterministic
+
+
+def _fused_ce_rank_main(rank, world_size, rows, vocab):
+    import torch
+
+    from fast_llm_b200.ops.cross_entropy import cross_entropy_forward_backward, cross_entropy_reference
+    from fast_llm_b200.parallel import fused_ce
+
+    torch.cuda.set_device(rank)
+    torch.distributed.init_process_group("nccl", rank=rank, world_size=world_size, device_id=torch.device("cuda", rank))
+    group = torch.distributed.group.WORLD
+    torch.manual_seed(0)
+    full = (torch.randn(rows, vocab, device="cuda") * 3).bfloat16()
+    labels = torch.randint(0, vocab, (rows,), device="cuda")
+    labels[::7] = -100
+    shard = vocab // world_size
+    local = full[:, rank * shard : (rank + 1) * shard].contiguous()
+    reference = cross_entropy_reference(full.float(), labels, 0.5, 1.0, 1e-4)
+    plain = cross_entropy_forward_backward(local.clone(), labels, 0.5, 1.0, 1e-4, group, rank * shard)
+    context = fused_ce.enable(group, torch.device("cuda", rank))
+    results = []
+    for _ in range(3):  # both halves of the double buffer, and reuse
+        results.append(cross_entropy_forward_backward(local.clone(), labels, 0.5, 1.0, 1e-4, group, rank * shard))
+    torch.cuda.synchronize()
+    context._arena.check_errors()
+    fused_ce.disable(group)
+    out = []
+    for loss, z, grad in results:
+        out.append((float((loss - plain[0]).abs().max()), float((z - plain[1]).abs().max()), float((grad.float() - plain[2].float()).abs().max()),
+                    float((loss - reference[0]).abs().max()),
+                    float((grad.float() - reference[2][:, rank * shard : (rank + 1) * shard]).abs().max())))
+    torch.distributed.barrier()
+    torch.distributed.destroy_process_group()
+    return out
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_cross_entropy_exchange_matches_all_reduce():
+    for per_rank in run_distributed(_fused_ce_rank_main, 2, 777, 4096, timeout=600):
+        for d_loss, d_z, d_grad, d_loss_ref, d_grad_ref in per_rank:
+            assert d_loss < 1e-4 and d_z < 1e-2 and d_grad < 1e-3, per_rank
+            assert d_loss_ref < 2e-2 and d_grad_ref < 2e-2, per_rank
+
+
+def _tp_training_rank_main(rank, world_size, updates, steps):
+    import torch
+
+    from fast_llm_b200.parallel import fused_ce, fused_tp
+    from tests.common import build_trainer, tiny_trainer_config, train_steps
+
+    torch.cuda.set_device(rank)
+    updates = {("model", "distributed", "use_cuda"): True, ("model", "distributed", "compute_dtype"): "bf16",
+               ("model", "distributed", "world_size"): world_size, ("model", "distributed", "rank"): rank,
+               ("model", "distributed", "local_world_size"): world_size, ("model", "distributed", "reproducible_init"): True,
+               ("model", "distributed", "tensor_parallel"): world_size, ("model", "distributed", "sequence_tensor_parallel"): True,
+               ("data", "micro_batch_size"): 512, **updates}
+    trainer, distributed = build_trainer(tiny_trainer_config(updates))
+    losses = train_steps(trainer, steps)
+    torch.cuda.synchronize()
+    group = distributed.tensor_group
+    linear_context, loss_context = fused_tp.get(group), fused_ce.get(group)
+    used = (linear_context is not None and linear_context.max_tokens is not None, loss_context is not None and loss_context._arena is not None)
+    for context in (linear_context, loss_context):
+        arena = getattr(context, "arena", None) or getattr(context, "_arena", None)
+        if arena is not None:
+            arena.check_errors()
+    distributed.shutdown()
+    return losses, used
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tensor_parallel_training_with_fused_collectives():
+    """Two tensor-parallel ranks (sequence-parallel): GEMMs fused with their collectives and the loss statistics exchange
+    over peer memory give the losses of the NCCL path."""
+    steps = 3
+    fused = run_distributed(_tp_training_rank_main, 2, {}, steps, timeout=600)
+    plain = run_distributed(_tp_training_rank_main, 2, {("model", "multi_stage", "fused_collectives"): False}, steps, timeout=600)
+    assert all(r[1] == (True, True) for r in fused), [r[1] for r in fused]
+    assert all(r[1] == (False, False) for r in plain), [r[1] for r in plain]
+    for (lf, _), (lp, _) in zip(fused, plain):
+        assert lf == pytest.approx(lp, rel=2e-2)
+    assert fused[0][0] == pytest.approx(fused[1][0], rel=1e-6)
