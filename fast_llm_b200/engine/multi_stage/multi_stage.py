@@ -203,6 +203,13 @@ class MultiStageModel:
 
             fused_ce.enable(self._distributed.tensor_group, device)
 
+        # sequence-data parallelism: key / value exchange through symmetric memory
+        if (ms.fused_collectives and dist_config.sequence_data_parallel > 1 and dist_config.compute_dtype.torch == torch.bfloat16
+                and symmetric_memory_available(self._distributed.sequence_data_group, device)):
+            from fast_llm_b200.parallel import fused_sdp
+
+            fused_sdp.enable(self._distributed.sequence_data_group, device)
+
         def carve(sizes_bytes: list[int], what: str):
             aligned = [(n + 255) // 256 * 256 for n in sizes_bytes]
             arena = SymmetricArena(sum(aligned), self._distributed.data_group, device)

@@ -218,9 +218,17 @@ class _GatherKV(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, kv, group):
+        from fast_llm_b200.parallel import fused_sdp
+
         ctx.group = group
+        fused = fused_sdp.get(group)
+        ctx.fused = fused if fused is not None and fused.usable(kv) else None
+        if ctx.fused is not None:
+            return ctx.fused.gather(kv)  # peers' slices pulled over NVLink by a copy kernel
         return gather_op(kv, group, 0)
 
     @staticmethod
     def backward(ctx, grad):
+        if ctx.fused is not None:
+            return ctx.fused.reduce_scatter(grad.contiguous()), None  # staged in the owners' buffers, summed in rank order
         return reduce_scatter_op(grad.contiguous(), ctx.group, dim=0), None

@@ -122,6 +122,11 @@ class _FlashAttention(torch.autograd.Function):
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         _flash_attn_varlen_backward(dout.contiguous(), q, k, v, out, lse, dq, dk, dv, cu_q, cu_k, max_q, max_k, dropout_p,
                                     scale, causal, wl, wr, 0.0, None, False, rng_state)
+        # Key rows past the last `cu_k` segment (another sequence-data rank's later tokens) are attended by no query here;
+        # the library leaves them unwritten (with grouped heads it sums an uninitialised staging buffer into them).
+        uncovered = torch.arange(k.shape[0], device=k.device) >= cu_k[-1]
+        dk.masked_fill_(uncovered[:, None, None], 0)
+        dv.masked_fill_(uncovered[:, None, None], 0)
         return dq, dk, dv, None, None, None, None, None, None, None, None
 
 

@@ -210,3 +210,35 @@ def test_tensor_parallel_training_with_fused_collectives():
     for (lf, _), (lp, _) in zip(fused, plain):
         assert lf == pytest.approx(lp, rel=2e-2)
     assert fused[0][0] == pytest.approx(fused[1][0], rel=1e-6)
+
+
+def _sdp_training_rank_main(rank, world_size, updates, steps):
+    import torch
+
+    from fast_llm_b200.parallel import fused_sdp
+    from tests.common import build_trainer, tiny_trainer_config, train_steps
+
+    torch.cuda.set_device(rank)
+    updates = {("model", "distributed", "use_cuda"): True, ("model", "distributed", "compute_dtype"): "bf16",
+               ("model", "distributed", "world_size"): world_size, ("model", "distributed", "rank"): rank,
+               ("model", "distributed", "local_world_size"): world_size, ("model", "distributed", "reproducible_init"): True,
+               ("model", "distributed", "sequence_data_parallel"): world_size, ("data", "micro_batch_size"): 512, **updates}
+    trainer, distributed = build_trainer(tiny_trainer_config(updates))
+    losses = train_steps(trainer, steps)
+    torch.cuda.synchronize()
+    context = fused_sdp.get(distributed.sequence_data_group)
+    used = context is not None and context.arena is not None and context._gathers > 0 and context._scatters > 0
+    if context is not None and context.arena is not None:
+        context.arena.check_errors()
+    distributed.shutdown()
+    return losses, used
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_sequence_data_parallel_exchange_through_symmetric_memory():
+    steps = 3
+    fused = run_distributed(_sdp_training_rank_main, 2, {}, steps, timeout=600)
+    plain = run_distributed(_sdp_training_rank_main, 2, {("model", "multi_stage", "fused_collectives"): False}, steps, timeout=600)
+    assert all(r[1] for r in fused) and not any(r[1] for r in plain)
+    for (lf, _), (lp, _) in zip(fused, plain):
+        assert lf == pytest.approx(lp, rel=1e-2)
