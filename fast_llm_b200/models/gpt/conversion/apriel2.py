@@ -88,7 +88,8 @@ def _mixer_export(mixer) -> dict:
         return out
     if kind == "MambaConfig":
         return {"type": "mamba", "state_size": mixer.state_size, "d_inner": mixer.d_inner, "d_xb": mixer.d_xb, "dt_rank": mixer.dt_rank,
-                "add_linear_biases": mixer.add_linear_biases, "d_conv": mixer.convolution_layer.kernel_size,
+                "add_linear_biases": mixer.add_linear_biases, "repeat_kv_before_conv": mixer.repeat_kv_before_conv,
+                "d_conv": mixer.convolution_layer.kernel_size,
                 "conv_bias": _enabled(mixer.convolution_layer, mixer.add_linear_biases), "dt_proj_bias": _enabled(mixer.dt_layer, mixer.add_linear_biases)}
     if kind == "GatedDeltaNetConfig":
         return {"type": "gdn", "value_heads": mixer.value_heads, "key_heads": mixer.key_heads, "key_head_dim": mixer.key_head_dim,
@@ -112,7 +113,7 @@ def _mixer_import(h: dict) -> dict:
                "rotary": _rotary_import(h.get("rotary", {"type": "mistral_1d"})), "add_linear_biases": h.get("add_linear_biases", True)}
         return out
     if kind == "mamba":
-        out = {"type": "mamba", **_copy_keys(h, ("state_size", "d_inner", "d_xb", "dt_rank", "add_linear_biases"))}
+        out = {"type": "mamba", **_copy_keys(h, ("state_size", "d_inner", "d_xb", "dt_rank", "add_linear_biases", "repeat_kv_before_conv"))}
         convolution, dt_layer = {}, {}
         if "d_conv" in h:
             convolution["kernel_size"] = h["d_conv"]
@@ -235,6 +236,15 @@ class Apriel2HuggingfaceCheckpointHandler(HuggingfaceStateDictCheckpointHandler)
         from fast_llm_b200.models.gpt.config import GPTModelConfig
 
         return GPTModelConfig
+
+    @classmethod
+    def get_extra_files(cls):
+        """Stand-alone modelling code that `transformers` loads from the exported directory (`auto_map`)."""
+        import pathlib
+
+        from fast_llm_b200.external_models.apriel2 import configuration_apriel2, modeling_apriel2
+
+        return [pathlib.Path(configuration_apriel2.__file__), pathlib.Path(modeling_apriel2.__file__)]
 
     @classmethod
     def export_config(cls, c) -> dict:

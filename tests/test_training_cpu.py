@@ -325,6 +325,18 @@ def test_apriel2_round_trip(tmp_path):
     from fast_llm_b200.models.gpt.model import GPTModel
 
     GPTModel.from_pretrained(CheckpointLoadConfig(path=tmp_path / "apriel2_text", format="auto"), use_cpu=True)
+    # the stand-alone modelling code shipped with the checkpoint gives the same logits (all five mixer kinds)
+    from fast_llm_b200.engine.inference.runner import InferenceRunner
+    from fast_llm_b200.external_models.apriel2.modeling_apriel2 import Apriel2ForCausalLM
+
+    assert (tmp_path / "apriel2_text" / "modeling_apriel2.py").exists() and (tmp_path / "apriel2_text" / "configuration_apriel2.py").exists()
+    external = Apriel2ForCausalLM.from_pretrained(str(tmp_path / "apriel2_text"), torch_dtype=torch.float32)
+    tokens = torch.randint(0, 512, (1, 24))
+    with torch.no_grad():
+        logits = external(input_ids=tokens).logits
+    runner = InferenceRunner(GPTModel.from_pretrained(CheckpointLoadConfig(path=tmp_path / "apriel2_text", format="apriel2_text"), use_cpu=True))
+    runner.setup()
+    torch.testing.assert_close(logits[0], runner.forward_tokens(tokens[0]), rtol=2e-4, atol=2e-4)
 
 
 @pytest.mark.parametrize("moe", [False, True])
