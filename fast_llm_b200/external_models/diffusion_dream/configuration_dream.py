@@ -1,0 +1,17 @@
+"""Configuration of Dream: a masked-diffusion language model on a Qwen2 decoder.
+
+Stand-alone file: it is copied next to exported checkpoints and loaded by `transformers` with `trust_remote_code`.
+"""
+
+from transformers.models.qwen2.configuration_qwen2 import Qwen2Config
+
+
+class DreamConfig(Qwen2Config):
+    model_type = "Dream"
+
+    def __init__(self, mask_token_id: int | None = None, bidirectional: bool = True, **kwargs):
+        super().__init__(**kwargs)
+        # token that stands for "not generated yet" during sampling (default: the last id of the vocabulary)
+        self.mask_token_id = self.vocab_size - 1 if mask_token_id is None else mask_token_id
+        # every position attends to every other one; False gives the causal decoder the weights were trained as
+        self.bidirectional = bidirectional

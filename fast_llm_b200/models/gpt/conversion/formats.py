@@ -408,6 +408,12 @@ class DiffusionDreamHuggingfaceCheckpointHandler(Qwen2HuggingfaceCheckpointHandl
         super()._export_extra(c, out)
         out["auto_map"] = {"AutoConfig": "configuration_dream.DreamConfig", "AutoModel": "modeling_dream.DreamModel"}
 
+    @classmethod
+    def get_extra_files(cls):
+        from fast_llm_b200.external_models.diffusion_dream import configuration_dream, modeling_dream
+
+        return [pathlib.Path(configuration_dream.__file__), pathlib.Path(modeling_dream.__file__)]
+
 
 class DiffusionLlamaHuggingfaceCheckpointHandler(LlamaHuggingfaceCheckpointHandler):
     format = DiffusionLlamaCheckpointFormat
@@ -417,6 +423,12 @@ class DiffusionLlamaHuggingfaceCheckpointHandler(LlamaHuggingfaceCheckpointHandl
     @classmethod
     def _export_extra(cls, c, out):
         out["auto_map"] = {"AutoConfig": "configuration_diffusion_llama.DiffusionLlamaConfig", "AutoModel": "modeling_diffusion_llama.DiffusionLlamaModel"}
+
+    @classmethod
+    def get_extra_files(cls):
+        from fast_llm_b200.external_models.diffusion_llama import configuration_diffusion_llama, modeling_diffusion_llama
+
+        return [pathlib.Path(configuration_diffusion_llama.__file__), pathlib.Path(modeling_diffusion_llama.__file__)]
 
 
 class AprielHybridSSMHuggingfaceCheckpointHandler(MistralHuggingfaceCheckpointHandler):
@@ -471,6 +483,12 @@ class AprielHybridSSMHuggingfaceCheckpointHandler(MistralHuggingfaceCheckpointHa
     @staticmethod
     def _enabled(bias_config, default: bool) -> bool:
         return default if bias_config.enabled is None else bias_config.enabled
+
+    @classmethod
+    def get_extra_files(cls):
+        from fast_llm_b200.external_models.apriel_hybrid_ssm import configuration_apriel_hybrid_ssm, modeling_apriel_hybrid_ssm
+
+        return [pathlib.Path(configuration_apriel_hybrid_ssm.__file__), pathlib.Path(modeling_apriel_hybrid_ssm.__file__)]
 
     @classmethod
     def import_config(cls, h: dict) -> dict:

@@ -281,8 +281,20 @@ def test_mtp_llama_and_apriel_hybrid_round_trip(tmp_path):
     mamba_block["mixer"] = {"type": "mamba", "d_inner": 64, "d_xb": 32, "state_size": 8, "dt_rank": 4, "add_linear_biases": False,
                             "convolution_layer": {"bias": {"enabled": True}}, "dt_layer": {"bias": {"enabled": True}}}
     hybrid["decoder"] = {"type": "pattern", "blocks": {"t": attention_block, "m2": mamba_block}, "pattern": ["t", "m2", "m2"], "num_blocks": 3}
+    gdn_block = copy.deepcopy(attention_block)
+    gdn_block["mixer"] = {"type": "gdn", "value_heads": 4, "key_heads": 2, "key_head_dim": 8, "value_head_dim": 8, "convolution_layer": {"kernel_size": 3}}
+    hybrid["decoder"] = {"type": "pattern", "blocks": {"t": attention_block, "m2": mamba_block, "gdn": gdn_block}, "pattern": ["t", "m2", "gdn"], "num_blocks": 3}
     config = _round_trip(tmp_path, hybrid, "apriel_hybrid_ssm")
-    assert config["hybrid_block_layout"] == ["t", "m2", "m2"] and config["ssm_cfg"]["d_state"] == 8
+    assert config["hybrid_block_layout"] == ["t", "m2", "gdn"] and config["ssm_cfg"]["d_state"] == 8
+    from fast_llm_b200.external_models.apriel_hybrid_ssm.modeling_apriel_hybrid_ssm import AprielHybridSSMForCausalLM
+
+    assert (tmp_path / "apriel_hybrid_ssm" / "modeling_apriel_hybrid_ssm.py").exists()
+    external = AprielHybridSSMForCausalLM.from_pretrained(str(tmp_path / "apriel_hybrid_ssm"), torch_dtype=torch.float32)
+    with torch.no_grad():
+        logits = external(input_ids=tokens).logits
+    runner = InferenceRunner(GPTModel.from_pretrained(CheckpointLoadConfig(path=tmp_path / "apriel_hybrid_ssm", format="apriel_hybrid_ssm"), use_cpu=True))
+    runner.setup()
+    torch.testing.assert_close(logits[0], runner.forward_tokens(tokens[0]), rtol=2e-4, atol=2e-4)
 
 
 def test_apriel2_round_trip(tmp_path):
@@ -399,6 +411,45 @@ def test_gemma4_round_trip(tmp_path, moe):
     if moe:
         assert shapes["model.layers.0.experts.gate_up_proj"] == [4, 64, hidden] and shapes["model.layers.0.experts.down_proj"] == [4, hidden, 32]
         assert "model.layers.0.router.per_expert_scale" in shapes and "model.layers.0.pre_feedforward_layernorm_2.weight" in shapes
+
+
+@pytest.mark.parametrize("format_name", ["diffusion_llama", "dream"])
+def test_diffusion_formats_round_trip(tmp_path, format_name):
+    """The diffusion formats carry a Llama / Qwen2 decoder; the stand-alone code shipped with them reproduces our logits when
+    told to stay causal, and samples by iterative unmasking with bidirectional attention."""
+    import copy
+    import importlib
+
+    from tests.common import TINY_BASE_MODEL
+
+    base = copy.deepcopy(TINY_BASE_MODEL)
+    if format_name == "dream":  # Qwen2-style: biases on the query / key / value projections only
+        mixer = base["decoder"]["block"]["mixer"]
+        mixer["add_linear_biases"] = False
+        for layer in ("query_layer", "key_layer", "value_layer"):
+            mixer[layer] = {"bias": {"enabled": True}}
+        mixer["dense_layer"] = {"bias": {"enabled": False}}
+    config = _round_trip(tmp_path, base, format_name)
+    assert config["model_type"] == ("Dream" if format_name == "dream" else "diffusion_llama")
+    module_name, class_name = ("diffusion_dream.modeling_dream", "DreamModel") if format_name == "dream" else ("diffusion_llama.modeling_diffusion_llama", "DiffusionLlamaModel")
+    model_class = getattr(importlib.import_module(f"fast_llm_b200.external_models.{module_name}"), class_name)
+    assert (tmp_path / format_name / (module_name.split(".")[1] + ".py")).exists()
+    from fast_llm_b200.engine.checkpoint.config import CheckpointLoadConfig
+    from fast_llm_b200.engine.inference.runner import InferenceRunner
+    from fast_llm_b200.models.gpt.model import GPTModel
+
+    tokens = torch.randint(0, 500, (1, 24))
+    causal = model_class.from_pretrained(str(tmp_path / format_name), torch_dtype=torch.float32, bidirectional=False)
+    with torch.no_grad():
+        logits = causal(input_ids=tokens).logits
+    runner = InferenceRunner(GPTModel.from_pretrained(CheckpointLoadConfig(path=tmp_path / format_name, format=format_name), use_cpu=True))
+    runner.setup()
+    torch.testing.assert_close(logits[0], runner.forward_tokens(tokens[0]), rtol=2e-4, atol=2e-4)
+    model = model_class.from_pretrained(str(tmp_path / format_name), torch_dtype=torch.float32)
+    with torch.no_grad():
+        assert (model(input_ids=tokens).logits - logits).abs().max() > 1e-3  # bidirectional attention sees later tokens
+    out = model.diffusion_generate(tokens[:, :8], max_new_tokens=10, steps=4)
+    assert out.shape == (1, 18) and (out[:, :8] == tokens[:, :8]).all() and (out != model.config.mask_token_id).all()
 
 
 def test_checkpoint_surgery_tools(tmp_path):
