@@ -262,6 +262,28 @@ def bench_ssm(results):
     results.append(r)
     print(json.dumps(r), flush=True)
 
+    # gated DeltaNet recurrence (chunked PyTorch restatement: batched matmuls + one triangular solve per chunk), 32 heads of 128
+    from fast_llm_b200.ops.ssm import chunk_delta_rule
+
+    heads, dk = 32, 128
+    q, k, v = (torch.randn(tokens, heads, dk, device=dev).bfloat16().requires_grad_() for _ in range(3))
+    log_decay = (-torch.rand(tokens, heads, device=dev) * 0.1).requires_grad_()
+    beta = torch.rand(tokens, heads, device=dev).requires_grad_()
+    go = torch.randn(tokens, heads, dk, device=dev).bfloat16()
+
+    def gdn_fwd():
+        out[0] = chunk_delta_rule(q, k, v, log_decay, beta, None, normalize_qk=True)
+
+    ms = time_op(gdn_fwd, iters=5)
+    flops = 2.0 * tokens * heads * dk * dk * 3  # state update, read and query per token (the recurrence itself)
+    r = {"op": "gdn_chunk_delta_rule_fwd", "ms": ms, "tflops": flops / ms / 1e9, "peak_kind": kind, "note": "PyTorch ops (cuBLAS batched matmuls), no custom kernel"}
+    results.append(r)
+    print(json.dumps(r), flush=True)
+    ms = time_op(lambda: torch.autograd.grad(out[0], (q, k, v, log_decay, beta), go.to(out[0].dtype), retain_graph=True), iters=5)
+    r = {"op": "gdn_chunk_delta_rule_bwd", "ms": ms, "tflops": 2 * flops / ms / 1e9, "peak_kind": kind, "note": "recomputes every chunk from its checkpointed boundary state"}
+    results.append(r)
+    print(json.dumps(r), flush=True)
+
 
 def profile_attention():
     """Small fixed workload for an ncu capture: two forward + backward launches of attention at the Mistral-7B shape."""
