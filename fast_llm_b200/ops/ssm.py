@@ -360,14 +360,89 @@ def _delta_rule_step(state, chunk_in, shared):
     return out.transpose(0, 1).to(chunk_in[2].dtype), new_state
 
 
+def _chunk_layout(boundaries: list[int], chunk: int, device):
+    """Cut every document into chunks of `chunk` tokens (the last one padded).  Returns the [chunks, chunk] token index of
+    every slot (-1: padding) and, per chunk, whether it starts a document."""
+    import numpy as np
+
+    rows, first = [], []
+    for begin, end in zip(boundaries[:-1], boundaries[1:]):
+        for lo in range(begin, end, chunk):
+            row = np.full(chunk, -1, dtype=np.int64)
+            row[: min(chunk, end - lo)] = np.arange(lo, min(lo + chunk, end))
+            rows.append(row)
+            first.append(lo == begin)
+    index = torch.from_numpy(np.stack(rows)) if rows else torch.zeros(0, chunk, dtype=torch.int64)
+    return index.to(device), first
+
+
+def _delta_rule_all_chunks(q, k, v, g, beta, boundaries: list[int], chunk: int) -> torch.Tensor:
+    """Scalar-decay delta rule with everything that does not depend on the carried state computed for ALL chunks at once.
+
+    With S the state entering a chunk, the corrected values are U = U0 - W S where (I + Lmat) [U0 | W] = [V | K o Gamma]
+    (one batched unit-triangular solve), so
+        out   = QK (beta U0) + (Q o Gamma - QK (beta W)) S
+        S_out = decay S - (Kout^T beta W) S + Kout^T beta U0
+    and only the last line is sequential: one [dk, dk] x [dk, dv] product per head and chunk."""
+    device, out_dtype = q.device, v.dtype
+    index, first = _chunk_layout(boundaries, chunk, device)
+    chunks = index.shape[0]
+    valid = index >= 0
+    gather = index.clamp(min=0)
+
+    def cut(t):  # [tokens, heads, ...] -> [chunks, heads, chunk, ...], zero in the padding
+        picked = t.float()[gather]
+        picked = picked * valid.view(chunks, chunk, *([1] * (picked.dim() - 2)))
+        return picked.transpose(1, 2)
+
+    qc, kc, vc = cut(q), cut(k), cut(v)  # [C, h, L, d]
+    gc, bc = cut(g), cut(beta)  # [C, h, L]
+    cum = gc.cumsum(-1)
+    low = _lower_mask(chunk, device, strict=False)
+    strict = _lower_mask(chunk, device, strict=True)
+    zero = torch.zeros((), device=device)
+    pair = torch.where(low, (cum[..., :, None] - cum[..., None, :]).clamp(max=0.0).exp(), zero)  # [C, h, t, s]
+    kk = (kc @ kc.transpose(-1, -2)) * pair
+    qk = (qc @ kc.transpose(-1, -2)) * pair
+    grow = cum.exp()[..., None]
+    system = torch.eye(chunk, device=device) + torch.where(strict, kk * bc[..., None, :], zero)
+    solved = torch.linalg.solve_triangular(system, torch.cat([vc, kc * grow], dim=-1), upper=False, unitriangular=True)
+    dv = vc.shape[-1]
+    values = solved[..., :dv] * bc[..., None]  # beta U0
+    reads = solved[..., dv:] * bc[..., None]  # beta W
+    out_local = qk @ values
+    q_state = qc * grow - qk @ reads
+    k_out = (kc * (cum[..., -1:] - cum).exp()[..., None]).transpose(-1, -2)  # [C, h, dk, L]
+    write = k_out @ values  # [C, h, dk, dv]
+    mix = k_out @ reads  # [C, h, dk, dk]
+    decay = cum[..., -1].exp()[..., None, None]  # [C, h, 1, 1]
+    heads, dk = qc.shape[1], qc.shape[-1]
+    state = torch.zeros(heads, dk, dv, dtype=torch.float32, device=device)
+    states = []
+    # unbind once: indexing inside the loop would make autograd build a full-size zero tensor per chunk and operand
+    for c, (decay_c, mix_c, write_c) in enumerate(zip(decay.unbind(0), mix.unbind(0), write.unbind(0))):
+        if first[c]:
+            state = torch.zeros_like(state)
+        states.append(state)
+        state = torch.baddbmm(state * decay_c, mix_c, state, alpha=-1.0) + write_c
+    out = out_local + q_state @ torch.stack(states) if chunks else out_local
+    return out.transpose(1, 2)[valid].to(out_dtype)
+
+
 def chunk_delta_rule(q, k, v, g, beta, cu_seqlens=None, chunk: int = 64, normalize_qk: bool = True, scale: float | None = None) -> torch.Tensor:
     """q, k [tokens, heads, dk]; v [tokens, heads, dv]; g [tokens, heads(, dk)] log decay; beta [tokens, heads] -> [tokens, heads, dv]."""
     if normalize_qk:
         q, k = l2_normalize(q.float()), l2_normalize(k.float())
     q = q * (q.shape[-1] ** -0.5 if scale is None else scale)
     heads, dk, dv = q.shape[1], q.shape[2], v.shape[2]
-    if g.dim() == 3:
-        chunk = min(chunk, 32)  # the pairwise per-channel decay tensor is [L, L, heads, dk]
+    if g.dim() == 2:
+        # scalar decay per head (gated DeltaNet): the chunk-local work of all chunks is batched
+        total = q.shape[0]
+        boundaries = [0, total] if cu_seqlens is None else [int(b) for b in cu_seqlens.tolist()]
+        if boundaries[-1] < total:  # trailing padding forms its own document
+            boundaries.append(total)
+        return _delta_rule_all_chunks(q, k, v, g, beta, boundaries, chunk)
+    chunk = min(chunk, 32)  # the pairwise per-channel decay tensor is [L, L, heads, dk]
     return chunked_scan(_delta_rule_step, (heads, dk, dv), [q, k, v, g, beta], [], cu_seqlens, chunk)
 
 
