@@ -321,45 +321,6 @@ def l2_normalize(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
     return x * torch.rsqrt((x * x).sum(-1, keepdim=True) + eps)
 
 
-def _delta_rule_step(state, chunk_in, shared):
-    """One chunk of S_t = Decay_t S_{t-1} + beta_t k_t (v_t - k_t^T Decay_t S_{t-1})^T ; o_t = S_t^T q_t.
-
-    state [h, dk, dv]; q, k [L, h, dk]; v [L, h, dv]; g [L, h] or [L, h, dk] (log decay); beta [L, h].
-    With u_t the corrected values, (I + Lmat) U = V - (K o Gamma) S_0 where Lmat[t, s] = beta_s <k_t, k_s>_{decay(t, s)} (s < t).
-    """
-    q, k, v, g, beta = (t.float() for t in chunk_in)
-    length = q.shape[0]
-    per_channel = g.dim() == 3
-    cum = g.cumsum(0)  # inclusive
-    low = _lower_mask(length, q.device, strict=False)
-    if per_channel:
-        pair = torch.where(low[:, :, None, None], (cum[:, None] - cum[None, :]).clamp(max=0.0).exp(), torch.zeros((), device=q.device))
-        kk = torch.einsum("thd,shd,tshd->hts", k, k, pair)
-        qk = torch.einsum("thd,shd,tshd->hts", q, k, pair)
-        k_in = k * cum.exp()  # reads of the incoming state
-        q_in = q * cum.exp()
-        k_out = k * (cum[-1:] - cum).exp()  # writes carried to the chunk end
-        state_decay = cum[-1].exp()[:, :, None]
-    else:
-        pair = torch.where(low[:, :, None], (cum[:, None] - cum[None, :]).clamp(max=0.0).exp(), torch.zeros((), device=q.device))  # [t, s, h]
-        pair = pair.permute(2, 0, 1)
-        kk = torch.einsum("thd,shd->hts", k, k) * pair
-        qk = torch.einsum("thd,shd->hts", q, k) * pair
-        k_in = k * cum.exp()[:, :, None]
-        q_in = q * cum.exp()[:, :, None]
-        k_out = k * (cum[-1:] - cum).exp()[:, :, None]
-        state_decay = cum[-1].exp()[:, None, None]
-    beta_h = beta.t()  # [h, L]
-    strict = _lower_mask(length, q.device, strict=True)
-    system = torch.eye(length, device=q.device)[None] + torch.where(strict[None], kk * beta_h[:, None, :], torch.zeros((), device=q.device))
-    rhs = v.transpose(0, 1) - torch.einsum("thd,hde->hte", k_in, state)  # [h, L, dv]
-    u = torch.linalg.solve_triangular(system, rhs, upper=False, unitriangular=True)
-    ub = u * beta_h[:, :, None]
-    out = torch.einsum("thd,hde->hte", q_in, state) + torch.einsum("hts,hse->hte", qk, ub)
-    new_state = state * state_decay + torch.einsum("shd,hse->hde", k_out, ub)
-    return out.transpose(0, 1).to(chunk_in[2].dtype), new_state
-
-
 def _chunk_layout(boundaries: list[int], chunk: int, device):
     """Cut every document into chunks of `chunk` tokens (the last one padded).  Returns the [chunks, chunk] token index of
     every slot (-1: padding) and, per chunk, whether it starts a document."""
@@ -377,7 +338,7 @@ def _chunk_layout(boundaries: list[int], chunk: int, device):
 
 
 def _delta_rule_all_chunks(q, k, v, g, beta, boundaries: list[int], chunk: int) -> torch.Tensor:
-    """Scalar-decay delta rule with everything that does not depend on the carried state computed for ALL chunks at once.
+    """Delta rule with everything that does not depend on the carried state computed for ALL chunks at once.
 
     With S the state entering a chunk, the corrected values are U = U0 - W S where (I + Lmat) [U0 | W] = [V | K o Gamma]
     (one batched unit-triangular solve), so
@@ -396,15 +357,28 @@ def _delta_rule_all_chunks(q, k, v, g, beta, boundaries: list[int], chunk: int) 
         return picked.transpose(1, 2)
 
     qc, kc, vc = cut(q), cut(k), cut(v)  # [C, h, L, d]
-    gc, bc = cut(g), cut(beta)  # [C, h, L]
-    cum = gc.cumsum(-1)
+    gc, bc = cut(g), cut(beta)  # [C, h, L] (or [C, h, L, dk] for a per-channel decay), [C, h, L]
+    per_channel = gc.dim() == 4
+    cum = gc.cumsum(2)
     low = _lower_mask(chunk, device, strict=False)
     strict = _lower_mask(chunk, device, strict=True)
     zero = torch.zeros((), device=device)
-    pair = torch.where(low, (cum[..., :, None] - cum[..., None, :]).clamp(max=0.0).exp(), zero)  # [C, h, t, s]
-    kk = (kc @ kc.transpose(-1, -2)) * pair
-    qk = (qc @ kc.transpose(-1, -2)) * pair
-    grow = cum.exp()[..., None]
+    if per_channel:
+        # decay between two tokens differs per key channel: weight every product k_t[d] k_s[d] separately
+        pair = torch.where(low[:, :, None], (cum[:, :, :, None] - cum[:, :, None, :]).clamp(max=0.0).exp(), zero)  # [C, h, t, s, d]
+        keys = kc[:, :, None, :, :] * pair  # k_s[d] * decay(t, s)[d]; plain products and sums: einsum maps this to tiny GEMMs
+        kk = (keys * kc[:, :, :, None, :]).sum(-1)
+        qk = (keys * qc[:, :, :, None, :]).sum(-1)
+        grow = cum.exp()
+        carry = (cum[:, :, -1:] - cum).exp()
+        decay = cum[:, :, -1].exp()[..., None]  # [C, h, dk, 1]
+    else:
+        pair = torch.where(low, (cum[..., :, None] - cum[..., None, :]).clamp(max=0.0).exp(), zero)  # [C, h, t, s]
+        kk = (kc @ kc.transpose(-1, -2)) * pair
+        qk = (qc @ kc.transpose(-1, -2)) * pair
+        grow = cum.exp()[..., None]
+        carry = (cum[..., -1:] - cum).exp()[..., None]
+        decay = cum[..., -1].exp()[..., None, None]  # [C, h, 1, 1]
     system = torch.eye(chunk, device=device) + torch.where(strict, kk * bc[..., None, :], zero)
     solved = torch.linalg.solve_triangular(system, torch.cat([vc, kc * grow], dim=-1), upper=False, unitriangular=True)
     dv = vc.shape[-1]
@@ -412,10 +386,9 @@ def _delta_rule_all_chunks(q, k, v, g, beta, boundaries: list[int], chunk: int) 
     reads = solved[..., dv:] * bc[..., None]  # beta W
     out_local = qk @ values
     q_state = qc * grow - qk @ reads
-    k_out = (kc * (cum[..., -1:] - cum).exp()[..., None]).transpose(-1, -2)  # [C, h, dk, L]
+    k_out = (kc * carry).transpose(-1, -2)  # [C, h, dk, L]
     write = k_out @ values  # [C, h, dk, dv]
     mix = k_out @ reads  # [C, h, dk, dk]
-    decay = cum[..., -1].exp()[..., None, None]  # [C, h, 1, 1]
     heads, dk = qc.shape[1], qc.shape[-1]
     state = torch.zeros(heads, dk, dv, dtype=torch.float32, device=device)
     states = []
@@ -435,15 +408,13 @@ def chunk_delta_rule(q, k, v, g, beta, cu_seqlens=None, chunk: int = 64, normali
         q, k = l2_normalize(q.float()), l2_normalize(k.float())
     q = q * (q.shape[-1] ** -0.5 if scale is None else scale)
     heads, dk, dv = q.shape[1], q.shape[2], v.shape[2]
-    if g.dim() == 2:
-        # scalar decay per head (gated DeltaNet): the chunk-local work of all chunks is batched
-        total = q.shape[0]
-        boundaries = [0, total] if cu_seqlens is None else [int(b) for b in cu_seqlens.tolist()]
-        if boundaries[-1] < total:  # trailing padding forms its own document
-            boundaries.append(total)
-        return _delta_rule_all_chunks(q, k, v, g, beta, boundaries, chunk)
-    chunk = min(chunk, 32)  # the pairwise per-channel decay tensor is [L, L, heads, dk]
-    return chunked_scan(_delta_rule_step, (heads, dk, dv), [q, k, v, g, beta], [], cu_seqlens, chunk)
+    if g.dim() == 3:
+        chunk = min(chunk, 32)  # the pairwise per-channel decay tensor is [chunks, heads, L, L, dk]
+    total = q.shape[0]
+    boundaries = [0, total] if cu_seqlens is None else [int(b) for b in cu_seqlens.tolist()]
+    if boundaries[-1] < total:  # trailing padding forms its own document
+        boundaries.append(total)
+    return _delta_rule_all_chunks(q, k, v, g, beta, boundaries, chunk)
 
 
 def delta_rule_reference(q, k, v, g, beta, cu_seqlens=None, normalize_qk: bool = True, scale: float | None = None) -> torch.Tensor:

@@ -284,6 +284,21 @@ def bench_ssm(results):
     results.append(r)
     print(json.dumps(r), flush=True)
 
+    # Kimi delta attention: the same recurrence with a decay per key channel (chunks of 32, pairwise decays kept per channel)
+    log_decay_kda = (-torch.rand(tokens, heads, dk, device=dev) * 0.1).requires_grad_()
+
+    def kda_fwd():
+        out[0] = chunk_delta_rule(q, k, v, log_decay_kda, beta, None, normalize_qk=True)
+
+    ms = time_op(kda_fwd, iters=3)
+    r = {"op": "kda_chunk_delta_rule_fwd", "ms": ms, "tflops": flops / ms / 1e9, "peak_kind": kind, "note": "PyTorch ops, no custom kernel"}
+    results.append(r)
+    print(json.dumps(r), flush=True)
+    ms = time_op(lambda: torch.autograd.grad(out[0], (q, k, v, log_decay_kda, beta), go.to(out[0].dtype), retain_graph=True), iters=3)
+    r = {"op": "kda_chunk_delta_rule_bwd", "ms": ms, "tflops": 2 * flops / ms / 1e9, "peak_kind": kind, "note": "autograd"}
+    results.append(r)
+    print(json.dumps(r), flush=True)
+
 
 def profile_attention():
     """Small fixed workload for an ncu capture: two forward + backward launches of attention at the Mistral-7B shape."""
