@@ -738,3 +738,146 @@ FLB_API int flb_selective_scan_bwd(const void* x, const void* dt, const float* a
     default: return scan_backward<32>(p, g, chunk_start, chunk_decay, chunk_adjoint, checkpoints, stream);
   }
 }
+
+// ----------------------------------------------------------------------------------------------------------------------
+// delta-rule state recurrence across chunks
+// ----------------------------------------------------------------------------------------------------------------------
+// The chunked delta rule (gated DeltaNet, Kimi delta attention) reduces, per head, to
+//     S_{c+1} = decay_c o S_c - mix_c S_c + write_c          S: [dk, dv], mix_c: [dk, dk], decay_c: scalar or one per row
+// with S reset to zero at chunks that start a document.  Everything else is batched over chunks; this is the only
+// sequential part.  Columns of S evolve independently, so a block owns 32 columns of one head and walks the chunks with its
+// [dk, 32] slice in shared memory.  REVERSE runs the adjoint:  A_c = grad_c + decay_c o A_{c+1} - mix_c^T A_{c+1}, where A_{c+1}
+// is dropped if chunk c + 1 starts a document; it emits A_{c+1} (the adjoint of the state LEAVING chunk c) for every chunk.
+namespace {
+constexpr int kStateCols = 32;      // columns of S per block
+constexpr int kStateThreads = 256;  // (dk / RPT... rows) x 8 column groups of 4; every thread owns RPT x 4 rows x 4 columns
+
+// dk = 32 * RPT.  Shared memory: mix_c [dk][dk] (natural layout, loaded with coalesced 16-byte loads) and two copies of the
+// block's [dk][32] slice of S.  Per step of the contraction a thread reads 16-byte vectors only: mix (one row, four contraction
+// indices; or for the adjoint four rows, one index) and the matching rows of S, and does 16 to 64 multiply-adds on them.
+template <int RPT, bool REVERSE>
+__global__ void __launch_bounds__(kStateThreads) delta_state_kernel(const float* __restrict__ decay, const float* __restrict__ mix,
+                                                                    const float* __restrict__ add, const unsigned char* __restrict__ first,
+                                                                    float* __restrict__ out, int chunks, int heads, int dv, int decay_per_row) {
+  constexpr int DK = 32 * RPT;
+  extern __shared__ __align__(16) float state_smem[];
+  float* mix_s = state_smem;                 // [DK][DK]
+  float* current = mix_s + DK * DK;          // [DK][32]
+  float* next = current + DK * kStateCols;
+  const int head = blockIdx.x, col0 = blockIdx.y * kStateCols;
+  const int cg = threadIdx.x % 8, rg = threadIdx.x / 8;  // column group (4 columns) and row group
+  // 32 row groups x (DK / 32) rows each = DK rows; a thread owns rows rg * RPT .. rg * RPT + RPT - 1
+  const int r_first = rg * RPT;
+  for (int i = threadIdx.x; i < DK * kStateCols; i += kStateThreads) current[i] = 0.f;
+  __syncthreads();
+  for (int step = 0; step < chunks; ++step) {
+    const int c = REVERSE ? chunks - 1 - step : step;
+    const long long ch = (long long)c * heads + head;
+    const float4* mix_c = reinterpret_cast<const float4*>(mix + ch * DK * DK);
+    const float* add_c = add + ch * DK * dv;
+    float* out_c = out + ch * DK * dv;
+    // stage mix_c
+    for (int i = threadIdx.x; i < DK * DK / 4; i += kStateThreads) reinterpret_cast<float4*>(mix_s)[i] = mix_c[i];
+    // what enters this step: zero across a document start (forward: chunk c starts one; adjoint: chunk c + 1 does)
+    const bool cut = REVERSE ? (c + 1 < chunks && first[c + 1]) : first[c];
+    if (cut) {
+      for (int i = threadIdx.x; i < DK * kStateCols; i += kStateThreads) current[i] = 0.f;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < DK * kStateCols / 4; i += kStateThreads) {
+      const int row = i / (kStateCols / 4), c4 = i % (kStateCols / 4);
+      *reinterpret_cast<float4*>(out_c + (long long)row * dv + col0 + c4 * 4) = reinterpret_cast<const float4*>(current)[i];
+    }
+    float acc[RPT][4];
+#pragma unroll
+    for (int r = 0; r < RPT; ++r)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[r][q] = 0.f;
+    if (!REVERSE) {
+#pragma unroll 2
+      for (int j = 0; j < DK; j += 4) {
+        float4 s[4];
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) s[jj] = *reinterpret_cast<const float4*>(current + (j + jj) * kStateCols + cg * 4);
+#pragma unroll
+        for (int r = 0; r < RPT; ++r) {
+          const float4 m = *reinterpret_cast<const float4*>(mix_s + (r_first + r) * DK + j);
+          const float mv[4] = {m.x, m.y, m.z, m.w};
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            acc[r][0] = fmaf(mv[jj], s[jj].x, acc[r][0]);
+            acc[r][1] = fmaf(mv[jj], s[jj].y, acc[r][1]);
+            acc[r][2] = fmaf(mv[jj], s[jj].z, acc[r][2]);
+            acc[r][3] = fmaf(mv[jj], s[jj].w, acc[r][3]);
+          }
+        }
+      }
+    } else {
+#pragma unroll 4
+      for (int j = 0; j < DK; ++j) {
+        const float4 sv = *reinterpret_cast<const float4*>(current + j * kStateCols + cg * 4);
+#pragma unroll
+        for (int r = 0; r < RPT; ++r) {
+          const float m = mix_s[j * DK + r_first + r];  // (mix^T)[row][j]
+          acc[r][0] = fmaf(m, sv.x, acc[r][0]);
+          acc[r][1] = fmaf(m, sv.y, acc[r][1]);
+          acc[r][2] = fmaf(m, sv.z, acc[r][2]);
+          acc[r][3] = fmaf(m, sv.w, acc[r][3]);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) {
+      const int row = r_first + r;
+      const float scale = decay[decay_per_row ? ch * DK + row : ch];
+      const float4 old = *reinterpret_cast<const float4*>(current + row * kStateCols + cg * 4);
+      const float4 plus = *reinterpret_cast<const float4*>(add_c + (long long)row * dv + col0 + cg * 4);
+      float4 result;
+      result.x = scale * old.x - acc[r][0] + plus.x;
+      result.y = scale * old.y - acc[r][1] + plus.y;
+      result.z = scale * old.z - acc[r][2] + plus.z;
+      result.w = scale * old.w - acc[r][3] + plus.w;
+      *reinterpret_cast<float4*>(next + row * kStateCols + cg * 4) = result;
+    }
+    __syncthreads();
+    float* swap = current;
+    current = next;
+    next = swap;
+  }
+}
+
+template <int RPT>
+int delta_state_launch(const float* decay, const float* mix, const float* add, const unsigned char* first, float* out, int chunks, int heads, int dv,
+                       int decay_per_row, int reverse, cudaStream_t stream) {
+  constexpr int DK = 32 * RPT;
+  constexpr int kSmem = (DK * DK + 2 * DK * kStateCols) * (int)sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(delta_state_kernel<RPT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(delta_state_kernel<RPT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess)
+      return FLB_ERR_CUDA;
+    configured = true;
+  }
+  dim3 grid((unsigned)heads, (unsigned)(dv / kStateCols));
+  if (reverse) delta_state_kernel<RPT, true><<<grid, kStateThreads, kSmem, stream>>>(decay, mix, add, first, out, chunks, heads, dv, decay_per_row);
+  else delta_state_kernel<RPT, false><<<grid, kStateThreads, kSmem, stream>>>(decay, mix, add, first, out, chunks, heads, dv, decay_per_row);
+  FLB_CHECK_LAUNCH();
+  return FLB_OK;
+}
+}  // namespace
+
+// decay: [chunks, heads] or [chunks, heads, dk] (decay_per_row); mix: [chunks, heads, dk, dk]; add: [chunks, heads, dk, dv]
+// (forward: the chunk's writes; reverse: the gradient of every entering state); first: [chunks] uint8; out: [chunks, heads, dk, dv]
+// (forward: the state entering every chunk; reverse: the adjoint of the state leaving every chunk).  fp32; dk in {32, 64, 128},
+// dv a multiple of 32.
+FLB_API int flb_delta_state_scan(const float* decay, const float* mix, const float* add, const unsigned char* first, float* out, int chunks,
+                                 int heads, int dk, int dv, int decay_per_row, int reverse, cudaStream_t stream) {
+  if (chunks < 0 || heads <= 0 || dv <= 0 || dv % kStateCols) return FLB_ERR_SHAPE;
+  if (chunks == 0) return FLB_OK;
+  switch (dk) {
+    case 32: return delta_state_launch<1>(decay, mix, add, first, out, chunks, heads, dv, decay_per_row, reverse, stream);
+    case 64: return delta_state_launch<2>(decay, mix, add, first, out, chunks, heads, dv, decay_per_row, reverse, stream);
+    case 128: return delta_state_launch<4>(decay, mix, add, first, out, chunks, heads, dv, decay_per_row, reverse, stream);
+    default: return FLB_ERR_SHAPE;
+  }
+}

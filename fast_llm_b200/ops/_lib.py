@@ -21,6 +21,7 @@ _SIGNATURES = {
     "flb_gemm_bf16": [_p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _i, _i, _p],
     "flb_causal_conv1d_fwd": [_p, _p, _p, _p, _p, _ll, _i, _i, _i, _p],
     "flb_causal_conv1d_bwd": [_p, _p, _p, _p, _p, _p, _p, _p, _ll, _i, _i, _i, _i, _p],
+    "flb_delta_state_scan": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "flb_selective_scan_chunks": [_ll],
     "flb_selective_scan_fwd": [_p] * 9 + [_ll, _i, _i, _i, _i, _p, _p, _p, _p],
     "flb_selective_scan_checkpoints": [_ll, _i],

@@ -337,6 +337,45 @@ def _chunk_layout(boundaries: list[int], chunk: int, device):
     return index.to(device), first
 
 
+class _DeltaStateScan(torch.autograd.Function):
+    """State entering every chunk of S_{c+1} = decay_c o S_c - mix_c S_c + write_c (zero at document starts): one CUDA kernel
+    walks the chunks (`flb_delta_state_scan`), a second one the adjoint recurrence; the gradients of mix, write and decay are
+    batched products of the two results."""
+
+    @staticmethod
+    def applies(mix: torch.Tensor, write: torch.Tensor) -> bool:
+        dk, dv = write.shape[-2:]
+        return mix.is_cuda and mix.dtype == torch.float32 and dv % 32 == 0 and dk in (32, 64, 128)
+
+    @staticmethod
+    def _scan(decay, mix, add, first, reverse: bool) -> torch.Tensor:
+        from fast_llm_b200.ops import _lib
+
+        chunks, heads, dk, dv = add.shape
+        per_row = decay.shape[-2] == dk
+        out = torch.empty_like(add)
+        _lib.check(_lib.get_lib().flb_delta_state_scan(decay.data_ptr(), mix.data_ptr(), add.data_ptr(), first.data_ptr(), out.data_ptr(), chunks, heads,
+                                                       dk, dv, int(per_row), int(reverse), _lib.stream_ptr()), "flb_delta_state_scan")
+        _lib.count_launch()
+        return out
+
+    @staticmethod
+    def forward(ctx, decay, mix, write, first):
+        decay, mix, write = decay.contiguous(), mix.contiguous(), write.contiguous()
+        states = _DeltaStateScan._scan(decay, mix, write, first, False)
+        ctx.save_for_backward(decay, mix, first, states)
+        return states
+
+    @staticmethod
+    def backward(ctx, grad_states):
+        decay, mix, first, states = ctx.saved_tensors
+        leaving = _DeltaStateScan._scan(decay, mix, grad_states.contiguous(), first, True)  # adjoint of the state leaving every chunk
+        grad_mix = -(leaving @ states.transpose(-1, -2))
+        weighted = leaving * states
+        grad_decay = weighted.sum(-1, keepdim=True) if decay.shape[-2] == states.shape[-2] else weighted.sum((-1, -2), keepdim=True)
+        return grad_decay, grad_mix, leaving, None
+
+
 def _delta_rule_all_chunks(q, k, v, g, beta, boundaries: list[int], chunk: int) -> torch.Tensor:
     """Delta rule with everything that does not depend on the carried state computed for ALL chunks at once.
 
@@ -391,14 +430,18 @@ def _delta_rule_all_chunks(q, k, v, g, beta, boundaries: list[int], chunk: int) 
     mix = k_out @ reads  # [C, h, dk, dk]
     heads, dk = qc.shape[1], qc.shape[-1]
     state = torch.zeros(heads, dk, dv, dtype=torch.float32, device=device)
-    states = []
-    # unbind once: indexing inside the loop would make autograd build a full-size zero tensor per chunk and operand
-    for c, (decay_c, mix_c, write_c) in enumerate(zip(decay.unbind(0), mix.unbind(0), write.unbind(0))):
-        if first[c]:
-            state = torch.zeros_like(state)
-        states.append(state)
-        state = torch.baddbmm(state * decay_c, mix_c, state, alpha=-1.0) + write_c
-    out = out_local + q_state @ torch.stack(states) if chunks else out_local
+    if chunks and _DeltaStateScan.applies(mix, write):
+        entering = _DeltaStateScan.apply(decay, mix, write, torch.tensor(first, dtype=torch.uint8).to(device, non_blocking=True))
+    else:
+        states = []
+        # unbind once: indexing inside the loop would make autograd build a full-size zero tensor per chunk and operand
+        for c, (decay_c, mix_c, write_c) in enumerate(zip(decay.unbind(0), mix.unbind(0), write.unbind(0))):
+            if first[c]:
+                state = torch.zeros_like(state)
+            states.append(state)
+            state = torch.baddbmm(state * decay_c, mix_c, state, alpha=-1.0) + write_c
+        entering = torch.stack(states) if chunks else None
+    out = out_local + q_state @ entering if chunks else out_local
     return out.transpose(1, 2)[valid].to(out_dtype)
 
 

@@ -276,11 +276,11 @@ def bench_ssm(results):
 
     ms = time_op(gdn_fwd, iters=5)
     flops = 2.0 * tokens * heads * dk * dk * 3  # state update, read and query per token (the recurrence itself)
-    r = {"op": "gdn_chunk_delta_rule_fwd", "ms": ms, "tflops": flops / ms / 1e9, "peak_kind": kind, "note": "PyTorch ops (cuBLAS batched matmuls), no custom kernel"}
+    r = {"op": "gdn_chunk_delta_rule_fwd", "ms": ms, "tflops": flops / ms / 1e9, "peak_kind": kind, "note": "chunk-local part in PyTorch ops (cuBLAS batched matmuls), state recurrence in flb_delta_state_scan"}
     results.append(r)
     print(json.dumps(r), flush=True)
     ms = time_op(lambda: torch.autograd.grad(out[0], (q, k, v, log_decay, beta), go.to(out[0].dtype), retain_graph=True), iters=5)
-    r = {"op": "gdn_chunk_delta_rule_bwd", "ms": ms, "tflops": 2 * flops / ms / 1e9, "peak_kind": kind, "note": "autograd through the batched chunk-local ops and the per-chunk state recurrence"}
+    r = {"op": "gdn_chunk_delta_rule_bwd", "ms": ms, "tflops": 2 * flops / ms / 1e9, "peak_kind": kind, "note": "autograd through the batched chunk-local ops; adjoint recurrence in flb_delta_state_scan"}
     results.append(r)
     print(json.dumps(r), flush=True)
 
@@ -291,7 +291,7 @@ def bench_ssm(results):
         out[0] = chunk_delta_rule(q, k, v, log_decay_kda, beta, None, normalize_qk=True)
 
     ms = time_op(kda_fwd, iters=3)
-    r = {"op": "kda_chunk_delta_rule_fwd", "ms": ms, "tflops": flops / ms / 1e9, "peak_kind": kind, "note": "PyTorch ops, no custom kernel"}
+    r = {"op": "kda_chunk_delta_rule_fwd", "ms": ms, "tflops": flops / ms / 1e9, "peak_kind": kind, "note": "as above with per-channel decays"}
     results.append(r)
     print(json.dumps(r), flush=True)
     ms = time_op(lambda: torch.autograd.grad(out[0], (q, k, v, log_decay_kda, beta), go.to(out[0].dtype), retain_graph=True), iters=3)

@@ -509,3 +509,28 @@ def test_selective_scan_kernel(tokens, channels, state, groups_b, groups_c, gate
     assert _rel_err(out, ref) < 1e-2
     for name, t, r in zip(["x", "dt", "a", "b", "c", "skip"] + (["z"] if gated else []) + ["bias"], inputs, refs):
         assert _rel_err(t.grad, r.grad) < 2e-2, name
+
+
+@pytest.mark.parametrize("per_channel", [False, True])
+def test_delta_rule_state_scan_kernel(per_channel):
+    """Gated DeltaNet / KDA recurrence on the GPU path (batched chunk-local work + the state-scan kernel and its adjoint)
+    against the token-by-token fp32 restatement, with documents."""
+    from fast_llm_b200.ops.ssm import _DeltaStateScan, chunk_delta_rule, delta_rule_reference
+
+    torch.manual_seed(0)
+    tokens, heads, dim = 300, 4, 64
+    dev = "cuda"
+    q, k, v = (torch.randn(tokens, heads, dim, device=dev).bfloat16().requires_grad_() for _ in range(3))
+    g = (-torch.rand((tokens, heads, dim) if per_channel else (tokens, heads), device=dev) * 0.2).requires_grad_()
+    beta = torch.rand(tokens, heads, device=dev).requires_grad_()
+    cu = torch.tensor([0, 70, 200, 300], device=dev, dtype=torch.int32)
+    grad_out = torch.randn(tokens, heads, dim, device=dev).bfloat16()
+    assert _DeltaStateScan.applies(torch.empty(1, heads, dim, dim, device=dev), torch.empty(1, heads, dim, dim, device=dev))
+    out = chunk_delta_rule(q, k, v, g, beta, cu)
+    grads = torch.autograd.grad(out, (q, k, v, g, beta), grad_out)
+    reference_inputs = [t.detach().float().requires_grad_() for t in (q, k, v, g, beta)]
+    reference = delta_rule_reference(*reference_inputs, cu)
+    reference_grads = torch.autograd.grad(reference, reference_inputs, grad_out.float())
+    assert _rel_err(out, reference) < 1e-2
+    for name, a, b in zip("q k v g beta".split(), grads, reference_grads):
+        assert _rel_err(a, b) < 1e-2, name
