@@ -17,6 +17,7 @@ import pathlib
 import statistics
 import subprocess
 import sys
+import tempfile
 import time
 
 ROOT = pathlib.Path(__file__).resolve().parent
@@ -46,7 +47,7 @@ class ClockSampler:
     def __init__(self, gpu_index: int):
         self._gpu = gpu_index
         self._proc = None
-        self._path = ROOT / "gpurun_out" / f"clocks_bench_{gpu_index}.csv"
+        self._path = pathlib.Path(os.environ.get("FLB_BENCH_CLOCK_DIR", tempfile.gettempdir())) / f"clocks_bench_{gpu_index}.csv"
 
     def start(self):
         try:
