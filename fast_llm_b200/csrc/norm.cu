@@ -176,18 +176,29 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
   }
 }
 
-// out[c] (+)= sum_p partial[p][c]; out is fp32 or bf16.
+// out[c] (+)= sum_p partial[p][c]; out is fp32 or bf16.  A block owns 32 columns; its 32 x 32 threads split the parts 32 ways
+// (coalesced 128-byte rows), then the 32 partial sums of a column are added in a fixed order through shared memory.
+constexpr int kColsumCols = 32, kColsumSplit = 32;
 template <typename OutT>
-__global__ void colsum_kernel(const float* __restrict__ partial, OutT* __restrict__ out, int parts, int cols,
-                              int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+__global__ void __launch_bounds__(kColsumCols * kColsumSplit) colsum_kernel(const float* __restrict__ partial, OutT* __restrict__ out, int parts,
+                                                                            int cols, int accumulate) {
+  __shared__ float sums[kColsumSplit][kColsumCols + 1];
+  const int lane = threadIdx.x % kColsumCols, group = threadIdx.x / kColsumCols;
+  const int c = blockIdx.x * kColsumCols + lane;
   float s = 0.f;
-  for (int p = 0; p < parts; ++p) s += partial[(long long)p * cols + c];
-  if constexpr (sizeof(OutT) == 4) {
-    out[c] = accumulate ? out[c] + s : s;
-  } else {
-    out[c] = f2bf(accumulate ? bf2f(out[c]) + s : s);
+  if (c < cols)
+    for (int p = group; p < parts; p += kColsumSplit) s += partial[(long long)p * cols + c];
+  sums[group][lane] = s;
+  __syncthreads();
+  if (group == 0 && c < cols) {
+    float total = 0.f;
+#pragma unroll
+    for (int g = 0; g < kColsumSplit; ++g) total += sums[g][lane];
+    if constexpr (sizeof(OutT) == 4) {
+      out[c] = accumulate ? out[c] + total : total;
+    } else {
+      out[c] = f2bf(accumulate ? bf2f(out[c]) + total : total);
+    }
   }
 }
 
@@ -245,7 +256,7 @@ FLB_API int flb_norm_fwd(const void* x, const void* delta, const void* w, const 
 }
 
 // Number of per-CTA partial rows flb_norm_bwd writes into dw_partial / db_partial.
-FLB_API int flb_norm_bwd_parts(int rows) { return rows < 592 ? rows : 592; }
+FLB_API int flb_norm_bwd_parts(int rows) { return rows < 1184 ? rows : 1184; }  // 8 resident CTAs on each of 148 SMs
 
 // dx = dnorm(dy) (+ dres).  dw_partial/db_partial: [flb_norm_bwd_parts(rows), cols] fp32 scratch (may be null
 // to skip parameter gradients).
@@ -265,8 +276,8 @@ FLB_API int flb_norm_bwd(const void* dy, const void* x, const void* w, const flo
 FLB_API int flb_colsum(const float* partial, void* out, int parts, int cols, int accumulate, int out_is_bf16,
                        cudaStream_t stream) {
   if (parts <= 0 || cols <= 0) return FLB_ERR_SHAPE;
-  const int threads = 128;
-  const int blocks = (cols + threads - 1) / threads;
+  const int threads = kColsumCols * kColsumSplit;
+  const int blocks = (cols + kColsumCols - 1) / kColsumCols;
   if (out_is_bf16) colsum_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(partial, (__nv_bfloat16*)out, parts, cols, accumulate);
   else colsum_kernel<float><<<blocks, threads, 0, stream>>>(partial, (float*)out, parts, cols, accumulate);
   FLB_CHECK_LAUNCH();
