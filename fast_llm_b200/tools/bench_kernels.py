@@ -341,6 +341,35 @@ def profile_gemm_shapes():
     print("profile_gemm_shapes done")
 
 
+def profile_ssm():
+    """ncu workload: two forward + backward passes of the selective scan (8192 x 4096 x 16) and of the gated DeltaNet
+    delta rule (8192 tokens x 16 heads x 128), about 1.5 GB on the device."""
+    from fast_llm_b200.ops.ssm import chunk_delta_rule, selective_scan
+
+    tokens, channels, state, groups = 8192, 4096, 16, 32
+    dev = "cuda"
+    x = torch.randn(tokens, channels, device=dev).bfloat16().requires_grad_()
+    dt = (torch.randn(tokens, channels, device=dev) - 1).bfloat16().requires_grad_()
+    z = torch.randn(tokens, channels, device=dev).bfloat16().requires_grad_()
+    a = (-torch.rand(channels, state, device=dev) - 0.1).requires_grad_()
+    b = torch.randn(tokens, groups, state, device=dev).bfloat16().requires_grad_()
+    c = torch.randn(tokens, channels // state, state, device=dev).bfloat16().requires_grad_()
+    skip = torch.randn(channels, device=dev).requires_grad_()
+    g = torch.randn(tokens, channels, device=dev).bfloat16()
+    heads, dk = 16, 128
+    q, k, v = (torch.randn(tokens, heads, dk, device=dev).bfloat16().requires_grad_() for _ in range(3))
+    log_decay = (-torch.rand(tokens, heads, device=dev) * 0.1).requires_grad_()
+    beta = torch.rand(tokens, heads, device=dev).requires_grad_()
+    go = torch.randn(tokens, heads, dk, device=dev).bfloat16()
+    for _ in range(2):
+        y = selective_scan(x, dt, a, b, c, skip, z, None, None)
+        torch.autograd.grad(y, (x, dt, a, b, c, skip, z), g)
+        o = chunk_delta_rule(q, k, v, log_decay, beta, None)
+        torch.autograd.grad(o, (q, k, v, log_decay, beta), go.to(o.dtype))
+    torch.cuda.synchronize()
+    print("profile_ssm done")
+
+
 def profile_gemm():
     """Small fixed workload for an ncu capture: three launches of the fprop GEMM on operands larger than L2."""
     from fast_llm_b200.ops.gemm import matmul_nt
@@ -362,6 +391,8 @@ def main(argv):
         return profile_gemm_shapes()
     if "profile_attention" in argv:
         return profile_attention()
+    if "profile_ssm" in argv:
+        return profile_ssm()
     if "gemm_tiles" in argv:
         bench_gemm_tiles(results)
     if "attention" in argv:
