@@ -370,6 +370,32 @@ def profile_ssm():
     print("profile_ssm done")
 
 
+def profile_moe():
+    """ncu workload: two forward + backward passes of a small dropless MoE layer (hidden 4096, 4 experts of FFN 4096, top-2,
+    8192 tokens; about 1 GB on the device), so that the grouped GEMM launches can be captured."""
+    import fast_llm_b200.models.auto  # noqa: F401
+    from fast_llm_b200.layers.moe import MoEMLPConfig
+    from fast_llm_b200.parallel.topology import DistributedConfig
+    from fast_llm_b200.tensor import TensorDim
+
+    tokens, hidden = 8192, 4096
+    config = MoEMLPConfig.from_dict({"type": "moe", "experts": 4, "experts_per_token": 2, "intermediate_size": 4096, "gated": True,
+                                     "activation": "silu", "add_linear_biases": False, "implementation": "dropless"})
+    config.validate()
+    dc = DistributedConfig.from_dict({"compute_dtype": "bf16", "seed": 0, "world_size": 1, "rank": 0, "local_world_size": 1})
+    dc.validate()
+    layer = config.get_layer(dc, TensorDim("hidden", hidden))
+    layer.set_names("mlp.")
+    layer = layer.materialize(device=torch.device("cuda"), dtype=torch.bfloat16)
+    x = torch.randn(tokens, hidden, device="cuda", dtype=torch.bfloat16)
+    g = torch.randn(tokens, hidden, device="cuda", dtype=torch.bfloat16)
+    for _ in range(2):
+        xi = x.detach().requires_grad_()
+        layer.forward(xi, {"training": True}).backward(g)
+    torch.cuda.synchronize()
+    print("profile_moe done")
+
+
 def profile_gemm():
     """Small fixed workload for an ncu capture: three launches of the fprop GEMM on operands larger than L2."""
     from fast_llm_b200.ops.gemm import matmul_nt
@@ -393,6 +419,8 @@ def main(argv):
         return profile_attention()
     if "profile_ssm" in argv:
         return profile_ssm()
+    if "profile_moe" in argv:
+        return profile_moe()
     if "gemm_tiles" in argv:
         bench_gemm_tiles(results)
     if "attention" in argv:
