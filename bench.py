@@ -35,6 +35,8 @@ def parse_args():
     p.add_argument("--layers", type=int, default=32, help="debug only: any value other than 32 marks the result invalid")
     p.add_argument("--global-batch-tokens", type=int, default=GLOBAL_BATCH_TOKENS)
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--tensor-parallel", type=int, default=1, help="extra measurement: tensor + sequence parallel groups of this size (default 1: the headline config)")
+    p.add_argument("--no-fused-collectives", action="store_true", help="extra measurement: NCCL collectives instead of the peer-memory kernels")
     return p.parse_args()
 
 
@@ -136,8 +138,15 @@ def _time_steps(step_fn, steps: int, world: int) -> float:
 
 
 def config_updates(args, world: int) -> dict:
-    depth = args.global_batch_tokens // MICRO_BATCH_TOKENS // world
+    depth = args.global_batch_tokens // MICRO_BATCH_TOKENS // (world // args.tensor_parallel)
+    extra = {}
+    if args.tensor_parallel > 1:
+        extra[("model", "distributed", "tensor_parallel")] = args.tensor_parallel
+        extra[("model", "distributed", "sequence_tensor_parallel")] = True
+    if args.no_fused_collectives:
+        extra[("model", "multi_stage", "fused_collectives")] = False
     return {
+        **extra,
         ("model", "multi_stage", "zero_stage"): 1,
         ("schedule", "depth_first_micro_batches"): depth,
         ("training", "train_iters"): 2 * (args.warmup + args.steps) + 2,
@@ -160,7 +169,9 @@ def result_line(args, world, ms_per_step, clocks, launches, e2e, impl, extra=Non
         "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights", "impl": impl,
         "config": {"model": "Mistral-7B (32 layers, hidden 4096, 32/8 heads, SwiGLU 14336, vocab 32000, window 4096)" if args.layers == 32 else f"INVALID: {args.layers} layers",
                    "global_batch": tokens, "seq_len": MICRO_BATCH_TOKENS, "micro_batch_tokens": MICRO_BATCH_TOKENS,
-                   "parallelism": f"dp{world} ZeRO-1, {tokens // MICRO_BATCH_TOKENS // world} sequential micro-batches",
+                   "parallelism": (f"dp{world // args.tensor_parallel} ZeRO-1" + (f" x tp{args.tensor_parallel} sequence-parallel" if args.tensor_parallel > 1 else "")
+                                   + f", {tokens // MICRO_BATCH_TOKENS // (world // args.tensor_parallel)} sequential micro-batches"
+                                   + (", NCCL collectives" if args.no_fused_collectives else "")),
                    "l2": "no explicit flush: every step streams > 100 GB of weights, gradients and activations per GPU (L2 is 126 MB)"},
         "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
     }
