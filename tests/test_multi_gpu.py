@@ -242,3 +242,17 @@ def test_sequence_data_parallel_exchange_through_symmetric_memory():
     assert all(r[1] for r in fused) and not any(r[1] for r in plain)
     for (lf, _), (lp, _) in zip(fused, plain):
         assert lf == pytest.approx(lp, rel=1e-2)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_fused_collectives_on_four_ranks():
+    """The peer-memory kernels at group size 4: tensor-parallel linears and the loss-statistics exchange."""
+    results = run_distributed(_fused_tp_rank_main, 4, 2048, 512, 2048, False, timeout=600)
+    for errors, _, _ in results:
+        for relative, repeat in errors:
+            assert relative < 0.15, errors
+            assert repeat == 0.0, errors
+    for per_rank in run_distributed(_fused_ce_rank_main, 4, 515, 8192, timeout=600):
+        for d_loss, d_z, d_grad, d_loss_ref, d_grad_ref in per_rank:
+            assert d_loss < 1e-4 and d_z < 1e-2 and d_grad < 1e-3, per_rank
+            assert d_loss_ref < 2e-2 and d_grad_ref < 2e-2, per_rank
