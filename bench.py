@@ -36,6 +36,7 @@ def parse_args():
     p.add_argument("--global-batch-tokens", type=int, default=GLOBAL_BATCH_TOKENS)
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--tensor-parallel", type=int, default=1, help="extra measurement: tensor + sequence parallel groups of this size (default 1: the headline config)")
+    p.add_argument("--no-reference-compat", action="store_true", help="reference arm: do not adapt the arguments of torch's AdamW (shows the reference's own TypeError)")
     p.add_argument("--no-fused-collectives", action="store_true", help="extra measurement: NCCL collectives instead of the peer-memory kernels")
     return p.parse_args()
 
@@ -259,14 +260,43 @@ def run_ours(args):
             e2e = {"value": args.global_batch_tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                    "how": "Trainer data iterator (pinned host batches) -> ScheduleRunner.run_step -> loss.item()"}
-        from fast_llm_b200.ops.gemm import check_device_errors
+        from fast_llm_b200.utils.device_errors import check_device_errors
 
-        check_device_errors()
+        check_device_errors(distributed.world_group, distributed.device)
         peak = torch.cuda.max_memory_allocated() / 2**30
     if rank == 0:
         extra = {"final_loss": loss_box.get("lm_loss"), "peak_memory_gib": peak}
         print(json.dumps(result_line(args, world, ms, clocks, launches, e2e, "ours", extra)), flush=True)
     distributed.shutdown()
+
+
+REFERENCE_COMPAT = ("torch.optim.adamw.adamw wrapped on torch's side of the call (baseline/_ref untouched): a None max_exp_avg_sqs "
+                    "becomes [] and integer step tensors become float32 with the same values, which is what torch 2.11's foreach "
+                    "AdamW accepts; the reference's no-apex optimizer fallback passes None and int64 steps")
+
+
+def _install_reference_adamw_compat():
+    """The reference's optimizer fallback (used when apex is absent) calls `torch.optim.adamw.adamw(params, grads, exp_avgs,
+    exp_avg_sqs, None, state_steps=<int64 tensors>, ...)`.  torch 2.11's multi-tensor path rejects both the `None` (it groups the
+    lists by device and wants a list) and integer step tensors (steps must be float32/64).  This adapts exactly those two argument
+    types before handing over to the stock function; the update rule, hyper-parameters and tensors are the reference's own."""
+    import torch
+    import torch.optim.adamw as adamw_module
+
+    stock = adamw_module.adamw
+    if getattr(stock, "_flb_compat", False):
+        return
+
+    def adamw(params, grads, exp_avgs, exp_avg_sqs, max_exp_avg_sqs, *args, **kwargs):
+        if max_exp_avg_sqs is None:
+            max_exp_avg_sqs = []
+        steps = kwargs.get("state_steps")
+        if steps is not None and any(not s.is_floating_point() for s in steps):
+            kwargs["state_steps"] = [s.to(torch.float32) for s in steps]
+        return stock(params, grads, exp_avgs, exp_avg_sqs, max_exp_avg_sqs, *args, **kwargs)
+
+    adamw._flb_compat = True
+    adamw_module.adamw = adamw
 
 
 def run_reference(args):
@@ -294,6 +324,11 @@ def run_reference(args):
             dynamo_ok = False
         if not dynamo_ok:
             os.environ["TORCHDYNAMO_DISABLE"] = "1"
+        compat = None
+        if world > 1 and not args.no_reference_compat:
+            # at one GPU the reference runs out of memory before its optimizer is reached: nothing to adapt
+            _install_reference_adamw_compat()
+            compat = REFERENCE_COMPAT
         import fast_llm.data.auto  # noqa: F401
         import fast_llm.models.auto  # noqa: F401
         from fast_llm.engine.distributed.config import PhaseType
@@ -345,6 +380,7 @@ def run_reference(args):
             e2e = {"value": args.global_batch_tokens / (ms / 1e3), "unit": "tokens/s", "ms_per_step": ms,
                    "how": "reference Trainer.run(): its own data loader (H2D) and loss reduction (D2H) are inside every step"}
             extra = {"torch_dynamo_enable": dynamo_ok, "peak_memory_gib": torch.cuda.max_memory_allocated() / 2**30,
+                     "reference_compat": compat,
                      "note": "apex / mamba_ssm absent: the reference uses its torch fallbacks for fused Adam and norms"}
             print(json.dumps(result_line(args, world, ms, clocks, None, e2e, "reference", extra)), flush=True)
     except Exception as e:  # report, do not crash the driver

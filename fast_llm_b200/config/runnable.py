@@ -54,9 +54,9 @@ class RunnableConfig(Config):
         parser.add_argument("-v", "--validate", dest="do_run", action="store_false", help="Validate the config without running.")
         parser.add_argument("--verbose", type=int, help="Verbosity of the config printout.", default=FieldVerboseLevel.core)
         parser.add_argument("-c", "--config", type=str, help="YAML config file (path or allow-listed https URL).")
-        parser.add_argument("--hydra", action="store_true", help="Accepted for compatibility; hydra composition is not available.")
-        parser.add_argument("--hydra-path", type=str, default=".")
-        parser.add_argument("--hydra-config", type=str, default="default")
+        parser.add_argument("--hydra", action="store_true", help="Hydra override syntax for the command-line updates: key=value, +key=value, ++key=value, ~key.")
+        parser.add_argument("--hydra-path", type=pathlib.Path, default=None, help="Directory of composable YAML configs (implies --hydra).")
+        parser.add_argument("--hydra-config", type=str, default=None, help="Base config inside --hydra-path (replaces --config); its `defaults` list is composed.")
         parser.add_argument("--config_auth_token_file", type=pathlib.Path, default=None)
         parser.add_argument("--trust-remote-code", action="store_true", help="Allow Hugging Face remote code when loading tokenizers/models.")
         return parser
@@ -64,6 +64,16 @@ class RunnableConfig(Config):
     @classmethod
     def _from_parsed_args(cls, parsed: argparse.Namespace, unparsed: list[str]):
         default = cls._load_default_config_dict(parsed)
+        if parsed.hydra or parsed.hydra_path is not None or parsed.hydra_config is not None:
+            from fast_llm_b200.config.compose import apply_overrides, compose_config
+
+            if parsed.hydra_config is not None:
+                if default:
+                    raise ValueError("--hydra-config replaces --config: give only one of them")
+                if parsed.hydra_path is None:
+                    raise ValueError("--hydra-config needs --hydra-path")
+            default, remaining = compose_config(parsed.hydra_path, parsed.hydra_config, default, unparsed)
+            return cls.from_dict(apply_overrides(default, remaining), {})
         updates = cls._parse_updates(unparsed)
         return cls.from_dict(default, updates)
 
@@ -81,8 +91,6 @@ class RunnableConfig(Config):
 
     @classmethod
     def _load_default_config_dict(cls, parsed: argparse.Namespace) -> dict:
-        if parsed.hydra:
-            raise NotImplementedError("Hydra composition is not supported; pass a YAML file with -c")
         if parsed.config is None:
             return {}
         url = urllib.parse.urlparse(parsed.config)

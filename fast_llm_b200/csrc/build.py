@@ -23,12 +23,18 @@ NVCC_FLAGS = [
     "-lineinfo",
     "-O3",
     "-std=c++17",
-    "--use_fast_math",
     "-Xcompiler",
     "-fPIC",
     "-Xcompiler",
     "-fvisibility=hidden",
 ]
+
+
+# Approximate division / sqrt / exp / log (`--use_fast_math`) only where the arithmetic tolerates it: the GEMM and
+# attention pipelines (exp2 on scaled scores, checked against fp32 restatements), activations, norms and the SSM scans.
+# The optimizer update, the loss kernels and the fused ZeRO kernels (AdamW's sqrt and divide, the cross-entropy's exp
+# and log) compile with IEEE-accurate math, like the apex / Triton kernels they stand in for.
+FAST_MATH_SOURCES = {"gemm_tcgen05.cu", "attention_fwd.cu", "attention_bwd.cu", "elementwise.cu", "norm.cu", "ssm.cu", "moe.cu"}
 
 
 def _nvcc() -> str:
@@ -48,7 +54,7 @@ def _stale(target: pathlib.Path, deps) -> bool:
 def _compile(src: pathlib.Path, headers, verbose: bool) -> pathlib.Path:
     obj = BUILD / (src.stem + ".o")
     if _stale(obj, [src, *headers]):
-        cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        cmd = [_nvcc(), *NVCC_FLAGS, *(["--use_fast_math"] if src.name in FAST_MATH_SOURCES else []), "-c", str(src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
@@ -63,7 +69,7 @@ def _compile(src: pathlib.Path, headers, verbose: bool) -> pathlib.Path:
 def build_kernels(verbose: bool = False, force: bool = False) -> pathlib.Path:
     BUILD.mkdir(exist_ok=True)
     sources = sorted(CSRC.glob("*.cu"))
-    headers = sorted(CSRC.glob("*.cuh"))
+    headers = sorted([*CSRC.glob("*.cuh"), *CSRC.glob("*.h"), pathlib.Path(__file__)])
     if force:
         for o in BUILD.glob("*.o"):
             o.unlink()

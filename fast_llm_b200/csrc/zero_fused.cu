@@ -20,13 +20,21 @@ namespace {
 using namespace flb;
 constexpr int kThreads = 256;
 constexpr int kMaxRanks = 16;
-constexpr long long kBarrierLimitCycles = 20000000000ll;  // about 10 s at boost clock
+// Longest wait of one barrier in SM clock cycles; about 10 s at boost clock unless flb_symm_set_barrier_limit changes it.
+long long g_barrier_limit_cycles = 20000000000ll;
+
+// True when an earlier bounded wait on this stream gave up: the kernels below then leave memory untouched, because
+// the peers' buffers they would read may be stale or half written.
+__device__ __forceinline__ bool wait_failed(const int* err_word) {
+  return err_word != nullptr && *reinterpret_cast<const volatile int*>(err_word) != 0;
+}
 
 struct PeerPtrs {
   void* p[kMaxRanks];
 };
 
-__global__ void symm_barrier_kernel(PeerPtrs signal_pads, int rank, int world, int slot, unsigned epoch, int* err_word) {
+__global__ void symm_barrier_kernel(PeerPtrs signal_pads, int rank, int world, int slot, unsigned epoch, int* err_word,
+                                    long long limit_cycles) {
   const int peer = threadIdx.x;
   if (peer >= world) return;
   // tell `peer` that this rank reached the barrier: pad layout [slot][source rank]
@@ -39,7 +47,7 @@ __global__ void symm_barrier_kernel(PeerPtrs signal_pads, int rank, int world, i
     unsigned v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local) : "memory");
     if ((int)(v - epoch) >= 0) break;
-    if (clock64() - t0 > kBarrierLimitCycles) {
+    if (clock64() - t0 > limit_cycles) {
       atomicExch(err_word, 100 + peer);
       break;
     }
@@ -66,8 +74,9 @@ __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p, l
 template <typename GradT>
 __global__ void __launch_bounds__(kThreads)
 rs_reduce_kernel(PeerPtrs grads, int rank, int world, long long shard, float scale, float* __restrict__ grad_shard,
-                 int accumulate, float* __restrict__ sumsq_partial) {
+                 int accumulate, float* __restrict__ sumsq_partial, const int* err_word) {
   __shared__ float scratch[32];
+  if (wait_failed(err_word)) return;
   const long long nvec = shard >> 2;
   const long long base = (long long)rank * nvec;
   float ss = 0.f;
@@ -93,7 +102,9 @@ rs_reduce_kernel(PeerPtrs grads, int rank, int world, long long shard, float sca
 __global__ void __launch_bounds__(kThreads)
 adam_push_kernel(float* __restrict__ w, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
                  PeerPtrs weight_buffers, int world, long long lp_offset, long long n, float lr, float beta1, float beta2,
-                 float eps, float wd, float inv_bc1, float inv_bc2, float gscale, const float* __restrict__ gscale_ptr) {
+                 float eps, float wd, float inv_bc1, float inv_bc2, float gscale, const float* __restrict__ gscale_ptr,
+                 const int* err_word) {
+  if (wait_failed(err_word)) return;
   const float sc = gscale * (gscale_ptr ? *gscale_ptr : 1.f);
   const long long nvec = n >> 2;
   for (long long i = blockIdx.x * (long long)kThreads + threadIdx.x; i < nvec; i += (long long)gridDim.x * kThreads) {
@@ -128,6 +139,12 @@ int fill_ptrs(PeerPtrs& out, const void* const* ptrs, int world) {
 }  // namespace
 
 FLB_API int flb_symm_max_ranks() { return kMaxRanks; }
+// Sets the longest wait of later barriers (SM clock cycles, > 0) and returns the previous limit.
+FLB_API long long flb_symm_set_barrier_limit(long long cycles) {
+  const long long old = g_barrier_limit_cycles;
+  if (cycles > 0) g_barrier_limit_cycles = cycles;
+  return old;
+}
 // Bytes of signal pad each rank must provide (zero-initialised): [slots][kMaxRanks] u32.
 FLB_API int flb_symm_signal_pad_bytes(int slots) { return slots * kMaxRanks * 4; }
 
@@ -137,7 +154,7 @@ FLB_API int flb_symm_barrier(const void* const* signal_pads, int rank, int world
   PeerPtrs pads;
   const int st = fill_ptrs(pads, signal_pads, world);
   if (st) return st;
-  symm_barrier_kernel<<<1, 32, 0, stream>>>(pads, rank, world, slot, epoch, err_word);
+  symm_barrier_kernel<<<1, 32, 0, stream>>>(pads, rank, world, slot, epoch, err_word, g_barrier_limit_cycles);
   FLB_CHECK_LAUNCH();
   return FLB_OK;
 }
@@ -145,7 +162,9 @@ FLB_API int flb_symm_barrier(const void* const* signal_pads, int rank, int world
 // out[i] = sum over slots s (in slot order) of in[s * n + i]; bf16 in and out, fp32 accumulation.  The reduce step of the
 // fused GEMM + reduce-scatter: every tensor-parallel peer stored its partial tile rows into one slot of this rank's
 // staging buffer from inside its GEMM epilogue.
-__global__ void slot_sum_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int slots, long long n) {
+__global__ void slot_sum_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int slots, long long n,
+                                const int* err_word) {
+  if (wait_failed(err_word)) return;
   const long long nvec = n >> 3;
   for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -182,12 +201,12 @@ FLB_API int flb_peer_copy(const void* src, void* dst, long long bytes, int ctas,
   return FLB_OK;
 }
 
-FLB_API int flb_slot_sum_bf16(const void* in, void* out, int slots, long long n, cudaStream_t stream) {
+FLB_API int flb_slot_sum_bf16(const void* in, void* out, int slots, long long n, const int* err_word, cudaStream_t stream) {
   if (n % 8 || slots <= 0) return FLB_ERR_SHAPE;
   if (n == 0) return FLB_OK;
   long long blocks = ((n >> 3) + kThreads - 1) / kThreads;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  slot_sum_kernel<<<(int)blocks, kThreads, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, slots, n);
+  slot_sum_kernel<<<(int)blocks, kThreads, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, slots, n, err_word);
   FLB_CHECK_LAUNCH();
   return FLB_OK;
 }
@@ -196,18 +215,19 @@ FLB_API int flb_rs_reduce_blocks() { return 148 * 4; }
 
 // grad_ptrs[r]: rank r's gradient buffer of the stage (grad_dtype 0 fp32 / 1 bf16).  sumsq_partial: flb_rs_reduce_blocks()
 // floats (may be null).  Call between two flb_symm_barrier's: peers must have finished writing, and must not overwrite
-// their buffers before every rank has read them.
+// their buffers before every rank has read them.  err_word (may be null): the error word of those barriers; when it is
+// set the kernel does nothing.
 FLB_API int flb_rs_reduce(const void* const* grad_ptrs, int grad_dtype, int rank, int world, long long shard, float scale,
-                          float* grad_shard, int accumulate, float* sumsq_partial, cudaStream_t stream) {
+                          float* grad_shard, int accumulate, float* sumsq_partial, const int* err_word, cudaStream_t stream) {
   if (shard % 4) return FLB_ERR_SHAPE;
   PeerPtrs grads;
   const int st = fill_ptrs(grads, grad_ptrs, world);
   if (st) return st;
   const int blocks = flb_rs_reduce_blocks();
   if (grad_dtype == 0)
-    rs_reduce_kernel<float><<<blocks, kThreads, 0, stream>>>(grads, rank, world, shard, scale, grad_shard, accumulate, sumsq_partial);
+    rs_reduce_kernel<float><<<blocks, kThreads, 0, stream>>>(grads, rank, world, shard, scale, grad_shard, accumulate, sumsq_partial, err_word);
   else
-    rs_reduce_kernel<__nv_bfloat16><<<blocks, kThreads, 0, stream>>>(grads, rank, world, shard, scale, grad_shard, accumulate, sumsq_partial);
+    rs_reduce_kernel<__nv_bfloat16><<<blocks, kThreads, 0, stream>>>(grads, rank, world, shard, scale, grad_shard, accumulate, sumsq_partial, err_word);
   FLB_CHECK_LAUNCH();
   return FLB_OK;
 }
@@ -215,7 +235,7 @@ FLB_API int flb_rs_reduce(const void* const* grad_ptrs, int grad_dtype, int rank
 // n % 4 == 0; lp_offset (elements into every rank's bf16 weight buffer) % 4 == 0.
 FLB_API int flb_adam_push(float* w, const float* g, float* m, float* v, const void* const* weight_buffers, int world,
                           long long lp_offset, long long n, float lr, float beta1, float beta2, float eps, float wd, int step,
-                          float gscale, const float* gscale_ptr, cudaStream_t stream) {
+                          float gscale, const float* gscale_ptr, const int* err_word, cudaStream_t stream) {
   if (n <= 0) return FLB_OK;
   if ((n % 4) || (lp_offset % 4)) return FLB_ERR_SHAPE;
   PeerPtrs bufs;
@@ -226,7 +246,7 @@ FLB_API int flb_adam_push(float* w, const float* g, float* m, float* v, const vo
   long long blocks = ((n >> 2) + kThreads - 1) / kThreads;
   if (blocks > 148 * 8) blocks = 148 * 8;
   adam_push_kernel<<<(int)blocks, kThreads, 0, stream>>>(w, g, m, v, bufs, world, lp_offset, n, lr, beta1, beta2, eps, wd,
-                                                          inv_bc1, inv_bc2, gscale, gscale_ptr);
+                                                          inv_bc1, inv_bc2, gscale, gscale_ptr, err_word);
   FLB_CHECK_LAUNCH();
   return FLB_OK;
 }

@@ -194,6 +194,9 @@ class HuggingfaceStateDictCheckpointHandler(ExternalStateDictCheckpointHandler):
         path.mkdir(parents=True, exist_ok=True)
         hf_config = cls.export_config(metadata.config.base_model)
         hf_config.setdefault("architectures", [cls.architecture] if cls.architecture else [])
+        # the dtype the tensors are written in: the cast requested for this save, else the fp32 master weights
+        data_type = getattr(config, "data_type", None)
+        hf_config["torch_dtype"] = str(data_type.torch if data_type is not None else torch.float32).removeprefix("torch.")
         (path / "config.json").write_text(json.dumps(hf_config, indent=2))
         if index is not None:
             (path / "model.safetensors.index.json").write_text(

@@ -192,7 +192,7 @@ class Stage:
                     ce = min(max(pbegin + (c + 1) * piece if c < chunks - 1 else pbegin + meta.numel(), 0), fsdp.shard_size)
                     if ce <= cb:
                         continue
-                    key = (bool(meta.param_weight_decay), 1.0 if lr_scale is None else lr_scale)
+                    key = (bool(meta.param_weight_decay), lr_scale)  # None: the optimizer's default_learning_rate_scale applies
                     if current is not None and current["key"] == key and current["end"] == cb:
                         current["end"] = ce
                         current["names"].append(name)

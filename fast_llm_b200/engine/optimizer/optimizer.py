@@ -25,19 +25,20 @@ class GradScaler:
         self._scale = scale
         self._distributed = distributed
 
-    @property
-    def pushes_weights_to_peers(self) -> bool:
-        return self._weight_arena is not None
+    # Name written as `type` in the optimizer metadata; the reference writes its own class names there
+    # (`fast_llm/engine/optimizer/optimizer.py:160-170`), so checkpoints resume in either framework.
+    type_name = "NoopGradScaler"
 
     @property
     def grad_scale(self) -> float:
         return self._scale
 
     def state_dict(self) -> dict:
-        return {"scale": self._scale}
+        return {"type": self.type_name}
 
-    def load(self, state: dict) -> None:
-        self._scale = state.get("scale", self._scale)
+    def load(self, state: dict, validate: bool = True) -> None:
+        if validate and "type" in state and state["type"] != self.type_name:
+            raise ValueError(f"Gradient scaler mismatch: checkpoint has {state['type']}, this run uses {self.type_name}")
 
     def check_overflow(self, grad_slices) -> bool:
         return False
@@ -47,7 +48,14 @@ class GradScaler:
 
 
 class ConstantGradScaler(GradScaler):
-    pass
+    type_name = "ConstantGradScaler"
+
+    def state_dict(self) -> dict:
+        return {"type": self.type_name, "scale": self._scale}
+
+    def load(self, state: dict, validate: bool = True) -> None:
+        super().load(state, validate)
+        self._scale = state.get("scale", self._scale)
 
 
 class DynamicGradScaler(GradScaler):
@@ -59,13 +67,17 @@ class DynamicGradScaler(GradScaler):
         self._growth_tracker = 0
         self._hysteresis_tracker = config.hysteresis
 
-    def state_dict(self):
-        return {"scale": self._scale, "growth_tracker": self._growth_tracker, "hysteresis_tracker": self._hysteresis_tracker}
+    type_name = "DynamicGradScaler"
 
-    def load(self, state):
-        super().load(state)
-        self._growth_tracker = state.get("growth_tracker", 0)
-        self._hysteresis_tracker = state.get("hysteresis_tracker", self._config.hysteresis)
+    def state_dict(self):
+        return {"type": self.type_name, "scale": self._scale, "growth": self._growth_tracker, "hysteresis": self._hysteresis_tracker}
+
+    def load(self, state, validate: bool = True):
+        super().load(state, validate)
+        self._scale = state.get("scale", self._scale)
+        # `growth_tracker` / `hysteresis_tracker` are the key names of older checkpoints of this framework
+        self._growth_tracker = state.get("growth", state.get("growth_tracker", 0))
+        self._hysteresis_tracker = state.get("hysteresis", state.get("hysteresis_tracker", self._config.hysteresis))
 
     def check_overflow(self, grad_slices) -> bool:
         flag = torch.zeros(1, dtype=torch.float32, device=grad_slices[0].device if grad_slices else "cpu")
@@ -159,7 +171,7 @@ class Optimizer:
         self._compute_clip_coefficient()
         c = self._config
         for group in self._param_groups:
-            lr_scale = group["lr_scale"] * (c.default_learning_rate_scale if group["lr_scale"] == 1.0 else 1.0)
+            lr_scale = c.default_learning_rate_scale if group["lr_scale"] is None else group["lr_scale"]
             wd = c.weight_decay if group["weight_decay"] else 0.0
             if self._weight_arena is not None and group.get("buffer") is not None and group["params"].numel() % 4 == 0:
                 from fast_llm_b200.parallel.symmetric import adam_push
@@ -183,7 +195,7 @@ class Optimizer:
 
     def load(self, state: dict, validate: bool = True) -> None:
         self._current_step = state.get("current_step", 0)
-        self._grad_scaler.load(state.get("grad_scaler", {}))
+        self._grad_scaler.load(state.get("grad_scaler", {}), validate)
 
     def reset_state(self) -> None:
         self._current_step = 0

@@ -20,6 +20,7 @@ from fast_llm_b200.engine.training.config import TrainerConfig
 from fast_llm_b200.parallel.collectives import allreduce_scalar, broadcast_scalar, safe_barrier
 from fast_llm_b200.parallel.topology import PhaseType
 from fast_llm_b200.utils import Interrupter, get_and_reset_memory_usage_mib
+from fast_llm_b200.utils.device_errors import check_device_errors, register_kernel_library_sources
 from fast_llm_b200.utils.metrics import format_metrics
 
 logger = logging.getLogger(__name__)
@@ -94,7 +95,14 @@ class Trainer:
             self._evaluators[name] = evaluator
         for name, callback_config in config.callbacks.items():
             self._callbacks[name] = callback_config.get_callback(self._multi_stage)
+        if distributed.device.type == "cuda":
+            register_kernel_library_sources()
         safe_barrier(distributed.world_group, "data_preparation", config.training.timeout)
+
+    def _check_device_errors(self) -> None:
+        """Every rank raises if a bounded device-side wait (peer barrier, TMA / tensor-core pipeline) ran out on any rank
+        since the last call.  Called where the host synchronises anyway; nothing is written to disk past a failure."""
+        check_device_errors(self._distributed.world_group, self._distributed.device)
 
     def _get_preprocessing(self, phase: PhaseType) -> dict:
         pre = self._multi_stage.base_model.get_preprocessing_config(phase)
@@ -165,6 +173,7 @@ class Trainer:
                 if is_logging:
                     if has_gpu:
                         torch.cuda.synchronize()
+                    self._check_device_errors()
                     now = time.perf_counter()
                     step_time = (now - last_time) / max(self._completed_steps - last_iteration, 1)
                     remaining = config.train_iters - self._completed_steps
@@ -193,6 +202,8 @@ class Trainer:
                     total_losses = {}
                 profiler.step()
                 done = self._completed_steps >= config.train_iters
+                if done:
+                    self._check_device_errors()
                 for name, evaluator in self._evaluators.items():
                     result = evaluator.run(self._completed_steps, force=done)
                     if result:
@@ -241,6 +252,7 @@ class Trainer:
 
     def _save_checkpoint(self, config, metrics: dict | None, iteration: int | None = None) -> None:
         iteration = self._completed_steps if iteration is None else iteration
+        self._check_device_errors()
         directory = self._checkpoint_base(config) / str(iteration)
         if self._run.is_main_rank:
             directory.mkdir(parents=True, exist_ok=True)

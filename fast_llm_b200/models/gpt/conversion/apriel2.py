@@ -257,7 +257,7 @@ class Apriel2HuggingfaceCheckpointHandler(HuggingfaceStateDictCheckpointHandler)
             decoder_out = {"type": "pattern", "num_blocks": decoder.num_blocks, "pattern": list(decoder.pattern),
                            "blocks": {name: _block_export(block) for name, block in decoder.blocks.items()}}
         return {
-            "model_type": cls.model_type, "architectures": [cls.architecture], "torch_dtype": "bfloat16",
+            "model_type": cls.model_type, "architectures": [cls.architecture],
             "hidden_size": c.hidden_size, "vocab_size": c.embeddings.vocab_size, "tie_word_embeddings": c.tied_embedding_weight,
             "decoder": decoder_out, "head": {"normalization": _normalization_export(c.head.normalization)},
             "auto_map": {"AutoConfig": "configuration_apriel2.Apriel2TextConfig", "AutoModel": "modeling_apriel2.Apriel2TextModel",

@@ -173,7 +173,7 @@ class LlamaHuggingfaceCheckpointHandler(HuggingfaceStateDictCheckpointHandler):
             "num_attention_heads": mixer.heads, "num_key_value_heads": mixer.head_groups, "head_dim": mixer.head_size,
             "intermediate_size": mlp.intermediate_size, "hidden_act": mlp.activation.hf_name, "rms_norm_eps": norm.epsilon,
             "rope_theta": theta, "rope_scaling": scaling, "tie_word_embeddings": c.tied_embedding_weight,
-            "mlp_bias": mlp.add_linear_biases, "attention_dropout": mixer.dropout, "torch_dtype": "bfloat16",
+            "mlp_bias": mlp.add_linear_biases, "attention_dropout": mixer.dropout,
             "max_position_embeddings": c.embeddings.num_position_embeddings,
         }
         out.update(cls._export_attention_bias(mixer))
@@ -461,7 +461,7 @@ class AprielHybridSSMHuggingfaceCheckpointHandler(MistralHuggingfaceCheckpointHa
             out = {"model_type": cls.model_type, "architectures": [cls.architecture], "vocab_size": c.embeddings.vocab_size,
                    "hidden_size": c.hidden_size, "num_hidden_layers": len(blocks), "intermediate_size": first.mlp.intermediate_size,
                    "hidden_act": first.mlp.activation.hf_name, "rms_norm_eps": first.normalization.epsilon,
-                   "tie_word_embeddings": c.tied_embedding_weight, "torch_dtype": "bfloat16"}
+                   "tie_word_embeddings": c.tied_embedding_weight}
         out["num_hidden_layers"] = len(blocks)
         out["hybrid_block_layout"] = layout
         mamba = next((b.mixer for b in blocks if type(b.mixer).__name__ == "MambaConfig"), None)

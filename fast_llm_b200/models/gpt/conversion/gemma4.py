@@ -97,7 +97,7 @@ class Gemma4HuggingfaceCheckpointHandler(HuggingfaceStateDictCheckpointHandler):
         hybrid = _is_hybrid(sliding.mlp)
         Assert.eq(_is_hybrid(full.mlp), hybrid)
         out = {
-            "model_type": cls.model_type, "architectures": [cls.architecture], "torch_dtype": "bfloat16",
+            "model_type": cls.model_type, "architectures": [cls.architecture],
             "vocab_size": c.embeddings.vocab_size, "hidden_size": c.hidden_size, "tie_word_embeddings": c.tied_embedding_weight,
             "num_hidden_layers": decoder.num_blocks, "layer_types": list(decoder.expanded_pattern),
             "num_attention_heads": s.heads, "num_key_value_heads": s.head_groups, "head_dim": s.head_size, "global_head_dim": f.head_size,

@@ -82,7 +82,7 @@ class LlavaHuggingfaceCheckpointHandler(HuggingfaceStateDictCheckpointHandler):
             },
             "projector_hidden_act": adapter.activation.hf_name, "multimodal_projector_bias": adapter.add_linear_biases,
             "image_token_index": c.image_token_index, "vision_feature_layer": -1, "vision_feature_select_strategy": "full",
-            "tie_word_embeddings": False, "torch_dtype": "bfloat16",
+            "tie_word_embeddings": False,
         }
 
     @classmethod

@@ -62,10 +62,11 @@ _SIGNATURES = {
     "flb_symm_signal_pad_bytes": [_i],
     "flb_symm_barrier": [_p, _i, _i, _i, ctypes.c_uint, _p, _p],
     "flb_rs_reduce_blocks": [],
-    "flb_rs_reduce": [_p, _i, _i, _i, _ll, _f, _p, _i, _p, _p],
-    "flb_slot_sum_bf16": [_p, _p, _i, _ll, _p],
+    "flb_symm_set_barrier_limit": [_ll],
+    "flb_rs_reduce": [_p, _i, _i, _i, _ll, _f, _p, _i, _p, _p, _p],
+    "flb_slot_sum_bf16": [_p, _p, _i, _ll, _p, _p],
     "flb_peer_copy": [_p, _p, _ll, _i, _p],
-    "flb_adam_push": [_p, _p, _p, _p, _p, _i, _ll, _ll, _f, _f, _f, _f, _f, _i, _f, _p, _p],
+    "flb_adam_push": [_p, _p, _p, _p, _p, _i, _ll, _ll, _f, _f, _f, _f, _f, _i, _f, _p, _p, _p],
 }
 
 _STATUS = {1: "unsupported shape or alignment", 2: "CUDA error", 3: "tensor map encoding failed", 4: "size exceeds the stated maximum"}
@@ -88,6 +89,7 @@ def get_lib() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = _i
+    lib.flb_symm_set_barrier_limit.restype = _ll
     lib.flb_last_cuda_error.restype = ctypes.c_char_p
     lib.flb_last_cuda_error.argtypes = []
     return lib

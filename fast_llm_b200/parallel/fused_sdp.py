@@ -87,6 +87,7 @@ class FusedSequenceDataExchange:
         self.arena.barrier(2)
         out = torch.empty(rows, width, dtype=full.dtype, device=full.device)
         staged = self.arena.buffer[base : base + self.world * nbytes]
-        _lib.check(lib.flb_slot_sum_bf16(staged.data_ptr(), out.data_ptr(), self.world, rows * width, _lib.stream_ptr()), "flb_slot_sum_bf16")
+        _lib.check(lib.flb_slot_sum_bf16(staged.data_ptr(), out.data_ptr(), self.world, rows * width, self.arena.error_word.data_ptr(),
+                                         _lib.stream_ptr()), "flb_slot_sum_bf16")
         _lib.count_launch()
         return out

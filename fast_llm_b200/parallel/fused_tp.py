@@ -175,7 +175,8 @@ class FusedTensorParallel:
                      c_ptr=self.arena.peer_ptrs[j] + offset + self.rank * slot_bytes, direct_store=self.direct_peer_stores and j != self.rank)
         self.arena.barrier(_SCATTER_SLOT)
         out = torch.empty(rows, n, dtype=x.dtype, device=x.device)
-        _lib.check(_lib.get_lib().flb_slot_sum_bf16(local.data_ptr(), out.data_ptr(), self.world, rows * n, _lib.stream_ptr()), "flb_slot_sum_bf16")
+        _lib.check(_lib.get_lib().flb_slot_sum_bf16(local.data_ptr(), out.data_ptr(), self.world, rows * n, self.arena.error_word.data_ptr(),
+                                                    _lib.stream_ptr()), "flb_slot_sum_bf16")
         _lib.count_launch()
         return out
 

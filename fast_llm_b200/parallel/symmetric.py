@@ -16,6 +16,36 @@ from fast_llm_b200.ops import _lib
 logger = logging.getLogger(__name__)
 
 _SIGNAL_SLOTS = 8
+# One error word per device, shared by every arena of the process: a barrier of the gradient arena that gives up must
+# also stop the Adam kernel that pushes through the weight arena.
+_error_words: dict[int, torch.Tensor] = {}
+
+
+def shared_error_word(device: torch.device) -> torch.Tensor:
+    index = torch.device(device).index
+    index = torch.cuda.current_device() if index is None else index
+    if index not in _error_words:
+        from fast_llm_b200.utils.device_errors import register_error_source
+
+        _error_words[index] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", index))
+        register_error_source(f"symmetric_memory_cuda{index}", lambda: read_error_word(index))
+    return _error_words[index]
+
+
+def read_error_word(index: int) -> str | None:
+    """Description of a device-side barrier that gave up since the last read (clears the word; synchronises)."""
+    word = int(_error_words[index].item())
+    if not word:
+        return None
+    _error_words[index].zero_()
+    return f"a symmetric-memory barrier on cuda:{index} timed out waiting for rank {word - 100} of its group"
+
+
+def set_barrier_limit_seconds(seconds: float, sm_clock_hz: float = 2.0e9) -> float:
+    """Longest wait of later device-side barriers (default about 10 s); returns the previous limit in seconds.
+    The kernel counts SM clock cycles, `sm_clock_hz` converts (the boost clock gives the shortest wait)."""
+    old = _lib.get_lib().flb_symm_set_barrier_limit(max(int(seconds * sm_clock_hz), 1))
+    return old / sm_clock_hz
 
 
 class SymmetricArena:
@@ -41,7 +71,7 @@ class SymmetricArena:
         self._pad_handle = symm_mem.rendezvous(self._pad, group)
         self._pad_ptrs = (ctypes.c_void_p * self.world_size)(*[int(p) for p in self._pad_handle.buffer_ptrs])
         self._epochs = [0] * _SIGNAL_SLOTS
-        self.error_word = torch.zeros(1, dtype=torch.int32, device=device)
+        self.error_word = shared_error_word(device)
         torch.cuda.synchronize(device)
         torch.distributed.barrier(group)  # pads are zeroed everywhere before the first device-side barrier
 
@@ -61,10 +91,9 @@ class SymmetricArena:
         _lib.count_launch()
 
     def check_errors(self) -> None:
-        word = int(self.error_word.item())
-        if word:
-            self.error_word.zero_()
-            raise RuntimeError(f"symmetric-memory barrier timed out waiting for rank {word - 100}")
+        message = read_error_word(self.error_word.device.index)
+        if message:
+            raise RuntimeError(message)
 
 
 def symmetric_memory_available(group, device) -> bool:
@@ -84,7 +113,8 @@ def rs_reduce(arena: SymmetricArena, grad_buffer: torch.Tensor, grad_shard: torc
     ptrs = arena.peer_pointer_array(arena.offset_of(grad_buffer))
     dtype_code = 0 if grad_buffer.dtype == torch.float32 else 1
     _lib.check(_lib.get_lib().flb_rs_reduce(ptrs, dtype_code, arena.rank, arena.world_size, shard_size, scale,
-                                            grad_shard.data_ptr(), int(accumulate), _lib.ptr(sumsq_partial), _lib.stream_ptr()), "flb_rs_reduce")
+                                            grad_shard.data_ptr(), int(accumulate), _lib.ptr(sumsq_partial), arena.error_word.data_ptr(),
+                                            _lib.stream_ptr()), "flb_rs_reduce")
     _lib.count_launch()
 
 
@@ -95,5 +125,5 @@ def adam_push(arena: SymmetricArena, w, g, m, v, buffer_slice: torch.Tensor, lr,
     ptrs = arena.peer_pointer_array(0)
     _lib.check(_lib.get_lib().flb_adam_push(w.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), ptrs, arena.world_size,
                                             byte_offset // 2, w.numel(), lr, beta1, beta2, eps, wd, step, 1.0,
-                                            _lib.ptr(gscale_tensor), _lib.stream_ptr()), "flb_adam_push")
+                                            _lib.ptr(gscale_tensor), arena.error_word.data_ptr(), _lib.stream_ptr()), "flb_adam_push")
     _lib.count_launch()
