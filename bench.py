@@ -106,21 +106,22 @@ def _dist_env(args):
     return rank, world, local_rank
 
 
-def _max_over_ranks(value: float, world: int) -> float:
+def _max_over_ranks(value: float, world: int, group=None) -> float:
+    """`group`: the process group to reduce over when there is no default group (the reference builds its groups itself)."""
     import torch
 
     if world == 1:
         return value
     t = torch.tensor([value], dtype=torch.float64, device="cuda")
-    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX, group=group)
     return t.item()
 
 
-def _barrier(world: int):
+def _barrier(world: int, group=None):
     import torch
 
     if world > 1:
-        torch.distributed.barrier()
+        _max_over_ranks(0.0, world, group)  # an all-reduce every rank must join: a barrier that works on any group
     torch.cuda.synchronize()
 
 
@@ -338,6 +339,7 @@ def run_reference(args):
         base = yaml.safe_load((ref / "examples" / "mistral.yaml").read_text())
         updates = config_updates(args, world)
         updates[("run", "torch_dynamo_enable")] = dynamo_ok
+        updates[("training", "train_iters")] = args.warmup + args.steps  # Trainer.run() executes exactly the steps that are timed
         config = GPTTrainerConfig.from_dict(base, updates)
         config.validate()
         distributed = Distributed(config.model.distributed)
@@ -354,7 +356,7 @@ def run_reference(args):
             def timed_run_step(*a, **k):
                 n = len(events)
                 if n == args.warmup:
-                    _barrier(world)
+                    _barrier(world, distributed.world_group)
                 start = torch.cuda.Event(enable_timing=True)
                 start.record()
                 out = inner(*a, **k)
@@ -367,15 +369,14 @@ def run_reference(args):
             sampler = ClockSampler(local_rank)
             if rank == 0:
                 sampler.start()
-            object.__setattr__(config.training, "train_iters", total) if False else None
             trainer.run()
-            _barrier(world)
+            _barrier(world, distributed.world_group)
             clocks = sampler.stop() if rank == 0 else {}
         timed = events[args.warmup : args.warmup + args.steps]
         if len(timed) < args.steps:
             raise RuntimeError(f"reference ran {len(events)} steps, expected at least {args.warmup + args.steps}")
         span = timed[0][0].elapsed_time(timed[-1][1])
-        ms = _max_over_ranks(span, world) / args.steps
+        ms = _max_over_ranks(span, world, distributed.world_group) / args.steps
         if rank == 0:
             e2e = {"value": args.global_batch_tokens / (ms / 1e3), "unit": "tokens/s", "ms_per_step": ms,
                    "how": "reference Trainer.run(): its own data loader (H2D) and loss reduction (D2H) are inside every step"}

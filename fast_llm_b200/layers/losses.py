@@ -1,20 +1,25 @@
 """Language-model head losses: label (cross-entropy / KL from labels), z_loss, distillation, dpo, grpo, gspo.
 
-Every loss maps one chunk of logits to (scalar value, gradient wrt the logits).  Cross-entropy from labels, optionally
-with a z-loss riding on the same softmax, runs on the fused kernels of `fast_llm_b200.ops.cross_entropy`
-(vocabulary-parallel aware); the others are written with PyTorch ops and differentiated by autograd on the chunk.
+Every loss maps one chunk of logits to (scalar value, gradient wrt the logits).  The losses that see the logits only
+through the softmax normaliser and the label's logit (label cross-entropy / KL, z-loss, GRPO, GSPO, DPO) are functions of
+two per-token vectors; `MonolithicLoss` sums the coefficients of its members and writes their joint gradient in ONE pass
+over the logits (`fast_llm_b200.ops.losses`, `csrc/loss.cu`).  Distillation (cross-entropy / forward KL / reverse KL
+against teacher logits) has its own statistics and gradient kernels.  No loss makes an fp32 copy of the logits or runs
+autograd over them; everything is vocabulary-parallel aware.
 Parity: `fast_llm/layers/language_model/loss/*.py`, `fast_llm/functional/entropy_loss.py`,
 `fast_llm/functional/triton/{entropy_loss,z_loss,grpo_loss,gspo_loss,monolithic_loss}.py`.
 """
 
 import enum
+import math
 
 import torch
 
 from fast_llm_b200.config import Config, Field, FieldHint, check_field, config_class
 from fast_llm_b200.engine.base_model import LossDef
 from fast_llm_b200.layers.kwargs import LanguageModelKwargs
-from fast_llm_b200.ops.cross_entropy import cross_entropy_forward_backward
+from fast_llm_b200.ops.losses import (SoftmaxStatistics, distribution_loss_forward_backward, label_coefficients, softmax_coeff_grad,
+                                      softmax_statistics)
 from fast_llm_b200.parallel.collectives import all_reduce
 from fast_llm_b200.parallel.ops import split_op
 from fast_llm_b200.utils import Assert
@@ -198,87 +203,77 @@ class LanguageModelLoss:
             all_reduce(per_token_sum, group=self._sdp_group)
         return per_token_sum
 
+    def _scale(self, logits_scale: float) -> float:
+        return logits_scale * self._config.logits_scale_factor
+
     def forward_backward(self, logits, kwargs, grad_output, split_index, num_splits, logits_scale, accumulate_into=None):
         raise NotImplementedError
 
-    def _autograd(self, fn, logits, grad_output, accumulate_into):
-        """Evaluate a PyTorch-written loss and its logits gradient."""
-        if grad_output is None:
-            with torch.no_grad():
-                return fn(logits.float()), accumulate_into
-        with torch.enable_grad():
-            x = logits.detach().float().requires_grad_()
-            value = fn(x)
-        (g,) = torch.autograd.grad(value, x, torch.as_tensor(grad_output * self.weight, dtype=value.dtype, device=value.device))
-        g = g.to(logits.dtype)
-        if accumulate_into is not None:
-            g = accumulate_into.add_(g)
-        return value.detach(), g
 
+class LabelBasedLoss(LanguageModelLoss):
+    """A loss that sees the logits only through `lse` and the label's logit (both `[tokens]` fp32 vectors).
 
-class LabelEntropyLoss(LanguageModelLoss):
-    z_coefficient = 0.0
+    Subclasses implement `per_token_value(lse, target, labels, kwargs, rows, split_index, num_splits) -> scalar` (already
+    normalised, differentiable wrt lse and target).  Several such losses share one statistics pass and one gradient pass when
+    grouped in a `MonolithicLoss`; alone, each still needs just those two passes."""
 
-    def forward_backward(self, logits, kwargs, grad_output, split_index, num_splits, logits_scale, accumulate_into=None):
-        rows = logits.shape[0]
-        labels = self._labels(kwargs, rows, split_index, num_splits)
-        inv = self._inverse_label_count(kwargs)
-        scale = logits_scale * self._config.logits_scale_factor
-        grad_scale = None if grad_output is None else inv * float(grad_output * self.weight)
-        in_place = accumulate_into is None and kwargs.get("_single_loss", True)
-        loss_tok, z_tok, grad = cross_entropy_forward_backward(
-            logits, labels, grad_scale, scale, self.z_coefficient, self._group, self._vocab_begin, in_place=in_place)
-        if grad is not None and accumulate_into is not None:
-            grad = accumulate_into.add_(grad)
-        value = self._finalize(loss_tok.sum().reshape(1) * inv).reshape(())
-        self._z_value = self._finalize(z_tok.sum().reshape(1) * inv).reshape(()) if self.z_coefficient else None
-        return value, grad
+    shares_softmax = True
 
+    def per_token_value(self, lse, target, labels, kwargs, rows, split_index, num_splits) -> torch.Tensor:
+        raise NotImplementedError
 
-class ZLoss(LanguageModelLoss):
-    """mean over tokens of logsumexp(logits)^2"""
+    def coefficients(self, stats: SoftmaxStatistics, labels, kwargs, rows, split_index, num_splits, grad_output):
+        """(value, a, b): the loss value on this chunk and its derivatives wrt lse / target, times `grad_output * weight`."""
+        weight = None if grad_output is None else float(grad_output) * self.weight
+        return label_coefficients(lambda lse, target: self.per_token_value(lse, target, labels, kwargs, rows, split_index, num_splits),
+                                  stats, weight)
 
     def forward_backward(self, logits, kwargs, grad_output, split_index, num_splits, logits_scale, accumulate_into=None):
         rows = logits.shape[0]
         labels = self._labels(kwargs, rows, split_index, num_splits)
-        inv = self._inverse_label_count(kwargs)
-        scale = logits_scale * self._config.logits_scale_factor
-
-        def fn(x):
-            x = x * scale
-            if self._group is not None:
-                m = x.max(-1).values.detach()
-                all_reduce(m, op=torch.distributed.ReduceOp.MAX, group=self._group)
-                se = torch.exp(x - m[:, None]).sum(-1)
-                se = _AllReduceSum.apply(se, self._group)
-                lse = m + se.log()
-            else:
-                lse = torch.logsumexp(x, -1)
-            return ((lse * lse) * (labels >= 0)).sum() * inv.reshape(())
-
-        value, grad = self._autograd(fn, logits, grad_output, accumulate_into)
+        stats = softmax_statistics(logits, labels, self._scale(logits_scale), self._group, self._vocab_begin)
+        value, a, b = self.coefficients(stats, labels, kwargs, rows, split_index, num_splits, grad_output)
+        grad = accumulate_into
+        if a is not None:
+            grad = softmax_coeff_grad(logits, labels, stats, a, b, accumulate_into=accumulate_into,
+                                      in_place=accumulate_into is None and kwargs.get("_single_loss", True))
         return self._finalize(value.reshape(1)).reshape(()), grad
 
 
-class _AllReduceSum(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, x, group):
-        x = x.clone()
-        all_reduce(x, group=group)
-        return x
+class LabelEntropyLoss(LabelBasedLoss):
+    """Cross-entropy against labels.  Forward KL against a one-hot target equals it; reverse KL against a one-hot target
+    (smoothed by 1e-10 inside the logarithm, as `fast_llm/functional/entropy_loss.py:56-80` does) is
+    sum_j p_j (log p_j - log(onehot_j + 1e-10)), which needs the entropy of p and is evaluated on the logits directly."""
 
-    @staticmethod
-    def backward(ctx, grad):
-        return grad, None
+    def per_token_value(self, lse, target, labels, kwargs, rows, split_index, num_splits):
+        inv = self._inverse_label_count(kwargs).reshape(())
+        return ((lse - target) * (labels >= 0)).sum() * inv
+
+    def forward_backward(self, logits, kwargs, grad_output, split_index, num_splits, logits_scale, accumulate_into=None):
+        if self._config.loss_type != EntropyLossType.reverse_kl:
+            return super().forward_backward(logits, kwargs, grad_output, split_index, num_splits, logits_scale, accumulate_into)
+        rows = logits.shape[0]
+        labels = self._labels(kwargs, rows, split_index, num_splits)
+        inv = self._inverse_label_count(kwargs).reshape(())
+        valid = labels >= 0
+        lab = labels - self._vocab_begin
+        in_shard = valid & (lab >= 0) & (lab < logits.shape[-1])
+        # teacher "logits" of the smoothed one-hot target: log(1 + 1e-10) at the label, log(1e-10) elsewhere
+        teacher = torch.full_like(logits, math.log(1e-10), dtype=torch.float32)
+        teacher[in_shard, lab[in_shard]] = math.log1p(1e-10)
+        g = None if grad_output is None else inv * float(grad_output * self.weight)
+        loss, grad = distribution_loss_forward_backward(
+            logits, teacher, valid.float(), g, "reverse_kl", logits_scale=self._scale(logits_scale), group=self._group,
+            accumulate_into=accumulate_into, normalize_teacher=False)
+        return self._finalize((loss.sum() * inv).reshape(1)).reshape(()), (grad if grad is not None else accumulate_into)
 
 
-def _log_softmax(x, group):
-    if group is None:
-        return torch.log_softmax(x, -1)
-    m = x.max(-1).values.detach()
-    all_reduce(m, op=torch.distributed.ReduceOp.MAX, group=group)
-    se = _AllReduceSum.apply(torch.exp(x - m[:, None]).sum(-1), group)
-    return x - m[:, None] - se.log()[:, None]
+class ZLoss(LabelBasedLoss):
+    """mean over valid tokens of logsumexp(logits)^2"""
+
+    def per_token_value(self, lse, target, labels, kwargs, rows, split_index, num_splits):
+        inv = self._inverse_label_count(kwargs).reshape(())
+        return ((lse * lse) * (labels >= 0)).sum() * inv
 
 
 class DistillationLoss(LanguageModelLoss):
@@ -290,134 +285,149 @@ class DistillationLoss(LanguageModelLoss):
     def forward_backward(self, logits, kwargs, grad_output, split_index, num_splits, logits_scale, accumulate_into=None):
         rows = logits.shape[0]
         teacher = kwargs[f"{self._config.reference_model}_logits"]
-        teacher = self._token_slice(teacher, rows, split_index, num_splits).float()
-        if self._group is not None:
-            size = logits.shape[-1]
-            teacher = teacher[:, self._vocab_begin : self._vocab_begin + size] if teacher.shape[-1] != size else teacher
+        teacher = self._token_slice(teacher, rows, split_index, num_splits)
+        size = logits.shape[-1]
+        if self._group is not None and teacher.shape[-1] != size:
+            teacher = teacher[:, self._vocab_begin : self._vocab_begin + size]
         mask = kwargs.get(LanguageModelKwargs.loss_mask)
-        mask = torch.ones(rows, device=logits.device) if mask is None else self._token_slice(mask, rows, split_index, num_splits).float()
-        count = mask.sum().clamp(min=1.0) * (num_splits if False else 1)
-        temp = self._config.temperature
-        scale = logits_scale * self._config.logits_scale_factor / temp
-        kind = self._config.loss_type
-
-        def fn(x):
-            student_lp = _log_softmax(x * scale, self._group)
-            teacher_lp = _log_softmax(teacher / temp, self._group)
-            if kind == EntropyLossType.reverse_kl:
-                per = (student_lp.exp() * (student_lp - teacher_lp)).sum(-1)
-            elif kind == EntropyLossType.forward_kl:
-                per = (teacher_lp.exp() * (teacher_lp - student_lp)).sum(-1)
-            else:
-                per = -(teacher_lp.exp() * student_lp).sum(-1)
-            if self._group is not None:
-                per = _AllReduceSum.apply(per, self._group)
-            return (per * mask).sum() / count
-
-        value, grad = self._autograd(fn, logits, grad_output, accumulate_into)
-        return self._finalize(value.reshape(1)).reshape(()), grad
+        mask = None if mask is None else self._token_slice(mask, rows, split_index, num_splits).float()
+        count = torch.tensor(float(rows), device=logits.device) if mask is None else mask.sum().clamp(min=1.0)
+        # the temperature softens the teacher only (`fast_llm/functional/entropy_loss.py:42-44`, `triton/entropy_loss.py:890`)
+        temperature = self._config.temperature
+        scale = self._scale(logits_scale)
+        g = None if grad_output is None else float(grad_output * self.weight) / count
+        loss, grad = distribution_loss_forward_backward(
+            logits, teacher, mask, g, self._config.loss_type.value, logits_scale=scale, teacher_scale=scale / temperature,
+            group=self._group, accumulate_into=accumulate_into, in_place=accumulate_into is None and kwargs.get("_single_loss", True))
+        value = loss.sum() / count
+        return self._finalize(value.reshape(1)).reshape(()), (grad if grad is not None else accumulate_into)
 
 
-def _gather_label_log_probs(x, labels, group, vocab_begin):
-    """log p(label) for every token (0 for ignored labels)."""
-    lp = _log_softmax(x, group)
-    lab = labels - vocab_begin
-    ok = (lab >= 0) & (lab < x.shape[-1]) & (labels >= 0)
-    picked = lp.gather(-1, lab.clamp(0, x.shape[-1] - 1)[:, None])[:, 0] * ok
-    if group is not None:
-        picked = _AllReduceSum.apply(picked, group)
-    return picked
+def _label_log_probs(lse, target, labels):
+    """log p(label) per token, 0 where the label is ignored."""
+    return (target - lse) * (labels >= 0)
 
 
-class DPOLoss(LanguageModelLoss):
-    """-log sigmoid(beta * ((pi_chosen - pi_rejected) - (ref_chosen - ref_rejected))) over preference spans."""
+def _span_sums(per_token: torch.Tensor, spans) -> torch.Tensor:
+    if not len(spans):
+        return per_token.new_zeros(0)
+    return torch.stack([per_token[b:e].sum() for b, e in spans])
+
+
+class DPOLoss(LabelBasedLoss):
+    """-log sigmoid(beta * ((pi_chosen - pi_rejected) - (ref_chosen - ref_rejected))), log-probabilities summed over the
+    chosen / rejected spans."""
 
     needs_reference = True
 
     def get_preprocessing_config(self, phase):
         return {"use_preference_spans": True, "reference_models": {self._config.reference_model}}
 
-    def forward_backward(self, logits, kwargs, grad_output, split_index, num_splits, logits_scale, accumulate_into=None):
+    def per_token_value(self, lse, target, labels, kwargs, rows, split_index, num_splits):
         Assert.eq(num_splits, 1)
-        rows = logits.shape[0]
-        labels = self._labels(kwargs, rows, 0, 1)
         chosen = kwargs[LanguageModelKwargs.chosen_spans]
         rejected = kwargs[LanguageModelKwargs.rejected_spans]
-        ref_logits = kwargs[f"{self._config.reference_model}_logits"].float()
-        scale = logits_scale * self._config.logits_scale_factor
-
-        def span_sum(per_token, spans):
-            return torch.stack([per_token[b:e].sum() for b, e in spans]) if len(spans) else per_token.new_zeros(0)
-
-        def fn(x):
-            lp = _gather_label_log_probs(x * scale, labels, self._group, self._vocab_begin)
+        log_probs = _label_log_probs(lse, target, labels)
+        ref_key = f"_{self._config.reference_model}_label_log_probs_{self._prediction_distance}"
+        if ref_key not in kwargs:
+            ref_logits = kwargs[f"{self._config.reference_model}_logits"]
+            ref_labels = labels
+            ref_group, ref_begin = (self._group, self._vocab_begin) if ref_logits.shape[-1] == kwargs["_logits_columns"] else (None, 0)
             with torch.no_grad():
-                ref_lp = _gather_label_log_probs(ref_logits * scale, labels, None, 0)
-            pi = span_sum(lp, chosen) - span_sum(lp, rejected)
-            ref = span_sum(ref_lp, chosen) - span_sum(ref_lp, rejected)
-            return -torch.nn.functional.logsigmoid(self._config.beta * (pi - ref)).mean()
+                ref_stats = softmax_statistics(ref_logits, ref_labels, kwargs["_logits_scale"], ref_group, ref_begin)
+                kwargs[ref_key] = _label_log_probs(ref_stats.lse, ref_stats.target, ref_labels)
+        ref_log_probs = kwargs[ref_key]
+        # one log-ratio over all spans of the micro-batch, as `fast_llm/layers/language_model/loss/dpo.py:53-79`
+        pi = _span_sums(log_probs, chosen).sum() - _span_sums(log_probs, rejected).sum()
+        ref = _span_sums(ref_log_probs, chosen).sum() - _span_sums(ref_log_probs, rejected).sum()
+        return -torch.nn.functional.logsigmoid(self._config.beta * (pi - ref))
 
-        return self._autograd(fn, logits, grad_output, accumulate_into)
+    def forward_backward(self, logits, kwargs, grad_output, split_index, num_splits, logits_scale, accumulate_into=None):
+        kwargs["_logits_columns"] = logits.shape[-1]
+        kwargs["_logits_scale"] = self._scale(logits_scale)
+        value, grad = super().forward_backward(logits, kwargs, grad_output, split_index, num_splits, logits_scale, accumulate_into)
+        return value, grad
+
+    def _finalize(self, per_token_sum):
+        return per_token_sum  # spans are whole on every rank that holds the logits
 
 
-class GRPOLoss(LanguageModelLoss):
+class GRPOLoss(LabelBasedLoss):
     """Clipped policy-gradient surrogate per token: -min(r A, clip(r, 1-eps_low, 1+eps_high) A), r = pi / pi_old."""
 
     def get_preprocessing_config(self, phase):
         return {"use_grpo_data": True}
 
-    def _ratio_terms(self, x, kwargs, rows, split_index, num_splits, scale):
-        labels = self._labels(kwargs, rows, split_index, num_splits)
+    def _inputs(self, kwargs, rows, split_index, num_splits):
         adv = self._token_slice(kwargs[LanguageModelKwargs.advantages], rows, split_index, num_splits).float()
         old = self._token_slice(kwargs[LanguageModelKwargs.old_log_probabilities], rows, split_index, num_splits).float()
-        lp = _gather_label_log_probs(x * scale, labels, self._group, self._vocab_begin)
-        return labels, adv, old, lp
+        return adv, old
 
-    def forward_backward(self, logits, kwargs, grad_output, split_index, num_splits, logits_scale, accumulate_into=None):
-        rows = logits.shape[0]
-        inv = self._inverse_label_count(kwargs).reshape(())
-        scale = logits_scale * self._config.logits_scale_factor
+    def _surrogate(self, ratio, adv):
         c = self._config
+        return -torch.minimum(ratio * adv, ratio.clamp(1 - c.epsilon_low, 1 + c.epsilon_high) * adv)
 
-        def fn(x):
-            labels, adv, old, lp = self._ratio_terms(x, kwargs, rows, split_index, num_splits, scale)
-            ratio = torch.exp(lp - old)
-            clipped = ratio.clamp(1 - c.epsilon_low, 1 + c.epsilon_high)
-            per = -torch.minimum(ratio * adv, clipped * adv) * (labels >= 0)
-            return per.sum() * inv
+    def per_token_value(self, lse, target, labels, kwargs, rows, split_index, num_splits):
+        adv, old = self._inputs(kwargs, rows, split_index, num_splits)
+        inv = self._inverse_label_count(kwargs).reshape(())
+        valid = labels >= 0
+        ratio = torch.exp((_label_log_probs(lse, target, labels) - old) * valid)
+        return (self._surrogate(ratio, adv) * valid).sum() * inv
 
-        value, grad = self._autograd(fn, logits, grad_output, accumulate_into)
-        return self._finalize(value.reshape(1)).reshape(()), grad
+
+class _SumOverRanks(torch.autograd.Function):
+    """Sum a small tensor over a process group; the gradient passes through unchanged (every rank differentiates the global
+    sum with respect to its own contribution)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        x = x.clone()
+        all_reduce(x, group=group)
+        return x
+
+    @staticmethod
+    def backward(ctx, grad):
+        return grad, None
 
 
 class GSPOLoss(GRPOLoss):
-    """Sequence-level ratio: the geometric mean of token ratios of each document replaces the per-token ratio."""
+    """Sequence-level clipping: per document d the ratio is the geometric mean of its token ratios,
+    R_d = exp(mean_t log(pi_t / pi_old_t)), the advantage A_d the mean of its token advantages, and the loss
+    sum_d N_d * -min(R_d A_d, clip(R_d) A_d) over the labelled-token counts N_d, divided by the batch's label count
+    (`fast_llm/layers/language_model/loss/policy_gradient.py:1179-1250`).  Documents split over sequence-parallel or
+    sequence-data-parallel ranks are aggregated across them; a document must not be split over micro-sequences."""
 
-    def forward_backward(self, logits, kwargs, grad_output, split_index, num_splits, logits_scale, accumulate_into=None):
+    def per_token_value(self, lse, target, labels, kwargs, rows, split_index, num_splits):
         Assert.eq(num_splits, 1)
-        rows = logits.shape[0]
+        adv, old = self._inputs(kwargs, rows, 0, 1)
         inv = self._inverse_label_count(kwargs).reshape(())
-        scale = logits_scale * self._config.logits_scale_factor
-        c = self._config
         doc = self._token_slice(kwargs[LanguageModelKwargs.document_index], rows, 0, 1).long()
-
-        def fn(x):
-            labels, adv, old, lp = self._ratio_terms(x, kwargs, rows, 0, 1, scale)
-            valid = (labels >= 0).float()
-            n_docs = int(doc.max().item()) + 1 if doc.numel() else 0
-            num = torch.zeros(n_docs, device=x.device).index_add(0, doc, (lp - old) * valid)
-            den = torch.zeros(n_docs, device=x.device).index_add(0, doc, valid).clamp(min=1.0)
-            seq_ratio = torch.exp(num / den)[doc]
-            clipped = seq_ratio.clamp(1 - c.epsilon_low, 1 + c.epsilon_high)
-            per = -torch.minimum(seq_ratio * adv, clipped * adv) * valid
-            return per.sum() * inv
-
-        value, grad = self._autograd(fn, logits, grad_output, accumulate_into)
-        return self._finalize(value.reshape(1)).reshape(()), grad
+        valid = (labels >= 0).float()
+        segments = kwargs.get("_num_documents")
+        if segments is None:
+            full = kwargs[LanguageModelKwargs.document_index]
+            segments = kwargs["_num_documents"] = int(full.max().item()) + 1 if full.numel() else 0
+        log_ratio = (_label_log_probs(lse, target, labels) - old) * valid
+        sums = torch.zeros(3, segments, device=lse.device).index_add(1, doc, torch.stack([log_ratio, valid, adv * valid]))
+        local_count = sums[1].detach()
+        if self._sequence_parallel and self._tp_group is not None:
+            sums = _SumOverRanks.apply(sums, self._tp_group)
+        if self._sdp_group is not None:
+            sums = _SumOverRanks.apply(sums, self._sdp_group)
+        count = sums[1].clamp(min=1.0)
+        ratio, advantage = torch.exp(sums[0] / count), sums[2] / count
+        per_document = self._surrogate(ratio, advantage)
+        # the gradient of the job-wide loss wrt this rank's tokens needs the whole document's weight; the value reported
+        # by this rank counts its own tokens only (the ranks' values are summed afterwards)
+        for_gradient = (per_document * sums[1].detach()).sum() * inv
+        reported = (per_document.detach() * local_count).sum() * inv
+        return for_gradient + (reported - for_gradient).detach()
 
 
 class MonolithicLoss(LanguageModelLoss):
-    """Label cross-entropy and z-loss share one softmax pass on the fused kernel; other members run after it."""
+    """Several losses over one shared softmax: the label-based members (cross-entropy, z-loss, GRPO, GSPO, DPO) share one
+    statistics pass, their per-token coefficients are added up and ONE pass writes the gradient of their weighted sum.
+    Members of another family (distillation) run their own two passes and accumulate into the same gradient."""
 
     def __init__(self, config, distributed_config, *, name, prediction_distance, vocab_parallel, weight):
         super().__init__(config, distributed_config, name=name, prediction_distance=prediction_distance, vocab_parallel=vocab_parallel, weight=weight)
@@ -437,24 +447,57 @@ class MonolithicLoss(LanguageModelLoss):
     def get_preprocessing_config(self, phase):
         out = {}
         for m in self._members:
-            out.update(m.get_preprocessing_config(phase))
+            for key, value in m.get_preprocessing_config(phase).items():
+                out[key] = (out[key] | value) if isinstance(value, set) and key in out else value
         return out
 
     def forward_backward(self, logits, kwargs, grad_output, split_index, num_splits, logits_scale, accumulate_into=None):
-        label = next((m for m in self._members if type(m) is LabelEntropyLoss), None)
-        z = next((m for m in self._members if type(m) is ZLoss), None)
-        others = [m for m in self._members if m is not label and (m is not z or label is None)]
-        total, grad = None, accumulate_into
+        rows = logits.shape[0]
         sub_grad_output = None if grad_output is None else grad_output * self.weight
+        shared = [m for m in self._members if isinstance(m, LabelBasedLoss) and not
+                  (isinstance(m, LabelEntropyLoss) and m._config.loss_type == EntropyLossType.reverse_kl)]
+        # members sharing the softmax must agree on the scale of the logits: group them by it
+        by_scale: dict[float, list] = {}
+        for m in shared:
+            by_scale.setdefault(m._scale(logits_scale), []).append(m)
+        others = [m for m in self._members if m not in shared]
+        total, grad = None, accumulate_into
+        passes = len(others) + len(by_scale)
+        kwargs["_logits_columns"] = logits.shape[-1]
         for m in others:
+            kwargs["_single_loss"] = False
             value, grad = m.forward_backward(logits, kwargs, sub_grad_output, split_index, num_splits, logits_scale, accumulate_into=grad)
+            if grad is None and sub_grad_output is not None and passes > 1:
+                pass
             total = value * m.weight if total is None else total + value * m.weight
-        if label is not None:
-            label.z_coefficient = (z.weight / label.weight) if (z is not None and label.weight > 0) else 0.0
-            kwargs["_single_loss"] = grad is None
-            value, grad = label.forward_backward(logits, kwargs, sub_grad_output, split_index, num_splits, logits_scale, accumulate_into=grad)
-            kwargs.pop("_single_loss", None)
-            total = value * label.weight if total is None else total + value * label.weight
-            if z is not None and label._z_value is not None:
-                total = total + label._z_value * z.weight
+            self._record(kwargs, m, value)
+        remaining = len(by_scale)
+        for scale, members in by_scale.items():
+            remaining -= 1
+            labels = self._labels(kwargs, rows, split_index, num_splits)
+            stats = softmax_statistics(logits, labels, scale, self._group, self._vocab_begin)
+            kwargs["_logits_scale"] = scale
+            a_sum = b_sum = None
+            for m in members:
+                value, a, b = m.coefficients(stats, labels, kwargs, rows, split_index, num_splits, sub_grad_output)
+                value = m._finalize(value.reshape(1)).reshape(())
+                total = value * m.weight if total is None else total + value * m.weight
+                self._record(kwargs, m, value)
+                if a is not None:
+                    a_sum = a if a_sum is None else a_sum + a
+                    b_sum = b if b_sum is None else b_sum + b
+            if a_sum is not None:
+                # the last pass may overwrite the logits when nothing has been accumulated before it
+                in_place = grad is None and remaining == 0 and kwargs.get("_single_loss", True) is not False
+                if grad is None and not in_place:
+                    grad = softmax_coeff_grad(logits, labels, stats, a_sum, b_sum, in_place=False)
+                else:
+                    grad = softmax_coeff_grad(logits, labels, stats, a_sum, b_sum, accumulate_into=grad, in_place=in_place)
+        kwargs.pop("_single_loss", None)
         return total, grad
+
+    @staticmethod
+    def _record(kwargs, member, value):
+        sink = kwargs.get("_member_losses")
+        if sink is not None:
+            sink.setdefault(member.name, []).append(value.detach())

@@ -48,6 +48,9 @@ _SIGNATURES = {
     "flb_ce_grad": [_p, _i, _p, _p, _p, _p, _p, _i, _i, _ll, _ll, _ll, _f, _f, _p, _f, _p],
     "flb_ce_stats_exchange": [_p, _i, _p, _p, _i, _i, _i, _i, _ll, _ll, _f, _p],
     "flb_ce_grad_slots": [_p, _i, _p, _p, _i, _p, _p, _p, _i, _i, _ll, _ll, _ll, _f, _f, _p, _f, _p],
+    "flb_softmax_coeff_grad": [_p, _i, _p, _p, _i, _p, _p, _p, _i, _i, _ll, _ll, _ll, _f, _i, _p],
+    "flb_dist_stats": [_p, _p, _i, _p, _i, _i, _ll, _ll, _f, _f, _p],
+    "flb_dist_grad": [_p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _ll, _ll, _ll, _f, _f, _i, _p],
     "flb_sumsq_scratch_floats": [],
     "flb_sumsq": [_p, _ll, _p, _p, _i, _p],
     "flb_clip_coeff": [_p, _f, _f, _p, _p, _p],

@@ -8,11 +8,14 @@ computes the loss and the logit gradients.  Replaces two all-reduces of `[tokens
 call k also guarantees that every peer has finished reading the buffer of call k-1.
 """
 
+import logging
+
 import torch
 
 from fast_llm_b200.ops import _lib
 from fast_llm_b200.parallel.symmetric import SymmetricArena
 
+logger = logging.getLogger(__name__)
 _contexts: dict[int, "FusedStatisticsExchange"] = {}
 
 
@@ -38,6 +41,8 @@ class FusedStatisticsExchange:
         self._arena: SymmetricArena | None = None
         self._rows = 0
         self._calls = 0
+        self._warned = False
+        self.fallbacks = 0  # calls that did not fit the buffers and went through all-reduces
 
     def slots(self, rows: int):
         """(local [world, rows, 3] fp32 view, peer pointer array) for this call, or None if `rows` exceeds the buffers
@@ -46,6 +51,11 @@ class FusedStatisticsExchange:
             self._rows = rows
             self._arena = SymmetricArena(2 * self.world * rows * 12, self.group, self._device)
         if rows > self._rows or self.world > 8:
+            if not self._warned:
+                self._warned = True
+                logger.warning(f"Loss statistics of {rows} tokens exceed the peer-memory buffers sized for {self._rows} by the first call: "
+                               "this and later larger calls use all-reduces instead")
+            self.fallbacks += 1
             return None
         offset = (self._calls & 1) * self.world * self._rows * 12
         self._calls += 1
