@@ -184,6 +184,11 @@ class LayerBase:
         """Forward FLOPs for one micro-batch described by kwargs (used for throughput accounting)."""
         return sum(sub.get_compute_usage(input_meta, kwargs, config) for sub in self._sublayers.values())
 
+    def get_recompute_usage(self, kwargs: dict) -> int:
+        """FLOPs of forward work that the backward pass repeats instead of keeping its result (activation recomputation):
+        the difference between the FLOPs the hardware executes and the model's."""
+        return sum(sub.get_recompute_usage(kwargs) for sub in self._sublayers.values() if hasattr(sub, "get_recompute_usage"))
+
     def get_loss_definitions(self, count: int = 1) -> list[LossDef]:
         out = []
         for sub in self._sublayers.values():

@@ -129,6 +129,15 @@ class Stage:
         self._weights_valid = False
 
     @property
+    def weight_buffer_index(self):
+        """Identity of the weight buffer this stage computes from (shared round-robin between stages under ZeRO-3)."""
+        return self._weight_buffer_index
+
+    @property
+    def grad_buffer_index(self):
+        return self._grad_buffer_index
+
+    @property
     def is_restored(self) -> bool:
         return self._weights_valid and self._buffer_registry.get(("weight", self._weight_buffer_index), self._index) == self._index
 
@@ -153,11 +162,44 @@ class Stage:
             output = input_
             for layer in self._layers:
                 output = layer.forward(output, kwargs, losses, metrics)
+                name = getattr(layer, "module_name", type(layer).__name__)
                 if self._config.debug_layer_outputs:
                     from fast_llm_b200.utils.tensor_logs import log_tensor
 
-                    log_tensor(f"{getattr(layer, 'module_name', type(layer).__name__)} output", output, level=self._config.debug_layer_outputs)
+                    log_tensor(f"{name} output", output, level=self._config.debug_layer_outputs)
+                if self._config.debug_tensor_parallel:
+                    self._check_replicated(output, name, training)
+                if self._config.debug_activation_memory:
+                    self._log_activation_memory(name)
         return (output.detach() if torch.is_tensor(output) else output), (input_, output)
+
+    def _check_replicated(self, output, name: str, training: bool) -> None:
+        """`debug_tensor_parallel`: a layer output that every rank of the tensor group holds in full (no sequence
+        parallelism) must be bit-identical on all of them, and so must its gradient (parity:
+        `fast_llm/engine/multi_stage/stage.py:209-215,239-248`).  A mismatch is logged, training goes on."""
+        from fast_llm_b200.parallel.collectives import check_parallel_match
+
+        group = getattr(self._distributed, "tensor_group", None)
+        if group is None or self._distributed.config.sequence_tensor_parallel or not torch.is_tensor(output) or not output.is_floating_point():
+            return
+        check_parallel_match(output.detach(), group, f"layer {name} fw")
+        if training and output.requires_grad:
+            output.register_hook(lambda grad: check_parallel_match(grad, group, f"layer {name} bw") and None)
+
+    def _log_activation_memory(self, name: str) -> None:
+        """`debug_activation_memory`: allocator state after every layer of the forward pass, on the first rank of each pipeline
+        stage group (parity: `fast_llm/engine/multi_stage/stage.py:233-234`)."""
+        config = self._distributed.config
+        if config.data_rank or config.tensor_rank:
+            return
+        if torch.cuda.is_available() and self._distributed.device.type == "cuda":
+            mib = 2**20
+            logger.info(f"layer {name} fw: allocated {torch.cuda.memory_allocated() / mib:,.2f} MiB | max allocated "
+                        f"{torch.cuda.max_memory_allocated() / mib:,.2f} MiB | reserved {torch.cuda.memory_reserved() / mib:,.2f} MiB")
+        else:
+            import resource
+
+            logger.info(f"layer {name} fw: host peak resident set {resource.getrusage(resource.RUSAGE_SELF).ru_maxrss / 1024:,.2f} MiB")
 
     def backward(self, output_grad, context) -> torch.Tensor | None:
         assert self._mode.support_backward

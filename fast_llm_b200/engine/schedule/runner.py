@@ -3,7 +3,13 @@ optimizer update and loss reduction.
 
 Streams: compute runs on the current stream; ZeRO weight gathers and gradient reductions run on a `data` stream and
 pipeline transfers on a `pipeline` stream, ordered against compute with events, so they overlap with the neighbouring
-stage's math.  On CPU the same code runs with mock streams.  Parity: `fast_llm/engine/schedule/runner.py:65-556`.
+stage's math.  Asynchronous work is issued where the schedule placed it: a stage's weight gather one step before its first
+use (`Step.restore_launch`), a pipeline receive while the step runs during which the peer sends (`Step.recv_launch`), into
+buffers allocated once per plan; the compute stream waits for each only at the point of use.  Shared weight / gradient
+buffers (ZeRO-2/3) are guarded by events: a gather into a shared buffer waits for the last math that read it, a backward
+that writes a shared gradient buffer waits for the reduction that last read it.  With `profile_schedule` every activity is
+timed on its stream (`engine/schedule/profiler.py`).  On CPU the same code runs with mock streams.
+Parity: `fast_llm/engine/schedule/runner.py:65-556`.
 """
 
 import collections
@@ -16,6 +22,7 @@ import torch
 from fast_llm_b200.engine.multi_stage.config import StageMode
 from fast_llm_b200.engine.multi_stage.multi_stage import MultiStageModel
 from fast_llm_b200.engine.schedule.config import EventType, MockEvent, MockStream, ScheduleConfig, StepType
+from fast_llm_b200.engine.schedule.profiler import NO_SPAN, ScheduleProfiler
 from fast_llm_b200.engine.schedule.schedule import Schedule, Step
 from fast_llm_b200.layers.kwargs import BlockKwargs, LanguageModelKwargs
 from fast_llm_b200.parallel.collectives import all_reduce, recv, send
@@ -39,8 +46,9 @@ class BatchContext:
         self.losses: dict[str, list] = collections.defaultdict(list)
         self.metrics: dict = {}
         self.pending_sends: list = []
-        self.profile_events: list = []
         self.data_iterator = None
+        self.restore_events: dict[int, typing.Any] = {}  # local step index -> event recorded after its weight gather
+        self.received: dict[tuple, tuple] = {}  # (step type, *step key) -> (buffer, event recorded after the receive)
 
 
 class ScheduleRunner:
@@ -72,6 +80,26 @@ class ScheduleRunner:
             self._event = MockEvent
         self._loss_definitions = {d.name: d for d in self._multi_stage.base_model.get_loss_definitions()}
         self._throttle_events: collections.deque = collections.deque()
+        self._stream_names = {id(self._compute_stream): "compute"}
+        self._stream_names.setdefault(id(self._data_stream), "data")
+        self._stream_names.setdefault(id(self._pipeline_stream), "pipeline")
+        self._profiler = ScheduleProfiler(self._use_cuda, self._distributed_config.rank) if self._config.profile_schedule else None
+        self.last_profile: dict | None = None
+        # events guarding shared buffers: weight buffer index -> after the last math that read it (compute stream);
+        # gradient buffer index -> after the last reduction that read it (data stream)
+        self._weight_buffer_used: dict = {}
+        self._grad_buffer_reduced: dict = {}
+        self._recv_buffers: dict[tuple, torch.Tensor] = {}
+        self._run = None
+
+    def set_run(self, run) -> None:
+        """The run whose artifact directory receives the schedule profiles."""
+        self._run = run
+
+    def _span(self, type_: EventType, stream, step: Step | None = None):
+        if self._profiler is None:
+            return NO_SPAN
+        return self._profiler.span(type_, self._stream_names.get(id(stream), "compute"), stream if self._use_cuda else None, step)
 
     def _stream_ctx(self, stream):
         if self._use_cuda and stream is not self._compute_stream:
@@ -94,6 +122,10 @@ class ScheduleRunner:
             self._data_stream.wait_stream(self._compute_stream)
         if self._pipeline_stream is not self._compute_stream:
             self._pipeline_stream.wait_stream(self._compute_stream)
+        if self._profiler is not None:
+            self._profiler.begin(self._compute_stream if self._use_cuda else None)
+        self._weight_buffer_used.clear()
+        self._grad_buffer_reduced.clear()
         if training:
             for stage in self._stages_on_device.values():
                 stage.reset_gradients()
@@ -110,7 +142,8 @@ class ScheduleRunner:
             with self._stream_ctx(self._data_stream):
                 self._multi_stage.exchange_tied_gradients()
                 for stage, accumulate in context.deferred_reduces:
-                    stage.reduce_gradients(accumulate)
+                    with self._span(EventType.reduce, self._data_stream):
+                        stage.reduce_gradients(accumulate)
         if self._data_stream is not self._compute_stream:
             self._compute_stream.wait_stream(self._data_stream)
         if self._pipeline_stream is not self._compute_stream:
@@ -119,27 +152,38 @@ class ScheduleRunner:
 
         update_successful = True
         if training and not self._config.skip_step:
-            update_successful = self._optimizer.step(context.metrics if return_metrics else None)
+            with self._span(EventType.optimizer, self._compute_stream):
+                update_successful = self._optimizer.step(context.metrics if return_metrics else None)
             # Adam wrote the new weights into this rank's slice of the weight buffers.  With one data rank that is the
             # whole buffer; otherwise the next restore all-gathers the other slices.
             fused = getattr(self._optimizer, "pushes_weights_to_peers", False)
             if (self._distributed_config.data_parallel > 1 and not fused) or self._multi_stage._num_weight_buffers < len(self._stages_on_device):
                 self._multi_stage.invalidate_buffers()
         losses = self._reduce_losses(context, schedule)
+        if self._profiler is not None:
+            self.last_profile = self._profiler.finish(iteration, schedule.phase.value)
+            if self._run is not None and self._run.experiment_directory is not None:
+                import yaml
+
+                name = f"schedule_profile_rank_{self._distributed_config.rank}_{schedule.phase.value}_step_{iteration}.yaml"
+                with self._run.open_artifact(name, verbose=False) as f:
+                    yaml.safe_dump(self.last_profile, f, sort_keys=False)
+            logger.info(ScheduleProfiler.format_summary(self.last_profile))
         return losses, update_successful, (context.metrics if return_metrics else None)
 
     # ------------------------------------------------------------------------------------------------
     def _get_data(self, context: BatchContext, data_index: int):
         if data_index not in context.data:
             t0 = time.perf_counter()
-            batch = next(context.data_iterator)
-            t1 = time.perf_counter()
-            if context.preprocessed:
-                inputs = batch
-            else:
-                inputs = self._multi_stage.base_model.preprocess_batch(
-                    batch, phase=context.schedule.phase, iteration=context.iteration, metrics=context.metrics,
-                    device=self._distributed.device)
+            with self._span(EventType.get_batch, self._compute_stream):
+                batch = next(context.data_iterator)
+                t1 = time.perf_counter()
+                if context.preprocessed:
+                    inputs = batch
+                else:
+                    inputs = self._multi_stage.base_model.preprocess_batch(
+                        batch, phase=context.schedule.phase, iteration=context.iteration, metrics=context.metrics,
+                        device=self._distributed.device)
             Assert.eq(len(inputs), self._config.micro_batch_splits)
             # Gradients are averaged over the whole data group, but the sequence-data ranks of one sample hold
             # partial gradients that must be summed: pre-multiply by their number.
@@ -156,15 +200,37 @@ class ScheduleRunner:
         if self._config.throttle_cpu and self._use_cuda:
             self._throttle()
         stage = self._stages_on_device[step.stage]
+        # ---- asynchronous work the schedule placed at this step
+        deferred = []
+        for target in step.restore_launch:
+            # a gather into the very buffer this step's math reads can only go behind that math
+            if target is not step and self._stages_on_device[target.stage].weight_buffer_index == stage.weight_buffer_index:
+                deferred.append(target)
+            else:
+                self._launch_restore(context, target)
+        for target in step.recv_launch:
+            self._launch_recv(context, target)
+        # ---- this step
         if step.restore:
-            with self._stream_ctx(self._data_stream):
-                stage.restore_parameters()
+            event = context.restore_events.pop(step.local_index)
             if self._data_stream is not self._compute_stream:
-                self._compute_stream.wait_stream(self._data_stream)
-        if step.type_ == StepType.forward:
-            self._forward(context, step, stage)
-        else:
-            self._backward(context, step, stage)
+                with self._span(EventType.compute_wait_data, self._compute_stream, step):
+                    self._compute_stream.wait_event(event)
+        if step.type_ == StepType.backward:
+            reduced = self._grad_buffer_reduced.pop(stage.grad_buffer_index, None)
+            if reduced is not None and self._data_stream is not self._compute_stream:
+                self._compute_stream.wait_event(reduced)  # the reduction that last read this (shared) gradient buffer
+        with self._span(EventType.run, self._compute_stream, step):
+            if step.type_ == StepType.forward:
+                self._forward(context, step, stage)
+            else:
+                self._backward(context, step, stage)
+        if self._shared_weight_buffers and self._data_stream is not self._compute_stream:
+            used = self._event()
+            used.record(self._compute_stream)
+            self._weight_buffer_used[stage.weight_buffer_index] = used
+        for target in deferred:
+            self._launch_restore(context, target)
         if step.reduce:
             if self._data_stream is not self._compute_stream:
                 self._data_stream.wait_stream(self._compute_stream)
@@ -174,9 +240,31 @@ class ScheduleRunner:
                 context.deferred_reduces.append((stage, step.reduce_accumulate))
                 return
             with self._stream_ctx(self._data_stream):
-                stage.reduce_gradients(step.reduce_accumulate)
+                with self._span(EventType.reduce, self._data_stream, step):
+                    stage.reduce_gradients(step.reduce_accumulate)
                 if step.reduce_accumulate or self._multi_stage._num_grad_buffers < len(self._stages_on_device):
                     stage.reset_gradients()
+                    if self._data_stream is not self._compute_stream:
+                        reduced = self._event()
+                        reduced.record(self._data_stream)
+                        self._grad_buffer_reduced[stage.grad_buffer_index] = reduced
+
+    @property
+    def _shared_weight_buffers(self) -> bool:
+        return self._multi_stage._num_weight_buffers < len(self._stages_on_device)
+
+    def _launch_restore(self, context: BatchContext, target: Step) -> None:
+        """Issue the weight gather of `target` on the data stream and remember the event its math will wait for."""
+        stage = self._stages_on_device[target.stage]
+        with self._stream_ctx(self._data_stream):
+            used = self._weight_buffer_used.pop(stage.weight_buffer_index, None)
+            if used is not None and self._data_stream is not self._compute_stream:
+                self._data_stream.wait_event(used)  # the last math that read the buffer about to be overwritten
+            with self._span(EventType.restore, self._data_stream, target):
+                stage.restore_parameters()
+            event = self._event()
+            event.record(self._data_stream if self._use_cuda else None)
+        context.restore_events[target.local_index] = event
 
     def _throttle(self) -> None:
         event = torch.cuda.Event()
@@ -192,7 +280,7 @@ class ScheduleRunner:
         if step.stage == 0:
             input_ = tokens
         elif step.recv_from is not None:
-            input_ = self._recv(step, kwargs, forward=True)
+            input_ = self._received(context, step)
         else:
             input_ = context.outputs.pop((step.stage - 1, step.data_index, step.micro_sequence))
         splits = self._config.micro_batch_splits
@@ -220,8 +308,7 @@ class ScheduleRunner:
         if step.stage == self._num_stages - 1:
             output_grad = None
         elif step.recv_from is not None:
-            _, kwargs = context.data[step.data_index][step.micro_sequence]
-            output_grad = self._recv(step, kwargs, forward=False)
+            output_grad = self._received(context, step)
         else:
             output_grad = context.grads.pop((step.stage + 1, step.data_index, step.micro_sequence))
         ctx, presents = context.contexts.pop(step.key)
@@ -258,24 +345,40 @@ class ScheduleRunner:
             tokens //= dc.tensor_parallel
         return (tokens, self._multi_stage.base_model._hidden_dim.size)
 
-    def _recv(self, step: Step, kwargs, forward: bool) -> torch.Tensor:
+    def _launch_recv(self, context: BatchContext, target: Step) -> None:
+        """Post the receive of `target`'s input (forward) or output gradient (backward) on the pipeline stream, into a buffer
+        that belongs to this step of the plan and is reused by every later optimizer step."""
+        kwargs = self._get_data(context, target.data_index)[target.micro_sequence][1]
         shape = self._hidden_shape(kwargs)
         dtype = self._distributed_config.compute_dtype.torch
+        key = (id(context.schedule), target.type_, *target.key)
+        buffer = self._recv_buffers.get(key)
+        if buffer is None or tuple(buffer.shape) != tuple(shape) or buffer.dtype != dtype:
+            buffer = self._recv_buffers[key] = torch.empty(shape, dtype=dtype, device=self._distributed.device)
         with self._stream_ctx(self._pipeline_stream):
-            buffer = torch.empty(shape, dtype=dtype, device=self._distributed.device)
-            if self._config.debug_send_recv:
-                header = torch.empty(2, dtype=torch.int64, device=self._distributed.device)
-                recv(header, step.recv_from, self._distributed.pipeline_group)
-                Assert.eq(header.tolist(), [step.data_index * 1000 + step.micro_sequence, buffer.numel()])
-            recv(buffer, step.recv_from, self._distributed.pipeline_group)
+            with self._span(EventType.recv, self._pipeline_stream, target):
+                if self._config.debug_send_recv:
+                    header = torch.empty(2, dtype=torch.int64, device=self._distributed.device)
+                    recv(header, target.recv_from, self._distributed.pipeline_group)
+                    Assert.eq(header.tolist(), [target.data_index * 1000 + target.micro_sequence, buffer.numel()])
+                recv(buffer, target.recv_from, self._distributed.pipeline_group)
+            event = self._event()
+            event.record(self._pipeline_stream if self._use_cuda else None)
+        context.received[(target.type_, *target.key)] = (buffer, event)
+
+    def _received(self, context: BatchContext, step: Step) -> torch.Tensor:
+        buffer, event = context.received.pop((step.type_, *step.key))
         if self._pipeline_stream is not self._compute_stream:
-            self._compute_stream.wait_stream(self._pipeline_stream)
+            with self._span(EventType.compute_wait_pipe, self._compute_stream, step):
+                self._compute_stream.wait_event(event)
+        # the buffer is reused by the same step of the next optimizer step: hand out a tensor of its own when autograd may
+        # keep it (a stage's input is saved for its backward) and the next step could overwrite it first
         return buffer
 
     def _send(self, context: BatchContext, step: Step, tensor: torch.Tensor) -> None:
         if self._pipeline_stream is not self._compute_stream:
             self._pipeline_stream.wait_stream(self._compute_stream)
-        with self._stream_ctx(self._pipeline_stream):
+        with self._stream_ctx(self._pipeline_stream), self._span(EventType.send, self._pipeline_stream, step):
             tensor = tensor.contiguous()
             if self._config.debug_send_recv:
                 header = torch.tensor([step.data_index * 1000 + step.micro_sequence, tensor.numel()], dtype=torch.int64, device=tensor.device)

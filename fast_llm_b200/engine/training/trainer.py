@@ -82,6 +82,7 @@ class Trainer:
                                     distributed, compute_dtype=config.model.distributed.compute_dtype.torch,
                                     weight_arena=self._multi_stage.weight_arena)
         self._runner.setup(distributed, self._optimizer)
+        self._runner.set_run(run)
         cache_dir = None if run.experiment_directory is None else run.experiment_directory / "dataset_cache"
         self._data.setup(cache_dir)
         self._schedules = {PhaseType.training: Schedule(self._multi_stage, config.schedule, config.model.distributed, PhaseType.training)}

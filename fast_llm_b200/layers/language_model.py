@@ -29,9 +29,12 @@ from fast_llm_b200.utils import Assert, div
 
 
 class LossImplementation(str, enum.Enum):
+    """`per_loss` runs every loss on its own; the other values group the losses that share the softmax (the reference's
+    `compiled` / `triton` choose between its two fused implementations, here both mean the CUDA kernels)."""
+
     auto = "auto"
-    torch = "torch"
-    fused = "fused"
+    per_loss = "per_loss"
+    compiled = "compiled"
     triton = "triton"
 
 
@@ -56,7 +59,7 @@ class LanguageModelHeadConfig(BlockConfig):
     _abstract = False
     normalization: NormalizationConfig = Field(desc="Final normalization.", hint=FieldHint.architecture)
     losses: dict[str, LanguageModelLossConfig] = Field(default_factory=dict, desc="Named losses (default: cross-entropy from labels).", hint=FieldHint.core)
-    loss_implementation: LossImplementation = Field(default=LossImplementation.auto, desc="Kept for schema compatibility.", hint=FieldHint.expert)
+    loss_implementation: LossImplementation = Field(default=LossImplementation.auto, desc="`per_loss`: one pass pair per loss; otherwise losses sharing the softmax are fused into one pass pair.", hint=FieldHint.expert)
     output_weight: ParameterConfig = Field(desc="Output projection (unless tied to the embeddings).", hint=FieldHint.architecture)
     cross_entropy_splits: int = Field(default=1, desc="Process the logits in this many token chunks to bound memory.", hint=FieldHint.feature, valid=skip_valid_if_none(check_field(Assert.gt, 0)))
     logits_scale_factor: float = Field(default=1.0, desc="Multiplier of the logits.", hint=FieldHint.feature, valid=check_field(Assert.geq, 0))
@@ -234,7 +237,7 @@ class LanguageModelHead(Layer):
         self.final_norm = config.normalization.get_layer(hidden_dim, lr_scale=self._lr_scale, peft=peft, distributed_config=distributed_config)
         self.output_weights = config.output_weight.get_parameter(
             (vocab_dim, hidden_dim), default_initialization=init_normal_(0.0, hidden_dim.global_size**-0.5), lr_scale=self._lr_scale, peft=peft)
-        loss_configs = config.losses or {"lm_loss": LanguageModelLabelEntropyLossConfig()}
+        loss_configs = self._effective_losses(config)
         suffix = "" if prediction_distance == 1 else f"_{prediction_distance}"
         self._losses = [
             lc.get_layer(distributed_config, name=name + suffix, prediction_distance=prediction_distance, vocab_parallel=self._vocab_parallel,
@@ -242,6 +245,44 @@ class LanguageModelHead(Layer):
             for name, lc in loss_configs.items()
         ]
         self._logits_group = None
+
+    @staticmethod
+    def _effective_losses(config) -> dict:
+        """The losses the head runs.  Losses that share the softmax over the vocabulary are grouped, by logits scale, into
+        one `MonolithicLoss` each, so that a group costs one statistics pass and one gradient pass over the logits however
+        many members it has (`loss_implementation: per_loss` keeps them apart).  Grouping rule and the reserved names
+        `monolithic` / `monolithic_<i>`: `fast_llm/layers/language_model/config.py:203-237`."""
+        from fast_llm_b200.layers.losses import CombinableLossConfig, MonolithicLossConfig
+
+        losses = dict(config.losses) or {"lm_loss": LanguageModelLabelEntropyLossConfig()}
+        for name in losses:
+            assert not (name == "monolithic" or (name.startswith("monolithic_") and name.removeprefix("monolithic_").isdigit())), \
+                f"loss name {name!r} is reserved"
+        combinable = {n: c for n, c in losses.items() if isinstance(c, CombinableLossConfig)}
+        if config.loss_implementation == LossImplementation.per_loss or len(combinable) < 2:
+            return losses
+        groups: dict[float, dict] = {}
+        slots = []
+        for name, loss in losses.items():
+            if name in combinable:
+                if loss.logits_scale_factor not in groups:
+                    groups[loss.logits_scale_factor] = {}
+                    slots.append(loss.logits_scale_factor)
+                groups[loss.logits_scale_factor][name] = loss
+            else:
+                slots.append((name, loss))
+        effective, index = {}, 0
+        for slot in slots:
+            if isinstance(slot, tuple):
+                effective[slot[0]] = slot[1]
+            elif len(groups[slot]) == 1:
+                effective.update(groups[slot])
+            else:
+                group = MonolithicLossConfig(losses=groups[slot])
+                group.validate()
+                effective[f"monolithic_{index}" if len(groups) > 1 else "monolithic"] = group
+                index += 1
+        return effective
 
     def setup(self, distributed):
         super().setup(distributed)
@@ -298,11 +339,16 @@ class LanguageModelHead(Layer):
         total, grad = None, None
         kwargs["_single_loss"] = len(self._losses) == 1
         for loss in self._losses:
+            members = kwargs["_member_losses"] = {}
             value, g = loss.forward_backward(logits, kwargs, grad_output, split_index, num_splits, logits_scale,
                                              accumulate_into=grad)
+            kwargs.pop("_member_losses", None)
             if g is not None:
                 grad = g
-            losses_out.setdefault(loss.name, []).append(value.detach()) if num_splits == 1 else _accumulate_split(losses_out, loss.name, value.detach(), split_index)
+            # a group reports its members under their own names, a plain loss reports itself
+            for name, entries in (members.items() if members else [(loss.name, [value.detach()])]):
+                for entry in entries:
+                    losses_out.setdefault(name, []).append(entry) if num_splits == 1 else _accumulate_split(losses_out, name, entry, split_index)
             weighted = value * loss.weight
             total = weighted if total is None else total + weighted
         if len(self._losses) > 1:

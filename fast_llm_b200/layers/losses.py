@@ -442,7 +442,7 @@ class MonolithicLoss(LanguageModelLoss):
             m.setup(distributed, logits_group, vocab_begin)
 
     def get_loss_definitions(self, count=1):
-        return [LossDef(self.name, self.name.replace("_", " "), count)] + [d for m in self._members for d in m.get_loss_definitions(count)]
+        return [d for m in self._members for d in m.get_loss_definitions(count)]
 
     def get_preprocessing_config(self, phase):
         out = {}

@@ -93,3 +93,9 @@ class MLP(LayerBase):
         c = self._config
         tokens = kwargs[BlockKwargs.num_tokens]
         return 2 * tokens * self._hidden_dim.global_size * c.intermediate_size * (3 if c.gated else 2)
+
+    def get_recompute_usage(self, kwargs) -> int:
+        c = self._config
+        if not c.recompute_level.recompute_layer_1:
+            return 0
+        return 2 * kwargs[BlockKwargs.num_tokens] * self._hidden_dim.global_size * c.intermediate_size * (2 if c.gated else 1)

@@ -58,6 +58,7 @@ _SIGNATURES = {
     "flb_abi_version": [],
     "flb_attention_fwd": [_p, _ll, _i, _p, _ll, _i, _i, _p, _p, _i, _i, _ll, _ll, _i, _i, _i, _p, _p, _i, _i, _f, _p],
     "flb_attention_error_word": [],
+    "flb_attention_set_forward_variant": [_i],
     "flb_attention_bwd": [_p, _ll, _i, _p, _ll, _i, _i, _p, _p, _p, _p, _p, _i, _i, _ll, _ll, _i, _i, _i, _p, _ll, _p, _ll, _p, _p,
                           _i, _i, _f, _p],
     "flb_attention_bwd_error_word": [],

@@ -169,9 +169,10 @@ def check_parallel_match(tensor: torch.Tensor, group: ProcessGroup | None, name:
     """Debug helper: log when a tensor that should be replicated over `group` differs between its ranks."""
     if group is None:
         return True
-    gathered = tensor.new_empty([group.size(), *tensor.shape])
-    dist.all_gather_into_tensor(gathered, tensor.contiguous(), group=group)
-    mismatches = (gathered != tensor[None]).any(dim=0).sum().item()
+    flat = tensor.contiguous().view(-1)
+    gathered = flat.new_empty(group.size() * flat.numel())
+    dist.all_gather_into_tensor(gathered, flat, group=group)
+    mismatches = (gathered.view(group.size(), -1) != flat[None]).any(dim=0).sum().item()
     if mismatches:
         logger.error(f"MISMATCH {name}: {mismatches} of {tensor.numel()} entries differ between ranks")
     return mismatches == 0

@@ -124,10 +124,9 @@ def bench_gemm_tiles(results):
 
 
 def bench_attention(results):
-    """Forward attention at the Mistral-7B shape (8192 tokens, 32/8 heads, window 4096): tcgen05 kernel vs the library."""
-    from flash_attn.flash_attn_interface import _flash_attn_varlen_forward
-
-    from fast_llm_b200.ops.attention import attention_forward_native
+    """Attention at the Mistral-7B shape (8192 tokens, 32/8 heads, window 4096): both forward kernels and the backward."""
+    from fast_llm_b200.ops import _lib
+    from fast_llm_b200.ops.attention import attention_backward_native, attention_forward_native
 
     _, tflops_peak, kind = _peaks()
     t, heads, kv, d, window = 8192, 32, 8, 128, 4096
@@ -136,29 +135,24 @@ def bench_attention(results):
     nq, nkv = heads * d, kv * d
     keys = (window * (window + 1) / 2 + (t - window) * window) / t  # average keys per query
     flops = 4.0 * t * keys * heads * d
-    q, k, v = qkv[:, :nq].view(t, heads, d), qkv[:, nq:nq + nkv].view(t, kv, d), qkv[:, nq + nkv:].view(t, kv, d)
     ours = lambda: attention_forward_native(qkv, 0, qkv, nq, nq + nkv, cu, cu, t, heads, kv, d, True, window, d**-0.5)
-    lib = lambda: _flash_attn_varlen_forward(q, k, v, cu, cu, t, t, 0.0, d**-0.5, True, window_size_left=window - 1, window_size_right=0)
-    ms, ms_lib = time_op(ours), time_op(lib)
-    r = {"op": "attention_fwd_mistral", "ms": ms, "tflops": flops / ms / 1e9, "frac_of_peak": flops / ms / 1e9 / tflops_peak,
-         "peak_kind": kind, "cublas_ms": ms_lib, "cublas_tflops": flops / ms_lib / 1e9, "note": "second pair = flash_attn 2 library"}
-    results.append(r)
-    print(json.dumps(r), flush=True)
+    lib = _lib.get_lib()
+    for variant, name in ((0, "p_in_tmem"), (1, "p_in_smem")):
+        old = lib.flb_attention_set_forward_variant(variant)
+        ms = time_op(ours)
+        lib.flb_attention_set_forward_variant(old)
+        r = {"op": f"attention_fwd_mistral_{name}", "ms": ms, "tflops": flops / ms / 1e9, "frac_of_peak": flops / ms / 1e9 / tflops_peak,
+             "peak_kind": kind, "cublas_ms": float("nan"), "cublas_tflops": float("nan")}
+        results.append(r)
+        print(json.dumps(r), flush=True)
     # backward: 2.5x the forward FLOPs (five tile products against two)
-    from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
-
-    from fast_llm_b200.ops.attention import attention_backward_native
-
     out, lse = ours()
     dout = torch.randn(t, nq, device="cuda", dtype=torch.bfloat16)
     dqkv = torch.empty_like(qkv)
-    dq, dk, dv = dqkv[:, :nq].view(t, heads, d), dqkv[:, nq:nq + nkv].view(t, kv, d), dqkv[:, nq + nkv:].view(t, kv, d)
     ours_b = lambda: attention_backward_native(qkv, 0, qkv, nq, nq + nkv, out, dout, lse, cu, cu, t, heads, kv, d, dqkv, dqkv, True, window, d**-0.5)
-    lib_b = lambda: _flash_attn_varlen_backward(dout.view(t, heads, d), q, k, v, out, lse, dq, dk, dv, cu, cu, t, t, 0.0, d**-0.5, True,
-                                                window - 1, 0, 0.0, None, False, None)
-    ms, ms_lib = time_op(ours_b), time_op(lib_b)
+    ms = time_op(ours_b)
     r = {"op": "attention_bwd_mistral", "ms": ms, "tflops": 2.5 * flops / ms / 1e9, "frac_of_peak": 2.5 * flops / ms / 1e9 / tflops_peak,
-         "peak_kind": kind, "cublas_ms": ms_lib, "cublas_tflops": 2.5 * flops / ms_lib / 1e9, "note": "second pair = flash_attn 2 library"}
+         "peak_kind": kind, "cublas_ms": float("nan"), "cublas_tflops": float("nan")}
     results.append(r)
     print(json.dumps(r), flush=True)
 

@@ -60,3 +60,37 @@ def test_layout_matches_single_process(name):
             # a copy of a tied weight on another pipeline rank is exported under its own name: compare with the owner
             reference = ref_weights[key if key in ref_weights else {"head.output_weights": "embeddings.word_embeddings_weight"}[key]]
             torch.testing.assert_close(torch.from_numpy(value), reference, rtol=2e-3, atol=2e-5, msg=lambda m: f"{name} {key}: {m}")
+
+
+def _debug_rank(rank, world_size):
+    import logging
+
+    records = []
+
+    class _Collect(logging.Handler):
+        def emit(self, record):
+            records.append(record.getMessage())
+
+    logging.getLogger("fast_llm_b200").addHandler(_Collect())
+    updates = {("model", "distributed", "world_size"): world_size, ("model", "distributed", "rank"): rank,
+               ("model", "distributed", "local_world_size"): world_size, ("model", "distributed", "backend"): "gloo",
+               ("model", "distributed", "tensor_parallel"): 2, ("model", "multi_stage", "debug_tensor_parallel"): True,
+               ("model", "multi_stage", "debug_activation_memory"): True}
+    trainer, distributed = build_trainer(tiny_trainer_config(updates))
+    train_steps(trainer, 1)
+    # make the ranks disagree on a replicated tensor: the check must notice
+    from fast_llm_b200.parallel.collectives import check_parallel_match
+
+    matched = check_parallel_match(torch.full((4,), float(rank)), distributed.tensor_group, "planted")
+    distributed.shutdown()
+    return [m for m in records if "MISMATCH" in m], any("fw: " in m for m in records), matched
+
+
+def test_debug_hooks_check_replicated_tensors_and_log_memory():
+    """`debug_tensor_parallel` compares every replicated layer output and gradient across the tensor group (silent when they
+    agree, loud when they do not); `debug_activation_memory` logs the allocator after every layer."""
+    results = run_distributed(_debug_rank, 2)
+    for mismatches, logged_memory, planted_matched in results:
+        assert mismatches == ["MISMATCH planted: 4 of 4 entries differ between ranks"]
+        assert not planted_matched
+    assert results[0][1], "rank 0 logs memory after every layer"

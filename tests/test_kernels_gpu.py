@@ -11,6 +11,66 @@ def _rel_err(a, b):
     return ((a - b).norm() / (b.norm() + 1e-12)).item()
 
 
+def _max_err(a, b):
+    return (a.float() - b.float()).abs().max().item()
+
+
+def _tile_errors(out, ref, tile=32):
+    """Largest relative error of any `tile` x `tile` block: a missing or misplaced store box shows up here even when it
+    vanishes in the norm of the whole matrix."""
+    diff = (out.float() - ref.float())
+    rows, cols = diff.shape
+    pr, pc = (-rows) % tile, (-cols) % tile
+    pad = lambda t: torch.nn.functional.pad(t, (0, pc, 0, pr))  # noqa: E731
+    d = pad(diff).reshape((rows + pr) // tile, tile, (cols + pc) // tile, tile).pow(2).sum((1, 3)).sqrt()
+    r = pad(ref.float()).reshape((rows + pr) // tile, tile, (cols + pc) // tile, tile).pow(2).sum((1, 3)).sqrt()
+    return (d / (r + 1e-3 * r.max() + 1e-12)).max().item()
+
+
+class _Guarded:
+    """An output matrix inside a larger buffer whose surrounding rows and columns hold a sentinel: any store outside the
+    matrix (a TMA box that is not clipped, a wrong leading dimension) changes a sentinel.  Stands in for a memory checker."""
+
+    def __init__(self, rows, cols, dtype, margin=8, fill=None, sentinel=-7777.0):
+        self.margin, self.sentinel = margin, sentinel
+        align = 8 if dtype == torch.bfloat16 else 4
+        ld = (cols + 2 * margin + align - 1) // align * align
+        self.buffer = torch.full((rows + 2 * margin, ld), sentinel, device="cuda", dtype=dtype)
+        self.view = self.buffer[margin : margin + rows, margin : margin + cols]
+        if fill is not None:
+            self.view.copy_(fill)
+        self._inside = torch.zeros_like(self.buffer, dtype=torch.bool)
+        self._inside[margin : margin + rows, margin : margin + cols] = True
+
+    def check(self):
+        outside = self.buffer[~self._inside]
+        assert torch.all(outside == self.sentinel), f"{int((outside != self.sentinel).sum())} elements outside the output were overwritten"
+
+
+@pytest.mark.parametrize("m,n,k", [(512, 768, 256), (1000, 520, 200), (130, 4104, 72), (384, 768, 320), (256, 264, 128)])
+@pytest.mark.parametrize("block_n", [0, 128, 256, 512])
+@pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
+def test_gemm_stays_inside_its_output_and_every_tile_is_right(m, n, k, block_n, epilogue):
+    """All four epilogues (store / accumulate, bf16 / fp32) of every kernel, written into a guarded sub-matrix whose margin
+    makes the TMA store boxes of edge tiles reach past the matrix: nothing outside may change, and every 32 x 32 block of
+    the result must be right on its own (not only the matrix norm)."""
+    from fast_llm_b200.ops.gemm import gemm_raw
+
+    torch.manual_seed(m + n + k + epilogue)
+    x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+    dtype = torch.float32 if epilogue in (1, 2) else torch.bfloat16
+    base = torch.randn(m, n, device="cuda", dtype=dtype) if epilogue >= 2 else None
+    guarded = _Guarded(m, n, dtype, fill=base)
+    gemm_raw(x, w, guarded.view, m, n, k, False, False, epilogue, block_n=block_n)
+    torch.cuda.synchronize()
+    guarded.check()
+    ref = x.float() @ w.float().t() + (base.float() if base is not None else 0)
+    assert _rel_err(guarded.view, ref) < 1e-2
+    assert _tile_errors(guarded.view, ref) < (4e-2 if dtype == torch.bfloat16 else 1e-2)
+    assert _max_err(guarded.view, ref) < 0.02 * ref.abs().max().item() + 0.25
+
+
 @pytest.fixture(scope="module", autouse=True)
 def _lib_loaded():
     from fast_llm_b200.ops import _lib
@@ -261,7 +321,8 @@ def test_embedding_and_pointwise():
     assert _rel_err(r, (x.float() + bias.float()) * 0.5 + x.float()) < 1e-2
 
 
-def _attention_case(doc_lengths, heads, kv_heads, causal, window, seed=0):
+def _attention_case(doc_lengths, heads, kv_heads, causal, window, seed=0, variant=0):
+    from fast_llm_b200.ops import _lib
     from fast_llm_b200.ops.attention import attention_forward_native, attention_reference
 
     torch.manual_seed(seed)
@@ -270,7 +331,11 @@ def _attention_case(doc_lengths, heads, kv_heads, causal, window, seed=0):
     qkv = torch.randn(total, (heads + 2 * kv_heads) * d, device="cuda", dtype=torch.bfloat16)
     cu = torch.tensor([0] + list(torch.tensor(doc_lengths).cumsum(0)), device="cuda", dtype=torch.int32)
     nq, nkv = heads * d, kv_heads * d
-    out, lse = attention_forward_native(qkv, 0, qkv, nq, nq + nkv, cu, cu, max(doc_lengths), heads, kv_heads, d, causal, window, d**-0.5)
+    old = _lib.get_lib().flb_attention_set_forward_variant(variant)
+    try:
+        out, lse = attention_forward_native(qkv, 0, qkv, nq, nq + nkv, cu, cu, max(doc_lengths), heads, kv_heads, d, causal, window, d**-0.5)
+    finally:
+        _lib.get_lib().flb_attention_set_forward_variant(old)
     q = qkv[:, :nq].reshape(total, heads, d)
     k = qkv[:, nq : nq + nkv].reshape(total, kv_heads, d)
     v = qkv[:, nq + nkv :].reshape(total, kv_heads, d)
@@ -288,13 +353,15 @@ def _attention_case(doc_lengths, heads, kv_heads, causal, window, seed=0):
     ([640], 2, 2, False, None),
     ([2048], 8, 2, True, 1024),
 ])
-def test_attention_forward_tcgen05(doc_lengths, heads, kv_heads, causal, window):
+@pytest.mark.parametrize("variant", [0, 1], ids=["p_in_tmem", "p_in_smem"])
+def test_attention_forward_tcgen05(doc_lengths, heads, kv_heads, causal, window, variant):
     from fast_llm_b200.ops import _lib
 
-    out, lse, ref, (q, k, v, cu) = _attention_case(doc_lengths, heads, kv_heads, causal, window)
+    out, lse, ref, (q, k, v, cu) = _attention_case(doc_lengths, heads, kv_heads, causal, window, variant=variant)
     assert _lib.get_lib().flb_attention_error_word() == 0
     assert torch.isfinite(out).all()
     assert _rel_err(out, ref) < 1.5e-2
+    assert _tile_errors(out.reshape(out.shape[0], -1), ref.reshape(ref.shape[0], -1)) < 6e-2
     # log-sum-exp against a direct computation for one head of the first document
     n = doc_lengths[0]
     s = (q[:n, 0].float() @ k[:n, 0].float().t()) * 128**-0.5
@@ -342,27 +409,81 @@ def test_attention_backward_tcgen05(doc_lengths, heads, kv_heads, causal, window
         assert _rel_err(qkv.grad[:, lo:hi], ref_in.grad[:, lo:hi]) < 3e-2, name
 
 
-def test_packed_attention_native_forward_library_backward(monkeypatch):
-    """The autograd path: tcgen05 forward, library backward fed with our log-sum-exp."""
-    from fast_llm_b200.ops.attention import attention_reference, packed_attention
+def _prefix_case(q_lengths, k_lengths, heads, kv_heads, d, window, seed=5):
+    torch.manual_seed(seed)
+    tq, tk = sum(q_lengths), sum(k_lengths)
+    q = torch.randn(tq, heads, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    kv = torch.randn(tk, 2 * kv_heads * d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    cu_q = torch.tensor([0] + list(torch.tensor(q_lengths).cumsum(0)), device="cuda", dtype=torch.int32)
+    cu_k = torch.tensor([0] + list(torch.tensor(k_lengths).cumsum(0)), device="cuda", dtype=torch.int32)
+    return q, kv, cu_q, cu_k
 
-    monkeypatch.setenv("FLB_ATTENTION_BWD", "library")
-    torch.manual_seed(1)
-    heads, kv_heads, d = 4, 2, 128
-    lengths = [384, 200]
-    total = sum(lengths)
-    qkv = torch.randn(total, (heads + 2 * kv_heads) * d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
-    cu = torch.tensor([0, 384, 584], device="cuda", dtype=torch.int32)
-    out = packed_attention(qkv, cu, max(lengths), heads, kv_heads, d, causal=True, window_size=128)
+
+@pytest.mark.parametrize("q_lengths,k_lengths,heads,kv_heads,d,window", [
+    ([128], [384], 2, 1, 128, None),          # a prefix of two key tiles
+    ([200, 60], [456, 60], 4, 2, 128, None),  # one document with a prefix, one without
+    ([300], [1000], 4, 2, 128, 256),          # prefix + sliding window
+    ([257, 100], [300, 612], 2, 2, 128, None),
+    ([384], [384], 4, 2, 64, None),           # head sizes below 128 are zero-padded
+    ([300, 100], [500, 100], 4, 1, 96, 128),
+])
+def test_attention_with_key_prefix_and_padded_heads(q_lengths, k_lengths, heads, kv_heads, d, window):
+    """General form: key segments longer than the query segments (bottom-right aligned causal mask), other head sizes;
+    forward and all three gradients against the fp32 restatement."""
+    from fast_llm_b200.ops import _lib
+    from fast_llm_b200.ops.attention import attention, attention_reference
+
+    q, kv, cu_q, cu_k = _prefix_case(q_lengths, k_lengths, heads, kv_heads, d, window)
+    tk = kv.shape[0]
+    k = kv[:, : kv_heads * d].reshape(tk, kv_heads, d)
+    v = kv[:, kv_heads * d :].reshape(tk, kv_heads, d)
+    before = _lib.launch_count
+    out = attention(q, k, v, cu_q, cu_k, max(q_lengths), max(k_lengths), causal=True, window_size=window)
     g = torch.randn_like(out)
     out.backward(g)
-    ref_in = qkv.detach().float().requires_grad_()
-    nq, nkv = heads * d, kv_heads * d
-    ref = attention_reference(ref_in[:, :nq].reshape(total, heads, d), ref_in[:, nq : nq + nkv].reshape(total, kv_heads, d),
-                              ref_in[:, nq + nkv :].reshape(total, kv_heads, d), cu, cu, True, 128, d**-0.5).reshape(total, nq)
+    assert _lib.launch_count - before == 4, "forward + delta / backward / dq-convert kernels of this library"
+    assert _lib.get_lib().flb_attention_error_word() == 0 and _lib.get_lib().flb_attention_bwd_error_word() == 0
+    q32, kv32 = q.detach().float().requires_grad_(), kv.detach().float().requires_grad_()
+    ref = attention_reference(q32, kv32[:, : kv_heads * d].reshape(tk, kv_heads, d), kv32[:, kv_heads * d :].reshape(tk, kv_heads, d), cu_q, cu_k,
+                              True, window, d**-0.5)
     ref.backward(g.float())
     assert _rel_err(out, ref) < 1.5e-2
-    assert _rel_err(qkv.grad, ref_in.grad) < 3e-2
+    assert _max_err(out, ref) < 0.05 * ref.abs().max().item()
+    assert _rel_err(q.grad, q32.grad) < 3e-2
+    assert _rel_err(kv.grad, kv32.grad) < 3e-2
+
+
+def test_attention_key_rows_outside_every_document_get_zero_gradient():
+    """Sequence-data parallelism hands every rank the whole key / value tensor; rows past the last `cu_k` belong to later
+    tokens of other ranks and must come back with an exactly zero gradient."""
+    from fast_llm_b200.ops.attention import attention
+
+    heads, kv_heads, d = 2, 1, 128
+    q, kv, cu_q, cu_k = _prefix_case([256], [512], heads, kv_heads, d, None)
+    kv_long = torch.cat([kv.detach(), torch.randn(300, 2 * kv_heads * d, device="cuda", dtype=torch.bfloat16)]).requires_grad_()
+    tk = kv_long.shape[0]
+    out = attention(q, kv_long[:, : kv_heads * d].reshape(tk, kv_heads, d), kv_long[:, kv_heads * d :].reshape(tk, kv_heads, d), cu_q, cu_k, 256, 512)
+    out.sum().backward()
+    assert torch.all(kv_long.grad[512:] == 0)
+    assert kv_long.grad[:512].abs().sum() > 0
+
+
+def test_attention_dropout_fallback_keeps_the_expectation():
+    """Dropout goes through the per-document PyTorch path: with p = 0 it equals the kernels, with p > 0 the mean over many
+    masks approaches the undropped output."""
+    from fast_llm_b200.ops.attention import attention
+
+    heads, kv_heads, d = 2, 1, 128
+    q, kv, cu_q, cu_k = _prefix_case([128], [128], heads, kv_heads, d, None)
+    k = kv[:, : kv_heads * d].reshape(128, kv_heads, d)
+    v = kv[:, kv_heads * d :].reshape(128, kv_heads, d)
+    with torch.no_grad():
+        exact = attention(q, k, v, cu_q, cu_k, 128, 128).float()
+        mean = torch.zeros_like(exact)
+        runs = 200
+        for _ in range(runs):
+            mean += attention(q, k, v, cu_q, cu_k, 128, 128, dropout_p=0.2).float() / runs
+    assert _rel_err(mean, exact) < 0.15
 
 
 def _expert_layout_case(tokens, k, experts, seed=0):

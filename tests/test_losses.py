@@ -281,3 +281,32 @@ def test_monolithic_loss_gpu_writes_one_gradient_in_place():
         expected_value, expected_grad = expected_value + w * v, expected_grad + w * g
     torch.testing.assert_close(value.cpu(), expected_value, rtol=1e-4, atol=1e-5)
     torch.testing.assert_close(grad.cpu(), expected_grad, rtol=1e-4, atol=1e-7)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# through the head: grouped (one softmax) and per-loss execution train identically
+def test_head_groups_losses_sharing_the_softmax():
+    from tests.common import build_trainer, tiny_trainer_config
+    from fast_llm_b200.layers.losses import MonolithicLoss
+    from fast_llm_b200.parallel.topology import PhaseType
+
+    losses = {"lm_loss": {"type": "label"}, "z_loss": {"type": "z_loss", "weight": 1e-2}}
+    results = {}
+    for implementation in ("auto", "per_loss"):
+        updates = {("model", "base_model", "head", "losses"): losses, ("model", "base_model", "head", "loss_implementation"): implementation,
+                   ("model", "distributed", "reproducible_init"): True}
+        trainer, _ = build_trainer(tiny_trainer_config(updates))
+        head = trainer.multi_stage.base_model.head
+        grouped = [type(l) for l in head._losses] == [MonolithicLoss]
+        assert grouped == (implementation == "auto")
+        schedule = trainer._schedules[PhaseType.training]
+        iterator = trainer._data.get_iterator("training", consumed_samples=0, num_workers=0)
+        out, ok, _ = trainer.runner.run_step(iterator, schedule, iteration=1)
+        weights = {n: t.clone() for n, _, t in trainer.multi_stage.get_state_tensor_iterator(("weights",))}
+        results[implementation] = (out, weights)
+    auto, per_loss = results["auto"], results["per_loss"]
+    assert set(auto[0]) >= {"lm_loss", "z_loss"}
+    for name in ("lm_loss", "z_loss"):
+        assert auto[0][name] == pytest.approx(per_loss[0][name], rel=1e-5)
+    for name, value in auto[1].items():
+        torch.testing.assert_close(value, per_loss[1][name], rtol=1e-3, atol=1e-4)  # Adam turns rounding differences of tiny gradients into steps of the order of the learning rate
