@@ -340,6 +340,19 @@ constexpr int SMEM2_Q = 0, SMEM2_K = 2 * TILE_BYTES_ATTN, SMEM2_V = 4 * TILE_BYT
 constexpr int SMEM2_BARS = 6 * TILE_BYTES_ATTN;
 constexpr int SMEM2_TOTAL = SMEM2_BARS + 256 + 1024;
 
+// 2^x for x <= 8 on the FMA pipe: x = n + f with n = round(x) taken from the mantissa of x + 1.5 * 2^23, 2^f by a cubic
+// (relative error below 1e-4, well under the bf16 rounding of the probabilities it feeds), 2^n by adding n to the exponent field.
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -125.f);
+  const float shifted = x + 12582912.f;                 // 1.5 * 2^23: the low mantissa bits now hold round(x)
+  const float f = x - (shifted - 12582912.f);           // in [-0.5, 0.5]
+  float pf = 0.05517167f;  // minimax cubic for 2^f on [-0.5, 0.5]: largest relative error 7.5e-5
+  pf = pf * f + 0.24261112f;
+  pf = pf * f + 0.69326099f;
+  pf = pf * f + 0.99992807f;
+  return __int_as_float(__float_as_int(pf) + (__float_as_int(shifted) << 23));
+}
+
 // D[tmem] (+)= A[tmem] * B[smem]: A is a 128-lane tile in tensor memory, two bf16 per 32-bit column.
 __device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -487,15 +500,19 @@ attn_fwd_kernel_v2(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(tmem_s + c * 32, v + c * 32);
       tmem_wait_ld();
-      float tile_max = -INFINITY;
+      // eight independent running maxima: one chain of 128 dependent comparisons would cost their latency 128 times
+      float mx[8];
+#pragma unroll
+      for (int a = 0; a < 8; ++a) mx[a] = -INFINITY;
       if (full_tile) {
 #pragma unroll
-        for (int i = 0; i < 128; ++i) tile_max = fmaxf(tile_max, __uint_as_float(v[i]));
+        for (int i = 0; i < 128; ++i) mx[i & 7] = fmaxf(mx[i & 7], __uint_as_float(v[i]));
       } else {
 #pragma unroll
         for (int i = 0; i < 128; ++i)
-          if (i >= col_lo && i < col_hi) tile_max = fmaxf(tile_max, __uint_as_float(v[i]));
+          if (i >= col_lo && i < col_hi) mx[i & 7] = fmaxf(mx[i & 7], __uint_as_float(v[i]));
       }
+      float tile_max = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
       tile_max *= p.scale_log2;
       float m_new = m;
       float alpha = 1.f;
@@ -517,25 +534,30 @@ attn_fwd_kernel_v2(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         }
       }
       // probabilities: packed to bf16 in place and stored over the first 64 columns of S_t
-      float row_sum = 0.f;
+      // The exponentials are the busiest resource of the loop (16 per clock and SM on the special-function unit, as long as
+      // the two MMAs they sit between): every fourth one is evaluated on the FMA pipe instead (exp2_poly).
+      float sums[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int hblk = 0; hblk < 2; ++hblk) {
         uint32_t packed[32];
 #pragma unroll
         for (int i = 0; i < 64; i += 2) {
           const int col = hblk * 64 + i;
-          float e0 = exp2f(__uint_as_float(v[col]) * p.scale_log2 - m_use);
-          float e1 = exp2f(__uint_as_float(v[col + 1]) * p.scale_log2 - m_use);
+          const float x0 = __uint_as_float(v[col]) * p.scale_log2 - m_use;
+          const float x1 = __uint_as_float(v[col + 1]) * p.scale_log2 - m_use;
+          float e0 = ((i & 6) == 0) ? exp2_poly(x0) : exp2f(x0);
+          float e1 = exp2f(x1);
           if (!full_tile) {
             if (col < col_lo || col >= col_hi) e0 = 0.f;
             if (col + 1 < col_lo || col + 1 >= col_hi) e1 = 0.f;
           }
-          row_sum += e0 + e1;
+          sums[(i >> 1) & 3] += e0 + e1;
           __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
           packed[i >> 1] = *reinterpret_cast<uint32_t*>(&b);
         }
         tmem_st32(tmem_s + hblk * 32, packed);
       }
+      const float row_sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
       l = l * alpha + row_sum;
       m = m_new;
       tmem_wait_st();

@@ -99,6 +99,15 @@ FLB_API int flb_sumsq(const float* x, long long n, float* partial, float* out, i
   return FLB_OK;
 }
 
+// out[0] (+)= sum of `parts` floats (one block, fixed order: deterministic).  Finishes norms whose per-block partial sums
+// were produced by other kernels (the fused gradient reduction writes them while it reduces).
+FLB_API int flb_sum_partials(const float* partial, int parts, float* out, int accumulate, cudaStream_t stream) {
+  if (parts <= 0) return FLB_ERR_SHAPE;
+  sumsq_final_kernel<<<1, kThreads, 0, stream>>>(partial, parts, out, accumulate);
+  FLB_CHECK_LAUNCH();
+  return FLB_OK;
+}
+
 FLB_API int flb_clip_coeff(const float* normsq, float max_norm, float extra_scale, float* coeff_out, float* norm_out,
                            cudaStream_t stream) {
   clip_coeff_kernel<<<1, 1, 0, stream>>>(normsq, max_norm, extra_scale, coeff_out, norm_out);

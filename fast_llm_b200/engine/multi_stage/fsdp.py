@@ -265,8 +265,10 @@ class FSDP:
             from fast_llm_b200.parallel.symmetric import rs_reduce
 
             self._grad_arena.barrier(0)
+            # the kernel also leaves the per-block sums of squares of the reduced shard: the gradient norm needs no pass of
+            # its own (`norm_partials` is a view into one buffer of all stages, finished by a single launch)
             rs_reduce(self._grad_arena, self._grad_buffer, self._grad_shard, self._shard_size, 1.0 / self._fsdp_dim.size,
-                      accumulate, None)
+                      accumulate, getattr(self, "norm_partials", None))
             return
         if self._fsdp_dim.size > 1:
             reduce_scatter_tensor(self._grad_buffer_local_shard, self._grad_buffer, op=torch.distributed.ReduceOp.AVG, group=self._fsdp_group)

@@ -276,6 +276,20 @@ class MultiStageModel:
                         weight_buffer_index=wi if num_weight_buffers < len(local) else ("own", s),
                         grad_buffer_index=gi if num_grad_buffers < len(local) else ("own", s))
         self._num_weight_buffers, self._num_grad_buffers = num_weight_buffers, num_grad_buffers
+        # The fused gradient reduction leaves per-block sums of squares of every reduced shard: when each of them counts in
+        # full towards this rank's share of the global norm, one launch over this buffer replaces a norm pass per stage.
+        self._grad_norm_partials = None
+        if mode.support_backward and self._grad_arena is not None:
+            from fast_llm_b200.ops import _lib
+
+            fsdps = [f for _, stage in local for f in stage.fsdps if f.requires_grad]
+            tensor_rank = dist_config.tensor_rank
+            counted_in_full = all(f.get_parameter_meta(n).is_tensor_parallel or tensor_rank == 0 for f in fsdps for n in f.parameter_names)
+            if fsdps and counted_in_full:
+                blocks = _lib.get_lib().flb_rs_reduce_blocks()
+                self._grad_norm_partials = torch.zeros(len(fsdps) * blocks, dtype=torch.float32, device=device)
+                for i, f in enumerate(fsdps):
+                    f.norm_partials = self._grad_norm_partials[i * blocks : (i + 1) * blocks]
         # tied duplicates alias their owner's tensors
         if mode.support_forward:
             for owner, dup, _, _ in self._tied_duplicates.values():
@@ -319,6 +333,12 @@ class MultiStageModel:
             state = {name: self.get_stage_shards(name, s) for name in self._state_shard_names[1:]}
             groups += stage.get_param_groups(state)
         return groups
+
+    @property
+    def grad_norm_partials(self) -> "torch.Tensor | None":
+        """Per-block sums of squares of all reduced gradient shards of this rank (written by the fused reduction), or None
+        when the norm has to be computed from `get_grad_norm_slices`."""
+        return getattr(self, "_grad_norm_partials", None)
 
     def get_grad_norm_slices(self) -> list[torch.Tensor]:
         return [sl for stage in self._stages_on_device.values() for sl in stage.get_grad_norm_slices()]

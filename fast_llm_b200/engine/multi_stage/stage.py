@@ -246,6 +246,7 @@ class Stage:
             sl = slice(g["begin"], g["end"])
             out.append({
                 "name": f"stage_{self._index}_{g['names'][0]}..{g['names'][-1]}",
+                "stage": self._index,
                 "weight_decay": g["key"][0],
                 "lr_scale": g["key"][1],
                 "params": self._fsdps[g["fsdp"]].weight_shard[sl],

@@ -12,7 +12,7 @@ import torch
 
 from fast_llm_b200.engine.optimizer.config import GradientScalerConfig, OptimizerConfig
 from fast_llm_b200.engine.optimizer.learning_rate import create_schedule_from_config
-from fast_llm_b200.ops.optim import adamw, clip_coeff, sumsq
+from fast_llm_b200.ops.optim import adamw, clip_coeff, sum_partials, sumsq
 from fast_llm_b200.parallel.collectives import all_reduce
 
 logger = logging.getLogger(__name__)
@@ -111,7 +111,7 @@ def get_grad_scaler(config: GradientScalerConfig, compute_dtype: torch.dtype, di
 
 class Optimizer:
     def __init__(self, config: OptimizerConfig, param_groups: list[dict], grad_norm_slices: list[torch.Tensor], distributed,
-                 compute_dtype: torch.dtype = torch.float32, weight_arena=None):
+                 compute_dtype: torch.dtype = torch.float32, weight_arena=None, grad_norm_partials: torch.Tensor | None = None):
         config.validate()
         self._config = config
         self._param_groups = param_groups
@@ -119,6 +119,10 @@ class Optimizer:
         self._distributed = distributed
         # weight buffers in NVLink symmetric memory: Adam pushes the new bf16 weights to every data-parallel peer
         self._weight_arena = weight_arena
+        # per-block sums of squares of every reduced gradient shard, left by the fused reduction kernels
+        self._grad_norm_partials = grad_norm_partials
+        # stage index -> event recorded once every data rank's new weights of that stage have landed in the buffers
+        self.stage_ready_events: dict[int, torch.cuda.Event] = {}
         self._lr_schedule = create_schedule_from_config(config.learning_rate)
         self._current_step = 0
         self._grad_scaler = get_grad_scaler(config.gradient_scaler, compute_dtype, distributed)
@@ -148,10 +152,14 @@ class Optimizer:
 
     def _compute_clip_coefficient(self) -> None:
         first = True
-        for g in self._grad_norm_slices:
-            if g.numel():
-                sumsq(g, self._normsq, accumulate=not first)
-                first = False
+        if self._grad_norm_partials is not None:
+            sum_partials(self._grad_norm_partials, self._normsq)
+            first = False
+        else:
+            for g in self._grad_norm_slices:
+                if g.numel():
+                    sumsq(g, self._normsq, accumulate=not first)
+                    first = False
         if first:
             self._normsq.zero_()
         all_reduce(self._normsq, group=self._distributed.world_group)
@@ -170,7 +178,8 @@ class Optimizer:
         lr = self._lr_schedule(self._current_step)
         self._compute_clip_coefficient()
         c = self._config
-        for group in self._param_groups:
+        self.stage_ready_events.clear()
+        for index, group in enumerate(self._param_groups):
             lr_scale = c.default_learning_rate_scale if group["lr_scale"] is None else group["lr_scale"]
             wd = c.weight_decay if group["weight_decay"] else 0.0
             if self._weight_arena is not None and group.get("buffer") is not None and group["params"].numel() % 4 == 0:
@@ -182,9 +191,16 @@ class Optimizer:
                 assert self._weight_arena is None, "parameter group not aligned for the fused update"
                 adamw(group["params"], group["grads"], group["exp_avgs"], group["exp_avgs_sq"], group.get("buffer"),
                       lr * lr_scale, c.beta_1, c.beta_2, c.epsilon, wd, self._current_step, 1.0, self._coeff)
-        if self._weight_arena is not None:
-            # every rank's pushes have landed (and every rank is done reading gradients) once all pass this barrier
-            self._weight_arena.barrier(1)
+            stage = group.get("stage")
+            last_of_stage = index + 1 == len(self._param_groups) or self._param_groups[index + 1].get("stage") != stage
+            if self._weight_arena is not None and last_of_stage:
+                # Every rank's pushes of this stage have landed once all ranks pass this barrier.  One barrier per stage (not
+                # one at the end) lets the next step's first forwards start while the later stages are still being updated.
+                self._weight_arena.barrier(1)
+                if stage is not None:
+                    event = torch.cuda.Event()
+                    event.record()
+                    self.stage_ready_events[stage] = event
         if metrics is not None:
             metrics["learning_rate"] = lr
             metrics["grad_norm"] = self._norm  # device tensor; converted when logged

@@ -90,7 +90,15 @@ class ScheduleRunner:
         self._weight_buffer_used: dict = {}
         self._grad_buffer_reduced: dict = {}
         self._recv_buffers: dict[tuple, torch.Tensor] = {}
+        self._stage_ready: dict = {}  # stage -> event after which its updated weights are complete (overlapped update)
         self._run = None
+
+    def wait_for_optimizer(self) -> None:
+        """Make the compute stream wait for an optimizer step that is still running on the data stream; call before
+        anything but the next training step reads the weights (evaluation, checkpoints, export)."""
+        if self._stage_ready and self._data_stream is not self._compute_stream:
+            self._compute_stream.wait_stream(self._data_stream)
+        self._stage_ready = {}
 
     def set_run(self, run) -> None:
         """The run whose artifact directory receives the schedule profiles."""
@@ -113,6 +121,8 @@ class ScheduleRunner:
         training = schedule.phase.is_training
         if training:
             assert self._multi_stage.stages_on_device is not None and self._optimizer is not None or self._config.skip_step
+        if not training:
+            self.wait_for_optimizer()
         context = BatchContext(iteration, schedule)
         context.data_iterator = data_iterator
         context.preprocessed = preprocessed
@@ -144,7 +154,12 @@ class ScheduleRunner:
                 for stage, accumulate in context.deferred_reduces:
                     with self._span(EventType.reduce, self._data_stream):
                         stage.reduce_gradients(accumulate)
-        if self._data_stream is not self._compute_stream:
+        fused = training and getattr(self._optimizer, "pushes_weights_to_peers", False)
+        # With the fused update (Adam stores the new weights into every data rank's buffers, stage by stage) the optimizer runs
+        # on the data stream right behind the reductions and the compute stream is not held back: the next step's first
+        # forward of a stage waits only for that stage's weights (`_stage_ready`), so the weight push overlaps with it.
+        overlap_update = fused and not self._config.skip_step and self._data_stream is not self._compute_stream
+        if self._data_stream is not self._compute_stream and not overlap_update:
             self._compute_stream.wait_stream(self._data_stream)
         if self._pipeline_stream is not self._compute_stream:
             self._compute_stream.wait_stream(self._pipeline_stream)
@@ -152,11 +167,13 @@ class ScheduleRunner:
 
         update_successful = True
         if training and not self._config.skip_step:
-            with self._span(EventType.optimizer, self._compute_stream):
+            update_stream = self._data_stream if overlap_update else self._compute_stream
+            with self._stream_ctx(update_stream), self._span(EventType.optimizer, update_stream):
                 update_successful = self._optimizer.step(context.metrics if return_metrics else None)
+            if overlap_update:
+                self._stage_ready = dict(self._optimizer.stage_ready_events)
             # Adam wrote the new weights into this rank's slice of the weight buffers.  With one data rank that is the
             # whole buffer; otherwise the next restore all-gathers the other slices.
-            fused = getattr(self._optimizer, "pushes_weights_to_peers", False)
             if (self._distributed_config.data_parallel > 1 and not fused) or self._multi_stage._num_weight_buffers < len(self._stages_on_device):
                 self._multi_stage.invalidate_buffers()
         losses = self._reduce_losses(context, schedule)
@@ -216,6 +233,9 @@ class ScheduleRunner:
             if self._data_stream is not self._compute_stream:
                 with self._span(EventType.compute_wait_data, self._compute_stream, step):
                     self._compute_stream.wait_event(event)
+        ready = self._stage_ready.pop(step.stage, None)
+        if ready is not None:
+            self._compute_stream.wait_event(ready)  # the previous step's update of this stage, still running when we got here
         if step.type_ == StepType.backward:
             reduced = self._grad_buffer_reduced.pop(stage.grad_buffer_index, None)
             if reduced is not None and self._data_stream is not self._compute_stream:

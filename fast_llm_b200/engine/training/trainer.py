@@ -80,7 +80,7 @@ class Trainer:
             self._multi_stage.base_model.add_reference_model(name, runner)
         self._optimizer = Optimizer(config.optimizer, self._multi_stage.get_param_groups(), self._multi_stage.get_grad_norm_slices(),
                                     distributed, compute_dtype=config.model.distributed.compute_dtype.torch,
-                                    weight_arena=self._multi_stage.weight_arena)
+                                    weight_arena=self._multi_stage.weight_arena, grad_norm_partials=self._multi_stage.grad_norm_partials)
         self._runner.setup(distributed, self._optimizer)
         self._runner.set_run(run)
         cache_dir = None if run.experiment_directory is None else run.experiment_directory / "dataset_cache"
@@ -206,6 +206,7 @@ class Trainer:
                 if done:
                     self._check_device_errors()
                 for name, evaluator in self._evaluators.items():
+                    self._runner.wait_for_optimizer()
                     result = evaluator.run(self._completed_steps, force=done)
                     if result:
                         metrics.update(result)
@@ -253,6 +254,7 @@ class Trainer:
 
     def _save_checkpoint(self, config, metrics: dict | None, iteration: int | None = None) -> None:
         iteration = self._completed_steps if iteration is None else iteration
+        self._runner.wait_for_optimizer()
         self._check_device_errors()
         directory = self._checkpoint_base(config) / str(iteration)
         if self._run.is_main_rank:

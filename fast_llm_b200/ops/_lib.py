@@ -53,6 +53,7 @@ _SIGNATURES = {
     "flb_dist_grad": [_p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _ll, _ll, _ll, _f, _f, _i, _p],
     "flb_sumsq_scratch_floats": [],
     "flb_sumsq": [_p, _ll, _p, _p, _i, _p],
+    "flb_sum_partials": [_p, _i, _p, _i, _p],
     "flb_clip_coeff": [_p, _f, _f, _p, _p, _p],
     "flb_adamw": [_p, _p, _p, _p, _p, _ll, _f, _f, _f, _f, _f, _i, _f, _p, _p, _p],
     "flb_abi_version": [],

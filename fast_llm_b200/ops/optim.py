@@ -27,6 +27,17 @@ def sumsq(x: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> torch
     return out
 
 
+def sum_partials(partials: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> torch.Tensor:
+    """out[0] (+)= partials.sum() in a fixed order (one block); `partials` fp32 on the device."""
+    if partials.is_cuda:
+        _lib.check(_lib.get_lib().flb_sum_partials(partials.data_ptr(), partials.numel(), out.data_ptr(), int(accumulate),
+                                                   _lib.stream_ptr()), "flb_sum_partials")
+        _lib.count_launch()
+        return out
+    s = partials.float().sum()
+    return out.add_(s) if accumulate else out.fill_(s)
+
+
 def clip_coeff(normsq: torch.Tensor, max_norm: float, extra_scale: float, coeff_out: torch.Tensor,
                norm_out: torch.Tensor) -> None:
     """coeff = extra_scale * min(1, max_norm / (norm + 1e-6)), norm = sqrt(normsq) * extra_scale; max_norm <= 0 disables."""

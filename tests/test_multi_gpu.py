@@ -57,6 +57,102 @@ def test_fused_zero_matches_nccl_path():
         assert (fused[0][2][name] == fused[1][2][name]).all(), name
 
 
+def _gradient_rank_main(rank, world_size, updates):
+    """One step without the optimizer: this rank's reduced fp32 gradient shards and the global gradient norm."""
+    import torch
+
+    from tests.common import build_trainer, tiny_trainer_config, train_steps
+    from fast_llm_b200.engine.multi_stage.multi_stage import ShardName
+
+    torch.cuda.set_device(rank)
+    updates = {("model", "distributed", "use_cuda"): True, ("model", "distributed", "compute_dtype"): "bf16",
+               ("model", "distributed", "world_size"): world_size, ("model", "distributed", "rank"): rank,
+               ("model", "distributed", "local_world_size"): world_size, ("model", "distributed", "reproducible_init"): True,
+               ("data", "micro_batch_size"): 512, ("schedule", "depth_first_micro_batches"): 2, **updates}
+    trainer, distributed = build_trainer(tiny_trainer_config(updates))
+    fused = trainer.multi_stage.weight_arena is not None
+    from fast_llm_b200.parallel.topology import PhaseType
+
+    schedule = trainer._schedules[PhaseType.training]
+    iterator = trainer._data.get_iterator("training", consumed_samples=0, num_workers=0)
+    losses, ok, metrics = trainer.runner.run_step(iterator, schedule, iteration=1, return_metrics=True)
+    torch.cuda.synchronize()
+    from fast_llm_b200.utils.device_errors import check_device_errors
+
+    check_device_errors(distributed.world_group, distributed.device)
+    grads = trainer.multi_stage._shards[ShardName.grads].float().cpu().numpy()
+    norm = float(metrics["grad_norm"])
+    distributed.shutdown()
+    return losses, grads, norm, fused
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_reduction_gives_the_same_gradient_shards_and_norm_as_nccl():
+    """The reduced fp32 gradient shards themselves (not weights after Adam, where a step is about one learning rate whatever
+    the gradient): peer-load reduction in rank order against NCCL's reduce-scatter, and the norm finished from the kernel's
+    per-block partial sums against the separate norm pass.  The embedding backward adds rows with atomics, so the last bits of
+    its gradient depend on the order of arrival: tolerance 1e-5 relative."""
+    fused = run_distributed(_gradient_rank_main, 2, {("optimizer", "learning_rate", "base"): 0.0}, timeout=600)
+    plain = run_distributed(_gradient_rank_main, 2, {("optimizer", "learning_rate", "base"): 0.0, ("model", "multi_stage", "fused_collectives"): False},
+                            timeout=600)
+    assert all(r[3] for r in fused) and not any(r[3] for r in plain)
+    for (lf, gf, nf, _), (lp, gp, np_, _) in zip(fused, plain):
+        assert lf == pytest.approx(lp, rel=1e-6)
+        torch.testing.assert_close(torch.from_numpy(gf), torch.from_numpy(gp), rtol=1e-5, atol=1e-8)
+        assert nf == pytest.approx(np_, rel=1e-5)
+    assert fused[0][2] == fused[1][2], "every rank computes the same global norm"
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("name,updates", [
+    ("zero2", {("model", "multi_stage", "zero_stage"): 2}),
+    ("zero3", {("model", "multi_stage", "zero_stage"): 3}),
+    ("zero3_two_buffers", {("model", "multi_stage", "zero_stage"): 3, ("model", "multi_stage", "num_weight_buffers"): 2,
+                           ("model", "multi_stage", "num_grad_buffers"): 2}),
+])
+def test_zero_stages_on_gpus_match_stage_one(name, updates):
+    """ZeRO-2 / ZeRO-3 on real streams: weight gathers issued one step ahead into buffers shared round-robin between stages,
+    gradient buffers reused after their reduction - the events that guard them are only exercised on a GPU."""
+    steps = 3
+    base = {("schedule", "depth_first_micro_batches"): 2, ("model", "multi_stage", "fused_collectives"): False}
+    reference = run_distributed(_gpu_rank_main, 2, base, steps, timeout=600)
+    sharded = run_distributed(_gpu_rank_main, 2, {**base, **updates}, steps, timeout=600)
+    for (lr_, wr, _, _), (ls, ws, _, _) in zip(reference, sharded):
+        assert ls == pytest.approx(lr_, rel=2e-3), name
+        for key in wr:
+            torch.testing.assert_close(torch.from_numpy(ws[key]), torch.from_numpy(wr[key]), rtol=1e-3, atol=4e-3, msg=lambda m: f"{name} {key}: {m}")
+
+
+def _pipeline_rank_main(rank, world_size, updates, steps):
+    import torch
+
+    from tests.common import build_trainer, tiny_trainer_config, train_steps
+
+    torch.cuda.set_device(rank)
+    updates = {("model", "distributed", "use_cuda"): True, ("model", "distributed", "compute_dtype"): "bf16",
+               ("model", "distributed", "world_size"): world_size, ("model", "distributed", "rank"): rank,
+               ("model", "distributed", "local_world_size"): world_size, ("model", "distributed", "reproducible_init"): True,
+               ("data", "micro_batch_size"): 512, **updates}
+    trainer, distributed = build_trainer(tiny_trainer_config(updates))
+    losses = train_steps(trainer, steps)
+    torch.cuda.synchronize()
+    distributed.shutdown()
+    return losses
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("tied", [False, True])
+def test_pipeline_parallel_on_gpus_matches_one_gpu(tied):
+    """Two pipeline ranks over NCCL point-to-point with the receives posted early in the common transfer order (four
+    micro-batches in flight, so every rank has sends and receives interleaved): same losses as the whole model on one GPU."""
+    steps = 3
+    common = {("schedule", "breadth_first_micro_batches"): 4, ("model", "base_model", "tied_embedding_weight"): tied}
+    single = run_distributed(_pipeline_rank_main, 1, common, steps, timeout=600)[0]
+    piped = run_distributed(_pipeline_rank_main, 2, {**common, ("model", "distributed", "pipeline_parallel"): 2}, steps, timeout=600)
+    for losses in piped:
+        assert losses == pytest.approx(single, rel=5e-3)
+
+
 def _fused_tp_rank_main(rank, world_size, tokens, hidden, ffn, timing):
     """Sequence-parallel column- and row-parallel linears, forward and backward: fused peer-memory kernels vs NCCL."""
     import torch
