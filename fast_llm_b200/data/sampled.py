@@ -2,8 +2,8 @@
 
 Documents are visited epoch after epoch in a seeded shuffled order and laid end to end into one token stream; sample
 `i` covers tokens `[i * micro_batch_size, (i + 1) * micro_batch_size + predicted_tokens)` of that stream, so consecutive
-samples overlap by the label token(s).  With `truncate_documents` documents are cut at sample boundaries (and documents
-longer than `maximum_document_length` are split); without it documents stay whole: one that does not fit the rest of a
+samples overlap by the label token(s).  With `truncate_documents` documents are cut at sample boundaries (and the part of a
+document inside a sample is split into pieces of at most `maximum_document_length`); without it documents stay whole: one that does not fit the rest of a
 sample starts the next one and the gap is padding (native helper `flb_build_padded_token_cumsum`), over-long documents
 are dropped.  Only a sub-sampled token cumsum is stored (every `token_cumsum_rate` documents), so the index stays small
 for billions of documents; the index is cached as `.npy` next to a `.yaml` description of what produced it.
@@ -147,14 +147,13 @@ class SampledIndexedDataset:
                 return
             logger.warning(f"Sampling cache {paths[1]} does not match the configuration; rebuilding")
         sizes = np.asarray(self._dataset.get_document_sizes(), dtype=np.int64)
-        # --- units: whole documents, or chunks of at most `max_doc` tokens when truncating
+        # --- units: whole documents.  When truncating, the stream is the plain concatenation of the documents; the part of a
+        # document that falls into a sample is cut into pieces of at most `max_doc` tokens when the sample is assembled,
+        # counted from where that part starts (`fast_llm/data/dataset/sampled.py:397-415`), so with the default limit (one
+        # sample) a document is never split inside a sample.
         if self._truncate:
-            chunks_per_doc = np.maximum((sizes + self._max_doc - 1) // self._max_doc, 1)
-            unit_doc = np.repeat(np.arange(len(sizes)), chunks_per_doc)
-            first = np.concatenate([[0], np.cumsum(chunks_per_doc)[:-1]])
-            unit_begin = (np.arange(len(unit_doc)) - np.repeat(first, chunks_per_doc)) * self._max_doc
-            unit_size = np.minimum(sizes[unit_doc] - unit_begin, self._max_doc)
-            keep = unit_size > 0
+            unit_doc, unit_begin, unit_size = np.arange(len(sizes)), np.zeros(len(sizes), dtype=np.int64), sizes
+            keep = sizes > 0
         else:
             unit_doc, unit_begin, unit_size = np.arange(len(sizes)), np.zeros(len(sizes), dtype=np.int64), sizes
             keep = sizes <= min(self._max_doc, self._sample_size)
@@ -243,7 +242,9 @@ class SampledIndexedDataset:
                 lo, hi = max(begin - start, 0), min(end - start, size)
                 if hi > lo:
                     base = int(self._chunk_begin[unit])
-                    documents.append(self._dataset.get_document(int(self._doc_order[unit]), base + lo, base + hi))
+                    step = self._max_doc if self._truncate else hi - lo
+                    for piece in range(lo, hi, step):
+                        documents.append(self._dataset.get_document(int(self._doc_order[unit]), base + piece, base + min(piece + step, hi)))
             if done:
                 break
             anchor += 4 + 64 // self._rate
