@@ -550,3 +550,23 @@ def test_megatron_initialization_replays_one_stream():
     trainer2, _ = build_trainer(config2)
     for name, _, tensor in trainer2.multi_stage.get_state_tensor_iterator(("weights",)):
         assert torch.equal(tensor, weights[name]), name
+
+
+def test_safe_load_names_the_parameter_that_was_not_loaded(tmp_path):
+    """A checkpoint load that skips one parameter must fail, and say which one."""
+    from fast_llm_b200.engine.checkpoint.safe_load import SafeLoad
+
+    trainer, _ = build_trainer(tiny_trainer_config())
+    model = trainer.multi_stage
+    names = [n for _, _, fsdp, _ in model.iter_fsdps() for n in fsdp.parameter_names]
+    skipped = names[3]
+    with pytest.raises(RuntimeError, match=skipped.replace(".", r"\.")):
+        with SafeLoad(model, shard_names=("weights",)) as context:
+            for _, _, fsdp, sl in model.iter_fsdps():
+                shard = model.get_shard("weights")[sl]
+                for name in fsdp.parameter_names:
+                    begin, end = fsdp.parameter_range_in_shard(name)
+                    if name == skipped:
+                        continue
+                    shard[begin:end].zero_()
+                    context.mark_as_loaded(end - begin, (name, "weights"))
