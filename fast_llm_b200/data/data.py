@@ -57,7 +57,10 @@ class GPTData:
             use_grpo_data=preprocessing.get("use_grpo_data", False), use_images=preprocessing.get("use_images", False),
         ).validate()
         t0 = time.perf_counter()
-        self._datasets[dataset_name] = c.datasets[dataset_name].build_and_sample(sampling, num_samples, c.seed)
+        from fast_llm_b200.data.monitor import DatasetMonitor
+
+        self._datasets[dataset_name] = DatasetMonitor(c.datasets[dataset_name].build_and_sample(sampling, num_samples, c.seed),
+                                                      c.data_sample_warn_time_ms)
         self._sampling[dataset_name] = sampling
         self._preprocessing[dataset_name] = dict(preprocessing)
         if self._distributed_config.rank == 0:
@@ -76,9 +79,6 @@ class GPTData:
             micro_batch_size=sampling.micro_batch_size, predicted_tokens=sampling.predicted_tokens,
             micro_batch_splits=pre.get("micro_batch_splits", 1), sequence_data_parallel=dc.sequence_data_parallel,
             sequence_data_rank=dc.sequence_data_rank, pin=pin)
-        elapsed = (time.perf_counter() - t0) * 1e3
-        if elapsed > self._config.data_sample_warn_time_ms:
-            logger.warning(f"Sample {index} of dataset {dataset_name} took {elapsed:.0f} ms to load")
         return inputs
 
     def get_iterator(self, dataset_name: str, *, consumed_samples: int, num_workers: int = 2, prefetch_factor: int | None = None,

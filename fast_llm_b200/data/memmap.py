@@ -16,6 +16,7 @@ its shape.  Sections:
 
 import io
 import json
+import logging
 import pathlib
 import typing
 
@@ -31,14 +32,24 @@ from fast_llm_b200.utils.data_type import DataType
 FILE_HEADER = b"fast_llm_prepared_dataset"
 
 
+logger = logging.getLogger(__name__)
+
 @config_class(dynamic_type={SampledDatasetConfig: "memmap"})
 class MemmapDatasetConfig(IndexedDatasetConfig):
     _abstract: typing.ClassVar[bool] = False
-    path: pathlib.Path = Field(default=None, desc="Path of the dataset file.", hint=FieldHint.core)
+    path: pathlib.Path = Field(default=None, desc="Path of the dataset file (or the prefix of a Megatron-style `.bin` / `.idx` pair).", hint=FieldHint.core)
 
-    def build(self) -> "MemmapDataset":
+    def build(self):
         name = str(self.path).replace("/", "__")
-        return MemmapDataset(name, self.path)
+        path = pathlib.Path(self.path)
+        if path.is_file():
+            return MemmapDataset(name, path)
+        if path.with_suffix(".bin").is_file() and path.with_suffix(".idx").is_file():
+            from fast_llm_b200.data.legacy_memmap import LegacyMemmapDataset
+
+            logger.warning(f"{path}: Megatron-style pair of files; new datasets should use the single-file format")
+            return LegacyMemmapDataset(name, path)
+        raise FileNotFoundError(path)
 
 
 # ---------------------------------------------------------------------------------------------------------------------

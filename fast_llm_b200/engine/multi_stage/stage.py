@@ -163,15 +163,33 @@ class Stage:
             for layer in self._layers:
                 output = layer.forward(output, kwargs, losses, metrics)
                 name = getattr(layer, "module_name", type(layer).__name__)
-                if self._config.debug_layer_outputs:
-                    from fast_llm_b200.utils.tensor_logs import log_tensor
-
-                    log_tensor(f"{name} output", output, level=self._config.debug_layer_outputs)
+                if (self._config.debug_layer_outputs or self._config.debug_layer_gradients) and torch.is_tensor(output):
+                    self._log_layer(output, name, kwargs, training)
                 if self._config.debug_tensor_parallel:
                     self._check_replicated(output, name, training)
                 if self._config.debug_activation_memory:
                     self._log_activation_memory(name)
         return (output.detach() if torch.is_tensor(output) else output), (input_, output)
+
+    def _log_layer(self, output: torch.Tensor, name: str, kwargs: dict, training: bool) -> None:
+        """`debug_layer_outputs` / `debug_layer_gradients`: one record per layer output (and per gradient reaching it), with
+        the micro-batch and micro-sequence in the name.  Block outputs are replicated over the tensor group, or sharded by
+        tokens over it with sequence parallelism; with `debug_global_tensors` the whole tensor is logged once, so the records
+        of different layouts line up (parity: `fast_llm/engine/multi_stage/stage.py:216-232,249-263`)."""
+        from fast_llm_b200.utils.tensor_logs import log_distributed_grad, log_distributed_tensor
+
+        if (count := kwargs.get("num_micro_batches", 1)) > 1:
+            name = f"{name}, mb={kwargs.get('micro_batch', 0)}/{count}"
+        if (count := kwargs.get("micro_batch_splits", 1)) > 1:
+            name = f"{name}, ms={kwargs.get('micro_batch_split', 0)}/{count}"
+        group = getattr(self._distributed, "tensor_group", None)
+        sharded = group is not None and self._distributed.config.sequence_tensor_parallel and output.dim() == 2 and output.is_floating_point()
+        layout = dict(shard_group=group if sharded else None, shard_dim=0, duplicate_groups=() if sharded else (group,),
+                      global_=self._config.debug_global_tensors)
+        if self._config.debug_layer_outputs:
+            log_distributed_tensor(f"{name} fw", output, level=self._config.debug_layer_outputs, **layout)
+        if self._config.debug_layer_gradients and training and output.requires_grad:
+            log_distributed_grad(f"{name} bw", output, level=self._config.debug_layer_gradients, **layout)
 
     def _check_replicated(self, output, name: str, training: bool) -> None:
         """`debug_tensor_parallel`: a layer output that every rank of the tensor group holds in full (no sequence

@@ -45,6 +45,9 @@ class _SpanContext:
 
     def __enter__(self):
         if self._profiler.use_cuda:
+            # an NVTX range of the same name, so that a timeline viewer shows the schedule's events over the kernels
+            label = self._span.type_.value if self._span.stage is None else f"{self._span.type_.value} s{self._span.stage} mb{self._span.data_index}"
+            torch.cuda.nvtx.range_push(label)
             self._span.gpu_begin = torch.cuda.Event(enable_timing=True)
             self._span.gpu_begin.record(self._stream)
         self._span.cpu_begin = time.perf_counter()
@@ -55,6 +58,7 @@ class _SpanContext:
         if self._profiler.use_cuda:
             self._span.gpu_end = torch.cuda.Event(enable_timing=True)
             self._span.gpu_end.record(self._stream)
+            torch.cuda.nvtx.range_pop()
         self._profiler.spans.append(self._span)
 
 

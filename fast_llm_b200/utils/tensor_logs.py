@@ -68,10 +68,44 @@ def log_grad(name: str, tensor: torch.Tensor, *, level: int = 2, scale: float = 
     tensor.register_hook(lambda grad: log_tensor(name, grad, level=level, scale=scale, log_fn=log_fn) and None)
 
 
-def log_generator(name: str, generator: torch.Generator | None = None, log_fn=logger.info):
-    generator = generator or torch.random.default_generator
-    state = generator.get_state()
-    return log_fn(f"{name} generator state checksum: {int(state.long().sum())}")
+def log_distributed_tensor(name: str, tensor: torch.Tensor, *, level: int = 2, scale: float = 1.0, log_fn=logger.info, storage: bool = True,
+                           shard_group=None, shard_dim: int = 0, duplicate_groups: tuple = (), global_: bool = True):
+    """Log a tensor of which every rank of `shard_group` holds one slice along `shard_dim` (sequence-parallel activations, a
+    tensor-parallel weight) and which is replicated over `duplicate_groups`.  With `global_` the slices are gathered and the
+    whole tensor is logged once, by the first rank of all the groups, so the line (and the stored record) is the one a
+    single-process run produces: logs of different parallel layouts can be compared record by record.  Otherwise every rank
+    logs its own slice.  Every rank of the groups must make the call (the gather is a collective).
+    Parity: `fast_llm/logging.py:247-277`."""
+    if level < 1 or not torch.is_tensor(tensor):
+        return None
+    if not global_:
+        return log_tensor(f"Local {name}", tensor, level=level, scale=scale, log_fn=log_fn, storage=storage)
+    if shard_group is not None and shard_group.size() > 1:
+        from fast_llm_b200.parallel.ops import gather_op
+
+        tensor = gather_op(tensor.detach().contiguous(), shard_group, shard_dim)
+    first = (shard_group is None or shard_group.rank() == 0) and all(g is None or g.rank() == 0 for g in duplicate_groups)
+    if not first:
+        return None
+    return log_tensor(f"Global {name}", tensor, level=level, scale=scale, log_fn=log_fn, storage=storage)
+
+
+def log_distributed_grad(name: str, tensor: torch.Tensor, *, level: int = 2, scale: float = 1.0, log_fn=logger.info, storage: bool = True,
+                         shard_group=None, shard_dim: int = 0, duplicate_groups: tuple = (), global_: bool = True, grad_fn=None):
+    """The same for the gradient that reaches `tensor` during backward (parity: `fast_llm/logging.py:280-307`)."""
+    if level < 1 or not tensor.requires_grad:
+        return
+    tensor.register_hook(lambda grad: log_distributed_tensor(
+        name, grad if grad_fn is None else grad_fn(grad), level=level, scale=scale, log_fn=log_fn, storage=storage, shard_group=shard_group,
+        shard_dim=shard_dim, duplicate_groups=duplicate_groups, global_=global_) and None)
+
+
+def log_generator(name: str, generator: "torch.Generator | torch.Tensor | None" = None, log_fn=logger.info):
+    """The last words of a generator's state: equal on ranks (or runs) whose random streams are in step."""
+    if generator is None:
+        generator = torch.cuda.default_generators[torch.cuda.current_device()] if torch.cuda.is_available() else torch.random.default_generator
+    state = generator.get_state() if isinstance(generator, torch.Generator) else generator
+    return log_fn(f"{name} {state.view(torch.int64)[-8:].tolist() if state.numel() % 8 == 0 else int(state.long().sum())}")
 
 
 def log_memory_usage(header: str, log_fn=logger.info):

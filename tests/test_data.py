@@ -220,3 +220,78 @@ def test_training_on_memmap_dataset(dataset, tmp_path):
     losses = train_steps(trainer, 3)
     assert all(l == l for l in losses)
     assert (tmp_path / "exp" / "dataset_cache").is_dir()
+
+
+def test_megatron_style_pair_of_files_round_trip(tmp_path):
+    """The `.bin` / `.idx` format in its three index versions, through the `memmap` dataset type (which picks the reader by what
+    is on disk), and, where the reference tree is present, read back by the reference's own reader."""
+    import pathlib
+    import sys
+
+    from fast_llm_b200.data.config import SampledDatasetConfig
+    from fast_llm_b200.data.legacy_memmap import LegacyMemmapDataset
+
+    plain = _documents(60)
+    spans = _documents(60, seed=1, spans=True)
+    preference = _documents(40, seed=2)
+    for d in preference:
+        d.chosen_span, d.rejected_span = (0, 2), (1, 3)
+    for name, docs in (("plain", plain), ("spans", spans), ("preference", preference)):
+        prefix = tmp_path / name
+        LegacyMemmapDataset.write_dataset(prefix, docs)
+        import fast_llm_b200.models.auto  # noqa: F401
+
+        dataset = SampledDatasetConfig.from_dict({"type": "memmap", "path": str(prefix)}).build()
+        assert isinstance(dataset, LegacyMemmapDataset)
+        assert len(dataset) == len(docs) and dataset.num_tokens == sum(len(d) for d in docs)
+        for i in (0, 7, len(docs) - 1):
+            got = dataset.get_document(i)
+            assert torch.equal(got.tokens, docs[i].tokens.long())
+            assert (got.loss_masking_spans or None) == (docs[i].loss_masking_spans or None)
+            assert got.chosen_span == docs[i].chosen_span and got.rejected_span == docs[i].rejected_span
+        part = dataset.get_document(5, 2, 9)
+        assert torch.equal(part.tokens, docs[5].tokens[2:9].long())
+        ref = pathlib.Path("/root/reference")
+        # (the reference's reader fails on index versions 2 and 3 in this version: it crops spans with a method its span class
+        # does not have; the plain version is compared)
+        if name == "plain" and (ref / "fast_llm" / "data" / "dataset" / "gpt" / "legacy_memmap.py").exists():
+            sys.path.insert(0, str(ref))
+            try:
+                from fast_llm.data.dataset.gpt.legacy_memmap import LegacyMemmapDataset as Reference
+
+                theirs = Reference("ref", prefix)
+                assert len(theirs) == len(docs)
+                assert torch.equal(theirs.get_document(7).tokens.long(), docs[7].tokens.long())
+                assert theirs.get_document_sizes().tolist() == [len(d) for d in docs]
+            finally:
+                sys.path.remove(str(ref))
+                for module in [m for m in sys.modules if m == "fast_llm" or m.startswith("fast_llm.")]:
+                    del sys.modules[module]
+
+
+def test_dataset_monitor_reports_slow_and_failing_samples(caplog):
+    import logging
+    import time
+
+    from fast_llm_b200.data.monitor import DatasetMonitor
+
+    class Slow:
+        name = "slow"
+
+        def __len__(self):
+            return 3
+
+        def __getitem__(self, index):
+            if index == 2:
+                raise KeyError("broken sample")
+            time.sleep(0.02 * index)
+            return index
+
+    monitor = DatasetMonitor(Slow(), data_sample_warn_time_ms=10)
+    with caplog.at_level(logging.WARNING):
+        assert monitor[0] == 0 and monitor[1] == 1
+        with pytest.raises(KeyError):
+            monitor[2]
+    assert monitor.slow_samples == 1
+    assert any("Sample 1 from dataset slow took" in r.getMessage() for r in caplog.records)
+    assert any("Failed to get sample 2 from dataset slow" in r.getMessage() for r in caplog.records)

@@ -94,3 +94,46 @@ def test_debug_hooks_check_replicated_tensors_and_log_memory():
         assert mismatches == ["MISMATCH planted: 4 of 4 entries differ between ranks"]
         assert not planted_matched
     assert results[0][1], "rank 0 logs memory after every layer"
+
+
+def _tensor_log_rank(rank, world_size, parallel_updates):
+    from fast_llm_b200.utils.tensor_logs import TensorLogs
+
+    updates = {("model", "distributed", "world_size"): world_size, ("model", "distributed", "rank"): rank,
+               ("model", "distributed", "local_world_size"): world_size, ("model", "distributed", "backend"): "gloo",
+               ("model", "distributed", "reproducible_init"): True, ("model", "multi_stage", "debug_layer_outputs"): 2,
+               ("model", "multi_stage", "debug_layer_gradients"): 2, **parallel_updates}
+    config = tiny_trainer_config(updates)
+    config.validate()
+    from fast_llm_b200.parallel.distributed import Distributed
+
+    distributed = Distributed(config.model.distributed)
+    run = config.get_run(distributed)
+    trainer = config.get_trainer_class()(config=config)
+    with run:
+        TensorLogs.reset(save=True, show=False)  # keep the records in memory (storing them as artifacts needs an experiment directory)
+        trainer.setup(distributed, run)
+        trainer._prepare_training_state()
+        train_steps(trainer, 1)
+        records = [{k: v for k, v in r.items() if k in ("name", "shape", "mu", "std", "min", "max")} for r in TensorLogs.get()]
+    distributed.shutdown()
+    return records
+
+
+@pytest.mark.parametrize("name,world_size,updates", [
+    ("tp2", 2, {("model", "distributed", "tensor_parallel"): 2}),
+    ("stp2", 2, {("model", "distributed", "tensor_parallel"): 2, ("model", "distributed", "sequence_tensor_parallel"): True}),
+])
+def test_tensor_logs_of_a_parallel_layout_match_the_single_process_run(name, world_size, updates):
+    """Every layer output and every gradient reaching it, reconstructed to the global tensor and logged once: the records of a
+    tensor-parallel run (replicated activations) and of a sequence-parallel run (token shards gathered) must be those of the
+    single-process run, name by name (the reference's way of comparing layouts: `tests/utils/compare_tensor_logs.py`)."""
+    reference = run_distributed(_tensor_log_rank, 1, {})[0]
+    records = run_distributed(_tensor_log_rank, world_size, updates)
+    assert len(reference) >= 6
+    assert records[1] == [], "only the first rank of the groups logs the global tensors"
+    assert [r["name"] for r in records[0]] == [r["name"] for r in reference]
+    for got, expected in zip(records[0], reference):
+        assert got["shape"] == expected["shape"], got["name"]
+        for key in ("mu", "std", "min", "max"):
+            assert got[key] == pytest.approx(expected[key], rel=2e-4, abs=2e-6), (name, got["name"], key)
