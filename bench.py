@@ -26,19 +26,80 @@ GLOBAL_BATCH_TOKENS = 262144
 MICRO_BATCH_TOKENS = 8192
 
 
+def _llama(layers, hidden, heads, kv_heads, ffn, vocab, theta, mlp=None):
+    return {
+        "embeddings": {"vocab_size": vocab, "dropout": 0.0},
+        "decoder": {"num_blocks": layers, "block": {
+            "mixer": {"type": "attention", "rotary": {"type": "default", "theta": theta}, "heads": heads, "head_groups": kv_heads, "head_size": hidden // heads,
+                      "add_linear_biases": False, "dropout": 0.0},
+            "mlp": mlp or {"intermediate_size": ffn, "add_linear_biases": False, "gated": True, "activation": "silu"},
+            "normalization": {"type": "rms_norm", "epsilon": 1.0e-05}, "dropout": 0.0}},
+        "head": {"normalization": {"type": "rms_norm", "epsilon": 1.0e-05}},
+        "hidden_size": hidden, "tied_embedding_weight": False,
+    }
+
+
+# Extra measurements next to the headline benchmark: model, tokens per micro-batch, sequence length, layout (for 8 GPUs) and
+# default micro-batches per step.  `layers` may be lowered with --layers where the full depth does not fit (stated in the result).
+CONFIGS = {
+    "mistral_7b_dp": None,  # examples/mistral.yaml: the headline benchmark
+    "llama3_8b_tp4": {
+        "name": "Llama-3-8B (32 layers, hidden 4096, 32/8 heads, SwiGLU 14336, vocab 128256, theta 500000)",
+        "base_model": _llama(32, 4096, 32, 8, 14336, 128256, 500000), "layers": 32, "micro_batch_tokens": 8192, "document_length": 8192,
+        "distributed": {"tensor_parallel": 4, "sequence_tensor_parallel": True}, "multi_stage": {"zero_stage": 2}, "schedule": {},
+        "sequential": 4, "layout": "tp4 sequence-parallel x dp{dp} ZeRO-2",
+    },
+    "mixtral_8x7b_z3": {
+        "name": "Mixtral-8x7B-style dropless MoE (32 layers, hidden 4096, 32/8 heads, 8 SwiGLU experts of 14336, top-2, vocab 32000)",
+        "base_model": _llama(32, 4096, 32, 8, 14336, 32000, 1000000, mlp={
+            "type": "moe", "experts": 8, "experts_per_token": 2, "intermediate_size": 14336, "add_linear_biases": False, "gated": True,
+            "activation": "silu", "auxiliary_loss_coefficient": 0.01}),
+        "layers": 32, "micro_batch_tokens": 4096, "document_length": 4096, "distributed": {}, "multi_stage": {"zero_stage": 3}, "schedule": {},
+        "sequential": 4, "layout": "dp{dp} ZeRO-3",
+    },
+    "llama3_70b_pp2_tp4": {
+        "name": "Llama-3-70B (80 layers, hidden 8192, 64/8 heads, SwiGLU 28672, vocab 128256)",
+        "base_model": _llama(80, 8192, 64, 8, 28672, 128256, 500000), "layers": 80, "micro_batch_tokens": 4096, "document_length": 4096,
+        "distributed": {"tensor_parallel": 4, "sequence_tensor_parallel": True, "pipeline_parallel": 2}, "multi_stage": {"zero_stage": 1},
+        "schedule": {"breadth_first_micro_batches": 8}, "sequential": 8, "layout": "pp2 x tp4 sequence-parallel x dp{dp}, breadth-first",
+    },
+}
+
+
 def parse_args():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=int(os.environ.get("WORLD_SIZE", 1)))
     p.add_argument("--steps", type=int, default=3)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    p.add_argument("--layers", type=int, default=32, help="debug only: any value other than 32 marks the result invalid")
-    p.add_argument("--global-batch-tokens", type=int, default=GLOBAL_BATCH_TOKENS)
+    p.add_argument("--layers", type=int, default=None, help="decoder blocks; anything but the configuration's own depth is stated in the result (invalid for the headline)")
+    p.add_argument("--global-batch-tokens", type=int, default=None)
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--tensor-parallel", type=int, default=1, help="extra measurement: tensor + sequence parallel groups of this size (default 1: the headline config)")
+    p.add_argument("--config", default="mistral_7b_dp", choices=sorted(CONFIGS), help="model / layout to measure (default: the headline benchmark)")
+    p.add_argument("--sequential-micro-batches", type=int, default=None, help="extra configs: micro-batches per optimizer step and data rank")
+    p.add_argument("--profile-schedule", action="store_true", help="record the schedule profile of the last timed step and print its summary (adds synchronisations: not a benchmark run)")
     p.add_argument("--no-reference-compat", action="store_true", help="reference arm: do not adapt the arguments of torch's AdamW (shows the reference's own TypeError)")
     p.add_argument("--no-fused-collectives", action="store_true", help="extra measurement: NCCL collectives instead of the peer-memory kernels")
-    return p.parse_args()
+    args = p.parse_args()
+    spec = CONFIGS[args.config]
+    args.spec = spec
+    if spec is None:
+        args.layers = 32 if args.layers is None else args.layers
+        args.full_layers = 32
+        args.micro_batch_tokens = MICRO_BATCH_TOKENS
+        args.global_batch_tokens = GLOBAL_BATCH_TOKENS if args.global_batch_tokens is None else args.global_batch_tokens
+    else:
+        args.full_layers = spec["layers"]
+        args.layers = spec["layers"] if args.layers is None else args.layers
+        args.micro_batch_tokens = spec["micro_batch_tokens"]
+        model_parallel = spec["distributed"].get("tensor_parallel", 1) * spec["distributed"].get("pipeline_parallel", 1)
+        if args.gpus % model_parallel:
+            raise SystemExit(f"--config {args.config} needs a multiple of {model_parallel} GPUs")
+        args.data_parallel = args.gpus // model_parallel
+        args.sequential = args.sequential_micro_batches or spec["sequential"]
+        args.global_batch_tokens = args.micro_batch_tokens * args.sequential * args.data_parallel
+    return args
 
 
 class ClockSampler:
@@ -140,6 +201,31 @@ def _time_steps(step_fn, steps: int, world: int) -> float:
 
 
 def config_updates(args, world: int) -> dict:
+    common = {
+        ("training", "train_iters"): 2 * (args.warmup + args.steps) + 2,
+        ("training", "num_workers"): 2,
+        ("training", "logs", "interval"): 10**9,
+        ("training", "evaluators"): {},
+        ("run", "experiment_dir"): None,
+    }
+    if args.profile_schedule:
+        common[("schedule", "profile_schedule")] = True
+    spec = args.spec
+    if spec is not None:
+        base_model = {**spec["base_model"], "decoder": {**spec["base_model"]["decoder"], "num_blocks": args.layers}}
+        schedule = dict(spec["schedule"])
+        if "breadth_first_micro_batches" in schedule:
+            schedule["breadth_first_micro_batches"] = args.sequential
+        else:
+            schedule["depth_first_micro_batches"] = args.sequential
+        updates = {**common, ("model", "base_model"): base_model, ("data", "micro_batch_size"): spec["micro_batch_tokens"],
+                   ("data", "maximum_document_length"): spec["document_length"]}
+        updates.update({("model", "distributed", k): v for k, v in spec["distributed"].items()})
+        updates.update({("model", "multi_stage", k): v for k, v in spec["multi_stage"].items()})
+        updates.update({("schedule", k): v for k, v in schedule.items()})
+        if args.no_fused_collectives:
+            updates[("model", "multi_stage", "fused_collectives")] = False
+        return updates
     depth = args.global_batch_tokens // MICRO_BATCH_TOKENS // (world // args.tensor_parallel)
     extra = {}
     if args.tensor_parallel > 1:
@@ -148,14 +234,10 @@ def config_updates(args, world: int) -> dict:
     if args.no_fused_collectives:
         extra[("model", "multi_stage", "fused_collectives")] = False
     return {
+        **common,
         **extra,
         ("model", "multi_stage", "zero_stage"): 1,
         ("schedule", "depth_first_micro_batches"): depth,
-        ("training", "train_iters"): 2 * (args.warmup + args.steps) + 2,
-        ("training", "num_workers"): 2,
-        ("training", "logs", "interval"): 10**9,
-        ("training", "evaluators"): {},
-        ("run", "experiment_dir"): None,
         ("model", "base_model", "decoder", "num_blocks"): args.layers,
     }
 
@@ -163,6 +245,8 @@ def config_updates(args, world: int) -> dict:
 def result_line(args, world, ms_per_step, clocks, launches, e2e, impl, extra=None):
     tokens = args.global_batch_tokens
     value = tokens / (ms_per_step / 1e3)
+    if args.spec is not None:
+        return extra_result_line(args, world, ms_per_step, value, clocks, launches, e2e, impl, extra)
     line = {
         "metric": "tokens/s, Mistral-7B 8k-token micro-batch, 256k-token global batch (whole job)",
         "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -175,6 +259,25 @@ def result_line(args, world, ms_per_step, clocks, launches, e2e, impl, extra=Non
                                    + f", {tokens // MICRO_BATCH_TOKENS // (world // args.tensor_parallel)} sequential micro-batches"
                                    + (", NCCL collectives" if args.no_fused_collectives else "")),
                    "l2": "no explicit flush: every step streams > 100 GB of weights, gradients and activations per GPU (L2 is 126 MB)"},
+        "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
+    }
+    if extra:
+        line.update(extra)
+    return line
+
+
+def extra_result_line(args, world, ms_per_step, value, clocks, launches, e2e, impl, extra):
+    spec = args.spec
+    depth_note = "" if args.layers == args.full_layers else f" - REDUCED DEPTH: {args.layers} of {args.full_layers} layers"
+    line = {
+        "metric": f"tokens/s, {args.config} (whole job)", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "tokens_per_sec_per_gpu": value / world,
+        "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights", "impl": impl,
+        "config": {"model": spec["name"] + depth_note, "global_batch": args.global_batch_tokens, "seq_len": spec["document_length"],
+                   "micro_batch_tokens": args.micro_batch_tokens,
+                   "parallelism": spec["layout"].format(dp=args.data_parallel) + f", {args.sequential} micro-batches per step and data rank"
+                                  + (", NCCL collectives" if args.no_fused_collectives else ""),
+                   "l2": "no explicit flush: every step streams far more than the 126 MB of L2 per GPU"},
         "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
     }
     if extra:
@@ -267,6 +370,9 @@ def run_ours(args):
         peak = torch.cuda.max_memory_allocated() / 2**30
     if rank == 0:
         extra = {"final_loss": loss_box.get("lm_loss"), "peak_memory_gib": peak}
+        if args.profile_schedule and runner.last_profile is not None:
+            extra["schedule_profile_summary"] = runner.last_profile["summary"]
+            extra["note"] = "schedule profiling synchronises at the end of every step: not a benchmark number"
         print(json.dumps(result_line(args, world, ms, clocks, launches, e2e, "ours", extra)), flush=True)
     distributed.shutdown()
 
