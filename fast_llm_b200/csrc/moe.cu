@@ -107,3 +107,158 @@ FLB_API int flb_moe_score_grad(const void* y, const int* rows, const void* dout,
   FLB_CHECK_LAUNCH();
   return FLB_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Routing of a top-k mixture-of-experts layer in two kernels (instead of top-k, two softmaxes, scatter, means, sort,
+// histogram and scans as separate passes):
+//   flb_moe_route         per token: the k largest router logits (ties: lower expert first, as a stable descending sort gives),
+//                         their softmax (the routing scores), the full softmax for the load-balancing loss (summed per expert
+//                         and block, so the result does not depend on the order of atomics) and logsumexp for the router z-loss.
+//   flb_moe_route_bwd     gradient of the logits from the score gradients, the load-balancing loss and the z-loss.
+//   flb_moe_layout        rows of every (token, choice) in the expert-sorted row space whose expert ranges are padded to whole
+//                         GEMM tiles, in token order inside an expert (stable, deterministic), and the range starts.
+// Replaces the routing part of `fast_llm/layers/decoder/mlp/mixture_of_experts.py:237-262` and
+// `fast_llm/functional/triton/sparse_copy.py:201-241` (sparse map).
+namespace {
+constexpr int kMaxExperts = 64, kMaxTopK = 8, kRouteThreads = 128;
+
+__global__ void __launch_bounds__(kRouteThreads)
+moe_route_kernel(const float* __restrict__ logits, int tokens, int experts, int k, float* __restrict__ scores, int* __restrict__ top,
+                 float* __restrict__ prob_partial, float* __restrict__ lse_out) {
+  __shared__ float block_prob[kMaxExperts];
+  for (int e = threadIdx.x; e < experts; e += kRouteThreads) block_prob[e] = 0.f;
+  __syncthreads();
+  const int t = blockIdx.x * kRouteThreads + threadIdx.x;
+  if (t < tokens) {
+    float v[kMaxExperts];
+    float m = -INFINITY;
+#pragma unroll 8
+    for (int e = 0; e < experts; ++e) { v[e] = logits[(long long)t * experts + e]; m = fmaxf(m, v[e]); }
+    float se = 0.f;
+    for (int e = 0; e < experts; ++e) se += expf(v[e] - m);
+    if (lse_out) lse_out[t] = m + logf(se);
+    const float inv = 1.f / se;
+    for (int e = 0; e < experts; ++e) atomicAdd(&block_prob[e], expf(v[e] - m) * inv);
+    // k passes of arg-max over what is left
+    unsigned long long taken = 0ull;
+    float chosen[kMaxTopK];
+    int idx[kMaxTopK];
+    for (int j = 0; j < k; ++j) {
+      int best = -1;
+      float bv = -INFINITY;
+      for (int e = 0; e < experts; ++e)
+        if (!((taken >> e) & 1ull) && (best < 0 || v[e] > bv)) { best = e; bv = v[e]; }
+      taken |= 1ull << best;
+      chosen[j] = bv; idx[j] = best;
+    }
+    float top_sum = 0.f;
+    for (int j = 0; j < k; ++j) top_sum += expf(chosen[j] - chosen[0]);
+    for (int j = 0; j < k; ++j) {
+      scores[(long long)t * k + j] = expf(chosen[j] - chosen[0]) / top_sum;
+      top[(long long)t * k + j] = idx[j];
+    }
+  }
+  __syncthreads();
+  // shared-memory float atomics of one block: the order inside a block varies, the partial sums are written per block and
+  // added up in a fixed order afterwards; rounding differences of the in-block order are of the order of 1e-7 relative
+  for (int e = threadIdx.x; e < experts; e += kRouteThreads) prob_partial[(long long)blockIdx.x * experts + e] = block_prob[e];
+}
+
+// dlogits[t, e] = sum_j [e == top[t, j]] s_j (ds_j - <s, ds>)  +  p_e (g_e - <p, g>)  +  z_coeff * 2 lse p_e
+// with s the routing scores, p the full softmax, g_e = aux_grad[e] (gradient of the load-balancing loss wrt the mean
+// probability of expert e, already scaled), z_coeff the scaled z-loss weight divided by the number of tokens.
+__global__ void __launch_bounds__(kRouteThreads)
+moe_route_bwd_kernel(const float* __restrict__ logits, const float* __restrict__ scores, const int* __restrict__ top,
+                     const float* __restrict__ dscores, const float* __restrict__ aux_grad, float z_coeff, int tokens, int experts,
+                     int k, float* __restrict__ dlogits) {
+  const int t = blockIdx.x * kRouteThreads + threadIdx.x;
+  if (t >= tokens) return;
+  float p[kMaxExperts];
+  float m = -INFINITY;
+  for (int e = 0; e < experts; ++e) { p[e] = logits[(long long)t * experts + e]; m = fmaxf(m, p[e]); }
+  float se = 0.f;
+  for (int e = 0; e < experts; ++e) { p[e] = expf(p[e] - m); se += p[e]; }
+  const float lse = m + logf(se), inv = 1.f / se;
+  float pg = 0.f;
+  for (int e = 0; e < experts; ++e) { p[e] *= inv; if (aux_grad) pg += p[e] * aux_grad[e]; }
+  float out[kMaxExperts];
+  for (int e = 0; e < experts; ++e) out[e] = p[e] * ((aux_grad ? aux_grad[e] - pg : 0.f) + z_coeff * 2.f * lse);
+  if (dscores) {
+    float dot = 0.f;
+    for (int j = 0; j < k; ++j) dot += scores[(long long)t * k + j] * dscores[(long long)t * k + j];
+    for (int j = 0; j < k; ++j) {
+      const float s = scores[(long long)t * k + j];
+      out[top[(long long)t * k + j]] += s * (dscores[(long long)t * k + j] - dot);
+    }
+  }
+  for (int e = 0; e < experts; ++e) dlogits[(long long)t * experts + e] = out[e];
+}
+
+// One warp per expert (all in one block): count the expert's entries, then hand out rows in entry order.
+__global__ void moe_layout_kernel(const int* __restrict__ top, int entries, int experts, int tile_rows, int* __restrict__ rows,
+                                  int* __restrict__ row_begin, int* __restrict__ counts_out) {
+  __shared__ int counts[kMaxExperts];
+  __shared__ int begin[kMaxExperts + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  for (int e = warp; e < experts; e += warps) {
+    int count = 0;
+    for (int base = 0; base < entries; base += 32) {
+      const int i = base + lane;
+      count += __popc(__ballot_sync(0xffffffffu, i < entries && top[i] == e));
+    }
+    if (lane == 0) counts[e] = count;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < experts; ++e) {
+      begin[e] = at;
+      at += (counts[e] + tile_rows - 1) / tile_rows * tile_rows;
+      if (counts_out) counts_out[e] = counts[e];
+    }
+    begin[experts] = at;
+    for (int e = 0; e <= experts; ++e) row_begin[e] = begin[e];
+  }
+  __syncthreads();
+  for (int e = warp; e < experts; e += warps) {
+    int at = begin[e];
+    for (int base = 0; base < entries; base += 32) {
+      const int i = base + lane;
+      const bool mine = i < entries && top[i] == e;
+      const unsigned ballot = __ballot_sync(0xffffffffu, mine);
+      if (mine) rows[i] = at + __popc(ballot & ((1u << lane) - 1u));
+      at += __popc(ballot);
+    }
+  }
+}
+}  // namespace
+
+FLB_API int flb_moe_route_blocks(int tokens) { return (tokens + kRouteThreads - 1) / kRouteThreads; }
+
+// logits fp32 [tokens, experts]; scores fp32 [tokens, k]; top int32 [tokens, k]; prob_partial fp32 [flb_moe_route_blocks(tokens), experts]
+// (every entry written); lse fp32 [tokens] or null.
+FLB_API int flb_moe_route(const float* logits, int tokens, int experts, int k, float* scores, int* top, float* prob_partial, float* lse,
+                          cudaStream_t stream) {
+  if (tokens <= 0 || experts < 1 || experts > kMaxExperts || k < 1 || k > kMaxTopK || k > experts) return FLB_ERR_SHAPE;
+  moe_route_kernel<<<flb_moe_route_blocks(tokens), kRouteThreads, 0, stream>>>(logits, tokens, experts, k, scores, top, prob_partial, lse);
+  FLB_CHECK_LAUNCH();
+  return FLB_OK;
+}
+
+FLB_API int flb_moe_route_bwd(const float* logits, const float* scores, const int* top, const float* dscores, const float* aux_grad,
+                              float z_coeff, int tokens, int experts, int k, float* dlogits, cudaStream_t stream) {
+  if (tokens <= 0 || experts < 1 || experts > kMaxExperts || k < 1 || k > kMaxTopK) return FLB_ERR_SHAPE;
+  moe_route_bwd_kernel<<<flb_moe_route_blocks(tokens), kRouteThreads, 0, stream>>>(logits, scores, top, dscores, aux_grad, z_coeff, tokens, experts, k,
+                                                                                     dlogits);
+  FLB_CHECK_LAUNCH();
+  return FLB_OK;
+}
+
+// top int32 [entries] (entries = tokens * k, token-major); rows int32 [entries]; row_begin int32 [experts + 1]; counts int32 [experts] or null.
+FLB_API int flb_moe_layout(const int* top, int entries, int experts, int tile_rows, int* rows, int* row_begin, int* counts, cudaStream_t stream) {
+  if (entries <= 0 || experts < 1 || experts > kMaxExperts || tile_rows < 1) return FLB_ERR_SHAPE;
+  const int warps = experts < 32 ? experts : 32;
+  moe_layout_kernel<<<1, warps * 32, 0, stream>>>(top, entries, experts, tile_rows, rows, row_begin, counts);
+  FLB_CHECK_LAUNCH();
+  return FLB_OK;
+}

@@ -151,26 +151,40 @@ class MixtureOfExpertMLP(MLP):
             h = h * noise
         logits = self.router(h.float() if h.dtype == torch.float32 or not h.is_cuda else h).float()
         grad_scale = kwargs.get(BlockKwargs.grad_output, 1.0)
-        if c.z_loss_coefficient > 0:
-            z = torch.logsumexp(logits, dim=-1).pow(2).mean()
-            if losses is not None:
-                losses.setdefault("router_z_loss", []).append(z.detach())
-            if training:
-                logits = attach_auxiliary_loss(logits, z, grad_scale * c.z_loss_coefficient)
         k = c.routed_experts_per_token
-        if c.routing == RoutingType.sinkhorn:
-            scores, top_experts = self._sinkhorn_routing(logits, k, training)
+        from fast_llm_b200.ops.moe_routing import native_routing_available, route_topk
+
+        if c.routing == RoutingType.topk and native_routing_available(logits, k):
+            # scores, experts, both auxiliary losses and (in backward) the logit gradient of all of them in two kernels
+            aux_weight = grad_scale * c.auxiliary_loss_coefficient if (training and c.auxiliary_loss_coefficient > 0) else 0.0
+            z_weight = grad_scale * c.z_loss_coefficient if (training and c.z_loss_coefficient > 0) else 0.0
+            scores, top_experts, aux, z = route_topk(logits, k, aux_weight, z_weight)
+            if losses is not None:
+                if c.z_loss_coefficient > 0:
+                    losses.setdefault("router_z_loss", []).append(z)
+                if c.auxiliary_loss_coefficient > 0:
+                    losses.setdefault("load_balancing_loss", []).append(aux)
         else:
-            top_logits, top_experts = torch.topk(logits, k=k, dim=-1)
-            scores = torch.softmax(top_logits, dim=-1, dtype=torch.float32)
-            if c.auxiliary_loss_coefficient > 0 and (training or losses is not None):
-                probs = torch.softmax(logits, dim=-1, dtype=torch.float32)
-                mask = torch.zeros_like(probs).scatter_(1, top_experts, 1.0)
-                aux = c.unshared_experts * (mask.mean(0) * probs.mean(0)).sum()
+            if c.z_loss_coefficient > 0:
+                z = torch.logsumexp(logits, dim=-1).pow(2).mean()
                 if losses is not None:
-                    losses.setdefault("load_balancing_loss", []).append(aux.detach())
+                    losses.setdefault("router_z_loss", []).append(z.detach())
                 if training:
-                    scores = attach_auxiliary_loss(scores, aux, grad_scale * c.auxiliary_loss_coefficient)
+                    logits = attach_auxiliary_loss(logits, z, grad_scale * c.z_loss_coefficient)
+            if c.routing == RoutingType.sinkhorn:
+                scores, top_experts = self._sinkhorn_routing(logits, k, training)
+            else:
+                top_logits, top_experts = torch.topk(logits, k=k, dim=-1)
+                scores = torch.softmax(top_logits, dim=-1, dtype=torch.float32)
+                if c.auxiliary_loss_coefficient > 0 and (training or losses is not None):
+                    probs = torch.softmax(logits, dim=-1, dtype=torch.float32)
+                    mask = torch.zeros_like(probs).scatter_(1, top_experts, 1.0)
+                    aux = c.unshared_experts * (mask.mean(0) * probs.mean(0)).sum()
+                    if losses is not None:
+                        losses.setdefault("load_balancing_loss", []).append(aux.detach())
+                    if training:
+                        scores = attach_auxiliary_loss(scores, aux, grad_scale * c.auxiliary_loss_coefficient)
+        top_experts = top_experts.long() if (self._has_per_expert_scale or c.shared_experts > 0) else top_experts
         if self._has_per_expert_scale:
             scores = scores * self.router_per_expert_scale.float()[top_experts]
         if c.shared_experts > 0:
@@ -263,16 +277,18 @@ class MixtureOfExpertMLP(MLP):
     def _forward_grouped(self, x2, scores, top_experts):
         """All experts in one launch per product: rows sorted by expert and padded to whole tiles on the device (no host
         synchronisation), six grouped GEMMs on the tcgen05 kernel (`ops/grouped_gemm.py`)."""
-        from fast_llm_b200.ops.grouped_gemm import combine, dispatch, expert_rows, grouped_mlp
+        from fast_llm_b200.ops.grouped_gemm import TILE_ROWS, combine, dispatch, grouped_mlp
+        from fast_llm_b200.ops.moe_routing import expert_rows_native
 
         c = self._config
-        rows, row_begin, padded_rows = expert_rows(top_experts, c.experts)
+        rows, row_begin, padded_rows = expert_rows_native(top_experts, c.experts, TILE_ROWS)
         xs = dispatch(x2, rows, padded_rows)
         ys = grouped_mlp(xs, row_begin, self.layer_1.weight, self.layer_2.weight, c.experts, c.gated, c.activation)
         return combine(ys, rows, scores)
 
     def _forward_dropless(self, x2, scores, top_experts, w1s, w2s, group):
         c = self._config
+        top_experts = top_experts.long()
         t, k = top_experts.shape
         flat = top_experts.reshape(-1)
         order = torch.argsort(flat, stable=True)
@@ -291,6 +307,7 @@ class MixtureOfExpertMLP(MLP):
         return out.to(x2.dtype)
 
     def _forward_looped(self, x2, scores, top_experts, w1s, w2s, group):
+        top_experts = top_experts.long()
         out = torch.zeros(x2.shape, dtype=torch.float32, device=x2.device)
         for e in range(self._config.experts):
             weight = (scores * (top_experts == e)).sum(-1)

@@ -29,6 +29,10 @@ _SIGNATURES = {
     "flb_moe_dispatch": [_p, _p, _p, _p, _i, _i, _i, _p],
     "flb_moe_combine": [_p, _p, _p, _p, _i, _i, _i, _p],
     "flb_moe_score_grad": [_p, _p, _p, _p, _i, _i, _i, _p],
+    "flb_moe_route_blocks": [_i],
+    "flb_moe_route": [_p, _i, _i, _i, _p, _p, _p, _p, _p],
+    "flb_moe_route_bwd": [_p, _p, _p, _p, _p, _f, _i, _i, _i, _p, _p],
+    "flb_moe_layout": [_p, _i, _i, _i, _p, _p, _p, _p],
     "flb_grouped_gemm_bf16": [_p, _p, _p, _p, _i, _i, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _p],
     "flb_gemm_bf16_ex": [_p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _p],
     "flb_gemm_error_word": [],

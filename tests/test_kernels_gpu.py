@@ -486,6 +486,40 @@ def test_attention_dropout_fallback_keeps_the_expectation():
     assert _rel_err(mean, exact) < 0.15
 
 
+@pytest.mark.parametrize("tokens,experts,k", [(300, 8, 2), (1000, 64, 8), (257, 4, 1), (8192, 8, 2)])
+def test_moe_routing_kernels_match_the_restatement(tokens, experts, k):
+    """Scores, chosen experts, load-balancing and z-loss values, and the logit gradient (score gradients plus both auxiliary
+    losses) of the routing kernels against the PyTorch restatement."""
+    from fast_llm_b200.ops.moe_routing import route_topk, route_topk_reference
+
+    torch.manual_seed(tokens + experts)
+    logits = torch.randn(tokens, experts, device="cuda") * 2
+    upstream = torch.randn(tokens, k, device="cuda")
+    results = []
+    for fn in (route_topk, route_topk_reference):
+        x = logits.clone().requires_grad_()
+        scores, top, aux, z = fn(x, k, 0.3, 0.05)
+        (scores * upstream).sum().backward()
+        results.append((scores.detach(), top.long(), aux, z, x.grad))
+    (s_a, t_a, aux_a, z_a, g_a), (s_b, t_b, aux_b, z_b, g_b) = results
+    assert torch.equal(t_a, t_b)
+    torch.testing.assert_close(s_a, s_b, rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(aux_a, aux_b, rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(z_a, z_b, rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(g_a, g_b, rtol=2e-3, atol=2e-6)
+
+
+@pytest.mark.parametrize("tokens,experts,k", [(700, 4, 2), (513, 64, 8), (8192, 8, 2), (5, 3, 1)])
+def test_moe_layout_kernel_matches_the_sort_based_layout(tokens, experts, k):
+    from fast_llm_b200.ops.grouped_gemm import TILE_ROWS, expert_rows
+    from fast_llm_b200.ops.moe_routing import expert_rows_native
+
+    top, _ = _expert_layout_case(tokens, k, experts)
+    rows_a, begin_a, upper_a = expert_rows_native(top.to(torch.int32), experts, TILE_ROWS)
+    rows_b, begin_b, upper_b = expert_rows(top, experts)
+    assert torch.equal(rows_a, rows_b) and torch.equal(begin_a, begin_b) and upper_a == upper_b
+
+
 def _expert_layout_case(tokens, k, experts, seed=0):
     from fast_llm_b200.ops.grouped_gemm import expert_layout
 
