@@ -25,6 +25,7 @@
 // global error word, every role leaves its loop, TMEM is released and the kernel returns.  The host reads the error
 // word with flb_gemm_error_word().
 #include "tcgen05.cuh"
+#include "activations.cuh"
 #include <cstdlib>
 #include <mutex>
 
@@ -286,11 +287,64 @@ __device__ __forceinline__ TileInfo grouped_tile(const GroupArgs& g, int tile, i
   return t;
 }
 
+// Epilogue of the first GEMM of a gated MLP: the tile holds gate columns [n0, n0 + 128) in accumulator columns 0..127 and the
+// matching up columns in 128..255.  Per 64-column piece three stores leave the warp's staging buffers: the gate piece of h at
+// column n0 + c, the up piece of h at column half + n0 + c, and act(gate) * up at column n0 + c of the second matrix.  The
+// activation is evaluated on the bf16-rounded values, i.e. on what h holds, so a later recomputation from h reproduces it.
+__device__ __forceinline__ void epilogue_gated(const CUtensorMap* tmap_h, const CUtensorMap* tmap_act, uint8_t* warp_buf, uint32_t taddr, int row0,
+                                               int n0, int half, int M, int act_type, int lane, uint32_t& counter) {
+  auto rounded = [](uint32_t bits) { return __bfloat162float(__float2bfloat16_rn(__uint_as_float(bits))); };
+#pragma unroll 1
+  for (int c = 0; c < 128; c += 64) {
+    if (row0 >= M || n0 + c >= half) break;
+    // three staged pieces per 64 columns (gate, up, activation); the accumulator columns are re-read from tensor memory for
+    // each instead of being kept in registers (a 64-column read costs far less than the store it feeds)
+#pragma unroll
+    for (int which = 0; which < 3; ++which) {
+      uint8_t* buf = warp_buf + (counter & 1u) * 4096;
+      ++counter;
+      if (lane == 0) tma_store_wait_read_1();
+      __syncwarp();
+      uint8_t* row_ptr = buf + lane * 128;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t g[32], u[32];
+        if (which != 1) tmem_ld32(taddr + c + h * 32, g);
+        if (which != 0) tmem_ld32(taddr + 128 + c + h * 32, u);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t pk[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = 8 * j + 2 * e;
+            float a, b;
+            if (which == 0) { a = rounded(g[i]); b = rounded(g[i + 1]); }
+            else if (which == 1) { a = rounded(u[i]); b = rounded(u[i + 1]); }
+            else { a = act_fwd(rounded(g[i]), act_type) * rounded(u[i]); b = act_fwd(rounded(g[i + 1]), act_type) * rounded(u[i + 1]); }
+            __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+            pk[e] = *reinterpret_cast<uint32_t*>(&v);
+          }
+          *reinterpret_cast<uint4*>(row_ptr + (((h * 4 + j) ^ (lane & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        if (which == 0) tma_store_2d(tmap_h, smem_u32(buf), n0 + c, row0);
+        else if (which == 1) tma_store_2d(tmap_h, smem_u32(buf), half + n0 + c, row0);
+        else tma_store_2d(tmap_act, smem_u32(buf), n0 + c, row0);
+        tma_store_commit();
+      }
+    }
+  }
+}
+
 template <bool A_MN, bool B_MN, int EPI, int GROUP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_c, int use_tma_c, void* __restrict__ Cv, int M, int N, int K, long long ldc,
-                 int* __restrict__ err_word, const GroupArgs group) {
+                 int* __restrict__ err_word, const GroupArgs group, const __grid_constant__ CUtensorMap tmap_act, int act_type) {
   using C = PairCfg;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -339,8 +393,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  constexpr bool kGated = (EPI == EPI_GATED_BF16);
+  // gated: N counts the rows of the stacked weight (gate rows, then up rows); a tile pairs 128 gate columns with their 128 up columns
+  const int gated_half = N / 2;
   const int num_m = (M + C::TILE_M - 1) / C::TILE_M;
-  const int num_n = (N + C::TILE_N - 1) / C::TILE_N;
+  const int num_n = kGated ? (gated_half + 127) / 128 : (N + C::TILE_N - 1) / C::TILE_N;
   const int num_tiles = grouped_num_tiles<GROUP>(group, M, N, num_m, num_n);
   const int c_rows = (GROUP == kGroupWgrad) ? group.experts * M : ((GROUP == kGroupRows) ? group.row_begin[group.experts] : M);
   const int cluster_id = blockIdx.x >> 1;
@@ -355,7 +412,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         const TileInfo ti = grouped_tile<GROUP>(group, tile, num_m, num_n, M, K);
         const int m0 = ti.m0 + (int)cta_rank * BLOCK_M;
-        const int n0 = ti.n0 + (int)cta_rank * (C::TILE_N / 2);
+        // this CTA's half of the B tile: the second 128 columns, or (gated) the up rows that belong to the leader's gate rows
+        const int n0 = kGated ? ti.n0 / 2 + (int)cta_rank * gated_half : ti.n0 + (int)cta_rank * (C::TILE_N / 2);
         for (int kb = 0; kb < ti.num_kb; ++kb) {
           if (!mbar_wait<true>(empty_bar(stage), phase ^ 1u, abort_flag, err_word, 11)) { ok = false; break; }
           const uint32_t a_dst = smem_base + stage * C::STAGE_BYTES;
@@ -444,13 +502,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * C::TILE_N;
       const bool empty = ti.num_kb == 0;  // grouped weight gradient of an expert without rows: the tile is zero
       if (empty) {
-        if constexpr (EPI == EPI_STORE_BF16 || EPI == EPI_STORE_F32) {
+        if constexpr (EPI == EPI_STORE_BF16 || EPI == EPI_STORE_F32 || EPI == EPI_GATED_BF16) {
           uint32_t zeros[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) zeros[i] = 0u;
 #pragma unroll 1
           for (int c = 0; c < C::TILE_N / 32; ++c) store_chunk<EPI>(zeros, Cv, row0 + lane, ti.n0 + c * 32, c_rows, N, ldc);
         }
+      } else if constexpr (kGated) {
+        epilogue_gated(&tmap_c, &tmap_act, smem + C::RING_BYTES + q * kEpiWarpBytes, taddr, row0, ti.n0 / 2, gated_half, M, act_type, lane, epi_counter);
       } else if (use_tma_c) {
         epilogue_tma<EPI>(&tmap_c, smem + C::RING_BYTES + q * kEpiWarpBytes, taddr, C::TILE_N, row0, ti.n0, c_rows, N, lane, epi_counter);
       } else {
@@ -588,7 +648,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, 
 template <bool A_MN, bool B_MN, int EPI, int GROUP = kGroupNone>
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, int use_tc, void* C, int M, int N, int K,
                 long long ldc, int max_ctas, DeviceState* st, cudaStream_t stream, GroupArgs group = GroupArgs{nullptr, 0, 0},
-                int tiles_upper_bound = 0) {
+                int tiles_upper_bound = 0, const CUtensorMap* tact = nullptr, int act_type = 0) {
   auto kern = gemm_pair_kernel<A_MN, B_MN, EPI, GROUP>;
   static bool configured = false;
   if (!configured) {
@@ -597,11 +657,12 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
     configured = true;
   }
   int tiles = ((M + PairCfg::TILE_M - 1) / PairCfg::TILE_M) * ((N + PairCfg::TILE_N - 1) / PairCfg::TILE_N);
+  if (EPI == EPI_GATED_BF16) tiles = ((M + PairCfg::TILE_M - 1) / PairCfg::TILE_M) * ((N / 2 + 127) / 128);
   if (GROUP != kGroupNone) tiles = tiles_upper_bound;
   int clusters = st->num_sms / 2;
   if (max_ctas > 1 && max_ctas / 2 < clusters) clusters = max_ctas / 2;
   if (tiles < clusters) clusters = tiles;
-  kern<<<2 * clusters, kNumThreads, PairCfg::SMEM_BYTES, stream>>>(ta, tb, tc, use_tc, C, M, N, K, ldc, st->err_word, group);
+  kern<<<2 * clusters, kNumThreads, PairCfg::SMEM_BYTES, stream>>>(ta, tb, tc, use_tc, C, M, N, K, ldc, st->err_word, group, tact ? *tact : tc, act_type);
   FLB_CHECK_LAUNCH();
   return FLB_OK;
 }
@@ -729,6 +790,25 @@ FLB_API int flb_grouped_gemm_bf16(const void* A, const void* B, void* C, const i
     }
   }
   return FLB_ERR_SHAPE;
+}
+
+// First GEMM of a gated MLP fused with the activation: H[M, 2F] = A[M, K] W^T with W = [gate rows; up rows] stacked ([2F, K],
+// K contiguous), and ACT[M, F] = act(H[:, :F]) * H[:, F:], both bf16, from one pass over the accumulators (CTA-pair kernel).
+// F must be a multiple of 8 (TMA strides); rows and columns past M / F are clipped.  act_type: see activations.cuh.
+FLB_API int flb_gemm_gated_bf16(const void* A, const void* W, void* H, void* ACT, int M, int F, int K, long long lda, long long ldw,
+                                long long ldh, long long ldact, int act_type, cudaStream_t stream) {
+  if (M <= 0 || F <= 0 || K <= 0) return FLB_ERR_SHAPE;
+  if ((lda % 8) || (ldw % 8) || (ldh % 8) || (ldact % 8) || (F % 8)) return FLB_ERR_SHAPE;
+  for (const void* ptr : {A, W, (const void*)H, (const void*)ACT})
+    if (reinterpret_cast<uintptr_t>(ptr) & 15) return FLB_ERR_SHAPE;
+  DeviceState* st = device_state();
+  if (!st) return FLB_ERR_CUDA;
+  CUtensorMap ta, tb, th, tact;
+  if (!make_tmap(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BLOCK_K, BLOCK_M)) return FLB_ERR_TMA;
+  if (!make_tmap(&tb, W, (uint64_t)K, (uint64_t)2 * F, (uint64_t)ldw, BLOCK_K, 128u)) return FLB_ERR_TMA;
+  if (!make_tmap_c(&th, H, (uint64_t)2 * F, (uint64_t)M, (uint64_t)ldh, false)) return FLB_ERR_TMA;
+  if (!make_tmap_c(&tact, ACT, (uint64_t)F, (uint64_t)M, (uint64_t)ldact, false)) return FLB_ERR_TMA;
+  return launch_pair<false, false, EPI_GATED_BF16>(ta, tb, th, 1, H, M, 2 * F, K, ldh, 0, st, stream, GroupArgs{nullptr, 0, 0}, 0, &tact, act_type);
 }
 
 FLB_API int flb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,

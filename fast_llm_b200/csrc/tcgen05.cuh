@@ -13,7 +13,9 @@ constexpr int UMMA_K = 16;
 constexpr int kGroupM = 16;  // tile rasterisation: this many row-blocks share a sweep over N (L2 reuse)
 constexpr long long kSpinLimitCycles = 4000000000ll;  // about 2 s at boost clock
 
-enum Epilogue : int { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ACC_F32 = 2, EPI_ACC_BF16 = 3 };
+// EPI_GATED_BF16: the 256 accumulator columns of a tile are 128 gate columns followed by their 128 up columns; the epilogue
+// writes both halves of h (bf16) and act(gate) * up into a second matrix.
+enum Epilogue : int { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ACC_F32 = 2, EPI_ACC_BF16 = 3, EPI_GATED_BF16 = 4 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

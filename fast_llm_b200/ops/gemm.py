@@ -115,6 +115,29 @@ def matmul_tn(dy: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None
     return out.add_(res) if accumulate else out.copy_(res)
 
 
+def gated_ok(x: torch.Tensor, w1: torch.Tensor) -> bool:
+    """Whether `matmul_nt_gated` can run on these operands (otherwise: `matmul_nt` followed by the activation kernel)."""
+    return _native_ok(x, w1) and x.dim() == 2 and w1.dim() == 2 and w1.shape[0] % 16 == 0 and x.shape[0] > 256
+
+
+def matmul_nt_gated(x: torch.Tensor, w1: torch.Tensor, act_code: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """First layer of a gated MLP and its activation from one kernel: `h = x @ w1.T` with `w1 = [gate rows; up rows]` and
+    `a = act(h[:, :F]) * h[:, F:]`, both bf16.  The activation is applied to the bf16-rounded `h`, so `a` equals what the
+    standalone activation kernel computes from the stored `h`.  Replaces the Triton activation launch that follows the
+    layer-1 GEMM in `fast_llm/functional/triton/mlp.py:207-290`."""
+    m, k = x.shape
+    f = w1.shape[0] // 2
+    h = torch.empty(m, 2 * f, dtype=torch.bfloat16, device=x.device)
+    a = torch.empty(m, f, dtype=torch.bfloat16, device=x.device)
+    _lib.check(
+        _lib.get_lib().flb_gemm_gated_bf16(x.data_ptr(), w1.data_ptr(), h.data_ptr(), a.data_ptr(), m, f, k, x.stride(0),
+                                           w1.stride(0), h.stride(0), a.stride(0), act_code, _lib.stream_ptr()),
+        "flb_gemm_gated_bf16",
+    )
+    _lib.count_launch()
+    return h, a
+
+
 def check_device_errors() -> None:
     """Raise if a GEMM kernel gave up on a bounded wait since the last check (synchronises the device)."""
     word = _lib.get_lib().flb_gemm_error_word()

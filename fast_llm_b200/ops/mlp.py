@@ -16,7 +16,7 @@ import enum
 import torch
 
 from fast_llm_b200.ops.activation import ActivationType, _native as _act_native, act_bwd_native, act_fwd_native, mlp_activation_reference
-from fast_llm_b200.ops.gemm import matmul_nn, matmul_nt
+from fast_llm_b200.ops.gemm import gated_ok, matmul_nn, matmul_nt, matmul_nt_gated
 from fast_llm_b200.ops.linear import bias_grad, weight_grad
 from fast_llm_b200.parallel.ops import gather_op, reduce_op, reduce_scatter_op
 
@@ -62,10 +62,13 @@ class _MLP(torch.autograd.Function):
         shape = x.shape
         x_in = x.reshape(-1, shape[-1])
         x2 = gather_op(x_in, group, 0) if (sequence_parallel and group is not None) else x_in
-        h = matmul_nt(x2, w1)
-        if b1 is not None:
-            h = h + b1
-        a = _act_fwd(h, gated, act)
+        if gated and b1 is None and gated_ok(x2, w1):
+            h, a = matmul_nt_gated(x2, w1, act.code)  # the activation rides in the GEMM's epilogue
+        else:
+            h = matmul_nt(x2, w1)
+            if b1 is not None:
+                h = h + b1
+            a = _act_fwd(h, gated, act)
         y = matmul_nn(a, w2)
         if group is not None:
             y = reduce_scatter_op(y, group, dim=0) if sequence_parallel else reduce_op(y, group)

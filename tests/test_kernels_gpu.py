@@ -235,6 +235,53 @@ def test_mlp_activation(gated, act):
     assert _rel_err(x.grad, xr.grad) < 1e-2
 
 
+@pytest.mark.parametrize("m,f,k", [(512, 1024, 512), (1000, 328, 192), (4096, 3584, 1024), (257, 136, 64)])
+@pytest.mark.parametrize("act", ["silu", "gelu"])
+def test_gated_gemm_epilogue_matches_gemm_then_activation(m, f, k, act):
+    """Layer-1 GEMM with the gated activation in its epilogue: `h` against an fp32 matmul, the activation output against
+    the fp32 activation of the stored (bf16) `h`, and the whole MLP node (which takes this path) against its fp32 restatement."""
+    from fast_llm_b200.ops.activation import ActivationType, mlp_activation_reference
+    from fast_llm_b200.ops.gemm import gated_ok, matmul_nt_gated
+
+    torch.manual_seed(0)
+    a_type = ActivationType(act)
+    x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    w1 = torch.randn(2 * f, k, device="cuda", dtype=torch.bfloat16) / k**0.5
+    assert gated_ok(x, w1)
+    h, a = matmul_nt_gated(x, w1, a_type.code)
+    h_ref = x.float() @ w1.float().t()
+    assert _rel_err(h, h_ref) < 5e-3
+    a_ref = mlp_activation_reference(h.float(), True, a_type)
+    assert _rel_err(a, a_ref) < 5e-3
+    assert _max_err(a, a_ref) <= 2e-2 * a_ref.abs().max().item()
+
+
+def test_mlp_node_with_fused_gated_epilogue_matches_fp32():
+    from fast_llm_b200.ops.activation import ActivationType, mlp_activation_reference
+    from fast_llm_b200.ops.mlp import MLPRecomputeLevel, mlp
+
+    torch.manual_seed(0)
+    m, k, f = 1024, 512, 768
+    x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w1 = (torch.randn(2 * f, k, device="cuda", dtype=torch.bfloat16) / k**0.5).requires_grad_()
+    w2 = (torch.randn(f, k, device="cuda", dtype=torch.bfloat16) / f**0.5).requires_grad_()
+    for level in (MLPRecomputeLevel.none, MLPRecomputeLevel.activation, MLPRecomputeLevel.full):
+        for t in (x, w1, w2):
+            t.grad = None
+            if hasattr(t, "grad_buffer"):
+                del t.grad_buffer
+        y = mlp(x, w1, None, w2, None, gated=True, activation=ActivationType.silu, recompute_level=level)
+        g = torch.randn_like(y)
+        y.backward(g)
+        xr, w1r, w2r = (t.detach().float().requires_grad_() for t in (x, w1, w2))
+        yr = mlp_activation_reference(xr @ w1r.t(), True, ActivationType.silu) @ w2r
+        yr.backward(g.float())
+        assert _rel_err(y, yr) < 1e-2
+        assert _rel_err(x.grad, xr.grad) < 2e-2
+        assert _rel_err(w1.grad, w1r.grad) < 2e-2
+        assert _rel_err(w2.grad, w2r.grad) < 2e-2
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("vocab", [32000, 1003])
 def test_cross_entropy(dtype, vocab):
