@@ -180,10 +180,12 @@ class _HeadLoss(torch.autograd.Function):
     """logits = x W^T -> losses -> d logits -> (dx, dW), all in forward; backward hands dx on."""
 
     @staticmethod
-    def forward(ctx, x, weight, head, kwargs, losses_out, split_index, num_splits):
+    def forward(ctx, x, weight, head, kwargs, losses_out, split_index, num_splits, gathered=False):
         x2 = x.detach()
         group = head._logits_group
-        if head._sequence_parallel_logits_gather and group is not None:
+        if gathered:
+            x_full = x2  # the caller gathered the token shards (and reduce-scatters the gradient)
+        elif head._sequence_parallel_logits_gather and group is not None:
             x_full = gather_op(x2, group, 0)
         else:
             x_full = x2
@@ -203,7 +205,7 @@ class _HeadLoss(torch.autograd.Function):
             if softcap_state is not None:
                 grad_logits = (grad_logits.float() * (1 - softcap_state * softcap_state) * c.logits_scale_factor).to(grad_logits.dtype)
             dx = matmul_nn(grad_logits, weight)
-            if group is not None:
+            if group is not None and not gathered:
                 if head._sequence_parallel_logits_gather:
                     dx = reduce_scatter_op(dx, group, dim=0)
                 elif head._vocab_parallel:
@@ -215,7 +217,7 @@ class _HeadLoss(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_loss):
         (dx,) = ctx.saved_tensors
-        return dx, None, None, None, None, None, None
+        return dx, None, None, None, None, None, None, None
 
 
 class LanguageModelHead(Layer):
@@ -315,8 +317,15 @@ class LanguageModelHead(Layer):
             total = _HeadLoss.apply(hidden, self.output_weights, self, kwargs, loss_dict, 0, 1)
         else:
             total = None
+            # Vocab-parallel logits of token shards: gather the (small) hidden states once, so that chunk i holds the same
+            # contiguous tokens as chunk i of the labels; the gather's backward reduce-scatters the summed chunk gradients.
+            gathered = self._sequence_parallel_logits_gather and self._logits_group is not None
+            if gathered:
+                from fast_llm_b200.parallel.ops import gather
+
+                hidden = gather(hidden, self._logits_group, 0, reduce_grads=True)
             for i, chunk in enumerate(hidden.chunk(splits, dim=0)):
-                part = _HeadLoss.apply(chunk, self.output_weights, self, kwargs, loss_dict, i, splits)
+                part = _HeadLoss.apply(chunk, self.output_weights, self, kwargs, loss_dict, i, splits, gathered)
                 total = part if total is None else total + part
         return total
 

@@ -44,6 +44,22 @@ LAYOUTS = {
                  {("schedule", "breadth_first_micro_batches"): 2, ("model", "base_model", "tied_embedding_weight"): True}),
     "dp2_stp2": (4, {("model", "distributed", "tensor_parallel"): 2, ("model", "distributed", "sequence_tensor_parallel"): True},
                  {("schedule", "depth_first_micro_batches"): 2}),
+    # combinations (the reference's `tests/utils/distributed_configs.py:212-463` runs the same families)
+    "dp2_z2_df4": (2, {("model", "multi_stage", "zero_stage"): 2, ("schedule", "depth_first_micro_batches"): 4},
+                   {("schedule", "depth_first_micro_batches"): 8}),
+    "stp2_ce4": (2, {("model", "distributed", "tensor_parallel"): 2, ("model", "distributed", "sequence_tensor_parallel"): True,
+                     ("model", "base_model", "head", "cross_entropy_splits"): 4},
+                 {("model", "base_model", "head", "cross_entropy_splits"): 4}),
+    "sdp2_stp2": (4, {("model", "distributed", "sequence_data_parallel"): 2, ("model", "distributed", "tensor_parallel"): 2,
+                      ("model", "distributed", "sequence_tensor_parallel"): True}, {}),
+    "pp2_ms4": (2, {("model", "distributed", "pipeline_parallel"): 2, ("schedule", "breadth_first_micro_batches"): 2,
+                    ("schedule", "micro_batch_splits"): 4},
+                {("schedule", "breadth_first_micro_batches"): 2, ("schedule", "micro_batch_splits"): 4}),
+    "tp2_pp2": (4, {("model", "distributed", "tensor_parallel"): 2, ("model", "distributed", "pipeline_parallel"): 2,
+                    ("schedule", "breadth_first_micro_batches"): 2}, {("schedule", "breadth_first_micro_batches"): 2}),
+    "dp2_stp2_pp2": (8, {("model", "distributed", "tensor_parallel"): 2, ("model", "distributed", "sequence_tensor_parallel"): True,
+                         ("model", "distributed", "pipeline_parallel"): 2, ("schedule", "breadth_first_micro_batches"): 2},
+                     {("schedule", "breadth_first_micro_batches"): 2, ("schedule", "depth_first_micro_batches"): 2}),
 }
 
 
