@@ -95,7 +95,8 @@ class DistributedCheckpointHandler(CheckpointHandler):
                         shards = {name: model.get_shard(name)[sl] for name in shard_names}
                         for _, loaded_fsdp, lsl in replica_ranges:
                             loaded_shards = {name: saved[name][lsl] for name in shard_names}
-                            counts = fsdp.copy_shard_overlaps(loaded_fsdp, shards, loaded_shards)
+                            counts = fsdp.copy_shard_overlaps(loaded_fsdp, shards, loaded_shards,
+                                                              skip_replicated=replica_config.distributed.tensor_rank != 0)
                             for pname, count in counts.items():
                                 context.mark_as_loaded(count * len(shard_names), (pname, "all"))
         return loaded_metadata.metadata

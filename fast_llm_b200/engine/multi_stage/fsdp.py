@@ -306,10 +306,12 @@ class FSDP:
         return self._shard_pad
 
     def copy_shard_overlaps(self, loaded_fsdp: "FSDP", shards: dict[str, torch.Tensor], loaded_shards: dict[str, torch.Tensor],
-                            loaded_rank_in_data: int | None = None) -> dict[str, int]:
+                            loaded_rank_in_data: int | None = None, skip_replicated: bool = False) -> dict[str, int]:
         """Copy into `shards` whatever part of each of our parameters is present in `loaded_shards`, the shards of
         one rank of a model saved under another layout (`loaded_fsdp` describes that rank).  Handles different
         data-parallel sizes (different shard boundaries) and different tensor-parallel splits (via index maps).
+        `skip_replicated`: the loaded rank is not the first of its tensor group, so its copies of the parameters that are not
+        split over that group repeat what the first rank holds and are left out (each element is then loaded exactly once).
         Returns elements copied per parameter, for load verification."""
         counter: dict[str, int] = {}
         device = next(iter(shards.values())).device if shards else "cpu"
@@ -317,6 +319,8 @@ class FSDP:
             if name not in loaded_fsdp:
                 continue
             loaded_meta = loaded_fsdp.get_parameter_meta(name)
+            if skip_replicated and not loaded_meta.is_tensor_parallel:
+                continue
             begin, end = self.parameter_range_in_shard(name)
             lbegin, lend = loaded_fsdp.parameter_range_in_shard(name)
             if end <= begin or lend <= lbegin:

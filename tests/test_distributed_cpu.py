@@ -153,3 +153,69 @@ def test_tensor_logs_of_a_parallel_layout_match_the_single_process_run(name, wor
         assert got["shape"] == expected["shape"], got["name"]
         for key in ("mu", "std", "min", "max"):
             assert got[key] == pytest.approx(expected[key], rel=2e-4, abs=2e-6), (name, got["name"], key)
+
+
+# ---- save in one layout, load in another (reference: `tests/utils/save_load_configs.py:76-157`, `tests/models/test_checkpoint.py`)
+_SHARDS = ("weights", "exp_avgs", "exp_avgs_sq")
+_CROSS_LAYOUTS = {
+    "dp2": (2, {}),
+    "tp2": (2, {("distributed", "tensor_parallel"): 2}),
+    "stp2": (2, {("distributed", "tensor_parallel"): 2, ("distributed", "sequence_tensor_parallel"): True}),
+    "pp2": (2, {("distributed", "pipeline_parallel"): 2}),
+    "dp2_z3": (2, {("multi_stage", "zero_stage"): 3}),
+}
+
+
+def _global_state(model):
+    return {f"{shard}/{name}": tensor.clone().numpy() for name, shard, tensor in model.get_state_tensor_iterator(_SHARDS)}
+
+
+def _save_rank(rank, world_size, model_updates, path):
+    from fast_llm_b200.engine.checkpoint.config import CheckpointSaveConfig
+
+    updates = {("model", *key): value for key, value in model_updates.items()}
+    if ("model", "distributed", "pipeline_parallel") in updates:
+        updates[("schedule", "breadth_first_micro_batches")] = 2
+    updates.update({("model", "distributed", "world_size"): world_size, ("model", "distributed", "rank"): rank,
+                    ("model", "distributed", "local_world_size"): world_size, ("model", "distributed", "backend"): "gloo",
+                    ("model", "distributed", "reproducible_init"): True})
+    trainer, distributed = build_trainer(tiny_trainer_config(updates))
+    train_steps(trainer, 2)  # two optimizer steps: both Adam moments are non-trivial
+    trainer.multi_stage.save_checkpoint(CheckpointSaveConfig(path=path, format="distributed", optimizer_state=True))
+    state = _global_state(trainer.multi_stage)
+    distributed.shutdown()
+    return state
+
+
+def _load_rank(rank, world_size, model_updates, path):
+    from fast_llm_b200.engine.checkpoint.config import CheckpointLoadConfig
+    from fast_llm_b200.models.gpt.model import GPTModel
+
+    updates = {("distributed", "tensor_parallel"): 1, ("distributed", "sequence_tensor_parallel"): False,
+               ("distributed", "pipeline_parallel"): 1, ("multi_stage", "zero_stage"): 1, **model_updates,
+               ("distributed", "world_size"): world_size, ("distributed", "rank"): rank, ("distributed", "local_world_size"): world_size,
+               ("distributed", "backend"): "gloo", ("distributed", "use_cuda"): False}
+    model = GPTModel.from_pretrained(CheckpointLoadConfig(path=path, format="distributed", optimizer_state=True), updates, use_cpu=True)
+    state = _global_state(model)
+    model.distributed.shutdown()
+    return state
+
+
+@pytest.mark.parametrize("saved,loaded", [("dp2", "tp2"), ("tp2", "pp2"), ("stp2", "dp2_z3"), ("pp2", "stp2"), ("dp2_z3", "pp2")])
+def test_checkpoint_saved_in_one_layout_loads_in_another(saved, loaded, tmp_path):
+    """Weights and both Adam moments written by the ranks of one layout are read back bit for bit by the ranks of another
+    (every rank's shard is assembled from the overlapping pieces of the saved shards)."""
+    save_world, save_updates = _CROSS_LAYOUTS[saved]
+    load_world, load_updates = _CROSS_LAYOUTS[loaded]
+    path = str(tmp_path / "ckpt")
+    written = {}
+    for state in run_distributed(_save_rank, save_world, save_updates, path):
+        written.update(state)
+    assert any(k.startswith("exp_avgs_sq/") and v.any() for k, v in written.items())
+    seen = set()
+    for state in run_distributed(_load_rank, load_world, load_updates, path):
+        for key, value in state.items():
+            reference_key = key if key in written else key.replace("head.output_weights", "embeddings.word_embeddings_weight")
+            assert (value == written[reference_key]).all(), f"{saved}->{loaded}: {key}"
+            seen.add(reference_key)
+    assert seen == set(written)
