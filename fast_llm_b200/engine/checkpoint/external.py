@@ -185,14 +185,134 @@ class ExternalStateDictCheckpointHandler(StateDictCheckpointHandler):
         return [(n, "weights", t) for n, t in zip(converter.fast_llm_name, imported, strict=True)]
 
 
+class TrackedConfig(dict):
+    """An external configuration dictionary that remembers which of its keys a converter looked at (nested dictionaries
+    included), so that the fields a format silently dropped can be named after the import."""
+
+    def __init__(self, data: dict, prefix: str = "", root: "TrackedConfig | None" = None):
+        super().__init__(data)
+        self._prefix = prefix
+        self._root = self if root is None else root
+        if root is None:
+            self._read: set[str] = set()
+
+    def _touch(self, key):
+        self._root._read.add(self._prefix + str(key))
+
+    def _wrap(self, key, value):
+        return TrackedConfig(value, f"{self._prefix}{key}.", self._root) if isinstance(value, dict) and not isinstance(value, TrackedConfig) else value
+
+    def __getitem__(self, key):
+        self._touch(key)
+        return self._wrap(key, super().__getitem__(key))
+
+    def get(self, key, default=None):
+        self._touch(key)
+        return self._wrap(key, super().get(key, default))
+
+    def __contains__(self, key):
+        self._touch(key)
+        return super().__contains__(key)
+
+    def unread(self) -> list[str]:
+        """Leaf keys never read, a nested dictionary counting as read when it was fetched whole and not looked into."""
+        out = []
+
+        def walk(data: dict, prefix: str):
+            for key, value in dict.items(data):
+                name = prefix + str(key)
+                if isinstance(value, dict) and value and any(r.startswith(name + ".") for r in self._root._read):
+                    walk(value, name + ".")
+                elif name not in self._root._read:
+                    out.append(name)
+
+        walk(self, "")
+        return out
+
+
+def effective_architecture(config) -> dict:
+    """The architecture of a configuration in a form where two spellings of the same model compare equal: every field hinted
+    `architecture`, the dynamic type of every sub-configuration (a rotary or mixer of another type is another model), and
+    for each linear layer whether it really has a bias (its own `bias.enabled`, else the owner's `add_linear_biases`)."""
+    from fast_llm_b200.config.core import Config, FieldHint, _serialize
+
+    out = {}
+    if type(config)._dynamic_type_names:
+        out["type"] = next(iter(type(config)._dynamic_type_names.values()))
+    default_bias = getattr(config, "add_linear_biases", None)
+    for name, field in config.fields().items():
+        value = getattr(config, name)
+        if isinstance(value, Config):
+            bias = getattr(value, "bias", None)
+            if default_bias is not None and bias is not None and hasattr(bias, "enabled"):
+                out[f"{name}.has_bias"] = bool(default_bias if bias.enabled is None else bias.enabled)
+            sub = effective_architecture(value)
+            if sub:
+                out[name] = sub
+        elif isinstance(value, dict) and any(isinstance(v, Config) for v in value.values()):
+            out[name] = {k: effective_architecture(v) for k, v in value.items()}
+        elif isinstance(value, (list, tuple)) and any(isinstance(v, Config) for v in value):
+            out[name] = [effective_architecture(v) for v in value]
+        elif field.hint == FieldHint.architecture and name != "add_linear_biases":
+            out[name] = _serialize(value, None, True, True)
+    return out
+
+
+# keys of a Hugging Face `config.json` that describe the file or the runtime, not the architecture
+_BOOKKEEPING_KEYS = frozenset({
+    "architectures", "model_type", "torch_dtype", "dtype", "transformers_version", "_name_or_path", "auto_map", "use_cache",
+    "bos_token_id", "eos_token_id", "pad_token_id", "initializer_range", "pretraining_tp", "id2label", "label2id", "return_dict",
+    "output_attentions", "output_hidden_states", "is_decoder", "is_encoder_decoder", "chunk_size_feed_forward", "problem_type",
+    "tokenizer_class", "torchscript", "use_bfloat16", "tf_legacy_loss", "pruned_heads", "add_cross_attention", "tie_encoder_decoder",
+    "cross_attention_hidden_size", "finetuning_task", "task_specific_params", "prefix", "sep_token_id", "decoder_start_token_id",
+    "layer_types", "max_window_layers",
+})
+
+
 class HuggingfaceStateDictCheckpointHandler(ExternalStateDictCheckpointHandler):
-    """Hugging Face layout: `config.json`, `model_{i}.safetensors`, `model.safetensors.index.json`."""
+    """Hugging Face layout: `config.json`, `model_{i}.safetensors`, `model.safetensors.index.json`.
+
+    Two coverage checks surround the format's hand-written `export_config` / `import_config` (the declarative converters of
+    `fast_llm/engine/checkpoint/external.py:83-540` enforce the same two properties field by field):
+
+      * export: the exported dictionary is imported again and every *architecture* field of the result must equal the
+        model's - a field the format has no place for fails the export instead of being dropped (`check_export_coverage`);
+      * import: every key of the external `config.json` must have been read by the converter or be listed as
+        bookkeeping / explicitly ignored (`ignored_import_keys`); the rest is reported (`check_import_coverage`), and
+        raises under `strict_import`.
+    """
+
+    ignored_import_keys: typing.ClassVar[frozenset[str]] = frozenset()
+    strict_import: typing.ClassVar[bool] = False
+
+    @classmethod
+    def check_import_coverage(cls, hf_config: dict) -> tuple[dict, list[str]]:
+        """(imported base-model dictionary, external keys nobody claimed)."""
+        tracked = TrackedConfig(hf_config)
+        base_model = cls.import_config(tracked)
+        ignored = _BOOKKEEPING_KEYS | cls.ignored_import_keys
+        unclaimed = [key for key in tracked.unread() if key.split(".")[0] not in ignored and key not in ignored]
+        return _plain(base_model), unclaimed
+
+    @classmethod
+    def check_export_coverage(cls, base_model_config, hf_config: dict) -> list[str]:
+        """Architecture fields of `base_model_config` that do not survive export followed by import."""
+        from fast_llm_b200.utils import compare_nested
+
+        model_class = cls.get_model_config_class()
+        again = model_class.from_dict({"base_model": cls.import_config(json.loads(json.dumps(_jsonable(hf_config))))}).base_model
+        again.validate()
+        return compare_nested(effective_architecture(base_model_config), effective_architecture(again))
 
     @classmethod
     def save_metadata(cls, config: CheckpointSaveMetadataConfig, metadata: CheckpointMetadata, index: dict | None = None) -> None:
         path = pathlib.Path(config.path)
         path.mkdir(parents=True, exist_ok=True)
         hf_config = cls.export_config(metadata.config.base_model)
+        lost = cls.check_export_coverage(metadata.config.base_model, hf_config)
+        if lost:
+            raise ValueError(f"Format {cls.format.name!r} cannot represent this model; architecture fields that would be lost or changed:\n  "
+                             + "\n  ".join(lost[:40]))
         hf_config.setdefault("architectures", [cls.architecture] if cls.architecture else [])
         # the dtype the tensors are written in: the cast requested for this save, else the fp32 master weights
         data_type = getattr(config, "data_type", None)
@@ -219,7 +339,12 @@ class HuggingfaceStateDictCheckpointHandler(ExternalStateDictCheckpointHandler):
         from fast_llm_b200.engine.multi_stage.config import FastLLMModelConfig
 
         model_class = cls.get_model_config_class()
-        base_model = cls.import_config(hf_config)
+        base_model, unclaimed = cls.check_import_coverage(hf_config)
+        if unclaimed:
+            message = f"Format {cls.format.name!r}: fields of config.json that no converter claimed: {unclaimed}"
+            if cls.strict_import:
+                raise ValueError(message)
+            logger.warning(message)
         extra = {}
         index_path = path / "model.safetensors.index.json"
         if index_path.exists():
@@ -243,6 +368,15 @@ class HuggingfaceStateDictCheckpointHandler(ExternalStateDictCheckpointHandler):
 
                 return {name: single for name, _ in _iter_file(path / single)}
         raise FileNotFoundError(f"No weights found in {path}")
+
+
+def _plain(obj):
+    """Nested `TrackedConfig`s back to plain dictionaries."""
+    if isinstance(obj, dict):
+        return {k: _plain(v) for k, v in dict.items(obj)}
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(_plain(v) for v in obj)
+    return obj
 
 
 def _jsonable(obj):

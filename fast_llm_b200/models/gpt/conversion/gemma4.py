@@ -130,10 +130,12 @@ class Gemma4HuggingfaceCheckpointHandler(HuggingfaceStateDictCheckpointHandler):
         eps = h["rms_norm_eps"]
         if sliding:
             rope = h["rope_parameters"][_SLIDING]
+            Assert.eq(rope.get("rope_type", "default"), "default")
             out = {"rotary": {"type": "default", "theta": rope["rope_theta"]}, "head_size": h["head_dim"], "head_groups": h["num_key_value_heads"],
                    "window_size": h["sliding_window"]}
         else:
             rope = h["rope_parameters"][_FULL]
+            Assert.eq(rope.get("rope_type", "proportional"), "proportional")
             groups = h.get("num_global_key_value_heads")
             out = {"rotary": {"type": "proportional", "theta": rope["rope_theta"], "partial_rotary_factor": rope["partial_rotary_factor"]},
                    "head_size": h["global_head_dim"], "head_groups": h["num_key_value_heads"] if groups is None else groups}
@@ -168,6 +170,12 @@ class Gemma4HuggingfaceCheckpointHandler(HuggingfaceStateDictCheckpointHandler):
     def import_config(cls, h: dict) -> dict:
         if h.get("use_bidirectional_attention") == "all":
             raise NotImplementedError("Gemma 4 with bidirectional text attention is not supported")
+        # features of the Hugging Face model that have no counterpart here: a checkpoint that uses one is refused, not
+        # loaded as a different model
+        for key, off in (("attention_bias", (False, None)), ("hidden_size_per_layer_input", (0, None)), ("num_kv_shared_layers", (0, None)),
+                         ("use_double_wide_mlp", (False, None))):
+            if h.get(key) not in off:
+                raise NotImplementedError(f"Gemma 4 checkpoints with {key}={h.get(key)!r} are not supported")
         layer_types = list(h["layer_types"])
         head = {"normalization": {"type": "rms_norm", "epsilon": h["rms_norm_eps"]}}
         if h.get("final_logit_softcapping") is not None:

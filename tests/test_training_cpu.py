@@ -247,7 +247,11 @@ def _round_trip(tmp_path, base_model, format_name):
         runner.setup()
         runners.append(runner)
     torch.testing.assert_close(runners[0].forward_tokens(tokens), runners[1].forward_tokens(tokens), rtol=1e-4, atol=1e-4)
-    return json.loads((path / "config.json").read_text())
+    exported = json.loads((path / "config.json").read_text())
+    # every field the format writes is read back by its own importer (or listed as ignored): nothing is dropped in silence
+    handler = type(trainer.multi_stage.config).get_checkpoint_handler_class(format_name)
+    assert handler.check_import_coverage(exported)[1] == [], format_name
+    return exported
 
 
 def test_mtp_llama_and_apriel_hybrid_round_trip(tmp_path):
@@ -570,3 +574,34 @@ def test_safe_load_names_the_parameter_that_was_not_loaded(tmp_path):
                         continue
                     shard[begin:end].zero_()
                     context.mark_as_loaded(end - begin, (name, "weights"))
+
+
+@pytest.mark.parametrize("format_name", ["llama", "mistral", "mtp_llama", "apriel_hybrid_ssm", "apriel2_text"])
+def test_export_refuses_what_the_format_cannot_represent(tmp_path, format_name):
+    """A model whose architecture has no place in the external format fails the export with the fields named, instead of
+    writing a checkpoint that loads as a different model; an unknown key of a foreign `config.json` is reported on import."""
+    import copy
+
+    from fast_llm_b200.engine.checkpoint.config import CheckpointSaveConfig
+    from tests.common import TINY_BASE_MODEL
+
+    base = copy.deepcopy(TINY_BASE_MODEL)
+    base["decoder"]["block"]["mixer"]["softmax_scale_power"] = 0.75  # no Hugging Face format carries this
+    trainer, _ = build_trainer(tiny_trainer_config({("model", "base_model"): base}))
+    with pytest.raises((ValueError, AssertionError), match="softmax_scale_power|cannot represent|needs|Mismatch|Assert"):
+        trainer.multi_stage.save_checkpoint(CheckpointSaveConfig(path=tmp_path / "bad", format=format_name))
+
+
+def test_import_reports_fields_nobody_claimed(tmp_path):
+    from fast_llm_b200.engine.checkpoint.config import CheckpointSaveConfig
+    from fast_llm_b200.models.gpt.config import GPTModelConfig
+
+    trainer, _ = build_trainer(tiny_trainer_config())
+    trainer.multi_stage.save_checkpoint(CheckpointSaveConfig(path=tmp_path / "hf", format="llama"))
+    exported = json.loads((tmp_path / "hf" / "config.json").read_text())
+    handler = GPTModelConfig.get_checkpoint_handler_class("llama")
+    assert handler.check_import_coverage(exported)[1] == []
+    exported["mystery_gate"] = 3
+    exported["rope_scaling"] = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                "original_max_position_embeddings": 8192, "mystery_inner": 1}
+    assert sorted(handler.check_import_coverage(exported)[1]) == ["mystery_gate", "rope_scaling.mystery_inner"]
