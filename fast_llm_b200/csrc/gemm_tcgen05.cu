@@ -26,6 +26,7 @@
 // word with flb_gemm_error_word().
 #include "tcgen05.cuh"
 #include "activations.cuh"
+#include <vector>
 #include <cstdlib>
 #include <mutex>
 
@@ -558,41 +559,80 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 2-D bf16 tensor map over a matrix whose contiguous dimension has `inner` elements.
-bool make_tmap(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld_elems, uint32_t box_inner,
-               uint32_t box_outer) {
+// Tensor maps are pure functions of (address, extents, stride, box, kind) and a training step asks for the same few hundred
+// of them again and again (weights, gradient buffers and the allocator's recycled activation blocks): each host thread keeps
+// a direct-mapped table of the ones it built, so the driver's encoder runs only on a miss.
+struct TmapKey {
+  const void* ptr;
+  uint64_t inner, outer, ld;
+  uint32_t box_inner, box_outer, kind;
+  bool operator==(const TmapKey& o) const {
+    return ptr == o.ptr && inner == o.inner && outer == o.outer && ld == o.ld && box_inner == o.box_inner && box_outer == o.box_outer && kind == o.kind;
+  }
+};
+struct TmapEntry {
+  CUtensorMap map;
+  TmapKey key;
+  bool valid = false;
+};
+constexpr size_t kTmapCacheSize = 2048;  // power of two
+struct TmapCounters {
+  unsigned long long hits = 0, misses = 0;
+};
+TmapCounters& tmap_counters() {
+  thread_local TmapCounters c;
+  return c;
+}
+
+bool encode_tmap(CUtensorMap* map, const TmapKey& k) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return false;
-  cuuint64_t dims[2] = {inner, outer};
-  cuuint64_t strides[1] = {ld_elems * 2};
-  cuuint32_t box[2] = {box_inner, box_outer};
+  const bool f32 = k.kind == 2;
+  cuuint64_t dims[2] = {k.inner, k.outer};
+  cuuint64_t strides[1] = {k.ld * (f32 ? 4 : 2)};
+  cuuint32_t box[2] = {k.box_inner, k.box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = CUDA_SUCCESS;
   for (int attempt = 0; attempt < 2; ++attempt) {
-    r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    r = enc(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(k.ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            k.kind == 0 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_ERROR_INVALID_CONTEXT) break;
     cudaFree(nullptr);  // a thread that made no runtime call yet has no current context: bind the primary one
   }
   return r == CUDA_SUCCESS;
 }
 
+bool cached_tmap(CUtensorMap* map, const TmapKey& k) {
+  thread_local std::vector<TmapEntry> cache(kTmapCacheSize);
+  uint64_t h = reinterpret_cast<uintptr_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+  h ^= (k.inner * 0xC2B2AE3D27D4EB4Full) ^ (k.outer * 0x165667B19E3779F9ull) ^ (k.ld << 17) ^ ((uint64_t)k.box_outer << 40) ^ ((uint64_t)k.box_inner << 52) ^ k.kind;
+  TmapEntry& e = cache[(h >> 20) & (kTmapCacheSize - 1)];
+  if (e.valid && e.key == k) {
+    ++tmap_counters().hits;
+    *map = e.map;
+    return true;
+  }
+  ++tmap_counters().misses;
+  if (!encode_tmap(&e.map, k)) {
+    e.valid = false;
+    return false;
+  }
+  e.key = k;
+  e.valid = true;
+  *map = e.map;
+  return true;
+}
+
+// 2-D bf16 operand map with the given box and a 128-byte swizzle.
+bool make_tmap(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld_elems, uint32_t box_inner,
+               uint32_t box_outer) {
+  return cached_tmap(map, TmapKey{ptr, inner, outer, ld_elems, box_inner, box_outer, 0u});
+}
+
 // 2-D tensor map over the output: boxes of 32 rows x 128 bytes (64 bf16 or 32 fp32 columns), 128-byte swizzle.
 bool make_tmap_c(CUtensorMap* map, void* ptr, uint64_t cols, uint64_t rows, uint64_t ld_elems, bool f32) {
-  EncodeTiledFn enc = get_encode_fn();
-  if (!enc) return false;
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {ld_elems * (f32 ? 4 : 2)};
-  cuuint32_t box[2] = {f32 ? 32u : 64u, 32u};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = CUDA_SUCCESS;
-  for (int attempt = 0; attempt < 2; ++attempt) {
-    r = enc(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_ERROR_INVALID_CONTEXT) break;
-    cudaFree(nullptr);
-  }
-  return r == CUDA_SUCCESS;
+  return cached_tmap(map, TmapKey{ptr, cols, rows, ld_elems, f32 ? 32u : 64u, 32u, f32 ? 2u : 1u});
 }
 
 // FLB_GEMM_EPILOGUE=direct keeps the register -> global epilogue (for comparisons); default is the TMA epilogue.
@@ -815,6 +855,12 @@ FLB_API int flb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, i
                           long long ldc, int a_mn_major, int b_mn_major, int epilogue, int block_n, int max_ctas,
                           cudaStream_t stream) {
   return flb_gemm_bf16_ex(A, B, C, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, epilogue, block_n, max_ctas, 0, stream);
+}
+
+// Hits and misses of the calling thread's tensor-map table since the thread started (out[0], out[1]).
+FLB_API void flb_gemm_tmap_cache_stats(unsigned long long* out) {
+  out[0] = tmap_counters().hits;
+  out[1] = tmap_counters().misses;
 }
 
 FLB_API int flb_gemm_error_word() {

@@ -13,35 +13,56 @@ namespace {
 using namespace flb;
 constexpr int kThreads = 256;
 
+// Both kernels are persistent: a CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ... and issues the loads of its NEXT row
+// (kept as packed bf16 in registers) before it reduces and stores the current one, so every resident CTA always has a row of
+// reads in flight and the block-wide reduction and the stores of one row hide under the DRAM latency of the next.
 template <int VPT, bool LAYER_NORM>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, VPT <= 2 ? 4 : (VPT == 4 ? 2 : 1))
 norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
                 const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b,
                 __nv_bfloat16* __restrict__ res_out, __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out,
                 float* __restrict__ mean_out, int rows, int cols, float eps, int zero_centered) {
   __shared__ float scratch[32];
   const int nvec = cols >> 3;
+  bf16x8 nx[VPT], nd[VPT];
+  auto fetch = [&](int row) {
+    const long long base = (long long)row * cols;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int vec = threadIdx.x + i * kThreads;
+      if (vec < nvec) {
+        nx[i] = *reinterpret_cast<const bf16x8*>(x + base + vec * 8);
+        if (delta) nd[i] = *reinterpret_cast<const bf16x8*>(delta + base + vec * 8);
+      }
+    }
+  };
+  if ((int)blockIdx.x < rows) fetch(blockIdx.x);
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const long long base = (long long)row * cols;
     float v[VPT][8];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int vec = threadIdx.x + i * kThreads;
+      if (vec < nvec) {
+        unpack8(nx[i], v[i]);
+        if (delta) {
+          float d[8];
+          unpack8(nd[i], d);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] += d[j];
+        }
+      }
+    }
+    if (row + (int)gridDim.x < rows) fetch(row + gridDim.x);
     float s = 0.f, ss = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int vec = threadIdx.x + i * kThreads;
       if (vec < nvec) {
-        bf16x8 p = *reinterpret_cast<const bf16x8*>(x + base + vec * 8);
-        unpack8(p, v[i]);
-        if (delta) {
-          float d[8];
-          bf16x8 q = *reinterpret_cast<const bf16x8*>(delta + base + vec * 8);
-          unpack8(q, d);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v[i][j] += d[j];
-          if (res_out) {
-            bf16x8 o = pack8(v[i]);
-            *reinterpret_cast<bf16x8*>(res_out + base + vec * 8) = o;
-            unpack8(o, v[i]);  // normalise the rounded residual: backward sees exactly this tensor
-          }
+        if (delta && res_out) {
+          bf16x8 o = pack8(v[i]);
+          *reinterpret_cast<bf16x8*>(res_out + base + vec * 8) = o;
+          unpack8(o, v[i]);  // normalise the rounded residual: backward sees exactly this tensor
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -98,8 +119,10 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   }
 }
 
+// The row is held as packed bf16 (x, dy) and unpacked once per pass instead of living in fp32 registers between the passes:
+// half the registers, so three CTAs stay resident per SM beside the prefetched next row.
 template <int VPT, bool LAYER_NORM>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, VPT <= 2 ? 3 : 1)
 norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                 const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
                 const float* __restrict__ mean_in, const __nv_bfloat16* __restrict__ dres,
@@ -113,29 +136,53 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
 #pragma unroll
     for (int j = 0; j < 8; ++j) dw_acc[i][j] = db_acc[i][j] = 0.f;
 
+  bf16x8 nx[VPT], ny[VPT];
+  float n_rstd = 0.f, n_mean = 0.f;
+  auto fetch = [&](int row) {
+    const long long base = (long long)row * cols;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int vec = threadIdx.x + i * kThreads;
+      if (vec < nvec) {
+        nx[i] = *reinterpret_cast<const bf16x8*>(x + base + vec * 8);
+        ny[i] = *reinterpret_cast<const bf16x8*>(dy + base + vec * 8);
+      }
+    }
+    n_rstd = rstd_in[row];
+    if (LAYER_NORM) n_mean = mean_in[row];
+  };
+  if ((int)blockIdx.x < rows) fetch(blockIdx.x);
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const long long base = (long long)row * cols;
-    const float rstd = rstd_in[row];
-    const float mean = LAYER_NORM ? mean_in[row] : 0.f;
-    float xh[VPT][8], g[VPT][8];
+    const float rstd = n_rstd;
+    const float mean = LAYER_NORM ? n_mean : 0.f;
+    bf16x8 cx[VPT], cy[VPT], cr[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      cx[i] = nx[i];
+      cy[i] = ny[i];
+      const int vec = threadIdx.x + i * kThreads;
+      if (dres && vec < nvec) cr[i] = *reinterpret_cast<const bf16x8*>(dres + base + vec * 8);  // needed only after the reduction
+    }
+    if (row + (int)gridDim.x < rows) fetch(row + gridDim.x);
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int vec = threadIdx.x + i * kThreads;
       if (vec < nvec) {
         float xv[8], dyv[8], wf[8];
-        unpack8(*reinterpret_cast<const bf16x8*>(x + base + vec * 8), xv);
-        unpack8(*reinterpret_cast<const bf16x8*>(dy + base + vec * 8), dyv);
+        unpack8(cx[i], xv);
+        unpack8(cy[i], dyv);
         if (w) unpack8(*reinterpret_cast<const bf16x8*>(w + vec * 8), wf);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          xh[i][j] = (xv[j] - mean) * rstd;
+          const float xh = (xv[j] - mean) * rstd;
           const float wj = w ? (zero_centered ? wf[j] + 1.f : wf[j]) : 1.f;
-          g[i][j] = dyv[j] * wj;
-          dw_acc[i][j] += dyv[j] * xh[i][j];
+          const float g = dyv[j] * wj;
+          dw_acc[i][j] += dyv[j] * xh;
           db_acc[i][j] += dyv[j];
-          s1 += g[i][j] * xh[i][j];
-          s2 += g[i][j];
+          s1 += g * xh;
+          s2 += g;
         }
       }
     }
@@ -145,12 +192,19 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
     for (int i = 0; i < VPT; ++i) {
       const int vec = threadIdx.x + i * kThreads;
       if (vec < nvec) {
-        float o[8];
+        float xv[8], dyv[8], wf[8], o[8];
+        unpack8(cx[i], xv);
+        unpack8(cy[i], dyv);
+        if (w) unpack8(*reinterpret_cast<const bf16x8*>(w + vec * 8), wf);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - xh[i][j] * m1 - m2);
+        for (int j = 0; j < 8; ++j) {
+          const float xh = (xv[j] - mean) * rstd;
+          const float wj = w ? (zero_centered ? wf[j] + 1.f : wf[j]) : 1.f;
+          o[j] = rstd * (dyv[j] * wj - xh * m1 - m2);
+        }
         if (dres) {
           float d[8];
-          unpack8(*reinterpret_cast<const bf16x8*>(dres + base + vec * 8), d);
+          unpack8(cr[i], d);
 #pragma unroll
           for (int j = 0; j < 8; ++j) o[j] += d[j];
         }
@@ -165,11 +219,11 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
       if (vec < nvec) {
         float* dst = dw_partial + (long long)blockIdx.x * cols + vec * 8;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) dst[j] = dw_acc[i][j];
+        for (int j = 0; j < 8; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(dw_acc[i][j], dw_acc[i][j + 1], dw_acc[i][j + 2], dw_acc[i][j + 3]);
         if (LAYER_NORM && db_partial) {
           float* dstb = db_partial + (long long)blockIdx.x * cols + vec * 8;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) dstb[j] = db_acc[i][j];
+          for (int j = 0; j < 8; j += 4) *reinterpret_cast<float4*>(dstb + j) = make_float4(db_acc[i][j], db_acc[i][j + 1], db_acc[i][j + 2], db_acc[i][j + 3]);
         }
       }
     }
@@ -202,15 +256,51 @@ __global__ void __launch_bounds__(kColsumCols * kColsumSplit) colsum_kernel(cons
   }
 }
 
+int sm_count() {
+  static const int sms = [] {
+    int device = 0, count = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0)
+      count = 148;
+    return count;
+  }();
+  return sms;
+}
+// CTAs that are resident at once (occupancy of this instantiation x SMs): the persistent grid is one full wave, no tail
+template <typename Kernel>
+int resident_ctas(Kernel kernel) {
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess || per_sm <= 0) per_sm = 1;
+  return per_sm * sm_count();
+}
+template <int VPT, bool LN>
+int fwd_ctas() {
+  static const int n = resident_ctas(norm_fwd_kernel<VPT, LN>);
+  return n;
+}
+template <int VPT, bool LN>
+int bwd_ctas() {
+  static const int n = resident_ctas(norm_bwd_kernel<VPT, LN>);
+  return n;
+}
 template <bool LN>
-int fwd_dispatch(int vpt, dim3 grid, cudaStream_t st, const __nv_bfloat16* x, const __nv_bfloat16* delta,
+int bwd_ctas_for(int vpt) {
+  switch (vpt) {
+    case 1: return bwd_ctas<1, LN>();
+    case 2: return bwd_ctas<2, LN>();
+    case 4: return bwd_ctas<4, LN>();
+    default: return bwd_ctas<8, LN>();
+  }
+}
+
+template <bool LN>
+int fwd_dispatch(int vpt, cudaStream_t st, const __nv_bfloat16* x, const __nv_bfloat16* delta,
                  const __nv_bfloat16* w, const __nv_bfloat16* b, __nv_bfloat16* res_out, __nv_bfloat16* y, float* rstd,
                  float* mean, int rows, int cols, float eps, int zc) {
   switch (vpt) {
-    case 1: norm_fwd_kernel<1, LN><<<grid, kThreads, 0, st>>>(x, delta, w, b, res_out, y, rstd, mean, rows, cols, eps, zc); break;
-    case 2: norm_fwd_kernel<2, LN><<<grid, kThreads, 0, st>>>(x, delta, w, b, res_out, y, rstd, mean, rows, cols, eps, zc); break;
-    case 4: norm_fwd_kernel<4, LN><<<grid, kThreads, 0, st>>>(x, delta, w, b, res_out, y, rstd, mean, rows, cols, eps, zc); break;
-    case 8: norm_fwd_kernel<8, LN><<<grid, kThreads, 0, st>>>(x, delta, w, b, res_out, y, rstd, mean, rows, cols, eps, zc); break;
+    case 1: norm_fwd_kernel<1, LN><<<min(rows, fwd_ctas<1, LN>()), kThreads, 0, st>>>(x, delta, w, b, res_out, y, rstd, mean, rows, cols, eps, zc); break;
+    case 2: norm_fwd_kernel<2, LN><<<min(rows, fwd_ctas<2, LN>()), kThreads, 0, st>>>(x, delta, w, b, res_out, y, rstd, mean, rows, cols, eps, zc); break;
+    case 4: norm_fwd_kernel<4, LN><<<min(rows, fwd_ctas<4, LN>()), kThreads, 0, st>>>(x, delta, w, b, res_out, y, rstd, mean, rows, cols, eps, zc); break;
+    case 8: norm_fwd_kernel<8, LN><<<min(rows, fwd_ctas<8, LN>()), kThreads, 0, st>>>(x, delta, w, b, res_out, y, rstd, mean, rows, cols, eps, zc); break;
     default: return FLB_ERR_SHAPE;
   }
   FLB_CHECK_LAUNCH();
@@ -248,24 +338,28 @@ FLB_API int flb_norm_fwd(const void* x, const void* delta, const void* w, const 
                          cudaStream_t stream) {
   const int vpt = pick_vpt(cols);
   if (!vpt || rows <= 0) return FLB_ERR_SHAPE;
-  dim3 grid(rows);
   auto X = (const __nv_bfloat16*)x; auto D = (const __nv_bfloat16*)delta; auto W = (const __nv_bfloat16*)w;
   auto B = (const __nv_bfloat16*)b; auto R = (__nv_bfloat16*)res_out; auto Y = (__nv_bfloat16*)y;
-  if (layer_norm) return fwd_dispatch<true>(vpt, grid, stream, X, D, W, B, R, Y, rstd, mean, rows, cols, eps, zero_centered);
-  return fwd_dispatch<false>(vpt, grid, stream, X, D, W, B, R, Y, rstd, mean, rows, cols, eps, zero_centered);
+  if (layer_norm) return fwd_dispatch<true>(vpt, stream, X, D, W, B, R, Y, rstd, mean, rows, cols, eps, zero_centered);
+  return fwd_dispatch<false>(vpt, stream, X, D, W, B, R, Y, rstd, mean, rows, cols, eps, zero_centered);
 }
 
 // Number of per-CTA partial rows flb_norm_bwd writes into dw_partial / db_partial.
-FLB_API int flb_norm_bwd_parts(int rows) { return rows < 1184 ? rows : 1184; }  // 8 resident CTAs on each of 148 SMs
+FLB_API int flb_norm_bwd_parts(int rows, int cols, int layer_norm) {
+  const int vpt = pick_vpt(cols);
+  if (!vpt) return 0;
+  const int ctas = layer_norm ? bwd_ctas_for<true>(vpt) : bwd_ctas_for<false>(vpt);
+  return rows < ctas ? rows : ctas;
+}
 
-// dx = dnorm(dy) (+ dres).  dw_partial/db_partial: [flb_norm_bwd_parts(rows), cols] fp32 scratch (may be null
+// dx = dnorm(dy) (+ dres).  dw_partial/db_partial: [flb_norm_bwd_parts(rows, cols, layer_norm), cols] fp32 scratch (may be null
 // to skip parameter gradients).
 FLB_API int flb_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const float* mean,
                          const void* dres, void* dx, float* dw_partial, float* db_partial, int rows, int cols,
                          int zero_centered, int layer_norm, cudaStream_t stream) {
   const int vpt = pick_vpt(cols);
   if (!vpt || rows <= 0) return FLB_ERR_SHAPE;
-  dim3 grid(flb_norm_bwd_parts(rows));
+  dim3 grid(flb_norm_bwd_parts(rows, cols, layer_norm));
   auto DY = (const __nv_bfloat16*)dy; auto X = (const __nv_bfloat16*)x; auto W = (const __nv_bfloat16*)w;
   auto DR = (const __nv_bfloat16*)dres; auto DX = (__nv_bfloat16*)dx;
   if (layer_norm) return bwd_dispatch<true>(vpt, grid, stream, DY, X, W, rstd, mean, DR, DX, dw_partial, db_partial, rows, cols, zero_centered);

@@ -37,8 +37,9 @@ _SIGNATURES = {
     "flb_gemm_bf16_ex": [_p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _p],
     "flb_gemm_gated_bf16": [_p, _p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _ll, _i, _p],
     "flb_gemm_error_word": [],
+    "flb_gemm_tmap_cache_stats": [_p],
     "flb_norm_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _f, _i, _i, _p],
-    "flb_norm_bwd_parts": [_i],
+    "flb_norm_bwd_parts": [_i, _i, _i],
     "flb_norm_bwd": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p],
     "flb_colsum": [_p, _p, _i, _i, _i, _i, _p],
     "flb_rope": [_p, _p, _p, _ll, _ll, _i, _i, _i, _i, _p],

@@ -138,6 +138,15 @@ def matmul_nt_gated(x: torch.Tensor, w1: torch.Tensor, act_code: int) -> tuple[t
     return h, a
 
 
+def tensor_map_cache_stats() -> tuple[int, int]:
+    """(hits, misses) of this thread's tensor-map table in the GEMM library."""
+    import ctypes
+
+    out = (ctypes.c_ulonglong * 2)()
+    _lib.get_lib().flb_gemm_tmap_cache_stats(ctypes.cast(out, ctypes.c_void_p))
+    return int(out[0]), int(out[1])
+
+
 def check_device_errors() -> None:
     """Raise if a GEMM kernel gave up on a bounded wait since the last check (synchronises the device)."""
     word = _lib.get_lib().flb_gemm_error_word()

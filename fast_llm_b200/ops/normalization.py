@@ -50,7 +50,7 @@ def _bwd_native(dy2, x2, weight, bias, rstd, mean, dres2, zero_centered, layer_n
     rows, cols = x2.shape
     lib = _lib.get_lib()
     dx = torch.empty_like(x2)
-    parts = lib.flb_norm_bwd_parts(rows)
+    parts = lib.flb_norm_bwd_parts(rows, cols, int(layer_norm))
     dwp = torch.empty(parts, cols, dtype=torch.float32, device=x2.device) if need_param_grads and weight is not None else None
     dbp = torch.empty(parts, cols, dtype=torch.float32, device=x2.device) if need_param_grads and bias is not None else None
     _lib.check(

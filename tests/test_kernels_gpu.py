@@ -235,6 +235,24 @@ def test_mlp_activation(gated, act):
     assert _rel_err(x.grad, xr.grad) < 1e-2
 
 
+def test_gemm_reuses_tensor_maps_for_repeated_operands():
+    from fast_llm_b200.ops.gemm import matmul_nt, tensor_map_cache_stats
+
+    x = torch.randn(512, 256, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(384, 256, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(512, 384, device="cuda", dtype=torch.bfloat16)
+    matmul_nt(x, w, out=out)
+    hits, misses = tensor_map_cache_stats()
+    first = out.clone()
+    matmul_nt(x, w, out=out)
+    hits2, misses2 = tensor_map_cache_stats()
+    assert misses2 == misses and hits2 >= hits + 3  # A, B and C maps all came from the table
+    assert torch.equal(out, first)
+    # another operand at the same address with another shape must not reuse a stale map
+    matmul_nt(x[:256], w, out=out[:256])
+    assert _rel_err(out[:256], x[:256].float() @ w.float().t()) < 5e-3
+
+
 @pytest.mark.parametrize("m,f,k", [(512, 1024, 512), (1000, 328, 192), (4096, 3584, 1024), (257, 136, 64)])
 @pytest.mark.parametrize("act", ["silu", "gelu"])
 def test_gated_gemm_epilogue_matches_gemm_then_activation(m, f, k, act):
