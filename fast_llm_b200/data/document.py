@@ -187,7 +187,7 @@ class LanguageModelBatch:
             positions = torch.arange(len(tokens))
             lengths = [len(tokens)]
             starts = torch.tensor([0])
-        inputs_tokens = tokens[:size].clamp(min=0)
+        inputs_tokens = tokens[:size]  # negative ids (image placeholders, padding) stay: the embedding layer maps them to zero
         labels, num_labels = {}, {}
         for d in range(1, predicted_tokens + 1):
             lab = tokens[d : d + size].clone()
@@ -222,6 +222,8 @@ class LanguageModelBatch:
                 max_q, max_k = max(max_q, qlen), max(max_k, ke - kb)
             sl = slice(q_begin, q_end)
             extras = {"max_position": int(positions[:size].max()) if size else 0}
+            if bool((inputs_tokens[sl] < 0).any()):
+                extras[LanguageModelKwargs.mask_inputs] = True
             if self.advantages is not None:
                 extras[LanguageModelKwargs.advantages] = self.advantages[1 : size + 1][sl].clone()
                 extras[LanguageModelKwargs.old_log_probabilities] = self.old_log_probabilities[1 : size + 1][sl].clone()

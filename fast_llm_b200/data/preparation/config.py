@@ -149,7 +149,7 @@ class ImagePreparationConfig(Config):
     max_image_width: int = Field(default=1024, hint=FieldHint.optional, valid=check_field(Assert.gt, 0))
     image_break_token: int | None = Field(default=None, desc="Token inserted after every row of patches.", hint=FieldHint.optional)
     image_end_token: int | None = Field(default=None, desc="Token inserted after the image.", hint=FieldHint.optional)
-    placeholder_token: int = Field(default=0, desc="Token occupying the position of each patch.", hint=FieldHint.optional)
+    placeholder_token: int = Field(default=-100, desc="Token occupying the position of each patch; negative ids embed to zero, so the patch embedding stands alone there, and are ignored as labels.", hint=FieldHint.optional)
 
 
 @config_class(dynamic_type={RunnableConfig: "prepare_gpt_memmap", DatasetPreparatorConfig: "gpt_memmap"})

@@ -121,7 +121,9 @@ class LanguageModelEmbedding(Layer):
         ids = kwargs.get(LanguageModelKwargs.token_ids, input_)
         if torch.is_floating_point(ids):
             ids = input_
-        mask_inputs = kwargs.get(LanguageModelKwargs.mask_inputs, False)
+        # negative ids (image placeholders, padding) embed to zero; always checked when encoder outputs are merged in, so that
+        # a patch's embedding replaces its placeholder instead of being added to some token's embedding
+        mask_inputs = kwargs.get(LanguageModelKwargs.mask_inputs, False) or kwargs.get(LanguageModelKwargs.embedding_map) is not None
         if mask_inputs:
             token_mask = ids >= 0
             ids = ids * token_mask

@@ -11,6 +11,7 @@ Weight map (parity: `fast_llm/models/multimodal/conversion/llava.py:43-417`):
   embeddings / decoder / head                                        <-> language_model.* with the Mistral names
 """
 
+import pathlib
 import typing
 
 import torch
@@ -163,6 +164,12 @@ class LlavaHybridSSMHuggingfaceCheckpointHandler(LlavaHuggingfaceCheckpointHandl
                            "AutoModelForCausalLM": "modeling_llava_hybrid.LlavaHybridForConditionalGeneration",
                            "AutoModelForImageTextToText": "modeling_llava_hybrid.LlavaHybridForConditionalGeneration"}
         return out
+
+    @classmethod
+    def get_extra_files(cls):
+        from fast_llm_b200.external_models.llava_hybrid import configuration_llava_hybrid, modeling_llava_hybrid
+
+        return [*cls.text_handler.get_extra_files(), pathlib.Path(configuration_llava_hybrid.__file__), pathlib.Path(modeling_llava_hybrid.__file__)]
 
 
 class Apriel2CheckpointFormat(CheckpointFormat):

@@ -161,3 +161,68 @@ def test_llava_hybrid_round_trip(tmp_path):
         torch.testing.assert_close(tensor.float(), original[name].float(), rtol=1e-2, atol=1e-2, msg=lambda m: f"{name}: {m}")
         count += 1
     assert count == len(original)
+
+
+def test_llava_hybrid_modeling_code_loads_the_export_and_reproduces_the_logits(tmp_path):
+    """The stand-alone Llava-hybrid modelling files shipped with a `llava_hybrid_ssm` export load every tensor of it, and the
+    `transformers` model they build (Pixtral vision tower, projector, Apriel hybrid decoder) gives this framework's logits for
+    text alone and for text with an image."""
+    import json
+
+    from fast_llm_b200.data.document import LanguageModelBatch, LanguageModelDocument
+    from fast_llm_b200.engine.checkpoint.config import CheckpointSaveConfig
+    from fast_llm_b200.external_models.llava_hybrid.modeling_llava_hybrid import LlavaHybridForConditionalGeneration
+    from fast_llm_b200.parallel.topology import PhaseType
+
+    attention_block = copy.deepcopy(TINY_BASE_MODEL["decoder"]["block"])
+    mamba_block = copy.deepcopy(attention_block)
+    mamba_block["mixer"] = {"type": "mamba", "d_inner": 64, "d_xb": 32, "state_size": 8, "dt_rank": 4, "add_linear_biases": False,
+                            "convolution_layer": {"bias": {"enabled": True}}, "dt_layer": {"bias": {"enabled": True}}}
+    decoder = {"type": "pattern", "blocks": {"t": attention_block, "m2": mamba_block}, "pattern": ["t", "m2"], "num_blocks": 2}
+    trainer, _ = build_trainer(_config({("model", "base_model", "image_token_index"): 7, ("model", "base_model", "decoder"): decoder,
+                                        ("model", "base_model", "vision_encoder", "adapter", "intermediate_size"): 64}))
+    path = tmp_path / "llava_hybrid"
+    trainer.multi_stage.save_checkpoint(CheckpointSaveConfig(path=path, format="llava_hybrid_ssm"))
+    for name in ("configuration_llava_hybrid.py", "modeling_llava_hybrid.py", "configuration_apriel_hybrid_ssm.py", "modeling_apriel_hybrid_ssm.py"):
+        assert (path / name).exists(), name
+    assert json.loads((path / "config.json").read_text())["auto_map"]["AutoModelForCausalLM"].endswith("LlavaHybridForConditionalGeneration")
+    external, info = LlavaHybridForConditionalGeneration.from_pretrained(str(path), torch_dtype=torch.float32, output_loading_info=True)
+    assert not info["missing_keys"] and not info["unexpected_keys"], info
+    external.eval()
+
+    model = trainer._multi_stage.base_model
+    for stage in trainer._multi_stage.stages:
+        stage.restore_parameters()
+
+    def ours(tokens, **image):
+        document = LanguageModelDocument(tokens=tokens, **image)
+        batch = LanguageModelBatch.from_documents([document], tokens.numel())
+        inputs = batch.get_model_inputs(micro_batch_size=tokens.numel() - 1)
+        (ids, kwargs), = model.preprocess_batch(inputs, phase=PhaseType.inference, iteration=0)
+        kwargs["return_logits"] = True
+        hidden = None
+        with torch.no_grad():
+            for layer in model.get_layers():
+                hidden = layer.forward(ids if hidden is None else hidden, kwargs)
+        return kwargs["logits"]
+
+    torch.manual_seed(0)
+    tokens = torch.randint(8, 512, (41,))
+    with torch.no_grad():
+        theirs = external(input_ids=tokens[None, :-1]).logits[0]
+    torch.testing.assert_close(ours(tokens), theirs, rtol=2e-4, atol=2e-4)
+
+    # one 2 x 3 grid of 4 x 4 patches at tokens 5..10; the Hugging Face side takes the normalised image
+    pixels = torch.randint(0, 256, (3, 8, 12), dtype=torch.uint8)
+    patches = pixels.view(3, 2, 4, 3, 4).permute(1, 3, 0, 2, 4).reshape(6, 3, 4, 4)
+    coordinates = torch.tensor([[r, c] for r in range(2) for c in range(3)])
+    positions = torch.arange(5, 11)
+    with_image = tokens.clone()
+    with_image[positions] = 7
+    masked = with_image.clone()
+    masked[positions] = -100  # this framework marks the patch positions with a negative id, Llava with `image_token_index`
+    mine = ours(masked, image_patches=patches, image_patch_positions=positions, image_patch_coordinates=coordinates)
+    image = trainer._config.model.base_model.vision_encoder.normalization.normalize(pixels[None])  # what an image processor hands over
+    with torch.no_grad():
+        theirs = external(input_ids=with_image[None, :-1], pixel_values=image, image_sizes=[(8, 12)]).logits[0]
+    torch.testing.assert_close(mine, theirs, rtol=5e-4, atol=5e-4)
