@@ -241,11 +241,22 @@ struct PairCfg {
 //                (fprop and dgrad of both MLP layers)
 //   kGroupWgrad  C_e (+)= A[rows of e]^T * B[rows of e] : contraction over the expert's rows, C holds E matrices stacked
 //                along its rows (weight gradients)
-enum GroupMode : int { kGroupNone = 0, kGroupRows = 1, kGroupWgrad = 2 };
+//   kGroupGathered  an ordinary GEMM whose A rows arrive chunk by chunk from tensor-parallel peers (the all-gather of a
+//                sequence-parallel linear layer): chunk c of `arrive_chunk_rows` rows may be read once the word arrive[c],
+//                which the peer's push kernel sets after its last store, has reached `arrive_target`.  Tiles are visited
+//                starting at the local chunk (`m_rotate` row blocks in), so the math on rows that are already here covers
+//                the transfer of the others; the wait is bounded like every other wait of this kernel.
+enum GroupMode : int { kGroupNone = 0, kGroupRows = 1, kGroupWgrad = 2, kGroupGathered = 3 };
 struct GroupArgs {
   const int* row_begin;  // [experts + 1]
   int experts;
   int b_rows_per_expert;  // kGroupRows: rows of B (N if K-major, K if MN-major) per expert
+  // kGroupGathered
+  int m_rotate;
+  const unsigned* arrive;
+  unsigned arrive_target;
+  int arrive_chunk_rows;
+  int arrive_local_chunk;
 };
 struct TileInfo {
   int m0, n0;      // coordinates in A (row or M index) and B (N index) of the tile, before the CTA's half offset
@@ -265,8 +276,9 @@ template <int GROUP>
 __device__ __forceinline__ TileInfo grouped_tile(const GroupArgs& g, int tile, int num_m, int num_n, int M, int K) {
   TileInfo t;
   int m_blk, n_blk;
-  if constexpr (GROUP == kGroupNone) {
+  if constexpr (GROUP == kGroupNone || GROUP == kGroupGathered) {
     tile_coords(tile, num_m, num_n, m_blk, n_blk);
+    if constexpr (GROUP == kGroupGathered) m_blk = (m_blk + g.m_rotate) % num_m;
     t.m0 = m_blk * PairTileM; t.n0 = n_blk * PairTileN; t.c_row0 = t.m0; t.b_row_off = 0; t.k_begin = 0;
     t.num_kb = (K + BLOCK_K - 1) / BLOCK_K;
   } else if constexpr (GROUP == kGroupRows) {
@@ -410,11 +422,24 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      [[maybe_unused]] uint32_t arrived_chunks = 0;  // kGroupGathered: chunks this producer has already seen arrive (at most 16 ranks)
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         const TileInfo ti = grouped_tile<GROUP>(group, tile, num_m, num_n, M, K);
         const int m0 = ti.m0 + (int)cta_rank * BLOCK_M;
         // this CTA's half of the B tile: the second 128 columns, or (gated) the up rows that belong to the leader's gate rows
         const int n0 = kGated ? ti.n0 / 2 + (int)cta_rank * gated_half : ti.n0 + (int)cta_rank * (C::TILE_N / 2);
+        if constexpr (GROUP == kGroupGathered) {
+          // rows [m0, m0 + BLOCK_M) must have arrived from the rank(s) that own them
+          const int last_row = min(m0 + BLOCK_M, M) - 1;
+          for (int c = m0 / group.arrive_chunk_rows; c <= last_row / group.arrive_chunk_rows && ok; ++c) {
+            if (c == group.arrive_local_chunk || ((arrived_chunks >> c) & 1u)) continue;
+            if (!flag_wait(group.arrive + c, group.arrive_target, abort_flag, err_word, 15)) { ok = false; break; }
+            arrived_chunks |= 1u << c;
+            // the peer wrote the rows with ordinary stores; the loads below go through the async proxy
+            asm volatile("fence.proxy.async;" ::: "memory");
+          }
+          if (!ok) break;
+        }
         for (int kb = 0; kb < ti.num_kb; ++kb) {
           if (!mbar_wait<true>(empty_bar(stage), phase ^ 1u, abort_flag, err_word, 11)) { ok = false; break; }
           const uint32_t a_dst = smem_base + stage * C::STAGE_BYTES;
@@ -698,7 +723,7 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
   }
   int tiles = ((M + PairCfg::TILE_M - 1) / PairCfg::TILE_M) * ((N + PairCfg::TILE_N - 1) / PairCfg::TILE_N);
   if (EPI == EPI_GATED_BF16) tiles = ((M + PairCfg::TILE_M - 1) / PairCfg::TILE_M) * ((N / 2 + 127) / 128);
-  if (GROUP != kGroupNone) tiles = tiles_upper_bound;
+  if (GROUP == kGroupRows || GROUP == kGroupWgrad) tiles = tiles_upper_bound;
   int clusters = st->num_sms / 2;
   if (max_ctas > 1 && max_ctas / 2 < clusters) clusters = max_ctas / 2;
   if (tiles < clusters) clusters = tiles;
@@ -849,6 +874,32 @@ FLB_API int flb_gemm_gated_bf16(const void* A, const void* W, void* H, void* ACT
   if (!make_tmap_c(&th, H, (uint64_t)2 * F, (uint64_t)M, (uint64_t)ldh, false)) return FLB_ERR_TMA;
   if (!make_tmap_c(&tact, ACT, (uint64_t)F, (uint64_t)M, (uint64_t)ldact, false)) return FLB_ERR_TMA;
   return launch_pair<false, false, EPI_GATED_BF16>(ta, tb, th, 1, H, M, 2 * F, K, ldh, 0, st, stream, GroupArgs{nullptr, 0, 0}, 0, &tact, act_type);
+}
+
+// C[M, N] = A[M, K] * B (bf16 store) where A is the landing zone of a tensor-parallel all-gather: `world` chunks of
+// `chunk_rows` rows, chunk `local_chunk` already in place, chunk c readable once arrive[c] >= arrive_target (set by the
+// peers' flb_tp_push).  One CTA-pair launch over all rows; row blocks are visited starting at the local chunk.
+// b_mn_major as in flb_gemm_bf16.  The wait gives up after the kernel's spin limit and raises the GEMM error word (15).
+FLB_API int flb_gemm_gathered_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
+                                   int b_mn_major, const unsigned* arrive, unsigned arrive_target, int chunk_rows, int local_chunk,
+                                   cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || chunk_rows <= 0 || arrive == nullptr) return FLB_ERR_SHAPE;
+  if ((lda % 8) || (ldb % 8) || (ldc % 8) || (M + chunk_rows - 1) / chunk_rows > 16) return FLB_ERR_SHAPE;
+  for (const void* ptr : {A, B, (const void*)C})
+    if (reinterpret_cast<uintptr_t>(ptr) & 15) return FLB_ERR_SHAPE;
+  DeviceState* st = device_state();
+  if (!st) return FLB_ERR_CUDA;
+  CUtensorMap ta, tb, tc;
+  if (!make_tmap(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BLOCK_K, BLOCK_M)) return FLB_ERR_TMA;
+  const bool ok = b_mn_major ? make_tmap(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BLOCK_K)
+                             : make_tmap(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BLOCK_K, 128u);
+  if (!ok) return FLB_ERR_TMA;
+  if (!make_tmap_c(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, false)) return FLB_ERR_TMA;
+  GroupArgs group{nullptr, 0, 0, 0, arrive, arrive_target, chunk_rows, local_chunk};
+  const int num_m = (M + PairCfg::TILE_M - 1) / PairCfg::TILE_M;
+  group.m_rotate = (int)(((long long)local_chunk * chunk_rows / PairCfg::TILE_M) % num_m);
+  if (b_mn_major) return launch_pair<false, true, EPI_STORE_BF16, kGroupGathered>(ta, tb, tc, 1, C, M, N, K, ldc, 0, st, stream, group);
+  return launch_pair<false, false, EPI_STORE_BF16, kGroupGathered>(ta, tb, tc, 1, C, M, N, K, ldc, 0, st, stream, group);
 }
 
 FLB_API int flb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,

@@ -70,6 +70,24 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Bounded wait until the 32-bit word at `flag` (written by another GPU with st.release.sys) has reached `target`
+// (wrap-around compare).  Same contract as mbar_wait: false after the limit, with the CTA's abort flag and the error word set.
+__device__ __forceinline__ bool flag_wait(const unsigned* flag, unsigned target, volatile int* abort_flag, int* err_word, int where) {
+  const long long t0 = clock64();
+  for (;;) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if ((int)(v - target) >= 0) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kSpinLimitCycles) {
+      *abort_flag = 1;
+      atomicExch(err_word, where);
+      return false;
+    }
+    __nanosleep(100);
+  }
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tmap, uint32_t bar, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"

@@ -192,6 +192,88 @@ __global__ void peer_copy_kernel(const uint4* __restrict__ src, uint4* __restric
   for (; i < n16; i += stride) dst[i] = src[i];
 }
 
+// Push half of the fused all-gather + GEMM.  Every rank stores its [rows, width] shard into slot `rank` of the landing zone
+// of each peer (one read of the source, world - 1 peer stores per 16 bytes) and then raises the peer's arrival word for that
+// slot to `call`; the peer's GEMM (flb_gemm_gathered_bf16) waits on that word tile by tile.  Landing zones alternate
+// between two halves by call parity.  Before it overwrites a half, the kernel waits until every peer has reported that it
+// is done with the GEMM of call - 2 (the words at done_offset, written by the peers' pushes of call - 1: a rank's push runs
+// after its previous GEMM in stream order, so these words were written long ago and the wait is a formality - bounded all
+// the same).  Nothing on this GPU waits for this kernel, and this kernel waits only for kernels of other GPUs.
+__global__ void tp_push_kernel(const uint4* __restrict__ src, long long n16, PeerPtrs bases, long long dst_offset, long long flag_offset,
+                               long long done_offset, int rank, int world, unsigned call, unsigned* local_counter, int* err_word,
+                               long long limit_cycles) {
+  __shared__ int failed;
+  if (threadIdx.x == 0) failed = 0;
+  __syncthreads();
+  if (threadIdx.x < world && threadIdx.x != rank) {
+    const int peer = threadIdx.x;
+    if (blockIdx.x == 0) {  // this rank has finished every GEMM up to call - 1
+      unsigned* remote = reinterpret_cast<unsigned*>(reinterpret_cast<char*>(bases.p[peer]) + done_offset) + rank;
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(call - 1u) : "memory");
+    }
+    if (call > 2u) {
+      const unsigned* local = reinterpret_cast<const unsigned*>(reinterpret_cast<const char*>(bases.p[rank]) + done_offset) + peer;
+      const long long t0 = clock64();
+      for (;;) {
+        unsigned v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local) : "memory");
+        if ((int)(v - (call - 2u)) >= 0) break;
+        if (clock64() - t0 > limit_cycles) {
+          atomicExch(err_word, 200 + peer);
+          failed = 1;
+          break;
+        }
+        __nanosleep(200);
+      }
+    }
+  }
+  __syncthreads();
+  if (failed || wait_failed(err_word)) return;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n16; i += 2 * stride) {
+    const bool second = i + stride < n16;
+    const uint4 a = src[i];
+    const uint4 b = second ? src[i + stride] : a;
+    for (int step = 1; step < world; ++step) {
+      const int peer = (rank + step) % world;
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(bases.p[peer]) + dst_offset);
+      dst[i] = a;
+      if (second) dst[i + stride] = b;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned ticket = atomicAdd(local_counter, 1u);
+    if (ticket == gridDim.x - 1) {  // every CTA's stores are out: raise the arrival words
+      *local_counter = 0u;
+      __threadfence_system();
+      for (int step = 1; step < world; ++step) {
+        const int peer = (rank + step) % world;
+        unsigned* flag = reinterpret_cast<unsigned*>(reinterpret_cast<char*>(bases.p[peer]) + flag_offset);
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(call) : "memory");
+      }
+    }
+  }
+}
+
+// bases[r]: rank r's symmetric buffer.  dst_offset: byte offset of this rank's slot in the landing half of this call;
+// flag_offset: byte offset of the arrival word for (half, this rank); done_offset: byte offset of the `world` done words.
+// local_counter: one zero-initialised word in this rank's memory.  bytes % 16 == 0.
+FLB_API int flb_tp_push(const void* src, long long bytes, const void* const* bases, long long dst_offset, long long flag_offset,
+                        long long done_offset, int rank, int world, unsigned call, unsigned* local_counter, int* err_word, int ctas,
+                        cudaStream_t stream) {
+  if (world < 2 || world > kMaxRanks || rank < 0 || rank >= world) return FLB_ERR_SHAPE;
+  if (bytes % 16 || dst_offset % 16 || flag_offset % 4 || done_offset % 4 || (reinterpret_cast<uintptr_t>(src) & 15)) return FLB_ERR_SHAPE;
+  PeerPtrs ptrs;
+  for (int r = 0; r < world; ++r) ptrs.p[r] = const_cast<void*>(bases[r]);
+  if (ctas <= 0) ctas = 32;
+  tp_push_kernel<<<ctas, 512, 0, stream>>>((const uint4*)src, bytes >> 4, ptrs, dst_offset, flag_offset, done_offset, rank, world, call,
+                                           local_counter, err_word, g_barrier_limit_cycles);
+  FLB_CHECK_LAUNCH();
+  return FLB_OK;
+}
+
 FLB_API int flb_peer_copy(const void* src, void* dst, long long bytes, int ctas, cudaStream_t stream) {
   if (bytes % 16 || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15)) return FLB_ERR_SHAPE;
   if (bytes == 0) return FLB_OK;

@@ -36,6 +36,7 @@ _SIGNATURES = {
     "flb_grouped_gemm_bf16": [_p, _p, _p, _p, _i, _i, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _p],
     "flb_gemm_bf16_ex": [_p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _p],
     "flb_gemm_gated_bf16": [_p, _p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _ll, _i, _p],
+    "flb_gemm_gathered_bf16": [_p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _p, ctypes.c_uint, _i, _i, _p],
     "flb_gemm_error_word": [],
     "flb_gemm_tmap_cache_stats": [_p],
     "flb_norm_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _f, _i, _i, _p],
@@ -71,6 +72,7 @@ _SIGNATURES = {
     "flb_attention_bwd_error_word": [],
     "flb_symm_max_ranks": [],
     "flb_symm_signal_pad_bytes": [_i],
+    "flb_tp_push": [_p, _ll, _p, _ll, _ll, _ll, _i, _i, ctypes.c_uint, _p, _p, _i, _p],
     "flb_symm_barrier": [_p, _i, _i, _i, ctypes.c_uint, _p, _p],
     "flb_rs_reduce_blocks": [],
     "flb_symm_set_barrier_limit": [_ll],

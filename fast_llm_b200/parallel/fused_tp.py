@@ -2,11 +2,18 @@
 
 The three collectives around a sequence-parallel linear layer never run as separate operations here:
 
-    all-gather -> GEMM      `all_gather_matmul`: every rank publishes its [T/tp, H] shard in symmetric memory; a small
-                            copy kernel (`flb_peer_copy`, 24 CTAs, plain peer loads) pulls chunk j+1 into local memory on a
-                            side stream while the GEMM of chunk j runs on the other SMs.  (Reading the A operand straight
-                            from the peer through TMA works but is 3.7x slower: remote lines are not cached in the local
-                            L2, so every N-tile re-fetches its A rows over NVLink.)
+    all-gather -> GEMM      `all_gather_matmul`: ONE GEMM launch over all T rows.  Every rank pushes its [T/tp, H] shard into
+                            its slot of each peer's landing zone (`flb_tp_push`, 32 CTAs on a side stream, one read and
+                            tp - 1 peer stores per 16 bytes) and then raises an arrival word on the peer; the GEMM's TMA
+                            producer visits the row blocks of the local chunk first and, before the first load of a row
+                            block that belongs to another rank, waits (bounded, error word) for that rank's arrival word
+                            (`flb_gemm_gathered_bf16`).  The math on rows that are already here covers the transfer of the
+                            rest, and the tile grid is that of the full GEMM instead of tp launches of a quarter of the rows.
+                            Landing zones alternate by call parity; a push into a zone first checks the peers' "done with
+                            call - 2" words.  (Reading the A operand straight from the peer through TMA works but is 3.7x
+                            slower: remote lines are not cached in the local L2, so every N-tile re-fetches its A rows over
+                            NVLink.)  `single_launch = False` selects the older pipeline: a pull kernel (`flb_peer_copy`) per
+                            peer chunk on a side stream and one GEMM launch per chunk, ordered by events.
     GEMM -> reduce-scatter  `matmul_reduce_scatter`: the GEMM for token chunk j stores its partial tiles from the epilogue
                             into slot `rank` of rank j's staging buffer (peer stores leave as each tile finishes, under
                             the remaining math); one `flb_slot_sum_bf16` adds the tp slots in rank order (deterministic).
@@ -19,6 +26,7 @@ so the barrier of call k also releases the buffers of call k-1.  Replaces the NC
 """
 
 import logging
+import os
 
 import torch
 
@@ -31,6 +39,9 @@ logger = logging.getLogger(__name__)
 _contexts: dict[int, "FusedTensorParallel"] = {}
 
 _GATHER_SLOT, _SCATTER_SLOT = 1, 2
+# control words at the end of the arena: arrival words [2 halves][16 ranks], then done words [16 ranks] (4 bytes each)
+_MAX_RANKS = 16
+_CONTROL_BYTES = 256 * ((3 * _MAX_RANKS * 4 + 255) // 256)
 
 
 def get(group) -> "FusedTensorParallel | None":
@@ -86,7 +97,18 @@ class FusedTensorParallel:
         shard_bytes = max_tokens // self.world * max_width * 2
         staging_bytes = max_tokens * max_width * 2
         self._shard_bytes, self._staging_bytes = shard_bytes, staging_bytes
-        self.arena = SymmetricArena(2 * shard_bytes + 2 * staging_bytes, self.group, device)
+        # [2 published shards | 2 reduce-scatter staging zones | 2 landing zones of the pushed all-gather | control words]
+        self._landing_base = 2 * shard_bytes + 2 * staging_bytes
+        self._control_base = self._landing_base + 2 * staging_bytes
+        self.arena = SymmetricArena(self._control_base + _CONTROL_BYTES, self.group, device)
+        self.arena.buffer[self._control_base :].zero_()
+        torch.cuda.synchronize(device)
+        torch.distributed.barrier(self.group)  # nobody pushes before every rank's control words are zero
+        self._push_counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self._push_calls = 0
+        self._push_event, self._push_done_event = torch.cuda.Event(), torch.cuda.Event()
+        self._bases = self.arena.peer_pointer_array()
+        self.single_launch = os.environ.get("FLB_TP_SINGLE_LAUNCH", "1") != "0"
         self._gather_calls = self._scatter_calls = 0
         self.direct_peer_stores = False  # True: register stores instead of TMA tensor stores into the peers' staging slots
         # local landing zone of gathered operands, side stream and per-chunk events for the copy / GEMM pipeline
@@ -147,6 +169,8 @@ class FusedTensorParallel:
         """concat_j(x_j) @ W^T (b_mn False: W is [N, K]) or @ W (b_mn True: W is [K, N]) -> [T, N]."""
         rows, k = x_shard.shape
         n = weight.shape[1] if b_mn else weight.shape[0]
+        if self.single_launch and self.world <= _MAX_RANKS:
+            return self._pushed_all_gather_matmul(x_shard, weight, b_mn)
         gathered, events = self._gather(x_shard)
         out = torch.empty(rows * self.world, n, dtype=x_shard.dtype, device=x_shard.device)
         main = torch.cuda.current_stream()
@@ -156,6 +180,42 @@ class FusedTensorParallel:
                 main.wait_event(events[j])
             gemm_raw(gathered[j * rows : (j + 1) * rows], weight, out[j * rows : (j + 1) * rows], rows, n, k, False, b_mn, _EPI_STORE_BF16)
         self._release_gathered()
+        return out
+
+    def _pushed_all_gather_matmul(self, x_shard: torch.Tensor, weight: torch.Tensor, b_mn: bool) -> torch.Tensor:
+        rows, k = x_shard.shape
+        n = weight.shape[1] if b_mn else weight.shape[0]
+        self._push_calls += 1
+        call = self._push_calls
+        half = call & 1
+        nbytes = rows * k * 2
+        zone = self._landing_base + half * self._staging_bytes
+        landing = self.arena.buffer[zone : zone + self.world * nbytes].view(torch.bfloat16).view(self.world * rows, k)
+        flags = self._control_base + half * _MAX_RANKS * 4
+        done = self._control_base + 2 * _MAX_RANKS * 4
+        lib = _lib.get_lib()
+        main = torch.cuda.current_stream()
+        if not x_shard.is_contiguous():
+            x_shard = x_shard.contiguous()
+        # the push starts once the shard exists; being behind this point of the main stream it also follows the previous GEMM
+        self._push_event.record(main)
+        self._copy_stream.wait_event(self._push_event)
+        x_shard.record_stream(self._copy_stream)
+        with torch.cuda.stream(self._copy_stream):
+            _lib.check(lib.flb_tp_push(x_shard.data_ptr(), nbytes, self._bases, zone + self.rank * nbytes, flags + self.rank * 4, done,
+                                       self.rank, self.world, call, self._push_counter.data_ptr(), self.arena.error_word.data_ptr(), 32,
+                                       _lib.stream_ptr()), "flb_tp_push")
+            _lib.count_launch()
+        landing[self.rank * rows : (self.rank + 1) * rows].copy_(x_shard)
+        out = torch.empty(rows * self.world, n, dtype=x_shard.dtype, device=x_shard.device)
+        _lib.check(lib.flb_gemm_gathered_bf16(landing.data_ptr(), weight.data_ptr(), out.data_ptr(), rows * self.world, n, k, k, weight.stride(0), n,
+                                              int(b_mn), self.arena.buffer.data_ptr() + flags, call, rows, self.rank, _lib.stream_ptr()),
+                   "flb_gemm_gathered_bf16")
+        _lib.count_launch()
+        # the shard may be rewritten in place by later work on this stream: not before the push has read it (the GEMM cannot
+        # finish before the peers' pushes, which run beside this rank's, so this wait costs nothing)
+        self._push_done_event.record(self._copy_stream)
+        main.wait_event(self._push_done_event)
         return out
 
     # ---- GEMM + reduce-scatter

@@ -92,6 +92,16 @@ def bench_elementwise(results):
     go = torch.randn(t, f, device="cuda", dtype=torch.bfloat16)
     rec("swiglu_fwd", 3 * t * f * 2, lambda: act_fwd_native(gu, True, ActivationType.silu))
     rec("swiglu_bwd_recompute", 6 * t * f * 2, lambda: act_bwd_native(go, gu, True, ActivationType.silu, True))
+    # layer-1 GEMM with the gated activation in its epilogue against the GEMM followed by the activation kernel
+    from fast_llm_b200.ops.gemm import matmul_nt, matmul_nt_gated
+
+    w1 = torch.randn(2 * f, h, device="cuda", dtype=torch.bfloat16) / h**0.5
+    fused_ms = time_op(lambda: matmul_nt_gated(x, w1, ActivationType.silu.code))
+    split_ms = time_op(lambda: act_fwd_native(matmul_nt(x, w1), True, ActivationType.silu))
+    r = {"op": "mlp1_gated_fprop", "shape": [t, 2 * f, h], "fused_ms": fused_ms, "gemm_then_activation_ms": split_ms,
+         "tflops_fused": 2.0 * t * 2 * f * h / fused_ms / 1e9}
+    results.append(r)
+    print(json.dumps(r), flush=True)
     qkv = torch.randn(t, 6144, device="cuda", dtype=torch.bfloat16)
     ang = torch.arange(t, device="cuda", dtype=torch.float64)[:, None] * (10000.0 ** (-torch.arange(0, 128, 2, device="cuda", dtype=torch.float64) / 128))[None]
     table = torch.cat([ang.cos(), ang.sin()], -1).float().contiguous()

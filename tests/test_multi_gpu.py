@@ -217,6 +217,49 @@ def _fused_tp_rank_main(rank, world_size, tokens, hidden, ffn, timing):
     return errors, plain_ms, fused_ms
 
 
+def _pushed_gather_rank_main(rank, world_size, shapes, repeats):
+    """`all_gather_matmul` as one GEMM launch fed by the peers' pushes, against an NCCL all-gather followed by the same GEMM."""
+    import torch
+
+    from fast_llm_b200.ops.gemm import check_device_errors, matmul_nn, matmul_nt
+    from fast_llm_b200.parallel import fused_tp
+
+    torch.cuda.set_device(rank)
+    torch.distributed.init_process_group("nccl", rank=rank, world_size=world_size, device_id=torch.device("cuda", rank))
+    group = torch.distributed.group.WORLD
+    device = torch.device("cuda", rank)
+    max_tokens = max(rows for rows, _, _ in shapes) * world_size
+    context = fused_tp.enable(group, device, max_tokens, max(k for _, k, _ in shapes))
+    assert context.single_launch
+    worst = 0.0
+    for repeat in range(repeats):
+        for index, (rows, k, n) in enumerate(shapes):
+            generator = torch.Generator(device=device).manual_seed(100 * repeat + index)
+            full = torch.randn(rows * world_size, k, device=device, dtype=torch.bfloat16, generator=generator)
+            b_mn = (repeat + index) % 2 == 1
+            weight = torch.randn((k, n) if b_mn else (n, k), device=device, dtype=torch.bfloat16, generator=generator) * k**-0.5
+            shard = full[rank * rows : (rank + 1) * rows].clone()
+            out = context.all_gather_matmul(shard, weight, b_mn)
+            shard.zero_()  # the caller may reuse its shard at once
+            gathered = torch.empty_like(full)
+            torch.distributed.all_gather_into_tensor(gathered, full[rank * rows : (rank + 1) * rows].contiguous())
+            reference = matmul_nn(gathered, weight) if b_mn else matmul_nt(gathered, weight)
+            worst = max(worst, (out.float() - reference.float()).abs().max().item())
+    torch.cuda.synchronize()
+    context.arena.check_errors()
+    check_device_errors()
+    fused_tp.disable(group)
+    torch.distributed.barrier()
+    return worst
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_pushed_all_gather_matmul_is_the_gathered_gemm_bit_for_bit():
+    # shard rows that are and are not multiples of the 256-row tile; calls alternate landing halves and weight layouts
+    shapes = [(512, 256, 384), (328, 192, 520), (1024, 512, 1024), (72, 64, 136)]
+    assert run_distributed(_pushed_gather_rank_main, 2, shapes, 3, timeout=600) == [0.0, 0.0]
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_fused_tensor_parallel_linear_matches_nccl():
     results = run_distributed(_fused_tp_rank_main, 2, 1024, 512, 1536, False, timeout=600)
@@ -348,6 +391,7 @@ def test_fused_collectives_on_four_ranks():
         for relative, repeat in errors:
             assert relative < 0.15, errors
             assert repeat == 0.0, errors
+    assert run_distributed(_pushed_gather_rank_main, 4, [(512, 256, 384), (200, 192, 520), (768, 512, 1024)], 3, timeout=600) == [0.0] * 4
     for per_rank in run_distributed(_fused_ce_rank_main, 4, 515, 8192, timeout=600):
         for d_loss, d_z, d_grad, d_loss_ref, d_grad_ref in per_rank:
             assert d_loss < 1e-4 and d_z < 1e-2 and d_grad < 1e-3, per_rank
