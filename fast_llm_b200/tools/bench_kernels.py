@@ -413,8 +413,93 @@ def profile_gemm():
     print("profile_gemm done")
 
 
+def bench_tp_linear(results):
+    """Sequence-parallel column- and row-parallel linears (forward + backward) and the all-gather + GEMM alone, per path:
+    NCCL collectives around the GEMMs, the pull pipeline (peer-copy kernel + one GEMM per chunk) and the single-launch
+    GEMM fed by the peers' pushes.  Run one process per GPU:
+        python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m fast_llm_b200.tools.bench_kernels tp_linear
+    Times are CUDA events on the launching stream, maximum over ranks."""
+    import os
+
+    from fast_llm_b200.ops.linear import linear
+    from fast_llm_b200.parallel import fused_tp
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    device = torch.device("cuda", torch.cuda.current_device())
+    torch.distributed.init_process_group("nccl", device_id=device)
+    group = torch.distributed.group.WORLD
+    tokens, hidden, ffn = 8192, 4096, 14336
+    _, tflops_peak, kind = _peaks()
+    generator = torch.Generator(device=device).manual_seed(1234 + rank)
+    rows, cols = tokens // world, 2 * ffn // world
+    x_shard = torch.randn(rows, hidden, device=device, dtype=torch.bfloat16, generator=generator)
+    grad_shard = torch.randn(rows, hidden, device=device, dtype=torch.bfloat16, generator=generator)
+    w1 = (torch.randn(cols, hidden, device=device, dtype=torch.bfloat16, generator=generator) * hidden**-0.5).requires_grad_()
+    w2 = (torch.randn(cols, hidden, device=device, dtype=torch.bfloat16, generator=generator) * cols**-0.5).requires_grad_()
+
+    def layer():
+        x = x_shard.clone().requires_grad_()
+        h = linear(x, w1, None, mode="output", group=group, sequence_parallel=True)
+        y = linear(h, w2, None, transposed_weight=True, mode="input", group=group, sequence_parallel=True)
+        y.backward(grad_shard)
+        w1.grad = w2.grad = None
+
+    def timed(fn, iters=10):
+        for _ in range(3):
+            fn()
+        times = []
+        for _ in range(iters):
+            torch.cuda.synchronize()
+            torch.distributed.barrier()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            fn()
+            end.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(end))
+        times.sort()
+        t = torch.tensor([times[len(times) // 2]], device=device)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        return t.item()
+
+    flops_layer = 3 * 2.0 * tokens * hidden * cols * 2  # two linears, forward + two backward GEMMs each, per rank
+    flops_gather = 2.0 * tokens * hidden * cols
+    out = {"op": "tp_linear", "world": world, "shape": [tokens, hidden, cols], "peak_kind": kind}
+    out["nccl_ms"] = timed(layer)
+    context = fused_tp.enable(group, device, tokens, hidden)
+    for name, single in (("pull_pipeline", False), ("pushed_single_launch", True)):
+        context.single_launch = single
+        out[f"{name}_ms"] = timed(layer)
+        out[f"{name}_gather_gemm_ms"] = timed(lambda: context.all_gather_matmul(x_shard, w1.detach(), False))
+    gathered = torch.empty(tokens, hidden, device=device, dtype=torch.bfloat16)
+
+    def nccl_gather_gemm():
+        from fast_llm_b200.ops.gemm import matmul_nt
+
+        torch.distributed.all_gather_into_tensor(gathered, x_shard, group=group)
+        matmul_nt(gathered, w1.detach())
+
+    out["nccl_gather_gemm_ms"] = timed(nccl_gather_gemm)
+    bound_ms = flops_layer / (tflops_peak * 1e9)
+    out["compute_bound_ms"] = bound_ms
+    out["gather_gemm_compute_bound_ms"] = flops_gather / (tflops_peak * 1e9)
+    out["gather_bytes_per_rank"] = (world - 1) * rows * hidden * 2
+    out["gather_link_bound_ms"] = out["gather_bytes_per_rank"] / 770e6  # measured peer copy, 770 GB/s per direction
+    torch.cuda.synchronize()
+    context.arena.check_errors()
+    fused_tp.disable(group)
+    if rank == 0:
+        results.append(out)
+        print(json.dumps(out), flush=True)
+    torch.distributed.barrier()
+    torch.distributed.destroy_process_group()
+
+
 def main(argv):
     results = []
+    if "tp_linear" in argv:
+        return bench_tp_linear(results)
     if "profile_gemm" in argv:
         return profile_gemm()
     if "profile_gemm_shapes" in argv:
