@@ -195,10 +195,12 @@ __global__ void peer_copy_kernel(const uint4* __restrict__ src, uint4* __restric
 // Push half of the fused all-gather + GEMM.  Every rank stores its [rows, width] shard into slot `rank` of the landing zone
 // of each peer (one read of the source, world - 1 peer stores per 16 bytes) and then raises the peer's arrival word for that
 // slot to `call`; the peer's GEMM (flb_gemm_gathered_bf16) waits on that word tile by tile.  Landing zones alternate
-// between two halves by call parity.  Before it overwrites a half, the kernel waits until every peer has reported that it
-// is done with the GEMM of call - 2 (the words at done_offset, written by the peers' pushes of call - 1: a rank's push runs
-// after its previous GEMM in stream order, so these words were written long ago and the wait is a formality - bounded all
-// the same).  Nothing on this GPU waits for this kernel, and this kernel waits only for kernels of other GPUs.
+// between two halves by call parity, and the host side promises that everything that reads the zone of call j is in the
+// stream before the push of call j + 2 starts.  So the push of call k may overwrite a peer's half as soon as that peer's own
+// push of call k has started: each push first tells every peer "my call k has begun" (the words at done_offset) and then
+// waits, bounded, for the same word from every peer.  A peer's rows cannot arrive before its push begins anyway, so this
+// meeting costs the consuming GEMM nothing.  Nothing on this GPU waits for this kernel, and this kernel waits only for
+// kernels of other GPUs.
 __global__ void tp_push_kernel(const uint4* __restrict__ src, long long n16, PeerPtrs bases, long long dst_offset, long long flag_offset,
                                long long done_offset, int rank, int world, unsigned call, unsigned* local_counter, int* err_word,
                                long long limit_cycles) {
@@ -207,17 +209,17 @@ __global__ void tp_push_kernel(const uint4* __restrict__ src, long long n16, Pee
   __syncthreads();
   if (threadIdx.x < world && threadIdx.x != rank) {
     const int peer = threadIdx.x;
-    if (blockIdx.x == 0) {  // this rank has finished every GEMM up to call - 1
+    if (blockIdx.x == 0) {  // this rank's call has begun: its readers of the half that is about to be overwritten are done
       unsigned* remote = reinterpret_cast<unsigned*>(reinterpret_cast<char*>(bases.p[peer]) + done_offset) + rank;
-      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(call - 1u) : "memory");
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(call) : "memory");
     }
-    if (call > 2u) {
+    {
       const unsigned* local = reinterpret_cast<const unsigned*>(reinterpret_cast<const char*>(bases.p[rank]) + done_offset) + peer;
       const long long t0 = clock64();
       for (;;) {
         unsigned v;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local) : "memory");
-        if ((int)(v - (call - 2u)) >= 0) break;
+        if ((int)(v - call) >= 0) break;
         if (clock64() - t0 > limit_cycles) {
           atomicExch(err_word, 200 + peer);
           failed = 1;
@@ -270,6 +272,31 @@ FLB_API int flb_tp_push(const void* src, long long bytes, const void* const* bas
   if (ctas <= 0) ctas = 32;
   tp_push_kernel<<<ctas, 512, 0, stream>>>((const uint4*)src, bytes >> 4, ptrs, dst_offset, flag_offset, done_offset, rank, world, call,
                                            local_counter, err_word, g_barrier_limit_cycles);
+  FLB_CHECK_LAUNCH();
+  return FLB_OK;
+}
+
+// Stream-ordered wait until every peer's push of `call` has arrived (for consumers that are not flb_gemm_gathered_bf16, e.g. a
+// weight-gradient GEMM over the whole gathered operand).  Waits only on words written by other GPUs; bounded.
+__global__ void tp_wait_kernel(const unsigned* flags, unsigned call, int world, int rank, int* err_word, long long limit_cycles) {
+  const int peer = threadIdx.x;
+  if (peer >= world || peer == rank) return;
+  const long long t0 = clock64();
+  for (;;) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + peer) : "memory");
+    if ((int)(v - call) >= 0) break;
+    if (clock64() - t0 > limit_cycles) {
+      atomicExch(err_word, 300 + peer);
+      break;
+    }
+    __nanosleep(200);
+  }
+}
+
+FLB_API int flb_tp_wait(const unsigned* flags, unsigned call, int world, int rank, int* err_word, cudaStream_t stream) {
+  if (world < 2 || world > kMaxRanks || rank < 0 || rank >= world) return FLB_ERR_SHAPE;
+  tp_wait_kernel<<<1, 32, 0, stream>>>(flags, call, world, rank, err_word, g_barrier_limit_cycles);
   FLB_CHECK_LAUNCH();
   return FLB_OK;
 }

@@ -22,6 +22,7 @@ from fast_llm_b200.layers.normalization import NormalizationConfig
 from fast_llm_b200.ops.gemm import matmul_nn, matmul_nt
 from fast_llm_b200.ops.linear import weight_grad
 from fast_llm_b200.ops.pointwise import embedding
+from fast_llm_b200.parallel import fused_tp
 from fast_llm_b200.parallel.ops import gather_op, reduce_forward, reduce_op, reduce_scatter_op, split_op
 from fast_llm_b200.parallel.topology import DistributedDimNames
 from fast_llm_b200.tensor import TensorDim
@@ -185,13 +186,21 @@ class _HeadLoss(torch.autograd.Function):
     def forward(ctx, x, weight, head, kwargs, losses_out, split_index, num_splits, gathered=False):
         x2 = x.detach()
         group = head._logits_group
+        logits = None
         if gathered:
             x_full = x2  # the caller gathered the token shards (and reduce-scatters the gradient)
         elif head._sequence_parallel_logits_gather and group is not None:
-            x_full = gather_op(x2, group, 0)
+            x_full = None
+            fused = fused_tp.usable(group, True, x2, weight)
+            if fused is not None and fused.single_launch and fused.fits(x2.shape[0] * group.size(), x2.shape[1]):
+                # the token shards arrive inside the logits GEMM (peers push, the GEMM waits per row block)
+                logits, x_full = fused.all_gather_matmul(x2, weight, False, return_gathered=True)
+            else:
+                x_full = gather_op(x2, group, 0)
         else:
             x_full = x2
-        logits = matmul_nt(x_full, weight)
+        if logits is None:
+            logits = matmul_nt(x_full, weight)
         c = head._config
         scale = c.logits_scale_factor
         softcap_state = None
@@ -206,8 +215,14 @@ class _HeadLoss(torch.autograd.Function):
         if grad_logits is not None:
             if softcap_state is not None:
                 grad_logits = (grad_logits.float() * (1 - softcap_state * softcap_state) * c.logits_scale_factor).to(grad_logits.dtype)
-            dx = matmul_nn(grad_logits, weight)
-            if group is not None and not gathered:
+            fused = fused_tp.usable(group, True, grad_logits, weight) if (head._sequence_parallel_logits_gather and not gathered) else None
+            use_fused = fused is not None and fused.fits(grad_logits.shape[0], weight.shape[1])
+            if use_fused:
+                # partial input gradients leave for their owners from the GEMM's epilogue
+                dx = fused.matmul_reduce_scatter(grad_logits, weight, True)
+            else:
+                dx = matmul_nn(grad_logits, weight)
+            if group is not None and not gathered and not use_fused:
                 if head._sequence_parallel_logits_gather:
                     dx = reduce_scatter_op(dx, group, dim=0)
                 elif head._vocab_parallel:

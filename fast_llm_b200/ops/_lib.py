@@ -38,6 +38,7 @@ _SIGNATURES = {
     "flb_gemm_gated_bf16": [_p, _p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _ll, _i, _p],
     "flb_gemm_gathered_bf16": [_p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _p, ctypes.c_uint, _i, _i, _p],
     "flb_gemm_error_word": [],
+    "flb_norm_error_word": [],
     "flb_gemm_tmap_cache_stats": [_p],
     "flb_norm_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _f, _i, _i, _p],
     "flb_norm_bwd_parts": [_i, _i, _i],
@@ -72,6 +73,7 @@ _SIGNATURES = {
     "flb_attention_bwd_error_word": [],
     "flb_symm_max_ranks": [],
     "flb_symm_signal_pad_bytes": [_i],
+    "flb_tp_wait": [_p, ctypes.c_uint, _i, _i, _p, _p],
     "flb_tp_push": [_p, _ll, _p, _ll, _ll, _ll, _i, _i, ctypes.c_uint, _p, _p, _i, _p],
     "flb_symm_barrier": [_p, _i, _i, _i, ctypes.c_uint, _p, _p],
     "flb_rs_reduce_blocks": [],

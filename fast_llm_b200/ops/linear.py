@@ -112,13 +112,22 @@ def _backward_fused(ctx, fused, dy2, x_in, weight, transposed_weight, mode, db):
     out = buf.view(weight.shape) if buf is not None else (torch.empty(weight.shape, dtype=weight.dtype, device=weight.device) if has_buffer else None)
     if mode == "output":
         # dy holds all tokens (local output features); x is sharded over tokens
+        pending = fused.start_gather(x_in) if (out is not None and fused.single_launch) else None  # crosses NVLink under the dgrad
         dx = fused.matmul_reduce_scatter(dy2, weight, not transposed_weight) if ctx.needs_input_grad[0] else None
-        if out is not None:  # dW = dy^T gather(x)   (or gather(x)^T dy for a transposed weight)
+        if pending is not None:  # dW = dy^T gather(x)   (or gather(x)^T dy for a transposed weight): one GEMM over all tokens
+            fused.wgrad_from_gathered(dy2, fused.finish_gather(pending), out, accumulate, gathered_is_a=transposed_weight)
+        elif out is not None:
             fused.gathered_wgrad(dy2, x_in, out, accumulate, shard_is_a=transposed_weight)
-    else:
-        # dy is sharded over tokens; x holds all tokens (local input features)
-        dx = fused.all_gather_matmul(dy2, weight, not transposed_weight) if ctx.needs_input_grad[0] else None
+    elif fused.single_launch:
+        # dy is sharded over tokens; x holds all tokens (local input features).  dy is gathered once: the dgrad GEMM takes the
+        # rows as they arrive, the weight gradient reads the same landing zone afterwards.
+        pending = fused.start_gather(dy2)
+        dx = fused.matmul_gathered(pending, weight, not transposed_weight) if ctx.needs_input_grad[0] else None
         if out is not None:  # dW = gather(dy)^T x   (or x^T gather(dy))
+            fused.wgrad_from_gathered(x_in, fused.finish_gather(pending), out, accumulate, gathered_is_a=not transposed_weight)
+    else:
+        dx = fused.all_gather_matmul(dy2, weight, not transposed_weight) if ctx.needs_input_grad[0] else None
+        if out is not None:
             fused.gathered_wgrad(x_in, dy2, out, accumulate, shard_is_a=not transposed_weight)
     dw = None if buf is not None else out
     return dx, dw, db, None, None, None, None

@@ -9,8 +9,11 @@ The three collectives around a sequence-parallel linear layer never run as separ
                             block that belongs to another rank, waits (bounded, error word) for that rank's arrival word
                             (`flb_gemm_gathered_bf16`).  The math on rows that are already here covers the transfer of the
                             rest, and the tile grid is that of the full GEMM instead of tp launches of a quarter of the rows.
-                            Landing zones alternate by call parity; a push into a zone first checks the peers' "done with
-                            call - 2" words.  (Reading the A operand straight from the peer through TMA works but is 3.7x
+                            Landing zones alternate by call parity; a zone may be read until the second next gather starts,
+                            and a push begins by meeting the peers' pushes of the same call (a word each way), which tells
+                            it that their readers of the zone it is about to overwrite are done.  `start_gather` /
+                            `matmul_gathered` / `finish_gather` expose the pieces, so that one gather serves the dgrad GEMM
+                            and the weight-gradient GEMM of a layer.  (Reading the A operand straight from the peer through TMA works but is 3.7x
                             slower: remote lines are not cached in the local L2, so every N-tile re-fetches its A rows over
                             NVLink.)  `single_launch = False` selects the older pipeline: a pull kernel (`flb_peer_copy`) per
                             peer chunk on a side stream and one GEMM launch per chunk, ordered by events.
@@ -82,6 +85,15 @@ def disable(group) -> None:
     _contexts.pop(id(group), None)
 
 
+class _PendingGather:
+    """A pushed all-gather in flight: the landing zone, the address of its arrival words and the call number they will reach."""
+
+    __slots__ = ("landing", "flags", "call", "rows", "done_event")
+
+    def __init__(self, landing, flags, call, rows, done_event):
+        self.landing, self.flags, self.call, self.rows, self.done_event = landing, flags, call, rows, done_event
+
+
 class FusedTensorParallel:
     def __init__(self, group, device, max_tokens: int | None, max_width: int | None):
         self.group, self.world, self.rank = group, group.size(), group.rank()
@@ -106,7 +118,7 @@ class FusedTensorParallel:
         torch.distributed.barrier(self.group)  # nobody pushes before every rank's control words are zero
         self._push_counter = torch.zeros(1, dtype=torch.int32, device=device)
         self._push_calls = 0
-        self._push_event, self._push_done_event = torch.cuda.Event(), torch.cuda.Event()
+        self._push_event = torch.cuda.Event()
         self._bases = self.arena.peer_pointer_array()
         self.single_launch = os.environ.get("FLB_TP_SINGLE_LAUNCH", "1") != "0"
         self._gather_calls = self._scatter_calls = 0
@@ -165,12 +177,15 @@ class FusedTensorParallel:
         self._done_event.record(torch.cuda.current_stream())
 
     # ---- all-gather + GEMM
-    def all_gather_matmul(self, x_shard: torch.Tensor, weight: torch.Tensor, b_mn: bool) -> torch.Tensor:
-        """concat_j(x_j) @ W^T (b_mn False: W is [N, K]) or @ W (b_mn True: W is [K, N]) -> [T, N]."""
+    def all_gather_matmul(self, x_shard: torch.Tensor, weight: torch.Tensor, b_mn: bool, return_gathered: bool = False):
+        """concat_j(x_j) @ W^T (b_mn False: W is [N, K]) or @ W (b_mn True: W is [K, N]) -> [T, N].
+        `return_gathered` (single-launch path only): also return the [T, K] gathered operand, a view of the landing zone that
+        stays valid until the second next call of this method."""
         rows, k = x_shard.shape
         n = weight.shape[1] if b_mn else weight.shape[0]
         if self.single_launch and self.world <= _MAX_RANKS:
-            return self._pushed_all_gather_matmul(x_shard, weight, b_mn)
+            return self._pushed_all_gather_matmul(x_shard, weight, b_mn, return_gathered)
+        assert not return_gathered
         gathered, events = self._gather(x_shard)
         out = torch.empty(rows * self.world, n, dtype=x_shard.dtype, device=x_shard.device)
         main = torch.cuda.current_stream()
@@ -182,41 +197,65 @@ class FusedTensorParallel:
         self._release_gathered()
         return out
 
-    def _pushed_all_gather_matmul(self, x_shard: torch.Tensor, weight: torch.Tensor, b_mn: bool) -> torch.Tensor:
-        rows, k = x_shard.shape
-        n = weight.shape[1] if b_mn else weight.shape[0]
+    def start_gather(self, shard: torch.Tensor) -> "_PendingGather":
+        """Begin the all-gather of `shard` ([T/tp, width]) into the landing zone of this call: the push to the peers runs on the
+        side stream, this rank's rows are copied in place on the current stream.  The gathered rows of the peers may be read by
+        `flb_gemm_gathered_bf16` (which waits per row block) or after `finish_gather`.  The landing zone stays valid until the
+        second next `start_gather`: everything that reads it must be in the stream by then (the push of call k + 2 tells the
+        peers that this rank is done with the zone of call k)."""
+        rows, width = shard.shape
         self._push_calls += 1
         call = self._push_calls
         half = call & 1
-        nbytes = rows * k * 2
+        nbytes = rows * width * 2
         zone = self._landing_base + half * self._staging_bytes
-        landing = self.arena.buffer[zone : zone + self.world * nbytes].view(torch.bfloat16).view(self.world * rows, k)
+        landing = self.arena.buffer[zone : zone + self.world * nbytes].view(torch.bfloat16).view(self.world * rows, width)
         flags = self._control_base + half * _MAX_RANKS * 4
         done = self._control_base + 2 * _MAX_RANKS * 4
-        lib = _lib.get_lib()
         main = torch.cuda.current_stream()
-        if not x_shard.is_contiguous():
-            x_shard = x_shard.contiguous()
-        # the push starts once the shard exists; being behind this point of the main stream it also follows the previous GEMM
+        if not shard.is_contiguous():
+            shard = shard.contiguous()
+        # the push starts once the shard exists; being behind this point of the main stream it also follows every earlier
+        # consumer of a landing zone
         self._push_event.record(main)
         self._copy_stream.wait_event(self._push_event)
-        x_shard.record_stream(self._copy_stream)
+        shard.record_stream(self._copy_stream)
         with torch.cuda.stream(self._copy_stream):
-            _lib.check(lib.flb_tp_push(x_shard.data_ptr(), nbytes, self._bases, zone + self.rank * nbytes, flags + self.rank * 4, done,
-                                       self.rank, self.world, call, self._push_counter.data_ptr(), self.arena.error_word.data_ptr(), 32,
-                                       _lib.stream_ptr()), "flb_tp_push")
+            _lib.check(_lib.get_lib().flb_tp_push(shard.data_ptr(), nbytes, self._bases, zone + self.rank * nbytes, flags + self.rank * 4, done,
+                                                  self.rank, self.world, call, self._push_counter.data_ptr(), self.arena.error_word.data_ptr(), 32,
+                                                  _lib.stream_ptr()), "flb_tp_push")
             _lib.count_launch()
-        landing[self.rank * rows : (self.rank + 1) * rows].copy_(x_shard)
-        out = torch.empty(rows * self.world, n, dtype=x_shard.dtype, device=x_shard.device)
-        _lib.check(lib.flb_gemm_gathered_bf16(landing.data_ptr(), weight.data_ptr(), out.data_ptr(), rows * self.world, n, k, k, weight.stride(0), n,
-                                              int(b_mn), self.arena.buffer.data_ptr() + flags, call, rows, self.rank, _lib.stream_ptr()),
-                   "flb_gemm_gathered_bf16")
+            done_event = torch.cuda.Event()
+            done_event.record(self._copy_stream)
+        landing[self.rank * rows : (self.rank + 1) * rows].copy_(shard)
+        return _PendingGather(landing, self.arena.buffer.data_ptr() + flags, call, rows, done_event)
+
+    def finish_gather(self, pending: "_PendingGather") -> torch.Tensor:
+        """The gathered [T, width] operand, complete on the current stream from here on."""
+        _lib.check(_lib.get_lib().flb_tp_wait(pending.flags, pending.call, self.world, self.rank, self.arena.error_word.data_ptr(),
+                                              _lib.stream_ptr()), "flb_tp_wait")
+        _lib.count_launch()
+        torch.cuda.current_stream().wait_event(pending.done_event)
+        return pending.landing
+
+    def matmul_gathered(self, pending: "_PendingGather", weight: torch.Tensor, b_mn: bool) -> torch.Tensor:
+        """gathered @ W^T (or @ W) in one GEMM launch that waits, row block by row block, for the peers' rows of `pending`."""
+        tokens, k = pending.landing.shape
+        n = weight.shape[1] if b_mn else weight.shape[0]
+        out = torch.empty(tokens, n, dtype=pending.landing.dtype, device=pending.landing.device)
+        _lib.check(_lib.get_lib().flb_gemm_gathered_bf16(pending.landing.data_ptr(), weight.data_ptr(), out.data_ptr(), tokens, n, k, k,
+                                                         weight.stride(0), n, int(b_mn), pending.flags, pending.call, pending.rows, self.rank,
+                                                         _lib.stream_ptr()), "flb_gemm_gathered_bf16")
         _lib.count_launch()
         # the shard may be rewritten in place by later work on this stream: not before the push has read it (the GEMM cannot
         # finish before the peers' pushes, which run beside this rank's, so this wait costs nothing)
-        self._push_done_event.record(self._copy_stream)
-        main.wait_event(self._push_done_event)
+        torch.cuda.current_stream().wait_event(pending.done_event)
         return out
+
+    def _pushed_all_gather_matmul(self, x_shard: torch.Tensor, weight: torch.Tensor, b_mn: bool, return_gathered: bool = False):
+        pending = self.start_gather(x_shard)
+        out = self.matmul_gathered(pending, weight, b_mn)
+        return (out, pending.landing) if return_gathered else out
 
     # ---- GEMM + reduce-scatter
     def matmul_reduce_scatter(self, x: torch.Tensor, weight: torch.Tensor, b_mn: bool) -> torch.Tensor:
@@ -245,6 +284,8 @@ class FusedTensorParallel:
         """out (+)= sum_j a_j^T b_j over token chunks j, where one operand (`full`, [T, .]) is local and the other is the
         gather of every rank's `shard` ([T/tp, .]).  `shard_is_a`: the gathered side is `a`."""
         rows = shard.shape[0]
+        if self.single_launch and self.world <= _MAX_RANKS:
+            return self.wgrad_from_gathered(full, self.finish_gather(self.start_gather(shard)), out, accumulate, shard_is_a)
         gathered, events = self._gather(shard)
         m = shard.shape[1] if shard_is_a else full.shape[1]
         n = full.shape[1] if shard_is_a else shard.shape[1]
@@ -260,4 +301,13 @@ class FusedTensorParallel:
             a, b = (peer_chunk, chunk) if shard_is_a else (chunk, peer_chunk)
             gemm_raw(a, b, out, m, n, rows, True, True, epilogue)
         self._release_gathered()
+        return out
+
+    @staticmethod
+    def wgrad_from_gathered(full: torch.Tensor, gathered: torch.Tensor, out: torch.Tensor, accumulate: bool, gathered_is_a: bool) -> torch.Tensor:
+        """out (+)= a^T b over all tokens with one operand already gathered ([T, .]): one GEMM launch, one accumulate pass."""
+        a, b = (gathered, full) if gathered_is_a else (full, gathered)
+        f32 = out.dtype == torch.float32
+        epilogue = (_EPI_ACC_F32 if accumulate else _EPI_STORE_F32) if f32 else (_EPI_ACC_BF16 if accumulate else _EPI_STORE_BF16)
+        gemm_raw(a, b, out, a.shape[1], b.shape[1], a.shape[0], True, True, epilogue)
         return out

@@ -70,7 +70,7 @@ def _gemm_source() -> str | None:
     from fast_llm_b200.ops import _lib
 
     word = _lib.get_lib().flb_gemm_error_word()
-    return f"tcgen05 GEMM gave up on a pipeline barrier (role code {word})" if word > 0 else None
+    return f"tcgen05 GEMM gave up on a pipeline barrier (role code {word}; 15: rows of a tensor-parallel peer did not arrive)" if word > 0 else None
 
 
 def _attention_source() -> str | None:
@@ -83,7 +83,16 @@ def _attention_source() -> str | None:
     return None
 
 
+def _norm_source() -> str | None:
+    from fast_llm_b200.ops import _lib
+
+    if _lib.get_lib().flb_norm_error_word() > 0:
+        return "a normalisation kernel gave up waiting for one of its row copies into shared memory"
+    return None
+
+
 def register_kernel_library_sources() -> None:
-    """The error words that live inside the kernel library (GEMM and attention pipelines); needs a GPU and the library."""
+    """The error words that live inside the kernel library (GEMM, attention and normalisation pipelines); needs a GPU and the library."""
     register_error_source("gemm", _gemm_source)
     register_error_source("attention", _attention_source)
+    register_error_source("normalisation", _norm_source)
