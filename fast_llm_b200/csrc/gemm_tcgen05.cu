@@ -902,6 +902,28 @@ FLB_API int flb_gemm_gathered_bf16(const void* A, const void* B, void* C, int M,
   return launch_pair<false, false, EPI_STORE_BF16, kGroupGathered>(ta, tb, tc, 1, C, M, N, K, ldc, 0, st, stream, group);
 }
 
+// flb_gemm_gathered_bf16 and flb_gemm_gated_bf16 in one: the first GEMM of a tensor-parallel gated MLP, whose A rows arrive
+// from the peers while the tiles of the local chunk are computed, with the activation in the epilogue.
+FLB_API int flb_gemm_gathered_gated_bf16(const void* A, const void* W, void* H, void* ACT, int M, int F, int K, long long lda, long long ldw,
+                                         long long ldh, long long ldact, int act_type, const unsigned* arrive, unsigned arrive_target,
+                                         int chunk_rows, int local_chunk, cudaStream_t stream) {
+  if (M <= 0 || F <= 0 || K <= 0 || chunk_rows <= 0 || arrive == nullptr) return FLB_ERR_SHAPE;
+  if ((lda % 8) || (ldw % 8) || (ldh % 8) || (ldact % 8) || (F % 8) || (M + chunk_rows - 1) / chunk_rows > 16) return FLB_ERR_SHAPE;
+  for (const void* ptr : {A, W, (const void*)H, (const void*)ACT})
+    if (reinterpret_cast<uintptr_t>(ptr) & 15) return FLB_ERR_SHAPE;
+  DeviceState* st = device_state();
+  if (!st) return FLB_ERR_CUDA;
+  CUtensorMap ta, tb, th, tact;
+  if (!make_tmap(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BLOCK_K, BLOCK_M)) return FLB_ERR_TMA;
+  if (!make_tmap(&tb, W, (uint64_t)K, (uint64_t)2 * F, (uint64_t)ldw, BLOCK_K, 128u)) return FLB_ERR_TMA;
+  if (!make_tmap_c(&th, H, (uint64_t)2 * F, (uint64_t)M, (uint64_t)ldh, false)) return FLB_ERR_TMA;
+  if (!make_tmap_c(&tact, ACT, (uint64_t)F, (uint64_t)M, (uint64_t)ldact, false)) return FLB_ERR_TMA;
+  GroupArgs group{nullptr, 0, 0, 0, arrive, arrive_target, chunk_rows, local_chunk};
+  const int num_m = (M + PairCfg::TILE_M - 1) / PairCfg::TILE_M;
+  group.m_rotate = (int)(((long long)local_chunk * chunk_rows / PairCfg::TILE_M) % num_m);
+  return launch_pair<false, false, EPI_GATED_BF16, kGroupGathered>(ta, tb, th, 1, H, M, 2 * F, K, ldh, 0, st, stream, group, 0, &tact, act_type);
+}
+
 FLB_API int flb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                           long long ldc, int a_mn_major, int b_mn_major, int epilogue, int block_n, int max_ctas,
                           cudaStream_t stream) {

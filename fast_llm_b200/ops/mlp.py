@@ -66,8 +66,11 @@ class _MLP(torch.autograd.Function):
         if fused is not None:
             # both collectives ride in the GEMMs: the token shards arrive inside the layer-1 GEMM (peers push, the GEMM waits per
             # row block), the partial outputs of layer 2 leave for their owners from its epilogue
-            h = fused.matmul_gathered(fused.start_gather(x_in), w1, False)
-            a = _act_fwd(h, gated, act)
+            if gated and w1.shape[0] % 16 == 0:
+                h, a = fused.matmul_gathered_gated(fused.start_gather(x_in), w1, act.code)  # and the activation in its epilogue
+            else:
+                h = fused.matmul_gathered(fused.start_gather(x_in), w1, False)
+                a = _act_fwd(h, gated, act)
             y = fused.matmul_reduce_scatter(a, w2, True)
             ctx.save_for_backward(x_in, None if recompute.recompute_layer_1 else h, None if recompute.recompute_activation else a)
             ctx.params = (w1, b1, w2, b2)

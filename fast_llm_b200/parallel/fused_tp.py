@@ -252,6 +252,20 @@ class FusedTensorParallel:
         torch.cuda.current_stream().wait_event(pending.done_event)
         return out
 
+    def matmul_gathered_gated(self, pending: "_PendingGather", w1: torch.Tensor, act_code: int) -> tuple[torch.Tensor, torch.Tensor]:
+        """`matmul_gathered` for the first layer of a gated MLP (`w1` = [gate rows; up rows]) with the activation in the GEMM's
+        epilogue: returns (h, act(gate) * up)."""
+        tokens, k = pending.landing.shape
+        f = w1.shape[0] // 2
+        h = torch.empty(tokens, 2 * f, dtype=torch.bfloat16, device=w1.device)
+        a = torch.empty(tokens, f, dtype=torch.bfloat16, device=w1.device)
+        _lib.check(_lib.get_lib().flb_gemm_gathered_gated_bf16(pending.landing.data_ptr(), w1.data_ptr(), h.data_ptr(), a.data_ptr(), tokens, f, k, k,
+                                                               w1.stride(0), 2 * f, f, act_code, pending.flags, pending.call, pending.rows,
+                                                               self.rank, _lib.stream_ptr()), "flb_gemm_gathered_gated_bf16")
+        _lib.count_launch()
+        torch.cuda.current_stream().wait_event(pending.done_event)
+        return h, a
+
     def _pushed_all_gather_matmul(self, x_shard: torch.Tensor, weight: torch.Tensor, b_mn: bool, return_gathered: bool = False):
         pending = self.start_gather(x_shard)
         out = self.matmul_gathered(pending, weight, b_mn)

@@ -472,7 +472,29 @@ def bench_tp_linear(results):
         context.single_launch = single
         out[f"{name}_ms"] = timed(layer)
         out[f"{name}_gather_gemm_ms"] = timed(lambda: context.all_gather_matmul(x_shard, w1.detach(), False))
+    # the pieces of the backward, each against its NCCL counterpart
+    from fast_llm_b200.ops.gemm import matmul_nn, matmul_tn
+
+    context.single_launch = True
+    h_full = torch.randn(tokens, cols, device=device, dtype=torch.bfloat16, generator=generator)
+    dw = torch.zeros(cols, hidden, device=device, dtype=torch.float32)
+    out["fused_gemm_reduce_scatter_ms"] = timed(lambda: context.matmul_reduce_scatter(h_full, w2.detach(), True))
+    scattered = torch.empty(rows, hidden, device=device, dtype=torch.bfloat16)
+
+    def nccl_gemm_reduce_scatter():
+        torch.distributed.reduce_scatter_tensor(scattered, matmul_nn(h_full, w2.detach()), group=group)
+
+    out["nccl_gemm_reduce_scatter_ms"] = timed(nccl_gemm_reduce_scatter)
+    out["gemm_only_ms"] = timed(lambda: matmul_nn(h_full, w2.detach()))
+    out["fused_gather_wgrad_ms"] = timed(lambda: context.wgrad_from_gathered(h_full, context.finish_gather(context.start_gather(x_shard)), dw, True, False))
     gathered = torch.empty(tokens, hidden, device=device, dtype=torch.bfloat16)
+
+    def nccl_gather_wgrad():
+        torch.distributed.all_gather_into_tensor(gathered, x_shard, group=group)
+        matmul_tn(h_full, gathered, out=dw, accumulate=True)
+
+    out["nccl_gather_wgrad_ms"] = timed(nccl_gather_wgrad)
+    out["wgrad_only_ms"] = timed(lambda: matmul_tn(h_full, gathered, out=dw, accumulate=True))
 
     def nccl_gather_gemm():
         from fast_llm_b200.ops.gemm import matmul_nt

@@ -157,7 +157,9 @@ def _fused_tp_rank_main(rank, world_size, tokens, hidden, ffn, timing):
     """Sequence-parallel column- and row-parallel linears, forward and backward: fused peer-memory kernels vs NCCL."""
     import torch
 
+    from fast_llm_b200.ops.activation import ActivationType
     from fast_llm_b200.ops.linear import linear
+    from fast_llm_b200.ops.mlp import MLPRecomputeLevel, mlp
     from fast_llm_b200.parallel import fused_tp
 
     torch.cuda.set_device(rank)
@@ -180,7 +182,16 @@ def _fused_tp_rank_main(rank, world_size, tokens, hidden, ffn, timing):
         h = linear(x, w1, None, mode="output", group=group, sequence_parallel=True)          # [T, ffn/tp]
         y = linear(h, w2, None, transposed_weight=True, mode="input", group=group, sequence_parallel=True)  # [T/tp, hidden]
         y.backward(grad_shard)
-        return [t.detach().float() for t in (h, y, x.grad, w1.grad, w2.grad)]
+        outputs = [t.detach().float() for t in (h, y, x.grad, w1.grad, w2.grad)]
+        # the MLP node: gated layer 1 (gate rows, then up rows, of this rank's slice), layer 2 stored [ffn/tp, hidden]
+        xm = x_shard.clone().requires_grad_()
+        half = cols // 2
+        m1 = torch.cat([w_out_full[rank * half : (rank + 1) * half], w_out_full[ffn // 2 + rank * half : ffn // 2 + (rank + 1) * half]]).clone().requires_grad_()
+        m2 = w_in_full[rank * half : (rank + 1) * half].clone().requires_grad_()
+        out = mlp(xm, m1, None, m2, None, gated=True, activation=ActivationType.silu, group=group, sequence_parallel=True,
+                  recompute_level=MLPRecomputeLevel.activation)
+        out.backward(grad_shard)
+        return outputs + [t.detach().float() for t in (out, xm.grad, m1.grad, m2.grad)]
 
     def time_it():
         for _ in range(3):
