@@ -246,7 +246,12 @@ struct PairCfg {
 //                which the peer's push kernel sets after its last store, has reached `arrive_target`.  Tiles are visited
 //                starting at the local chunk (`m_rotate` row blocks in), so the math on rows that are already here covers
 //                the transfer of the others; the wait is bounded like every other wait of this kernel.
-enum GroupMode : int { kGroupNone = 0, kGroupRows = 1, kGroupWgrad = 2, kGroupGathered = 3 };
+//   kGroupScatter  an ordinary GEMM whose output rows leave for their owners (the reduce-scatter of a sequence-parallel linear
+//                layer): rows of chunk c (`scatter_chunk_rows` rows, a multiple of the tile height) are written through
+//                `scatter_maps[c]`, a tensor map in device memory over rank c's staging slot for this rank, with TMA stores from
+//                the epilogue.  Row blocks are visited starting `m_rotate` blocks in (the first remote chunk), so the peer
+//                stores travel under the remaining math.
+enum GroupMode : int { kGroupNone = 0, kGroupRows = 1, kGroupWgrad = 2, kGroupGathered = 3, kGroupScatter = 4 };
 struct GroupArgs {
   const int* row_begin;  // [experts + 1]
   int experts;
@@ -257,6 +262,9 @@ struct GroupArgs {
   unsigned arrive_target;
   int arrive_chunk_rows;
   int arrive_local_chunk;
+  // kGroupScatter
+  const CUtensorMap* scatter_maps;
+  int scatter_chunk_rows;
 };
 struct TileInfo {
   int m0, n0;      // coordinates in A (row or M index) and B (N index) of the tile, before the CTA's half offset
@@ -276,9 +284,9 @@ template <int GROUP>
 __device__ __forceinline__ TileInfo grouped_tile(const GroupArgs& g, int tile, int num_m, int num_n, int M, int K) {
   TileInfo t;
   int m_blk, n_blk;
-  if constexpr (GROUP == kGroupNone || GROUP == kGroupGathered) {
+  if constexpr (GROUP == kGroupNone || GROUP == kGroupGathered || GROUP == kGroupScatter) {
     tile_coords(tile, num_m, num_n, m_blk, n_blk);
-    if constexpr (GROUP == kGroupGathered) m_blk = (m_blk + g.m_rotate) % num_m;
+    if constexpr (GROUP == kGroupGathered || GROUP == kGroupScatter) m_blk = (m_blk + g.m_rotate) % num_m;
     t.m0 = m_blk * PairTileM; t.n0 = n_blk * PairTileN; t.c_row0 = t.m0; t.b_row_off = 0; t.k_begin = 0;
     t.num_kb = (K + BLOCK_K - 1) / BLOCK_K;
   } else if constexpr (GROUP == kGroupRows) {
@@ -537,6 +545,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       } else if constexpr (kGated) {
         epilogue_gated(&tmap_c, &tmap_act, smem + C::RING_BYTES + q * kEpiWarpBytes, taddr, row0, ti.n0 / 2, gated_half, M, act_type, lane, epi_counter);
+      } else if (GROUP == kGroupScatter) {
+        // the tile lies inside one chunk: its rows go to that rank's staging slot, addressed from the slot's first row
+        const int chunk = ti.m0 / group.scatter_chunk_rows;
+        const int first = chunk * group.scatter_chunk_rows;
+        epilogue_tma<EPI>(group.scatter_maps + chunk, smem + C::RING_BYTES + q * kEpiWarpBytes, taddr, C::TILE_N, row0 - first, ti.n0,
+                          min(group.scatter_chunk_rows, M - first), N, lane, epi_counter);
       } else if (use_tma_c) {
         epilogue_tma<EPI>(&tmap_c, smem + C::RING_BYTES + q * kEpiWarpBytes, taddr, C::TILE_N, row0, ti.n0, c_rows, N, lane, epi_counter);
       } else {
@@ -922,6 +936,44 @@ FLB_API int flb_gemm_gathered_gated_bf16(const void* A, const void* W, void* H, 
   const int num_m = (M + PairCfg::TILE_M - 1) / PairCfg::TILE_M;
   group.m_rotate = (int)(((long long)local_chunk * chunk_rows / PairCfg::TILE_M) % num_m);
   return launch_pair<false, false, EPI_GATED_BF16, kGroupGathered>(ta, tb, th, 1, H, M, 2 * F, K, ldh, 0, st, stream, group, 0, &tact, act_type);
+}
+
+// Tensor maps for flb_gemm_scatter_bf16: `world` maps of 128 bytes each written to `host_out` (64-byte aligned host memory), map
+// c over the bf16 matrix [rows, n] (leading dimension ld elements) at dst_ptrs[c].  The caller copies them to device memory.
+FLB_API int flb_gemm_scatter_maps(void* host_out, const void* const* dst_ptrs, int world, int rows, int n, long long ld) {
+  if (world <= 0 || rows <= 0 || n <= 0 || (ld % 8) || (reinterpret_cast<uintptr_t>(host_out) & 63)) return FLB_ERR_SHAPE;
+  CUtensorMap* maps = reinterpret_cast<CUtensorMap*>(host_out);
+  for (int c = 0; c < world; ++c) {
+    if (reinterpret_cast<uintptr_t>(dst_ptrs[c]) & 15) return FLB_ERR_SHAPE;
+    if (!encode_tmap(&maps[c], TmapKey{dst_ptrs[c], (uint64_t)n, (uint64_t)rows, (uint64_t)ld, 64u, 32u, 1u})) return FLB_ERR_TMA;
+  }
+  return FLB_OK;
+}
+
+// C = A[M, K] * B (bf16) where the rows of C are scattered: chunk c of `chunk_rows` rows (a multiple of 256) is stored through
+// scatter_maps[c] (device memory, from flb_gemm_scatter_maps), i.e. straight into rank c's staging slot over NVLink.  One
+// CTA-pair launch over all rows, starting at row block `first_chunk * chunk_rows / 256`.
+FLB_API int flb_gemm_scatter_bf16(const void* A, const void* B, const void* scatter_maps, int M, int N, int K, long long lda, long long ldb,
+                                  int b_mn_major, int chunk_rows, int first_chunk, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || chunk_rows <= 0 || (chunk_rows % PairCfg::TILE_M) || scatter_maps == nullptr) return FLB_ERR_SHAPE;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(scatter_maps) & 63)) return FLB_ERR_SHAPE;
+  for (const void* ptr : {A, B})
+    if (reinterpret_cast<uintptr_t>(ptr) & 15) return FLB_ERR_SHAPE;
+  DeviceState* st = device_state();
+  if (!st) return FLB_ERR_CUDA;
+  CUtensorMap ta, tb;
+  if (!make_tmap(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BLOCK_K, BLOCK_M)) return FLB_ERR_TMA;
+  const bool ok = b_mn_major ? make_tmap(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BLOCK_K)
+                             : make_tmap(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BLOCK_K, 128u);
+  if (!ok) return FLB_ERR_TMA;
+  GroupArgs group{};
+  group.scatter_maps = reinterpret_cast<const CUtensorMap*>(scatter_maps);
+  group.scatter_chunk_rows = chunk_rows;
+  const int num_m = (M + PairCfg::TILE_M - 1) / PairCfg::TILE_M;
+  group.m_rotate = (int)(((long long)first_chunk * chunk_rows / PairCfg::TILE_M) % num_m);
+  // the kernel's own output map is unused in this mode: pass A's as a placeholder
+  if (b_mn_major) return launch_pair<false, true, EPI_STORE_BF16, kGroupScatter>(ta, tb, ta, 1, nullptr, M, N, K, N, 0, st, stream, group);
+  return launch_pair<false, false, EPI_STORE_BF16, kGroupScatter>(ta, tb, ta, 1, nullptr, M, N, K, N, 0, st, stream, group);
 }
 
 FLB_API int flb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,

@@ -38,6 +38,8 @@ _SIGNATURES = {
     "flb_gemm_gated_bf16": [_p, _p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _ll, _i, _p],
     "flb_gemm_gathered_bf16": [_p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _p, ctypes.c_uint, _i, _i, _p],
     "flb_gemm_gathered_gated_bf16": [_p, _p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _ll, _i, _p, ctypes.c_uint, _i, _i, _p],
+    "flb_gemm_scatter_maps": [_p, _p, _i, _i, _i, _ll],
+    "flb_gemm_scatter_bf16": [_p, _p, _p, _i, _i, _i, _ll, _ll, _i, _i, _i, _p],
     "flb_gemm_error_word": [],
     "flb_norm_error_word": [],
     "flb_gemm_tmap_cache_stats": [_p],

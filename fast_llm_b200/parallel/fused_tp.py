@@ -118,6 +118,7 @@ class FusedTensorParallel:
         torch.distributed.barrier(self.group)  # nobody pushes before every rank's control words are zero
         self._push_counter = torch.zeros(1, dtype=torch.int32, device=device)
         self._push_calls = 0
+        self._scatter_map_cache: dict = {}
         self._push_event = torch.cuda.Event()
         self._bases = self.arena.peer_pointer_array()
         self.single_launch = os.environ.get("FLB_TP_SINGLE_LAUNCH", "1") != "0"
@@ -282,16 +283,48 @@ class FusedTensorParallel:
         offset = self._staging_offset(call)
         slot_bytes = rows * n * 2
         local = self.arena.buffer[offset : offset + self.world * slot_bytes].view(torch.bfloat16).view(self.world, rows, n)
+        if self.single_launch and rows % 256 == 0:
+            # one GEMM over all tokens; each row block leaves through the tensor map of its owner's staging slot
+            maps = self._scatter_maps(offset, rows, n)
+            _lib.check(_lib.get_lib().flb_gemm_scatter_bf16(x.data_ptr(), weight.data_ptr(), maps.data_ptr(), tokens, n, k, x.stride(0), weight.stride(0),
+                                                            int(b_mn), rows, (self.rank + 1) % self.world, _lib.stream_ptr()), "flb_gemm_scatter_bf16")
+            _lib.count_launch()
+            return self._sum_slots(local, rows, n, x)
         for step in range(self.world):
             j = (self.rank + 1 + step) % self.world  # remote chunks first: their stores travel while the local one computes
             gemm_raw(x[j * rows : (j + 1) * rows], weight, local[self.rank], rows, n, k, False, b_mn, _EPI_STORE_BF16,
                      c_ptr=self.arena.peer_ptrs[j] + offset + self.rank * slot_bytes, direct_store=self.direct_peer_stores and j != self.rank)
+        return self._sum_slots(local, rows, n, x)
+
+    def _sum_slots(self, local: torch.Tensor, rows: int, n: int, like: torch.Tensor) -> torch.Tensor:
         self.arena.barrier(_SCATTER_SLOT)
-        out = torch.empty(rows, n, dtype=x.dtype, device=x.device)
+        out = torch.empty(rows, n, dtype=like.dtype, device=like.device)
         _lib.check(_lib.get_lib().flb_slot_sum_bf16(local.data_ptr(), out.data_ptr(), self.world, rows * n, self.arena.error_word.data_ptr(),
                                                     _lib.stream_ptr()), "flb_slot_sum_bf16")
         _lib.count_launch()
         return out
+
+    def _scatter_maps(self, offset: int, rows: int, n: int) -> torch.Tensor:
+        """Device array of one tensor map per rank over that rank's staging slot for this rank's partial rows (built once per
+        staging half and shape)."""
+        key = (offset, rows, n)
+        maps = self._scatter_map_cache.get(key)
+        if maps is None:
+            import ctypes
+
+            host = torch.empty(self.world * 128 + 64, dtype=torch.uint8)
+            shift = (-host.data_ptr()) % 64
+            aligned = host[shift : shift + self.world * 128]
+            slot_bytes = rows * n * 2
+            destinations = (ctypes.c_void_p * self.world)(*[self.arena.peer_ptrs[j] + offset + self.rank * slot_bytes for j in range(self.world)])
+            _lib.check(_lib.get_lib().flb_gemm_scatter_maps(aligned.data_ptr(), destinations, self.world, rows, n, n), "flb_gemm_scatter_maps")
+            device_buffer = torch.empty(self.world * 128 + 64, dtype=torch.uint8, device=self._device)
+            device_shift = (-device_buffer.data_ptr()) % 64
+            maps = device_buffer[device_shift : device_shift + self.world * 128]
+            maps.copy_(aligned)
+            torch.cuda.current_stream().synchronize()  # once per shape: the host buffer may go away
+            self._scatter_map_cache[key] = maps
+        return maps
 
     # ---- all-gather + weight gradient
     def gathered_wgrad(self, full: torch.Tensor, shard: torch.Tensor, out: torch.Tensor, accumulate: bool, shard_is_a: bool) -> torch.Tensor:

@@ -21,20 +21,23 @@ def _peaks():
 
 
 def time_op(fn, iters=10, warmup=3):
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    """Median device time of `fn` in ms.  All iterations are queued without a host synchronisation in between: each one writes a
+    1 GiB buffer (an L2 flush that also keeps the GPU busy while the host queues the next launches), then records an event,
+    runs `fn` and records another event - so the interval holds the kernels of `fn` and not the host's launch latency."""
+    flush = torch.empty(1024 * 1024 * 1024, dtype=torch.uint8, device="cuda")
     for _ in range(warmup):
         fn()
-    times = []
+    torch.cuda.synchronize()
+    pairs = []
     for _ in range(iters):
         flush.zero_()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
         start.record()
         fn()
         end.record()
-        torch.cuda.synchronize()
-        times.append(start.elapsed_time(end))
-    times.sort()
+        pairs.append((start, end))
+    torch.cuda.synchronize()
+    times = sorted(start.elapsed_time(end) for start, end in pairs)
     return times[len(times) // 2]
 
 
