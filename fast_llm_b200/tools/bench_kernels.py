@@ -521,10 +521,95 @@ def bench_tp_linear(results):
     torch.distributed.destroy_process_group()
 
 
+def bench_zero(results):
+    """The two ZeRO kernels over NVLink peer memory in isolation: `flb_rs_reduce` (each rank sums its 1/n slice of every rank's
+    fp32 gradient buffer with peer loads) and `flb_adam_push` (AdamW on the shard, bf16 weights stored into every rank's weight
+    buffer), against NCCL's reduce-scatter / all-gather of the same buffers.  Run one process per GPU:
+        python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m fast_llm_b200.tools.bench_kernels zero
+    CUDA events, median of 10, maximum over ranks; rates are the bytes that cross NVLink per rank and direction."""
+    import os
+
+    from fast_llm_b200.parallel.symmetric import SymmetricArena, adam_push, rs_reduce
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    device = torch.device("cuda", torch.cuda.current_device())
+    torch.distributed.init_process_group("nccl", device_id=device)
+    group = torch.distributed.group.WORLD
+    elements = 218 * 1024 * 1024  # one Mistral-7B decoder layer: 218 M parameters
+    elements -= elements % (world * 8)
+    shard = elements // world
+    arena = SymmetricArena(elements * 4 + elements * 2, group, device)
+    grads = arena.buffer[: elements * 4].view(torch.float32)
+    weights = arena.buffer[elements * 4 :].view(torch.bfloat16)
+    grads.normal_()
+    grad_shard = torch.empty(shard, device=device)
+    w, m, v = (torch.zeros(shard, device=device) for _ in range(3))
+    lib = _lib_module().get_lib()
+    partial = torch.empty(lib.flb_rs_reduce_blocks(), device=device)
+
+    def timed(fn, iters=10):
+        for _ in range(3):
+            fn()
+        times = []
+        for _ in range(iters):
+            torch.cuda.synchronize()
+            torch.distributed.barrier()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            fn()
+            end.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(end))
+        times.sort()
+        t = torch.tensor([times[len(times) // 2]], device=device)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        return t.item()
+
+    def fused_reduce():
+        arena.barrier(0)
+        rs_reduce(arena, grads, grad_shard, shard, 1.0 / world, False, partial)
+        arena.barrier(0)
+
+    def fused_update():
+        adam_push(arena, w, grad_shard, m, v, weights[rank * shard : (rank + 1) * shard], 1e-4, 0.9, 0.95, 1e-8, 0.1, 1, None)
+        arena.barrier(1)
+
+    gathered = torch.empty(elements, dtype=torch.bfloat16, device=device)
+    low = torch.empty(shard, dtype=torch.bfloat16, device=device)
+    out = {"op": "zero_kernels", "world": world, "elements": elements}
+    out["rs_reduce_ms"] = timed(fused_reduce)
+    out["nccl_reduce_scatter_ms"] = timed(lambda: torch.distributed.reduce_scatter_tensor(grad_shard, grads, group=group))
+    out["adam_push_ms"] = timed(fused_update)
+    out["nccl_all_gather_ms"] = timed(lambda: torch.distributed.all_gather_into_tensor(gathered, low, group=group))
+    pulled = (world - 1) * shard * 4  # fp32 gradient slices read from the peers
+    pushed = (world - 1) * shard * 2  # bf16 weights stored into the peers
+    out["rs_reduce_nvlink_gbs"] = pulled / out["rs_reduce_ms"] / 1e6
+    out["adam_push_nvlink_gbs"] = pushed / out["adam_push_ms"] / 1e6
+    out["rs_reduce_link_bound_ms"] = pulled / 770e6
+    out["adam_push_link_bound_ms"] = pushed / 770e6
+    out["adam_push_hbm_bound_ms"] = shard * 30 / (_peaks()[0] * 1e6)  # 28 bytes per element locally + the local bf16 copy
+    torch.cuda.synchronize()
+    arena.check_errors()
+    if rank == 0:
+        results.append(out)
+        print(json.dumps(out), flush=True)
+    torch.distributed.barrier()
+    torch.distributed.destroy_process_group()
+
+
+def _lib_module():
+    from fast_llm_b200.ops import _lib
+
+    return _lib
+
+
 def main(argv):
     results = []
     if "tp_linear" in argv:
         return bench_tp_linear(results)
+    if "zero" in argv:
+        return bench_zero(results)
     if "profile_gemm" in argv:
         return profile_gemm()
     if "profile_gemm_shapes" in argv:
