@@ -36,6 +36,31 @@ def _native_ok(a: torch.Tensor, b: torch.Tensor) -> bool:
     )
 
 
+library_fallbacks: dict[str, int] = {}  # reason -> number of CUDA GEMMs that went to torch.matmul (cuBLAS) instead
+
+
+def _note_library_fallback(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+    """A CUDA GEMM that the tcgen05 kernels do not take is counted and announced once per reason: nothing falls back silently."""
+    if not a.is_cuda:
+        return
+    if _backend() != "tcgen05":
+        reason = f"FLB_GEMM={_backend()}"
+    elif a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        reason = f"operand dtypes {a.dtype}, {b.dtype} (the tcgen05 kernels take bf16)"
+    elif a.stride(-1) != 1 or b.stride(-1) != 1 or out.stride(-1) != 1:
+        reason = "an operand whose last dimension is not contiguous"
+    else:
+        reason = "an operand that is not 16-byte aligned or whose row stride is not a multiple of 8 elements"
+    count = library_fallbacks.get(reason, 0)
+    library_fallbacks[reason] = count + 1
+    if count == 0:
+        import logging
+
+        logging.getLogger(__name__).warning(f"GEMM runs on torch.matmul (cuBLAS), not on the tcgen05 kernels: {reason}; "
+                                            f"shapes {tuple(a.shape)} x {tuple(b.shape)}.  Further ones of this kind are only counted "
+                                            f"(`fast_llm_b200.ops.gemm.library_fallbacks`).")
+
+
 def gemm_raw(a, b, out, m, n, k, a_mn, b_mn, epilogue, block_n=None, max_ctas=0, *, a_ptr=None, b_ptr=None, c_ptr=None,
              direct_store: bool = False):
     """block_n: None/0 = choose (CTA-pair kernel for large shapes), 128/256 = one-CTA kernel, 512 = CTA-pair kernel.
@@ -77,6 +102,7 @@ def matmul_nt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
         return out
     if _native_ok(x, w) and out.stride(-1) == 1:
         return gemm_raw(x, w, out, m, n, k, False, False, _epilogue(out, accumulate))
+    _note_library_fallback(x, w, out)
     res = torch.matmul(x, w.t())
     return out.add_(res) if accumulate else out.copy_(res)
 
@@ -94,6 +120,7 @@ def matmul_nn(dy: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None
         return out
     if _native_ok(dy, w) and out.stride(-1) == 1:
         return gemm_raw(dy, w, out, m, n, k, False, True, _epilogue(out, accumulate))
+    _note_library_fallback(dy, w, out)
     res = torch.matmul(dy, w)
     return out.add_(res) if accumulate else out.copy_(res)
 
@@ -111,6 +138,7 @@ def matmul_tn(dy: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None
         return out if accumulate else out.zero_()
     if _native_ok(dy, x) and out.stride(-1) == 1:
         return gemm_raw(dy, x, out, m, n, t, True, True, _epilogue(out, accumulate))
+    _note_library_fallback(dy, x, out)
     res = torch.matmul(dy.t(), x)
     return out.add_(res) if accumulate else out.copy_(res)
 
