@@ -822,8 +822,6 @@ FLB_API int flb_gemm_bf16_ex(const void* A, const void* B, void* C, int M, int N
   return dispatch_major<128>(a_mn_major, b_mn_major, epilogue, ta, tb, tc, use_tc, C, M, N, K, ldc, max_ctas, st, stream);
 }
 
-// Reads (and clears) the error word the GEMM kernels raise when a bounded wait expires.
-// Synchronises the device.  0 = no error; 1..4 / 11..14 = which role gave up (one-CTA / pair kernel).
 // Grouped GEMMs of a mixture-of-experts layer (CTA-pair kernel).  `row_begin`: device array [experts + 1] of the first row of
 // every expert in the expert-sorted row space, each a multiple of 256; `rows_upper_bound`: host-side bound on
 // row_begin[experts] (a multiple of 256; the A / C buffers have that many rows).
@@ -869,6 +867,28 @@ FLB_API int flb_grouped_gemm_bf16(const void* A, const void* B, void* C, const i
     }
   }
   return FLB_ERR_SHAPE;
+}
+
+// Grouped form of flb_gemm_gated_bf16 for the experts' first layer: rows of A / H / ACT sorted by expert (`row_begin` as in
+// flb_grouped_gemm_bf16), W = experts stacked matrices [2F, K] ([gate rows; up rows] each).
+FLB_API int flb_grouped_gemm_gated_bf16(const void* A, const void* W, void* H, void* ACT, const int* row_begin, int experts,
+                                        int rows_upper_bound, int F, int K, long long lda, long long ldw, long long ldh, long long ldact,
+                                        int act_type, cudaStream_t stream) {
+  if (experts <= 0 || rows_upper_bound <= 0 || rows_upper_bound % PairTileM || F <= 0 || K <= 0) return FLB_ERR_SHAPE;
+  if ((lda % 8) || (ldw % 8) || (ldh % 8) || (ldact % 8) || (F % 8)) return FLB_ERR_SHAPE;
+  for (const void* ptr : {A, W, (const void*)H, (const void*)ACT})
+    if (reinterpret_cast<uintptr_t>(ptr) & 15) return FLB_ERR_SHAPE;
+  DeviceState* st = device_state();
+  if (!st) return FLB_ERR_CUDA;
+  CUtensorMap ta, tb, th, tact;
+  if (!make_tmap(&ta, A, (uint64_t)K, (uint64_t)rows_upper_bound, (uint64_t)lda, BLOCK_K, BLOCK_M)) return FLB_ERR_TMA;
+  if (!make_tmap(&tb, W, (uint64_t)K, (uint64_t)experts * 2 * F, (uint64_t)ldw, BLOCK_K, 128u)) return FLB_ERR_TMA;
+  if (!make_tmap_c(&th, H, (uint64_t)2 * F, (uint64_t)rows_upper_bound, (uint64_t)ldh, false)) return FLB_ERR_TMA;
+  if (!make_tmap_c(&tact, ACT, (uint64_t)F, (uint64_t)rows_upper_bound, (uint64_t)ldact, false)) return FLB_ERR_TMA;
+  GroupArgs group{row_begin, experts, 2 * F};
+  const int tiles = rows_upper_bound / PairTileM * ((F + 127) / 128);
+  return launch_pair<false, false, EPI_GATED_BF16, kGroupRows>(ta, tb, th, 1, H, rows_upper_bound, 2 * F, K, ldh, 0, st, stream, group, tiles, &tact,
+                                                               act_type);
 }
 
 // First GEMM of a gated MLP fused with the activation: H[M, 2F] = A[M, K] W^T with W = [gate rows; up rows] stacked ([2F, K],
@@ -988,6 +1008,8 @@ FLB_API void flb_gemm_tmap_cache_stats(unsigned long long* out) {
   out[1] = tmap_counters().misses;
 }
 
+// Reads (and clears) the error word the GEMM kernels raise when a bounded wait expires.
+// Synchronises the device.  0 = no error; 1..4 / 11..14 = which role gave up (one-CTA / pair kernel); 15 = rows of a peer did not arrive.
 FLB_API int flb_gemm_error_word() {
   DeviceState* st = device_state();
   if (!st) return -1;

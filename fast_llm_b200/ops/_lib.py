@@ -33,6 +33,7 @@ _SIGNATURES = {
     "flb_moe_route": [_p, _i, _i, _i, _p, _p, _p, _p, _p],
     "flb_moe_route_bwd": [_p, _p, _p, _p, _p, _f, _i, _i, _i, _p, _p],
     "flb_moe_layout": [_p, _i, _i, _i, _p, _p, _p, _p],
+    "flb_grouped_gemm_gated_bf16": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _ll, _ll, _ll, _ll, _i, _p],
     "flb_grouped_gemm_bf16": [_p, _p, _p, _p, _i, _i, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _p],
     "flb_gemm_bf16_ex": [_p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _p],
     "flb_gemm_gated_bf16": [_p, _p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _ll, _i, _p],

@@ -11,7 +11,7 @@ matmuls), `fast_llm/functional/triton/mlp.py:207-477` (`mlp_autograd` with a spa
 import torch
 
 from fast_llm_b200.ops import _lib
-from fast_llm_b200.ops.activation import ActivationType, mlp_activation
+from fast_llm_b200.ops.activation import ActivationType, act_bwd_native, mlp_activation
 from fast_llm_b200.ops.gemm import _EPI_STORE_BF16, _epilogue
 from fast_llm_b200.ops.param_grad import wgrad_target
 
@@ -33,6 +33,20 @@ def grouped_rows(a: torch.Tensor, b: torch.Tensor, row_begin: torch.Tensor, expe
     return out
 
 
+def grouped_rows_gated(x: torch.Tensor, w1: torch.Tensor, row_begin: torch.Tensor, experts: int, ffn: int,
+                       activation: ActivationType) -> tuple[torch.Tensor, torch.Tensor]:
+    """First layer of gated experts with the activation in the GEMM's epilogue: h[rows of e] = x[rows of e] @ W1_e^T
+    (W1_e = [gate rows; up rows], [2 ffn, hidden]) and act(gate) * up, both bf16, from one launch."""
+    rows, hidden = x.shape
+    h = torch.empty(rows, 2 * ffn, dtype=x.dtype, device=x.device)
+    a = torch.empty(rows, ffn, dtype=x.dtype, device=x.device)
+    _lib.check(_lib.get_lib().flb_grouped_gemm_gated_bf16(x.data_ptr(), w1.data_ptr(), h.data_ptr(), a.data_ptr(), row_begin.data_ptr(), experts, rows,
+                                                         ffn, hidden, x.stride(0), w1.stride(0), h.stride(0), a.stride(0), activation.code,
+                                                         _lib.stream_ptr()), "flb_grouped_gemm_gated_bf16")
+    _lib.count_launch()
+    return h, a
+
+
 def grouped_wgrad(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, row_begin: torch.Tensor, experts: int, accumulate: bool) -> torch.Tensor:
     """out[e * m : (e + 1) * m] (+)= a[rows of e]^T @ b[rows of e];  a [rows, m], b [rows, n], out [experts * m, n]."""
     m, n = a.shape[1], b.shape[1]
@@ -51,8 +65,11 @@ class _GroupedMLP(torch.autograd.Function):
     def forward(ctx, x, row_begin, w1, w2, experts, gated, activation):
         hidden = x.shape[1]
         ffn = w2.shape[0] // experts
-        h = grouped_rows(x, w1, row_begin, experts, w1.shape[0] // experts, hidden, b_mn=False)
-        a = mlp_activation(h, gated, activation)
+        if gated:
+            h, a = grouped_rows_gated(x, w1, row_begin, experts, ffn, activation)  # the activation rides in the GEMM's epilogue
+        else:
+            h = grouped_rows(x, w1, row_begin, experts, w1.shape[0] // experts, hidden, b_mn=False)
+            a = mlp_activation(h, gated, activation)
         y = grouped_rows(a, w2, row_begin, experts, hidden, ffn, b_mn=True)
         ctx.save_for_backward(x, h, row_begin)
         ctx.weights = (w1, w2)  # buffer views: kept outside autograd's version tracking
@@ -67,12 +84,10 @@ class _GroupedMLP(torch.autograd.Function):
         hidden = x.shape[1]
         dy = dy.contiguous()
         da = grouped_rows(dy, w2, row_begin, experts, ffn, hidden, b_mn=False)
-        with torch.enable_grad():
-            h_ = h.detach().requires_grad_()
-            a = mlp_activation(h_, gated, activation)
-        (dh,) = torch.autograd.grad(a, h_, da)
+        dh, a = act_bwd_native(da, h, gated, activation, True)  # one kernel: the gradient and the recomputed activation
+        del da
         grads = []
-        for weight, lhs, rhs in ((w2, a.detach(), dy), (w1, dh, x)):
+        for weight, lhs, rhs in ((w2, a, dy), (w1, dh, x)):
             needs = weight.requires_grad or getattr(weight, "grad_buffer", None) is not None
             if not needs:
                 grads.append(None)
