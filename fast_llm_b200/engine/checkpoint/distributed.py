@@ -138,8 +138,10 @@ def _serialize_metadata(metadata: CheckpointMetadata) -> dict:
     # the layout that wrote the shards must be recoverable without the environment of the writer
     dist = out["config"].setdefault("distributed", {})
     dist["world_size"] = metadata.config.distributed.world_size
+    # (the reference validates this section in the reading process, where a missing `local_world_size` defaults to that
+    # process's environment and must still be a multiple of the writer's tensor-parallel size)
+    dist["local_world_size"] = metadata.config.distributed.local_world_size
     dist.pop("rank", None)
-    dist.pop("local_world_size", None)
     out["shards"] = list(metadata.shards)
     out["metadata"] = metadata.metadata
     out.pop("type", None)

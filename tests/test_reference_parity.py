@@ -130,3 +130,58 @@ def test_default_betas_first_step_is_identical_and_the_rest_close(workspace):
     assert ours[0][0] == pytest.approx(reference[0][0], abs=1e-5) and ours[1][0] == pytest.approx(reference[1][0], abs=1e-4)
     # later steps: the reference's no-apex optimizer is one step ahead in its bias correction (see the module docstring)
     assert ours[0] == pytest.approx(reference[0], rel=1e-2)
+
+
+def _save_in_layout(rank, world_size, model_updates, path, hf_path):
+    """Ranks of one layout train two steps and save a distributed checkpoint; rank 0 also exports Hugging Face tensors."""
+    from fast_llm_b200.engine.checkpoint.config import CheckpointSaveConfig
+    from tests.common import build_trainer, tiny_trainer_config, train_steps
+
+    updates = {("model", *key): value for key, value in model_updates.items()}
+    if ("model", "distributed", "pipeline_parallel") in updates:
+        updates[("schedule", "breadth_first_micro_batches")] = 2
+    updates.update({("model", "distributed", "world_size"): world_size, ("model", "distributed", "rank"): rank,
+                    ("model", "distributed", "local_world_size"): world_size, ("model", "distributed", "backend"): "gloo",
+                    ("model", "distributed", "reproducible_init"): True})
+    trainer, distributed = build_trainer(tiny_trainer_config(updates))
+    train_steps(trainer, 2)
+    trainer.multi_stage.save_checkpoint(CheckpointSaveConfig(path=path, format="distributed"))
+    trainer.multi_stage.save_checkpoint(CheckpointSaveConfig(path=hf_path, format="llama"))
+    distributed.shutdown()
+    return True
+
+
+@pytest.mark.parametrize("layout,updates", [
+    ("tp2", {("distributed", "tensor_parallel"): 2}),
+    ("pp2", {("distributed", "pipeline_parallel"): 2}),
+    ("dp2_z3", {("multi_stage", "zero_stage"): 3}),
+])
+def test_the_reference_reads_checkpoints_written_by_two_ranks_of_this_framework(layout, updates, tmp_path):
+    """A distributed checkpoint written by two ranks here (tensor-, pipeline- or data-parallel shards) is converted to
+    Hugging Face tensors by the unmodified reference CLI in one process, i.e. through the reference's own cross-layout
+    loader; the tensors equal this framework's own export of the same model bit for bit."""
+    import safetensors
+
+    from tests.distributed_utils import run_distributed
+
+    path, ours = tmp_path / "distributed", tmp_path / "ours_hf"
+    run_distributed(_save_in_layout, 2, updates, str(path), str(ours))
+    theirs = tmp_path / "reference_hf"
+    env = {**os.environ, "PYTHONPATH": str(REFERENCE), "TORCHDYNAMO_DISABLE": "1", "PYTHONHASHSEED": "0"}
+    out = subprocess.run([sys.executable, "-m", "fast_llm.cli", "convert", "gpt", f"input.path={path}", "input.format=distributed",
+                          f"output.path={theirs}", "output.format=llama", "use_cpu=true"],
+                         cwd=tmp_path, env=env, capture_output=True, text=True, timeout=900)
+    assert out.returncode == 0, "\n".join(line for line in (out.stdout + out.stderr).splitlines() if "Warning" not in line and "warnings.warn" not in line)[-3000:]
+
+    def tensors(directory):
+        found = {}
+        for file in sorted(pathlib.Path(directory).glob("*.safetensors")):
+            with safetensors.safe_open(str(file), framework="pt") as f:
+                for key in f.keys():
+                    found[key] = f.get_tensor(key)
+        return found
+
+    a, b = tensors(ours), tensors(theirs)
+    assert set(a) == set(b) and len(a) > 10
+    for key in a:
+        assert torch.equal(a[key].float(), b[key].float()), f"{layout}: {key}"
