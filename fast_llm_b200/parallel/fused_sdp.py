@@ -13,10 +13,14 @@ Both buffers are double-buffered, so the barrier of call k also proves that ever
 k - 1.  bf16 only; anything else, or a slice larger than the buffers sized by the first call, takes the NCCL path.
 """
 
+import logging
+
 import torch
 
 from fast_llm_b200.ops import _lib
 from fast_llm_b200.parallel.symmetric import SymmetricArena
+
+logger = logging.getLogger(__name__)
 
 _contexts: dict[int, "FusedSequenceDataExchange"] = {}
 _COPY_CTAS = 32
@@ -44,6 +48,7 @@ class FusedSequenceDataExchange:
         self.arena: SymmetricArena | None = None
         self._slice_bytes = 0
         self._gathers = self._scatters = 0
+        self._warned = False
 
     def usable(self, slice_: torch.Tensor) -> bool:
         """`slice_`: this rank's [t, w] part (every rank passes the same shape)."""
@@ -54,6 +59,10 @@ class FusedSequenceDataExchange:
             self._slice_bytes = (nbytes + 255) // 256 * 256
             # [publish x2 | staging (world slots) x2]
             self.arena = SymmetricArena(2 * self._slice_bytes + 2 * self.world * self._slice_bytes, self.group, self._device)
+        if nbytes > self._slice_bytes and not self._warned:
+            self._warned = True  # not silent: larger slices take the NCCL path
+            logger.warning(f"Sequence-data exchange: a slice of {nbytes} bytes does not fit the symmetric buffers sized for "
+                           f"{self._slice_bytes} bytes by the first call; slices of this size use NCCL.")
         return nbytes <= self._slice_bytes
 
     def gather(self, slice_: torch.Tensor) -> torch.Tensor:

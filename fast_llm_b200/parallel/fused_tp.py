@@ -99,6 +99,7 @@ class FusedTensorParallel:
         self.group, self.world, self.rank = group, group.size(), group.rank()
         self._device = device
         self.max_tokens = self.max_width = None
+        self._refused: set = set()
         if max_tokens is not None:
             self._allocate(max_tokens, max_width)
 
@@ -137,7 +138,14 @@ class FusedTensorParallel:
             if tokens % self.world or width % 8:
                 return False
             self._allocate(tokens, width)
-        return tokens <= self.max_tokens and width <= self.max_width and tokens % self.world == 0 and width % 8 == 0
+        ok = tokens <= self.max_tokens and width <= self.max_width and tokens % self.world == 0 and width % 8 == 0
+        if not ok and (tokens, width) not in self._refused:
+            # not silent: the caller takes the NCCL path for this shape
+            self._refused.add((tokens, width))
+            logger.warning(f"Fused tensor-parallel kernels: a [{tokens}, {width}] activation does not fit the symmetric buffers sized for "
+                           f"[{self.max_tokens}, {self.max_width}] by the first fused call (or is not divisible by the group size {self.world} / 8); "
+                           f"this shape uses NCCL collectives.")
+        return ok
 
     def _gather_offset(self, call: int) -> int:
         return (call & 1) * self._shard_bytes
