@@ -34,7 +34,7 @@ class LmEvalEvaluatorConfig(EvaluatorConfig):
     max_length: int | None = Field(default=None, desc="Context limit (longer prompts are left-truncated).", hint=FieldHint.feature)
     max_new_tokens: int = Field(default=256, desc="Default generation budget.", hint=FieldHint.feature)
     add_bos_token: bool = Field(default=False, desc="Prepend the beginning-of-document token to contexts.", hint=FieldHint.feature)
-    cli_args: list[str] = Field(default_factory=list, desc="Extra `key=value` arguments forwarded to `simple_evaluate`.", hint=FieldHint.optional)
+    cli_args: list[str] = Field(default_factory=list, desc="Extra arguments for `simple_evaluate`: `key=value` items or the harness' own command line (`--tasks a,b --num_fewshot 5 ...`).", hint=FieldHint.optional)
 
     def get_evaluator(self, name, *args, **kwargs):
         return LmEvalEvaluator(name, self)
@@ -59,6 +59,41 @@ class FastLLMLmEvalWrapper:
     @property
     def tokenizer_name(self) -> str:
         return str(self._tokenizer._config.path)
+
+    @property
+    def prefix_token_id(self) -> int:
+        """The token that stands in for an empty context (the harness scores `P(continuation | prefix)`)."""
+        return self._tokenizer.bod_id if self._tokenizer.bod_id is not None else self.eot_token_id
+
+    @property
+    def max_length(self) -> int:
+        return self._max_length
+
+    @property
+    def max_gen_toks(self) -> int:
+        return self._max_new_tokens
+
+    # the harness runs in one process per model replica here: it sees one rank
+    rank, world_size = 0, 1
+
+    def apply_chat_template(self, chat_history: list[dict[str, str]], add_generation_prompt: bool = True) -> str:
+        """Render a list of {"role", "content"} messages with the tokenizer's chat template (needed for `--apply_chat_template`)."""
+        inner = getattr(self._tokenizer, "tokenizer", None)
+        if inner is not None and getattr(inner, "chat_template", None):
+            return inner.apply_chat_template(chat_history, tokenize=False, add_generation_prompt=add_generation_prompt)
+        text = "".join(f"{m['role']}: {m['content']}\n" for m in chat_history)  # plain fallback for tokenizers without a template
+        return text + ("assistant: " if add_generation_prompt else "")
+
+    def tok_batch_encode(self, texts: list[str], left_truncate_len: int | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+        """Left-padded token batch and its attention mask."""
+        rows = [self.tok_encode(t) for t in texts]
+        if left_truncate_len is not None:
+            rows = [r[-left_truncate_len:] for r in rows]
+        width = max((len(r) for r in rows), default=0)
+        pad = self.eot_token_id or 0
+        ids = torch.tensor([[pad] * (width - len(r)) + r for r in rows], dtype=torch.int64, device=self.device)
+        mask = torch.tensor([[0] * (width - len(r)) + [1] * len(r) for r in rows], dtype=torch.int64, device=self.device)
+        return ids, mask
 
     @staticmethod
     def _args(request):
@@ -137,27 +172,90 @@ class FastLLMLmEvalWrapper:
         return out
 
     def generate_until(self, requests) -> list[str]:
-        out = []
-        for request in requests:
+        """Requests are grouped by their generation options and sorted by prompt length, then generated `batch_size` at a time
+        (left-padded); every answer is cut at the first of its stop strings."""
+        prepared = []
+        for index, request in enumerate(requests):
             context, options = self._args(request)[:2]
             options = dict(options or {})
-            until = options.get("until") or []
+            until = options.pop("until", None) or []
             until = [until] if isinstance(until, str) else list(until)
-            budget = int(options.get("max_gen_toks", self._max_new_tokens))
+            budget = int(options.pop("max_gen_toks", self._max_new_tokens))
             tokens = self.tok_encode(context)
             if self._add_bos and self._tokenizer.bod_id is not None:
                 tokens = [self._tokenizer.bod_id, *tokens]
             tokens = tokens[-max(self._max_length - budget, 1):]
-            input_ids = torch.tensor([tokens], dtype=torch.int64, device=self.device)
-            generated = self._model.generate(input_ids, attention_mask=torch.ones_like(input_ids), max_new_tokens=budget,
-                                             do_sample=bool(options.get("do_sample", False)), pad_token_id=self.eot_token_id or 0,
-                                             eos_token_id=self.eot_token_id)
-            text = self.tok_decode(generated[0, len(tokens):].tolist())
-            for stop in until:
-                if stop and stop in text:
-                    text = text.split(stop)[0]
-            out.append(text)
+            key = (budget, bool(options.get("do_sample", False)), float(options.get("temperature", 0.0) or 0.0), tuple(until))
+            prepared.append((key, len(tokens), index, tokens))
+        out: list[str | None] = [None] * len(prepared)
+        prepared.sort(key=lambda item: (item[0], -item[1]))
+        start = 0
+        while start < len(prepared):
+            key = prepared[start][0]
+            chunk = [item for item in prepared[start : start + self.batch_size] if item[0] == key]
+            start += len(chunk)
+            budget, do_sample, temperature, until = key
+            width = max(item[1] for item in chunk)
+            pad = self.eot_token_id or 0
+            input_ids = torch.tensor([[pad] * (width - n) + tokens for _, n, _, tokens in chunk], dtype=torch.int64, device=self.device)
+            mask = torch.tensor([[0] * (width - n) + [1] * n for _, n, _, _ in chunk], dtype=torch.int64, device=self.device)
+            sampling = {"do_sample": True, "temperature": temperature} if (do_sample and temperature > 0) else {"do_sample": False}
+            generated = self._model.generate(input_ids, attention_mask=mask, max_new_tokens=budget, pad_token_id=pad,
+                                             eos_token_id=self.eot_token_id, **sampling)
+            for row, (_, _, index, _) in enumerate(chunk):
+                new_tokens = generated[row, width:].tolist()
+                if self.eot_token_id in new_tokens:
+                    new_tokens = new_tokens[: new_tokens.index(self.eot_token_id)]
+                text = self.tok_decode(new_tokens)
+                for stop in until:
+                    if stop and stop in text:
+                        text = text.split(stop)[0]
+                out[index] = text
         return out
+
+
+def parse_harness_arguments(cli_args: list[str]) -> dict:
+    """Arguments for `lm_eval.simple_evaluate` from either spelling: `key=value` items, or the harness' own command line
+    (`--tasks a,b --num_fewshot 5 --limit 0.1 --apply_chat_template --gen_kwargs temperature=0,top_p=1`).  Numbers, booleans
+    and `None` are converted; `tasks` becomes a list."""
+    def convert(value: str):
+        lowered = value.lower()
+        if lowered in ("true", "false"):
+            return lowered == "true"
+        if lowered in ("none", "null"):
+            return None
+        for kind in (int, float):
+            try:
+                return kind(value)
+            except ValueError:
+                pass
+        return value
+
+    out: dict = {}
+    index = 0
+    while index < len(cli_args):
+        item = cli_args[index]
+        if item.startswith("--"):
+            key = item[2:].replace("-", "_")
+            if "=" in key:
+                key, value = key.split("=", 1)
+                out[key] = convert(value)
+            elif index + 1 < len(cli_args) and not cli_args[index + 1].startswith("--"):
+                index += 1
+                out[key] = convert(cli_args[index])
+            else:
+                out[key] = True  # a flag
+        elif "=" in item:
+            key, value = item.split("=", 1)
+            out[key] = convert(value)
+        else:
+            raise ValueError(f"cannot parse harness argument {item!r}")
+        index += 1
+    if isinstance(out.get("tasks"), str):
+        out["tasks"] = [t for t in out["tasks"].split(",") if t]
+    if isinstance(out.get("gen_kwargs"), str):
+        out["gen_kwargs"] = {k: convert(v) for k, v in (pair.split("=", 1) for pair in out["gen_kwargs"].split(","))}
+    return out
 
 
 class LmEvalEvaluator(Evaluator):
@@ -182,14 +280,19 @@ class LmEvalEvaluator(Evaluator):
         except ImportError as e:
             self._hf_model.stop_workers()
             raise ImportError("The lm_eval evaluator needs the `lm_eval` package (lm-evaluation-harness)") from e
-        extra = dict(arg.split("=", 1) for arg in self._config.cli_args)
+        arguments = {"tasks": list(self._config.tasks), "num_fewshot": self._config.num_fewshot, "limit": self._config.limit,
+                     **parse_harness_arguments(self._config.cli_args)}
         try:
-            results = lm_eval.simple_evaluate(model=_as_harness_model(self._wrapper), tasks=list(self._config.tasks), num_fewshot=self._config.num_fewshot,
-                                              limit=self._config.limit, **extra)
+            results = lm_eval.simple_evaluate(model=_as_harness_model(self._wrapper), **arguments)
         finally:
             self._hf_model.stop_workers()
         metrics = {task: {k: v for k, v in values.items() if isinstance(v, (int, float))} for task, values in results["results"].items()}
-        logger.info(f"lm_eval [{self._name}] step {completed_steps}: {metrics}")
+        try:  # the harness' own table, as its command line prints it
+            from lm_eval.utils import make_table
+
+            logger.info(f"lm_eval [{self._name}] step {completed_steps}:\n{make_table(results)}")
+        except Exception:
+            logger.info(f"lm_eval [{self._name}] step {completed_steps}: {metrics}")
         return {f"lm_eval.{self._name}": metrics}
 
 
@@ -206,6 +309,21 @@ def _as_harness_model(wrapper: FastLLMLmEvalWrapper):
 
         def generate_until(self, requests):
             return wrapper.generate_until(requests)
+
+        def apply_chat_template(self, chat_history, add_generation_prompt=True):
+            return wrapper.apply_chat_template(chat_history, add_generation_prompt)
+
+        @property
+        def tokenizer_name(self):
+            return wrapper.tokenizer_name
+
+        @property
+        def eot_token_id(self):
+            return wrapper.eot_token_id
+
+        @property
+        def max_length(self):
+            return wrapper.max_length
 
     return _Model()
 

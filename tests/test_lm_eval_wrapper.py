@@ -46,3 +46,30 @@ def test_evaluate_command(tmp_path, capsys):
     fast_llm_main(args)
     captured = capsys.readouterr()
     assert "validation @ validation" in captured.out + captured.err and "lm loss" in captured.out + captured.err
+
+
+def test_batched_generation_matches_one_by_one_and_harness_arguments_parse(tokenizer_path):  # noqa: F811
+    from fast_llm_b200.data.config import TokenizerConfig
+    from fast_llm_b200.engine.evaluation.evaluators import FastLLMLmEvalWrapper, parse_harness_arguments
+    from fast_llm_b200.engine.inference.huggingface import HuggingfaceGPTModelForCausalLM
+
+    trainer, _ = build_trainer(tiny_trainer_config())
+    model = HuggingfaceGPTModelForCausalLM(trainer._multi_stage)
+    tokenizer = TokenizerConfig.from_dict({"path": str(tokenizer_path)}).get_tokenizer()
+    requests = [("the quick brown fox", {"until": ["\n"], "max_gen_toks": 4}), ("hello", {"until": ["\n"], "max_gen_toks": 4}),
+                ("pack my box", {"max_gen_toks": 3}), ("a", {"until": "\n", "max_gen_toks": 4})]
+    batched = FastLLMLmEvalWrapper(model, tokenizer, batch_size=3).generate_until(requests)
+    single = FastLLMLmEvalWrapper(model, tokenizer, batch_size=1).generate_until(requests)
+    # prompts of different lengths share a left-padded batch: padding must not change what is generated
+    assert batched == single and all(isinstance(t, str) for t in batched)
+    wrapper = FastLLMLmEvalWrapper(model, tokenizer, batch_size=2, max_length=64)
+    ids, mask = wrapper.tok_batch_encode(["the quick brown fox", "hello"])
+    assert ids.shape == mask.shape and mask[1].sum() < mask[0].sum() and mask[1, 0] == 0 and mask[0, 0] == 1
+    assert wrapper.max_length == 64 and wrapper.prefix_token_id == tokenizer.bod_id
+    rendered = wrapper.apply_chat_template([{"role": "user", "content": "hi"}])
+    assert "hi" in rendered and rendered != "hi"  # the tokenizer's own template when it has one, else a plain "role: content" form
+
+    parsed = parse_harness_arguments(["--tasks", "hellaswag,arc_easy", "--num_fewshot", "5", "--limit=0.25", "--apply_chat_template",
+                                      "--gen_kwargs", "temperature=0,top_p=1", "bootstrap_iters=0", "--log-samples"])
+    assert parsed == {"tasks": ["hellaswag", "arc_easy"], "num_fewshot": 5, "limit": 0.25, "apply_chat_template": True,
+                      "gen_kwargs": {"temperature": 0, "top_p": 1}, "bootstrap_iters": 0, "log_samples": True}
