@@ -360,26 +360,32 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ out, const _
   if (sub == 0) delta[(long long)h * total_q + t] = s;
 }
 
-// dq (bf16, packed rows) = dq_accum (fp32, layout [head][token / 32][column / 4][token % 32][4])
-__global__ void attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long dq_stride, int q_col0,
-                                       long long total_q, long long tok_groups, int heads) {
-  // consecutive threads take consecutive tokens of one (head, 8-column group): coalesced 16-byte reads
-  const long long per_head = tok_groups * 32 * (D / 8);
-  const long long total = per_head * heads;
-  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
-    const int lane_tok = (int)(idx & 31);
-    long long rest = idx >> 5;
-    const int c8 = (int)(rest % (D / 8));
-    rest /= (D / 8);
-    const long long grp = rest % tok_groups;
-    const int head = (int)(rest / tok_groups);
-    const long long tok = grp * 32 + lane_tok;
-    if (tok >= total_q) continue;
-    const float* src = acc + ((((long long)head * tok_groups + grp) * (D / 4) + c8 * 2) * 32 + lane_tok) * 4;
-    float f[8];
-    *reinterpret_cast<float4*>(f) = *reinterpret_cast<const float4*>(src);
-    *reinterpret_cast<float4*>(f + 4) = *reinterpret_cast<const float4*>(src + 128);
-    *reinterpret_cast<flb::bf16x8*>(dq + tok * dq_stride + q_col0 + head * D + c8 * 8) = flb::pack8(f);
+// dq (bf16, packed rows) = dq_accum (fp32, layout [head][token / 32][column / 4][token % 32][4]).
+// One CTA per (head, group of 32 tokens): the group's 16 KB are read as they lie (coalesced), turned in shared memory, and
+// written as 256-byte row segments (half a warp per token), instead of 16-byte pieces at the row stride.
+constexpr int kConvertStride = 33;  // float4 per column group in shared memory (32 tokens + 1: spreads the turned reads over banks)
+__global__ void __launch_bounds__(256) attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long dq_stride,
+                                                              int q_col0, long long total_q, long long tok_groups, int heads) {
+  __shared__ float4 tile[(D / 4) * kConvertStride];
+  const long long blocks = tok_groups * heads;
+  for (long long block = blockIdx.x; block < blocks; block += gridDim.x) {
+    const long long grp = block % tok_groups;
+    const int head = (int)(block / tok_groups);
+    const float4* src = reinterpret_cast<const float4*>(acc) + ((long long)head * tok_groups + grp) * (D / 4) * 32;
+    __syncthreads();  // the previous block's reads of the tile are done
+#pragma unroll
+    for (int i = threadIdx.x; i < (D / 4) * 32; i += 256) tile[(i >> 5) * kConvertStride + (i & 31)] = src[i];
+    __syncthreads();
+#pragma unroll
+    for (int i = threadIdx.x; i < 32 * (D / 8); i += 256) {
+      const int tok_in = i / (D / 8), c8 = i % (D / 8);
+      const long long tok = grp * 32 + tok_in;
+      if (tok >= total_q) continue;
+      float f[8];
+      *reinterpret_cast<float4*>(f) = tile[(2 * c8) * kConvertStride + tok_in];
+      *reinterpret_cast<float4*>(f + 4) = tile[(2 * c8 + 1) * kConvertStride + tok_in];
+      *reinterpret_cast<flb::bf16x8*>(dq + tok * dq_stride + q_col0 + head * D + c8 * 8) = flb::pack8(f);
+    }
   }
 }
 
