@@ -1,6 +1,7 @@
 """Layer-level parity with the reference's own modules where its tree is present: rotary frequency tables (default, llama3,
 yarn), the dynamic fp16 loss scaler's state machine, LoRA's forward and gradients against a plain restatement."""
 
+import os
 import pathlib
 import sys
 import types
@@ -8,7 +9,8 @@ import types
 import pytest
 import torch
 
-REFERENCE = pathlib.Path("/root/reference")
+# the reference checkout: $FAST_LLM_REFERENCE, else a `reference` directory beside this repository
+REFERENCE = pathlib.Path(os.environ.get("FAST_LLM_REFERENCE") or pathlib.Path(__file__).resolve().parents[2] / "reference")
 needs_reference = pytest.mark.skipif(not (REFERENCE / "fast_llm" / "layers").is_dir(), reason="reference tree not present")
 
 

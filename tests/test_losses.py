@@ -2,6 +2,7 @@
 PyTorch functions where that tree is present, over 1 and 2 vocabulary shards (Gloo), with and without a loss mask.
 Model of the cases: `tests/layers/test_lm_losses.py:1103-1634` of the reference."""
 
+import os
 import pathlib
 import sys
 
@@ -10,7 +11,8 @@ import torch
 
 from tests.distributed_utils import run_distributed
 
-REFERENCE = pathlib.Path("/root/reference")
+# the reference checkout: $FAST_LLM_REFERENCE, else a `reference` directory beside this repository
+REFERENCE = pathlib.Path(os.environ.get("FAST_LLM_REFERENCE") or pathlib.Path(__file__).resolve().parents[2] / "reference")
 T, V = 48, 96
 
 

@@ -19,7 +19,8 @@ import pytest
 import torch
 import yaml
 
-REFERENCE = pathlib.Path("/root/reference")
+# the reference checkout: $FAST_LLM_REFERENCE, else a `reference` directory beside this repository
+REFERENCE = pathlib.Path(os.environ.get("FAST_LLM_REFERENCE") or pathlib.Path(__file__).resolve().parents[2] / "reference")
 pytestmark = pytest.mark.skipif(not (REFERENCE / "fast_llm" / "cli.py").exists(), reason="reference tree not present")
 
 CONFIG = {
