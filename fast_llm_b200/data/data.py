@@ -31,13 +31,17 @@ class GPTData:
         self._preprocessing = {}
         self._is_setup = False
         self._cache_directory = None
+        self._distributed = None
 
     @property
     def config(self):
         return self._config
 
-    def setup(self, cache_directory: pathlib.Path | None = None) -> None:
+    def setup(self, cache_directory: pathlib.Path | None = None, distributed=None) -> None:
+        """`distributed`: the process groups of the run; needed by datasets that only one rank of a model replica may read
+        (a stream): that rank reads and the documents are broadcast to the ranks that share its batch."""
         self._cache_directory = cache_directory
+        self._distributed = distributed
         self._is_setup = True
 
     def sample_dataset(self, dataset_name: str, preprocessing: dict, num_samples: int) -> None:
@@ -72,7 +76,14 @@ class GPTData:
         sampling = self._sampling[dataset_name]
         pre = self._preprocessing[dataset_name]
         dataset = self._datasets[dataset_name]
-        documents = dataset[index % max(len(dataset), 1)]
+        group = self._shared_batch_group(dataset)
+        if group is None:
+            documents = dataset[index % max(len(dataset), 1)]
+        else:
+            # tensor / pipeline / sequence-data ranks of one replica work on the same batch: the first of them reads it
+            from fast_llm_b200.parallel.collectives import broadcast_object
+
+            documents = broadcast_object(dataset[index % max(len(dataset), 1)] if group.rank() == 0 else None, group, 0)
         batch = LanguageModelBatch.from_documents(documents, sampling.sample_size, sampling.use_loss_masking_spans)
         dc = self._distributed_config
         inputs = batch.get_model_inputs(
@@ -81,6 +92,13 @@ class GPTData:
             sequence_data_rank=dc.sequence_data_rank, pin=pin)
         return inputs
 
+    def _shared_batch_group(self, dataset):
+        """The group to broadcast documents over, for datasets that must be read once per batch (`requires_broadcast`)."""
+        if not getattr(dataset, "requires_broadcast", False) or self._distributed is None:
+            return None
+        group = getattr(self._distributed, "model_and_sequence_data_group", None)
+        return group if group is not None and group.size() > 1 else None
+
     def get_iterator(self, dataset_name: str, *, consumed_samples: int, num_workers: int = 2, prefetch_factor: int | None = None,
                      timeout: float = 60, preprocess: bool = True, pin_memory: bool | None = None) -> typing.Iterator[list[LanguageModelInput]]:
         """Yields, forever, the model inputs of this rank's next micro-batch."""
@@ -88,6 +106,8 @@ class GPTData:
         pin = (dc.use_cuda and torch.cuda.is_available()) if pin_memory is None else pin_memory
         stride, offset = dc.batch_data_parallel, dc.batch_data_rank
         depth = max(num_workers * (prefetch_factor or 2), 1)
+        if self._shared_batch_group(self._datasets[dataset_name]) is not None:
+            num_workers = 0  # the broadcast is a collective: it runs in the calling thread, in step with the other ranks
 
         def generator():
             index = consumed_samples + offset

@@ -104,9 +104,9 @@ class RedisStreamingDataset:
                 raise TimeoutError(f"No document received after {waited:.0f} seconds")
 
     def __getitem__(self, index: int) -> list[LanguageModelDocument]:
-        if index != self._next_index:
-            raise IndexError(f"A stream is read in order: expected sample {self._next_index}, got {index}")
-        self._next_index += 1
+        if index < self._next_index:
+            raise IndexError(f"A stream is read in order: sample {index} was asked for after sample {self._next_index - 1}")
+        self._next_index = index + 1  # batch-data ranks ask for every n-th index: each is its own consumer of the stream
         size = self._sampling.sample_size
         documents, used = [], 0
         while True:

@@ -84,7 +84,7 @@ class Trainer:
         self._runner.setup(distributed, self._optimizer)
         self._runner.set_run(run)
         cache_dir = None if run.experiment_directory is None else run.experiment_directory / "dataset_cache"
-        self._data.setup(cache_dir)
+        self._data.setup(cache_dir, distributed)
         self._schedules = {PhaseType.training: Schedule(self._multi_stage, config.schedule, config.model.distributed, PhaseType.training)}
         self._samples_per_batch = self._schedules[PhaseType.training].samples_per_batch
         preprocessing = self._get_preprocessing(PhaseType.training)

@@ -55,10 +55,47 @@ def test_streaming_dataset_packs_documents_in_arrival_order():
     assert [len(d) for d in first] == [5, 7, 4]  # 16 tokens: exactly full
     assert [len(d) for d in second] == [9, 3]  # the 10-token document opens the third sample
     try:
-        dataset[5]
-        raise AssertionError("out-of-order access must fail")
+        dataset[0]
+        raise AssertionError("going back in a stream must fail")
     except IndexError:
         pass
+
+
+def _shared_stream_rank(rank, world_size):
+    """Two tensor-parallel ranks share every batch: only the first reads the stream (the other rank's client is empty and would
+    time out), the documents reach the second by broadcast."""
+    from fast_llm_b200.data.config import GPTDataConfig, SamplingConfig, StreamingDatasetConfig
+    from fast_llm_b200.data.data import GPTData
+    from fast_llm_b200.data.monitor import DatasetMonitor
+    from fast_llm_b200.data.streaming import REDIS_DATA_STREAM, RedisStreamingDataset, encode_document
+    from fast_llm_b200.parallel.distributed import Distributed
+    from fast_llm_b200.parallel.topology import DistributedConfig
+
+    config = DistributedConfig.from_dict({"world_size": world_size, "rank": rank, "local_world_size": world_size, "tensor_parallel": 2,
+                                          "backend": "gloo", "use_cuda": False})
+    config.validate()
+    distributed = Distributed(config)
+    client = FakeRedis()
+    if rank == 0:
+        for i, n in enumerate([5, 7, 4, 9, 3, 10, 6]):
+            client.xadd(REDIS_DATA_STREAM, encode_document(list(range(i * 100, i * 100 + n))))
+    data = GPTData(GPTDataConfig.from_dict({"datasets": {"training": {"type": "streaming", "timeout": 0.2}}, "micro_batch_size": 15}), config)
+    data.setup(None, distributed)
+    sampling = SamplingConfig.from_dict({"micro_batch_size": 15, "predicted_tokens": 1, "num_samples": 2}).validate()
+    data._datasets["training"] = DatasetMonitor(RedisStreamingDataset(StreamingDatasetConfig.from_dict({"timeout": 0.2}), sampling, client=client), 1e9)
+    data._sampling["training"], data._preprocessing["training"] = sampling, {}
+    iterator = data.get_iterator("training", consumed_samples=0, num_workers=2, pin_memory=False)
+    tokens = [next(iterator)[0].tokens.tolist() for _ in range(2)]
+    distributed.shutdown()
+    return tokens
+
+
+def test_a_stream_is_read_once_per_model_replica():
+    from tests.distributed_utils import run_distributed
+
+    first, second = run_distributed(_shared_stream_rank, 2)
+    assert first == second and len(first[0]) == 15
+    assert first[0][:5] == [0, 1, 2, 3, 4] and first[1][:9] == list(range(300, 309))
 
 
 def _receive(port, received):
