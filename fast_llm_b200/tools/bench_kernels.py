@@ -348,6 +348,35 @@ def profile_gemm_shapes():
     print("profile_gemm_shapes done")
 
 
+def profile_elementwise():
+    """ncu workload: two rounds of every memory-bound kernel of a dense step at [8192, 4096] (ffn 14336, vocabulary 32000), each
+    operand larger than L2 together with its outputs, about 3 GB on the device."""
+    from fast_llm_b200.ops.activation import ActivationType, act_bwd_native
+    from fast_llm_b200.ops.cross_entropy import cross_entropy_forward_backward
+    from fast_llm_b200.ops.normalization import _bwd_native, _fwd_native
+    from fast_llm_b200.ops.rotary import rope_
+
+    t, h, f = 8192, 4096, 14336
+    x = torch.randn(t, h, device="cuda", dtype=torch.bfloat16)
+    d = torch.randn(t, h, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(h, device="cuda", dtype=torch.bfloat16)
+    gu = torch.randn(t, 2 * f, device="cuda", dtype=torch.bfloat16)
+    go = torch.randn(t, f, device="cuda", dtype=torch.bfloat16)
+    qkv = torch.randn(t, 6144, device="cuda", dtype=torch.bfloat16)
+    ang = torch.arange(t, device="cuda", dtype=torch.float64)[:, None] * (10000.0 ** (-torch.arange(0, 128, 2, device="cuda", dtype=torch.float64) / 128))[None]
+    table = torch.cat([ang.cos(), ang.sin()], -1).float().contiguous()
+    logits = torch.randn(t, 32000, device="cuda", dtype=torch.bfloat16)
+    labels = torch.randint(0, 32000, (t,), device="cuda")
+    for _ in range(2):
+        _, y, rstd, _ = _fwd_native(x, d, w, None, 1e-5, False, False)
+        _bwd_native(y, x, w, None, rstd, None, d, False, False, True)
+        act_bwd_native(go, gu, True, ActivationType.silu, True)
+        rope_(qkv, table, None, 40, 128, 128)
+        cross_entropy_forward_backward(logits, labels, 1.0, in_place=False)
+    torch.cuda.synchronize()
+    print("profile_elementwise done")
+
+
 def profile_ssm():
     """ncu workload: two forward + backward passes of the selective scan (8192 x 4096 x 16) and of the gated DeltaNet
     delta rule (8192 tokens x 16 heads x 128), about 1.5 GB on the device."""
@@ -618,6 +647,8 @@ def main(argv):
         return profile_attention()
     if "profile_ssm" in argv:
         return profile_ssm()
+    if "profile_elementwise" in argv:
+        return profile_elementwise()
     if "profile_moe" in argv:
         return profile_moe()
     if "gemm_tiles" in argv:
