@@ -348,6 +348,20 @@ def profile_gemm_shapes():
     print("profile_gemm_shapes done")
 
 
+def profile_gated():
+    """ncu workload: three launches of the layer-1 GEMM with the gated activation in its epilogue, [8192, 4096] x [28672, 4096]^T
+    (operands and outputs about 1 GB)."""
+    from fast_llm_b200.ops.activation import ActivationType
+    from fast_llm_b200.ops.gemm import matmul_nt_gated
+
+    x = torch.randn(8192, 4096, device="cuda", dtype=torch.bfloat16)
+    w1 = torch.randn(28672, 4096, device="cuda", dtype=torch.bfloat16) / 64
+    for _ in range(3):
+        matmul_nt_gated(x, w1, ActivationType.silu.code)
+    torch.cuda.synchronize()
+    print("profile_gated done")
+
+
 def profile_elementwise():
     """ncu workload: two rounds of every memory-bound kernel of a dense step at [8192, 4096] (ffn 14336, vocabulary 32000), each
     operand larger than L2 together with its outputs, about 3 GB on the device."""
@@ -649,6 +663,8 @@ def main(argv):
         return profile_ssm()
     if "profile_elementwise" in argv:
         return profile_elementwise()
+    if "profile_gated" in argv:
+        return profile_gated()
     if "profile_moe" in argv:
         return profile_moe()
     if "gemm_tiles" in argv:
