@@ -235,6 +235,50 @@ def test_mlp_activation(gated, act):
     assert _rel_err(x.grad, xr.grad) < 1e-2
 
 
+@pytest.mark.parametrize("b_mn", [False, True])
+def test_gathered_and_scattered_gemm_modes_on_one_gpu(b_mn):
+    """The two tensor-parallel modes of the CTA-pair GEMM with the peers' side played on the same GPU: arrival words already
+    raised (the gathered GEMM starts at the "local" chunk and must still produce every row), and per-owner output maps that point
+    at two local buffers (row blocks of chunk c must land in buffer c, nothing else touched)."""
+    import ctypes
+
+    from fast_llm_b200.ops import _lib
+    from fast_llm_b200.ops.gemm import check_device_errors
+
+    torch.manual_seed(0)
+    lib = _lib.get_lib()
+    rows, world, k, n = 512, 2, 384, 640
+    a = torch.randn(rows * world, k, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn((k, n) if b_mn else (n, k), device="cuda", dtype=torch.bfloat16) / k**0.5
+    reference = a.float() @ (w.float() if b_mn else w.float().t())
+    # gathered: chunk 1 is "local", the arrival word of chunk 0 already holds the call number
+    flags = torch.tensor([7, 0] + [0] * 14, device="cuda", dtype=torch.int32)
+    out = torch.full((rows * world + 2, n), 3.0, device="cuda", dtype=torch.bfloat16)
+    _lib.check(lib.flb_gemm_gathered_bf16(a.data_ptr(), w.data_ptr(), out[1:-1].data_ptr(), rows * world, n, k, k, w.stride(0), n, int(b_mn),
+                                          flags.data_ptr(), 7, rows, 1, _lib.stream_ptr()), "flb_gemm_gathered_bf16")
+    assert _rel_err(out[1:-1], reference) < 5e-3 and _max_err(out[1:-1], reference) < 0.1
+    assert (out[0] == 3).all() and (out[-1] == 3).all()
+    # scattered: chunk c -> buffer c
+    buffers = torch.full((world, rows + 2, n), 5.0, device="cuda", dtype=torch.bfloat16)
+    host = torch.empty(world * 128 + 64, dtype=torch.uint8)
+    shift = (-host.data_ptr()) % 64
+    aligned = host[shift : shift + world * 128]
+    destinations = (ctypes.c_void_p * world)(*[buffers[c, 1:-1].data_ptr() for c in range(world)])
+    _lib.check(lib.flb_gemm_scatter_maps(aligned.data_ptr(), destinations, world, rows, n, n), "flb_gemm_scatter_maps")
+    device_buffer = torch.empty(world * 128 + 64, dtype=torch.uint8, device="cuda")
+    device_shift = (-device_buffer.data_ptr()) % 64
+    maps = device_buffer[device_shift : device_shift + world * 128]
+    maps.copy_(aligned)
+    torch.cuda.synchronize()
+    _lib.check(lib.flb_gemm_scatter_bf16(a.data_ptr(), w.data_ptr(), maps.data_ptr(), rows * world, n, k, k, w.stride(0), int(b_mn), rows, 1,
+                                         _lib.stream_ptr()), "flb_gemm_scatter_bf16")
+    torch.cuda.synchronize()
+    check_device_errors()
+    for c in range(world):
+        assert _rel_err(buffers[c, 1:-1], reference[c * rows : (c + 1) * rows]) < 5e-3, c
+        assert (buffers[c, 0] == 5).all() and (buffers[c, -1] == 5).all()
+
+
 def test_gemm_reuses_tensor_maps_for_repeated_operands():
     from fast_llm_b200.ops.gemm import matmul_nt, tensor_map_cache_stats
 
