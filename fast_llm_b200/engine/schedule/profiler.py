@@ -127,13 +127,17 @@ class ScheduleProfiler:
                            "cpu_start_ms": round(cpu_start, 4), "cpu_ms": round(cpu_ms, 4)})
             by_stream.setdefault(span.stream, []).append((gpu_start, gpu_start + gpu_ms))
         per_type: dict[str, float] = {}
+        host_per_type: dict[str, float] = {}
         for e in events:
             per_type[e["event_type"]] = per_type.get(e["event_type"], 0.0) + e["gpu_ms"]
+            host_per_type[e["event_type"]] = host_per_type.get(e["event_type"], 0.0) + e["cpu_ms"]
         compute = by_stream.get("compute", [])
         step_ms = max((b for spans in by_stream.values() for _, b in spans), default=0.0)
         summary = {
             "step_ms": round(step_ms, 3),
             "gpu_ms_by_event_type": {k: round(v, 3) for k, v in sorted(per_type.items())},
+            # host time spent queueing the work of each event type: close to the device time means the host is the limiter
+            "cpu_ms_by_event_type": {k: round(v, 3) for k, v in sorted(host_per_type.items())},
             "busy_ms_by_stream": {k: round(_union_length(v), 3) for k, v in sorted(by_stream.items())},
             "exposed_ms_by_stream": {k: round(_subtract(v, compute), 3) for k, v in sorted(by_stream.items()) if k != "compute"},
             "compute_stream_idle_ms": round(step_ms - _union_length(compute), 3),
@@ -145,6 +149,8 @@ class ScheduleProfiler:
         s = table["summary"]
         lines = [f"Schedule profile, rank {table['rank']}, {table['phase']} step {table['iteration']}: {s['step_ms']:.2f} ms"]
         lines.append("  device ms by event:  " + ", ".join(f"{k} {v:.2f}" for k, v in s["gpu_ms_by_event_type"].items()))
+        if "cpu_ms_by_event_type" in s:
+            lines.append("  host ms by event:    " + ", ".join(f"{k} {v:.2f}" for k, v in s["cpu_ms_by_event_type"].items()))
         lines.append("  busy ms by stream:   " + ", ".join(f"{k} {v:.2f}" for k, v in s["busy_ms_by_stream"].items()))
         lines.append("  exposed (not under compute): " + (", ".join(f"{k} {v:.2f}" for k, v in s["exposed_ms_by_stream"].items()) or "-")
                      + f"; compute stream idle {s['compute_stream_idle_ms']:.2f}")
