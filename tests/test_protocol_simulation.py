@@ -33,11 +33,14 @@ class Rank:
         self.reading = [None, None]  # per half: the call a consumer is reading right now
         self.consumed = 0  # consumers finish in order on the main stream
         self.lock = threading.Lock()
+        self.errors: list = []  # shared by all ranks of a run
 
 
-def _wait(predicate, what: str):
+def _wait(predicate, what: str, errors: list):
     start = time.monotonic()
     while not predicate():
+        if errors:
+            raise Violation("stopped: another rank reported a violation")  # like the error word: everybody gives up
         if time.monotonic() - start > DEADLINE:
             raise Violation(f"deadline: {what}")
         time.sleep(0)
@@ -55,7 +58,7 @@ def _push(ranks, me: Rank, call: int, rng, meet: bool):
     if meet:
         for peer in ranks:
             if peer is not me:
-                _wait(lambda p=peer: me.begun[p.index] >= call, f"rank {me.index} waits for the push of call {call} on rank {peer.index}")
+                _wait(lambda p=peer: me.begun[p.index] >= call, f"rank {me.index} waits for the push of call {call} on rank {peer.index}", me.errors)
     for peer in ranks:
         if peer is me:
             continue
@@ -74,7 +77,7 @@ def _consume(ranks, me: Rank, call: int, rng):
     half = call & 1
     for peer in ranks:
         if peer is not me:
-            _wait(lambda p=peer: me.arrival[half][p.index] >= call, f"rank {me.index} waits for rows of rank {peer.index}, call {call}")
+            _wait(lambda p=peer: me.arrival[half][p.index] >= call, f"rank {me.index} waits for rows of rank {peer.index}, call {call}", me.errors)
     with me.lock:
         me.reading[half] = call
     _jitter(rng, 0.004)
@@ -86,14 +89,14 @@ def _consume(ranks, me: Rank, call: int, rng):
         me.consumed = call
 
 
-def _main_stream(ranks, me: Rank, program, seed: int, meet: bool, errors: list):
+def _main_stream(ranks, me: Rank, program, seed: int, meet: bool, errors: list, slow: float = 1.0):
     """`program`: list of ("start", call) / ("consume", call) in main-stream order.  A push runs on the side stream: after every
     earlier push of this rank and after everything queued on the main stream before its start."""
     rng = random.Random(seed)
     side = None
     try:
         for kind, call in program:
-            _jitter(rng)
+            _jitter(rng, 0.002 * slow)
             if kind == "start":
                 previous = side
 
@@ -109,6 +112,8 @@ def _main_stream(ranks, me: Rank, program, seed: int, meet: bool, errors: list):
                 side = threading.Thread(target=run)
                 side.start()
             else:
+                if slow > 1:
+                    time.sleep(0.002 * slow)  # a rank that lags behind its peers
                 _consume(ranks, me, call, rng)
         if side is not None:
             side.join(DEADLINE)
@@ -130,10 +135,13 @@ def _program(calls: int, paired: bool):
     return program
 
 
-def _run(world: int, calls: int, paired: bool, meet: bool, seed: int):
+def _run(world: int, calls: int, paired: bool, meet: bool, seed: int, slow_last_rank: float = 1.0):
     ranks = [Rank(i, world) for i in range(world)]
     errors: list = []
-    threads = [threading.Thread(target=_main_stream, args=(ranks, rank, _program(calls, paired), seed * 17 + rank.index, meet, errors)) for rank in ranks]
+    for rank in ranks:
+        rank.errors = errors
+    threads = [threading.Thread(target=_main_stream, args=(ranks, rank, _program(calls, paired), seed * 17 + rank.index, meet, errors,
+                                                             slow_last_rank if rank.index == world - 1 else 1.0)) for rank in ranks]
     for t in threads:
         t.start()
     for t in threads:
@@ -146,7 +154,7 @@ def _run(world: int, calls: int, paired: bool, meet: bool, seed: int):
 @pytest.mark.parametrize("paired", [False, True])
 def test_gather_protocol_holds_under_random_interleavings(world, paired):
     for seed in range(6):
-        errors = _run(world, 14, paired, True, seed)
+        errors = _run(world, 14, paired, True, seed, slow_last_rank=3.0 if seed % 2 else 1.0)
         assert not errors, errors[0]
 
 
@@ -156,7 +164,7 @@ def test_the_checks_catch_a_protocol_without_the_meeting():
     above proves nothing).  With one gather in flight the arrival words alone order everything, so that case cannot fail."""
     found = False
     for seed in range(40):
-        if _run(3, 12, True, False, seed):
+        if _run(3, 8, True, False, seed, slow_last_rank=4.0):
             found = True
             break
     assert found
