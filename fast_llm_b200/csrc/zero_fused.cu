@@ -98,6 +98,36 @@ rs_reduce_kernel(PeerPtrs grads, int rank, int world, long long shard, float sca
   if (threadIdx.x == 0 && sumsq_partial) sumsq_partial[blockIdx.x] = t;
 }
 
+// The same reduction with the sum formed inside NVSwitch: `mc` is the MULTICAST address of the gradient buffer (one address that
+// stands for the same offset in every rank's symmetric allocation); `multimem.ld_reduce` returns the fp32 sum over all ranks of
+// the 16 bytes it names, so a rank pulls its slice once instead of once per peer.  The order of the additions is the switch's,
+// not rank order: results can differ from rs_reduce_kernel in the last bit, and this path is an option, off by default.
+__global__ void __launch_bounds__(kThreads)
+rs_reduce_multimem_kernel(const float* __restrict__ mc, int rank, long long shard, float scale, float* __restrict__ grad_shard,
+                          int accumulate, float* __restrict__ sumsq_partial, const int* err_word) {
+  __shared__ float scratch[32];
+  if (wait_failed(err_word)) return;
+  const long long nvec = shard >> 2;
+  const float4* src = reinterpret_cast<const float4*>(mc) + (long long)rank * nvec;
+  float ss = 0.f;
+  for (long long i = blockIdx.x * (long long)kThreads + threadIdx.x; i < nvec; i += (long long)gridDim.x * kThreads) {
+    float4 acc;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(acc.x), "=f"(acc.y), "=f"(acc.z), "=f"(acc.w)
+                 : "l"(src + i)
+                 : "memory");
+    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+    if (accumulate) {
+      const float4 o = reinterpret_cast<const float4*>(grad_shard)[i];
+      acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w;
+    }
+    reinterpret_cast<float4*>(grad_shard)[i] = acc;
+    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+  }
+  const float t = block_sum(ss, scratch);
+  if (threadIdx.x == 0 && sumsq_partial) sumsq_partial[blockIdx.x] = t;
+}
+
 // AdamW on n fp32 elements; the bf16 result goes to element offset `lp_offset` of every rank's weight buffer.
 __global__ void __launch_bounds__(kThreads)
 adam_push_kernel(float* __restrict__ w, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
@@ -337,6 +367,18 @@ FLB_API int flb_rs_reduce(const void* const* grad_ptrs, int grad_dtype, int rank
     rs_reduce_kernel<float><<<blocks, kThreads, 0, stream>>>(grads, rank, world, shard, scale, grad_shard, accumulate, sumsq_partial, err_word);
   else
     rs_reduce_kernel<__nv_bfloat16><<<blocks, kThreads, 0, stream>>>(grads, rank, world, shard, scale, grad_shard, accumulate, sumsq_partial, err_word);
+  FLB_CHECK_LAUNCH();
+  return FLB_OK;
+}
+
+// flb_rs_reduce through the multicast mapping of the fp32 gradient buffer (`multicast_grads`: the multicast address of the
+// buffer's first element).  Same contract: between two barriers; shard % 4 == 0.
+FLB_API int flb_rs_reduce_multimem(const void* multicast_grads, int rank, int world, long long shard, float scale, float* grad_shard,
+                                   int accumulate, float* sumsq_partial, const int* err_word, cudaStream_t stream) {
+  if (shard <= 0) return FLB_OK;
+  if ((shard % 4) || multicast_grads == nullptr || rank < 0 || rank >= world || (reinterpret_cast<uintptr_t>(multicast_grads) & 15)) return FLB_ERR_SHAPE;
+  rs_reduce_multimem_kernel<<<flb_rs_reduce_blocks(), kThreads, 0, stream>>>((const float*)multicast_grads, rank, shard, scale, grad_shard,
+                                                                            accumulate, sumsq_partial, err_word);
   FLB_CHECK_LAUNCH();
   return FLB_OK;
 }

@@ -81,6 +81,7 @@ _SIGNATURES = {
     "flb_tp_push": [_p, _ll, _p, _ll, _ll, _ll, _i, _i, ctypes.c_uint, _p, _p, _i, _p],
     "flb_symm_barrier": [_p, _i, _i, _i, ctypes.c_uint, _p, _p],
     "flb_rs_reduce_blocks": [],
+    "flb_rs_reduce_multimem": [_p, _i, _i, _ll, _f, _p, _i, _p, _p, _p],
     "flb_symm_set_barrier_limit": [_ll],
     "flb_rs_reduce": [_p, _i, _i, _i, _ll, _f, _p, _i, _p, _p, _p],
     "flb_slot_sum_bf16": [_p, _p, _i, _ll, _p, _p],

@@ -7,6 +7,7 @@ own kernels (`csrc/zero_fused.cu`).  Device-side waits are bounded and report th
 """
 
 import ctypes
+import os
 import logging
 
 import torch
@@ -65,6 +66,9 @@ class SymmetricArena:
         self._handle = symm_mem.rendezvous(self.buffer, group)
         self.peer_ptrs = [int(p) for p in self._handle.buffer_ptrs]
         assert self.peer_ptrs[self.rank] == self.buffer.data_ptr()
+        # one address for the same offset in every rank's allocation (NVLink multicast through NVSwitch); 0 where the fabric
+        # or the driver has none
+        self.multicast_ptr = int(getattr(self._handle, "multicast_ptr", 0) or 0)
         pad_bytes = lib.flb_symm_signal_pad_bytes(_SIGNAL_SLOTS)
         self._pad = symm_mem.empty(pad_bytes, dtype=torch.uint8, device=device)
         self._pad.zero_()
@@ -107,9 +111,23 @@ def symmetric_memory_available(group, device) -> bool:
         return False
 
 
+def multimem_reduction_enabled() -> bool:
+    """`FLB_ZERO_MULTIMEM=1`: gradient reduce-scatter through `multimem.ld_reduce` (in-switch sums).  Off by default: the order of
+    the additions is the switch's, so results are not bit-identical to the rank-ordered kernel, and a rank that dies while its
+    memory is bound to a multicast object disturbs its peers (runs that test failures keep this off)."""
+    return os.environ.get("FLB_ZERO_MULTIMEM", "0") == "1"
+
+
 def rs_reduce(arena: SymmetricArena, grad_buffer: torch.Tensor, grad_shard: torch.Tensor, shard_size: int, scale: float,
               accumulate: bool, sumsq_partial: torch.Tensor | None) -> None:
     """grad_shard (+)= scale * sum over ranks of their grad_buffer[rank*shard : (rank+1)*shard] (peer loads)."""
+    if multimem_reduction_enabled() and arena.multicast_ptr and grad_buffer.dtype == torch.float32:
+        # the sum is formed inside NVSwitch: this rank pulls its slice once instead of once per peer
+        _lib.check(_lib.get_lib().flb_rs_reduce_multimem(arena.multicast_ptr + arena.offset_of(grad_buffer), arena.rank, arena.world_size, shard_size,
+                                                         scale, grad_shard.data_ptr(), int(accumulate), _lib.ptr(sumsq_partial),
+                                                         arena.error_word.data_ptr(), _lib.stream_ptr()), "flb_rs_reduce_multimem")
+        _lib.count_launch()
+        return
     ptrs = arena.peer_pointer_array(arena.offset_of(grad_buffer))
     dtype_code = 0 if grad_buffer.dtype == torch.float32 else 1
     _lib.check(_lib.get_lib().flb_rs_reduce(ptrs, dtype_code, arena.rank, arena.world_size, shard_size, scale,

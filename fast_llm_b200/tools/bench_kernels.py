@@ -622,6 +622,15 @@ def bench_zero(results):
     low = torch.empty(shard, dtype=torch.bfloat16, device=device)
     out = {"op": "zero_kernels", "world": world, "elements": elements}
     out["rs_reduce_ms"] = timed(fused_reduce)
+    if arena.multicast_ptr:
+        # the same reduction with the sums formed inside NVSwitch (multimem.ld_reduce): one pull of the slice instead of one per peer
+        rank_ordered = grad_shard.clone()
+        os.environ["FLB_ZERO_MULTIMEM"] = "1"
+        out["rs_reduce_multimem_ms"] = timed(fused_reduce)
+        out["rs_reduce_multimem_max_abs_difference"] = (grad_shard - rank_ordered).abs().max().item()
+        os.environ["FLB_ZERO_MULTIMEM"] = "0"
+    else:
+        out["rs_reduce_multimem_ms"] = None  # no multicast mapping on this fabric / driver
     out["nccl_reduce_scatter_ms"] = timed(lambda: torch.distributed.reduce_scatter_tensor(grad_shard, grads, group=group))
     out["adam_push_ms"] = timed(fused_update)
     out["nccl_all_gather_ms"] = timed(lambda: torch.distributed.all_gather_into_tensor(gathered, low, group=group))

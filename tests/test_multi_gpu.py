@@ -407,3 +407,43 @@ def test_fused_collectives_on_four_ranks():
         for d_loss, d_z, d_grad, d_loss_ref, d_grad_ref in per_rank:
             assert d_loss < 1e-4 and d_z < 1e-2 and d_grad < 1e-3, per_rank
             assert d_loss_ref < 2e-2 and d_grad_ref < 2e-2, per_rank
+
+
+def _multimem_rank_main(rank, world_size):
+    import os
+
+    import torch
+
+    from fast_llm_b200.parallel.symmetric import SymmetricArena, rs_reduce
+
+    torch.cuda.set_device(rank)
+    torch.distributed.init_process_group("nccl", rank=rank, world_size=world_size, device_id=torch.device("cuda", rank))
+    device = torch.device("cuda", rank)
+    elements = 8 * 1024 * 1024
+    shard = elements // world_size
+    arena = SymmetricArena(elements * 4, torch.distributed.group.WORLD, device)
+    grads = arena.buffer.view(torch.float32)
+    grads.copy_(torch.randn(elements, device=device, generator=torch.Generator(device=device).manual_seed(rank)))
+    outputs = []
+    for flag in ("0", "1"):
+        os.environ["FLB_ZERO_MULTIMEM"] = flag
+        out = torch.zeros(shard, device=device)
+        arena.barrier(0)
+        rs_reduce(arena, grads, out, shard, 1.0 / world_size, False, None)
+        arena.barrier(0)
+        outputs.append(out)
+    os.environ["FLB_ZERO_MULTIMEM"] = "0"
+    torch.cuda.synchronize()
+    arena.check_errors()
+    result = (bool(arena.multicast_ptr), (outputs[0] - outputs[1]).abs().max().item(), outputs[0].abs().max().item())
+    torch.distributed.barrier()
+    return result
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_in_switch_gradient_reduction_agrees_with_the_rank_ordered_kernel():
+    """`FLB_ZERO_MULTIMEM=1`: the slice sums come from `multimem.ld_reduce` (one pull through NVSwitch); same values as the
+    peer-load kernel up to the order of the fp32 additions.  Without a multicast mapping the option changes nothing."""
+    for available, difference, magnitude in run_distributed(_multimem_rank_main, 2, timeout=600):
+        assert magnitude > 0.1
+        assert difference <= (1e-6 * magnitude if available else 0.0) + 1e-7
