@@ -110,12 +110,15 @@ rs_reduce_multimem_kernel(const float* __restrict__ mc, int rank, long long shar
   const long long nvec = shard >> 2;
   const float4* src = reinterpret_cast<const float4*>(mc) + (long long)rank * nvec;
   float ss = 0.f;
-  for (long long i = blockIdx.x * (long long)kThreads + threadIdx.x; i < nvec; i += (long long)gridDim.x * kThreads) {
-    float4 acc;
+  auto pull = [&](long long i) {
+    float4 v;
     asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
-                 : "=f"(acc.x), "=f"(acc.y), "=f"(acc.z), "=f"(acc.w)
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
                  : "l"(src + i)
                  : "memory");
+    return v;
+  };
+  auto finish = [&](long long i, float4 acc) {
     acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
     if (accumulate) {
       const float4 o = reinterpret_cast<const float4*>(grad_shard)[i];
@@ -123,7 +126,15 @@ rs_reduce_multimem_kernel(const float* __restrict__ mc, int rank, long long shar
     }
     reinterpret_cast<float4*>(grad_shard)[i] = acc;
     ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+  };
+  const long long stride = (long long)gridDim.x * kThreads;
+  long long i = blockIdx.x * (long long)kThreads + threadIdx.x;
+  // four reductions in flight per thread: a round trip through the switch is several microseconds
+  for (; i + 3 * stride < nvec; i += 4 * stride) {
+    const float4 a = pull(i), b = pull(i + stride), c = pull(i + 2 * stride), d = pull(i + 3 * stride);
+    finish(i, a); finish(i + stride, b); finish(i + 2 * stride, c); finish(i + 3 * stride, d);
   }
+  for (; i < nvec; i += stride) finish(i, pull(i));
   const float t = block_sum(ss, scratch);
   if (threadIdx.x == 0 && sumsq_partial) sumsq_partial[blockIdx.x] = t;
 }
