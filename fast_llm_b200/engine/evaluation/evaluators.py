@@ -45,8 +45,12 @@ class FastLLMLmEvalWrapper:
     (anything with `.args`, or the argument tuple itself)."""
 
     def __init__(self, model, tokenizer, *, batch_size: int = 8, max_length: int | None = None, max_new_tokens: int = 256,
-                 add_bos_token: bool = False):
+                 add_bos_token: bool = False, data_group=None):
+        """`data_group`: the process group of the model replicas (batch-data parallel).  Every replica's coordinator runs the same
+        harness code on the same requests; with a group each scores / generates every n-th request and the results are
+        exchanged, so the replicas share the work instead of repeating it."""
         self._model, self._tokenizer = model, tokenizer
+        self._data_group = data_group if (data_group is not None and data_group.size() > 1) else None
         self.batch_size, self._max_length = batch_size, max_length or 2**30
         self._max_new_tokens, self._add_bos = max_new_tokens, add_bos_token
         self.device = model.fast_llm_model.distributed.device
@@ -116,7 +120,25 @@ class FastLLMLmEvalWrapper:
             return context_tokens, whole
         return context_tokens, whole[len(context_tokens):]
 
+    def _shared(self, items: list, compute) -> list:
+        """`compute(items)` with the items dealt out over the model replicas (round robin) and the results put back in order."""
+        if self._data_group is None:
+            return compute(items)
+        rank, size = self._data_group.rank(), self._data_group.size()
+        mine = list(range(rank, len(items), size))
+        local = compute([items[i] for i in mine]) if mine else []
+        gathered: list = [None] * size
+        torch.distributed.all_gather_object(gathered, (mine, local), group=self._data_group)
+        out: list = [None] * len(items)
+        for indices, values in gathered:
+            for index, value in zip(indices, values):
+                out[index] = value
+        return out
+
     def _score(self, sequences: list[tuple[list[int], list[int]]]) -> list[tuple[float, bool]]:
+        return self._shared(sequences, self._score_local)
+
+    def _score_local(self, sequences: list[tuple[list[int], list[int]]]) -> list[tuple[float, bool]]:
         """For each (context, continuation): sum of continuation log-probabilities, and whether it is the greedy choice."""
         results: list[tuple[float, bool] | None] = [None] * len(sequences)
         order = sorted(range(len(sequences)), key=lambda i: -(len(sequences[i][0]) + len(sequences[i][1])))
@@ -155,6 +177,9 @@ class FastLLMLmEvalWrapper:
         return self._score(pairs)
 
     def loglikelihood_rolling(self, requests) -> list[float]:
+        return self._shared(list(requests), self._rolling_local)
+
+    def _rolling_local(self, requests) -> list[float]:
         """Log-likelihood of whole documents, in windows of the context limit (each token scored once)."""
         out = []
         for request in requests:
@@ -166,12 +191,15 @@ class FastLLMLmEvalWrapper:
             while position < len(tokens):
                 targets = tokens[position : position + window]
                 context = prefix if position == 0 else tokens[max(position - 1, 0) : position]
-                total += self._score([(context, targets)])[0][0]
+                total += self._score_local([(context, targets)])[0][0]
                 position += len(targets)
             out.append(total)
         return out
 
     def generate_until(self, requests) -> list[str]:
+        return self._shared(list(requests), self._generate_local)
+
+    def _generate_local(self, requests) -> list[str]:
         """Requests are grouped by their generation options and sorted by prompt length, then generated `batch_size` at a time
         (left-padded); every answer is cut at the first of its stop strings."""
         prepared = []
@@ -266,7 +294,7 @@ class LmEvalEvaluator(Evaluator):
         self._hf_model = HuggingfaceGPTModelForCausalLM(trainer.multi_stage)
         self._wrapper = FastLLMLmEvalWrapper(self._hf_model, self._config.tokenizer.get_tokenizer(), batch_size=self._config.batch_size,
                                              max_length=self._config.max_length, max_new_tokens=self._config.max_new_tokens,
-                                             add_bos_token=self._config.add_bos_token)
+                                             add_bos_token=self._config.add_bos_token, data_group=getattr(distributed, "batch_data_group", None))
 
     def run(self, completed_steps: int, force: bool = False) -> dict | None:
         if not (force or self._config.enabled(completed_steps)):

@@ -73,3 +73,48 @@ def test_batched_generation_matches_one_by_one_and_harness_arguments_parse(token
                                       "--gen_kwargs", "temperature=0,top_p=1", "bootstrap_iters=0", "--log-samples"])
     assert parsed == {"tasks": ["hellaswag", "arc_easy"], "num_fewshot": 5, "limit": 0.25, "apply_chat_template": True,
                       "gen_kwargs": {"temperature": 0, "top_p": 1}, "bootstrap_iters": 0, "log_samples": True}
+
+
+def _replica_rank(rank, world_size, tokenizer_file):
+    """Two data-parallel replicas of the same model share the harness' requests."""
+    from fast_llm_b200.data.config import TokenizerConfig
+    from fast_llm_b200.engine.evaluation.evaluators import FastLLMLmEvalWrapper
+    from fast_llm_b200.engine.inference.huggingface import HuggingfaceGPTModelForCausalLM
+
+    trainer, distributed = build_trainer(tiny_trainer_config({
+        ("model", "distributed", "world_size"): world_size, ("model", "distributed", "rank"): rank, ("model", "distributed", "local_world_size"): world_size,
+        ("model", "distributed", "backend"): "gloo", ("model", "distributed", "reproducible_init"): True}))
+    model = HuggingfaceGPTModelForCausalLM(trainer._multi_stage)
+    tokenizer = TokenizerConfig.from_dict({"path": tokenizer_file}).get_tokenizer()
+    requests = [("the quick brown", " fox jumps"), ("hello", " world"), ("pack my box with", " five"), ("", "hello world"), ("a b c", " d")]
+    prompts = [("the quick", {"max_gen_toks": 3}), ("hello there", {"max_gen_toks": 3}), ("pack", {"max_gen_toks": 3})]
+    shared = FastLLMLmEvalWrapper(model, tokenizer, batch_size=2, data_group=distributed.batch_data_group)
+    alone = FastLLMLmEvalWrapper(model, tokenizer, batch_size=2)
+    counted = {"forwards": 0}
+    original = model.forward
+
+    def counting_forward(*args, **kwargs):
+        counted["forwards"] += 1
+        return original(*args, **kwargs)
+
+    model.forward = counting_forward
+    together = (shared.loglikelihood(requests), shared.loglikelihood_rolling([("the quick brown fox",), ("hello world",)]), shared.generate_until(prompts))
+    shared_forwards = counted["forwards"]
+    counted["forwards"] = 0
+    separately = (alone.loglikelihood(requests), alone.loglikelihood_rolling([("the quick brown fox",), ("hello world",)]), alone.generate_until(prompts))
+    alone_forwards = counted["forwards"]
+    distributed.shutdown()
+    return together, separately, shared_forwards, alone_forwards
+
+
+def test_replicas_share_the_requests(tokenizer_path):  # noqa: F811
+    from tests.distributed_utils import run_distributed
+
+    results = run_distributed(_replica_rank, 2, str(tokenizer_path))
+    for together, separately, shared_forwards, alone_forwards in results:
+        for a, b in zip(together[0], separately[0]):
+            assert abs(a[0] - b[0]) < 1e-4 and a[1] == b[1]
+        assert all(abs(a - b) < 1e-4 for a, b in zip(together[1], separately[1]))
+        assert together[2] == separately[2]
+        assert shared_forwards < alone_forwards  # each replica ran only its share
+    assert results[0][0] == results[1][0]
