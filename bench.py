@@ -432,8 +432,9 @@ def run_reference(args):
         if not dynamo_ok:
             os.environ["TORCHDYNAMO_DISABLE"] = "1"
         compat = None
-        if world > 1 and not args.no_reference_compat:
-            # at one GPU the reference runs out of memory before its optimizer is reached: nothing to adapt
+        if not args.no_reference_compat:
+            # (at one GPU and full depth the reference runs out of memory before its optimizer is reached; reduced-depth
+            # comparisons on one GPU do reach it)
             _install_reference_adamw_compat()
             compat = REFERENCE_COMPAT
         import fast_llm.data.auto  # noqa: F401
