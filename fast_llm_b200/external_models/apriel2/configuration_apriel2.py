@@ -1,4 +1,4 @@
-"""Configuration of Apriel2 (text): a decoder whose blocks name their mixer by type.
+"""Configuration of Apriel2: a decoder whose blocks name their mixer by type; the multimodal variant adds a vision encoder.
 
 Stand-alone file: it is copied next to exported checkpoints and loaded by `transformers` with `trust_remote_code`.
 
@@ -7,6 +7,11 @@ Stand-alone file: it is copied next to exported checkpoints and loaded by `trans
     BLOCK    {"mixer": MIXER, "mlp": {"type": "mlp", "intermediate_size", "gated", "activation", "add_linear_biases"},
               "normalization": {"type": "rms_norm", "epsilon"}}
     MIXER    {"type": "attention" | "mamba" | "gdn" | "kda" | "stochastic", ...}
+
+`Apriel2Config` (model type `apriel2`) adds `image_token_index` and
+    vision_encoder {"hidden_size", "embeddings": {"patch_height", "patch_width", "normalization"},
+                    "encoder": {"type": "fixed", "num_blocks", "block": BLOCK (non-causal attention, `pixtral_2d` rotary)},
+                    "adapter": {"type": "mlp", "intermediate_size", "activation", "add_linear_biases"}}
 """
 
 from transformers import PretrainedConfig
@@ -44,3 +49,12 @@ class Apriel2TextConfig(PretrainedConfig):
             return [decoder["block"]] * decoder["num_blocks"]
         pattern = decoder["pattern"]
         return [decoder["blocks"][pattern[i % len(pattern)]] for i in range(decoder["num_blocks"])]
+
+
+class Apriel2Config(Apriel2TextConfig):
+    model_type = "apriel2"
+
+    def __init__(self, vision_encoder: dict | None = None, image_token_index: int | None = None, **kwargs):
+        self.vision_encoder = vision_encoder
+        self.image_token_index = image_token_index
+        super().__init__(**kwargs)

@@ -199,6 +199,13 @@ class Apriel2MultimodalHuggingfaceCheckpointHandler(HuggingfaceStateDictCheckpoi
         return MultiModalModelConfig
 
     @classmethod
+    def get_extra_files(cls):
+        """The stand-alone Apriel2 modelling files hold the multimodal classes the `auto_map` below names."""
+        from fast_llm_b200.models.gpt.conversion import apriel2 as text
+
+        return text.Apriel2HuggingfaceCheckpointHandler.get_extra_files()
+
+    @classmethod
     def export_config(cls, c) -> dict:
         from fast_llm_b200.models.gpt.conversion import apriel2 as text
 

@@ -226,3 +226,76 @@ def test_llava_hybrid_modeling_code_loads_the_export_and_reproduces_the_logits(t
     with torch.no_grad():
         theirs = external(input_ids=with_image[None, :-1], pixel_values=image, image_sizes=[(8, 12)]).logits[0]
     torch.testing.assert_close(mine, theirs, rtol=5e-4, atol=5e-4)
+
+
+def test_apriel2_multimodal_modeling_code_loads_the_export_and_reproduces_the_logits(tmp_path):
+    """The stand-alone Apriel2 modelling files shipped with an `apriel2` export hold the classes its `auto_map` names, load every
+    tensor of it, and give this framework's logits for text alone and for text with two images of different sizes."""
+    import json
+
+    from fast_llm_b200.data.document import LanguageModelBatch, LanguageModelDocument
+    from fast_llm_b200.engine.checkpoint.config import CheckpointSaveConfig
+    from fast_llm_b200.external_models.apriel2 import modeling_apriel2
+    from fast_llm_b200.parallel.topology import PhaseType
+
+    trainer, _ = build_trainer(_config({("model", "base_model", "image_token_index"): 7}))
+    path = tmp_path / "apriel2"
+    trainer.multi_stage.save_checkpoint(CheckpointSaveConfig(path=path, format="apriel2"))
+    auto_map = json.loads((path / "config.json").read_text())["auto_map"]
+    for target in auto_map.values():
+        file, name = target.split(".")
+        assert (path / f"{file}.py").exists(), target
+        assert f"class {name}(" in (path / f"{file}.py").read_text(), target
+    external, info = modeling_apriel2.Apriel2ForConditionalGeneration.from_pretrained(str(path), torch_dtype=torch.float32, output_loading_info=True)
+    assert not info["missing_keys"] and not info["unexpected_keys"], info
+    external.eval()
+
+    model = trainer._multi_stage.base_model
+    for stage in trainer._multi_stage.stages:
+        stage.restore_parameters()
+
+    def ours(tokens, **image):
+        document = LanguageModelDocument(tokens=tokens, **image)
+        batch = LanguageModelBatch.from_documents([document], tokens.numel())
+        inputs = batch.get_model_inputs(micro_batch_size=tokens.numel() - 1)
+        (ids, kwargs), = model.preprocess_batch(inputs, phase=PhaseType.inference, iteration=0)
+        kwargs["return_logits"] = True
+        hidden = None
+        with torch.no_grad():
+            for layer in model.get_layers():
+                hidden = layer.forward(ids if hidden is None else hidden, kwargs)
+        return kwargs["logits"]
+
+    torch.manual_seed(0)
+    tokens = torch.randint(8, 512, (41,))
+    with torch.no_grad():
+        theirs = external(input_ids=tokens[None, :-1]).logits[0]
+    torch.testing.assert_close(ours(tokens), theirs, rtol=2e-4, atol=2e-4)
+
+    # a 2 x 3 grid of 4 x 4 patches at tokens 5..10 and a 1 x 2 grid at tokens 20..21
+    first, second = torch.randint(0, 256, (3, 8, 12), dtype=torch.uint8), torch.randint(0, 256, (3, 4, 8), dtype=torch.uint8)
+    patches = torch.cat([first.view(3, 2, 4, 3, 4).permute(1, 3, 0, 2, 4).reshape(6, 3, 4, 4),
+                         second.view(3, 1, 4, 2, 4).permute(1, 3, 0, 2, 4).reshape(2, 3, 4, 4)])
+    coordinates = torch.tensor([[r, c] for r in range(2) for c in range(3)] + [[0, 0], [0, 1]])
+    positions = torch.cat([torch.arange(5, 11), torch.arange(20, 22)])
+    with_image = tokens.clone()
+    with_image[positions] = 7
+    masked = with_image.clone()
+    masked[positions] = -100  # this framework marks the patch positions with a negative id, the export with `image_token_index`
+    mine = ours(masked, image_patches=patches, image_patch_positions=positions, image_patch_coordinates=coordinates)
+    normalize = trainer._config.model.base_model.vision_encoder.normalization.normalize
+    with torch.no_grad():
+        theirs = external(input_ids=with_image[None, :-1], pixel_values=[normalize(first[None])[0], normalize(second[None])[0]]).logits[0]
+    torch.testing.assert_close(mine, theirs, rtol=5e-4, atol=5e-4)
+    # the same through a padded batch with the true sizes
+    padded = torch.zeros(2, 3, 8, 12)
+    padded[0], padded[1, :, :4, :8] = normalize(first[None])[0], normalize(second[None])[0]
+    with torch.no_grad():
+        again = external(input_ids=with_image[None, :-1], pixel_values=padded, image_sizes=[(8, 12), (4, 8)]).logits[0]
+    torch.testing.assert_close(again, theirs, rtol=1e-5, atol=1e-5)
+    # generation with the cache: the images go in with the prompt only
+    with torch.no_grad():
+        cached = external.generate(with_image[None, :30], pixel_values=padded, image_sizes=[(8, 12), (4, 8)], max_new_tokens=5, do_sample=False)
+        uncached = external.generate(with_image[None, :30], pixel_values=padded, image_sizes=[(8, 12), (4, 8)], max_new_tokens=5, do_sample=False,
+                                     use_cache=False)
+    assert torch.equal(cached, uncached)
