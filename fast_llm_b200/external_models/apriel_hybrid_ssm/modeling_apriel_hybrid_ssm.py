@@ -2,7 +2,9 @@
 Mamba ("m2") or gated DeltaNet ("gdn") as listed in `hybrid_block_layout`.
 
 Stand-alone file: it is copied next to exported checkpoints and loaded with `trust_remote_code`.  It favours clarity
-over speed: the recurrent mixers step through the sequence token by token and nothing is cached between calls.
+over speed: the recurrent mixers step through the sequence token by token.  During generation every mixer keeps what it
+needs of the prefix in a `HybridCache` (rotated keys and values, the last inputs of the causal convolution, the
+recurrent state), so a step runs the new tokens only.
 """
 
 import math
@@ -53,10 +55,17 @@ class CausalConv1d(nn.Module):
         self.weight = nn.Parameter(torch.zeros(channels, 1, kernel_size))
         self.bias = nn.Parameter(torch.zeros(channels)) if bias else None
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, state: dict | None = None, key: str = "conv") -> torch.Tensor:
+        """`state[key]` holds the last kernel_size - 1 inputs of the prefix ([batch, channels, kernel_size - 1], fp32)."""
         k = self.weight.shape[-1]
-        y = F.conv1d(F.pad(x.transpose(1, 2).float(), (k - 1, 0)), self.weight.float(), None if self.bias is None else self.bias.float(),
-                     groups=self.weight.shape[0])
+        inputs = x.transpose(1, 2).float()
+        if state is not None and key in state:
+            inputs = torch.cat([state[key], inputs], dim=-1)
+        else:
+            inputs = F.pad(inputs, (k - 1, 0))
+        if state is not None:
+            state[key] = inputs[..., inputs.shape[-1] - (k - 1):]
+        y = F.conv1d(inputs, self.weight.float(), None if self.bias is None else self.bias.float(), groups=self.weight.shape[0])
         return F.silu(y).transpose(1, 2).to(x.dtype)
 
 
@@ -94,20 +103,28 @@ class Attention(nn.Module):
         self.rotary = c.get("rotary", {"type": "mistral_1d"})
         self.window = c.get("window_size")
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, state: dict | None = None) -> torch.Tensor:
+        """`state`: rotated keys and values of the prefix (trimmed to the window) and its length."""
         batch, tokens, _ = x.shape
         q = self.q_proj(x).view(batch, tokens, self.heads, self.head_size)
         k = self.k_proj(x).view(batch, tokens, self.groups, self.head_size)
         v = self.v_proj(x).view(batch, tokens, self.groups, self.head_size)
-        positions = torch.arange(tokens, device=x.device, dtype=torch.float64)
-        angles = (positions[:, None] * _rotary_frequencies(self.rotary, self.head_size, x.device)[None, :]).float()
+        past = 0 if state is None else state.get("length", 0)
+        index = torch.arange(past, past + tokens, device=x.device)
+        angles = (index.double()[:, None] * _rotary_frequencies(self.rotary, self.head_size, x.device)[None, :]).float()
         q, k = _apply_rotary(q, angles), _apply_rotary(k, angles)
+        key_index = index
+        if state is not None:
+            if "k" in state:
+                k, v = torch.cat([state["k"], k], dim=1), torch.cat([state["v"], v], dim=1)
+                key_index = torch.arange(past + tokens - k.shape[1], past + tokens, device=x.device)
+            keep = k.shape[1] if self.window is None else min(k.shape[1], self.window - 1)  # what later tokens can still see
+            state["k"], state["v"], state["length"] = k[:, k.shape[1] - keep:], v[:, v.shape[1] - keep:], past + tokens
         repeat = self.heads // self.groups
         k, v = k.repeat_interleave(repeat, dim=2), v.repeat_interleave(repeat, dim=2)
-        index = torch.arange(tokens, device=x.device)
-        mask = index[:, None] >= index[None, :]
+        mask = index[:, None] >= key_index[None, :]
         if self.window is not None:  # the current token plus window - 1 earlier ones
-            mask = mask & (index[:, None] - index[None, :] < self.window)
+            mask = mask & (index[:, None] - key_index[None, :] < self.window)
         out = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), attn_mask=mask)
         return self.o_proj(out.transpose(1, 2).reshape(batch, tokens, self.heads * self.head_size))
 
@@ -150,7 +167,8 @@ class Mamba(nn.Module):
         self.A_log = nn.Parameter(torch.zeros(self.inner, self.state))
         self.D = nn.Parameter(torch.ones(self.inner))
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, state: dict | None = None) -> torch.Tensor:
+        cache = state
         batch, tokens, _ = x.shape
         n, groups, heads = self.state, self.xb // self.state, self.inner // self.state
         z, xs, b, c = torch.split(self.in_proj(x), [self.inner, self.xb, self.xb, self.inner], dim=-1)
@@ -162,16 +180,18 @@ class Mamba(nn.Module):
         def expand(t):  # [.., groups * n] -> [.., heads * n]
             return t.reshape(batch, tokens, groups, 1, n).expand(-1, -1, -1, heads // groups, -1).reshape(batch, tokens, self.inner)
 
-        xs = self.conv1d(expand(xs)) if self.repeat_before_conv else expand(self.conv1d(xs))
+        xs = self.conv1d(expand(xs), cache) if self.repeat_before_conv else expand(self.conv1d(xs, cache))
         a = -torch.exp(self.A_log.float())
         b = b.float().reshape(batch, tokens, groups, 1, n).expand(-1, -1, -1, self.inner // groups, -1).reshape(batch, tokens, self.inner, n)
         c = c.float().reshape(batch, tokens, heads, 1, n).expand(-1, -1, -1, n, -1).reshape(batch, tokens, self.inner, n)
         xf = xs.float()
-        state = torch.zeros(batch, self.inner, n, dtype=torch.float32, device=x.device)
+        state = cache["ssm"] if cache is not None and "ssm" in cache else torch.zeros(batch, self.inner, n, dtype=torch.float32, device=x.device)
         outputs = []
         for t in range(tokens):
             state = torch.exp(dt[:, t, :, None] * a) * state + (dt[:, t] * xf[:, t])[:, :, None] * b[:, t]
             outputs.append((state * c[:, t]).sum(-1) + self.D.float() * xf[:, t])
+        if cache is not None:
+            cache["ssm"] = state
         y = torch.stack(outputs, dim=1) * F.silu(z.float())
         return self.out_proj(y.to(x.dtype))
 
@@ -180,13 +200,16 @@ def _l2_normalize(x: torch.Tensor) -> torch.Tensor:
     return x * torch.rsqrt((x * x).sum(-1, keepdim=True) + 1e-6)
 
 
-def _delta_rule(q, k, v, log_decay, beta):
+def _delta_rule(q, k, v, log_decay, beta, cache: dict | None = None):
     """q, k [batch, tokens, heads, dk]; v [batch, tokens, heads, dv]; log_decay [batch, tokens, heads] or [.., heads, dk];
     beta [batch, tokens, heads].  S_t = decay S_{t-1} + beta k (v - k^T decay S_{t-1});  o_t = q^T S_t."""
     q, k = _l2_normalize(q.float()) * q.shape[-1] ** -0.5, _l2_normalize(k.float())
     v, beta = v.float(), beta.float()
     batch, tokens, heads, dk = q.shape
-    state = torch.zeros(batch, heads, dk, v.shape[-1], dtype=torch.float32, device=q.device)
+    if cache is not None and "delta" in cache:  # S carried over from the prefix
+        state = cache["delta"]
+    else:
+        state = torch.zeros(batch, heads, dk, v.shape[-1], dtype=torch.float32, device=q.device)
     outputs = []
     for t in range(tokens):
         decay = log_decay[:, t].float().exp()
@@ -194,6 +217,8 @@ def _delta_rule(q, k, v, log_decay, beta):
         read = torch.einsum("bhd,bhde->bhe", k[:, t], state)
         state = state + beta[:, t, :, None, None] * torch.einsum("bhd,bhe->bhde", k[:, t], v[:, t] - read)
         outputs.append(torch.einsum("bhd,bhde->bhe", q[:, t], state))
+    if cache is not None:
+        cache["delta"] = state
     return torch.stack(outputs, dim=1)
 
 
@@ -211,18 +236,18 @@ class GatedDeltaNet(nn.Module):
         self.A_log = nn.Parameter(torch.zeros(self.value_heads))
         self.norm = RMSNorm(self.value_dim, epsilon)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, state: dict | None = None) -> torch.Tensor:
         batch, tokens, _ = x.shape
         key_size, value_size = self.key_heads * self.key_dim, self.value_heads * self.value_dim
         qkv, z = torch.split(self.in_proj_qkvz(x), [2 * key_size + value_size, value_size], dim=-1)
-        q, k, v = torch.split(self.conv1d(qkv), [key_size, key_size, value_size], dim=-1)
+        q, k, v = torch.split(self.conv1d(qkv, state), [key_size, key_size, value_size], dim=-1)
         repeat = self.value_heads // self.key_heads
         q = q.reshape(batch, tokens, self.key_heads, self.key_dim).repeat_interleave(repeat, dim=2)
         k = k.reshape(batch, tokens, self.key_heads, self.key_dim).repeat_interleave(repeat, dim=2)
         v = v.reshape(batch, tokens, self.value_heads, self.value_dim)
         beta, alpha = torch.split(self.in_proj_ba(x), [self.value_heads, self.value_heads], dim=-1)
         log_decay = -self.A_log.float().exp() * F.softplus(alpha.float() + self.dt_bias.float())
-        out = _delta_rule(q, k, v, log_decay, beta.float().sigmoid()).to(x.dtype)
+        out = _delta_rule(q, k, v, log_decay, beta.float().sigmoid(), state).to(x.dtype)
         out = self.norm(out, z.reshape(batch, tokens, self.value_heads, self.value_dim))
         return self.out_proj(out.reshape(batch, tokens, value_size))
 
@@ -268,16 +293,39 @@ class Layer(nn.Module):
             raise NotImplementedError(f"layer type {kind}")
         self.mlp = MLP(hidden, {"intermediate_size": config.intermediate_size, "gated": True, "activation": config.hidden_act, "add_linear_biases": False})
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, state: dict | None = None) -> torch.Tensor:
         mixer = self.self_attn if self.kind == "t" else self.mixer
-        x = x + mixer(self.input_layernorm(x))
+        x = x + mixer(self.input_layernorm(x), state)
         return x + self.mlp(self.post_attention_layernorm(x))
+
+
+class HybridCache:
+    """What each layer's mixer keeps of the prefix: one dictionary per layer, filled by the mixers themselves."""
+
+    def __init__(self, layers: int):
+        self.layers: list[dict] = [{} for _ in range(layers)]
+        self.length = 0
+
+    def get_seq_length(self, layer_idx: int = 0) -> int:
+        return self.length
+
+    def reorder_cache(self, beam_idx: torch.Tensor) -> None:
+        """Beam search: row i continues from row beam_idx[i]."""
+        for layer in self.layers:
+            for name, value in layer.items():
+                if torch.is_tensor(value):
+                    layer[name] = value.index_select(0, beam_idx.to(value.device))
 
 
 class AprielHybridSSMPreTrainedModel(PreTrainedModel):
     config_class = AprielHybridSSMConfig
     base_model_prefix = "model"
     _no_split_modules = ["Layer"]
+    _is_stateful = True  # recurrent states cannot be rolled back to a shorter prefix
+
+    @classmethod
+    def _supports_default_dynamic_cache(cls) -> bool:
+        return False  # `forward` makes its own `HybridCache`
 
 
 class AprielHybridSSMModel(AprielHybridSSMPreTrainedModel):
@@ -294,14 +342,21 @@ class AprielHybridSSMModel(AprielHybridSSMPreTrainedModel):
     def set_input_embeddings(self, value):
         self.embed_tokens = value
 
-    def forward(self, input_ids=None, inputs_embeds=None, output_hidden_states: bool = False, **kwargs):
+    def forward(self, input_ids=None, inputs_embeds=None, past_key_values: HybridCache | None = None, use_cache: bool = False,
+                output_hidden_states: bool = False, **kwargs):
+        """With `past_key_values` the inputs are the tokens that follow the cached prefix."""
         hidden = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds
+        if use_cache and past_key_values is None:
+            past_key_values = HybridCache(len(self.layers))
         states = [hidden] if output_hidden_states else None
-        for layer in self.layers:
-            hidden = layer(hidden)
+        for index, layer in enumerate(self.layers):
+            hidden = layer(hidden, None if past_key_values is None else past_key_values.layers[index])
             if states is not None:
                 states.append(hidden)
-        return BaseModelOutputWithPast(last_hidden_state=self.norm(hidden), hidden_states=tuple(states) if states is not None else None)
+        if past_key_values is not None:
+            past_key_values.length += hidden.shape[1]
+        return BaseModelOutputWithPast(last_hidden_state=self.norm(hidden), past_key_values=past_key_values,
+                                       hidden_states=tuple(states) if states is not None else None)
 
 
 class AprielHybridSSMForCausalLM(AprielHybridSSMPreTrainedModel, GenerationMixin):
@@ -319,13 +374,17 @@ class AprielHybridSSMForCausalLM(AprielHybridSSMPreTrainedModel, GenerationMixin
     def set_output_embeddings(self, value):
         self.lm_head = value
 
-    def prepare_inputs_for_generation(self, input_ids, **kwargs):
-        return {"input_ids": input_ids}  # nothing is cached: the whole prefix is run again
+    def prepare_inputs_for_generation(self, input_ids, past_key_values: HybridCache | None = None, use_cache: bool = True, **kwargs):
+        if past_key_values is not None:
+            input_ids = input_ids[:, past_key_values.get_seq_length():]  # the cache holds the rest
+        return {"input_ids": input_ids, "past_key_values": past_key_values, "use_cache": use_cache}
 
-    def forward(self, input_ids=None, inputs_embeds=None, labels=None, output_hidden_states: bool = False, **kwargs):
-        outputs = self.model(input_ids=input_ids, inputs_embeds=inputs_embeds, output_hidden_states=output_hidden_states)
+    def forward(self, input_ids=None, inputs_embeds=None, labels=None, past_key_values: HybridCache | None = None, use_cache: bool = False,
+                output_hidden_states: bool = False, **kwargs):
+        outputs = self.model(input_ids=input_ids, inputs_embeds=inputs_embeds, past_key_values=past_key_values, use_cache=use_cache,
+                             output_hidden_states=output_hidden_states)
         logits = self.lm_head(outputs.last_hidden_state)
         loss = None
         if labels is not None:
             loss = F.cross_entropy(logits[:, :-1].reshape(-1, logits.shape[-1]).float(), labels[:, 1:].reshape(-1), ignore_index=-100)
-        return CausalLMOutputWithPast(loss=loss, logits=logits, hidden_states=outputs.hidden_states)
+        return CausalLMOutputWithPast(loss=loss, logits=logits, past_key_values=outputs.past_key_values, hidden_states=outputs.hidden_states)

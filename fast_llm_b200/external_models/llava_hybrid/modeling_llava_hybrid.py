@@ -2,8 +2,8 @@
 
 Weight names follow the checkpoint layout the `llava_hybrid_ssm` format writes: `vision_tower.*` (a Pixtral vision model),
 `multi_modal_projector.linear_{1,2}.*`, `language_model.model.*` and `language_model.lm_head.*`.  Image features replace the
-embeddings of the `image_token_index` placeholders, one feature per placeholder in order.  Nothing is cached during
-generation (the language model re-runs the prefix), so `pixel_values` are passed at every step.
+embeddings of the `image_token_index` placeholders, one feature per placeholder in order.  During generation the language
+model's cache holds the prompt, images included, so `pixel_values` go in with the first step only.
 Same role as `fast_llm_external_models/llava_hybrid/modeling_llava_hybrid.py`.
 """
 
@@ -39,6 +39,11 @@ class LlavaHybridPreTrainedModel(PreTrainedModel):
     config_class = LlavaHybridConfig
     base_model_prefix = ""
     _no_split_modules = ["Layer"]
+    _is_stateful = True
+
+    @classmethod
+    def _supports_default_dynamic_cache(cls) -> bool:
+        return False  # the language model makes its own cache
 
 
 class LlavaHybridModel(LlavaHybridPreTrainedModel):
@@ -81,10 +86,12 @@ class LlavaHybridModel(LlavaHybridPreTrainedModel):
             raise ValueError(f"{int(mask.sum())} image placeholder tokens but {features.shape[0]} image features")
         return embeddings.masked_scatter(mask.unsqueeze(-1), features)
 
-    def forward(self, input_ids=None, pixel_values=None, image_sizes=None, inputs_embeds=None, output_hidden_states: bool = False, **kwargs):
+    def forward(self, input_ids=None, pixel_values=None, image_sizes=None, inputs_embeds=None, past_key_values=None, use_cache: bool = False,
+                output_hidden_states: bool = False, **kwargs):
         if inputs_embeds is None:
             inputs_embeds = self.merge(input_ids, pixel_values, image_sizes)
-        return self.language_model.model(inputs_embeds=inputs_embeds, output_hidden_states=output_hidden_states)
+        return self.language_model.model(inputs_embeds=inputs_embeds, past_key_values=past_key_values, use_cache=use_cache,
+                                         output_hidden_states=output_hidden_states)
 
 
 class LlavaHybridForConditionalGeneration(LlavaHybridModel, GenerationMixin):
@@ -94,18 +101,22 @@ class LlavaHybridForConditionalGeneration(LlavaHybridModel, GenerationMixin):
     def set_output_embeddings(self, value):
         self.language_model.lm_head = value
 
-    def prepare_inputs_for_generation(self, input_ids, pixel_values=None, image_sizes=None, **kwargs):
-        return {"input_ids": input_ids, "pixel_values": pixel_values, "image_sizes": image_sizes}
+    def prepare_inputs_for_generation(self, input_ids, pixel_values=None, image_sizes=None, past_key_values=None, use_cache: bool = True, **kwargs):
+        if past_key_values is not None and past_key_values.get_seq_length() > 0:  # the images went in with the prompt
+            return {"input_ids": input_ids[:, past_key_values.get_seq_length():], "past_key_values": past_key_values, "use_cache": use_cache}
+        return {"input_ids": input_ids, "pixel_values": pixel_values, "image_sizes": image_sizes, "past_key_values": past_key_values,
+                "use_cache": use_cache}
 
-    def forward(self, input_ids=None, pixel_values=None, image_sizes=None, inputs_embeds=None, labels=None,
-                output_hidden_states: bool = False, **kwargs):
+    def forward(self, input_ids=None, pixel_values=None, image_sizes=None, inputs_embeds=None, labels=None, past_key_values=None,
+                use_cache: bool = False, output_hidden_states: bool = False, **kwargs):
         outputs = LlavaHybridModel.forward(self, input_ids=input_ids, pixel_values=pixel_values, image_sizes=image_sizes,
-                                           inputs_embeds=inputs_embeds, output_hidden_states=output_hidden_states)
+                                           inputs_embeds=inputs_embeds, past_key_values=past_key_values, use_cache=use_cache,
+                                           output_hidden_states=output_hidden_states)
         logits = self.language_model.lm_head(outputs.last_hidden_state)
         loss = None
         if labels is not None:
             loss = F.cross_entropy(logits[:, :-1].reshape(-1, logits.shape[-1]).float(), labels[:, 1:].reshape(-1), ignore_index=-100)
-        return CausalLMOutputWithPast(loss=loss, logits=logits, hidden_states=outputs.hidden_states)
+        return CausalLMOutputWithPast(loss=loss, logits=logits, past_key_values=outputs.past_key_values, hidden_states=outputs.hidden_states)
 
 
 __all__ = ["LlavaHybridForConditionalGeneration", "LlavaHybridModel", "LlavaHybridPreTrainedModel"]

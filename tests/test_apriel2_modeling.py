@@ -72,3 +72,34 @@ def test_generate_uses_the_cache_and_matches_generation_without():
         beams_plain = model.generate(prompt, max_new_tokens=6, do_sample=False, num_beams=3, use_cache=False)
     assert torch.equal(cached, plain)
     assert torch.equal(beams, beams_plain)  # beam search reorders the rows of every cached tensor
+
+
+def test_hybrid_ssm_model_cache():
+    """The Apriel hybrid SSM modelling code keeps the same kind of cache (attention with a sliding window, Mamba, gated DeltaNet)."""
+    from fast_llm_b200.external_models.apriel_hybrid_ssm.configuration_apriel_hybrid_ssm import AprielHybridSSMConfig
+    from fast_llm_b200.external_models.apriel_hybrid_ssm.modeling_apriel_hybrid_ssm import AprielHybridSSMForCausalLM, HybridCache
+
+    torch.manual_seed(0)
+    config = AprielHybridSSMConfig(
+        hidden_size=32, intermediate_size=48, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=8, vocab_size=96,
+        sliding_window=6, hybrid_block_layout=["t", "m2", "gdn"], ssm_cfg={"d_state": 8, "d_inner": 32, "d_xb": 16, "dt_rank": 4, "d_conv": 4},
+        linear_attn_config={"gdn_num_value_heads": 4, "gdn_num_key_heads": 2, "gdn_key_head_dim": 8, "gdn_value_head_dim": 8,
+                            "gdn_linear_conv_kernel_size": 3})
+    model = AprielHybridSSMForCausalLM(config).eval()
+    with torch.no_grad():
+        for name, parameter in model.named_parameters():
+            if name.endswith(("A_log", "dt_bias", "D")) or "conv" in name:
+                parameter.copy_(torch.randn_like(parameter) * 0.5)
+    tokens = torch.randint(0, 96, (2, 17))
+    with torch.no_grad():
+        full = model(input_ids=tokens).logits
+        out = model(input_ids=tokens[:, :9], use_cache=True)
+        cache, pieces = out.past_key_values, [out.logits]
+        assert isinstance(cache, HybridCache)
+        for begin, end in ((9, 10), (10, 11), (11, 17)):
+            pieces.append(model(input_ids=tokens[:, begin:end], past_key_values=cache, use_cache=True).logits)
+        assert cache.get_seq_length() == 17 and cache.layers[0]["k"].shape[1] == 5
+        torch.testing.assert_close(torch.cat(pieces, dim=1), full, rtol=1e-4, atol=1e-5)
+        cached = model.generate(tokens[:, :5], max_new_tokens=6, do_sample=False)
+        plain = model.generate(tokens[:, :5], max_new_tokens=6, do_sample=False, use_cache=False)
+    assert torch.equal(cached, plain)

@@ -226,6 +226,11 @@ def test_llava_hybrid_modeling_code_loads_the_export_and_reproduces_the_logits(t
     with torch.no_grad():
         theirs = external(input_ids=with_image[None, :-1], pixel_values=image, image_sizes=[(8, 12)]).logits[0]
     torch.testing.assert_close(mine, theirs, rtol=5e-4, atol=5e-4)
+    # generation keeps the prompt (image included) in the language model's cache: the image goes in once
+    with torch.no_grad():
+        cached = external.generate(with_image[None, :30], pixel_values=image, image_sizes=[(8, 12)], max_new_tokens=4, do_sample=False)
+        plain = external.generate(with_image[None, :30], pixel_values=image, image_sizes=[(8, 12)], max_new_tokens=4, do_sample=False, use_cache=False)
+    assert torch.equal(cached, plain)
 
 
 def test_apriel2_multimodal_modeling_code_loads_the_export_and_reproduces_the_logits(tmp_path):
