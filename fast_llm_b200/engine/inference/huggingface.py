@@ -3,8 +3,10 @@
 `HuggingfaceGPTModelForCausalLM(model)` behaves like a `transformers` causal LM: `forward(input_ids, attention_mask)`
 returns `CausalLMOutputWithPast` with logits `[batch, sequence, vocab]`.  Every call packs the (left-padded) rows into one
 variable-length token stream - padding becomes a document of its own that nothing attends to - runs the stages forward
-and unpacks.  There is no KV cache: each generated token re-runs the prompt (`use_cache` is forced off), which keeps the
-engine's packed attention path the only one.
+and unpacks.  Decoders made of attention blocks generate with a key / value cache (`use_cache`, the default of `generate`):
+the prompt runs once, every later step runs the new tokens against the cached keys and values of its row (the attention
+layer's `past_key_values` / `presents` lists, the ones micro-sequences use in training).  Decoders with recurrent mixers
+re-run the prompt for every token.
 
 With tensor parallelism rank 0 of the tensor group acts as coordinator: it broadcasts the batch (or a stop signal) and
 every other rank sits in `worker_forward()` executing the same forward passes.
@@ -22,7 +24,7 @@ import transformers
 import transformers.modeling_outputs
 
 from fast_llm_b200.engine.checkpoint.config import CheckpointLoadConfig, FastLLMCheckpointFormat
-from fast_llm_b200.engine.inference.runner import InferenceRunner
+from fast_llm_b200.engine.inference.runner import InferenceRunner, KeyValueCache
 from fast_llm_b200.engine.multi_stage.config import StageMode
 from fast_llm_b200.utils import Assert
 
@@ -39,7 +41,7 @@ class HuggingfaceModelConfig(transformers.PretrainedConfig):
     def from_fast_llm_config(cls, fast_llm_config, **kwargs) -> "HuggingfaceModelConfig":
         config = cls(**kwargs)
         base = fast_llm_config.base_model
-        config.use_cache = False
+        config.use_cache = False  # the wrapper turns it on when the decoder can keep a cache
         config.vocab_size = base.embeddings.vocab_size
         config.hidden_size = base.hidden_size
         config.num_hidden_layers = len(base.decoder.block_configs())
@@ -77,6 +79,10 @@ class HuggingfacePreTrainedModel(transformers.PreTrainedModel, transformers.gene
     def can_generate(cls) -> bool:
         return True
 
+    @classmethod
+    def _supports_default_dynamic_cache(cls) -> bool:
+        return False  # `forward` makes its own `KeyValueCache`
+
     def __init__(self, fast_llm_model, config: HuggingfaceModelConfig | None = None, runner: InferenceRunner | None = None, **kwargs):
         if config is None:
             config = self.config_class.from_fast_llm_config(fast_llm_model.config)
@@ -87,6 +93,10 @@ class HuggingfacePreTrainedModel(transformers.PreTrainedModel, transformers.gene
         self._fast_llm_model = fast_llm_model
         self._inference_runner = runner or self.runner_class(fast_llm_model)
         self._inference_runner.setup()
+        self._cache_supported = self._inference_runner.supports_key_value_cache()
+        self._worker_cache: KeyValueCache | None = None  # tensor-parallel workers keep their own heads' cache here
+        self.config.use_cache = self._cache_supported
+        self.generation_config.use_cache = self._cache_supported
         distributed_config = fast_llm_model.distributed.config
         Assert.eq(distributed_config.pipeline_parallel, 1)
         Assert.eq(distributed_config.sequence_data_parallel, 1)
@@ -133,25 +143,50 @@ class HuggingfacePreTrainedModel(transformers.PreTrainedModel, transformers.gene
                 output_hidden_states=None, return_dict=None, coordinator_forward: bool = False, **kwargs):
         if inputs_embeds is not None or labels is not None or output_attentions:
             raise NotImplementedError("The wrapper supports token inputs and logits / hidden-state outputs only")
+        if past_key_values is not None and not isinstance(past_key_values, KeyValueCache):
+            raise NotImplementedError("`past_key_values` must be the cache an earlier call of this model returned")
+        cache_mode = None
+        if past_key_values is not None and past_key_values.length > 0:
+            cache_mode = "continue"
+        elif self._cache_supported and (self.config.use_cache if use_cache is None else use_cache):
+            cache_mode = "new"
         if self._tensor_group is not None and self._is_coordinator:
-            self._broadcast(("forward", input_ids.cpu(), None if attention_mask is None else attention_mask.cpu(), bool(output_hidden_states)))
-        return self._inner_forward(input_ids, attention_mask, output_hidden_states, return_dict)
+            self._broadcast(("forward", input_ids.cpu(), None if attention_mask is None else attention_mask.cpu(), bool(output_hidden_states),
+                             cache_mode))
+        return self._inner_forward(input_ids, attention_mask, output_hidden_states, return_dict, cache_mode, past_key_values)
 
-    def _inner_forward(self, input_ids, attention_mask, output_hidden_states, return_dict):
+    def _inner_forward(self, input_ids, attention_mask, output_hidden_states, return_dict, cache_mode=None, cache: KeyValueCache | None = None):
         batch, length = input_ids.shape
-        lengths = self._document_lengths(input_ids, attention_mask)
         hidden_names = None
         if output_hidden_states:
             hidden_names = [layer.unwrap().module_name for layer in self._fast_llm_model.base_model.get_layers()
                             if layer.unwrap().module_name.startswith("decoder.")]
-        logits, hidden = self._inference_runner.forward_tokens(input_ids.reshape(-1), lengths, output_hidden_states=hidden_names or [])
+        if cache_mode is None:
+            cache = None
+            lengths = self._document_lengths(input_ids, attention_mask)
+            logits, hidden = self._inference_runner.forward_tokens(input_ids.reshape(-1), lengths, output_hidden_states=hidden_names or [])
+        else:
+            if cache_mode == "new":  # the whole (left-padded) prompt
+                cache = KeyValueCache(self._left_padding(input_ids, attention_mask))
+                cache.on_reorder = self._reorder_workers
+            Assert.eq(cache.rows, batch)
+            logits, hidden = self._inference_runner.forward_rows(input_ids, cache, hidden_names or [])
         logits = logits.reshape(batch, length, -1)
         hidden_states = None
         if hidden_names:
             hidden_states = tuple(hidden[name].reshape(batch, length, -1) for name in hidden_names if name in hidden)
         if return_dict is False:
-            return (logits, hidden_states) if hidden_states is not None else (logits,)
-        return transformers.modeling_outputs.CausalLMOutputWithPast(logits=logits, hidden_states=hidden_states, past_key_values=None)
+            return tuple(x for x in (logits, hidden_states, cache) if x is not None)
+        return transformers.modeling_outputs.CausalLMOutputWithPast(logits=logits, hidden_states=hidden_states, past_key_values=cache)
+
+    @staticmethod
+    def _left_padding(input_ids: torch.Tensor, attention_mask: torch.Tensor | None) -> list[int]:
+        batch, length = input_ids.shape
+        if attention_mask is None:
+            return [0] * batch
+        first = attention_mask.argmax(dim=1)
+        Assert.custom(lambda ok: bool(ok), (attention_mask.sum(1) == length - first).all())  # left-padded, contiguous
+        return first.tolist()
 
     @staticmethod
     def _document_lengths(input_ids: torch.Tensor, attention_mask: torch.Tensor | None) -> list[int]:
@@ -166,8 +201,15 @@ class HuggingfacePreTrainedModel(transformers.PreTrainedModel, transformers.gene
             lengths += [length] if pad == 0 else [pad, length - pad]
         return lengths
 
-    def prepare_inputs_for_generation(self, input_ids, attention_mask=None, **kwargs):
-        return {"input_ids": input_ids, "attention_mask": attention_mask, "use_cache": False}
+    def prepare_inputs_for_generation(self, input_ids, attention_mask=None, past_key_values=None, use_cache=None, **kwargs):
+        if past_key_values is not None and past_key_values.length > 0:
+            input_ids = input_ids[:, past_key_values.length:]  # the cache holds the rest; the padding was settled by the first call
+        return {"input_ids": input_ids, "attention_mask": attention_mask, "past_key_values": past_key_values,
+                "use_cache": bool(use_cache) and self._cache_supported}
+
+    def _reorder_workers(self, index: torch.Tensor) -> None:
+        if self._tensor_group is not None and self._is_coordinator:
+            self._broadcast(("reorder", index.cpu()))
 
     # ---- tensor-parallel coordination
     def _broadcast(self, message) -> None:
@@ -183,9 +225,14 @@ class HuggingfacePreTrainedModel(transformers.PreTrainedModel, transformers.gene
             message = self._broadcast(None)
             if message[0] == "stop":
                 return
-            _, input_ids, attention_mask, output_hidden_states = message
+            if message[0] == "reorder":
+                self._worker_cache.reorder(message[1])
+                continue
+            _, input_ids, attention_mask, output_hidden_states, cache_mode = message
             device = self._fast_llm_model.distributed.device
-            self._inner_forward(input_ids.to(device), None if attention_mask is None else attention_mask.to(device), output_hidden_states, True)
+            out = self._inner_forward(input_ids.to(device), None if attention_mask is None else attention_mask.to(device), output_hidden_states,
+                                      True, cache_mode, self._worker_cache if cache_mode == "continue" else None)
+            self._worker_cache = out.past_key_values
 
     def stop_workers(self) -> None:
         if self._tensor_group is not None and self._is_coordinator:

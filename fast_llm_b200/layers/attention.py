@@ -176,9 +176,13 @@ class Attention(LayerBase):
                 # Sequence-data parallelism: every rank needs the keys/values of the whole sequence.
                 kv = _GatherKV.apply(kv.contiguous(), self._sdp_dim.group)
             if past is not None and len(past) > 0:
-                kv = torch.cat([past.pop(0), kv], dim=0)
+                previous, rows = past.pop(0), kwargs.get(BlockKwargs.key_value_rows, 1)
+                if rows > 1:  # a batch of sequences, each continuing its own cached prefix
+                    kv = torch.cat([previous.view(rows, -1, kv.shape[-1]), kv.view(rows, -1, kv.shape[-1])], dim=1).reshape(-1, kv.shape[-1])
+                else:
+                    kv = torch.cat([previous, kv], dim=0)
             if presents is not None:
-                presents.append(kv.detach().requires_grad_() if False else kv)
+                presents.append(kv)
             tk = kv.shape[0]
             k = kv[:, : groups * d].reshape(tk, groups, d)
             v = kv[:, groups * d :].reshape(tk, groups, d)

@@ -22,6 +22,7 @@ class BlockKwargs:
     output_hidden_states = "output_hidden_states"
     past_key_values = "past_key_values"
     presents = "presents"
+    key_value_rows = "key_value_rows"  # generation: cached and new keys / values are both [rows * n, width]; joined row by row
     micro_sequence_index = "micro_sequence_index"
     sequence_k_offset = "sequence_k_offset"
 

@@ -83,6 +83,7 @@ def attention_backward_native(q2d, q_col0, kv2d, k_col0, v_col0, out, dout, lse,
 
 
 _NATIVE_HEAD = 128  # head size of the tcgen05 kernels; smaller heads are zero-padded to it
+_MIN_ROWS = 128  # fewer query or key rows than one tile are padded with rows of no document
 
 
 def _joint_key_value_rows(k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
@@ -193,11 +194,16 @@ def attention(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int, max_seqlen
         return attention_reference(q, k, v, cu_seqlens_q, cu_seqlens_k, causal, window_size, scale)
     if not (_native_dtype_ok(q, dropout_p) and d <= _NATIVE_HEAD and d % 8 == 0 and _kernel_supports(causal, window_size)):
         return _sdpa_fallback(q, k, v, cu_seqlens_q, cu_seqlens_k, causal, window_size, scale, dropout_p)
-    if d < _NATIVE_HEAD:
-        pad = (0, _NATIVE_HEAD - d)  # zero columns change neither the scores nor the first d output columns
-        q, k, v = (torch.nn.functional.pad(t, pad) for t in (q, k, v))
+    tq = q.shape[0]
+    # generation steps hold a few rows only: the tensor maps always cover at least one full 128-row tile (rows past the last
+    # `cu_seqlens` entry belong to no document: nothing reads or writes them)
+    rows_q, rows_k = max(_MIN_ROWS - tq, 0), max(_MIN_ROWS - k.shape[0], 0)
+    if d < _NATIVE_HEAD or rows_q or rows_k:
+        # zero columns change neither the scores nor the first d output columns
+        q = torch.nn.functional.pad(q, (0, _NATIVE_HEAD - d, 0, 0, 0, rows_q))
+        k, v = (torch.nn.functional.pad(t, (0, _NATIVE_HEAD - d, 0, 0, 0, rows_k)) for t in (k, v))
     out = _NativeAttention.apply(q, k, v, cu_seqlens_q.int(), cu_seqlens_k.int(), max_seqlen_q, max_seqlen_k, causal, window_size, scale)
-    return out[:, :, :d] if d < _NATIVE_HEAD else out
+    return out[:tq, :, :d] if (d < _NATIVE_HEAD or rows_q) else out
 
 
 def packed_attention(qkv, cu_seqlens, max_seqlen: int, heads: int, kv_heads: int, head_dim: int, *, causal: bool = True,
