@@ -650,6 +650,54 @@ def bench_zero(results):
     torch.distributed.destroy_process_group()
 
 
+def bench_generate(results):
+    """Greedy generation through the Hugging Face wrapper with and without the key / value cache (one GPU): a decoder of
+    8 blocks, hidden 2048, 16 heads of 128 (4 groups), vocabulary 32000; 8 prompts of 512 tokens, 32 new tokens each."""
+    import fast_llm_b200.models.auto  # noqa: F401
+    from fast_llm_b200.engine.inference.huggingface import HuggingfaceGPTModelForCausalLM
+    from fast_llm_b200.engine.multi_stage.config import StageMode
+    from fast_llm_b200.models.gpt.config import GPTModelConfig
+    from fast_llm_b200.models.gpt.model import GPTModel
+    from fast_llm_b200.parallel.distributed import Distributed
+
+    config = GPTModelConfig.from_dict({
+        "base_model": {
+            "embeddings": {"vocab_size": 32000}, "hidden_size": 2048,
+            "decoder": {"num_blocks": 8, "block": {
+                "mixer": {"type": "attention", "rotary": {"type": "default"}, "heads": 16, "head_groups": 4, "head_size": 128, "add_linear_biases": False},
+                "mlp": {"intermediate_size": 8192, "gated": True, "activation": "silu", "add_linear_biases": False},
+                "normalization": {"type": "rms_norm"}}},
+            "head": {"normalization": {"type": "rms_norm"}}},
+        "distributed": {"compute_dtype": "bf16", "world_size": 1, "rank": 0, "local_world_size": 1}})
+    config.validate()
+    model = GPTModel(config)
+    model.setup(Distributed(config.distributed), mode=StageMode.inference)
+    model.initialize_weights()
+    wrapper = HuggingfaceGPTModelForCausalLM(model)
+    torch.manual_seed(0)
+    rows, prompt_length, new_tokens = 8, 512, 32
+    prompt = torch.randint(1, 32000, (rows, prompt_length), device="cuda")
+    mask = torch.ones_like(prompt)
+    for use_cache in (True, False):
+        arguments = dict(attention_mask=mask, max_new_tokens=new_tokens, min_new_tokens=new_tokens, do_sample=False, pad_token_id=0, use_cache=use_cache)
+        wrapper.generate(prompt, **{**arguments, "max_new_tokens": 4, "min_new_tokens": 4})  # warm-up
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        out = wrapper.generate(prompt, **arguments)
+        end.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(end)
+        assert out.shape == (rows, prompt_length + new_tokens)
+        entry = {"name": f"generate_{'cached' if use_cache else 'uncached'}", "ms": ms, "new_tokens_per_s": rows * new_tokens / ms * 1e3}
+        results.append(entry)
+        print(f"generate use_cache={use_cache}: {ms:9.1f} ms for {rows} x {new_tokens} new tokens after {prompt_length}: {entry['new_tokens_per_s']:8.1f} tokens/s")
+    from fast_llm_b200.utils.device_errors import check_device_errors
+
+    check_device_errors()
+    return results
+
+
 def _lib_module():
     from fast_llm_b200.ops import _lib
 
@@ -662,6 +710,8 @@ def main(argv):
         return bench_tp_linear(results)
     if "zero" in argv:
         return bench_zero(results)
+    if "generate" in argv:
+        return bench_generate(results)
     if "profile_gemm" in argv:
         return profile_gemm()
     if "profile_gemm_shapes" in argv:
