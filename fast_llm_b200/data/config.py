@@ -181,6 +181,8 @@ class GPTDatasetFromFileConfig(SamplableDatasetConfig):
 
         Assert.custom(lambda p: p is not None and pathlib.Path(p).is_file(), self.path)
         data = yaml.safe_load(self.path.read_text())
+        if isinstance(data, dict) and set(data) == {"config", "metadata"}:
+            data = data["config"]  # what `prepare` writes: the dataset config next to token / document counts
         data = _resolve_paths(data, self.path.parent)
         return SampledDatasetConfig.from_dict(data).validate()
 
