@@ -137,11 +137,56 @@ class ExternalStateDictCheckpointHandler(StateDictCheckpointHandler):
             for name in c.fast_llm_name:
                 assert name not in self._export_converters, f"parameter {name} claimed twice"
                 self._export_converters[name] = c
+        self._adapt_to_lora(model)
         self._import_converters = {name: c for c in converters for name in c.export_name}
-        missing = [n for n in model.parameter_names if n not in self._export_converters]
+        missing = [n for n in model.parameter_names if n not in self._export_converters and n not in self._adapter_owner]
         unknown = [n for n in self._export_converters if n not in model.parameter_names]
         if missing or unknown:
             raise ValueError(f"{type(self).__name__}: converters do not cover the model: missing {missing[:8]}, unknown {unknown[:8]}")
+
+    def _adapt_to_lora(self, model) -> None:
+        """External formats know nothing of LoRA.  A wrapped layer keeps its weight as `<layer>.base.weight` next to
+        `<layer>.lora_a_weight` / `lora_b_weight`: the converter of `<layer>.weight` is pointed at the base weight; on export
+        the low-rank update is merged into it (W + alpha / rank * B A, so the exported model computes what the trained one
+        does); on import the adapters start from their initialisers (A random, B zero)."""
+        from fast_llm_b200.layers.peft import LoRALinear
+
+        self._adapter_owner: dict[str, WeightConverter] = {}  # adapter parameter -> converter of its base weight
+        self._adapters: dict[int, list[tuple[str, str, str, float, bool]]] = {}  # converter -> (weight, A, B, scale, transposed)
+        names = set(model.parameter_names)
+        wrapped = {}
+        for layer in model.base_model.get_layers():
+            inner = layer.unwrap()
+            for name, sub in inner.named_sublayers(f"{inner.module_name}."):
+                if isinstance(sub, LoRALinear):
+                    wrapped[name] = sub
+        for prefix, lora in wrapped.items():
+            for suffix in ("weight", "bias"):
+                plain, based = f"{prefix}.{suffix}", f"{prefix}.base.{suffix}"
+                if plain in self._export_converters and based in names:
+                    converter = self._export_converters.pop(plain)
+                    converter.fast_llm_name = tuple(based if n == plain else n for n in converter.fast_llm_name)
+                    self._export_converters[based] = converter
+            converter = self._export_converters.get(f"{prefix}.base.weight")
+            if converter is None:
+                continue
+            a_name, b_name = f"{prefix}.lora_a_weight", f"{prefix}.lora_b_weight"
+            self._adapter_owner[a_name] = self._adapter_owner[b_name] = converter
+            self._adapters.setdefault(id(converter), []).append(
+                (f"{prefix}.base.weight", a_name, b_name, lora._config.alpha / lora._config.rank, bool(getattr(lora.base, "transposed_weight", False))))
+
+    def _generated_tensors(self):
+        """Adapters have no counterpart in the checkpoint: they start from their initialisers."""
+        model = self._model
+        for name in self._adapter_owner:
+            stage = model._stages[model._parameter_stages[name]]
+            if model._parameter_stages[name] not in model._stages_on_device:
+                continue
+            meta = stage.get_parameter_meta(name)
+            Assert.custom(lambda m: not m.is_tensor_parallel, meta)
+            tensor = torch.empty(meta.global_shape, dtype=torch.float32, device=model.distributed.device)
+            meta.init_parameter(tensor, model.distributed)
+            yield name, "weights", tensor
 
     # ---- to implement
     @classmethod
@@ -162,12 +207,16 @@ class ExternalStateDictCheckpointHandler(StateDictCheckpointHandler):
         return ("weights",) if config.model_weights else ()
 
     def _export_tensors(self, parameter_name, shard_name, tensor, pending):
-        converter = self._export_converters[parameter_name]
+        converter = self._export_converters.get(parameter_name) or self._adapter_owner[parameter_name]
+        adapters = self._adapters.get(id(converter), ())
         slot = pending.setdefault(id(converter), {})
         slot[parameter_name] = tensor
-        if len(slot) < len(converter.fast_llm_name):
+        if len(slot) < len(converter.fast_llm_name) + 2 * len(adapters):
             return {}
         del pending[id(converter)]
+        for weight_name, a_name, b_name, scale, transposed in adapters:
+            update = slot[b_name].float() @ slot[a_name].float() * scale  # [out, in]
+            slot[weight_name] = (slot[weight_name].float() + (update.t() if transposed else update)).to(slot[weight_name].dtype)
         exported = converter.export_weight(tuple(slot[n] for n in converter.fast_llm_name))
         return dict(zip(converter.export_name, exported, strict=True))
 
@@ -233,7 +282,8 @@ class TrackedConfig(dict):
 def effective_architecture(config) -> dict:
     """The architecture of a configuration in a form where two spellings of the same model compare equal: every field hinted
     `architecture`, the dynamic type of every sub-configuration (a rotary or mixer of another type is another model), and
-    for each linear layer whether it really has a bias (its own `bias.enabled`, else the owner's `add_linear_biases`)."""
+    for each linear layer whether it really has a bias (its own `bias.enabled`, else the owner's `add_linear_biases`).
+    Parameter-efficient fine-tuning is left out: it adds trainable tensors, not architecture."""
     from fast_llm_b200.config.core import Config, FieldHint, _serialize
 
     out = {}
@@ -242,6 +292,8 @@ def effective_architecture(config) -> dict:
     default_bias = getattr(config, "add_linear_biases", None)
     for name, field in config.fields().items():
         value = getattr(config, name)
+        if name == "peft":
+            continue  # adapters are merged into the weights they adapt when a model leaves in an external format
         if isinstance(value, Config):
             bias = getattr(value, "bias", None)
             if default_bias is not None and bias is not None and hasattr(bias, "enabled"):

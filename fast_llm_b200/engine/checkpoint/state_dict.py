@@ -11,6 +11,7 @@ import abc
 import json
 import logging
 import pathlib
+import typing
 
 import safetensors
 import safetensors.torch
@@ -96,6 +97,10 @@ class StateDictCheckpointHandler(CheckpointHandler):
     def _import_tensors(self, name: str, tensor: torch.Tensor, pending: dict) -> list[tuple[str, str, torch.Tensor]]:
         """Returns (parameter name, shard name, global tensor) triples that became complete by adding this one."""
 
+    def _generated_tensors(self) -> typing.Iterable[tuple[str, str, torch.Tensor]]:
+        """(parameter name, shard name, global tensor) triples that come from no file (parameters the format does not hold)."""
+        return ()
+
     def _serialize_metadata(self, config: CheckpointSaveMetadataConfig, metadata: CheckpointMetadata, index: dict) -> None:
         raise NotImplementedError
 
@@ -137,6 +142,9 @@ class StateDictCheckpointHandler(CheckpointHandler):
                             continue
                         count = model.import_state_tensor(parameter_name, shard_name, converted)
                         context.mark_as_loaded(count, (parameter_name, shard_name))
+            for parameter_name, shard_name, generated in self._generated_tensors():
+                if shard_name in shard_names:
+                    context.mark_as_loaded(model.import_state_tensor(parameter_name, shard_name, generated), (parameter_name, shard_name))
         return metadata.metadata if metadata is not None else None
 
 

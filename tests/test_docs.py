@@ -114,3 +114,106 @@ def test_quick_start_flow(tmp_path, monkeypatch):
     with torch.no_grad():
         expected = reference.generate(prompt, attention_mask=torch.ones_like(prompt), max_new_tokens=3, do_sample=False, pad_token_id=0)
     assert torch.equal(tokens, expected)
+
+
+def _tiny_tokenizer(path, corpus, chat_template=None):
+    import tokenizers
+    import transformers
+
+    tok = tokenizers.Tokenizer(tokenizers.models.BPE())
+    tok.pre_tokenizer = tokenizers.pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tok.decoder = tokenizers.decoders.ByteLevel()
+    tok.train_from_iterator(corpus, tokenizers.trainers.BpeTrainer(vocab_size=300, initial_alphabet=tokenizers.pre_tokenizers.ByteLevel.alphabet(),
+                                                                   special_tokens=["<s>", "</s>", "<u>", "<a>"]))
+    fast = transformers.PreTrainedTokenizerFast(tokenizer_object=tok, bos_token="<s>", eos_token="</s>")
+    if chat_template:
+        fast.chat_template = chat_template
+    fast.save_pretrained(str(path))
+
+
+_TINY = ["model.base_model.embeddings.vocab_size=300", "model.base_model.hidden_size=32", "model.base_model.decoder.num_blocks=2",
+         "model.base_model.decoder.block.mixer.heads=4", "model.base_model.decoder.block.mixer.head_groups=2",
+         "model.base_model.decoder.block.mixer.head_size=8", "model.base_model.decoder.block.mixer.add_linear_biases=false",
+         "model.base_model.decoder.block.mixer.rotary.type=default", "model.base_model.decoder.block.mlp.intermediate_size=64",
+         "model.base_model.decoder.block.mlp.gated=true", "model.base_model.decoder.block.mlp.add_linear_biases=false",
+         "model.base_model.decoder.block.normalization.type=rms_norm", "model.base_model.head.normalization.type=rms_norm"]
+_CPU = ["model.distributed.compute_dtype=float32", "model.distributed.use_cuda=false", "training.num_workers=0", "training.logs.interval=1"]
+
+
+def _doc_block(page: str, index: int) -> dict:
+    return yaml.safe_load(re.findall(r"```yaml\n(.*?)```", (DOCS / page).read_text(), re.S)[index])
+
+
+def test_fine_tuning_and_continued_training_recipes(tmp_path, monkeypatch):
+    """docs/recipes/instruction-finetuning.md and continue-training.md: chat data through the conversation schema, a pretrained
+    Llama checkpoint continued with whole documents, LoRA on top, then `fast-llm evaluate` on the result."""
+    from fast_llm_b200.cli import fast_llm_main
+
+    monkeypatch.chdir(tmp_path)
+    template = ("{% for m in messages %}{% if m['role'] == 'assistant' %}<a>{% generation %}{{ m['content'] }}</s>{% endgeneration %}"
+                "{% else %}<u>{{ m['content'] }}{% endif %}{% endfor %}")
+    lines = ["the quick brown fox", "jumps over the lazy dog", "hello world", "this is a test"]
+    _tiny_tokenizer(tmp_path / "tokenizer", lines * 10, template)
+    rows = [{"messages": [{"role": "user", "content": lines[i % 4]}, {"role": "assistant", "content": lines[(i + 1) % 4] + f" {i}"}]} for i in range(60)]
+    (tmp_path / "chat.jsonl").write_text("\n".join(json.dumps(r) for r in rows))
+
+    # a "pretrained" Llama checkpoint: two iterations of the tiny model, exported
+    fast_llm_main(["train", "gpt", "run.experiment_dir=base", "training.train_iters=1", "training.export.interval=1", "training.export.format=llama",
+                   "data.datasets.training.type=random", "data.micro_batch_size=64", *_TINY, *_CPU])
+    pretrained = tmp_path / "base/export/llama/1"
+    assert (pretrained / "config.json").exists()
+
+    prepare = _doc_block("recipes/instruction-finetuning.md", 0)
+    prepare["dataset"].update(path="json", data_files="chat.jsonl", split="train")
+    prepare.update(output_path="sft_data", tokenizer={"path": "tokenizer"}, num_workers=1)
+    (tmp_path / "prepare.yaml").write_text(yaml.safe_dump(prepare))
+    fast_llm_main(["prepare", "gpt_memmap", "-c", "prepare.yaml"])
+
+    train = _doc_block("recipes/instruction-finetuning.md", 1)
+    train["pretrained"]["path"] = str(pretrained)
+    train["data"]["datasets"]["training"]["path"] = "sft_data/fast_llm_config.yaml"
+    train["model"]["base_model"] = _doc_block("recipes/instruction-finetuning.md", 2)["model"]["base_model"]  # the LoRA section
+    train["run"]["experiment_dir"] = "sft"
+    (tmp_path / "sft.yaml").write_text(yaml.safe_dump(train))
+    fast_llm_main(["train", "gpt", "-c", "sft.yaml", "training.train_iters=2", "training.export.interval=2", "data.micro_batch_size=64",
+                   "data.maximum_document_length=64", "optimizer.learning_rate.decay_iterations=2", "optimizer.learning_rate.warmup_iterations=1", *_CPU])
+    assert (tmp_path / "sft/export/llama/2/config.json").exists()
+    sft_config = yaml.safe_load((tmp_path / "sft/config.yaml").read_text())
+    assert sft_config["model"]["base_model"]["peft"]["type"] == "lora"
+
+    # continued training + evaluation from the documented files
+    evaluate = _doc_block("recipes/generate.md", 0)
+    evaluate["pretrained"] = {"path": str(pretrained), "format": "llama"}
+    evaluate["training"]["evaluators"].pop("harness")  # needs the lm-eval package and its task data
+    evaluate["data"]["datasets"]["validation"] = {"type": "file", "path": "sft_data/fast_llm_config.yaml"}
+    evaluate["run"] = {"experiment_dir": "evaluation"}
+    (tmp_path / "evaluate.yaml").write_text(yaml.safe_dump(evaluate))
+    fast_llm_main(["evaluate", "gpt", "-c", "evaluate.yaml", "training.evaluators.validation.iterations=2", "data.micro_batch_size=64",
+                   "model.distributed.compute_dtype=float32", "model.distributed.use_cuda=false", "training.num_workers=0"])
+    logs = "".join(p.read_text() for p in (tmp_path / "evaluation/runs/0/logs").glob("*.txt"))
+    assert "validation @ validation" in logs and "lm loss" in logs
+
+
+def test_upcycling_recipe(tmp_path, monkeypatch):
+    """docs/recipes/upcycle-to-moe.md: a Mixtral-style export, `add_experts`, then training from the result."""
+    from fast_llm_b200.cli import fast_llm_main
+    from fast_llm_b200.tools import checkpoint_surgery  # noqa: F401  (registers the commands)
+
+    monkeypatch.chdir(tmp_path)
+    moe = ["model.base_model.decoder.block.mlp.type=moe", "model.base_model.decoder.block.mlp.experts=2", "model.base_model.decoder.block.mlp.experts_per_token=1"]
+    fast_llm_main(["train", "gpt", "run.experiment_dir=base", "training.train_iters=1", "training.export.interval=1", "training.export.format=mixtral",
+                   "data.datasets.training.type=random", "data.micro_batch_size=64", *_TINY, *moe, *_CPU])
+    source = tmp_path / "base/export/mixtral/1"
+    fast_llm_main(["add_experts", f"hf_checkpoint={source}", "output_dir=upcycled", "num_new_experts=2", "expert_init_method=from_existing",
+                   "expert_init_std=0.01", "router_init_method=from_scratch", "router_init_std=0.02", "seed=0"])
+    assert json.loads((tmp_path / "upcycled/config.json").read_text())["num_local_experts"] == 4
+
+    train = _doc_block("recipes/upcycle-to-moe.md", 0)
+    train["pretrained"]["path"] = "upcycled"
+    train["data"]["datasets"]["training"] = {"type": "random"}
+    train["run"]["experiment_dir"] = "upcycled_run"
+    (tmp_path / "train.yaml").write_text(yaml.safe_dump(train))
+    fast_llm_main(["train", "gpt", "-c", "train.yaml", "training.train_iters=2", "training.checkpoint.interval=2", "data.micro_batch_size=64",
+                   "optimizer.learning_rate.decay_iterations=2", "optimizer.learning_rate.warmup_iterations=1", *_CPU])
+    saved = yaml.safe_load((tmp_path / "upcycled_run/checkpoint/2/metadata.yaml").read_text())
+    assert "experts: 4" in yaml.safe_dump(saved)

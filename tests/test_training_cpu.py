@@ -605,3 +605,44 @@ def test_import_reports_fields_nobody_claimed(tmp_path):
     exported["rope_scaling"] = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
                                 "original_max_position_embeddings": 8192, "mystery_inner": 1}
     assert sorted(handler.check_import_coverage(exported)[1]) == ["mystery_gate", "rope_scaling.mystery_inner"]
+
+
+def test_lora_model_exports_merged_weights_and_imports_a_plain_checkpoint(tmp_path):
+    """External formats hold no adapters: on export the low-rank update is merged into the weight it adapts (the exported
+    model computes what the LoRA model does, here on the query and, transposed storage, on the MLP's second layer); on import
+    the base weights come from the checkpoint and the adapters from their initialisers (B = 0: the same function again)."""
+    import copy
+
+    from fast_llm_b200.engine.checkpoint.config import CheckpointLoadConfig, CheckpointSaveConfig
+    from fast_llm_b200.engine.inference.runner import InferenceRunner
+    from fast_llm_b200.models.gpt.model import GPTModel
+    from tests.common import TINY_BASE_MODEL
+
+    base = copy.deepcopy(TINY_BASE_MODEL)
+    base["peft"] = {"type": "lora", "rank": 4, "alpha": 8.0}
+    base["decoder"]["block"]["mlp"]["layer_2"] = {"apply_peft": True}
+    trainer, _ = build_trainer(tiny_trainer_config({("model", "base_model"): base, ("optimizer", "learning_rate", "base"): 3e-2}))
+    names = [n for n, _, _ in trainer.multi_stage.get_state_tensor_iterator(("weights",))]
+    assert "decoder.0.mixer.query.lora_b_weight" in names and "decoder.1.mlp.layer_2.lora_a_weight" in names
+    train_steps(trainer, 3)  # B leaves zero
+    state = {n: t for n, _, t in trainer.multi_stage.get_state_tensor_iterator(("weights",))}
+    assert float(state["decoder.0.mixer.query.lora_b_weight"].abs().max()) > 0 and float(state["decoder.1.mlp.layer_2.lora_b_weight"].abs().max()) > 0
+    path = tmp_path / "merged"
+    trainer.multi_stage.save_checkpoint(CheckpointSaveConfig(path=path, format="llama"))
+    tokens = torch.randint(0, 512, (40,))
+
+    def logits(model):
+        runner = InferenceRunner(model)
+        runner.setup()
+        return runner.forward_tokens(tokens)
+
+    expected = logits(trainer.multi_stage)
+    plain = GPTModel.from_pretrained(CheckpointLoadConfig(path=path, format="llama"), use_cpu=True)
+    assert not any("lora" in n for n in plain.parameter_names)
+    torch.testing.assert_close(logits(plain), expected, rtol=1e-4, atol=1e-4)
+    # a LoRA model started from the merged checkpoint: fresh adapters, same function
+    again = GPTModel.from_pretrained(CheckpointLoadConfig(path=path, format="llama"), {("base_model", "peft"): {"type": "lora", "rank": 4, "alpha": 8.0}},
+                                     use_cpu=True)
+    loaded = {n: t for n, _, t in again.get_state_tensor_iterator(("weights",))}
+    assert float(loaded["decoder.0.mixer.query.lora_b_weight"].abs().max()) == 0 and float(loaded["decoder.0.mixer.query.lora_a_weight"].abs().max()) > 0
+    torch.testing.assert_close(logits(again), expected, rtol=1e-4, atol=1e-4)
