@@ -448,7 +448,7 @@ def _write_language_model(stream: io.BufferedWriter, documents: typing.Iterable[
             patches.append(p)
             patch_pos.append(np.asarray(doc.image_patch_positions, dtype=np.int32))
             coords = doc.image_patch_coordinates if doc.image_patch_coordinates is not None else np.zeros((len(p), len(patch_shape) - 1))
-            patch_coord.append(np.asarray(coords, dtype=np.int32).reshape(len(p), -1))
+            patch_coord.append(np.asarray(coords, dtype=np.int32).reshape(len(p), 2))  # (row, column); a document may have no image
             patch_counts.append(patch_counts[-1] + len(p))
         if flags[3]:
             advantages.append(np.asarray(doc.advantages, dtype=np.float32))

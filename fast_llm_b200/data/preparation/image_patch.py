@@ -17,8 +17,8 @@ def load_image(image) -> torch.Tensor:
     """bytes / path / PIL image / array -> uint8 [3, height, width]."""
     if torch.is_tensor(image):
         array = image.numpy()
-    elif isinstance(image, np.ndarray):
-        array = image
+    elif isinstance(image, (np.ndarray, list, tuple)):  # nested lists: arrays that went through a dataset without an Image feature
+        array = np.asarray(image, dtype=np.uint8)
     else:
         import PIL.Image
 

@@ -70,7 +70,7 @@ class LlavaHuggingfaceCheckpointHandler(HuggingfaceStateDictCheckpointHandler):
         Assert.eq(vision.embeddings.patch_height, vision.embeddings.patch_width)
         assert not mixer.causal and mixer.heads == mixer.head_groups and mlp.gated
         adapter = vision.adapter
-        Assert.eq(adapter.intermediate_size, c.hidden_size)
+        Assert.eq(adapter.intermediate_size, c.hidden_size, msg="the Llava projector is hidden -> hidden: vision_encoder.adapter.intermediate_size must equal hidden_size")
         text = cls.text_handler.export_config(c)
         text.pop("architectures", None)
         return {

@@ -217,3 +217,49 @@ def test_upcycling_recipe(tmp_path, monkeypatch):
                    "optimizer.learning_rate.decay_iterations=2", "optimizer.learning_rate.warmup_iterations=1", *_CPU])
     saved = yaml.safe_load((tmp_path / "upcycled_run/checkpoint/2/metadata.yaml").read_text())
     assert "experts: 4" in yaml.safe_dump(saved)
+
+
+def test_multimodal_recipe(tmp_path, monkeypatch):
+    """docs/recipes/multimodal.md: a dataset with an Image feature (rows with zero, one and two pictures of two sizes) is
+    prepared into patches, a tiny vision-language model trains on it, and the Llava export loads in `transformers`."""
+    import datasets
+    import numpy as np
+    import PIL.Image
+    import transformers
+
+    from fast_llm_b200.cli import fast_llm_main
+
+    monkeypatch.chdir(tmp_path)
+    lines = ["the quick brown fox", "jumps over the lazy dog", "hello world", "this is a test"]
+    _tiny_tokenizer(tmp_path / "tokenizer", lines * 10)
+    rng = np.random.RandomState(0)
+    rows = {"text": [], "images": [], "positions": []}
+    for i in range(40):
+        count = i % 3
+        rows["text"].append(f"{lines[i % 4]} and {lines[(i + 1) % 4]} {i}")
+        rows["images"].append([PIL.Image.fromarray(rng.randint(0, 256, size=(8 + 4 * (i % 2), 12, 3)).astype(np.uint8)) for _ in range(count)])
+        rows["positions"].append([3 + 5 * k for k in range(count)])
+    features = datasets.Features({"text": datasets.Value("string"), "images": datasets.Sequence(datasets.Image()),
+                                  "positions": datasets.Sequence(datasets.Value("int32"))})
+    datasets.Dataset.from_dict(rows, features=features).save_to_disk(str(tmp_path / "raw"))
+
+    prepare = _doc_block("recipes/multimodal.md", 0)
+    prepare["dataset"]["path"] = "raw"
+    prepare.update(output_path="captions", tokenizer={"path": "tokenizer"}, num_workers=1, documents_per_shard=16)
+    prepare["image_patches"].update(height=4, width=4, max_image_height=16, max_image_width=16, image_break_token=None, image_end_token=None)
+    (tmp_path / "prepare.yaml").write_text(yaml.safe_dump(prepare))
+    fast_llm_main(["prepare", "gpt_memmap", "-c", "prepare.yaml"])
+
+    train = _doc_block("recipes/multimodal.md", 1)
+    train["data"]["datasets"]["training"]["path"] = "captions/fast_llm_config.yaml"
+    (tmp_path / "train.yaml").write_text(yaml.safe_dump(train))
+    vision = "model.base_model.vision_encoder"
+    fast_llm_main(["train", "multimodal", "-c", "train.yaml", "training.train_iters=3", "training.checkpoint.interval=null", "training.export.interval=3",
+                   "data.micro_batch_size=96", "data.maximum_document_length=96", "optimizer.learning_rate.decay_iterations=3",
+                   "optimizer.learning_rate.warmup_iterations=1", "model.base_model.image_token_index=7", *_TINY,
+                   f"{vision}.hidden_size=32", f"{vision}.embeddings.patch_height=4", f"{vision}.embeddings.patch_width=4", f"{vision}.encoder.num_blocks=2",
+                   f"{vision}.encoder.block.mixer.heads=2", f"{vision}.encoder.block.mixer.head_groups=2", f"{vision}.encoder.block.mixer.head_size=16",
+                   f"{vision}.encoder.block.mlp.intermediate_size=64", f"{vision}.adapter.intermediate_size=32", *_CPU])
+    export = tmp_path / "runs/vlm/export/llava/3"
+    model, info = transformers.LlavaForConditionalGeneration.from_pretrained(str(export), torch_dtype=torch.float32, output_loading_info=True)
+    assert not info["missing_keys"] and not info["unexpected_keys"], info
