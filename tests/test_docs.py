@@ -263,3 +263,53 @@ def test_multimodal_recipe(tmp_path, monkeypatch):
     export = tmp_path / "runs/vlm/export/llava/3"
     model, info = transformers.LlavaForConditionalGeneration.from_pretrained(str(export), torch_dtype=torch.float32, output_loading_info=True)
     assert not info["missing_keys"] and not info["unexpected_keys"], info
+
+
+def test_reference_model_flows(tmp_path, monkeypatch):
+    """Losses that need a frozen reference model, driven from the command line as docs/recipes/train.md and
+    instruction-finetuning.md describe them: distillation from a teacher checkpoint, and DPO on prepared preference pairs
+    (policy and reference start equal, so the first loss is ln 2)."""
+    import math
+
+    from fast_llm_b200.cli import fast_llm_main
+
+    monkeypatch.chdir(tmp_path)
+    fast_llm_main(["train", "gpt", "run.experiment_dir=base", "training.train_iters=1", "training.export.interval=1", "training.export.format=llama",
+                   "data.datasets.training.type=random", "data.micro_batch_size=64", *_TINY, *_CPU])
+    teacher = str(tmp_path / "base/export/llama/1")
+
+    def losses(run: str, name: str) -> list[float]:
+        logs = "".join(p.read_text() for p in (tmp_path / run / "runs/0/logs").glob("*.txt"))
+        return [float(v) for v in re.findall(rf"training iteration .*\| {name}: ([0-9.]+)", logs)]
+
+    distill = {"run": {"experiment_dir": "distill"}, "training": {"train_iters": 3},
+               "reference_models": {"teacher": {"pretrained": {"path": teacher, "format": "llama"}}},
+               "data": {"datasets": {"training": {"type": "random"}}, "micro_batch_size": 64},
+               "model": {"base_model": {"head": {"losses": {"lm": {"type": "label", "weight": 0.5},
+                                                            "distill": {"type": "distillation", "reference_model": "teacher", "weight": 0.5}}}}}}
+    (tmp_path / "distill.yaml").write_text(yaml.safe_dump(distill))
+    fast_llm_main(["train", "gpt", "-c", "distill.yaml", *_TINY, *_CPU])
+    assert len(losses("distill", "distill")) == 3 and len(losses("distill", "lm")) == 3
+
+    lines = ["the quick brown fox", "jumps over the lazy dog", "hello world", "this is a test"]
+    _tiny_tokenizer(tmp_path / "tokenizer", lines * 10)
+    rows = []
+    for i in range(60):
+        prompt, chosen, rejected = f"{lines[i % 4]} {i} : ", lines[(i + 1) % 4], lines[(i + 2) % 4]
+        rows.append({"text": prompt + chosen + rejected, "chosen": [len(prompt), len(prompt) + len(chosen)],
+                     "rejected": [len(prompt) + len(chosen), len(prompt) + len(chosen) + len(rejected)]})
+    (tmp_path / "prefs.jsonl").write_text("\n".join(json.dumps(r) for r in rows))
+    prepare = {"output_path": "prefs", "tokenizer": {"path": "tokenizer"},
+               "dataset": {"path": "json", "data_files": "prefs.jsonl",
+                           "source_schema": {"type": "document", "text": "text", "chosen_span": "chosen", "rejected_span": "rejected"}}}
+    (tmp_path / "prepare.yaml").write_text(yaml.safe_dump(prepare))
+    fast_llm_main(["prepare", "gpt_memmap", "-c", "prepare.yaml"])
+    dpo = {"run": {"experiment_dir": "dpo"}, "training": {"train_iters": 3}, "pretrained": {"path": teacher, "format": "llama"},
+           "reference_models": {"reference": {"pretrained": {"path": teacher, "format": "llama"}}},
+           "data": {"datasets": {"training": {"type": "file", "path": "prefs/fast_llm_config.yaml"}}, "micro_batch_size": 64,
+                    "maximum_document_length": 64, "truncate_documents": False},
+           "model": {"base_model": {"head": {"losses": {"dpo": {"type": "dpo", "beta": 0.1, "reference_model": "reference"}}}}}}
+    (tmp_path / "dpo.yaml").write_text(yaml.safe_dump(dpo))
+    fast_llm_main(["train", "gpt", "-c", "dpo.yaml", *_CPU])
+    values = losses("dpo", "dpo")
+    assert len(values) == 3 and values[0] == pytest.approx(math.log(2), abs=1e-4) and values[-1] < values[0]
