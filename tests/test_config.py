@@ -134,3 +134,42 @@ def test_cli_validate_only(tmp_path):
     config = fast_llm_main(["train", "gpt", "-v", "-c", str(root / "examples" / "tiny_llama.yaml"), "training.train_iters=3",
                             "model.base_model.decoder.block.mixer.heads=4"])
     assert config.training.train_iters == 3 and config.model.base_model.decoder.block.mixer.heads == 4
+
+
+def test_hydra_style_composition_and_override_grammar(tmp_path):
+    """`--hydra-path DIR --hydra-config NAME`: the base file's `defaults` list pulls in group files under their group's key, a
+    group is re-selected on the command line, and the override grammar (`k=v` existing key, `+k=v` new key, `++k=v` either,
+    `~k` delete) applies to the composed dictionary."""
+    import yaml
+
+    from fast_llm_b200.cli import fast_llm_main
+    from fast_llm_b200.config.compose import apply_overrides, compose_config
+
+    conf = tmp_path / "conf"
+    (conf / "model").mkdir(parents=True)
+    (conf / "data").mkdir()
+    (conf / "base.yaml").write_text(yaml.safe_dump({"defaults": [{"model": "tiny"}, {"data": "random"}, "_self_"],
+                                                    "training": {"train_iters": 2, "num_workers": 0}}))
+    block = {"mixer": {"type": "attention", "heads": 4, "head_groups": 2, "head_size": 8}, "mlp": {"intermediate_size": 64}}
+    distributed = {"compute_dtype": "float32", "use_cuda": False}
+    (conf / "model/tiny.yaml").write_text(yaml.safe_dump({"base_model": {"hidden_size": 32, "decoder": {"num_blocks": 2, "block": block}}, "distributed": distributed}))
+    (conf / "model/wide.yaml").write_text(yaml.safe_dump({"base_model": {"hidden_size": 64, "decoder": {"num_blocks": 1, "block": block}}, "distributed": distributed}))
+    (conf / "data/random.yaml").write_text(yaml.safe_dump({"datasets": {"training": {"type": "random"}}, "micro_batch_size": 64}))
+
+    composed, remaining = compose_config(conf, "base", {}, ["model=wide", "training.train_iters=3"])
+    assert composed["model"]["base_model"]["hidden_size"] == 64 and composed["data"]["micro_batch_size"] == 64 and remaining == ["training.train_iters=3"]
+    (conf / "optimizer").mkdir()
+    with pytest.raises(ValueError):
+        compose_config(conf, "base", {}, ["optimizer=adam"])  # a group that no defaults list mentions
+
+    config = fast_llm_main(["train", "gpt", "-v", "--hydra-path", str(conf), "--hydra-config", "base", "model=wide", "training.train_iters=3",
+                            "+optimizer.weight_decay=0.0", "~training.num_workers"])
+    assert config.model.base_model.hidden_size == 64 and config.training.train_iters == 3 and config.optimizer.weight_decay == 0.0
+    assert config.training.num_workers == 2  # deleted from the composed dictionary: the class default again
+
+    data = {"a": {"b": 1}}
+    assert apply_overrides(data, ["a.b=2", "+a.c=3", "++a.d.e=4", "~a.b"]) == {"a": {"c": 3, "d": {"e": 4}}}
+    with pytest.raises(KeyError):
+        apply_overrides({"a": {}}, ["a.x=1"])  # changing a key that does not exist needs `+`
+    with pytest.raises(KeyError):
+        apply_overrides({"a": {}}, ["~a.x"])
