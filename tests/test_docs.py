@@ -313,3 +313,18 @@ def test_reference_model_flows(tmp_path, monkeypatch):
     fast_llm_main(["train", "gpt", "-c", "dpo.yaml", *_CPU])
     values = losses("dpo", "dpo")
     assert len(values) == 3 and values[0] == pytest.approx(math.log(2), abs=1e-4) and values[-1] < values[0]
+
+
+def test_configuration_reference_is_current(tmp_path):
+    """`docs/reference/configuration` is what `tools/generate_config_docs` writes from the classes as they are now."""
+    import fast_llm_b200.models.auto  # noqa: F401
+    from fast_llm_b200.tools import checkpoint_surgery, push_model  # noqa: F401  (their configs are part of the reference)
+    from fast_llm_b200.tools.generate_config_docs import generate
+
+    generate(tmp_path)
+    committed = DOCS / "reference" / "configuration"
+    fresh = {p.relative_to(tmp_path): p.read_text() for p in tmp_path.rglob("*.md")}
+    current = {p.relative_to(committed): p.read_text() for p in committed.rglob("*.md")}
+    assert sorted(fresh) == sorted(current), "pages added or removed: run python -m fast_llm_b200.tools.generate_config_docs"
+    stale = [str(name) for name in fresh if fresh[name] != current[name]]
+    assert not stale, f"stale pages (run python -m fast_llm_b200.tools.generate_config_docs): {stale[:10]}"
