@@ -159,6 +159,7 @@ class LlavaHybridSSMHuggingfaceCheckpointHandler(LlavaHuggingfaceCheckpointHandl
     @classmethod
     def export_config(cls, c) -> dict:
         out = super().export_config(c)
+        out["model_type"] = "llava_hybrid"  # the type of `LlavaHybridConfig`, which `auto_map` resolves
         out["text_config"].pop("auto_map", None)
         out["auto_map"] = {"AutoConfig": "configuration_llava_hybrid.LlavaHybridConfig", "AutoModel": "modeling_llava_hybrid.LlavaHybridModel",
                            "AutoModelForCausalLM": "modeling_llava_hybrid.LlavaHybridForConditionalGeneration",

@@ -304,3 +304,44 @@ def test_apriel2_multimodal_modeling_code_loads_the_export_and_reproduces_the_lo
         uncached = external.generate(with_image[None, :30], pixel_values=padded, image_sizes=[(8, 12), (4, 8)], max_new_tokens=5, do_sample=False,
                                      use_cache=False)
     assert torch.equal(cached, uncached)
+
+
+def test_auto_classes_load_custom_exports_with_remote_code(tmp_path, monkeypatch):
+    """What a user of an exported checkpoint does: `transformers.AutoModelForCausalLM.from_pretrained(path, trust_remote_code=True)`
+    resolves `auto_map` to the modelling files shipped in the directory (copied into the dynamic-module cache and imported from
+    there, with their relative imports), for the text-only and the multimodal custom architectures; `model_type` in the exported
+    `config.json` is the type of the configuration class that loads it."""
+    import json
+
+    import transformers
+    import transformers.dynamic_module_utils
+
+    from fast_llm_b200.engine.checkpoint.config import CheckpointSaveConfig
+    from tests.common import tiny_trainer_config
+
+    monkeypatch.setattr(transformers.dynamic_module_utils, "HF_MODULES_CACHE", str(tmp_path / "modules"))
+    block = copy.deepcopy(TINY_BASE_MODEL["decoder"]["block"])
+    mamba = copy.deepcopy(block)
+    mamba["mixer"] = {"type": "mamba", "d_inner": 64, "d_xb": 32, "state_size": 8, "dt_rank": 4, "add_linear_biases": False,
+                      "convolution_layer": {"bias": {"enabled": True}}, "dt_layer": {"bias": {"enabled": True}}}
+    hybrid_decoder = {"type": "pattern", "blocks": {"t": block, "m2": mamba}, "pattern": ["t", "m2"], "num_blocks": 2}
+    hybrid = copy.deepcopy(TINY_BASE_MODEL)
+    hybrid["decoder"] = hybrid_decoder
+    cases = [
+        ("apriel2_text", tiny_trainer_config({("model", "base_model"): hybrid}), "Apriel2ForCausalLM", "apriel2_text"),
+        ("apriel_hybrid_ssm", tiny_trainer_config({("model", "base_model"): hybrid}), "AprielHybridSSMForCausalLM", "apriel_ssm_thinker_hybrid"),
+        ("apriel2", _config({("model", "base_model", "image_token_index"): 7}), "Apriel2ForConditionalGeneration", "apriel2"),
+        ("llava_hybrid_ssm", _config({("model", "base_model", "image_token_index"): 7, ("model", "base_model", "decoder"): hybrid_decoder,
+                                      ("model", "base_model", "vision_encoder", "adapter", "intermediate_size"): 64}),
+         "LlavaHybridForConditionalGeneration", "llava_hybrid"),
+    ]
+    for format_name, config, class_name, model_type in cases:
+        trainer, _ = build_trainer(config)
+        path = tmp_path / format_name
+        trainer.multi_stage.save_checkpoint(CheckpointSaveConfig(path=path, format=format_name))
+        assert json.loads((path / "config.json").read_text())["model_type"] == model_type
+        model = transformers.AutoModelForCausalLM.from_pretrained(str(path), trust_remote_code=True, dtype=torch.float32)
+        assert type(model).__name__ == class_name and type(model).__module__.startswith("transformers_modules"), format_name
+        assert type(model.config).model_type == model_type
+        tokens = torch.randint(8, 512, (1, 9))
+        assert model.generate(tokens, max_new_tokens=2, do_sample=False).shape == (1, 11), format_name
