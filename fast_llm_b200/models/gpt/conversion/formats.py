@@ -314,14 +314,21 @@ class Qwen2HuggingfaceCheckpointHandler(LlamaHuggingfaceCheckpointHandler):
         out["use_sliding_window"] = mixer.window_size is not None
         if mixer.window_size is not None:
             out["sliding_window"] = mixer.window_size
+            out["max_window_layers"] = 0  # every layer uses the window (Hugging Face keeps full attention below this layer index)
         out.pop("mlp_bias", None)
 
     @classmethod
     def _import_attention_extra(cls, h, mixer):
         mixer["add_linear_biases"] = True
         mixer["dense_layer"] = {"bias": {"enabled": False}}
-        if h.get("use_sliding_window") and h.get("sliding_window") is not None:
-            mixer["window_size"] = h["sliding_window"]
+        window = h.get("sliding_window")  # always read: the key is present (and inert) when `use_sliding_window` is off
+        if h.get("use_sliding_window") and window is not None:
+            # layers below `max_window_layers` attend to everything, the others through the window
+            full_layers = min(h.get("max_window_layers") or 0, h["num_hidden_layers"])
+            if full_layers == 0:
+                mixer["window_size"] = window
+            elif full_layers < h["num_hidden_layers"]:
+                raise NotImplementedError(f"Qwen2 with a sliding window on layers {full_layers}.. only: import it as a pattern decoder")
 
 
 class MixtralHuggingfaceCheckpointHandler(MistralHuggingfaceCheckpointHandler):
@@ -338,11 +345,15 @@ class MixtralHuggingfaceCheckpointHandler(MistralHuggingfaceCheckpointHandler):
         out["num_local_experts"] = mlp.experts
         out["num_experts_per_tok"] = mlp.experts_per_token
         out["router_aux_loss_coef"] = mlp.auxiliary_loss_coefficient
+        out["router_jitter_noise"] = mlp.jitter_eps
+
+    # `output_router_logits` asks the Hugging Face model to return router logits: a run-time switch, not architecture
+    ignored_import_keys = MistralHuggingfaceCheckpointHandler.ignored_import_keys | {"output_router_logits"}
 
     @classmethod
     def _import_mlp_extra(cls, h, mlp):
         mlp.update(type="moe", experts=h["num_local_experts"], experts_per_token=h["num_experts_per_tok"],
-                   auxiliary_loss_coefficient=h.get("router_aux_loss_coef", 0.01))
+                   auxiliary_loss_coefficient=h.get("router_aux_loss_coef", 0.01), jitter_eps=h.get("router_jitter_noise", 0.0))
 
     @classmethod
     def _mlp_converters(cls, mlp, ours, theirs):

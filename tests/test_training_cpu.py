@@ -646,3 +646,49 @@ def test_lora_model_exports_merged_weights_and_imports_a_plain_checkpoint(tmp_pa
     loaded = {n: t for n, _, t in again.get_state_tensor_iterator(("weights",))}
     assert float(loaded["decoder.0.mixer.query.lora_b_weight"].abs().max()) == 0 and float(loaded["decoder.0.mixer.query.lora_a_weight"].abs().max()) > 0
     torch.testing.assert_close(logits(again), expected, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("format_name,window", [("mistral", 6), ("qwen2", 6), ("qwen2", None)])
+def test_sliding_window_exports_match_transformers(tmp_path, format_name, window):
+    """A window shorter than the sequence: the exported `config.json` must make `transformers` apply it on every layer
+    (Qwen2 keeps full attention below `max_window_layers`, so the export says 0), and both sides give the same logits.
+    Default Hugging Face configurations of the formats import without an unread key."""
+    import copy
+
+    transformers = pytest.importorskip("transformers")
+    from fast_llm_b200.engine.checkpoint.config import CheckpointSaveConfig
+    from fast_llm_b200.engine.inference.runner import InferenceRunner
+    from fast_llm_b200.models.gpt.config import GPTModelConfig
+    from tests.common import TINY_BASE_MODEL
+
+    base = copy.deepcopy(TINY_BASE_MODEL)
+    mixer = base["decoder"]["block"]["mixer"]
+    if window is not None:
+        mixer["window_size"] = window
+    if format_name == "qwen2":
+        mixer.update(add_linear_biases=True, dense_layer={"bias": {"enabled": False}})
+    trainer, _ = build_trainer(tiny_trainer_config({("model", "base_model"): base}))
+    path = tmp_path / format_name
+    trainer.multi_stage.save_checkpoint(CheckpointSaveConfig(path=path, format=format_name))
+    hf = transformers.AutoModelForCausalLM.from_pretrained(path, dtype=torch.float32, attn_implementation="eager")
+    tokens = torch.randint(0, 512, (1, 24))
+    with torch.no_grad():
+        expected = hf(tokens).logits[0]
+    runner = InferenceRunner(trainer.multi_stage)
+    runner.setup()
+    torch.testing.assert_close(runner.forward_tokens(tokens[0]), expected, rtol=2e-4, atol=2e-4)
+    if window is not None:
+        exported = json.loads((path / "config.json").read_text())
+        assert exported["sliding_window"] == window and exported.get("max_window_layers", 0) == 0
+    defaults = {"mistral": transformers.MistralConfig(), "qwen2": transformers.Qwen2Config()}[format_name]
+    _, unread = GPTModelConfig.get_checkpoint_handler_class(format_name).check_import_coverage(json.loads(defaults.to_json_string()))
+    assert unread == []
+
+
+def test_mixtral_default_configuration_imports_without_unread_keys():
+    transformers = pytest.importorskip("transformers")
+    from fast_llm_b200.models.gpt.config import GPTModelConfig
+
+    config = json.loads(transformers.MixtralConfig(router_jitter_noise=0.02).to_json_string())
+    base, unread = GPTModelConfig.get_checkpoint_handler_class("mixtral").check_import_coverage(config)
+    assert unread == [] and base["decoder"]["block"]["mlp"]["jitter_eps"] == 0.02
