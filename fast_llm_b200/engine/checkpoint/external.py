@@ -343,7 +343,9 @@ class HuggingfaceStateDictCheckpointHandler(ExternalStateDictCheckpointHandler):
         tracked = TrackedConfig(hf_config)
         base_model = cls.import_config(tracked)
         ignored = _BOOKKEEPING_KEYS | cls.ignored_import_keys
-        unclaimed = [key for key in tracked.unread() if key.split(".")[0] not in ignored and key not in ignored]
+        # nested configurations (`text_config`, `vision_config`) carry the same bookkeeping keys as the top level
+        unclaimed = [key for key in tracked.unread()
+                     if key.split(".")[0] not in ignored and key not in ignored and key.split(".")[-1] not in _BOOKKEEPING_KEYS]
         return _plain(base_model), unclaimed
 
     @classmethod

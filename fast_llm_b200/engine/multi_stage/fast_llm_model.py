@@ -53,6 +53,8 @@ class FastLLMModel(MultiStageModel):
     def from_pretrained(cls, pretrained_config: CheckpointLoadConfig, *updates, optimizer_state_names: tuple[str, ...] | None = None,
                         setup: bool = True, mode: StageMode = StageMode.training, use_cpu: bool = False,
                         stage_filter: set | None = None, distributed: Distributed | None = None) -> typing.Self:
+        import fast_llm_b200.models.auto  # noqa: F401  (fills the registries: mixers, formats, datasets; the command line does the same)
+
         pretrained_config.validate()
         pretrained_config.setup(cls.config_class)
         metadata = cls.config_class.load_metadata(pretrained_config)

@@ -51,6 +51,8 @@ class PatchEmbeddingWeightConverter(WeightConverter):
 class LlavaHuggingfaceCheckpointHandler(HuggingfaceStateDictCheckpointHandler):
     format = LlavaCheckpointFormat
     architecture = "LlavaForConditionalGeneration"
+    # the number of placeholder tokens per image and the largest image are properties of the processor / the data
+    ignored_import_keys = frozenset({"image_seq_length", "vision_config.image_size"})
     text_handler = MistralHuggingfaceCheckpointHandler
 
     @classmethod
@@ -90,6 +92,16 @@ class LlavaHuggingfaceCheckpointHandler(HuggingfaceStateDictCheckpointHandler):
     def import_config(cls, h: dict) -> dict:
         out = cls.text_handler.import_config(h["text_config"])
         v = h["vision_config"]
+        # what this model implements of Llava: features of the last vision layer, every patch, untied output weights, RGB
+        layer, strategy = h.get("vision_feature_layer", -1), h.get("vision_feature_select_strategy", "full")
+        if layer not in (-1, v["num_hidden_layers"] - 1) or strategy != "full":
+            raise NotImplementedError(f"Llava with vision_feature_layer={layer}, vision_feature_select_strategy={strategy!r}")
+        Assert.eq(v.get("num_channels", 3), 3)
+        Assert.eq(v.get("attention_dropout", 0.0), 0.0)
+        if h.get("tie_word_embeddings"):
+            out["tied_embedding_weight"] = True
+        rope_kind = (v.get("rope_parameters") or {}).get("rope_type", "default")
+        Assert.eq(rope_kind, "default")
         heads = v["num_attention_heads"]
         head_size = v.get("head_dim") or div(v["hidden_size"], heads)
         norm = {"type": "rms_norm", "epsilon": 1e-5}
@@ -111,6 +123,23 @@ class LlavaHuggingfaceCheckpointHandler(HuggingfaceStateDictCheckpointHandler):
         return out
 
     # ---- weights
+    @staticmethod
+    def _legacy_name(name: str) -> str:
+        """Llava files come in three spellings: the original one that this exporter writes and `transformers` still loads
+        (`vision_tower.*`, `multi_modal_projector.*`, `language_model.model.*`, `language_model.lm_head.*`); the in-memory
+        names of `transformers` >= 4.52 (`model.vision_tower.*`, `model.language_model.*`, `lm_head.*`); and what its
+        `save_pretrained` writes today (`model.language_model.model.*`, `language_model.lm_head.*`).  All map to the first."""
+        if name.startswith("lm_head."):
+            return f"language_model.{name}"
+        if name.startswith(("model.vision_tower.", "model.multi_modal_projector.", "model.language_model.")):
+            name = name[len("model."):]
+        if name.startswith("language_model.") and not name.startswith(("language_model.model.", "language_model.lm_head.")):
+            name = "language_model.model." + name[len("language_model."):]
+        return name
+
+    def _import_tensors(self, name, tensor, pending):
+        return super()._import_tensors(self._legacy_name(name), tensor, pending)
+
     @classmethod
     def get_weight_converters(cls, c) -> list[WeightConverter]:
         vision = c.vision_encoder

@@ -345,3 +345,68 @@ def test_auto_classes_load_custom_exports_with_remote_code(tmp_path, monkeypatch
         assert type(model.config).model_type == model_type
         tokens = torch.randint(8, 512, (1, 9))
         assert model.generate(tokens, max_new_tokens=2, do_sample=False).shape == (1, 11), format_name
+
+
+def test_llava_created_by_transformers_imports_and_gives_its_logits(tmp_path):
+    """The import direction: a Llava model (Pixtral vision tower, Mistral decoder) built and saved by `transformers` loads through
+    `format: auto`, whichever of the three key spellings the file uses, and gives `transformers`' logits for text and for text
+    with an image."""
+    import safetensors.torch
+    import transformers
+
+    from fast_llm_b200.data.document import LanguageModelBatch, LanguageModelDocument
+    from fast_llm_b200.engine.checkpoint.config import CheckpointLoadConfig
+    from fast_llm_b200.models.multimodal.conversion import LlavaHuggingfaceCheckpointHandler
+    from fast_llm_b200.models.multimodal.model import MultiModalModel
+    from fast_llm_b200.parallel.topology import PhaseType
+
+    text = transformers.MistralConfig(vocab_size=320, hidden_size=48, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                                      num_key_value_heads=2, head_dim=12, sliding_window=None)
+    vision = transformers.PixtralVisionConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2, head_dim=16,
+                                              patch_size=4, image_size=16, num_channels=3)
+    config = transformers.LlavaConfig(vision_config=vision, text_config=text, image_token_index=7, projector_hidden_act="gelu",
+                                      vision_feature_layer=-1, vision_feature_select_strategy="full", multimodal_projector_bias=True)
+    torch.manual_seed(0)
+    hf = transformers.LlavaForConditionalGeneration(config).eval()
+    hf.save_pretrained(tmp_path / "saved", safe_serialization=True)
+    # the same weights under the in-memory names of recent `transformers` (`model.language_model.*`, `lm_head.*`)
+    (tmp_path / "in_memory_names").mkdir()
+    safetensors.torch.save_file({k: v.contiguous() for k, v in hf.state_dict().items()}, str(tmp_path / "in_memory_names/model.safetensors"),
+                                metadata={"format": "pt"})
+    (tmp_path / "in_memory_names/config.json").write_text((tmp_path / "saved/config.json").read_text())
+    assert {LlavaHuggingfaceCheckpointHandler._legacy_name(k) for k in hf.state_dict()} == \
+        {LlavaHuggingfaceCheckpointHandler._legacy_name(k) for k in safetensors.torch.load_file(str(tmp_path / "saved/model.safetensors"))}
+
+    tokens = torch.randint(8, 320, (41,))
+    pixels = torch.randint(0, 256, (3, 8, 12), dtype=torch.uint8)
+    patches = pixels.view(3, 2, 4, 3, 4).permute(1, 3, 0, 2, 4).reshape(6, 3, 4, 4)
+    coordinates = torch.tensor([[r, c] for r in range(2) for c in range(3)])
+    positions = torch.arange(5, 11)
+    with_image = tokens.clone()
+    with_image[positions] = 7
+    masked = with_image.clone()
+    masked[positions] = -100
+    for directory in ("saved", "in_memory_names"):
+        model = MultiModalModel.from_pretrained(CheckpointLoadConfig(path=tmp_path / directory, format="auto"), use_cpu=True)
+        base = model.base_model
+        for stage in model.stages:
+            stage.restore_parameters()
+
+        def ours(ids, **image):
+            batch = LanguageModelBatch.from_documents([LanguageModelDocument(tokens=ids, **image)], ids.numel())
+            (inputs, kwargs), = base.preprocess_batch(batch.get_model_inputs(micro_batch_size=ids.numel() - 1), phase=PhaseType.inference, iteration=0)
+            kwargs["return_logits"] = True
+            hidden = None
+            with torch.no_grad():
+                for layer in base.get_layers():
+                    hidden = layer.forward(inputs if hidden is None else hidden, kwargs)
+            return kwargs["logits"]
+
+        with torch.no_grad():
+            expected = hf(input_ids=tokens[None, :-1]).logits[0]
+        torch.testing.assert_close(ours(tokens), expected, rtol=2e-4, atol=2e-4)
+        image = model.config.base_model.vision_encoder.normalization.normalize(pixels[None])
+        with torch.no_grad():
+            expected = hf(input_ids=with_image[None, :-1], pixel_values=image, image_sizes=[(8, 12)]).logits[0]
+        mine = ours(masked, image_patches=patches, image_patch_positions=positions, image_patch_coordinates=coordinates)
+        torch.testing.assert_close(mine, expected, rtol=5e-4, atol=5e-4)
