@@ -692,3 +692,31 @@ def test_mixtral_default_configuration_imports_without_unread_keys():
     config = json.loads(transformers.MixtralConfig(router_jitter_noise=0.02).to_json_string())
     base, unread = GPTModelConfig.get_checkpoint_handler_class("mixtral").check_import_coverage(config)
     assert unread == [] and base["decoder"]["block"]["mlp"]["jitter_eps"] == 0.02
+
+
+@pytest.mark.parametrize("head_groups", [4, 1], ids=["gpt2", "starcoder"])
+def test_absolute_position_architectures_train_and_generate(head_groups):
+    """The GPT-2 / StarCoder family: learned absolute positions instead of rotary, LayerNorm, a plain GELU MLP, biases everywhere,
+    tied embeddings, multi-query attention for StarCoder.  Trains, and generates through the key / value cache (the cached
+    steps take their absolute positions from the cache length) exactly as without it."""
+    from fast_llm_b200.engine.inference.huggingface import HuggingfaceGPTModelForCausalLM
+
+    base = {"embeddings": {"vocab_size": 512, "position_embeddings": {"enabled": True}, "num_position_embeddings": 256},
+            "decoder": {"num_blocks": 2, "block": {
+                "mixer": {"type": "attention", "rotary": {"type": "none"}, "heads": 4, "head_groups": head_groups, "head_size": 16, "add_linear_biases": True},
+                "mlp": {"intermediate_size": 128, "gated": False, "activation": "gelu", "add_linear_biases": True},
+                "normalization": {"type": "layer_norm"}}},
+            "head": {"normalization": {"type": "layer_norm"}}, "hidden_size": 64, "tied_embedding_weight": True}
+    trainer, _ = build_trainer(tiny_trainer_config({("model", "base_model"): base}))
+    names = {n for n, _, _ in trainer.multi_stage.get_state_tensor_iterator(("weights",))}
+    assert "embeddings.position_embeddings_weight" in names and "decoder.0.mlp.layer_1.bias" in names and "decoder.0.norm_1.bias" in names
+    assert "head.output_weights" not in names
+    losses = train_steps(trainer, 4)
+    assert all(torch.isfinite(torch.tensor(losses)))
+    model = HuggingfaceGPTModelForCausalLM(trainer.multi_stage)
+    prompt = torch.randint(1, 512, (2, 7))
+    mask = torch.ones_like(prompt)
+    mask[1, :3] = 0
+    cached = model.generate(prompt * mask, attention_mask=mask, max_new_tokens=4, do_sample=False, pad_token_id=0)
+    plain = model.generate(prompt * mask, attention_mask=mask, max_new_tokens=4, do_sample=False, pad_token_id=0, use_cache=False)
+    assert torch.equal(cached, plain)
