@@ -219,3 +219,37 @@ def test_checkpoint_saved_in_one_layout_loads_in_another(saved, loaded, tmp_path
             assert (value == written[reference_key]).all(), f"{saved}->{loaded}: {key}"
             seen.add(reference_key)
     assert seen == set(written)
+
+
+def _load_external_rank(rank, world_size, model_updates, path):
+    from fast_llm_b200.engine.checkpoint.config import CheckpointLoadConfig
+    from fast_llm_b200.models.gpt.model import GPTModel
+
+    updates = {**model_updates, ("distributed", "world_size"): world_size, ("distributed", "rank"): rank,
+               ("distributed", "local_world_size"): world_size, ("distributed", "backend"): "gloo", ("distributed", "use_cuda"): False}
+    model = GPTModel.from_pretrained(CheckpointLoadConfig(path=path, format="llama"), updates, use_cpu=True)
+    state = {name: tensor.clone().numpy() for name, _, tensor in model.get_state_tensor_iterator(("weights",))}
+    model.distributed.shutdown()
+    return state
+
+
+@pytest.mark.parametrize("layout", ["tp2", "stp2", "pp2", "dp2_z3"])
+def test_hugging_face_checkpoint_loads_in_every_layout(layout, tmp_path):
+    """A Hugging Face checkpoint read by the ranks of a parallel layout: every rank fills its own shards from the global tensors
+    (a pipeline rank reports nothing for the stages it does not hold, which the completeness check must accept), and together
+    the ranks hold exactly the weights a single process reads."""
+    from fast_llm_b200.engine.checkpoint.config import CheckpointLoadConfig, CheckpointSaveConfig
+    from fast_llm_b200.models.gpt.model import GPTModel
+
+    trainer, _ = build_trainer(tiny_trainer_config())
+    path = tmp_path / "hf"
+    trainer.multi_stage.save_checkpoint(CheckpointSaveConfig(path=path, format="llama"))
+    single = GPTModel.from_pretrained(CheckpointLoadConfig(path=path, format="llama"), use_cpu=True)
+    expected = {name: tensor.clone() for name, _, tensor in single.get_state_tensor_iterator(("weights",))}
+    world, updates = _CROSS_LAYOUTS[layout]
+    seen = set()
+    for state in run_distributed(_load_external_rank, world, updates, str(path)):
+        for name, value in state.items():
+            torch.testing.assert_close(torch.from_numpy(value), expected[name], rtol=0, atol=0, msg=lambda m: f"{layout} {name}: {m}")
+            seen.add(name)
+    assert seen == set(expected)
