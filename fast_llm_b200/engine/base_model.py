@@ -260,6 +260,11 @@ class BaseModel(LayerBase):
         """name -> metas that share one tensor (first is the owner)."""
         return {}
 
+    def get_activation_shape(self, layer_index: int, kwargs: dict) -> tuple[int, int] | None:
+        """Shape of the activation that enters layer `layer_index` on this rank, for pipeline transfers; None: the default
+        `[tokens (/ tensor ranks with sequence parallelism), hidden]`."""
+        return None
+
     def add_reference_model(self, name: str, inference_runner) -> None:
         assert name not in self._reference_models
         self._reference_models[name] = inference_runner

@@ -358,7 +358,11 @@ class ScheduleRunner:
                 context.data.pop(step.data_index, None)
 
     # ---- pipeline transfers (NCCL / Gloo point to point on the pipeline stream)
-    def _hidden_shape(self, kwargs) -> tuple[int, int]:
+    def _hidden_shape(self, kwargs, layer_index: int | None = None) -> tuple[int, int]:
+        if layer_index is not None:  # models whose layers do not all work on [tokens, hidden] (a vision encoder in front)
+            shape = self._multi_stage.base_model.get_activation_shape(layer_index, kwargs)
+            if shape is not None:
+                return tuple(shape)
         tokens = kwargs[BlockKwargs.num_tokens]
         dc = self._distributed_config
         if dc.sequence_tensor_parallel:
@@ -369,7 +373,9 @@ class ScheduleRunner:
         """Post the receive of `target`'s input (forward) or output gradient (backward) on the pipeline stream, into a buffer
         that belongs to this step of the plan and is reused by every later optimizer step."""
         kwargs = self._get_data(context, target.data_index)[target.micro_sequence][1]
-        shape = self._hidden_shape(kwargs)
+        # forward: what enters the target stage; backward: the gradient of what leaves it (= what enters the next stage)
+        stage = self._multi_stage.stages[target.stage]
+        shape = self._hidden_shape(kwargs, stage._begin if target.type_ == StepType.forward else stage._end)
         dtype = self._distributed_config.compute_dtype.torch
         key = (id(context.schedule), target.type_, *target.key)
         buffer = self._recv_buffers.get(key)

@@ -23,7 +23,7 @@ from fast_llm_b200.ops.gemm import matmul_nn, matmul_nt
 from fast_llm_b200.ops.linear import weight_grad
 from fast_llm_b200.ops.pointwise import embedding
 from fast_llm_b200.parallel import fused_tp
-from fast_llm_b200.parallel.ops import gather_op, reduce_forward, reduce_op, reduce_scatter_op, split_op
+from fast_llm_b200.parallel.ops import gather, gather_op, reduce_forward, reduce_op, reduce_scatter_op, split_op
 from fast_llm_b200.parallel.topology import DistributedDimNames
 from fast_llm_b200.tensor import TensorDim
 from fast_llm_b200.utils import Assert, div
@@ -152,7 +152,15 @@ class LanguageModelEmbedding(Layer):
         if emb_map is not None:
             # multimodal: add encoder outputs (input_) at the mapped token positions
             src_index, dst_index = emb_map
-            out = out.index_add(0, dst_index, input_[src_index].to(out.dtype))
+            features = input_
+            if self._sequence_parallel and group is not None:
+                # every rank holds a share of the encoder outputs and a share of the tokens: gather the former (their
+                # gradients are summed back to the owners) and keep the pairs whose token lies in this rank's range
+                features = gather(features, group, 0, reduce_grads=True)
+                dst_index = dst_index - self._tp_dim.rank * out.shape[0]
+                local = (dst_index >= 0) & (dst_index < out.shape[0])
+                src_index, dst_index = src_index[local], dst_index[local]
+            out = out.index_add(0, dst_index, features[src_index].to(out.dtype))
         if c.dropout > 0 and kwargs.get("training", True):
             from fast_llm_b200.parallel.collectives import set_generator
 

@@ -78,6 +78,10 @@ class PatchEmbeddings(Layer):
 
     def forward(self, input_, kwargs, losses=None, metrics=None):
         patches = kwargs[VisionKwargs.patches]
+        dc = self._distributed_config
+        if dc.sequence_tensor_parallel and dc.tensor_parallel > 1:
+            # the layers that follow hold their rank's share of the patch sequence (the batch was padded to a multiple)
+            patches = patches.chunk(dc.tensor_parallel)[dc.tensor_rank]
         weight = self.patch_embeddings.weight
         flat = patches.flatten(1).to(weight.dtype if torch.is_tensor(weight) else patches.dtype)
         return self.normalization(self.patch_embeddings(flat)).to(self._residual_dtype)

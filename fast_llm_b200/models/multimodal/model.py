@@ -30,6 +30,21 @@ class MultiModalBaseModel(GPTBaseModel):
     def get_layers(self):
         return [*self._vision_layers, *super().get_layers()]
 
+    def _sequence_split(self) -> int:
+        """Ranks the patch sequence is split over between vision layers (sequence-tensor parallelism)."""
+        dc = self._distributed_config
+        return dc.tensor_parallel if dc.sequence_tensor_parallel else 1
+
+    def get_activation_shape(self, layer_index: int, kwargs: dict):
+        """Between vision layers the activation is `[patches, vision width]`; the adapter hands `[patches, hidden]` to the
+        embedding layer; from there on the default `[tokens, hidden]`."""
+        vision_layers = len(self._vision_layers)
+        if not 0 < layer_index <= vision_layers:
+            return None
+        patches = kwargs[VISION_NAMESPACE][BlockKwargs.num_tokens] // self._sequence_split()
+        width = self._config.vision_encoder.hidden_size if layer_index < vision_layers else self._hidden_dim.size
+        return (patches, width)
+
     def preprocess_batch(self, model_inputs, *, phase, iteration, metrics=None, device=None):
         device = device or (self._distributed.device if self._distributed is not None else "cpu")
         normalization = self._config.vision_encoder.normalization
@@ -55,6 +70,14 @@ class MultiModalBaseModel(GPTBaseModel):
                 starts = [0, *starts]
             bounds = [*starts, len(patches)]
             lengths = [b - a for a, b in zip(bounds[:-1], bounds[1:])]
+            real_patches = len(patches)
+            padding = -real_patches % self._sequence_split()
+            if padding:
+                # sequence parallelism splits the patch sequence evenly over the tensor ranks: blank patches that form an
+                # image of their own (nothing attends to them, no token takes their output) fill it up
+                patches = torch.cat([patches, patches.new_zeros((padding, *patches.shape[1:]))])
+                coordinates = torch.cat([coordinates, coordinates.new_zeros((padding, 2))])
+                lengths.append(padding)
             cu = torch.tensor([0, *torch.tensor(lengths, dtype=torch.int64).cumsum(0).tolist()] if lengths else [0, 0], dtype=torch.int32)
             extras[VISION_NAMESPACE] = {
                 VisionKwargs.patches: normalization.normalize(patches).to(compute_dtype),
@@ -63,7 +86,7 @@ class MultiModalBaseModel(GPTBaseModel):
                 BlockKwargs.max_seqlen_q: max(lengths, default=0), BlockKwargs.max_seqlen_k: max(lengths, default=0),
                 BlockKwargs.num_tokens: len(patches), "training": phase.is_training,
             }
-            extras[LanguageModelKwargs.embedding_map] = (torch.arange(len(patches)), token_positions.to(torch.int64))
+            extras[LanguageModelKwargs.embedding_map] = (torch.arange(real_patches), token_positions.to(torch.int64))
         out = super().preprocess_batch(model_inputs, phase=phase, iteration=iteration, metrics=metrics, device=device)
         for _, kwargs in out:
             vision = kwargs[VISION_NAMESPACE]

@@ -253,3 +253,56 @@ def test_hugging_face_checkpoint_loads_in_every_layout(layout, tmp_path):
             torch.testing.assert_close(torch.from_numpy(value), expected[name], rtol=0, atol=0, msg=lambda m: f"{layout} {name}: {m}")
             seen.add(name)
     assert seen == set(expected)
+
+
+def _multimodal_rank(rank, world_size, updates, steps):
+    from tests.test_multimodal import _config
+
+    updates = {**updates, ("model", "distributed", "world_size"): world_size, ("model", "distributed", "rank"): rank,
+               ("model", "distributed", "local_world_size"): world_size, ("model", "distributed", "backend"): "gloo",
+               ("model", "distributed", "reproducible_init"): True}
+    trainer, distributed = build_trainer(_config(updates))
+    losses = train_steps(trainer, steps)
+    weights = {n: t.clone().numpy() for n, _, t in trainer.multi_stage.get_state_tensor_iterator(("weights",))}
+    distributed.shutdown()
+    return losses, weights
+
+
+_MULTIMODAL_LAYOUTS = {
+    "tp2": (2, {("model", "distributed", "tensor_parallel"): 2}, {}),
+    # 3 images of 1 x 3 patches: 9 patches, padded to 10 for the two sequence-parallel ranks
+    "stp2_odd_patches": (2, {("model", "distributed", "tensor_parallel"): 2, ("model", "distributed", "sequence_tensor_parallel"): True,
+                             ("data", "datasets", "training", "image_patch_grid"): [1, 3]},
+                         {("data", "datasets", "training", "image_patch_grid"): [1, 3]}),
+    "pp2": (2, {("model", "distributed", "pipeline_parallel"): 2, ("schedule", "breadth_first_micro_batches"): 2},
+            {("schedule", "breadth_first_micro_batches"): 2}),
+    "stp2_pp2": (4, {("model", "distributed", "tensor_parallel"): 2, ("model", "distributed", "sequence_tensor_parallel"): True,
+                     ("model", "distributed", "pipeline_parallel"): 2, ("schedule", "breadth_first_micro_batches"): 2},
+                 {("schedule", "breadth_first_micro_batches"): 2}),
+}
+
+
+@pytest.mark.parametrize("name", list(_MULTIMODAL_LAYOUTS))
+def test_multimodal_layout_matches_single_process(name):
+    """The vision encoder under the parallel layouts: with sequence parallelism the patch sequence is split over the tensor
+    ranks (padded with blank patches to a multiple) and the embedding layer gathers the encoder outputs for its share of the
+    tokens; with pipeline parallelism the activations sent between vision stages are `[patches, vision width]`, not
+    `[tokens, hidden]`.  Losses and final weights equal the single-process run (the reference runs `llava` through the same
+    layouts: `tests/utils/model_configs.py:690-703`)."""
+    from tests.test_multimodal import _config
+
+    world_size, parallel_updates, single_updates = _MULTIMODAL_LAYOUTS[name]
+    common = {("model", "distributed", "reproducible_init"): True}
+    trainer, _ = build_trainer(_config({**common, **single_updates}))
+    reference_losses = train_steps(trainer, STEPS)
+    reference_weights = {n: t.clone() for n, _, t in trainer.multi_stage.get_state_tensor_iterator(("weights",))}
+    results = run_distributed(_multimodal_rank, world_size, {**common, **parallel_updates}, STEPS)
+    seen = set()
+    for losses, weights in results:
+        assert losses == pytest.approx(reference_losses, rel=2e-4), name
+        for key, value in weights.items():
+            # Adam divides by the root of the second moment: where a gradient is next to zero, a different summation order
+            # moves the update by a fraction of the learning rate (1e-3); a wrong gradient would move it by all of it
+            torch.testing.assert_close(torch.from_numpy(value), reference_weights[key], rtol=2e-3, atol=3e-4, msg=lambda m: f"{name} {key}: {m}")
+            seen.add(key)
+    assert seen == set(reference_weights)
