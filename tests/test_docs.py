@@ -328,3 +328,25 @@ def test_configuration_reference_is_current(tmp_path):
     assert sorted(fresh) == sorted(current), "pages added or removed: run python -m fast_llm_b200.tools.generate_config_docs"
     stale = [str(name) for name in fresh if fresh[name] != current[name]]
     assert not stale, f"stale pages (run python -m fast_llm_b200.tools.generate_config_docs): {stale[:10]}"
+
+
+@pytest.mark.parametrize("name", ["tiny_llama.yaml", "mistral.yaml"])
+def test_example_configurations_validate(name):
+    import fast_llm_b200.models.auto  # noqa: F401
+    from fast_llm_b200.models.gpt.trainer import GPTTrainerConfig
+
+    config = GPTTrainerConfig.from_dict(yaml.safe_load((DOCS.parent / "examples" / name).read_text()))
+    config.validate()
+    assert config.model.base_model.decoder.num_blocks >= 2
+
+
+def test_launch_examples_parse():
+    """The Slurm script is valid shell and the Kubeflow manifest valid YAML that starts the documented module."""
+    import subprocess
+
+    examples = DOCS.parent / "examples"
+    subprocess.run(["bash", "-n", str(examples / "slurm_train.sbatch")], check=True)
+    assert "fast_llm_b200.cli train gpt" in (examples / "slurm_train.sbatch").read_text()
+    job = yaml.safe_load((examples / "pytorchjob.yaml").read_text())
+    container = job["spec"]["pytorchReplicaSpecs"]["Worker"]["template"]["spec"]["containers"][0]
+    assert container["command"] == ["torchrun"] and "fast_llm_b200.cli" in container["args"]
