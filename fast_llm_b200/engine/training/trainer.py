@@ -131,7 +131,10 @@ class Trainer:
             done, metrics = True, {}
         if done and self._evaluators and not self._config.training.train_iters:
             for evaluator in self._evaluators.values():
-                metrics.update(evaluator.run(self._completed_steps, force=True) or {})
+                result = evaluator.run(self._completed_steps, force=True) or {}
+                metrics.update(result)
+                if result and getattr(self, "_wandb", None) is not None:
+                    self._wandb.log_metrics(self._completed_steps, result)
         self._final_metrics = metrics
 
     def _train(self, profiler) -> tuple[bool, dict]:
@@ -210,6 +213,9 @@ class Trainer:
                     result = evaluator.run(self._completed_steps, force=done)
                     if result:
                         metrics.update(result)
+                        wandb = getattr(self, "_wandb", None)
+                        if wandb is not None:  # evaluation results travel with the step they were measured at
+                            wandb.log_metrics(self._completed_steps, result)
                 if config.export.enabled(None if done else self._completed_steps):
                     self._save_checkpoint(config.export, metrics)
                 if interrupter.enabled:

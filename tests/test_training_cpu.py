@@ -720,3 +720,58 @@ def test_absolute_position_architectures_train_and_generate(head_groups):
     cached = model.generate(prompt * mask, attention_mask=mask, max_new_tokens=4, do_sample=False, pad_token_id=0)
     plain = model.generate(prompt * mask, attention_mask=mask, max_new_tokens=4, do_sample=False, pad_token_id=0, use_cache=False)
     assert torch.equal(cached, plain)
+
+
+def test_planned_shutdown_resume_and_wandb_logging(tmp_path):
+    """`training.shutdown` stops the run at its interval after saving a checkpoint; the next start resumes there and finishes.
+    With an entity configured the metrics of every logged step, evaluator results included, reach W&B (a stand-in module)."""
+    from fast_llm_b200.cli import fast_llm_main
+    from fast_llm_b200.engine.training import trainer as trainer_module
+
+    class FakeWandb:
+        def __init__(self):
+            self.inits, self.logs, self.alerts, self.finished = [], [], [], []
+
+        def Settings(self, **kwargs):
+            return kwargs
+
+        def init(self, **kwargs):
+            self.inits.append(kwargs)
+
+        def log(self, metrics, step=None, commit=True):
+            self.logs.append((step, metrics))
+
+        def alert(self, **kwargs):
+            self.alerts.append(kwargs)
+
+        def finish(self, exit_code=0):
+            self.finished.append(exit_code)
+
+    fake = FakeWandb()
+    arguments = ["train", "gpt", f"run.experiment_dir={tmp_path / 'run'}", "training.train_iters=4", "training.logs.interval=1", "training.num_workers=0",
+                 "training.checkpoint.interval=2", "training.shutdown.interval=2", "training.wandb.entity_name=team", "training.wandb.project_name=project",
+                 "training.evaluators.validation.type=loss", "training.evaluators.validation.interval=2", "training.evaluators.validation.iterations=1",
+                 "data.datasets.training.type=random", "data.datasets.validation.type=random", "data.micro_batch_size=64",
+                 "model.base_model.embeddings.vocab_size=300", "model.base_model.hidden_size=32", "model.base_model.decoder.num_blocks=1",
+                 "model.base_model.decoder.block.mixer.heads=4", "model.base_model.decoder.block.mixer.head_groups=2",
+                 "model.base_model.decoder.block.mixer.head_size=8", "model.base_model.decoder.block.mlp.intermediate_size=64",
+                 "model.distributed.compute_dtype=float32", "model.distributed.use_cuda=false"]
+    original = trainer_module.Trainer.run
+
+    def run_with_fake(self):
+        self._wandb_module = fake
+        return original(self)
+
+    trainer_module.Trainer.run = run_with_fake
+    try:
+        fast_llm_main(arguments)
+        assert (tmp_path / "run/checkpoint/2/ok").exists() and not (tmp_path / "run/checkpoint/4").exists()  # stopped at the planned point
+        fast_llm_main(arguments)
+    finally:
+        trainer_module.Trainer.run = original
+    assert (tmp_path / "run/checkpoint/4/ok").exists()
+    assert len(fake.inits) == 2 and fake.inits[0]["entity"] == "team" and fake.inits[0]["project"] == "project" and fake.finished == [0, 0]
+    steps = [step for step, _ in fake.logs]
+    assert sorted(set(steps)) == [1, 2, 3, 4]
+    keys = {key for _, metrics in fake.logs for key in metrics}
+    assert any(key.startswith("train") and "lm_loss" in key for key in keys) and any("validation" in key for key in keys), keys
