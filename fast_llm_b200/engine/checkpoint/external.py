@@ -139,7 +139,15 @@ class ExternalStateDictCheckpointHandler(StateDictCheckpointHandler):
                 self._export_converters[name] = c
         self._adapt_to_lora(model)
         self._import_converters = {name: c for c in converters for name in c.export_name}
-        missing = [n for n in model.parameter_names if n not in self._export_converters and n not in self._adapter_owner]
+        # A tied weight whose users sit on different pipeline ranks has a copy with a name of its own there (the output
+        # weights next to the embedding table).  The format holds the tensor once: the owner exports it, and an import
+        # hands the owner's tensor to the copy as well (every rank reads every file, so no message is needed).
+        self._tied_copies: dict[str, list[str]] = {}
+        for owner, copy_, _, _ in getattr(model, "_tied_remote", ()):
+            if copy_.tensor_name not in self._export_converters:
+                self._tied_copies.setdefault(owner.tensor_name, []).append(copy_.tensor_name)
+        copies = {name for names in self._tied_copies.values() for name in names}
+        missing = [n for n in model.parameter_names if n not in self._export_converters and n not in self._adapter_owner and n not in copies]
         unknown = [n for n in self._export_converters if n not in model.parameter_names]
         if missing or unknown:
             raise ValueError(f"{type(self).__name__}: converters do not cover the model: missing {missing[:8]}, unknown {unknown[:8]}")
@@ -207,6 +215,8 @@ class ExternalStateDictCheckpointHandler(StateDictCheckpointHandler):
         return ("weights",) if config.model_weights else ()
 
     def _export_tensors(self, parameter_name, shard_name, tensor, pending):
+        if any(parameter_name in names for names in self._tied_copies.values()):
+            return {}  # the owner of the tied weight writes it
         converter = self._export_converters.get(parameter_name) or self._adapter_owner[parameter_name]
         adapters = self._adapters.get(id(converter), ())
         slot = pending.setdefault(id(converter), {})
@@ -231,7 +241,10 @@ class ExternalStateDictCheckpointHandler(StateDictCheckpointHandler):
             return []
         del pending[id(converter)]
         imported = converter.import_weight(tuple(slot[n] for n in converter.export_name))
-        return [(n, "weights", t) for n, t in zip(converter.fast_llm_name, imported, strict=True)]
+        out = [(n, "weights", t) for n, t in zip(converter.fast_llm_name, imported, strict=True)]
+        for name, _, value in list(out):
+            out += [(copy_, "weights", value) for copy_ in self._tied_copies.get(name, ())]
+        return out
 
 
 class TrackedConfig(dict):

@@ -306,3 +306,50 @@ def test_multimodal_layout_matches_single_process(name):
             torch.testing.assert_close(torch.from_numpy(value), reference_weights[key], rtol=2e-3, atol=3e-4, msg=lambda m: f"{name} {key}: {m}")
             seen.add(key)
     assert seen == set(reference_weights)
+
+
+def _tied_pipeline_rank(rank, world_size, path_out, path_in):
+    """Train a model with tied embeddings on two pipeline ranks, export it as Llama; then load `path_in` (a Llama checkpoint)."""
+    from fast_llm_b200.engine.checkpoint.config import CheckpointLoadConfig, CheckpointSaveConfig
+
+    updates = {("model", "base_model", "tied_embedding_weight"): True, ("model", "distributed", "pipeline_parallel"): 2,
+               ("schedule", "breadth_first_micro_batches"): 2, ("model", "distributed", "world_size"): world_size,
+               ("model", "distributed", "rank"): rank, ("model", "distributed", "local_world_size"): world_size,
+               ("model", "distributed", "backend"): "gloo", ("model", "distributed", "reproducible_init"): True}
+    trainer, distributed = build_trainer(tiny_trainer_config(updates))
+    train_steps(trainer, 1)
+    trainer.multi_stage.save_checkpoint(CheckpointSaveConfig(path=path_out, format="llama"))
+    trainer.multi_stage.load_checkpoint(CheckpointLoadConfig(path=path_in, format="llama"))
+    state = {name: tensor.clone().numpy() for name, _, tensor in trainer.multi_stage.get_state_tensor_iterator(("weights",))}
+    distributed.shutdown()
+    return state
+
+
+def test_tied_embeddings_across_pipeline_ranks_in_hugging_face_formats(tmp_path):
+    """With the embedding table on the first pipeline rank and the output layer on the last, the last rank keeps a copy under the
+    name `head.output_weights`.  A Hugging Face checkpoint holds the tensor once: the export writes the owner's only (and
+    `transformers` ties it again), the import gives the same tensor to the owner and to the copy."""
+    import safetensors.torch
+    import transformers
+
+    from fast_llm_b200.engine.checkpoint.config import CheckpointSaveConfig
+
+    single, _ = build_trainer(tiny_trainer_config({("model", "base_model", "tied_embedding_weight"): True}))
+    single.multi_stage.save_checkpoint(CheckpointSaveConfig(path=tmp_path / "source", format="llama"))
+    source = {}
+    for file in (tmp_path / "source").glob("*.safetensors"):
+        source.update(safetensors.torch.load_file(str(file)))
+    assert "lm_head.weight" not in source
+    states = run_distributed(_tied_pipeline_rank, 2, str(tmp_path / "exported"), str(tmp_path / "source"))
+    exported = {}
+    for file in (tmp_path / "exported").glob("*.safetensors"):
+        exported.update(safetensors.torch.load_file(str(file)))
+    assert sorted(exported) == sorted(source)
+    hf = transformers.AutoModelForCausalLM.from_pretrained(tmp_path / "exported", dtype=torch.float32)
+    assert hf.lm_head.weight.data_ptr() == hf.model.embed_tokens.weight.data_ptr()
+    # after the import both holders have the checkpoint's embedding table
+    embedding = source["model.embed_tokens.weight"].float()
+    holders = {name: value for state in states for name, value in state.items() if name in ("embeddings.word_embeddings_weight", "head.output_weights")}
+    assert set(holders) == {"embeddings.word_embeddings_weight", "head.output_weights"}
+    for name, value in holders.items():
+        torch.testing.assert_close(torch.from_numpy(value), embedding, rtol=0, atol=0, msg=lambda m: f"{name}: {m}")
